@@ -1,0 +1,58 @@
+// Shared helpers for the sm_100a kernels: dtype conversion, reductions, launch-error reporting.
+//
+// Every host entry point is `extern "C"`, takes raw device pointers plus the CUDA stream to launch
+// on, allocates nothing, and returns a cudaError_t cast to int (0 = launched). The Python side
+// (tokenmill_b200/kernels/lib.py) turns a non-zero code into an exception.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TM_DTYPE_F32 0
+#define TM_DTYPE_BF16 1
+
+// Refusal codes returned before any launch (outside the cudaError range in use).
+#define TM_ERR_UNSUPPORTED_SHAPE 90001
+#define TM_ERR_BAD_DTYPE 90002
+#define TM_ERR_SCRATCH_TOO_SMALL 90003
+
+namespace tmk {
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum in a fixed order (lane tree, then warps 0..n-1 in turn): the result depends only
+// on the values and the block size, never on scheduling. `red` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarp; ++w) total += red[w];
+  return total;
+}
+
+inline int launch_status() { return static_cast<int>(cudaPeekAtLastError()); }
+
+}  // namespace tmk

@@ -1,0 +1,236 @@
+// Token selection from 32-bit logits, one block per row.
+//
+// Greedy: the index of the largest logit, the lowest index on ties (torch.argmax's rule, which the
+// reference uses: src/infer/sampling.py:30-33).
+// Random rows (src/infer/sampling.py:34-45): z = logits / temperature; optional top-k (keep the k
+// largest) and top-p (after top-k, drop a token once the probability mass of the tokens ranked before
+// it exceeds top_p; the best token always stays); softmax over what is kept; one draw. The draw is an
+// inverse-CDF walk over the vocabulary in index order with a uniform number u in [0, 1) the caller
+// supplies: the token is the first index whose running sum of kept weights exceeds u * total. The
+// reference draws with torch.multinomial from a per-request generator instead; the distribution is
+// the same, the stream of numbers is this engine's own. Where the reference sorts, this kernel
+// finds the two cut values by bisection on the float bit pattern, so tokens tied exactly at a cut
+// are all kept.
+#include "common.cuh"
+
+namespace tmk {
+
+constexpr int kSampleThreads = 1024;
+
+__device__ __forceinline__ unsigned int float_order_bits(float f) {
+  const unsigned int b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone: a < b  <=>  bits(a) < bits(b)
+}
+__device__ __forceinline__ float order_bits_float(unsigned int u) {
+  const unsigned int b = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+  return __uint_as_float(b);
+}
+
+__global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __restrict__ logits, int V,
+                                                               long long row_stride, int* __restrict__ out) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const float* row = logits + (size_t)blockIdx.x * row_stride;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sval[warp] = best;
+    sidx[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sval[lane] : -INFINITY;
+    bi = lane < nw ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+// Block-wide deterministic sum of one float per thread; every thread gets the total.
+__device__ __forceinline__ float block_total(float v, float* red) { return block_sum(v, red); }
+
+__device__ __forceinline__ int block_count(int v, int* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  int total = 0;
+  for (int w = 0; w < nwarp; ++w) total += red[w];
+  return total;
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(
+    const float* __restrict__ logits, int V, long long row_stride, const float* __restrict__ temperature,
+    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
+    int* __restrict__ out) {
+  __shared__ float redf[32];
+  __shared__ int redi[32];
+  __shared__ float warp_tot[32];
+  __shared__ int s_token;
+  const int rowi = blockIdx.x;
+  const float* row = logits + (size_t)rowi * row_stride;
+  const float inv_t = 1.0f / temperature[rowi];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+
+  // Row maximum of z = logit / T.
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, row[i] * inv_t);
+  mx = warp_max(mx);
+  __syncthreads();
+  if (lane == 0) redf[warp] = mx;
+  __syncthreads();
+  mx = -INFINITY;
+  for (int w = 0; w < nwarp; ++w) mx = fmaxf(mx, redf[w]);
+  __syncthreads();
+
+  // Cut value: keep z >= cut. Starts at "everything".
+  float cut = -INFINITY;
+  const int k = top_k[rowi];
+  if (k > 0 && k < V) {
+    // Largest value v with count(z >= v) >= k, by bisection on the ordered bit pattern.
+    // Invariant: count(z >= value(lo)) >= k. It holds at -inf (every finite z counts); starting below
+    // -inf would put NaN patterns, for which no comparison holds, inside the searched range.
+    unsigned int lo = float_order_bits(-INFINITY), hi = float_order_bits(mx);
+    while (lo < hi) {
+      const unsigned int mid = lo + ((hi - lo + 1u) >> 1);
+      const float v = order_bits_float(mid);
+      int c = 0;
+      for (int i = tid; i < V; i += blockDim.x) c += (row[i] * inv_t >= v) ? 1 : 0;
+      c = block_count(c, redi);
+      if (c >= k) lo = mid; else hi = mid - 1u;
+    }
+    cut = order_bits_float(lo);
+  }
+  const float tp = top_p[rowi];
+  if (tp < 1.0f) {
+    float zk = 0.f;
+    for (int i = tid; i < V; i += blockDim.x) {
+      const float zv = row[i] * inv_t;
+      zk += zv >= cut ? expf(zv - mx) : 0.f;
+    }
+    zk = block_total(zk, redf);
+    const float budget = tp * zk;
+    // Smallest x >= cut with mass(z > x) <= budget; kept = z >= x.
+    unsigned int lo = float_order_bits(cut), hi = float_order_bits(mx);  // predicate true at hi (mass 0)
+    while (lo < hi) {
+      const unsigned int mid = lo + ((hi - lo) >> 1);
+      const float x = order_bits_float(mid);
+      float mass = 0.f;
+      for (int i = tid; i < V; i += blockDim.x) {
+        const float zv = row[i] * inv_t;
+        mass += (zv > x && zv >= cut) ? expf(zv - mx) : 0.f;
+      }
+      mass = block_total(mass, redf);
+      if (mass <= budget) hi = mid; else lo = mid + 1u;
+    }
+    cut = fmaxf(cut, order_bits_float(lo));
+  }
+
+  // Inverse CDF in index order. Warp w owns the contiguous span [w * span, (w + 1) * span).
+  const int span = (V + nwarp - 1) / nwarp;
+  const int begin = warp * span, end = min(V, begin + span);
+  float part = 0.f;
+  for (int i = begin + lane; i < end; i += 32) {
+    const float zv = row[i] * inv_t;
+    part += zv >= cut ? expf(zv - mx) : 0.f;
+  }
+  part = warp_sum(part);
+  if (lane == 0) warp_tot[warp] = part;
+  if (tid == 0) s_token = -1;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarp; ++w) total += warp_tot[w];
+  const float target = uniform[rowi] * total;
+  float before = 0.f;
+  int owner = -1;
+  for (int w = 0; w < nwarp; ++w) {
+    if (target < before + warp_tot[w]) {
+      owner = w;
+      break;
+    }
+    before += warp_tot[w];
+  }
+  if (owner < 0) {  // u * total rounded up to the total: the last warp with any weight owns it
+    before = 0.f;
+    for (int w = 0; w < nwarp; ++w) {
+      if (warp_tot[w] > 0.f) owner = w;
+    }
+    for (int w = 0; w < owner; ++w) before += warp_tot[w];
+  }
+  if (warp == owner) {
+    float run = before;
+    int found = -1, last_kept = -1;
+    for (int base = begin; base < end && found < 0; base += 32) {
+      const int i = base + lane;
+      float wgt = 0.f;
+      if (i < end) {
+        const float zv = row[i] * inv_t;
+        wgt = zv >= cut ? expf(zv - mx) : 0.f;
+      }
+      float incl = wgt;  // inclusive scan over the 32 lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      const bool hit = wgt > 0.f && target < run + incl;
+      const unsigned int ballot = __ballot_sync(0xffffffffu, hit);
+      const unsigned int kept = __ballot_sync(0xffffffffu, wgt > 0.f);
+      if (kept) last_kept = base + (31 - __clz(kept));
+      if (ballot) found = base + (__ffs(ballot) - 1);
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_token = found >= 0 ? found : last_kept;
+  }
+  __syncthreads();
+  if (tid == 0) out[rowi] = s_token < 0 ? 0 : s_token;
+}
+
+}  // namespace tmk
+
+extern "C" int tm_argmax(const float* logits, int n_rows, int V, long long row_stride, int* out,
+                         cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (V <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  tmk::argmax_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, out);
+  return tmk::launch_status();
+}
+
+// temperature [n] (> 0), top_k [n] (<= 0 or >= V: off), top_p [n] (>= 1: off), uniform [n] in [0, 1).
+extern "C" int tm_sample(const float* logits, int n_rows, int V, long long row_stride, const float* temperature,
+                         const int* top_k, const float* top_p, const float* uniform, int* out,
+                         cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (V <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  tmk::sample_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, temperature, top_k, top_p,
+                                                              uniform, out);
+  return tmk::launch_status();
+}

@@ -1,0 +1,181 @@
+"""Tensor-level wrappers over the kernel entry points.
+
+Each wrapper checks what the kernel assumes (device, dtype, contiguity, shapes) and launches on the
+current CUDA stream. None of them has a fallback: a tensor on the CPU or a missing library raises.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import lib
+
+F32, BF16 = 0, 1
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise lib.KernelError(f"kernels run in float32 or bfloat16, got {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _req(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> int:
+    if not t.is_cuda:
+        raise lib.KernelError(f"{name} is on {t.device}; the kernels have no CPU path")
+    if not t.is_contiguous():
+        raise lib.KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise lib.KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _opt(t: torch.Tensor | None, name: str, dtype: torch.dtype | None = None) -> int | None:
+    return None if t is None else _req(t, name, dtype)
+
+
+def add_rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+                branch: torch.Tensor | None = None, partials: torch.Tensor | None = None,
+                ids: torch.Tensor | None = None, table: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+    """resid [T, H] float32 (updated in place unless ``rows``); out [n, H] in the activation dtype.
+    ids + table: the stream starts as table[ids]. branch [T, H]: added to the stream. partials
+    [n, T, H] float32: summed in index order and added. rows [n] int32: norm only these rows."""
+    H = resid.shape[-1]
+    n_rows = rows.numel() if rows is not None else resid.shape[0]
+    if out.shape[0] < n_rows or out.shape[-1] != H or weight.numel() != H:
+        raise lib.KernelError(f"add_rmsnorm: out {tuple(out.shape)} / weight {tuple(weight.shape)} do not fit "
+                              f"{n_rows} rows of width {H}")
+    if (ids is None) != (table is None):
+        raise lib.KernelError("add_rmsnorm: ids and table come together")
+    n_part, part_stride = 0, 0
+    if partials is not None:
+        n_part, part_stride = partials.shape[0], partials.stride(0)
+    dt = out.dtype
+    lib.call("tm_add_rmsnorm", _code(dt), _req(resid, "resid", torch.float32), _opt(branch, "branch", dt),
+             _opt(partials, "partials", torch.float32), n_part, part_stride, _opt(ids, "ids", torch.int32),
+             _opt(table, "table", dt), _opt(rows, "rows", torch.int32), _req(weight, "weight", torch.float32),
+             float(eps), _req(out, "out"), n_rows, H, _stream())
+    return out
+
+
+def qkv_rope_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, cos: torch.Tensor,
+                   sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
+                   kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, D: int) -> None:
+    """qkv [T, (nh + 2 nkv) D]; cos/sin [P, D/2] float32; q_out [T, nh, D]; caches [pages, page, nkv, D]."""
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * D or cos.shape[1] * 2 != D or positions.numel() < T:
+        raise lib.KernelError(f"qkv_rope_write: shapes do not fit (qkv {tuple(qkv.shape)}, nh {nh}, nkv {nkv}, D {D})")
+    if slot_map is not None and (kcache is None or vcache is None):
+        raise lib.KernelError("qkv_rope_write: a slot map needs both caches")
+    dt = q_out.dtype
+    lib.call("tm_qkv_rope_write", _code(qkv.dtype), _code(dt), _req(qkv, "qkv"), _opt(bias, "bias", torch.float32),
+             _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32),
+             _req(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out"),
+             _opt(kcache, "kcache", dt), _opt(vcache, "vcache", dt), T, nh, nkv, D, cos.shape[0], _stream())
+
+
+def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                    cu_q: torch.Tensor, kv_before: torch.Tensor, tile_seq: torch.Tensor, tile_row0: torch.Tensor,
+                    n_tiles: int, out: torch.Tensor, *, scale: float, window: int = 0, split_keys: int = 0,
+                    max_splits: int = 0, part_acc: torch.Tensor | None = None,
+                    part_ml: torch.Tensor | None = None, seq_of_token: torch.Tensor | None = None) -> torch.Tensor:
+    """q, out [T, nh, D]; caches [pages, page_size, nkv, D]; block_table [S, W] int32. With split_keys
+    the partial results go through part_acc / part_ml and are merged into out by a second launch."""
+    T, nh, D = q.shape
+    page_size, nkv = kcache.shape[1], kcache.shape[2]
+    if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
+        raise lib.KernelError("paged_attention: q / cache / out shapes disagree")
+    dt = q.dtype
+    if split_keys:
+        need = T * nh * max_splits
+        if part_acc is None or part_ml is None or seq_of_token is None or part_acc.numel() < need * D \
+                or part_ml.numel() < need * 2:
+            raise lib.KernelError("paged_attention: split mode needs part_acc, part_ml and seq_of_token of full size")
+    lib.call("tm_paged_attention", _code(dt), _req(q, "q"), _req(kcache, "kcache", dt), _req(vcache, "vcache", dt),
+             _req(block_table, "block_table", torch.int32), block_table.stride(0),
+             _req(cu_q, "cu_q", torch.int32), _req(kv_before, "kv_before", torch.int32),
+             _req(tile_seq, "tile_seq", torch.int32), _req(tile_row0, "tile_row0", torch.int32), n_tiles,
+             _req(out, "out", dt), _opt(part_acc, "part_acc", torch.float32), _opt(part_ml, "part_ml", torch.float32),
+             nh, nkv, D, page_size, float(scale), int(window), int(split_keys), int(max_splits), _stream())
+    if split_keys:
+        lib.call("tm_attention_combine", _code(dt), part_acc.data_ptr(), part_ml.data_ptr(), cu_q.data_ptr(),
+                 kv_before.data_ptr(), _req(seq_of_token, "seq_of_token", torch.int32), out.data_ptr(), T, nh, D,
+                 int(window), int(split_keys), int(max_splits), _stream())
+    return out
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """gu [T, 2 I] (gate columns first) -> out [T, I] = silu(gate) * up."""
+    T, two_i = gu.shape
+    if two_i % 2 or out.shape[0] < T or out.shape[1] * 2 != two_i:
+        raise lib.KernelError(f"swiglu: gu {tuple(gu.shape)} and out {tuple(out.shape)} do not fit")
+    lib.call("tm_swiglu", _code(gu.dtype), _req(gu, "gu"), _req(out, "out", gu.dtype), T, two_i // 2, _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
+           out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x [T, K] . w [N, K]^T -> [T, N].
+
+    float32: this library's own CUDA-core kernel (true 32-bit, k-ordered accumulation).
+    bfloat16: the library matrix product (cuBLAS through torch.mm), as the reference uses a library
+    for its projections (src/infer/model/layers.py:144,150,163,164); fp32 accumulation, output in
+    ``out_dtype`` (bfloat16 or float32)."""
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise lib.KernelError(f"linear: x {tuple(x.shape)} and w {tuple(w.shape)} do not fit")
+    if x.dtype == torch.float32:
+        if out is None:
+            out = torch.empty((T, N), dtype=torch.float32, device=x.device)
+        lib.call("tm_gemm_f32_nt", _req(x, "x", torch.float32), x.stride(0), _req(w, "w", torch.float32),
+                 _opt(bias, "bias", torch.float32), _req(out, "out", torch.float32), out.stride(0), T, N, K,
+                 _stream())
+        return out
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_cuda:
+        raise lib.KernelError(f"linear: unsupported operands {x.dtype} / {w.dtype} on {x.device}")
+    if bias is not None:
+        raise lib.KernelError("linear: the bfloat16 product takes no bias (it is added by the kernel that follows)")
+    want = out_dtype or (out.dtype if out is not None else torch.bfloat16)
+    if want == torch.float32:
+        res = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if out is not None:
+        return torch.mm(x, w.t(), out=out)
+    return torch.mm(x, w.t())
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """logits [n, V] float32 -> [n] int32, lowest index on ties."""
+    n, V = logits.shape
+    if logits.stride(1) != 1:
+        raise lib.KernelError("argmax: rows must be contiguous")
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    if not logits.is_cuda or logits.dtype != torch.float32:
+        raise lib.KernelError("argmax: float32 logits on the GPU")
+    lib.call("tm_argmax", logits.data_ptr(), n, V, logits.stride(0), _req(out, "out", torch.int32), _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One draw per row of logits [n, V] float32. temperature/top_p/uniform float32 [n], top_k int32 [n]."""
+    n, V = logits.shape
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise lib.KernelError("sample: float32 logits with contiguous rows on the GPU")
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    lib.call("tm_sample", logits.data_ptr(), n, V, logits.stride(0), _req(temperature, "temperature", torch.float32),
+             _req(top_k, "top_k", torch.int32), _req(top_p, "top_p", torch.float32),
+             _req(uniform, "uniform", torch.float32), _req(out, "out", torch.int32), _stream())
+    return out

@@ -1,0 +1,128 @@
+"""Grouped-query attention mixer over the paged cache.
+
+Order of operations (src/infer/model/layers.py:127-150, src/infer/kv/context.py:63-80): fused
+q/k/v projection with bias; rotate-half position encoding of q and k; the step's k and v are
+written to their cache slots BEFORE attention, so a prompt portion reads its own keys back from the
+cache; causal attention of every query over its own request's keys; output projection without bias.
+The projection weights are stored fused, rows [q; k; v], from the checkpoint's q_proj / k_proj /
+v_proj tensors (src/infer/model/loader.py:45,68-70,111-113).
+
+Every size and constant is a constructor parameter: head counts, head size, whether q/k/v carry a
+bias, the softmax scale, an optional window, and the position encoding (itself a part, looked up by
+kind). A window of w keys means a query at position p reads keys p-w+1..p.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..registry import get_part, register_mixer
+from .base import LayerCache, StepInputs
+from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
+
+SPLIT_KEYS = 256     # decode attention cuts each request's keys at absolute multiples of this
+
+
+class AttentionScratch:
+    """Scratch for split-key attention partials, sized once for the largest decode step."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.part_acc: torch.Tensor | None = None
+        self.part_ml: torch.Tensor | None = None
+        self.frozen = False      # set once a graph has captured the pointers
+
+    def reserve(self, rows: int, max_splits: int, head_dim: int) -> None:
+        need_acc, need_ml = rows * max_splits * head_dim, rows * max_splits * 2
+        if self.part_acc is None or self.part_acc.numel() < need_acc or self.part_ml.numel() < need_ml:
+            if self.frozen:
+                raise RuntimeError("attention scratch would have to grow after a graph captured it")
+            self.part_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
+            self.part_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
+
+    def get(self, rows: int, max_splits: int, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
+        self.reserve(rows, max_splits, head_dim)
+        return self.part_acc, self.part_ml
+
+
+class GroupedQueryAttention:
+    def __init__(self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, qkv_bias: bool,
+                 position: PartSpec | None, window: int | None = None, scale: float | None = None,
+                 dtype: torch.dtype, device: torch.device):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads ({num_heads}) must be a multiple of num_kv_heads ({num_kv_heads})")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim must be a multiple of 16 up to 256, got {head_dim}")
+        self.hidden_size, self.nh, self.nkv, self.D = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qkv_bias = bool(qkv_bias)
+        self.window = int(window) if window else 0
+        self.scale = float(scale) if scale is not None else head_dim ** -0.5
+        self.dtype, self.device = dtype, device
+        self.q_size, self.kv_size = num_heads * head_dim, num_kv_heads * head_dim
+        self.position = None
+        if position is not None:
+            self.position = get_part("position", position.kind)(**position.params)
+        self.w_qkv: torch.Tensor | None = None
+        self.b_qkv: torch.Tensor | None = None
+        self.w_o: torch.Tensor | None = None
+
+    # --- declarations ---------------------------------------------------------------------------
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H = self.hidden_size
+        specs = []
+        for name, rows in (("q_proj", self.q_size), ("k_proj", self.kv_size), ("v_proj", self.kv_size)):
+            specs.append(WeightSpec(f"{name}.weight", (rows, H)))
+            if self.qkv_bias:
+                specs.append(WeightSpec(f"{name}.bias", (rows,), dtype="float32"))
+        specs.append(WeightSpec("o_proj.weight", (H, self.q_size)))
+        return specs
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(self.nkv, self.D, self.window or None)
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
+                               dim=0).contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]],
+                                   dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"]
+        if self.position is not None:
+            self.cos, self.sin = self.position.tables(self.device)
+
+    # --- run ------------------------------------------------------------------------------------
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+        T = x.shape[0]
+        qkv = ops.linear(x, self.w_qkv)
+        q = torch.empty((T, self.nh, self.D), dtype=self.dtype, device=x.device)
+        slot_map = step.slot_maps[cache.group] if cache.writes else None
+        if self.position is None:
+            raise NotImplementedError("an attention mixer without position encoding is not built")
+        ops.qkv_rope_write(qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
+                           cache.k if cache.writes else None, cache.v if cache.writes else None,
+                           self.nh, self.nkv, self.D)
+        out = torch.empty_like(q)
+        self.attend(q, step, cache, out)
+        return ops.linear(out.view(T, self.q_size), self.w_o)
+
+    def attend(self, q: torch.Tensor, step: StepInputs, cache: LayerCache, out: torch.Tensor) -> None:
+        G = self.nh // self.nkv
+        tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
+        split = step.split_keys if step.max_q_len * G <= 32 else 0
+        kw = {}
+        if split:
+            max_splits = step.max_splits
+            part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, max_splits, self.D)
+            kw = dict(split_keys=split, max_splits=max_splits, part_acc=part_acc, part_ml=part_ml,
+                      seq_of_token=step.seq_of_token)
+        ops.paged_attention(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q, step.kv_before,
+                            tile_seq, tile_row0, n_tiles, out, scale=self.scale, window=self.window, **kw)
+
+
+register_mixer("gqa_attention", GroupedQueryAttention)

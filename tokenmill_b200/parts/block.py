@@ -1,0 +1,45 @@
+"""Pre-norm block: ``x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x))``
+(src/infer/model/qwen2.py:13-23).
+
+The residual stream ``x`` is 32-bit. A branch output is not added where it is produced: it is
+handed on as ``Pending`` and the next norm adds it while it reads the row anyway (one pass over the
+stream instead of two). The embedding gather enters the same way, as the first pending item.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..registry import register_block
+from .base import LayerCache, StepInputs
+
+
+@dataclass
+class Pending:
+    """What still has to be added to the residual stream: a branch output, a stack of 32-bit partial
+    products, or (at the very start) the embedding rows of the token ids."""
+
+    branch: torch.Tensor | None = None
+    partials: torch.Tensor | None = None
+    ids: torch.Tensor | None = None
+    table: torch.Tensor | None = None
+
+    def kwargs(self) -> dict:
+        return {"branch": self.branch, "partials": self.partials, "ids": self.ids, "table": self.table}
+
+
+class PreNormBlock:
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
+        normed = self.mixer_norm.forward(resid, **pending.kwargs())
+        mixed = self.mixer.forward(normed, step, cache)
+        normed = self.feed_forward_norm.forward(resid, branch=mixed)
+        return Pending(branch=self.feed_forward.forward(normed, step))
+
+
+register_block("pre_norm", PreNormBlock)

@@ -1,0 +1,40 @@
+"""Dense SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))``, no biases.
+
+The gate and up matrices are stored fused, rows [gate; up], from the checkpoint's gate_proj and
+up_proj tensors (src/infer/model/layers.py:153-164, src/infer/model/loader.py:46,114-116).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..registry import register_feed_forward
+from .base import StepInputs
+from .spec import WeightSpec
+
+
+class SwiGLUFeedForward:
+    def __init__(self, *, hidden_size: int, intermediate_size: int, dtype: torch.dtype, device: torch.device):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.dtype, self.device = dtype, device
+        self.w_gate_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec("gate_proj.weight", (I, H)), WeightSpec("up_proj.weight", (I, H)),
+                WeightSpec("down_proj.weight", (H, I))]
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"]
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        gu = ops.linear(x, self.w_gate_up)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
+        ops.swiglu(gu, act)
+        return ops.linear(act, self.w_down)
+
+
+register_feed_forward("swiglu", SwiGLUFeedForward)
