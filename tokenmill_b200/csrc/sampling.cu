@@ -90,13 +90,13 @@ __device__ __forceinline__ int block_count(int v, int* red) {
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, int V, long long row_stride, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
-    int* __restrict__ out) {
+    const int* __restrict__ rows, int* __restrict__ out) {
   __shared__ float redf[32];
   __shared__ int redi[32];
   __shared__ float warp_tot[32];
   __shared__ int s_token;
-  const int rowi = blockIdx.x;
-  const float* row = logits + (size_t)rowi * row_stride;
+  const int rowi = blockIdx.x;  // index into the parameter arrays and `out`
+  const float* row = logits + (size_t)(rows ? rows[rowi] : rowi) * row_stride;
   const float inv_t = 1.0f / temperature[rowi];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
 
@@ -225,12 +225,13 @@ extern "C" int tm_argmax(const float* logits, int n_rows, int V, long long row_s
 }
 
 // temperature [n] (> 0), top_k [n] (<= 0 or >= V: off), top_p [n] (>= 1: off), uniform [n] in [0, 1).
+// rows [n] (or null): which row of `logits` draw i reads; out [n].
 extern "C" int tm_sample(const float* logits, int n_rows, int V, long long row_stride, const float* temperature,
-                         const int* top_k, const float* top_p, const float* uniform, int* out,
+                         const int* top_k, const float* top_p, const float* uniform, const int* rows, int* out,
                          cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
   tmk::sample_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, temperature, top_k, top_p,
-                                                              uniform, out);
+                                                              uniform, rows, out);
   return tmk::launch_status();
 }

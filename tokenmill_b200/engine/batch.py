@@ -1,0 +1,132 @@
+"""Turn a step's entries into device metadata: one packed int32 buffer, one host-to-device copy.
+
+The reference builds five int64 tensors from Python lists over every token and copies each
+(src/infer/engine/model_runner.py:30-32,40-74). Here the same information (token ids, absolute
+positions, cache slots, block tables, per-request offsets, rows whose logits are wanted) is laid out
+with numpy in a single pinned buffer; the device tensors the kernels read are views of one
+allocation.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheHandle, CacheManager
+from ..parts.base import StepInputs
+
+TILE_ROWS = 32       # rows of (token, head-in-group) one attention tile covers
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: ``tokens`` continue the request at position ``start``;
+    ``want`` lists the places among these tokens whose logits are asked for."""
+
+    handle: CacheHandle
+    tokens: list[int]
+    start: int
+    want: list[int] = field(default_factory=list)
+
+
+class Layout:
+    """Offsets of every section inside the packed buffer, for given sizes."""
+
+    def __init__(self, T: int, S: int, n_want: int, widths: list[int], tiles: dict[int, int]):
+        self.T, self.S, self.n_want, self.widths, self.tiles = T, S, n_want, widths, tiles
+        off = 0
+
+        def take(n: int) -> slice:
+            nonlocal off
+            s = slice(off, off + n)
+            off += (n + 3) // 4 * 4          # keep every section 16-byte aligned
+            return s
+
+        self.token_ids, self.positions, self.seq_of_token = take(T), take(T), take(T)
+        self.cu_q, self.kv_before, self.state_slots = take(S + 1), take(S), take(S)
+        self.want_rows = take(n_want)
+        self.slot_maps = [take(T) for _ in widths]
+        self.block_tables = [take(S * w) for w in widths]
+        self.tile_seq = {g: take(n) for g, n in tiles.items()}
+        self.tile_row0 = {g: take(n) for g, n in tiles.items()}
+        self.total = off
+
+
+def tiles_for(q_lens: np.ndarray, group_size: int) -> tuple[np.ndarray, np.ndarray]:
+    per_seq = (q_lens * group_size + TILE_ROWS - 1) // TILE_ROWS
+    tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), per_seq)
+    first = np.cumsum(per_seq) - per_seq
+    tile_row0 = (np.arange(tile_seq.size, dtype=np.int32) - np.repeat(first, per_seq).astype(np.int32)) * TILE_ROWS
+    return tile_seq.astype(np.int32), tile_row0.astype(np.int32)
+
+
+def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: torch.device,
+                      group_sizes: list[int], *, scratch=None, split_keys: int = 0,
+                      min_table_width: int = 0) -> StepInputs:
+    S = len(entries)
+    ps = cache.page_size
+    q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
+    if S == 0 or (q_lens <= 0).any():
+        raise ValueError("a step needs at least one entry, and every entry at least one token")
+    starts = np.array([e.start for e in entries], dtype=np.int32)
+    T = int(q_lens.sum())
+    cu_q = np.zeros(S + 1, dtype=np.int32)
+    np.cumsum(q_lens, out=cu_q[1:])
+    kv_after = starts + q_lens
+    max_kv = int(kv_after.max())
+    widths = [max(min_table_width, -(-max_kv // ps)) for _ in range(cache.num_groups)]
+    want_rows = [int(cu_q[i]) + w for i, e in enumerate(entries) for w in e.want]
+    for i, e in enumerate(entries):
+        if any(not (0 <= w < len(e.tokens)) for w in e.want):
+            raise ValueError(f"entry {i}: a wanted place lies outside its {len(e.tokens)} tokens")
+    tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
+    lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()})
+
+    host = torch.empty(lay.total, dtype=torch.int32, pin_memory=device.type == "cuda")
+    buf = host.numpy()
+    buf[lay.token_ids] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+    seq_of_token = np.repeat(np.arange(S, dtype=np.int32), q_lens)
+    positions = np.arange(T, dtype=np.int32) - np.repeat(cu_q[:-1], q_lens) + np.repeat(starts, q_lens)
+    buf[lay.positions] = positions
+    buf[lay.seq_of_token] = seq_of_token
+    buf[lay.cu_q] = cu_q
+    buf[lay.kv_before] = starts
+    buf[lay.state_slots] = [e.handle.state_slot for e in entries]
+    buf[lay.want_rows] = want_rows
+    for g in range(cache.num_groups):
+        w = widths[g]
+        table = np.zeros((S, w), dtype=np.int32)
+        slots = np.empty(T, dtype=np.int32)
+        for i, e in enumerate(entries):
+            row = np.asarray(e.handle.tables[g], dtype=np.int32)
+            need = -(-int(kv_after[i]) // ps)
+            if row.size < need:
+                raise RuntimeError(f"entry {i} holds {row.size} pages in group {g}, its {int(kv_after[i])} "
+                                   f"tokens need {need}")
+            table[i, :min(row.size, w)] = row[:w]
+            p = positions[cu_q[i]:cu_q[i + 1]]
+            pages = row[p // ps]
+            if (pages < 0).any():
+                raise RuntimeError(f"entry {i} writes into a page it has already given back")
+            slots[cu_q[i]:cu_q[i + 1]] = pages * ps + p % ps
+        buf[lay.block_tables[g]] = table.reshape(-1)
+        buf[lay.slot_maps[g]] = slots
+    for g, (tile_seq, tile_row0) in tile_arrays.items():
+        buf[lay.tile_seq[g]] = tile_seq
+        buf[lay.tile_row0[g]] = tile_row0
+
+    dev = host.to(device, non_blocking=True)
+    max_q = int(q_lens.max())
+    use_split = split_keys if (split_keys and max_kv > split_keys) else 0
+    return StepInputs(
+        n_tokens=T, n_seqs=S, token_ids=dev[lay.token_ids], positions=dev[lay.positions],
+        seq_of_token=dev[lay.seq_of_token], cu_q=dev[lay.cu_q], kv_before=dev[lay.kv_before],
+        state_slots=dev[lay.state_slots],
+        block_tables=[dev[lay.block_tables[g]].view(S, widths[g]) for g in range(cache.num_groups)],
+        slot_maps=[dev[lay.slot_maps[g]] for g in range(cache.num_groups)],
+        want_rows=dev[lay.want_rows], n_want=len(want_rows), max_q_len=max_q, max_kv_len=max_kv,
+        q_lens=q_lens.tolist(), kv_befores=starts.tolist(),
+        tiles={g: (dev[lay.tile_seq[g]], dev[lay.tile_row0[g]], a[0].size) for g, a in tile_arrays.items()},
+        scratch=scratch, split_keys=use_split, max_splits=-(-max_kv // use_split) if use_split else 0)

@@ -1,0 +1,222 @@
+"""The engine's Python entry point: ``LLMEngine(cfg).generate(prompts, params)``.
+
+Same shape as the reference's LLMEngine (src/infer/engine/engine.py:87-281): synchronous
+``add_request`` / ``abort_request`` / ``step`` / ``generate`` / ``has_unfinished``; every step
+re-plans the batch, so new requests join at the next step and finished ones leave at once. One step
+(engine.py:167-204): plan -> requests that can never fit finish with an error -> run the batch ->
+count computed tokens and publish full pages -> append the sampled tokens -> stop checks -> outputs.
+Prompts and outputs are token ids; the text side of the reference (tokenizer, HTTP) is not part of
+this engine.
+"""
+
+from __future__ import annotations
+
+import logging
+import random
+import time
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pool import CachePools
+from ..config.engine_config import EngineConfig
+from ..parts.model import DecoderModel
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from ..weights.loader import load_model, resolve_dtype
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Scheduler
+from .sequence import RequestOutput, Sequence
+
+log = logging.getLogger("tokenmill_b200.engine")
+
+
+class RequestRejected(ValueError):
+    """The request can never be served (empty prompt, prompt too long, duplicate id)."""
+
+
+def _element_size(dtype: torch.dtype) -> int:
+    return torch.empty((), dtype=dtype).element_size()
+
+
+def kv_budget_bytes(cfg: EngineConfig, model: DecoderModel) -> int:
+    """Bytes for the cache pool: ``kv_cache_mb`` if given, else what is left of
+    ``gpu_memory_utilization`` x device memory after what is already allocated (the weights) and an
+    allowance for the largest step's activations (src/infer/engine/engine.py:44-61; the reference
+    measures the activation peak with a dummy forward, here it is computed from the layer sizes)."""
+    if cfg.kv_cache_mb is not None:
+        return int(cfg.kv_cache_mb * 2 ** 20)
+    dev = model.device
+    total = torch.cuda.get_device_properties(dev).total_memory
+    used = torch.cuda.memory_allocated(dev)
+    s = model.spec
+    widest = 0
+    for b in model.blocks:
+        ffn, mixer = b.feed_forward, b.mixer
+        widest = max(widest, 3 * getattr(ffn, "intermediate_size", s.hidden_size),
+                     2 * (getattr(mixer, "q_size", s.hidden_size) + 2 * getattr(mixer, "kv_size", 0)))
+    act = cfg.max_num_batched_tokens * (8 * s.hidden_size + 4 * widest)
+    logits = 3 * min(cfg.max_num_seqs, cfg.max_num_batched_tokens) * s.vocab_size * 4
+    budget = int(total * cfg.gpu_memory_utilization) - used - act - logits - (512 << 20)
+    if budget <= 0:
+        raise RuntimeError("no memory left for the cache; lower --max-batched-tokens or raise "
+                           "--gpu-memory-utilization")
+    return budget
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, model: DecoderModel | None = None):
+        self.cfg = cfg
+        if model is None:
+            if not cfg.model:
+                raise ValueError("EngineConfig.model must name a model folder")
+            model = load_model(cfg.model, resolve_dtype(cfg.dtype), torch.device(cfg.device),
+                               max_positions=cfg.max_model_len)
+        self.model = model
+        self.device, self.dtype = model.device, model.dtype
+        self.eos_ids = set(model.spec.eos_token_ids)
+        layout = model.cache_layout()
+        per_token = layout.bytes_per_token(_element_size(self.dtype))
+        if per_token > 0:
+            num_pages = kv_budget_bytes(cfg, model) // (per_token * cfg.block_size)
+            num_pages = min(num_pages, cfg.max_num_seqs * -(-cfg.max_model_len // cfg.block_size))
+        else:
+            num_pages = cfg.max_num_seqs
+        if num_pages < 2:
+            raise RuntimeError("cache budget too small for the paged pool")
+        n_groups = len(layout.groups)
+        n_state = cfg.max_num_seqs if layout.entry_state else 0
+        self.cache = CacheManager([num_pages] * n_groups, cfg.block_size, layout.windows, cfg.watermark,
+                                  cfg.enable_prefix_caching, num_state_slots=n_state)
+        self.pools = CachePools(layout, [num_pages] * n_groups, cfg.block_size, self.dtype, self.device,
+                                num_state_slots=n_state, sink_page=cfg.cuda_graphs,
+                                run_order_cache_of=[e.cache_of for e in model.spec.run_order])
+        self.runner = ModelRunner(model, self.cache, self.pools, max_model_len=cfg.max_model_len,
+                                  cuda_graphs=cfg.cuda_graphs, cuda_graph_max_batch=cfg.cuda_graph_max_batch,
+                                  max_num_seqs=cfg.max_num_seqs)
+        self.scheduler = Scheduler(cfg, self.cache)
+        self.sampler = Sampler(self.device)
+        self.seqs: dict[str, Sequence] = {}
+        self._rng = random.Random(cfg.seed)
+        self._offline_counter = 0
+        self.stats = {"steps": 0, "peak_running": 0, "prefill_steps": 0, "decode_steps": 0,
+                      "generated_tokens": 0, "busy_time": 0.0}
+        log.info("engine ready: %d pages of %d tokens in %d group(s) (%.0f MiB), dtype %s, device %s", num_pages,
+                 cfg.block_size, n_groups, self.pools.nbytes / 2 ** 20, self.dtype, self.device)
+
+    # --- requests -------------------------------------------------------------------------------
+
+    def add_request(self, request_id: str, prompt_ids: list[int], params: SamplingParams,
+                    arrival_time: float | None = None) -> Sequence:
+        if not prompt_ids:
+            raise RequestRejected("prompt is empty")
+        if len(prompt_ids) >= self.cfg.max_model_len:
+            raise RequestRejected(f"prompt has {len(prompt_ids)} tokens; max_model_len is {self.cfg.max_model_len}")
+        if request_id in self.seqs:
+            raise RequestRejected(f"duplicate request id {request_id}")
+        vocab = self.model.spec.vocab_size
+        if any(not (0 <= t < vocab) for t in prompt_ids):
+            raise RequestRejected(f"a prompt token id lies outside the vocabulary of {vocab}")
+        seq = Sequence(request_id, list(prompt_ids), params, self.cache.new_handle(),
+                       arrival_time=time.monotonic() if arrival_time is None else arrival_time)
+        if not params.greedy:
+            seq.sample_seed = params.seed if params.seed is not None else self._rng.getrandbits(62)
+        self.seqs[request_id] = seq
+        self.scheduler.add(seq)
+        return seq
+
+    def abort_request(self, request_id: str, reason: str = "abort") -> RequestOutput | None:
+        seq = self.seqs.pop(request_id, None)
+        if seq is None:
+            return None
+        self.scheduler.finish(seq, reason)
+        seq.finish_time = time.monotonic()
+        return self._output(seq, [])
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # --- one step -------------------------------------------------------------------------------
+
+    def step(self) -> list[RequestOutput]:
+        outputs: list[RequestOutput] = []
+        t0 = time.perf_counter()
+        plan = self.scheduler.schedule()
+        for seq in plan.ignored:
+            self.seqs.pop(seq.id, None)
+            self.scheduler.finish(seq, "length")
+            seq.finish_time = time.monotonic()
+            outputs.append(self._output(seq, [], error=None if seq.output_ids else
+                                        "prompt does not fit in the KV cache"))
+        if plan.empty:
+            return outputs
+        entries, sampled = [], []
+        for item in plan.items:
+            seq = item.seq
+            tokens = seq.all_token_ids[item.start:item.start + item.num_tokens]
+            want = [item.num_tokens - 1] if item.samples else []
+            entries.append(StepEntry(seq.cache, tokens, item.start, want))
+            if item.samples:
+                sampled.append(seq)
+        logits = self.runner.step(entries)
+        tokens = self.sampler.sample(logits, [s.params for s in sampled], [s.sample_seed for s in sampled],
+                                     [s.num_draws for s in sampled]) if sampled else []
+        now = time.monotonic()
+        for item in plan.items:
+            seq = item.seq
+            seq.num_computed_tokens = item.start + item.num_tokens
+            self.cache.register_computed(seq.cache, seq.all_token_ids, seq.num_computed_tokens)
+            self.cache.release_behind_window(seq.cache, seq.num_computed_tokens)
+        for seq, tok in zip(sampled, tokens):
+            seq.output_ids.append(tok)
+            if not seq.params.greedy:
+                seq.num_draws += 1
+            if seq.first_token_time is None:
+                seq.first_token_time = now
+            reason = self._stop_reason(seq, tok)
+            if reason:
+                self.scheduler.finish(seq, reason)
+                seq.finish_time = now
+                self.seqs.pop(seq.id, None)
+            outputs.append(self._output(seq, [tok]))
+        self._record_step(plan, time.perf_counter() - t0, len(sampled))
+        return outputs
+
+    def _stop_reason(self, seq: Sequence, tok: int) -> str | None:
+        if tok in self.eos_ids and not seq.params.ignore_eos:
+            return "stop"
+        if seq.num_output_tokens >= seq.params.max_tokens or seq.length >= self.cfg.max_model_len:
+            return "length"
+        return None
+
+    def _output(self, seq: Sequence, new_tokens: list[int], error: str | None = None) -> RequestOutput:
+        return RequestOutput(seq.id, new_tokens, seq.is_finished, seq.finish_reason, seq.num_prompt_tokens,
+                             seq.num_output_tokens, seq.arrival_time, seq.first_token_time, seq.finish_time,
+                             seq.num_preemptions, error)
+
+    def _record_step(self, plan, step_time: float, n_generated: int) -> None:
+        s = self.stats
+        s["steps"] += 1
+        s["busy_time"] += step_time
+        s["prefill_steps" if plan.prefill_items else "decode_steps"] += 1
+        s["generated_tokens"] += n_generated
+        s["peak_running"] = max(s["peak_running"], len(self.scheduler.running))
+        if self.cfg.debug_steps:
+            log.info("step=%d batch=%d prefill_tokens=%d decode_tokens=%d step_ms=%.2f kv_usage=%.3f waiting=%d "
+                     "running=%d preempted=%d", s["steps"], len(plan.items), plan.num_prefill_tokens,
+                     len(plan.decode_items), step_time * 1e3, self.cache.usage(), len(self.scheduler.waiting),
+                     len(self.scheduler.running), len(plan.preempted))
+
+    # --- offline helper -------------------------------------------------------------------------
+
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[list[int]]:
+        """Run every prompt to completion through the step loop; output token ids in prompt order."""
+        plist = params if isinstance(params, list) else [params] * len(prompts)
+        seqs = []
+        for p, sp in zip(prompts, plist):
+            self._offline_counter += 1
+            seqs.append(self.add_request(f"offline-{self._offline_counter}", p, sp))
+        while self.has_unfinished():
+            self.step()
+        return [s.output_ids for s in seqs]

@@ -1,0 +1,185 @@
+"""The step function: run exactly the tokens a step brings, as one batch, from the cache earlier
+steps left, and return the logits at the wanted places.
+
+Counterpart of the reference's ModelRunner.prepare / execute (src/infer/engine/model_runner.py:40-97)
+with two differences: the result is logits (any wanted row, not only each request's last), sampling
+being a separate stage; and prompt portions and decoded tokens are the same kind of entry, so the
+attention kernel sees one list of requests instead of three code paths (src/infer/kv/context.py:63-80).
+
+Decode-only steps may replay a captured CUDA graph per batch-size bucket
+(src/infer/engine/cuda_graphs.py:45-158). Unlike the reference there are no context-length buckets:
+the attention kernel reads each request's true length from device memory, so one graph per batch
+size serves every context. Padded rows decode token 0 at position 0 into a sink page the manager
+never hands out.
+"""
+
+from __future__ import annotations
+
+import bisect
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pool import CachePools
+from ..parts.attention import SPLIT_KEYS, AttentionScratch
+from ..parts.base import StepInputs
+from ..parts.model import DecoderModel
+from .batch import Layout, StepEntry, build_step_inputs, tiles_for
+
+GRAPH_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64, 128, 256]
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, pools: CachePools, *, max_model_len: int,
+                 cuda_graphs: bool = False, cuda_graph_max_batch: int = 64, max_num_seqs: int = 128):
+        if model.device.type != "cuda":
+            raise RuntimeError(f"the engine runs on a CUDA device only, not on {model.device}")
+        self.model, self.cache, self.pools = model, cache, pools
+        self.device = model.device
+        self.max_model_len = max_model_len
+        self.layout = model.cache_layout()
+        self.layer_caches = pools.layer_caches(len(model.spec.run_order))
+        self.group_sizes = sorted({b.mixer.nh // b.mixer.nkv for b in model.blocks
+                                   if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")})
+        self.scratch = AttentionScratch(self.device)
+        self.graph_max_batch = min(cuda_graph_max_batch, max_num_seqs) if cuda_graphs else 0
+        self._graphs: dict[int, "_DecodeGraph"] = {}
+        self._graph_pool = None
+        self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0}
+        if self.graph_max_batch:
+            if any(s < 0 for s in pools.sink):
+                raise RuntimeError("decode graphs need pools built with a sink page")
+            self._reserve_scratch(self.graph_max_batch)
+
+    # --- the step -------------------------------------------------------------------------------
+
+    @torch.inference_mode()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Logits [n_wanted, vocab] float32, in the order of the entries and of each entry's want."""
+        for e in entries:
+            if e.handle.fresh_state:
+                self.pools.zero_state(e.handle.state_slot)
+                e.handle.fresh_state = False
+            if e.start + len(e.tokens) > self.max_model_len:
+                raise ValueError(f"a request would reach {e.start + len(e.tokens)} tokens; max_model_len is "
+                                 f"{self.max_model_len}")
+        self.stats["steps"] += 1
+        self.stats["tokens"] += sum(len(e.tokens) for e in entries)
+        if self.graph_max_batch and len(entries) <= self.graph_max_batch and \
+                all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+            return self._graph_step(entries)
+        step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
+                                 split_keys=SPLIT_KEYS)
+        return self.model.forward(step, self.layer_caches)
+
+    # --- decode graphs --------------------------------------------------------------------------
+
+    def _reserve_scratch(self, batch: int) -> None:
+        max_splits = -(-self.max_model_len // SPLIT_KEYS)
+        for b in self.model.blocks:
+            m = b.mixer
+            if hasattr(m, "nh"):
+                self.scratch.reserve(batch * m.nh, max_splits, m.D)
+
+    def _graph_step(self, entries: list[StepEntry]) -> torch.Tensor:
+        n = len(entries)
+        sizes = [b for b in GRAPH_BATCH_SIZES if b < self.graph_max_batch] + [self.graph_max_batch]
+        bucket = sizes[bisect.bisect_left(sizes, n)]
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = _DecodeGraph(self, bucket)
+            self._graphs[bucket] = g
+        self.stats["graph_steps"] += 1
+        return g.run(entries)
+
+
+class _DecodeGraph:
+    """One captured decode step for ``bucket`` requests with static metadata buffers."""
+
+    def __init__(self, runner: ModelRunner, bucket: int):
+        self.r, self.bucket = runner, bucket
+        self._copied: torch.cuda.Event | None = None
+        cache, dev = runner.cache, runner.device
+        ps = cache.page_size
+        self.width = -(-runner.max_model_len // ps)
+        B = bucket
+        q_lens = np.ones(B, dtype=np.int32)
+        self.tile_arrays = {g: tiles_for(q_lens, g) for g in runner.group_sizes}
+        self.lay = Layout(B, B, B, [self.width] * cache.num_groups, {g: a[0].size for g, a in self.tile_arrays.items()})
+        self.dev = torch.zeros(self.lay.total, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(self.lay.total, dtype=torch.int32, pin_memory=True)
+        self._fill([], first=True)
+        self.dev.copy_(self.host)
+        lay, d = self.lay, self.dev
+        max_splits = -(-runner.max_model_len // SPLIT_KEYS)
+        self.inputs = StepInputs(
+            n_tokens=B, n_seqs=B, token_ids=d[lay.token_ids], positions=d[lay.positions],
+            seq_of_token=d[lay.seq_of_token], cu_q=d[lay.cu_q], kv_before=d[lay.kv_before],
+            state_slots=d[lay.state_slots],
+            block_tables=[d[lay.block_tables[g]].view(B, self.width) for g in range(cache.num_groups)],
+            slot_maps=[d[lay.slot_maps[g]] for g in range(cache.num_groups)],
+            want_rows=d[lay.want_rows], n_want=B, max_q_len=1, max_kv_len=runner.max_model_len,
+            tiles={g: (d[lay.tile_seq[g]], d[lay.tile_row0[g]], a[0].size) for g, a in self.tile_arrays.items()},
+            scratch=runner.scratch, split_keys=SPLIT_KEYS, max_splits=max_splits)
+        runner._reserve_scratch(B)
+        # Warm up outside capture (library handles and workspaces), then capture.
+        torch.cuda.synchronize(dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                runner.model.forward(self.inputs, runner.layer_caches)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=runner._graph_pool):
+            self.logits = runner.model.forward(self.inputs, runner.layer_caches)
+        if runner._graph_pool is None:
+            runner._graph_pool = self.graph.pool()
+        runner.scratch.frozen = True
+
+    def _fill(self, entries: list[StepEntry], first: bool = False) -> None:
+        lay, buf, B = self.lay, self.host.numpy(), self.bucket
+        cache = self.r.cache
+        ps, n = cache.page_size, len(entries)
+        if first:
+            buf[lay.seq_of_token] = np.arange(B, dtype=np.int32)
+            buf[lay.cu_q] = np.arange(B + 1, dtype=np.int32)
+            buf[lay.want_rows] = np.arange(B, dtype=np.int32)
+            for g, (tile_seq, tile_row0) in self.tile_arrays.items():
+                buf[lay.tile_seq[g]] = tile_seq
+                buf[lay.tile_row0[g]] = tile_row0
+        tok, pos, slot_state = buf[lay.token_ids], buf[lay.positions], buf[lay.state_slots]
+        before = buf[lay.kv_before]
+        tok[:] = 0
+        pos[:] = 0
+        before[:] = 0
+        slot_state[:] = 0
+        for i, e in enumerate(entries):
+            tok[i], pos[i], before[i], slot_state[i] = e.tokens[0], e.start, e.start, max(e.handle.state_slot, 0)
+        for g in range(cache.num_groups):
+            sink = self.r.pools.sink[g]
+            table = buf[lay.block_tables[g]].reshape(B, self.width)
+            slots = buf[lay.slot_maps[g]]
+            table[n:, :] = sink
+            slots[n:] = sink * ps
+            for i, e in enumerate(entries):
+                row = e.handle.tables[g]
+                k = min(len(row), self.width)
+                table[i, :k] = row[:k]
+                page = row[e.start // ps]
+                if page < 0:
+                    raise RuntimeError("a decoded token would be written into a page already given back")
+                slots[i] = page * ps + e.start % ps
+
+    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+        if self._copied is not None:
+            self._copied.synchronize()       # the pinned buffer is about to be rewritten
+        self._fill(entries)
+        self.dev.copy_(self.host, non_blocking=True)
+        if self._copied is None:
+            self._copied = torch.cuda.Event()
+        self._copied.record()
+        self.graph.replay()
+        return self.logits[:len(entries)]

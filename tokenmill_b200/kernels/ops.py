@@ -168,14 +168,19 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           uniform: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """One draw per row of logits [n, V] float32. temperature/top_p/uniform float32 [n], top_k int32 [n]."""
-    n, V = logits.shape
+           uniform: torch.Tensor, rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One draw per entry: entry i reads row rows[i] (default i) of logits [*, V] float32.
+    temperature/top_p/uniform float32 [n], top_k int32 [n]; returns int32 [n]."""
+    V = logits.shape[1]
+    n = temperature.numel()
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise lib.KernelError("sample: float32 logits with contiguous rows on the GPU")
+    if rows is None and logits.shape[0] < n:
+        raise lib.KernelError("sample: fewer logits rows than draws")
     if out is None:
         out = torch.empty(n, dtype=torch.int32, device=logits.device)
     lib.call("tm_sample", logits.data_ptr(), n, V, logits.stride(0), _req(temperature, "temperature", torch.float32),
              _req(top_k, "top_k", torch.int32), _req(top_p, "top_p", torch.float32),
-             _req(uniform, "uniform", torch.float32), _req(out, "out", torch.int32), _stream())
+             _req(uniform, "uniform", torch.float32), _opt(rows, "rows", torch.int32),
+             _req(out, "out", torch.int32), _stream())
     return out
