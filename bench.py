@@ -1,0 +1,371 @@
+"""Decode and prefill throughput of the engine at the Qwen2.5-0.5B layer sizes, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+One JSON line on standard output. A "step" is one decode step of a batch of 8 requests (prompt 512,
+context limit 4096). ``value`` is decoded tokens per second timed on the device with CUDA events around
+exactly K steps of the engine's step function (one metadata copy, the captured decode graph and the
+arg-max kernel per step); ``e2e`` is the same quantity through the Python entry point
+(``LLMEngine.step``: scheduler, pinned host-to-device metadata copy, decode graph, sampling, token ids
+read back to the host every step), timed on the host between two device synchronisations. ``prefill``
+times one 2,048-token prompt; ``roofline`` relates the decode step to the memory bandwidth it needs
+(every weight once plus the live requests' cache); ``points`` holds decode at batch 1 and 64.
+
+The engine runs on one GPU: for --gpus N > 1 a line says so and the exit code is 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SIZES = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
+             num_attention_heads=14, num_key_value_heads=2, head_dim=64, rope_theta=1000000.0, rms_norm_eps=1e-6,
+             tie_word_embeddings=True, max_position_embeddings=32768)
+PROMPT_LEN, CONTEXT, BATCH, PREFILL_TOKENS, PAGE = 512, 4096, 8, 2048, 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            raw = json.loads(f.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"])}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples while the timed regions run (read-only queries)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.split(",") for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 5]
+        os.unlink(self.file.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_flops_bytes(cfg: dict, layers: int) -> dict:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = H * (nh + 2 * nkv) * D + nh * D * H + 3 * H * I
+    small = layers * (2 * H + (nh + 2 * nkv) * D) + H
+    return {"layer_matrix_params": per_layer, "weight_bytes": 2 * (layers * per_layer + V * H) + 4 * small,
+            "kv_bytes_per_token": 2 * layers * nkv * D * 2,
+            "prefill_flops": lambda T: layers * (2 * T * per_layer + 4 * nh * D * T * (T + 1) / 2) + 2 * V * H}
+
+
+def make_model_dir(layers: int) -> tempfile.TemporaryDirectory:
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    tmp = tempfile.TemporaryDirectory(prefix="tokenmill_bench_")
+    cfg = qwen2_config(**{**SIZES, "num_hidden_layers": layers})
+    t0 = time.time()
+    write_random_model(tmp.name, cfg, seed=0)
+    print(f"[bench] random weights ({layers} layers) written in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    return tmp
+
+
+def prompts(batch: int, length: int, seed: int = 0) -> list[list[int]]:
+    import random
+    rng = random.Random(seed)
+    return [[rng.randrange(1000, 150000) for _ in range(length)] for _ in range(batch)]
+
+
+def decode_device_timed(engine, batch: int, steps: int, warmup: int) -> dict:
+    """K decode steps of the step function, CUDA events on the launching stream."""
+    import torch
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.kernels import lib, ops
+
+    runner, cache = engine.runner, engine.cache
+    handles = []
+    for p in prompts(batch, PROMPT_LEN, seed=batch):
+        h = cache.new_handle()
+        cache.allocate(h, p)
+        handles.append((h, p))
+    for lo in range(0, batch, 4):                               # prefill, four prompts a step
+        runner.step([StepEntry(h, p, 0, []) for h, p in handles[lo:lo + 4]])
+    length = PROMPT_LEN
+    tok = [p[-1] for _, p in handles]
+
+    def one():
+        nonlocal length
+        for h, _ in handles:
+            cache.grow(h, length + 1)
+        logits = runner.step([StepEntry(h, [t], length, [0]) for (h, _), t in zip(handles, tok)])
+        ops.argmax(logits)
+        length += 1
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    launches0 = lib.launch_count
+    graph_kernels = getattr(runner, "kernels_per_graph", {}).get(batch, 0)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    launched = (lib.launch_count - launches0) + steps * graph_kernels
+    mean_ctx = length - steps / 2
+    for h, _ in handles:
+        cache.free(h)
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launched, "mean_ctx": mean_ctx}
+
+
+def decode_end_to_end(engine, batch: int, steps: int, warmup: int) -> dict:
+    """K decode steps through LLMEngine.step: host token ids in, host token ids out, every step."""
+    import torch
+    from tokenmill_b200.sampling import SamplingParams
+
+    sp = SamplingParams(max_tokens=steps + warmup + 2, ignore_eos=True)
+    seqs = [engine.add_request(f"e2e-{batch}-{i}", p, sp) for i, p in enumerate(prompts(batch, PROMPT_LEN, seed=99))]
+    while any(s.num_output_tokens == 0 for s in seqs):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(steps):
+        n += sum(len(o.new_token_ids) for o in engine.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    g = engine.runner._graphs.get(batch)
+    h2d = g.lay.total * 4 if g is not None else 0
+    for s in seqs:
+        engine.abort_request(s.id)
+    return {"tok_s": n / dt, "ms_per_step": 1e3 * dt / steps, "h2d": h2d, "d2h": batch * 4, "tokens": n}
+
+
+def prefill_timed(engine, tokens: int, reps: int = 5) -> dict:
+    import torch
+    from tokenmill_b200.engine.batch import StepEntry
+
+    runner, cache = engine.runner, engine.cache
+    p = prompts(1, tokens, seed=5)[0]
+    times = []
+    for i in range(reps + 3):
+        h = cache.new_handle()
+        cache.allocate(h, p)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry(h, p, 0, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(start.elapsed_time(end))
+        cache.free(h)
+    return {"ms": statistics.median(times)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    from tokenmill_b200 import EngineConfig
+    from tokenmill_b200.engine import LLMEngine
+    from tokenmill_b200.kernels import lib
+
+    layers = args.layers or SIZES["num_hidden_layers"]
+    pk, pk_kind = peaks()
+    info = model_flops_bytes(SIZES, layers)
+    tmp = make_model_dir(layers)
+    try:
+        cfg = EngineConfig(model=tmp.name, dtype="bfloat16", block_size=PAGE, max_model_len=CONTEXT, max_num_seqs=64,
+                           max_num_batched_tokens=4 * PROMPT_LEN, kv_cache_mb=64 * CONTEXT * info["kv_bytes_per_token"]
+                           / 2 ** 20, watermark=0.0, cuda_graphs=True, cuda_graph_max_batch=64)
+        engine = LLMEngine(cfg)
+        lib.load()
+        sampler = ClockSampler()
+        # warm every path once before the clocks are sampled
+        decode_device_timed(engine, BATCH, 4, 3)
+        sampler.start()
+        main = decode_device_timed(engine, BATCH, args.steps, args.warmup)
+        e2e = decode_end_to_end(engine, BATCH, args.steps, args.warmup)
+        b1 = decode_device_timed(engine, 1, max(16, args.steps // 2), args.warmup)
+        b64 = decode_device_timed(engine, 64, max(16, args.steps // 2), args.warmup)
+        pre = prefill_timed(engine, PREFILL_TOKENS)
+        clocks = sampler.stop()
+    finally:
+        tmp.cleanup()
+    step_bytes = info["weight_bytes"] + BATCH * main["mean_ctx"] * info["kv_bytes_per_token"]
+    achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
+    pf_flops = info["prefill_flops"](PREFILL_TOKENS)
+    pf_frac = pf_flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12)
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, prompt 512, bf16)", "value": round(main["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights seed 0", "impl": "ours",
+        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
+                   "hidden": SIZES["hidden_size"], "q_heads": SIZES["num_attention_heads"],
+                   "kv_heads": SIZES["num_key_value_heads"], "head_dim": SIZES["head_dim"],
+                   "intermediate": SIZES["intermediate_size"], "vocab": SIZES["vocab_size"], "tied_output": True,
+                   "global_batch": BATCH, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "kv_page": PAGE,
+                   "mean_decode_context": round(main["mean_ctx"], 1), "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights read per step: %.0f MB)" % (info["weight_bytes"] / 1e6),
+                   "peaks": pk_kind},
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
+                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
+        "gpu_launches": int(main["launches"]),
+        "prefill": {"value": round(PREFILL_TOKENS / (pre["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pre["ms"], 3), "frac": round(pf_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1),
+                   "decode_b1_ms": round(b1["ms_per_step"], 4), "decode_b64_ms": round(b64["ms_per_step"], 4)},
+        "clocks": clocks,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference, installed under baseline/_ref, through its own LLMEngine: the same
+    random model folder, bfloat16, its paged engine with its CUDA graphs enabled."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "infer").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref/infer is not installed on this machine"}
+    sys.path.insert(0, str(ref))
+    try:
+        import torch
+        from infer.config import EngineConfig
+        from infer.engine.engine import LLMEngine
+        from infer.engine.sequence import SamplingParams
+        from infer.model.loader import load_model
+    except Exception as e:  # a dependency of the reference is missing
+        return {"impl": "reference", "unavailable": f"the reference does not import here: {type(e).__name__}: {e}"}
+    layers = args.layers or SIZES["num_hidden_layers"]
+    info = model_flops_bytes(SIZES, layers)
+    tmp = make_model_dir(layers)
+    try:
+        dev = torch.device("cuda:0")
+        model = load_model(tmp.name, torch.bfloat16, dev, max_positions=CONTEXT)
+        cfg = EngineConfig(model=tmp.name, dtype="bfloat16", device="cuda:0", block_size=PAGE, max_model_len=CONTEXT,
+                           max_num_seqs=64, max_num_batched_tokens=4 * PROMPT_LEN,
+                           kv_cache_mb=64 * CONTEXT * info["kv_bytes_per_token"] / 2 ** 20, watermark=0.0,
+                           cuda_graphs=True, cuda_graph_max_batch=64, request_timeout=None)
+        engine = LLMEngine(cfg, model=model)
+        sampler = ClockSampler()
+
+        def timed(batch, steps, warmup):
+            sp = SamplingParams(max_tokens=steps + warmup + 2, ignore_eos=True)
+            seqs = [engine.add_request(f"r-{batch}-{i}-{time.time_ns()}", p, sp)
+                    for i, p in enumerate(prompts(batch, PROMPT_LEN, seed=99))]
+            while any(s.num_output_tokens == 0 for s in seqs):
+                engine.step()
+            for _ in range(warmup):
+                engine.step()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            start.record()
+            n = 0
+            for _ in range(steps):
+                n += sum(len(o.new_token_ids) for o in engine.step())
+            end.record()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            for s in seqs:
+                engine.abort_request(s.id)
+            return {"tok_s_dev": n / (start.elapsed_time(end) / 1e3), "tok_s": n / dt, "ms": 1e3 * dt / steps}
+
+        timed(BATCH, 4, 3)
+        sampler.start()
+        main = timed(BATCH, args.steps, args.warmup)
+        b1 = timed(1, max(16, args.steps // 2), args.warmup)
+        b64 = timed(64, max(16, args.steps // 2), args.warmup)
+        sp = SamplingParams(max_tokens=1, ignore_eos=True)
+        pre = []
+        for i in range(6):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            engine.generate([prompts(1, PREFILL_TOKENS, seed=5)[0]], sp)
+            torch.cuda.synchronize()
+            pre.append(1e3 * (time.perf_counter() - t0))
+        clocks = sampler.stop()
+    finally:
+        tmp.cleanup()
+    pf_ms = statistics.median(pre[2:])
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, prompt 512, bf16)", "value": round(main["tok_s_dev"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main["ms"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random weights seed 0", "impl": "reference",
+        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "global_batch": BATCH, "prompt_len": PROMPT_LEN,
+                   "seq_len": CONTEXT, "kv_page": PAGE, "reference_flags": "paged engine, cuda_graphs=True, max batch 64",
+                   "parallelism": "single GPU"},
+        "e2e": {"value": round(main["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": None,
+                "d2h_bytes_per_step": BATCH * 8},
+        "prefill": {"value": round(PREFILL_TOKENS / (pf_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3)},
+        "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)},
+        "clocks": clocks,
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
+    args = ap.parse_args()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,217 @@
+"""The engine through its Python entry point: greedy generation against the plain implementation,
+every scheduling option giving the same tokens, preemption with a tiny pool, decode graphs, long
+decoding, the first tokens of a sequence, seeded sampling."""
+
+from __future__ import annotations
+
+import json
+import random
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from plain_qwen2 import load_plain, plain_greedy, plain_logits, tolerance
+from replay_util import check_against_plain, make_requests, plain_for, run_trace, tail_decode_steps
+
+pytestmark = pytest.mark.gpu
+
+N_NEW = 12
+
+
+def engine_for(model_dir, dtype="float32", **kw):
+    from tokenmill_b200 import EngineConfig
+    from tokenmill_b200.engine import LLMEngine
+    base = dict(model=str(model_dir), dtype=dtype, kv_cache_mb=8, block_size=16, max_model_len=512,
+                max_num_seqs=16, max_num_batched_tokens=512, watermark=0.0)
+    base.update(kw)
+    return LLMEngine(EngineConfig(**base))
+
+
+def prompts_for(model_dir, lengths=(1, 2, 3, 5, 8, 17, 31, 40, 64, 3, 11, 90)):
+    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    rng = random.Random(0)
+    return [[rng.randrange(vocab) for _ in range(n)] for n in lengths]
+
+
+def greedy(n=N_NEW):
+    from tokenmill_b200.sampling import SamplingParams
+    return SamplingParams(max_tokens=n, ignore_eos=True)
+
+
+def assert_tokens_are_argmax_of_plain(model_dir, prompts, outs, dtype):
+    """Each generated token is the plain implementation's arg-max given the same history, or lies
+    within the dtype's tolerance of it (a near-tie)."""
+    cfg, w = load_plain(model_dir)
+    for p, o in zip(prompts, outs):
+        logits = plain_logits(cfg, w, p + o)
+        for i, tok in enumerate(o):
+            row = logits[len(p) - 1 + i]
+            assert float(row.max() - row[tok]) <= 2 * tolerance(row, dtype), (len(p), i, tok, int(row.argmax()))
+
+
+@pytest.fixture(scope="module")
+def baseline_tokens(tiny_dir):
+    eng = engine_for(tiny_dir)
+    prompts = prompts_for(tiny_dir)
+    outs = eng.generate(prompts, greedy())
+    assert eng.cache.all_free and not eng.scheduler.running
+    return prompts, outs
+
+
+def test_greedy_generation_equals_the_plain_implementation(tiny_dir, baseline_tokens):
+    prompts, outs = baseline_tokens
+    cfg, w = load_plain(tiny_dir)
+    assert all(len(o) == N_NEW for o in outs)
+    for p, o in list(zip(prompts, outs))[:6]:
+        assert o == plain_greedy(cfg, w, p, N_NEW)
+    assert_tokens_are_argmax_of_plain(tiny_dir, prompts, outs, "float32")
+
+
+@pytest.mark.parametrize("kw", [
+    dict(block_size=1), dict(block_size=8), dict(max_num_batched_tokens=40), dict(enable_prefix_caching=True),
+    dict(enable_chunked_prefill=True, max_num_batched_tokens=16),
+    dict(enable_chunked_prefill=True, max_num_batched_tokens=5, block_size=3),
+    dict(enable_chunked_prefill=True, max_num_batched_tokens=24, enable_prefix_caching=True),
+    dict(policy="decode_first", max_waiting_steps=2), dict(cuda_graphs=True), dict(max_num_seqs=3),
+    dict(cuda_graphs=True, enable_chunked_prefill=True, max_num_batched_tokens=32, cuda_graph_max_batch=4),
+], ids=["page1", "page8", "small_budget", "prefix", "chunked16", "chunked5_page3", "chunked+prefix", "decode_first",
+        "graphs", "three_seats", "graphs+chunked"])
+def test_every_scheduling_option_gives_the_same_tokens(tiny_dir, baseline_tokens, kw):
+    prompts, outs = baseline_tokens
+    eng = engine_for(tiny_dir, **kw)
+    assert eng.generate(prompts, greedy()) == outs
+    assert eng.cache.all_free and not eng.scheduler.running and not eng.scheduler.waiting
+    if kw.get("cuda_graphs"):
+        assert eng.runner.stats["graph_steps"] > 0
+
+
+@pytest.mark.parametrize("chunked", [False, True])
+def test_preemption_with_a_tiny_pool_keeps_the_tokens(tiny_b_dir, chunked):
+    eng = engine_for(tiny_b_dir)
+    prompts = prompts_for(tiny_b_dir)
+    outs = eng.generate(prompts, greedy(24))
+    per_token = eng.model.cache_layout().bytes_per_token(4)
+    small = engine_for(tiny_b_dir, block_size=4, kv_cache_mb=(34 * 4 + 1) * per_token / 2 ** 20,
+                       enable_chunked_prefill=chunked, max_num_batched_tokens=12 if chunked else 512)
+    assert small.cache.num_pages == [34]                    # far fewer than the 12 requests need at once
+    assert small.generate(prompts, greedy(24)) == outs
+    assert small.scheduler.num_preemptions > 0 and small.cache.all_free
+
+
+def test_prompt_that_never_fits_and_bad_requests(tiny_a_dir):
+    from tokenmill_b200.engine import RequestRejected
+    eng = engine_for(tiny_a_dir, block_size=4, kv_cache_mb=(8 * 4 + 1) * 512 / 2 ** 20)   # 8 pages of 4 tokens x 512 B
+    assert eng.cache.num_pages == [8]
+    with pytest.raises(RequestRejected, match="empty"):
+        eng.add_request("e", [], greedy())
+    with pytest.raises(RequestRejected, match="max_model_len"):
+        eng.add_request("l", [1] * 512, greedy())
+    with pytest.raises(RequestRejected, match="vocabulary"):
+        eng.add_request("v", [10 ** 6], greedy())
+    eng.add_request("big", [1] * 40, greedy())              # 10 pages: never fits
+    eng.add_request("ok", [1, 2, 3], greedy(4))
+    with pytest.raises(RequestRejected, match="duplicate"):
+        eng.add_request("ok", [1], greedy())
+    seen = {}
+    while eng.has_unfinished():
+        for out in eng.step():
+            seen.setdefault(out.request_id, []).append(out)
+    assert seen["big"][0].finished and seen["big"][0].error and seen["big"][0].finish_reason == "length"
+    assert sum(len(o.new_token_ids) for o in seen["ok"]) == 4 and seen["ok"][-1].finish_reason == "length"
+    assert eng.cache.all_free
+
+
+def test_stop_rules_and_abort(tiny_a_dir):
+    from tokenmill_b200.sampling import SamplingParams
+    eng = engine_for(tiny_a_dir, max_model_len=40)
+    first = eng.generate([[5, 6, 7]], SamplingParams(max_tokens=6, ignore_eos=True))[0]
+    eng.eos_ids = {first[2]}
+    assert eng.generate([[5, 6, 7]], SamplingParams(max_tokens=6))[0] == first[:first.index(first[2]) + 1]
+    assert eng.generate([[5, 6, 7]], SamplingParams(max_tokens=6, ignore_eos=True))[0] == first
+    eng.eos_ids = set()
+    assert len(eng.generate([[1] * 30], SamplingParams(max_tokens=64, ignore_eos=True))[0]) == 10   # max_model_len
+    eng.add_request("x", [1, 2, 3, 4], greedy(50))
+    eng.step()
+    eng.step()
+    out = eng.abort_request("x")
+    assert out.finished and out.finish_reason == "abort" and eng.cache.all_free and not eng.has_unfinished()
+    assert eng.abort_request("x") is None
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_bfloat16_and_float32_engines_follow_the_plain_argmax(tiny_b_dir, dtype):
+    prompts = prompts_for(tiny_b_dir)
+    eng = engine_for(tiny_b_dir, dtype=dtype, enable_chunked_prefill=True, max_num_batched_tokens=48, cuda_graphs=True)
+    outs = eng.generate(prompts, greedy())
+    assert_tokens_are_argmax_of_plain(tiny_b_dir, prompts, outs, dtype)
+    assert eng.model.embedding.dtype == (torch.float32 if dtype == "float32" else torch.bfloat16)
+    assert eng.pools.kv[0].dtype == eng.model.embedding.dtype
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_crosses_pages_and_key_cuts(tiny_dir, dtype, tmp_path, plain_cache):
+    """10 prompt tokens, then 600 tokens one by one: every page edge and the cuts at 256 and 512 keys."""
+    vocab = json.loads((Path(tiny_dir) / "config.json").read_text())["vocab_size"]
+    reqs = make_requests(vocab, [610], seed=21)
+    steps, max_tokens = tail_decode_steps(reqs, tail=600)
+    outputs = run_trace(tiny_dir, dtype, steps, max_tokens, tmp_path / "o")
+    check_against_plain(steps, outputs, reqs, plain_for(tiny_dir, reqs, plain_cache), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tiny_dir, dtype, tmp_path, plain_cache):
+    """Positions 0, 1, 2: alone, as a whole, and one by one (no earlier key exists for the first)."""
+    vocab = json.loads((Path(tiny_dir) / "config.json").read_text())["vocab_size"]
+    reqs = make_requests(vocab, [1, 2, 3, 4], seed=8)
+    steps = [{"step": i, "entries": [{"id": rid, "tokens": t, "want": list(range(len(t)))}], "end": [rid]}
+             for i, (rid, t) in enumerate(reqs.items())]
+    one_by_one = make_requests(vocab, [4], seed=9)
+    toks = one_by_one["r0"]
+    for p, t in enumerate(toks):
+        steps.append({"step": 10 + p, "entries": [{"id": "s", "tokens": [t], "want": [0]}],
+                      "end": ["s"] if p == len(toks) - 1 else []})
+    all_reqs = {**reqs, "s": toks}
+    outputs = run_trace(tiny_dir, dtype, steps, 64, tmp_path / "o")
+    check_against_plain(steps, outputs, all_reqs, plain_for(tiny_dir, all_reqs, plain_cache), dtype)
+
+
+def test_seeded_sampling_does_not_depend_on_batch_company(tiny_b_dir):
+    from tokenmill_b200.sampling import SamplingParams
+    prompts = prompts_for(tiny_b_dir)
+    sp = SamplingParams(max_tokens=10, temperature=0.8, seed=7, ignore_eos=True)
+    alone = engine_for(tiny_b_dir).generate([prompts[5]], sp)[0]
+    plist = [greedy(10)] * len(prompts)
+    plist[5] = sp
+    plist[7] = SamplingParams(max_tokens=10, temperature=1.2, top_k=20, top_p=0.9, ignore_eos=True)
+    eng = engine_for(tiny_b_dir, enable_chunked_prefill=True, max_num_batched_tokens=32)
+    mixed = eng.generate(prompts, plist)
+    assert mixed[5] == alone
+    assert engine_for(tiny_b_dir).generate([prompts[5]], sp)[0] == alone                  # same seed, same stream
+    other = engine_for(tiny_b_dir).generate([prompts[5]], SamplingParams(max_tokens=10, temperature=0.8, seed=8,
+                                                                         ignore_eos=True))[0]
+    assert other != alone
+    greedy_ref = engine_for(tiny_b_dir).generate(prompts, greedy(10))
+    assert [m for i, m in enumerate(mixed) if i not in (5, 7)] == [g for i, g in enumerate(greedy_ref) if i not in (5, 7)]
+    # sampled tokens lie in the support the plain rules give (temperature 1.2, top-k 20, top-p 0.9)
+    from plain_qwen2 import plain_filtered_probs
+    cfg, w = load_plain(tiny_b_dir)
+    logits = plain_logits(cfg, w, prompts[7] + mixed[7])
+    for i, tok in enumerate(mixed[7]):
+        probs = plain_filtered_probs(logits[len(prompts[7]) - 1 + i], 1.2, 20, 0.9)
+        assert probs[tok] > 0 or float(probs.max()) > 0.999
+
+
+def test_command_line_generates(tiny_a_dir):
+    root = Path(__file__).resolve().parents[1]
+    proc = subprocess.run([sys.executable, "-m", "tokenmill_b200.generate", "--model", str(tiny_a_dir), "--dtype",
+                           "float32", "--kv-cache-mb", "4", "--max-model-len", "128", "--prompt-ids", "5,6,7",
+                           "--prompt-ids", "9", "--max-tokens", "5", "--ignore-eos"],
+                          capture_output=True, text=True, cwd=root, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    rows = [json.loads(line) for line in proc.stdout.splitlines() if line.startswith("{")]
+    assert [r["prompt_ids"] for r in rows] == [[5, 6, 7], [9]] and all(len(r["output_ids"]) == 5 for r in rows)
+    cfg, w = load_plain(tiny_a_dir)
+    assert rows[0]["output_ids"] == plain_greedy(cfg, w, [5, 6, 7], 5)

@@ -1,0 +1,297 @@
+"""Each kernel alone against its plain float32 reference, at sizes other than the engine tests use:
+odd widths, head sizes in steps of 16, many groupings, several page sizes, float32 and bfloat16."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from plain_qwen2 import (plain_apply_rope, plain_causal_attention, plain_filtered_probs, plain_inverse_cdf,
+                         plain_rmsnorm, plain_rope_tables, plain_silu)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, ref, f32=2e-5, bf16=1.5e-2):
+    return (f32 if dtype == torch.float32 else bf16) * max(1e-6, float(ref.abs().max()))
+
+
+def _ops():
+    from tokenmill_b200.kernels import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H", [(1, 16), (7, 100), (33, 896), (5, 3000), (3, 12288)])
+def test_add_rmsnorm(dtype, T, H):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T * 1000 + H)
+    resid = torch.randn(T, H, generator=g)
+    branch = torch.randn(T, H, generator=g).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    eps = 1e-5
+    d_res = resid.to(DEV)
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(d_res, w.to(DEV), eps, out, branch=branch.to(DEV))
+    x = resid + branch.float()
+    assert torch.equal(d_res.cpu(), x)                           # the 32-bit sum is stored back
+    ref = plain_rmsnorm(x, w, eps)
+    assert (out.float().cpu() - ref).abs().max() <= tol(dtype, ref)
+    # norm only, selected rows, the stream untouched
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(d_res, w.to(DEV), eps, out2, rows=rows)
+    assert torch.equal(d_res.cpu(), x)
+    assert (out2.float().cpu() - ref[[T - 1, 0]]).abs().max() <= tol(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_gather_and_partials(dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    V, H, T = 301, 72, 9
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    w = torch.rand(H, generator=g) + 0.5
+    resid = torch.full((T, H), 7.0, device=DEV)                  # stale content must be overwritten
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(resid, w.to(DEV), 1e-6, out, ids=ids.to(DEV), table=table.to(DEV))
+    x = table.float()[ids.long()]
+    assert torch.equal(resid.cpu(), x)
+    ref = plain_rmsnorm(x, w, 1e-6)
+    assert (out.float().cpu() - ref).abs().max() <= tol(dtype, ref)
+    parts = torch.randn(3, T, H, generator=g)
+    ops.add_rmsnorm(resid, w.to(DEV), 1e-6, out, partials=parts.to(DEV))
+    x2 = x + ((parts[0] + parts[1]) + parts[2])
+    assert (resid.cpu() - x2).abs().max() <= 1e-6
+    assert (out.float().cpu() - plain_rmsnorm(x2, w, 1e-6)).abs().max() <= tol(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,D,page", [(4, 2, 16, 16), (3, 1, 32, 8), (14, 2, 64, 16), (5, 5, 48, 4), (8, 1, 128, 32)])
+def test_qkv_rope_write(dtype, nh, nkv, D, page):
+    ops = _ops()
+    g = torch.Generator().manual_seed(nh * 100 + D)
+    T, P, pages = 11, 300, 6
+    width = (nh + 2 * nkv) * D
+    qkv = torch.randn(T, width, generator=g).to(dtype)
+    bias = 0.3 * torch.randn(width, generator=g)
+    pos = torch.tensor([0, 1, 2, 3, 299, 17, 18, 19, 100, 101, 255], dtype=torch.int32)
+    cos, sin = plain_rope_tables(P, D, 10000.0)
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    kc = torch.zeros(pages, page, nkv, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, nh, D, dtype=dtype, device=DEV)
+    ops.qkv_rope_write(qkv.to(DEV), bias.to(DEV), pos.to(DEV), cos[:, :D // 2].contiguous().to(DEV),
+                       sin[:, :D // 2].contiguous().to(DEV), slots.to(DEV), q_out, kc, vc, nh, nkv, D)
+    x = qkv.float() + bias
+    q = plain_apply_rope(x[:, :nh * D].view(T, nh, D), cos, sin, pos)
+    k = plain_apply_rope(x[:, nh * D:(nh + nkv) * D].view(T, nkv, D), cos, sin, pos)
+    v = x[:, (nh + nkv) * D:].view(T, nkv, D)
+    f32 = 0 if dtype == torch.float32 else None
+    def close(a, b):
+        d = (a.float().cpu() - b).abs().max()
+        return d == 0 if f32 == 0 else d <= tol(dtype, b)
+    assert close(q_out, q)                                        # float32: bit-equal, products not fused
+    flat_k, flat_v = kc.view(-1, nkv, D), vc.view(-1, nkv, D)
+    assert close(flat_k[slots.long().to(DEV)], k) and close(flat_v[slots.long().to(DEV)], v)
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert float(flat_k[untouched.to(DEV)].abs().max()) == 0      # nothing written elsewhere
+
+
+def _paged_case(nh, nkv, D, page, q_lens, befores, dtype, seed, window=0):
+    """Random requests laid out in a shuffled paged cache; returns device tensors and the plain result."""
+    from tokenmill_b200.engine.batch import tiles_for
+    import numpy as np
+
+    g = torch.Generator().manual_seed(seed)
+    S = len(q_lens)
+    G = nh // nkv
+    totals = [b + n for b, n in zip(befores, q_lens)]
+    n_pages = sum(-(-t // page) for t in totals) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.randn(n_pages, page, nkv, D, generator=g).to(dtype)     # stale noise in every unused slot
+    vc = torch.randn(n_pages, page, nkv, D, generator=g).to(dtype)
+    W = max(-(-t // page) for t in totals)
+    table = torch.zeros(S, W, dtype=torch.int32)
+    qs, refs = [], []
+    for s in range(S):
+        k = torch.randn(totals[s], nkv, D, generator=g).to(dtype)
+        v = torch.randn(totals[s], nkv, D, generator=g).to(dtype)
+        q = torch.randn(q_lens[s], nh, D, generator=g).to(dtype)
+        if totals[s] > 40:                                           # one far key dominates one query head
+            q[-1, 0] = 0
+            q[-1, 0, 0] = 6.0
+            k[3, 0] = 0
+            k[3, 0, 0] = 6.0 * math.sqrt(D) / 1.5
+        for i in range(-(-totals[s] // page)):
+            table[s, i] = perm.pop()
+            lo, hi = i * page, min((i + 1) * page, totals[s])
+            kc[table[s, i], :hi - lo] = k[lo:hi]
+            vc[table[s, i], :hi - lo] = v[lo:hi]
+        qs.append(q)
+        refs.append(plain_causal_attention(q.float(), k.float(), v.float(), D ** -0.5, window=window or None))
+    q_all = torch.cat(qs)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    tile_seq, tile_row0 = tiles_for(np.array(q_lens, dtype=np.int32), G)
+    seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), torch.tensor(q_lens))
+    dev = lambda t: t.to(DEV)
+    return dict(q=dev(q_all), kc=dev(kc), vc=dev(vc), table=dev(table), cu=dev(cu),
+                before=dev(torch.tensor(befores, dtype=torch.int32)), tile_seq=dev(torch.from_numpy(tile_seq)),
+                tile_row0=dev(torch.from_numpy(tile_row0)), n_tiles=len(tile_seq), seq_of=dev(seq_of),
+                ref=torch.cat(refs))
+
+
+ATTN_SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (14, 2, 64, 16), (6, 3, 48, 5), (12, 2, 128, 32), (40, 1, 16, 16),
+               (2, 2, 256, 16), (5, 1, 80, 1)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,D,page", ATTN_SHAPES)
+def test_paged_attention_mixed_batch(dtype, nh, nkv, D, page):
+    """Prompt portions beside decoded tokens: whole prompts, later portions, single tokens."""
+    ops = _ops()
+    c = _paged_case(nh, nkv, D, page, q_lens=[37, 1, 5, 1, 64, 2], befores=[0, 130, 59, 0, 31, 300], dtype=dtype,
+                    seed=nh + D)
+    out = torch.empty_like(c["q"])
+    ops.paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["tile_seq"], c["tile_row0"],
+                        c["n_tiles"], out, scale=D ** -0.5)
+    diff = (out.float().cpu() - c["ref"]).abs().max()
+    assert diff <= tol(dtype, c["ref"], f32=1e-5, bf16=1e-2), diff
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,D,page", [(14, 2, 64, 16), (3, 1, 32, 8), (8, 8, 16, 4), (6, 1, 128, 16)])
+def test_paged_attention_split_keys_decode(dtype, nh, nkv, D, page):
+    """Decoded tokens over long contexts, keys cut at multiples of 256 and merged by the second kernel;
+    lengths sit on and around the cuts."""
+    ops = _ops()
+    befores = [0, 255, 256, 257, 511, 1000, 31]
+    c = _paged_case(nh, nkv, D, page, q_lens=[1] * len(befores), befores=befores, dtype=dtype, seed=D)
+    T = len(befores)
+    max_splits = -(-1001 // 256)
+    part_acc = torch.full((T * nh * max_splits * D,), float("nan"), device=DEV)
+    part_ml = torch.full((T * nh * max_splits * 2,), float("nan"), device=DEV)
+    out = torch.empty_like(c["q"])
+    ops.paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["tile_seq"], c["tile_row0"],
+                        c["n_tiles"], out, scale=D ** -0.5, split_keys=256, max_splits=max_splits,
+                        part_acc=part_acc, part_ml=part_ml, seq_of_token=c["seq_of"])
+    diff = (out.float().cpu() - c["ref"]).abs().max()
+    assert diff <= tol(dtype, c["ref"], f32=1e-5, bf16=1e-2), diff
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 32, 33, 100])
+def test_paged_attention_window_edge(dtype, window):
+    """A key exactly at the window's edge counts, the one before it does not."""
+    ops = _ops()
+    nh, nkv, D, page = 4, 2, 32, 8
+    c = _paged_case(nh, nkv, D, page, q_lens=[50, 1, 3], befores=[20, 140, 64], dtype=dtype, seed=window, window=window)
+    out = torch.empty_like(c["q"])
+    ops.paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["tile_seq"], c["tile_row0"],
+                        c["n_tiles"], out, scale=D ** -0.5, window=window)
+    diff = (out.float().cpu() - c["ref"]).abs().max()
+    assert diff <= tol(dtype, c["ref"], f32=1e-5, bf16=1e-2), diff
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 16), (9, 160), (4, 4864), (130, 77)])
+def test_swiglu(dtype, T, I):
+    ops = _ops()
+    gu = (3 * torch.randn(T, 2 * I, generator=torch.Generator().manual_seed(I))).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    ref = plain_silu(gu.float()[:, :I]) * gu.float()[:, I:]
+    assert (out.float().cpu() - ref).abs().max() <= tol(dtype, ref, f32=1e-6, bf16=8e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (64, 64, 16), (130, 257, 896), (3, 1000, 4864)])
+def test_gemm_f32(M, N, K):
+    ops = _ops()
+    g = torch.Generator().manual_seed(M + N + K)
+    a, w, b = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
+    ref = (a.double() @ w.double().T + b.double()).float()
+    out = torch.empty(M, N, device=DEV)
+    ops.linear(a.to(DEV), w.to(DEV), bias=b.to(DEV), out=out)
+    assert (out.cpu() - ref).abs().max() <= 3e-6 * math.sqrt(K) * max(1.0, float(ref.abs().max()))
+    # a row's result does not depend on the rows beside it
+    one = ops.linear(a[:1].contiguous().to(DEV), w.to(DEV))
+    many = ops.linear(a.to(DEV), w.to(DEV))
+    assert torch.equal(one[0], many[0])
+
+
+def test_linear_bf16_library_product_keeps_fp32_accumulation():
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    x, w = torch.randn(9, 896, generator=g).bfloat16(), torch.randn(301, 896, generator=g).bfloat16()
+    ref = x.float() @ w.float().T
+    out32 = ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and (out32.cpu() - ref).abs().max() <= 2e-4 * ref.abs().max()
+    out16 = ops.linear(x.to(DEV), w.to(DEV))
+    assert out16.dtype == torch.bfloat16 and (out16.float().cpu() - ref).abs().max() <= 6e-3 * ref.abs().max()
+
+
+@pytest.mark.parametrize("n,V", [(1, 5), (3, 1000), (2, 151936), (4, 1025)])
+def test_argmax_lowest_index_on_ties(n, V):
+    ops = _ops()
+    logits = torch.randn(n, V, generator=torch.Generator().manual_seed(V))
+    logits[0, V // 2] = 50.0
+    logits[0, V - 1] = 50.0                                        # a tie: the lower index wins
+    got = ops.argmax(logits.to(DEV)).cpu()
+    assert got.tolist() == logits.argmax(-1).tolist() and got[0] == V // 2
+
+
+@pytest.mark.parametrize("V", [7, 1000, 151936])
+def test_sampling_matches_the_plain_rules(V):
+    ops = _ops()
+    g = torch.Generator().manual_seed(V)
+    n = 12
+    logits = 3 * torch.randn(n, V, generator=g)
+    temps = torch.tensor([1.0, 0.7, 1.3, 0.8] * 3)
+    top_k = torch.tensor([-1, 5, -1, 3, 0, 50, -1, 2, 1000000, 4, -1, 6], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 0.3, 0.95, 0.01, 1.0, 1.0, 0.7, 0.6, 0.99])
+    u = torch.rand(n, generator=g)
+    u[0], u[1] = 0.0, 0.999999
+    got = ops.sample(logits.to(DEV), temps.to(DEV), top_k.to(DEV), top_p.to(DEV), u.to(DEV)).cpu().tolist()
+    for i in range(n):
+        probs = plain_filtered_probs(logits[i], float(temps[i]), int(top_k[i]), float(top_p[i]))
+        assert probs[got[i]] > 0, f"row {i}: token {got[i]} lies outside the kept set"
+        cdf = probs.cumsum(0)
+        lo = float(cdf[got[i]] - probs[got[i]])
+        assert lo - 1e-5 <= float(u[i]) <= float(cdf[got[i]]) + 1e-5, (i, got[i], plain_inverse_cdf(probs, float(u[i])))
+    # rows indirection: draw i reads row rows[i]
+    rows = torch.tensor([3, 3, 0], dtype=torch.int32)
+    again = ops.sample(logits.to(DEV), temps[[3, 3, 0]].to(DEV), top_k[[3, 3, 0]].to(DEV), top_p[[3, 3, 0]].to(DEV),
+                       u[[3, 3, 0]].to(DEV), rows=rows.to(DEV)).cpu().tolist()
+    assert again == [got[3], got[3], got[0]]
+
+
+def test_sampling_frequencies_follow_the_distribution():
+    ops = _ops()
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]]).repeat(4000, 1)
+    u = torch.rand(4000, generator=torch.Generator().manual_seed(1))
+    t = torch.full((4000,), 0.8)
+    got = ops.sample(logits.to(DEV), t.to(DEV), torch.full((4000,), -1, dtype=torch.int32, device=DEV),
+                     torch.ones(4000, device=DEV), u.to(DEV)).cpu()
+    freq = torch.bincount(got.long(), minlength=5).float() / 4000
+    assert (freq - torch.softmax(logits[0] / 0.8, 0)).abs().max() < 0.03
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from tokenmill_b200.kernels.lib import KernelError
+    ops = _ops()
+    q = torch.zeros(1, 2, 24, device=DEV)                            # head size 24 is no multiple of 16
+    kc = torch.zeros(2, 4, 1, 24, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="unsupported shape"):
+        ops.paged_attention(q, kc, kc.clone(), z.view(1, 2), z, z[:1], z[:1], z[:1], 1, torch.empty_like(q), scale=1.0)
+    with pytest.raises(KernelError, match="CPU"):
+        ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
+    with pytest.raises(KernelError, match="float32 or bfloat16"):
+        ops.swiglu(torch.zeros(2, 4, device=DEV, dtype=torch.float16), torch.zeros(2, 2, device=DEV, dtype=torch.float16))

@@ -22,6 +22,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pool import CachePools
+from ..kernels import lib
 from ..parts.attention import SPLIT_KEYS, AttentionScratch
 from ..parts.base import StepInputs
 from ..parts.model import DecoderModel
@@ -46,6 +47,7 @@ class ModelRunner:
         self.graph_max_batch = min(cuda_graph_max_batch, max_num_seqs) if cuda_graphs else 0
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
+        self.kernels_per_graph: dict[int, int] = {}
         self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0}
         if self.graph_max_batch:
             if any(s < 0 for s in pools.sink):
@@ -133,8 +135,10 @@ class _DecodeGraph:
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
+        launched_before = lib.launch_count
         with torch.cuda.graph(self.graph, pool=runner._graph_pool):
             self.logits = runner.model.forward(self.inputs, runner.layer_caches)
+        runner.kernels_per_graph[bucket] = lib.launch_count - launched_before   # this library's kernels per replay
         if runner._graph_pool is None:
             runner._graph_pool = self.graph.pool()
         runner.scratch.frozen = True

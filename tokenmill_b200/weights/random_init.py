@@ -54,7 +54,7 @@ def write_random_model(folder: str | Path, config: dict, seed: int = 0, store_dt
     model = DecoderModel(spec, torch.float32, torch.device("cpu"))      # declarations only; nothing runs
     tensors = random_tensors(model, seed, _STORE[store_dtype])
     (folder / "config.json").write_text(json.dumps(config, indent=1))
-    save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt", "seed": str(seed)})
+    save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt"})
     return folder
 
 
