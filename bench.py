@@ -221,9 +221,17 @@ def run_ours(args) -> dict:
     try:
         cfg = EngineConfig(model=tmp.name, dtype="bfloat16", block_size=PAGE, max_model_len=CONTEXT, max_num_seqs=64,
                            max_num_batched_tokens=4 * PROMPT_LEN, kv_cache_mb=64 * CONTEXT * info["kv_bytes_per_token"]
-                           / 2 ** 20, watermark=0.0, cuda_graphs=True, cuda_graph_max_batch=64)
+                           / 2 ** 20, watermark=0.0, cuda_graphs=not args.no_graphs, cuda_graph_max_batch=64)
         engine = LLMEngine(cfg)
         lib.load()
+        if args.only:                                             # a small case for profilers: no JSON contract
+            if args.only == "prefill":
+                print(json.dumps({"only": "prefill", **prefill_timed(engine, args.prefill_tokens, reps=args.steps)}))
+            else:
+                batch = int(args.only.split("_b")[1])
+                r = decode_device_timed(engine, batch, args.steps, args.warmup)
+                print(json.dumps({"only": args.only, "ms_per_step": r["ms_per_step"], "tok_s": r["tok_s"]}))
+            return {}
         sampler = ClockSampler()
         # warm every path once before the clocks are sampled
         decode_device_timed(engine, BATCH, 4, 3)
@@ -356,6 +364,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
+    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill' or 'decode_b<batch>' and print its time")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
@@ -363,7 +374,8 @@ def main() -> int:
         return 2
     args.warmup = max(args.warmup, 3)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
-    print(json.dumps(result), flush=True)
+    if result:
+        print(json.dumps(result), flush=True)
     return 0
 
 

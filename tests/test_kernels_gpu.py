@@ -186,6 +186,29 @@ def test_paged_attention_split_keys_decode(dtype, nh, nkv, D, page):
     assert diff <= tol(dtype, c["ref"], f32=1e-5, bf16=1e-2), diff
 
 
+@pytest.mark.parametrize("nh,nkv,D,page,q_lens,window", [
+    (14, 2, 64, 16, [1] * 7, 0), (12, 2, 128, 16, [1] * 7, 0), (16, 1, 64, 8, [1] * 7, 0), (4, 4, 128, 1, [1] * 7, 0),
+    (14, 2, 64, 16, [2, 1, 2, 1, 1, 2, 1], 0), (8, 4, 64, 5, [8, 1, 3, 1, 1, 2, 5], 0), (14, 2, 64, 16, [1] * 7, 100),
+    (6, 2, 128, 32, [4, 1, 1, 5, 1, 2, 1], 300),
+])
+def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
+    """The bfloat16 decode kernel: few query rows per request, long contexts on and around the key cuts,
+    one far key that dominates, windows, odd page sizes."""
+    ops = _ops()
+    befores = [0, 255, 256, 257, 511, 1000, 63]
+    c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=D + nh, window=window)
+    T = sum(q_lens)
+    max_splits = -(-(1000 + max(q_lens)) // 256)
+    part_acc = torch.full((T * nh * max_splits * D,), float("nan"), device=DEV)
+    part_ml = torch.full((T * nh * max_splits * 2,), float("nan"), device=DEV)
+    out = torch.empty_like(c["q"])
+    ops.decode_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["seq_of"], len(q_lens), out,
+                              scale=D ** -0.5, window=window, split_keys=256, max_splits=max_splits,
+                              part_acc=part_acc, part_ml=part_ml)
+    diff = (out.float().cpu() - c["ref"]).abs().max()
+    assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 32, 33, 100])
 def test_paged_attention_window_edge(dtype, window):

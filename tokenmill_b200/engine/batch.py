@@ -119,7 +119,7 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
 
     dev = host.to(device, non_blocking=True)
     max_q = int(q_lens.max())
-    use_split = split_keys if (split_keys and max_kv > split_keys) else 0
+    use_split = split_keys
     return StepInputs(
         n_tokens=T, n_seqs=S, token_ids=dev[lay.token_ids], positions=dev[lay.positions],
         seq_of_token=dev[lay.seq_of_token], cu_q=dev[lay.cu_q], kv_before=dev[lay.kv_before],

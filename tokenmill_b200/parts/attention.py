@@ -112,14 +112,23 @@ class GroupedQueryAttention:
         return ops.linear(out.view(T, self.q_size), self.w_o)
 
     def attend(self, q: torch.Tensor, step: StepInputs, cache: LayerCache, out: torch.Tensor) -> None:
+        """Pick the attention kernel for this step's shape: the tensor-core decode kernel when every
+        request brings at most 16 query rows per kv head (bfloat16, head size 64 or 128), else the
+        shape-generic kernel, with its keys split when the queries are few and the contexts long."""
         G = self.nh // self.nkv
+        rows = step.max_q_len * G
+        if step.split_keys and rows <= 16 and self.dtype == torch.bfloat16 and self.D in (64, 128):
+            part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, step.max_splits, self.D)
+            ops.decode_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
+                                      step.kv_before, step.seq_of_token, step.n_seqs, out, scale=self.scale,
+                                      window=self.window, split_keys=step.split_keys, max_splits=step.max_splits,
+                                      part_acc=part_acc, part_ml=part_ml)
+            return
         tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
-        split = step.split_keys if step.max_q_len * G <= 32 else 0
         kw = {}
-        if split:
-            max_splits = step.max_splits
-            part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, max_splits, self.D)
-            kw = dict(split_keys=split, max_splits=max_splits, part_acc=part_acc, part_ml=part_ml,
+        if step.split_keys and rows <= 32 and step.max_splits > 1:
+            part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, step.max_splits, self.D)
+            kw = dict(split_keys=step.split_keys, max_splits=step.max_splits, part_acc=part_acc, part_ml=part_ml,
                       seq_of_token=step.seq_of_token)
         ops.paged_attention(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q, step.kv_before,
                             tile_seq, tile_row0, n_tiles, out, scale=self.scale, window=self.window, **kw)
