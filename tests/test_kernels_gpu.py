@@ -209,6 +209,29 @@ def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
     assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
 
 
+@pytest.mark.parametrize("nh,nkv,D,page,window", [
+    (14, 2, 64, 16, 0), (12, 2, 128, 16, 0), (3, 3, 64, 1, 0), (4, 1, 128, 7, 0), (14, 2, 64, 16, 70), (4, 2, 64, 8, 1),
+    (6, 2, 128, 32, 200),
+])
+def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
+    """The bfloat16 prompt kernel: whole prompts, later portions that start off a tile or page edge, short
+    portions and single tokens in the same launch; tiles that end inside a key block; windows."""
+    from tokenmill_b200.engine.batch import token_tiles
+    import numpy as np
+    ops = _ops()
+    q_lens, befores = [200, 1, 64, 3, 129, 65, 17], [0, 300, 64, 5, 77, 191, 1000]
+    c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=D + nh + window,
+                    window=window)
+    tile_seq, tile_tok0 = token_tiles(np.array(q_lens, dtype=np.int32))
+    assert len(tile_seq) == sum(-(-n // 64) for n in q_lens)
+    out = torch.full_like(c["q"], float("nan"))
+    ops.prefill_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"],
+                               torch.from_numpy(tile_seq).to(DEV), torch.from_numpy(tile_tok0).to(DEV), len(tile_seq),
+                               out, scale=D ** -0.5, window=window)
+    diff = (out.float().cpu() - c["ref"]).abs().max()
+    assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 32, 33, 100])
 def test_paged_attention_window_edge(dtype, window):
@@ -260,7 +283,77 @@ def test_linear_bf16_library_product_keeps_fp32_accumulation():
     assert out16.dtype == torch.bfloat16 and (out16.float().cpu() - ref).abs().max() <= 6e-3 * ref.abs().max()
 
 
-@pytest.mark.parametrize("n,V", [(1, 5), (3, 1000), (2, 151936), (4, 1025)])
+@pytest.mark.parametrize("T,N,K,rows,splits", [
+    (1, 896, 896, 8, 1), (8, 904, 896, 8, 1), (17, 1000, 4864, 8, 2), (64, 896, 4864, 8, 4), (5, 3000, 200, 64, 1),
+    (33, 151936, 896, 64, 1), (64, 72, 40, 16, 1), (3, 100, 1536, 32, 3),
+])
+def test_skinny_linear(T, N, K, rows, splits):
+    """The decode-step product: plain store in either dtype, bias, K-range partial products."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + N + K)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, generator=g)
+    ref = x.float() @ w.float().T
+    dx, dw = x.to(DEV), w.to(DEV)
+    assert ops.skinny_ok(dx, dw, allow_split=True) == (T <= ops.SKINNY_MAX_TOKENS)    # the engine's own policy
+    if splits > 1:
+        parts = ops.skinny_linear(dx, dw, k_splits=splits, rows_per_block=rows)
+        assert parts.shape == (splits, T, N) and parts.dtype == torch.float32
+        assert (parts.sum(0).cpu() - ref).abs().max() <= 2e-5 * K ** 0.5 * max(1.0, float(ref.abs().max()))
+    else:
+        out32 = ops.skinny_linear(dx, dw, bias=b.to(DEV), out_dtype=torch.float32, rows_per_block=rows)
+        assert (out32.cpu() - (ref + b)).abs().max() <= 2e-5 * K ** 0.5 * max(1.0, float(ref.abs().max()))
+        out16 = ops.skinny_linear(dx, dw, rows_per_block=rows)
+        assert out16.dtype == torch.bfloat16 and (out16.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("T,H,nh,nkv,D", [(1, 896, 14, 2, 64), (8, 896, 14, 2, 64), (40, 1536, 12, 2, 128), (7, 72, 3, 1, 32),
+                                          (64, 264, 5, 5, 48), (2, 64, 4, 2, 16)])
+def test_skinny_qkv_with_rope_and_cache_write(T, H, nh, nkv, D):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + H + D)
+    width = (nh + 2 * nkv) * D
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w = (torch.randn(width, H, generator=g) / H ** 0.5).bfloat16()
+    bias = 0.3 * torch.randn(width, generator=g)
+    pos = torch.randint(0, 500, (T,), generator=g, dtype=torch.int32)
+    cos, sin = plain_rope_tables(500, D, 1e6)
+    page, pages = 8, 20
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    kc = torch.zeros(pages, page, nkv, D, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, nh, D, dtype=torch.bfloat16, device=DEV)
+    dx, dw = x.to(DEV), w.to(DEV)
+    ops.skinny_qkv_rope_write(dx, dw, bias.to(DEV), pos.to(DEV), cos[:, :D // 2].contiguous().to(DEV),
+                              sin[:, :D // 2].contiguous().to(DEV), slots.to(DEV), q_out, kc, vc, nh, nkv, D)
+    y = x.float() @ w.float().T + bias
+    q = plain_apply_rope(y[:, :nh * D].view(T, nh, D), cos, sin, pos)
+    k = plain_apply_rope(y[:, nh * D:(nh + nkv) * D].view(T, nkv, D), cos, sin, pos)
+    v = y[:, (nh + nkv) * D:].view(T, nkv, D)
+    t = 1e-2 * float(y.abs().max())
+    assert (q_out.float().cpu() - q).abs().max() <= t
+    assert (kc.view(-1, nkv, D)[slots.long().to(DEV)].float().cpu() - k).abs().max() <= t
+    assert (vc.view(-1, nkv, D)[slots.long().to(DEV)].float().cpu() - v).abs().max() <= t
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert float(kc.view(-1, nkv, D)[untouched.to(DEV)].abs().max()) == 0
+
+
+@pytest.mark.parametrize("T,H,I", [(1, 896, 4864), (8, 896, 4864), (64, 1536, 8960), (9, 96, 160), (20, 64, 100)])
+def test_skinny_gate_up_swiglu(T, H, I):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + H + I)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w = (2 * torch.randn(2 * I, H, generator=g) / H ** 0.5).bfloat16()
+    out = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
+    ops.skinny_gate_up_swiglu(x.to(DEV), w.to(DEV), out)
+    y = x.float() @ w.float().T
+    ref = plain_silu(y[:, :I]) * y[:, I:]
+    assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("n,V", [(1, 5), (3, 1000), (2, 151936), (4, 1025), (64, 151936), (3, 4097)])
 def test_argmax_lowest_index_on_ties(n, V):
     ops = _ops()
     logits = torch.randn(n, V, generator=torch.Generator().manual_seed(V))

@@ -72,6 +72,77 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __r
   }
 }
 
+// Two-stage arg-max for wide vocabularies: blockIdx.y takes one chunk of the row and leaves its best
+// (value, lowest index); the final kernel reduces the chunks. One block per row would read 600 KB alone.
+constexpr int kArgmaxChunk = 4096;
+
+__global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restrict__ logits, int V,
+                                                          long long row_stride, float* __restrict__ cval,
+                                                          int* __restrict__ cidx, int n_chunks) {
+  __shared__ float sval[8];
+  __shared__ int sidx[8];
+  const float* row = logits + (size_t)blockIdx.x * row_stride;
+  const int begin = blockIdx.y * kArgmaxChunk, end = min(V, begin + kArgmaxChunk);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sval[warp] = best;
+    sidx[warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sval[w] > best || (sval[w] == best && sidx[w] < bi)) {
+        best = sval[w];
+        bi = sidx[w];
+      }
+    cval[(size_t)blockIdx.x * n_chunks + blockIdx.y] = best;
+    cidx[(size_t)blockIdx.x * n_chunks + blockIdx.y] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(32) argmax_final_kernel(const float* __restrict__ cval,
+                                                         const int* __restrict__ cidx, int n_chunks,
+                                                         int* __restrict__ out) {
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < n_chunks; c += 32) {
+    const float v = cval[(size_t)blockIdx.x * n_chunks + c];
+    const int i = cidx[(size_t)blockIdx.x * n_chunks + c];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+}
+
 // Block-wide deterministic sum of one float per thread; every thread gets the total.
 __device__ __forceinline__ float block_total(float v, float* red) { return block_sum(v, red); }
 
@@ -216,11 +287,23 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
 
 }  // namespace tmk
 
+// How many chunks tm_argmax cuts a row of V logits into (scratch: n_rows * chunks floats and ints).
+extern "C" int tm_argmax_chunks(int V) { return (V + tmk::kArgmaxChunk - 1) / tmk::kArgmaxChunk; }
+
+// scratch_val / scratch_idx: [n_rows, tm_argmax_chunks(V)] (may be null when V fits one chunk).
 extern "C" int tm_argmax(const float* logits, int n_rows, int V, long long row_stride, int* out,
-                         cudaStream_t stream) {
+                         float* scratch_val, int* scratch_idx, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
-  tmk::argmax_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, out);
+  const int chunks = tm_argmax_chunks(V);
+  if (chunks <= 1) {
+    tmk::argmax_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, out);
+    return tmk::launch_status();
+  }
+  if (!scratch_val || !scratch_idx) return TM_ERR_SCRATCH_TOO_SMALL;
+  tmk::argmax_chunk_kernel<<<dim3(n_rows, chunks), 256, 0, stream>>>(logits, V, row_stride, scratch_val,
+                                                                    scratch_idx, chunks);
+  tmk::argmax_final_kernel<<<n_rows, 32, 0, stream>>>(scratch_val, scratch_idx, chunks, out);
   return tmk::launch_status();
 }
 

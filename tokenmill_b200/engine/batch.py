@@ -62,6 +62,20 @@ def tiles_for(q_lens: np.ndarray, group_size: int) -> tuple[np.ndarray, np.ndarr
     return tile_seq.astype(np.int32), tile_row0.astype(np.int32)
 
 
+TOKEN_TILE = 64      # tokens per block of the tensor-core prompt attention; its tile list has key 0
+
+
+def token_tiles(q_lens: np.ndarray, tile: int = TOKEN_TILE) -> tuple[np.ndarray, np.ndarray]:
+    """(request, first token within its portion) of every tile of ``tile`` consecutive tokens. Later
+    tiles of a request see more keys, so they are listed first: the longest blocks start earliest."""
+    per_seq = (q_lens + tile - 1) // tile
+    tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), per_seq)
+    first = np.cumsum(per_seq) - per_seq
+    tok0 = (np.arange(tile_seq.size, dtype=np.int32) - np.repeat(first, per_seq).astype(np.int32)) * tile
+    order = np.argsort(-tok0, kind="stable")
+    return tile_seq[order].astype(np.int32), tok0[order].astype(np.int32)
+
+
 def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: torch.device,
                       group_sizes: list[int], *, scratch=None, split_keys: int = 0,
                       min_table_width: int = 0) -> StepInputs:
@@ -82,6 +96,7 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
         if any(not (0 <= w < len(e.tokens)) for w in e.want):
             raise ValueError(f"entry {i}: a wanted place lies outside its {len(e.tokens)} tokens")
     tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
+    tile_arrays[0] = token_tiles(q_lens)
     lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()})
 
     host = torch.empty(lay.total, dtype=torch.int32, pin_memory=device.type == "cuda")

@@ -135,6 +135,25 @@ def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
     return out
 
 
+def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                           cu_q: torch.Tensor, kv_before: torch.Tensor, tile_seq: torch.Tensor,
+                           tile_tok0: torch.Tensor, n_tiles: int, out: torch.Tensor, *, scale: float,
+                           window: int = 0) -> torch.Tensor:
+    """Tensor-core causal attention for prompt portions (bfloat16, head size 64 or 128). tile_seq /
+    tile_tok0 list the 64-token tiles: request, and first token within the request's portion."""
+    T, nh, D = q.shape
+    page_size, nkv = kcache.shape[1], kcache.shape[2]
+    bf = torch.bfloat16
+    if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
+        raise lib.KernelError("prefill_attention_bf16: q / cache / out shapes disagree")
+    lib.call("tm_prefill_attention_bf16", _req(q, "q", bf), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf),
+             _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
+             _req(kv_before, "kv_before", torch.int32), _req(tile_seq, "tile_seq", torch.int32),
+             _req(tile_tok0, "tile_tok0", torch.int32), n_tiles, _req(out, "out", bf), nh, nkv, D, page_size,
+             float(scale), int(window), _stream())
+    return out
+
+
 def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """gu [T, 2 I] (gate columns first) -> out [T, I] = silu(gate) * up."""
     T, two_i = gu.shape
@@ -188,7 +207,13 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
         out = torch.empty(n, dtype=torch.int32, device=logits.device)
     if not logits.is_cuda or logits.dtype != torch.float32:
         raise lib.KernelError("argmax: float32 logits on the GPU")
-    lib.call("tm_argmax", logits.data_ptr(), n, V, logits.stride(0), _req(out, "out", torch.int32), _stream())
+    chunks = lib.load().tm_argmax_chunks(V)
+    sval = sidx = None
+    if chunks > 1:                      # wide vocabulary: per-chunk winners, then a final pick
+        sval = torch.empty(n * chunks, dtype=torch.float32, device=logits.device)
+        sidx = torch.empty(n * chunks, dtype=torch.int32, device=logits.device)
+    lib.call("tm_argmax", logits.data_ptr(), n, V, logits.stride(0), _req(out, "out", torch.int32),
+             _opt(sval, "scratch"), _opt(sidx, "scratch"), _stream())
     return out
 
 
@@ -208,4 +233,71 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
              _req(top_k, "top_k", torch.int32), _req(top_p, "top_p", torch.float32),
              _req(uniform, "uniform", torch.float32), _opt(rows, "rows", torch.int32),
              _req(out, "out", torch.int32), _stream())
+    return out
+
+
+# --- weight-streaming products for decode steps (bfloat16, at most 64 tokens) -------------------------
+
+SKINNY_MAX_TOKENS = 16             # the kernel takes up to 64; beyond 16 the library product is faster today
+_SKINNY_X_BYTES = 200 * 1024       # shared memory the staged activations may take
+
+
+def _padded_tokens(T: int) -> int:
+    return 16 if T <= 16 else (32 if T <= 32 else 64)
+
+
+def skinny_ok(x: torch.Tensor, w: torch.Tensor, allow_split: bool = False) -> bool:
+    """Whether the weight-streaming kernel takes this product (else the library product does).
+    A product with a fused epilogue cannot cut its K range, so its activations must fit shared memory."""
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
+            and x.shape[0] <= SKINNY_MAX_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()):
+        return False
+    return allow_split or _padded_tokens(x.shape[0]) * (x.shape[1] + 64) * 2 <= _SKINNY_X_BYTES
+
+
+def skinny_k_splits(T: int, K: int) -> int:
+    """Cuts of the K range so that the staged activations fit shared memory."""
+    return max(1, -(-(_padded_tokens(T) * K * 2) // _SKINNY_X_BYTES))
+
+
+def skinny_linear(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
+                  out_dtype: torch.dtype = torch.bfloat16, k_splits: int = 1, rows_per_block: int = 8) -> torch.Tensor:
+    """x [T, K] . w [N, K]^T for T <= 64. k_splits == 1: returns [T, N] in out_dtype. k_splits > 1:
+    returns float32 partial products [k_splits, T, N] for the add+norm kernel to sum."""
+    T, K = x.shape
+    N = w.shape[0]
+    ng = rows_per_block // 8
+    if k_splits > 1:
+        partials = torch.empty((k_splits, T, N), dtype=torch.float32, device=x.device)
+        lib.call("tm_skinny_linear", x.data_ptr(), x.stride(0), w.data_ptr(), None, None, 0, 0, partials.data_ptr(),
+                 k_splits, T, N, K, ng, _stream())
+        return partials
+    out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    lib.call("tm_skinny_linear", x.data_ptr(), x.stride(0), w.data_ptr(), _opt(bias, "bias", torch.float32),
+             out.data_ptr(), N, 1 if out_dtype == torch.float32 else 0, None, 1, T, N, K, ng, _stream())
+    return out
+
+
+def skinny_qkv_rope_write(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor,
+                          cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
+                          kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, D: int) -> None:
+    """The fused q/k/v projection of a decode step with its whole epilogue: bias, position encoding,
+    q to q_out, k and v to their cache slots."""
+    T, K = x.shape
+    if w.shape != ((nh + 2 * nkv) * D, K) or cos.shape[1] * 2 != D:
+        raise lib.KernelError("skinny_qkv_rope_write: shapes do not fit")
+    bf = torch.bfloat16
+    lib.call("tm_skinny_qkv_rope_write", x.data_ptr(), x.stride(0), _req(w, "w", bf), _opt(bias, "bias", torch.float32),
+             _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32),
+             _req(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out", bf),
+             _opt(kcache, "kcache", bf), _opt(vcache, "vcache", bf), T, K, nh, nkv, D, cos.shape[0], _stream())
+
+
+def skinny_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [T, I] = silu(x . gate^T) * (x . up^T), w_gate_up [2 I, K] with the gate rows first."""
+    T, K = x.shape
+    inter = w_gate_up.shape[0] // 2
+    lib.call("tm_skinny_gate_up_swiglu", x.data_ptr(), x.stride(0), _req(w_gate_up, "w_gate_up", torch.bfloat16),
+             _req(out, "out", torch.bfloat16), out.stride(0), T, K, inter, _stream())
     return out

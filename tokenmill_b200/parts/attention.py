@@ -99,17 +99,25 @@ class GroupedQueryAttention:
 
     def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
         T = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv)
         q = torch.empty((T, self.nh, self.D), dtype=self.dtype, device=x.device)
         slot_map = step.slot_maps[cache.group] if cache.writes else None
+        kc, vc = (cache.k, cache.v) if cache.writes else (None, None)
         if self.position is None:
             raise NotImplementedError("an attention mixer without position encoding is not built")
-        ops.qkv_rope_write(qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
-                           cache.k if cache.writes else None, cache.v if cache.writes else None,
-                           self.nh, self.nkv, self.D)
+        if ops.skinny_ok(x, self.w_qkv):
+            # decode step: one kernel streams the fused weight and finishes bias, rotation and cache write
+            ops.skinny_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
+                                      kc, vc, self.nh, self.nkv, self.D)
+        else:
+            qkv = ops.linear(x, self.w_qkv)
+            ops.qkv_rope_write(qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q, kc, vc,
+                               self.nh, self.nkv, self.D)
         out = torch.empty_like(q)
         self.attend(q, step, cache, out)
-        return ops.linear(out.view(T, self.q_size), self.w_o)
+        flat = out.view(T, self.q_size)
+        if ops.skinny_ok(flat, self.w_o, allow_split=True):
+            return ops.skinny_linear(flat, self.w_o, k_splits=ops.skinny_k_splits(T, self.q_size))
+        return ops.linear(flat, self.w_o)
 
     def attend(self, q: torch.Tensor, step: StepInputs, cache: LayerCache, out: torch.Tensor) -> None:
         """Pick the attention kernel for this step's shape: the tensor-core decode kernel when every
@@ -123,6 +131,12 @@ class GroupedQueryAttention:
                                       step.kv_before, step.seq_of_token, step.n_seqs, out, scale=self.scale,
                                       window=self.window, split_keys=step.split_keys, max_splits=step.max_splits,
                                       part_acc=part_acc, part_ml=part_ml)
+            return
+        if self.dtype == torch.bfloat16 and self.D in (64, 128) and 0 in step.tiles:
+            tile_seq, tile_tok0, n_tiles = step.attention_tiles(0)        # tiles of 64 tokens
+            ops.prefill_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
+                                       step.kv_before, tile_seq, tile_tok0, n_tiles, out, scale=self.scale,
+                                       window=self.window)
             return
         tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
         kw = {}

@@ -26,6 +26,12 @@ class Pending:
     ids: torch.Tensor | None = None
     table: torch.Tensor | None = None
 
+    @classmethod
+    def of(cls, y: torch.Tensor) -> "Pending":
+        """A part's output: [T, H] in the activation dtype, or [n, T, H] float32 partial products of a
+        matrix product whose K range was cut (the norm that follows adds them up in index order)."""
+        return cls(partials=y) if y.dim() == 3 else cls(branch=y)
+
     def kwargs(self) -> dict:
         return {"branch": self.branch, "partials": self.partials, "ids": self.ids, "table": self.table}
 
@@ -37,9 +43,9 @@ class PreNormBlock:
 
     def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
         normed = self.mixer_norm.forward(resid, **pending.kwargs())
-        mixed = self.mixer.forward(normed, step, cache)
-        normed = self.feed_forward_norm.forward(resid, branch=mixed)
-        return Pending(branch=self.feed_forward.forward(normed, step))
+        mixed = Pending.of(self.mixer.forward(normed, step, cache))
+        normed = self.feed_forward_norm.forward(resid, **mixed.kwargs())
+        return Pending.of(self.feed_forward.forward(normed, step))
 
 
 register_block("pre_norm", PreNormBlock)

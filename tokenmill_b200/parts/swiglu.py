@@ -31,8 +31,14 @@ class SwiGLUFeedForward:
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+        T = x.shape[0]
+        act = torch.empty((T, self.intermediate_size), dtype=self.dtype, device=x.device)
+        if ops.skinny_ok(x, self.w_gate_up) and ops.skinny_ok(act, self.w_down, allow_split=True):
+            # decode step: two weight-streaming kernels; the activation is the first one's epilogue, and
+            # the second may hand its K-range partials to the norm that follows
+            ops.skinny_gate_up_swiglu(x, self.w_gate_up, act)
+            return ops.skinny_linear(act, self.w_down, k_splits=ops.skinny_k_splits(T, self.intermediate_size))
         gu = ops.linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
         ops.swiglu(gu, act)
         return ops.linear(act, self.w_down)
 
