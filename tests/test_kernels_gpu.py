@@ -216,20 +216,24 @@ def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
 def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
     """The bfloat16 prompt kernel: whole prompts, later portions that start off a tile or page edge, short
     portions and single tokens in the same launch; tiles that end inside a key block; windows."""
-    from tokenmill_b200.engine.batch import token_tiles
+    from tokenmill_b200.engine.batch import packed_tiles
     import numpy as np
     ops = _ops()
     q_lens, befores = [200, 1, 64, 3, 129, 65, 17], [0, 300, 64, 5, 77, 191, 1000]
     c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=D + nh + window,
                     window=window)
-    tile_seq, tile_tok0 = token_tiles(np.array(q_lens, dtype=np.int32))
-    assert len(tile_seq) == sum(-(-n // 64) for n in q_lens)
-    out = torch.full_like(c["q"], float("nan"))
-    ops.prefill_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"],
-                               torch.from_numpy(tile_seq).to(DEV), torch.from_numpy(tile_tok0).to(DEV), len(tile_seq),
-                               out, scale=D ** -0.5, window=window)
-    diff = (out.float().cpu() - c["ref"]).abs().max()
-    assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
+    G = nh // nkv
+    tile_seq, tile_row0 = packed_tiles(np.array(q_lens, dtype=np.int32), np.array(befores, dtype=np.int32), G)
+    assert len(tile_seq) == sum(-(-n * G // 64) for n in q_lens)
+    counters = torch.zeros(2, dtype=torch.int32, device=DEV)
+    for _ in range(2):                                              # the second launch finds the counters at zero
+        out = torch.full_like(c["q"], float("nan"))
+        ops.prefill_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"],
+                                   torch.from_numpy(tile_seq).to(DEV), torch.from_numpy(tile_row0).to(DEV),
+                                   len(tile_seq), counters, out, scale=D ** -0.5, window=window)
+        diff = (out.float().cpu() - c["ref"]).abs().max()
+        assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
+        assert counters.tolist() == [0, 0]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -11,42 +11,71 @@
 // rows are normed and written densely (the final norm before the output matrix, engine/model_runner.py:96)
 // and the residual stream is left untouched. `branch` may also be a stack of `n_partials` 32-bit partial
 // products [n_partials, n_tokens, H] from a split-K matrix product; they are summed in index order.
+// Rows whose width is a multiple of 4 move four elements per access; the order of the row's sum of
+// squares is fixed by the width and the block size alone.
 #include "common.cuh"
 
 namespace tmk {
 
-template <typename T>
+template <typename T, int VEC>   // VEC = 1 or 4 elements per access
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(
     float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ partials,
     int n_partials, long long partial_stride, const int* __restrict__ ids, const T* __restrict__ table,
     const int* __restrict__ rows, const float* __restrict__ weight, float eps, T* __restrict__ out, int H) {
-  extern __shared__ float xs[];  // H floats + 32 for the reduction
+  extern __shared__ __align__(16) float xs[];  // H floats + 32 for the reduction
   float* red = xs + H;
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
+  const bool write_back = !rows && (ids || branch || partials);
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float x;
+  for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+    float x[VEC];
     if (ids) {
-      x = to_float(table[(size_t)ids[src] * H + i]);
+      const T* p = table + (size_t)ids[src] * H + i;
+      if constexpr (VEC == 4) load4<T>(p, x); else x[0] = to_float(p[0]);
     } else {
-      x = resid[(size_t)src * H + i];
-      if (branch) x += to_float(branch[(size_t)src * H + i]);
+      const float* p = resid + (size_t)src * H + i;
+      if constexpr (VEC == 4) load4<float>(p, x); else x[0] = p[0];
+      if (branch) {
+        float b[VEC];
+        const T* q = branch + (size_t)src * H + i;
+        if constexpr (VEC == 4) load4<T>(q, b); else b[0] = to_float(q[0]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] += b[e];
+      }
       if (partials) {
-        float acc = 0.f;
-        for (int p = 0; p < n_partials; ++p) acc += partials[(size_t)p * partial_stride + (size_t)src * H + i];
-        x += acc;
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+        for (int p2 = 0; p2 < n_partials; ++p2) {
+          float v[VEC];
+          const float* q = partials + (size_t)p2 * partial_stride + (size_t)src * H + i;
+          if constexpr (VEC == 4) load4<float>(q, v); else v[0] = q[0];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[e] += v[e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] += acc[e];
       }
     }
-    if (!rows && (ids || branch || partials)) resid[(size_t)src * H + i] = x;
-    xs[i] = x;
-    ss += x * x;
+    if (write_back) {
+      float* p = resid + (size_t)src * H + i;
+      if constexpr (VEC == 4) store4<float>(p, x); else p[0] = x[0];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      xs[i + e] = x[e];
+      ss += x[e] * x[e];
+    }
   }
   const float total = block_sum(ss, red);
   const float rstd = 1.0f / sqrtf(total / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const T normed = from_float<T>(xs[i] * rstd);
-    out[(size_t)r * H + i] = from_float<T>(weight[i] * to_float(normed));
+  for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+    float y[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) y[e] = weight[i + e] * to_float(from_float<T>(xs[i + e] * rstd));
+    T* p = out + (size_t)r * H + i;
+    if constexpr (VEC == 4) store4<T>(p, y); else p[0] = from_float<T>(y[0]);
   }
 }
 
@@ -57,14 +86,17 @@ int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, 
   if (n_rows <= 0) return 0;
   const size_t smem = (size_t)(H + 32) * sizeof(float);
   if (smem > 200 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(branch) |
+                        reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(table) |
+                        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight);
+  const bool vec = H % 4 == 0 && (all & 15) == 0 && (partial_stride % 4 == 0);
+  auto kern = vec ? add_rmsnorm_kernel<T, 4> : add_rmsnorm_kernel<T, 1>;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  add_rmsnorm_kernel<T><<<n_rows, 256, smem, stream>>>(resid, (const T*)branch, partials, n_partials,
-                                                       partial_stride, ids, (const T*)table, rows, weight, eps,
-                                                       (T*)out, H);
+  kern<<<n_rows, 256, smem, stream>>>(resid, (const T*)branch, partials, n_partials, partial_stride, ids,
+                                     (const T*)table, rows, weight, eps, (T*)out, H);
   return launch_status();
 }
 
@@ -79,9 +111,9 @@ extern "C" int tm_add_rmsnorm(int dtype, float* resid, const void* branch, const
                               cudaStream_t stream) {
   if (dtype == TM_DTYPE_F32)
     return tmk::launch_add_rmsnorm<float>(resid, branch, partials, n_partials, partial_stride, ids, table, rows,
-                                         weight, eps, out, n_rows, H, stream);
+                                          weight, eps, out, n_rows, H, stream);
   if (dtype == TM_DTYPE_BF16)
     return tmk::launch_add_rmsnorm<__nv_bfloat16>(resid, branch, partials, n_partials, partial_stride, ids, table,
-                                                 rows, weight, eps, out, n_rows, H, stream);
+                                                  rows, weight, eps, out, n_rows, H, stream);
   return TM_ERR_BAD_DTYPE;
 }

@@ -58,6 +58,66 @@ __global__ void qkv_rope_write_kernel(const TIn* __restrict__ qkv, const float* 
   }
 }
 
+// The same, four rotation pairs per thread (head sizes that are multiples of 8, 16-byte aligned rows).
+template <typename TIn, typename T>
+__global__ void qkv_rope_write_vec_kernel(const TIn* __restrict__ qkv, const float* __restrict__ bias,
+                                          const int* __restrict__ positions, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, const int* __restrict__ slot_map,
+                                          T* __restrict__ q_out, T* __restrict__ kcache, T* __restrict__ vcache,
+                                          int nh, int nkv, int D, int n_pos) {
+  const int t = blockIdx.x;
+  const int half = D >> 1, quads = half >> 2;
+  const int heads = nh + 2 * nkv;
+  const TIn* row = qkv + (size_t)t * heads * D;
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= n_pos ? n_pos - 1 : pos);
+  const int slot = slot_map ? slot_map[t] : -1;
+  for (int idx = threadIdx.x; idx < heads * quads; idx += blockDim.x) {
+    const int h = idx / quads, i = (idx - h * quads) * 4;
+    const int c0 = h * D + i, c1 = c0 + half;
+    float x1[4], x2[4], o1[4], o2[4];
+    load4<TIn>(row + c0, x1);
+    load4<TIn>(row + c1, x2);
+    if (bias) {
+      float b1[4], b2[4];
+      load4<float>(bias + c0, b1);
+      load4<float>(bias + c1, b2);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x1[e] += b1[e];
+        x2[e] += b2[e];
+      }
+    }
+    if (h < nh + nkv) {
+      float cs[4], sn[4];
+      load4<float>(cos_t + (size_t)pos * half + i, cs);
+      load4<float>(sin_t + (size_t)pos * half + i, sn);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o1[e] = __fadd_rn(__fmul_rn(x1[e], cs[e]), __fmul_rn(-x2[e], sn[e]));
+        o2[e] = __fadd_rn(__fmul_rn(x2[e], cs[e]), __fmul_rn(x1[e], sn[e]));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o1[e] = x1[e];
+        o2[e] = x2[e];
+      }
+    }
+    T* dst = nullptr;
+    if (h < nh) {
+      dst = q_out + ((size_t)t * nh + h) * D;
+    } else if (slot >= 0) {
+      const bool is_k = h < nh + nkv;
+      dst = (is_k ? kcache : vcache) + ((size_t)slot * nkv + (is_k ? h - nh : h - nh - nkv)) * D;
+    }
+    if (dst) {
+      store4<T>(dst + i, o1);
+      store4<T>(dst + i + half, o2);
+    }
+  }
+}
+
 }  // namespace tmk
 
 // in_dtype: dtype of qkv (a 32-bit product may feed a bfloat16 cache); dtype: dtype of q_out and caches.
@@ -67,22 +127,33 @@ extern "C" int tm_qkv_rope_write(int in_dtype, int dtype, const void* qkv, const
                                  int nkv, int D, int n_pos, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D % 2) return TM_ERR_UNSUPPORTED_SHAPE;
-  const int work = (nh + 2 * nkv) * (D / 2);
-  const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
   using bf16 = __nv_bfloat16;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(bias) |
+                        reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t) |
+                        reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(kcache) |
+                        reinterpret_cast<uintptr_t>(vcache);
+  const bool vec = D % 8 == 0 && (all & 15) == 0;
+  const int work = (nh + 2 * nkv) * (D / 2) / (vec ? 4 : 1);
+  const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
+#define TM_ROPE_LAUNCH(TIN, TOUT)                                                                            \
+  do {                                                                                                       \
+    if (vec)                                                                                                 \
+      tmk::qkv_rope_write_vec_kernel<TIN, TOUT><<<T, threads, 0, stream>>>(                                  \
+          (const TIN*)qkv, bias, positions, cos_t, sin_t, slot_map, (TOUT*)q_out, (TOUT*)kcache,             \
+          (TOUT*)vcache, nh, nkv, D, n_pos);                                                                 \
+    else                                                                                                     \
+      tmk::qkv_rope_write_kernel<TIN, TOUT><<<T, threads, 0, stream>>>(                                      \
+          (const TIN*)qkv, bias, positions, cos_t, sin_t, slot_map, (TOUT*)q_out, (TOUT*)kcache,             \
+          (TOUT*)vcache, nh, nkv, D, n_pos);                                                                 \
+  } while (0)
   if (in_dtype == TM_DTYPE_F32 && dtype == TM_DTYPE_F32)
-    tmk::qkv_rope_write_kernel<float, float><<<T, threads, 0, stream>>>(
-        (const float*)qkv, bias, positions, cos_t, sin_t, slot_map, (float*)q_out, (float*)kcache,
-        (float*)vcache, nh, nkv, D, n_pos);
+    TM_ROPE_LAUNCH(float, float);
   else if (in_dtype == TM_DTYPE_BF16 && dtype == TM_DTYPE_BF16)
-    tmk::qkv_rope_write_kernel<bf16, bf16><<<T, threads, 0, stream>>>(
-        (const bf16*)qkv, bias, positions, cos_t, sin_t, slot_map, (bf16*)q_out, (bf16*)kcache, (bf16*)vcache,
-        nh, nkv, D, n_pos);
+    TM_ROPE_LAUNCH(bf16, bf16);
   else if (in_dtype == TM_DTYPE_F32 && dtype == TM_DTYPE_BF16)
-    tmk::qkv_rope_write_kernel<float, bf16><<<T, threads, 0, stream>>>(
-        (const float*)qkv, bias, positions, cos_t, sin_t, slot_map, (bf16*)q_out, (bf16*)kcache, (bf16*)vcache,
-        nh, nkv, D, n_pos);
+    TM_ROPE_LAUNCH(float, bf16);
   else
     return TM_ERR_BAD_DTYPE;
+#undef TM_ROPE_LAUNCH
   return tmk::launch_status();
 }

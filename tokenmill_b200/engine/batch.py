@@ -62,18 +62,21 @@ def tiles_for(q_lens: np.ndarray, group_size: int) -> tuple[np.ndarray, np.ndarr
     return tile_seq.astype(np.int32), tile_row0.astype(np.int32)
 
 
-TOKEN_TILE = 64      # tokens per block of the tensor-core prompt attention; its tile list has key 0
+PACKED_TILE = 64     # rows of the tensor-core prompt attention's work unit; its tile list has key -G
 
 
-def token_tiles(q_lens: np.ndarray, tile: int = TOKEN_TILE) -> tuple[np.ndarray, np.ndarray]:
-    """(request, first token within its portion) of every tile of ``tile`` consecutive tokens. Later
-    tiles of a request see more keys, so they are listed first: the longest blocks start earliest."""
-    per_seq = (q_lens + tile - 1) // tile
+def packed_tiles(q_lens: np.ndarray, starts: np.ndarray, group_size: int,
+                 tile: int = PACKED_TILE) -> tuple[np.ndarray, np.ndarray]:
+    """(request, first row) of every tile of ``tile`` consecutive (token, head-in-group) rows, the
+    tiles that see the most keys first: a causal prompt's last tile has many times the work of its
+    first, and the kernel hands tiles out in this order."""
+    per_seq = (q_lens * group_size + tile - 1) // tile
     tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), per_seq)
     first = np.cumsum(per_seq) - per_seq
-    tok0 = (np.arange(tile_seq.size, dtype=np.int32) - np.repeat(first, per_seq).astype(np.int32)) * tile
-    order = np.argsort(-tok0, kind="stable")
-    return tile_seq[order].astype(np.int32), tok0[order].astype(np.int32)
+    row0 = (np.arange(tile_seq.size, dtype=np.int32) - np.repeat(first, per_seq).astype(np.int32)) * tile
+    last_pos = starts[tile_seq] + np.minimum(row0 + tile - 1, q_lens[tile_seq] * group_size - 1) // group_size
+    order = np.argsort(-last_pos, kind="stable")
+    return tile_seq[order].astype(np.int32), row0[order].astype(np.int32)
 
 
 def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: torch.device,
@@ -96,7 +99,8 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
         if any(not (0 <= w < len(e.tokens)) for w in e.want):
             raise ValueError(f"entry {i}: a wanted place lies outside its {len(e.tokens)} tokens")
     tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
-    tile_arrays[0] = token_tiles(q_lens)
+    for g in group_sizes:
+        tile_arrays[-g] = packed_tiles(q_lens, starts, g)
     lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()})
 
     host = torch.empty(lay.total, dtype=torch.int32, pin_memory=device.type == "cuda")

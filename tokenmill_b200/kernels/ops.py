@@ -137,10 +137,11 @@ def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
 
 def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                            cu_q: torch.Tensor, kv_before: torch.Tensor, tile_seq: torch.Tensor,
-                           tile_tok0: torch.Tensor, n_tiles: int, out: torch.Tensor, *, scale: float,
-                           window: int = 0) -> torch.Tensor:
+                           tile_row0: torch.Tensor, n_tiles: int, counters: torch.Tensor, out: torch.Tensor, *,
+                           scale: float, window: int = 0) -> torch.Tensor:
     """Tensor-core causal attention for prompt portions (bfloat16, head size 64 or 128). tile_seq /
-    tile_tok0 list the 64-token tiles: request, and first token within the request's portion."""
+    tile_row0 list the tiles of 64 (token, head-in-group) rows, heaviest first; counters: two int32
+    zeros the kernel uses as work ticket and leaves zero."""
     T, nh, D = q.shape
     page_size, nkv = kcache.shape[1], kcache.shape[2]
     bf = torch.bfloat16
@@ -149,8 +150,8 @@ def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
     lib.call("tm_prefill_attention_bf16", _req(q, "q", bf), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf),
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
              _req(kv_before, "kv_before", torch.int32), _req(tile_seq, "tile_seq", torch.int32),
-             _req(tile_tok0, "tile_tok0", torch.int32), n_tiles, _req(out, "out", bf), nh, nkv, D, page_size,
-             float(scale), int(window), _stream())
+             _req(tile_row0, "tile_row0", torch.int32), n_tiles, _req(counters, "counters", torch.int32),
+             _req(out, "out", bf), nh, nkv, D, page_size, float(scale), int(window), _stream())
     return out
 
 

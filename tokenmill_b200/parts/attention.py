@@ -32,6 +32,14 @@ class AttentionScratch:
         self.part_acc: torch.Tensor | None = None
         self.part_ml: torch.Tensor | None = None
         self.frozen = False      # set once a graph has captured the pointers
+        self._counters: torch.Tensor | None = None
+
+    def counters(self) -> torch.Tensor:
+        """Two zeroed ints the prompt-attention kernel uses as work ticket and done-counter (it leaves
+        them zero again)."""
+        if self._counters is None:
+            self._counters = torch.zeros(2, dtype=torch.int32, device=self.device)
+        return self._counters
 
     def reserve(self, rows: int, max_splits: int, head_dim: int) -> None:
         need_acc, need_ml = rows * max_splits * head_dim, rows * max_splits * 2
@@ -132,11 +140,11 @@ class GroupedQueryAttention:
                                       window=self.window, split_keys=step.split_keys, max_splits=step.max_splits,
                                       part_acc=part_acc, part_ml=part_ml)
             return
-        if self.dtype == torch.bfloat16 and self.D in (64, 128) and 0 in step.tiles:
-            tile_seq, tile_tok0, n_tiles = step.attention_tiles(0)        # tiles of 64 tokens
+        if self.dtype == torch.bfloat16 and self.D in (64, 128) and -G in step.tiles:
+            tile_seq, tile_row0, n_tiles = step.attention_tiles(-G)       # 64-row tiles, heaviest first
             ops.prefill_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
-                                       step.kv_before, tile_seq, tile_tok0, n_tiles, out, scale=self.scale,
-                                       window=self.window)
+                                       step.kv_before, tile_seq, tile_row0, n_tiles, step.scratch.counters(), out,
+                                       scale=self.scale, window=self.window)
             return
         tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
         kw = {}
