@@ -357,6 +357,67 @@ def test_skinny_gate_up_swiglu(T, H, I):
     assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("T,N,K", [(128, 256, 64), (2048, 896, 896), (300, 904, 4864), (129, 1152, 200), (1000, 72, 1536)])
+def test_tcgen05_linear(T, N, K):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + N + K)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    ref = x.float() @ w.float().T
+    dx, dw = x.to(DEV), w.to(DEV)
+    assert ops.tc_ok(dx, dw)
+    out = ops.tc_linear(dx, dw)
+    ops.tc_check(dx.device)
+    assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("T,H,I", [(128, 64, 128), (2048, 896, 4864), (333, 1536, 8960), (200, 96, 160), (130, 72, 1000)])
+def test_tcgen05_gate_up_swiglu(T, H, I):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + H + I)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w = (2 * torch.randn(2 * I, H, generator=g) / H ** 0.5).bfloat16()
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.tc_gate_up_swiglu(x.to(DEV), w.to(DEV), out)
+    ops.tc_check(out.device)
+    y = x.float() @ w.float().T
+    ref = plain_silu(y[:, :I]) * y[:, I:]
+    assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("T,H,nh,nkv,D", [(128, 896, 14, 2, 64), (2048, 896, 14, 2, 64), (300, 1536, 12, 2, 128),
+                                          (129, 264, 5, 5, 64), (200, 128, 3, 1, 256)])
+def test_tcgen05_qkv_with_rope_and_cache_write(T, H, nh, nkv, D):
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + H + D)
+    width = (nh + 2 * nkv) * D
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w = (torch.randn(width, H, generator=g) / H ** 0.5).bfloat16()
+    bias = 0.3 * torch.randn(width, generator=g)
+    pos = torch.randint(0, 3000, (T,), generator=g, dtype=torch.int32)
+    cos, sin = plain_rope_tables(3000, D, 1e6)
+    page = 8
+    pages = -(-T // page) + 3
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    kc = torch.zeros(pages, page, nkv, D, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.full((T, nh, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.tc_qkv_rope_write(x.to(DEV), w.to(DEV), bias.to(DEV), pos.to(DEV), cos[:, :D // 2].contiguous().to(DEV),
+                          sin[:, :D // 2].contiguous().to(DEV), slots.to(DEV), q_out, kc, vc, nh, nkv, D)
+    ops.tc_check(q_out.device)
+    y = x.float() @ w.float().T + bias
+    q = plain_apply_rope(y[:, :nh * D].view(T, nh, D), cos, sin, pos)
+    k = plain_apply_rope(y[:, nh * D:(nh + nkv) * D].view(T, nkv, D), cos, sin, pos)
+    v = y[:, (nh + nkv) * D:].view(T, nkv, D)
+    t = 1e-2 * float(y.abs().max())
+    assert (q_out.float().cpu() - q).abs().max() <= t
+    assert (kc.view(-1, nkv, D)[slots.long().to(DEV)].float().cpu() - k).abs().max() <= t
+    assert (vc.view(-1, nkv, D)[slots.long().to(DEV)].float().cpu() - v).abs().max() <= t
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert float(kc.view(-1, nkv, D)[untouched.to(DEV)].abs().max()) == 0
+
+
 @pytest.mark.parametrize("n,V", [(1, 5), (3, 1000), (2, 151936), (4, 1025), (64, 151936), (3, 4097)])
 def test_argmax_lowest_index_on_ties(n, V):
     ops = _ops()

@@ -1,0 +1,474 @@
+// Prompt-step matrix products on the 5th-generation tensor cores: out = x[T, K] . W[N, K]^T, bfloat16
+// operands, float32 accumulators in tensor memory, with the projection's own epilogue.
+//
+// One persistent block per SM, 8 warps with fixed roles:
+//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the 128 x 64
+//            activation tile and two 128 x 64 weight tiles into a 4-stage shared-memory ring;
+//   warp 1   one lane issues tcgen05.mma (M = 128 tokens, N = 256 weight rows, K = 16 per instruction,
+//            operands straight from shared memory through matrix descriptors) into one of two 256-column
+//            accumulators in tensor memory, and commits each stage back to the loader;
+//   warp 2   allocates and frees the 512 columns of tensor memory;
+//   warps 4-7 read a finished accumulator back with tcgen05.ld (each warp its own 32 lanes = 32 tokens)
+//            and run the epilogue while the next tile's products already go into the other accumulator.
+// Epilogues (the reference's projections, src/infer/model/layers.py:127-164):
+//   STORE   out[t, n] bfloat16                                                    (o_proj, down_proj)
+//   SWIGLU  the tile's 256 weight rows are 128 gate rows and the 128 matching up rows;
+//           out[t, i] = silu(gate) * up, so the [T, 2I] product never exists in memory
+//   QKV     + bias, rotate-half position encoding of q and k, q to q_out, k and v to their cache slots
+// Every wait on an mbarrier is bounded: when it runs out, the block raises an error word, skips the
+// rest of its work, still frees its tensor memory, and the host reports the failure.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tmk {
+
+constexpr int kT5BM = 128, kT5BN = 256, kT5BK = 64, kT5Stages = 4;
+constexpr int kT5ABytes = kT5BM * kT5BK * 2;            // 16 KB
+constexpr int kT5BBytes = kT5BN * kT5BK * 2;            // 32 KB
+constexpr int kT5StageBytes = kT5ABytes + kT5BBytes;    // 48 KB
+constexpr int kT5Threads = 256;
+constexpr uint32_t kT5SpinLimit = 1u << 24;             // polls (with back-off) before a wait gives up
+enum : int { T5_STORE = 0, T5_SWIGLU = 1, T5_QKV = 2 };
+
+struct T5Args {
+  int T, N, K, mode;
+  int n_tiles_m, n_tiles_n;
+  __nv_bfloat16* out;       // STORE: [T, N]; SWIGLU: [T, inter]
+  int ldo, inter;
+  // QKV
+  const float* bias;
+  const int* positions;
+  const float* cos_t;
+  const float* sin_t;
+  const int* slot_map;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  int nh, nkv, D, n_pos;
+  int* error;               // device word, 0 when all is well
+};
+
+// --- PTX wrappers ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t t5_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises the error word) when the limit is reached or another role
+// has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int* error, int code) {
+  for (uint32_t i = 0; i < kT5SpinLimit; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (i > 64) {
+      if (*s_abort) return false;
+      __nanosleep(64);
+    }
+  }
+  *s_abort = 1;
+  atomicCAS(error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void t5_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void t5_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread = lane (row), v[j] = column j.
+__device__ __forceinline__ void t5_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows, 128-byte swizzle: rows 128 B apart,
+// groups of 8 rows 1024 B apart (stride offset), leading offset unused (1), descriptor version 1.
+__device__ __forceinline__ uint64_t t5_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                  // leading byte offset (>> 4)
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset (>> 4)
+  d |= (uint64_t)1 << 46;                  // version
+  d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) {
+  uint4 o;
+  o.x = ([](float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); })(v[0], v[1]);
+  o.y = ([](float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); })(v[2], v[3]);
+  o.z = ([](float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); })(v[4], v[5]);
+  o.w = ([](float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); })(v[6], v[7]);
+  *reinterpret_cast<uint4*>(dst) = o;
+}
+
+// First weight row of each 128-row half of tile column `tn`.
+__device__ __forceinline__ void t5_tile_rows(const T5Args& a, int tn, int& row_lo, int& row_hi) {
+  if (a.mode == T5_SWIGLU) {
+    row_lo = tn * 128;              // gate rows
+    row_hi = a.inter + tn * 128;    // the matching up rows
+  } else {
+    row_lo = tn * kT5BN;
+    row_hi = row_lo + 128;
+  }
+}
+
+__global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                     const __grid_constant__ CUtensorMap map_w,
+                                                                     const T5Args a) {
+  extern __shared__ __align__(1024) unsigned char t5_smem_raw[];
+  // The dynamic region is used from the next 1024-byte boundary (the swizzle pattern repeats every 1024 B).
+  const uint32_t ring = (t5_smem(t5_smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * kT5Stages + 4];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  const uint32_t bar0 = t5_smem(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kT5Stages + s); };
+  auto tfull_bar = [&](int acc) { return bar0 + 8u * (2 * kT5Stages + acc); };
+  auto tempty_bar = [&](int acc) { return bar0 + 8u * (2 * kT5Stages + 2 + acc); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kT5Stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int acc = 0; acc < 2; ++acc) {
+      mbar_init(tfull_bar(acc), 1);
+      mbar_init(tempty_bar(acc), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(t5_smem(&s_tmem_base)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  t5_fence_before();
+  __syncthreads();
+  t5_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  const int n_tiles = a.n_tiles_m * a.n_tiles_n;
+  const int n_kb = (a.K + kT5BK - 1) / kT5BK;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ----
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const int tn = tile / a.n_tiles_m, tm = tile - tn * a.n_tiles_m;
+      int row_lo, row_hi;
+      t5_tile_rows(a, tn, row_lo, row_hi);
+      for (int kb = 0; kb < n_kb && ok; ++kb) {
+        ok = mbar_wait(empty_bar(stage), phase ^ 1u, &s_abort, a.error, 1);
+        if (!ok) break;
+        const uint32_t dst = ring + stage * kT5StageBytes;
+        mbar_expect_tx(full_bar(stage), kT5StageBytes);
+        tma_load_2d(dst, &map_x, kb * kT5BK, tm * kT5BM, full_bar(stage));
+        tma_load_2d(dst + kT5ABytes, &map_w, kb * kT5BK, row_lo, full_bar(stage));
+        tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, kb * kT5BK, row_hi, full_bar(stage));
+        if (++stage == kT5Stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    // Instruction descriptor: D float32, A and B bfloat16, both K-major, N = 256, M = 128.
+    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kT5BN >> 3) << 17) |
+                               ((uint32_t)(kT5BM >> 4) << 24);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &s_abort, a.error, 2);
+      if (!ok) break;
+      t5_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * kT5BN;
+      for (int kb = 0; kb < n_kb && ok; ++kb) {
+        ok = mbar_wait(full_bar(stage), phase, &s_abort, a.error, 3);
+        if (!ok) break;
+        t5_fence_after();
+        const uint32_t sa = ring + stage * kT5StageBytes, sb = sa + kT5ABytes;
+#pragma unroll
+        for (int k = 0; k < kT5BK / 16; ++k)
+          t5_mma(d_tmem, t5_desc(sa + k * 32), t5_desc(sb + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+        t5_commit(empty_bar(stage));                   // the stage is free once these products are done
+        if (++stage == kT5Stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) t5_commit(tfull_bar(acc));               // the accumulator is complete
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ---- epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 ----
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const int tn = tile / a.n_tiles_m, tm = tile - tn * a.n_tiles_m;
+      ok = mbar_wait(tfull_bar(acc), acc_phase, &s_abort, a.error, 4);
+      if (!ok) break;
+      t5_fence_after();
+      const int t = tm * kT5BM + quarter * 32 + lane;           // this thread's token row
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kT5BN;
+      const bool row_ok = t < a.T;
+      if (a.mode == T5_STORE) {
+#pragma unroll 1
+        for (int c = 0; c < kT5BN; c += 32) {
+          float v[32];
+          t5_ld32(taddr + c, v);
+          const int n = tn * kT5BN + c;
+          if (row_ok && n < a.N) {
+            __nv_bfloat16* dst = a.out + (size_t)t * a.ldo + n;
+            if (n + 32 <= a.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) store8_bf16(dst + j, v + j);
+            } else {
+              for (int j = 0; j < 32 && n + j < a.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      } else if (a.mode == T5_SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          float g[32], u[32];
+          t5_ld32(taddr + c, g);
+          t5_ld32(taddr + 128 + c, u);
+          const int n = tn * 128 + c;
+          if (row_ok && n < a.inter) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+            __nv_bfloat16* dst = a.out + (size_t)t * a.ldo + n;
+            if (n + 32 <= a.inter) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) store8_bf16(dst + j, g + j);
+            } else {
+              for (int j = 0; j < 32 && n + j < a.inter; ++j) dst[j] = __float2bfloat16_rn(g[j]);
+            }
+          }
+        }
+      } else {
+        // QKV: the tile's 256 columns are whole heads (D divides 256); a rotation pair is i and i + D/2.
+        const int half = a.D >> 1;
+        int pos = 0, slot = -1;
+        if (row_ok) {
+          pos = a.positions[t];
+          pos = pos < 0 ? 0 : (pos >= a.n_pos ? a.n_pos - 1 : pos);
+          slot = a.slot_map ? a.slot_map[t] : -1;
+        }
+#pragma unroll 1
+        for (int hc = 0; hc < kT5BN; hc += a.D) {
+          const int head = (tn * kT5BN + hc) / a.D;
+          const bool head_ok = head < a.nh + 2 * a.nkv;
+#pragma unroll 1
+          for (int i0 = 0; i0 < half; i0 += 32) {
+            float x1[32], x2[32];
+            t5_ld32(taddr + hc + i0, x1);
+            t5_ld32(taddr + hc + half + i0, x2);
+            if (!(row_ok && head_ok)) continue;
+            const int c0 = head * a.D + i0, c1 = c0 + half;
+            if (a.bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                x1[j] += a.bias[c0 + j];
+                x2[j] += a.bias[c1 + j];
+              }
+            }
+            if (head < a.nh + a.nkv) {
+              const float* cs = a.cos_t + (size_t)pos * half + i0;
+              const float* sn = a.sin_t + (size_t)pos * half + i0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float c = cs[j], s = sn[j];
+                const float o1 = __fadd_rn(__fmul_rn(x1[j], c), __fmul_rn(-x2[j], s));
+                const float o2 = __fadd_rn(__fmul_rn(x2[j], c), __fmul_rn(x1[j], s));
+                x1[j] = o1;
+                x2[j] = o2;
+              }
+            }
+            __nv_bfloat16* dst = nullptr;
+            if (head < a.nh) {
+              dst = a.q_out + ((size_t)t * a.nh + head) * a.D;
+            } else if (slot >= 0) {
+              const bool is_k = head < a.nh + a.nkv;
+              dst = (is_k ? a.kcache : a.vcache) + ((size_t)slot * a.nkv + (is_k ? head - a.nh : head - a.nh - a.nkv)) * a.D;
+            }
+            if (dst) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                store8_bf16(dst + i0 + j, x1 + j);
+                store8_bf16(dst + half + i0 + j, x2 + j);
+              }
+            }
+          }
+        }
+      }
+      // This warp has read everything it needs from the accumulator.
+      t5_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // Teardown: every role has left its loop (normally, or through a bounded wait).
+  t5_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    t5_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+  }
+}
+
+// --- host -----------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix viewed through boxes of 128 rows x 64 columns, 128-byte swizzle;
+// parts of a box outside the matrix read as zero.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long row_stride_elems) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kT5BK, 128u};
+  const cuuint32_t elem[2] = {1u, 1u};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream_t stream) {
+  if (a.T <= 0) return 0;
+  if (a.K % 8 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return TM_ERR_UNSUPPORTED_SHAPE;     // TMA wants 16-byte aligned rows
+  if (!a.error) return TM_ERR_SCRATCH_TOO_SMALL;
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, x, a.T, a.K, ldx) || !make_map(&map_w, w, a.N, a.K, a.K)) return 90006;
+  a.n_tiles_m = (a.T + kT5BM - 1) / kT5BM;
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int smem = kT5Stages * kT5StageBytes + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int tiles = a.n_tiles_m * a.n_tiles_n;
+  const int grid = tiles < n_sm ? tiles : n_sm;
+  gemm_tcgen05_kernel<<<grid, kT5Threads, smem, stream>>>(map_x, map_w, a);
+  return launch_status();
+}
+
+}  // namespace tmk
+
+// out [T, N] = x [T, K] . w [N, K]^T, all bfloat16. `error` is a device int that must be zero; a block
+// whose wait runs out writes a non-zero code there instead of hanging.
+extern "C" int tm_tc_linear(const void* x, int ldx, const void* w, void* out, int ldo, int T, int N, int K,
+                            int* error, cudaStream_t stream) {
+  tmk::T5Args a{};
+  a.T = T; a.N = N; a.K = K; a.mode = tmk::T5_STORE;
+  a.n_tiles_n = (N + tmk::kT5BN - 1) / tmk::kT5BN;
+  a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.error = error;
+  if (ldo % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return TM_ERR_UNSUPPORTED_SHAPE;
+  return tmk::t5_launch(a, x, ldx, w, stream);
+}
+
+// out [T, I] = silu(x . gate^T) * (x . up^T); w [2 I, K] with the gate rows first; I a multiple of 8.
+extern "C" int tm_tc_gate_up_swiglu(const void* x, int ldx, const void* w, void* out, int ldo, int T, int K,
+                                    int inter, int* error, cudaStream_t stream) {
+  tmk::T5Args a{};
+  a.T = T; a.N = 2 * inter; a.K = K; a.mode = tmk::T5_SWIGLU; a.inter = inter;
+  a.n_tiles_n = (inter + 127) / 128;
+  a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.error = error;
+  if (ldo % 8 || inter % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return TM_ERR_UNSUPPORTED_SHAPE;
+  return tmk::t5_launch(a, x, ldx, w, stream);
+}
+
+// Fused q/k/v projection with bias, rotate-half position encoding and cache write (see rope_cache.cu for the
+// formulas). Head sizes 64, 128 and 256 (a 256-column tile must hold whole heads; half a head in steps of 32).
+extern "C" int tm_tc_qkv_rope_write(const void* x, int ldx, const void* w, const float* bias, const int* positions,
+                                    const float* cos_t, const float* sin_t, const int* slot_map, void* q_out,
+                                    void* kcache, void* vcache, int T, int K, int nh, int nkv, int D, int n_pos,
+                                    int* error, cudaStream_t stream) {
+  if (D != 64 && D != 128 && D != 256) return TM_ERR_UNSUPPORTED_SHAPE;
+  tmk::T5Args a{};
+  a.T = T; a.N = (nh + 2 * nkv) * D; a.K = K; a.mode = tmk::T5_QKV;
+  a.n_tiles_n = (a.N + tmk::kT5BN - 1) / tmk::kT5BN;
+  a.bias = bias; a.positions = positions; a.cos_t = cos_t; a.sin_t = sin_t; a.slot_map = slot_map;
+  a.q_out = (__nv_bfloat16*)q_out; a.kcache = (__nv_bfloat16*)kcache; a.vcache = (__nv_bfloat16*)vcache;
+  a.nh = nh; a.nkv = nkv; a.D = D; a.n_pos = n_pos; a.error = error;
+  return tmk::t5_launch(a, x, ldx, w, stream);
+}

@@ -302,3 +302,66 @@ def skinny_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.T
     lib.call("tm_skinny_gate_up_swiglu", x.data_ptr(), x.stride(0), _req(w_gate_up, "w_gate_up", torch.bfloat16),
              _req(out, "out", torch.bfloat16), out.stride(0), T, K, inter, _stream())
     return out
+
+
+# --- prompt-step products on tcgen05 tensor cores (bfloat16) ------------------------------------------
+
+TC_MIN_TOKENS = 128                # below this the 128-token tiles are mostly padding
+_tc_error: dict[torch.device, torch.Tensor] = {}
+
+
+def _tc_flag(device: torch.device) -> torch.Tensor:
+    if device not in _tc_error:
+        _tc_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_error[device]
+
+
+def tc_check(device: torch.device) -> None:
+    """Raise if a tcgen05 kernel gave up on a bounded wait since the last check (reads one int back)."""
+    flag = _tc_error.get(device)
+    if flag is not None:
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise lib.KernelError(f"a tcgen05 matrix-product block gave up waiting (code {code}: 1 loader, "
+                                  f"2/3 issuer, 4 epilogue); its results are incomplete")
+
+
+def tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernels take this product: bfloat16, a prompt-sized batch, 16-byte aligned rows."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
+            and x.shape[0] >= TC_MIN_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0)
+
+
+def tc_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [T, K] . w [N, K]^T -> [T, N] bfloat16 on tcgen05 (N a multiple of 8)."""
+    T, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    lib.call("tm_tc_linear", x.data_ptr(), x.stride(0), w.data_ptr(), _req(out, "out", torch.bfloat16), out.stride(0),
+             T, N, K, _tc_flag(x.device).data_ptr(), _stream())
+    return out
+
+
+def tc_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [T, I] = silu(x . gate^T) * (x . up^T) on tcgen05; the [T, 2I] product stays in tensor memory."""
+    T, K = x.shape
+    lib.call("tm_tc_gate_up_swiglu", x.data_ptr(), x.stride(0), _req(w_gate_up, "w_gate_up", torch.bfloat16),
+             _req(out, "out", torch.bfloat16), out.stride(0), T, K, w_gate_up.shape[0] // 2,
+             _tc_flag(x.device).data_ptr(), _stream())
+    return out
+
+
+def tc_qkv_rope_write(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor,
+                      cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
+                      kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, D: int) -> None:
+    """The fused q/k/v projection of a prompt step on tcgen05, epilogue as skinny_qkv_rope_write."""
+    T, K = x.shape
+    bf = torch.bfloat16
+    lib.call("tm_tc_qkv_rope_write", x.data_ptr(), x.stride(0), _req(w, "w", bf), _opt(bias, "bias", torch.float32),
+             _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32),
+             _req(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out", bf),
+             _opt(kcache, "kcache", bf), _opt(vcache, "vcache", bf), T, K, nh, nkv, D, cos.shape[0],
+             _tc_flag(x.device).data_ptr(), _stream())
