@@ -215,3 +215,28 @@ def test_command_line_generates(tiny_a_dir):
     assert [r["prompt_ids"] for r in rows] == [[5, 6, 7], [9]] and all(len(r["output_ids"]) == 5 for r in rows)
     cfg, w = load_plain(tiny_a_dir)
     assert rows[0]["output_ids"] == plain_greedy(cfg, w, [5, 6, 7], 5)
+
+
+def test_prompt_products_on_tcgen05_when_switched_on(tmp_path, monkeypatch, plain_cache):
+    """With TOKENMILL_TC_GEMM on, prompt steps of 128 tokens or more run the fused q/k/v projection, the
+    gate/up projection with its SwiGLU epilogue and the down projection on the tcgen05 kernel; logits stay
+    within the bfloat16 tolerance of the plain implementation, and decoding afterwards reads what it wrote."""
+    from tokenmill_b200.kernels import lib, ops
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    cfg = qwen2_config(vocab_size=300, hidden_size=128, intermediate_size=264, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, rope_theta=10000.0, tie_word_embeddings=False,
+                       max_position_embeddings=1024)
+    folder = write_random_model(tmp_path / "m", cfg, seed=5)
+    monkeypatch.setattr(ops, "_TC_ENABLED", True)
+    calls = []
+    real = lib.call
+    monkeypatch.setattr(lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    reqs = make_requests(300, [330, 150], seed=4)
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": reqs["r0"][:300], "want": list(range(0, 300, 7))}], "end": []},
+             {"step": 1, "entries": [{"id": "r1", "tokens": reqs["r1"][:140], "want": [139]},
+                                     {"id": "r0", "tokens": reqs["r0"][300:310], "want": list(range(10))}], "end": []},
+             {"step": 2, "entries": [{"id": "r0", "tokens": reqs["r0"][310:], "want": list(range(20))},
+                                     {"id": "r1", "tokens": reqs["r1"][140:], "want": list(range(10))}], "end": ["r0", "r1"]}]
+    outputs = run_trace(folder, "bfloat16", steps, 512, tmp_path / "o")
+    check_against_plain(steps, outputs, reqs, plain_for(folder, reqs, plain_cache), "bfloat16")
+    assert {"tm_tc_qkv_rope_write", "tm_tc_gate_up_swiglu", "tm_tc_linear"} <= set(calls)

@@ -365,7 +365,6 @@ def test_tcgen05_linear(T, N, K):
     w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
     ref = x.float() @ w.float().T
     dx, dw = x.to(DEV), w.to(DEV)
-    assert ops.tc_ok(dx, dw)
     out = ops.tc_linear(dx, dw)
     ops.tc_check(dx.device)
     assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())

@@ -113,10 +113,11 @@ __device__ __forceinline__ void t5_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
+// The registers of earlier t5_ld32 calls may be read only after this.
+__device__ __forceinline__ void t5_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile of 128-byte rows, 128-byte swizzle: rows 128 B apart,
 // groups of 8 rows 1024 B apart (stride offset), leading offset unused (1), descriptor version 1.
@@ -267,6 +268,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
         for (int c = 0; c < kT5BN; c += 32) {
           float v[32];
           t5_ld32(taddr + c, v);
+          t5_ld_wait();
           const int n = tn * kT5BN + c;
           if (row_ok && n < a.N) {
             __nv_bfloat16* dst = a.out + (size_t)t * a.ldo + n;
@@ -284,6 +286,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
           float g[32], u[32];
           t5_ld32(taddr + c, g);
           t5_ld32(taddr + 128 + c, u);
+          t5_ld_wait();
           const int n = tn * 128 + c;
           if (row_ok && n < a.inter) {
 #pragma unroll
@@ -315,6 +318,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
             float x1[32], x2[32];
             t5_ld32(taddr + hc + i0, x1);
             t5_ld32(taddr + hc + half + i0, x2);
+            t5_ld_wait();
             if (!(row_ok && head_ok)) continue;
             const int c0 = head * a.D + i0, c1 = c0 + half;
             if (a.bias) {

@@ -22,7 +22,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pool import CachePools
-from ..kernels import lib
+from ..kernels import lib, ops
 from ..parts.attention import SPLIT_KEYS, AttentionScratch
 from ..parts.base import StepInputs
 from ..parts.model import DecoderModel
@@ -73,7 +73,10 @@ class ModelRunner:
             return self._graph_step(entries)
         step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                  split_keys=SPLIT_KEYS)
-        return self.model.forward(step, self.layer_caches)
+        logits = self.model.forward(step, self.layer_caches)
+        if self.model.dtype == torch.bfloat16 and step.n_tokens >= ops.TC_MIN_TOKENS:
+            ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
+        return logits
 
     # --- decode graphs --------------------------------------------------------------------------
 

@@ -6,6 +6,8 @@ current CUDA stream. None of them has a fallback: a tensor on the CPU or a missi
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import lib
@@ -307,6 +309,9 @@ def skinny_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.T
 # --- prompt-step products on tcgen05 tensor cores (bfloat16) ------------------------------------------
 
 TC_MIN_TOKENS = 128                # below this the 128-token tiles are mostly padding
+# Off unless TOKENMILL_TC_GEMM=1: with one SM per tile the kernel is bound by L2-to-shared-memory traffic and
+# the library's two-SM tiles are faster at these sizes, so prompt products go to the library by default.
+_TC_ENABLED = os.environ.get("TOKENMILL_TC_GEMM", "0") == "1"
 _tc_error: dict[torch.device, torch.Tensor] = {}
 
 
@@ -328,8 +333,9 @@ def tc_check(device: torch.device) -> None:
 
 
 def tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 kernels take this product: bfloat16, a prompt-sized batch, 16-byte aligned rows."""
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
+    """Whether the tcgen05 kernels take this product: switched on (TOKENMILL_TC_GEMM=1), bfloat16, a
+    prompt-sized batch, 16-byte aligned rows."""
+    return (_TC_ENABLED and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
             and x.shape[0] >= TC_MIN_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0)
 

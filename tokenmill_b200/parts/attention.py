@@ -116,6 +116,10 @@ class GroupedQueryAttention:
             # decode step: one kernel streams the fused weight and finishes bias, rotation and cache write
             ops.skinny_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
                                       kc, vc, self.nh, self.nkv, self.D)
+        elif self.D in (64, 128, 256) and ops.tc_ok(x, self.w_qkv):
+            # prompt step: the tcgen05 kernel keeps the product in tensor memory and finishes it the same way
+            ops.tc_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
+                                  kc, vc, self.nh, self.nkv, self.D)
         else:
             qkv = ops.linear(x, self.w_qkv)
             ops.qkv_rope_write(qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q, kc, vc,

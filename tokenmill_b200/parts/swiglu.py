@@ -38,6 +38,10 @@ class SwiGLUFeedForward:
             # the second may hand its K-range partials to the norm that follows
             ops.skinny_gate_up_swiglu(x, self.w_gate_up, act)
             return ops.skinny_linear(act, self.w_down, k_splits=ops.skinny_k_splits(T, self.intermediate_size))
+        if self.intermediate_size % 8 == 0 and ops.tc_ok(x, self.w_gate_up):
+            # prompt step on tcgen05 (when switched on): the activation is the product's epilogue
+            ops.tc_gate_up_swiglu(x, self.w_gate_up, act)
+            return ops.tc_linear(act, self.w_down) if ops.tc_ok(act, self.w_down) else ops.linear(act, self.w_down)
         gu = ops.linear(x, self.w_gate_up)
         ops.swiglu(gu, act)
         return ops.linear(act, self.w_down)
