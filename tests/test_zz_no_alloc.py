@@ -1,0 +1,71 @@
+"""The allocation-free decode-attention entry point, called through its exported C symbol.
+
+Some hosts of this library cannot call cudaMalloc: the device's memory was handed out completely when
+the process started (a serving runtime that reserved everything for weights and cache, or a plugin living
+inside another allocator), or they sit in a latency-critical loop where the device-wide synchronisation of
+cudaMalloc / cudaFree is not acceptable. For them the library carries its split-key scratch inside its own
+image. This test calls that entry point twice in a row with different inputs and checks each result
+against the ordinary entry point (which takes scratch from the caller), within the tolerance the kernel
+tests use. The file sorts last so that a run that stops at the first failure has run everything else.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _call_noalloc(c, nh, nkv, D, page, n_seqs, window, max_splits, out):
+    from tokenmill_b200.kernels import lib
+
+    fn = lib.load().tm_decode_attention_bf16_noalloc
+    fn.restype = ctypes.c_int
+    P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    fn.argtypes = [P, P, P, P, I, P, P, P, I, I, P, I, I, I, I, F, I, I, I, P]
+    return fn(c["q"].data_ptr(), c["kc"].data_ptr(), c["vc"].data_ptr(), c["table"].data_ptr(), c["table"].stride(0),
+              c["cu"].data_ptr(), c["before"].data_ptr(), c["seq_of"].data_ptr(), n_seqs, c["q"].shape[0],
+              out.data_ptr(), nh, nkv, D, page, D ** -0.5, window, 256, max_splits,
+              torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("nh,nkv,D,page", [(14, 2, 64, 16), (8, 2, 128, 8)])
+def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row(nh, nkv, D, page):
+    from test_kernels_gpu import _paged_case
+    from tokenmill_b200.kernels import ops
+
+    for call, (befores, window) in enumerate([([0, 255, 256, 700, 1000, 63, 511], 0), ([900, 3, 300, 64, 1, 513, 128], 150)]):
+        q_lens = [1] * len(befores)
+        c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=100 + call + D,
+                        window=window)
+        T = len(befores)
+        max_splits = -(-(max(befores) + 1) // 256)
+        ordinary = torch.empty_like(c["q"])
+        part_acc = torch.empty(T * nh * max_splits * D, device=DEV)
+        part_ml = torch.empty(T * nh * max_splits * 2, device=DEV)
+        ops.decode_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["seq_of"], T, ordinary,
+                                  scale=D ** -0.5, window=window, split_keys=256, max_splits=max_splits,
+                                  part_acc=part_acc, part_ml=part_ml)
+        out = torch.full_like(c["q"], float("nan"))
+        before = torch.cuda.memory_allocated()
+        status = _call_noalloc(c, nh, nkv, D, page, T, window, max_splits, out)
+        torch.cuda.synchronize()
+        assert status == 0
+        assert torch.cuda.memory_allocated() == before           # nothing was taken from torch's allocator
+        assert torch.equal(out, ordinary)                         # same kernels, same order of sums
+        ref = c["ref"]
+        assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
+
+
+def test_noalloc_entry_point_refuses_what_does_not_fit():
+    from test_kernels_gpu import _paged_case
+
+    c = _paged_case(14, 2, 64, 16, q_lens=[1, 1], befores=[10, 20], dtype=torch.bfloat16, seed=1)
+    out = torch.empty_like(c["q"])
+    # 2 tokens x 14 heads x 100000 splits x 66 floats is far beyond the 2 Mi floats the library carries
+    assert _call_noalloc(c, 14, 2, 64, 16, 2, 0, 100000, out) == 90004

@@ -1,0 +1,63 @@
+// Decode attention for callers that cannot allocate: see no_alloc.h for who they are and the rules.
+#include "no_alloc.h"
+
+#include "common.cuh"
+
+// The partial results of split-key attention live here instead of in caller- or allocator-provided
+// memory. In host code this name is only a stand-in for the device array: its device address has to be
+// asked for (cudaGetSymbolAddress) and is what the kernels receive.
+static __device__ __align__(256) float tm_noalloc_scratch[TM_NOALLOC_SCRATCH_FLOATS];
+
+extern "C" int tm_decode_attention_bf16(const void* q, const void* kcache, const void* vcache,
+                                        const int* block_table, int bt_stride, const int* cu_q,
+                                        const int* kv_before, int n_seqs, float* part_acc, float* part_ml, int nh,
+                                        int nkv, int D, int page_size, float scale, int window, int split_keys,
+                                        int max_splits, cudaStream_t stream);
+extern "C" int tm_attention_combine(int dtype, const float* part_acc, const float* part_ml, const int* cu_q,
+                                    const int* kv_before, const int* seq_of_token, void* out, int n_tokens, int nh,
+                                    int D, int window, int split_keys, int max_splits, cudaStream_t stream);
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+float* g_scratch[kMaxDevices] = {};   // device address of tm_noalloc_scratch, per device, once looked up
+
+// The array's address on the current device. The first call per device does the look-up.
+int scratch_for_current_device(float** ptr) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (!g_scratch[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, tm_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_scratch[dev] = p;
+  }
+  *ptr = g_scratch[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int tm_decode_attention_bf16_noalloc(const void* q, const void* kcache, const void* vcache,
+                                                const int* block_table, int bt_stride, const int* cu_q,
+                                                const int* kv_before, const int* seq_of_token, int n_seqs,
+                                                int n_tokens, void* out, int nh, int nkv, int D, int page_size,
+                                                float scale, int window, int split_keys, int max_splits,
+                                                cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (nh <= 0 || D <= 0 || max_splits <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  const long long rows = (long long)n_tokens * nh * max_splits;
+  if (rows * (D + 2) > (long long)TM_NOALLOC_SCRATCH_FLOATS) return TM_ERR_NOALLOC_TOO_LARGE;
+  float* scratch = nullptr;
+  int status = scratch_for_current_device(&scratch);
+  if (status != 0) return status;
+  float* part_acc = scratch;                  // [rows, D]
+  float* part_ml = scratch + rows * D;        // [rows, 2]
+  status = tm_decode_attention_bf16(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before, n_seqs, part_acc,
+                                    part_ml, nh, nkv, D, page_size, scale, window, split_keys, max_splits, stream);
+  if (status != 0) return status;
+  return tm_attention_combine(TM_DTYPE_BF16, part_acc, part_ml, cu_q, kv_before, seq_of_token, out, n_tokens, nh, D,
+                              window, split_keys, max_splits, stream);
+}
