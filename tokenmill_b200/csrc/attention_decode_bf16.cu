@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_bf16_kernel(
   // [stage][K | V] tiles; after the loop the same memory holds the 4 warps' states for the merge.
   const uint32_t smem_base = smem_u32(smem);
 
+  pdl_launch_dependents();
+  pdl_wait();                                  // q and this step's keys and values come from the kernel before
   const int G = nh / nkv;
   const int s = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int q_start = cu_q[s];
@@ -254,11 +256,10 @@ int launch_decode_attention(const void* q, const void* kcache, const void* vcach
     if (e != cudaSuccess) return (int)e;
   }
   const dim3 grid(n_seqs, nkv, max_splits);
-  kern<<<grid, kDecWarps * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,
-                                              (const __nv_bfloat16*)vcache, block_table, bt_stride, cu_q, kv_before,
-                                              part_acc, part_ml, nh, nkv, page_size,
-                                              scale * 1.4426950408889634f, window, split_keys, max_splits);
-  return launch_status();
+  return launch_pdl(kern, grid, dim3(kDecWarps * 32), (size_t)smem, stream, (const __nv_bfloat16*)q,
+                    (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, bt_stride, cu_q,
+                    kv_before, part_acc, part_ml, nh, nkv, page_size, scale * 1.4426950408889634f, window,
+                    split_keys, max_splits);
 }
 
 }  // namespace tmk

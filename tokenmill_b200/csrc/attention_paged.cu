@@ -201,6 +201,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc, con
                                          const int* __restrict__ cu_q, const int* __restrict__ kv_before,
                                          const int* __restrict__ seq_of_token, T* __restrict__ out, int n_tokens,
                                          int nh, int D, int window, int split_keys, int max_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= n_tokens * nh) return;
@@ -300,13 +302,13 @@ extern "C" int tm_attention_combine(int dtype, const float* part_acc, const floa
   const int warps = 4;
   const dim3 grid((rows + warps - 1) / warps);
   if (dtype == TM_DTYPE_F32)
-    tmk::attention_combine_kernel<float><<<grid, warps * 32, 0, stream>>>(
-        part_acc, part_ml, cu_q, kv_before, seq_of_token, (float*)out, n_tokens, nh, D, window, split_keys,
-        max_splits);
+    return tmk::launch_pdl(tmk::attention_combine_kernel<float>, grid, dim3(warps * 32), 0, stream, part_acc, part_ml,
+                           cu_q, kv_before, seq_of_token, (float*)out, n_tokens, nh, D, window, split_keys,
+                           max_splits);
   else if (dtype == TM_DTYPE_BF16)
-    tmk::attention_combine_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
-        part_acc, part_ml, cu_q, kv_before, seq_of_token, (__nv_bfloat16*)out, n_tokens, nh, D, window,
-        split_keys, max_splits);
+    return tmk::launch_pdl(tmk::attention_combine_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, stream, part_acc,
+                           part_ml, cu_q, kv_before, seq_of_token, (__nv_bfloat16*)out, n_tokens, nh, D, window,
+                           split_keys, max_splits);
   else
     return TM_ERR_BAD_DTYPE;
   return tmk::launch_status();

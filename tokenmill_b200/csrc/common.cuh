@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TM_DTYPE_F32 0
 #define TM_DTYPE_BF16 1
@@ -78,5 +79,40 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 }
 
 inline int launch_status() { return static_cast<int>(cudaPeekAtLastError()); }
+
+// Programmatic dependent launch. A kernel launched through launch_pdl may start while the kernel before it
+// on the stream is still running; it may touch nothing that kernel (or an earlier one) reads or writes until
+// it has passed pdl_wait(), which returns once the earlier kernel has completed and its writes are visible.
+// What it can do before that is what depends on no earlier kernel: read its weights. pdl_launch_dependents()
+// tells the scheduler that the kernel after this one may start. Every kernel in such a chain calls
+// pdl_wait() before it exits, so completion of one implies completion of all before it. Both calls do
+// nothing in a kernel that was launched the ordinary way. TOKENMILL_PDL=0 turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TOKENMILL_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
 
 }  // namespace tmk

@@ -93,19 +93,6 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(const Skinny
   unsigned char* xs = sk_smem;
   float* red = reinterpret_cast<float*>(sk_smem + (size_t)MT * 16 * row_bytes);   // [8 warps][MT*16][8]
 
-  // Stage the activations (rows beyond T and columns beyond the range are zero).
-  {
-    const int chunks = kpad / 8;
-    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(xs));
-    for (int idx = tid; idx < MT * 16 * chunks; idx += kSkWarps * 32) {
-      const int r = idx / chunks, c = idx - r * chunks;
-      const bool ok = r < a.T && c * 8 < kspan;
-      const __nv_bfloat16* src = ok ? a.x + (size_t)r * a.ldx + kc0 + c * 8 : a.x;
-      sk_cp_async16(base + r * row_bytes + c * 16, src, ok);
-    }
-    asm volatile("cp.async.commit_group;\n" ::);
-  }
-
   const int kw = kSkWarps / a.ng;                      // warps per feature group
   const int g = warp / kw, kpart = warp - g * kw;
   const int row0 = sk_group_row(a, blockIdx.x, g);
@@ -128,7 +115,23 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(const Skinny
     return make_uint4(0u, 0u, 0u, 0u);
   };
 #pragma unroll
-  for (int u = 0; u < U; ++u) wreg[u] = load_w(c_begin + u);
+  for (int u = 0; u < U; ++u) wreg[u] = load_w(c_begin + u);   // weights depend on no earlier kernel
+  pdl_launch_dependents();
+  pdl_wait();                                                  // the activations do
+
+  // Stage the activations (rows beyond T and columns beyond the range are zero).
+  {
+    const int chunks = kpad / 8;
+    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(xs));
+    for (int idx = tid; idx < MT * 16 * chunks; idx += kSkWarps * 32) {
+      const int r = idx / chunks, c = idx - r * chunks;
+      const bool ok = r < a.T && c * 8 < kspan;
+      const __nv_bfloat16* src = ok ? a.x + (size_t)r * a.ldx + kc0 + c * 8 : a.x;
+      sk_cp_async16(base + r * row_bytes + c * 16, src, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+
   asm volatile("cp.async.wait_group 0;\n" ::);
   __syncthreads();
 
@@ -249,7 +252,8 @@ static int sk_launch(const SkinnyArgs& a, int blocks_x, int blocks_y, cudaStream
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
       if (e != cudaSuccess) return (int)e;                                                                    \
     }                                                                                                         \
-    kern<<<grid, kSkWarps * 32, smem, stream>>>(a);                                                           \
+    const int st = launch_pdl(kern, grid, dim3(kSkWarps * 32), smem, stream, a);                              \
+    if (st != 0) return st;                                                                                   \
   }
   if (mt == 1) SK_CASE(1) else if (mt == 2) SK_CASE(2) else SK_CASE(4)
 #undef SK_CASE

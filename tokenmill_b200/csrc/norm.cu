@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(
     const int* __restrict__ rows, const float* __restrict__ weight, float eps, T* __restrict__ out, int H) {
   extern __shared__ __align__(16) float xs[];  // H floats + 32 for the reduction
   float* red = xs + H;
+  pdl_launch_dependents();
+  pdl_wait();                                  // everything this kernel reads comes from the kernels before it
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const bool write_back = !rows && (ids || branch || partials);
@@ -95,9 +97,8 @@ int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<n_rows, 256, smem, stream>>>(resid, (const T*)branch, partials, n_partials, partial_stride, ids,
-                                     (const T*)table, rows, weight, eps, (T*)out, H);
-  return launch_status();
+  return launch_pdl(kern, dim3(n_rows), dim3(256), smem, stream, resid, (const T*)branch, partials, n_partials,
+                    partial_stride, ids, (const T*)table, rows, weight, eps, (T*)out, H);
 }
 
 }  // namespace tmk
