@@ -240,3 +240,67 @@ def test_prompt_products_on_tcgen05_when_switched_on(tmp_path, monkeypatch, plai
     outputs = run_trace(folder, "bfloat16", steps, 512, tmp_path / "o")
     check_against_plain(steps, outputs, reqs, plain_for(folder, reqs, plain_cache), "bfloat16")
     assert {"tm_tc_qkv_rope_write", "tm_tc_gate_up_swiglu", "tm_tc_linear"} <= set(calls)
+
+
+@pytest.fixture(scope="module")
+def d64_dir(tmp_path_factory):
+    """A small model whose head size (64) the tensor-core decode kernels and the whole-step kernel take:
+    3 layers, hidden 192, 6 query heads over 2 kv heads, feed-forward 328, vocabulary 500, untied."""
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    cfg = qwen2_config(vocab_size=500, hidden_size=192, intermediate_size=328, num_hidden_layers=3,
+                       num_attention_heads=6, num_key_value_heads=2, head_dim=64, rope_theta=50000.0,
+                       rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2048)
+    assert cfg["hidden_size"] != cfg["num_attention_heads"] * cfg["head_dim"]      # o_proj is not square
+    return write_random_model(tmp_path_factory.mktemp("d64"), cfg, seed=9)
+
+
+@pytest.mark.parametrize("mode", ["tail", "mixed", "many"])
+def test_whole_step_decode_kernel_matches_plain(d64_dir, mode, tmp_path, plain_cache, monkeypatch):
+    """Decode steps of at most 16 tokens run as ONE kernel (norms, projections, attention, feed-forward of
+    every layer). Logits must match the plain implementation like every other path: one request decoded for
+    300 steps across page edges and the key cut at 256; several requests decoding side by side while others
+    still feed prompt portions; and twelve requests decoding together."""
+    from tokenmill_b200.engine import runner as runner_mod
+    from replay_util import mixed_steps
+    made = []
+    real = runner_mod.fused.FusedDecoder
+    monkeypatch.setattr(runner_mod.fused, "FusedDecoder", lambda *a, **k: made.append(real(*a, **k)) or made[-1])
+    if mode == "tail":
+        reqs = make_requests(500, [310], seed=2)
+        steps, max_tokens = tail_decode_steps(reqs, tail=300)
+    elif mode == "mixed":
+        reqs = make_requests(500, [70, 133, 45, 200, 96, 61], seed=11)
+        steps, max_tokens = mixed_steps(reqs, seed=7, decode_tail=20)
+    else:
+        reqs = make_requests(500, [40 + 7 * i for i in range(12)], seed=5)
+        steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:-6], "want": [len(t) - 7]} for r, t in list(reqs.items())[:6]], "end": []},
+                 {"step": 1, "entries": [{"id": r, "tokens": t[:-6], "want": [len(t) - 7]} for r, t in list(reqs.items())[6:]], "end": []}]
+        for i in range(6):
+            steps.append({"step": 2 + i, "entries": [{"id": r, "tokens": [t[len(t) - 6 + i]], "want": [0]} for r, t in reqs.items()],
+                          "end": list(reqs) if i == 5 else []})
+        max_tokens = sum(-(-len(t) // 64) * 64 for t in reqs.values())
+    outputs = run_trace(d64_dir, "bfloat16", steps, max_tokens, tmp_path / "o")
+    check_against_plain(steps, outputs, reqs, plain_for(d64_dir, reqs, plain_cache), "bfloat16")
+    assert made and made[0].launches >= (290 if mode == "tail" else 6)
+    made[0].check()
+    assert made[0].bar.item() == 0 and int(made[0].attn_count.abs().sum()) == 0      # left clean for the next launch
+
+
+def test_whole_step_decode_kernel_through_the_engine(d64_dir):
+    """Greedy generation with the whole-step kernel equals generation with it switched off, token for
+    token where the plain logits are not a near-tie, and the engine reports which path ran."""
+    from tokenmill_b200.kernels import fused
+    prompts = prompts_for(d64_dir, lengths=(3, 17, 40, 5, 64, 9, 33, 12))
+    eng = engine_for(d64_dir, dtype="bfloat16", max_model_len=512)
+    outs = eng.generate(prompts, greedy(40))
+    assert eng.runner.stats["fused_steps"] >= 39 and eng.cache.all_free
+    assert_tokens_are_argmax_of_plain(d64_dir, prompts, outs, "bfloat16")
+    old = fused._ENABLED
+    fused._ENABLED = False
+    try:
+        plain_path = engine_for(d64_dir, dtype="bfloat16", max_model_len=512)
+        assert plain_path.runner.fused is None
+        outs2 = plain_path.generate(prompts, greedy(40))
+    finally:
+        fused._ENABLED = old
+    assert_tokens_are_argmax_of_plain(d64_dir, prompts, outs2, "bfloat16")

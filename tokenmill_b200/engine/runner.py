@@ -22,7 +22,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pool import CachePools
-from ..kernels import lib, ops
+from ..kernels import fused, lib, ops
 from ..parts.attention import SPLIT_KEYS, AttentionScratch
 from ..parts.base import StepInputs
 from ..parts.model import DecoderModel
@@ -48,7 +48,11 @@ class ModelRunner:
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
         self.kernels_per_graph: dict[int, int] = {}
-        self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0}
+        self.stats = {"steps": 0, "graph_steps": 0, "fused_steps": 0, "tokens": 0}
+        # One kernel per decode step when the model is the arrangement that kernel implements.
+        self.fused = None
+        if fused.eligible(model) and len(self.layout.groups) == 1:
+            self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len, SPLIT_KEYS)
         if self.graph_max_batch:
             if any(s < 0 for s in pools.sink):
                 raise RuntimeError("decode graphs need pools built with a sink page")
@@ -68,6 +72,16 @@ class ModelRunner:
                                  f"{self.max_model_len}")
         self.stats["steps"] += 1
         self.stats["tokens"] += sum(len(e.tokens) for e in entries)
+        if self.fused is not None:
+            self.fused.check()
+            if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
+                step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
+                                         split_keys=SPLIT_KEYS)
+                if self.fused.takes(step):
+                    self.stats["fused_steps"] += 1
+                    hidden = self.fused.run(step, self.cache.page_size)
+                    return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
+                return self.model.forward(step, self.layer_caches)
         if self.graph_max_batch and len(entries) <= self.graph_max_batch and \
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return self._graph_step(entries)

@@ -1,0 +1,166 @@
+"""The whole-step decode kernel (csrc/decode_fused_bf16.cu) seen from Python.
+
+A ``FusedDecoder`` is built from a ``DecoderModel`` when every layer is the arrangement the kernel
+implements (pre-norm block, grouped-query attention with rotary encoding, SwiGLU feed-forward, RMSNorm,
+bfloat16, head size 64 or 128, one cache group). It owns the kernel's workspaces and the device table of
+per-layer pointers; ``run`` launches one cooperative kernel for a step of at most 16 tokens and returns the
+normed hidden rows the output matrix is applied to. Models that do not fit simply get no ``FusedDecoder``
+and keep the kernel-per-operation path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import lib
+
+MAX_TOKENS = 16
+_ENABLED = os.environ.get("TOKENMILL_FUSED_DECODE", "1") != "0"
+
+
+class _Layer(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in ("ln1_w", "w_qkv", "b_qkv", "kcache", "vcache", "w_o", "ln2_w", "w_gu", "w_down")]
+
+
+class _Args(ctypes.Structure):
+    _fields_ = (
+        [("layers", c_void_p), ("n_layers", c_int)]
+        + [(n, c_int) for n in ("H", "nh", "nkv", "D", "I")]
+        + [(n, c_float) for n in ("eps1", "eps2", "eps_f", "scale_log2")]
+        + [("window", c_int)]
+        + [(n, c_void_p) for n in ("embedding", "final_ln_w", "cos_t", "sin_t")]
+        + [("n_pos", c_int)]
+        + [(n, c_void_p) for n in ("token_ids", "positions", "slot_map", "block_table")]
+        + [("bt_stride", c_int)]
+        + [(n, c_void_p) for n in ("cu_q", "kv_before", "want_rows")]
+        + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
+        + [(n, c_void_p) for n in ("resid0", "resid1", "q", "part_acc", "part_ml", "attn", "o_out", "act", "d_out",
+                                   "attn_count", "bar", "error", "hidden_out")]
+    )
+
+
+def eligible(model) -> bool:
+    """Whether every layer of the model is the arrangement the fused kernel implements."""
+    from ..parts.attention import GroupedQueryAttention
+    from ..parts.block import PreNormBlock
+    from ..parts.norm import RMSNorm
+    from ..parts.swiglu import SwiGLUFeedForward
+
+    if not _ENABLED or model.dtype != torch.bfloat16 or model.device.type != "cuda":
+        return False
+    if not model.spec.run_order or any(e.cache_of is not None for e in model.spec.run_order):
+        return False
+    first = model.blocks[model.spec.run_order[0].layer].mixer
+    if not isinstance(first, GroupedQueryAttention):
+        return False
+    for e in model.spec.run_order:
+        b = model.blocks[e.layer]
+        m, f = b.mixer, b.feed_forward
+        if type(b) is not PreNormBlock or type(m) is not GroupedQueryAttention or type(f) is not SwiGLUFeedForward:
+            return False
+        if type(b.mixer_norm) is not RMSNorm or type(b.feed_forward_norm) is not RMSNorm:
+            return False
+        if (m.nh, m.nkv, m.D, m.window, m.scale, m.hidden_size) != (first.nh, first.nkv, first.D, first.window,
+                                                                   first.scale, first.hidden_size):
+            return False
+        if m.position is None or m.cos.data_ptr() != first.cos.data_ptr():
+            return False
+        if f.intermediate_size != model.blocks[model.spec.run_order[0].layer].feed_forward.intermediate_size:
+            return False
+        if b.mixer_norm.eps != model.blocks[model.spec.run_order[0].layer].mixer_norm.eps or \
+                b.feed_forward_norm.eps != model.blocks[model.spec.run_order[0].layer].feed_forward_norm.eps:
+            return False
+    H, I = model.spec.hidden_size, model.blocks[0].feed_forward.intermediate_size
+    return (type(model.final_norm) is RMSNorm and first.D in (64, 128) and H % 8 == 0 and I % 8 == 0
+            and first.q_size % 8 == 0 and first.nh // first.nkv <= 16 and len(model.cache_layout().groups) == 1)
+
+
+class FusedDecoder:
+    def __init__(self, model, layer_caches, max_model_len: int, split_keys: int):
+        assert ctypes.sizeof(_Args) == lib.load().tm_decode_fused_args_size(), "FusedArgs layout mismatch"
+        assert ctypes.sizeof(_Layer) == lib.load().tm_decode_fused_layer_size(), "FusedLayer layout mismatch"
+        self.model, self.device = model, model.device
+        dev, bf = self.device, torch.bfloat16
+        order = model.spec.run_order
+        first = model.blocks[order[0].layer]
+        m0, f0 = first.mixer, first.feed_forward
+        self.H, self.nh, self.nkv, self.D, self.I = model.spec.hidden_size, m0.nh, m0.nkv, m0.D, f0.intermediate_size
+        self.split_keys = split_keys
+        self.max_splits_cap = -(-max_model_len // split_keys)
+        layers = (_Layer * len(order))()
+        for i, e in enumerate(order):
+            b, lc = model.blocks[e.layer], layer_caches[i]
+            layers[i] = _Layer(b.mixer_norm.weight.data_ptr(), b.mixer.w_qkv.data_ptr(),
+                               b.mixer.b_qkv.data_ptr() if b.mixer.b_qkv is not None else None,
+                               lc.k.data_ptr(), lc.v.data_ptr(), b.mixer.w_o.data_ptr(),
+                               b.feed_forward_norm.weight.data_ptr(), b.feed_forward.w_gate_up.data_ptr(),
+                               b.feed_forward.w_down.data_ptr())
+        self._layers_dev = torch.frombuffer(bytearray(bytes(layers)), dtype=torch.uint8).to(dev)
+        self._keep = layer_caches           # the table holds raw pointers into these tensors
+        T, rows = MAX_TOKENS, MAX_TOKENS * self.nh * self.max_splits_cap
+        self.resid = torch.empty((2, T, self.H), dtype=torch.float32, device=dev)
+        self.q = torch.empty((T, self.nh, self.D), dtype=bf, device=dev)
+        self.part_acc = torch.empty(rows * self.D, dtype=torch.float32, device=dev)
+        self.part_ml = torch.empty(rows * 2, dtype=torch.float32, device=dev)
+        self.attn = torch.empty((T, self.nh * self.D), dtype=bf, device=dev)
+        self.o_out = torch.empty((T, self.H), dtype=torch.float32, device=dev)
+        self.act = torch.empty((T, self.I), dtype=bf, device=dev)
+        self.d_out = torch.empty((T, self.H), dtype=torch.float32, device=dev)
+        self.attn_count = torch.zeros(T * self.nkv, dtype=torch.int32, device=dev)
+        self.bar = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.error = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.hidden = torch.empty((T, self.H), dtype=bf, device=dev)
+        self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        a = _Args()
+        a.layers, a.n_layers = self._layers_dev.data_ptr(), len(order)
+        a.H, a.nh, a.nkv, a.D, a.I = self.H, self.nh, self.nkv, self.D, self.I
+        a.eps1, a.eps2, a.eps_f = first.mixer_norm.eps, first.feed_forward_norm.eps, model.final_norm.eps
+        a.scale_log2 = m0.scale * 1.4426950408889634
+        a.window = m0.window
+        a.embedding, a.final_ln_w = model.embedding.data_ptr(), model.final_norm.weight.data_ptr()
+        a.cos_t, a.sin_t, a.n_pos = m0.cos.data_ptr(), m0.sin.data_ptr(), m0.cos.shape[0]
+        a.resid0, a.resid1 = self.resid[0].data_ptr(), self.resid[1].data_ptr()
+        a.q, a.part_acc, a.part_ml, a.attn = (self.q.data_ptr(), self.part_acc.data_ptr(), self.part_ml.data_ptr(),
+                                              self.attn.data_ptr())
+        a.o_out, a.act, a.d_out = self.o_out.data_ptr(), self.act.data_ptr(), self.d_out.data_ptr()
+        a.attn_count, a.bar, a.error = self.attn_count.data_ptr(), self.bar.data_ptr(), self.error.data_ptr()
+        a.hidden_out = self.hidden.data_ptr()
+        a.split_keys = split_keys
+        self._args = a
+        self.launches = 0
+
+    def takes(self, step) -> bool:
+        G = self.nh // self.nkv
+        return (step.n_tokens <= MAX_TOKENS and step.max_q_len * G <= 16 and step.n_want > 0
+                and step.n_want <= MAX_TOKENS and len(step.block_tables) == 1)
+
+    def run(self, step, page_size: int) -> torch.Tensor:
+        """Normed hidden rows [n_want, H] (bfloat16) of the step's wanted places."""
+        a = self._args
+        a.token_ids, a.positions = step.token_ids.data_ptr(), step.positions.data_ptr()
+        a.slot_map, a.block_table = step.slot_maps[0].data_ptr(), step.block_tables[0].data_ptr()
+        a.bt_stride = step.block_tables[0].stride(0)
+        a.cu_q, a.kv_before, a.want_rows = step.cu_q.data_ptr(), step.kv_before.data_ptr(), step.want_rows.data_ptr()
+        a.T, a.S, a.n_want, a.page_size = step.n_tokens, step.n_seqs, step.n_want, page_size
+        a.max_splits = min(self.max_splits_cap, max(1, -(-step.max_kv_len // self.split_keys)))
+        lib.call("tm_decode_fused", ctypes.addressof(a), torch.cuda.current_stream().cuda_stream)
+        self._err_host.copy_(self.error, non_blocking=True)     # looked at by check() after the step's own sync
+        self.launches += 1
+        return self.hidden[:step.n_want]
+
+    def check(self) -> None:
+        """Raise if a block of the fused kernel gave up at a barrier in an earlier step. The error word
+        travels to pinned host memory behind every launch; this reads the host copy (no synchronisation),
+        so it reports a failure once the stream has been synchronised, at the latest one step later."""
+        code = int(self._err_host[0])
+        if code:
+            self._err_host.zero_()
+            self.error.zero_()
+            self.bar.zero_()
+            self.attn_count.zero_()
+            raise lib.KernelError(f"the fused decode kernel gave up at grid barrier {code - 100}; the step's "
+                                  f"results are incomplete")
