@@ -19,6 +19,7 @@ import torch
 from . import lib
 
 MAX_TOKENS = 16
+SPLIT_KEYS = 64          # one 64-key block per attention unit: all of a request's keys are read in parallel
 _ENABLED = os.environ.get("TOKENMILL_FUSED_DECODE", "1") != "0"
 
 
@@ -38,8 +39,8 @@ class _Args(ctypes.Structure):
         + [("bt_stride", c_int)]
         + [(n, c_void_p) for n in ("cu_q", "kv_before", "want_rows")]
         + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
-        + [(n, c_void_p) for n in ("resid0", "resid1", "q", "part_acc", "part_ml", "attn", "o_out", "act", "d_out",
-                                   "attn_count", "bar", "error", "hidden_out")]
+        + [(n, c_void_p) for n in ("resid", "q", "part_acc", "part_ml", "attn", "act", "attn_count", "bar",
+                                   "error", "hidden_out", "timing")]
     )
 
 
@@ -102,14 +103,12 @@ class FusedDecoder:
         self._layers_dev = torch.frombuffer(bytearray(bytes(layers)), dtype=torch.uint8).to(dev)
         self._keep = layer_caches           # the table holds raw pointers into these tensors
         T, rows = MAX_TOKENS, MAX_TOKENS * self.nh * self.max_splits_cap
-        self.resid = torch.empty((2, T, self.H), dtype=torch.float32, device=dev)
+        self.resid = torch.empty((T, self.H), dtype=torch.float32, device=dev)
         self.q = torch.empty((T, self.nh, self.D), dtype=bf, device=dev)
         self.part_acc = torch.empty(rows * self.D, dtype=torch.float32, device=dev)
         self.part_ml = torch.empty(rows * 2, dtype=torch.float32, device=dev)
         self.attn = torch.empty((T, self.nh * self.D), dtype=bf, device=dev)
-        self.o_out = torch.empty((T, self.H), dtype=torch.float32, device=dev)
         self.act = torch.empty((T, self.I), dtype=bf, device=dev)
-        self.d_out = torch.empty((T, self.H), dtype=torch.float32, device=dev)
         self.attn_count = torch.zeros(T * self.nkv, dtype=torch.int32, device=dev)
         self.bar = torch.zeros(1, dtype=torch.int32, device=dev)
         self.error = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -123,15 +122,24 @@ class FusedDecoder:
         a.window = m0.window
         a.embedding, a.final_ln_w = model.embedding.data_ptr(), model.final_norm.weight.data_ptr()
         a.cos_t, a.sin_t, a.n_pos = m0.cos.data_ptr(), m0.sin.data_ptr(), m0.cos.shape[0]
-        a.resid0, a.resid1 = self.resid[0].data_ptr(), self.resid[1].data_ptr()
+        a.resid = self.resid.data_ptr()
         a.q, a.part_acc, a.part_ml, a.attn = (self.q.data_ptr(), self.part_acc.data_ptr(), self.part_ml.data_ptr(),
                                               self.attn.data_ptr())
-        a.o_out, a.act, a.d_out = self.o_out.data_ptr(), self.act.data_ptr(), self.d_out.data_ptr()
+        a.act = self.act.data_ptr()
         a.attn_count, a.bar, a.error = self.attn_count.data_ptr(), self.bar.data_ptr(), self.error.data_ptr()
         a.hidden_out = self.hidden.data_ptr()
         a.split_keys = split_keys
         self._args = a
         self.launches = 0
+        self.timing: torch.Tensor | None = None
+
+    def enable_timing(self) -> torch.Tensor:
+        """Profiling aid: block 0 stamps the nanosecond timer at every phase boundary into the returned
+        int64 tensor [n_layers * 10 + 1] (slots per layer: 0 start, 1 norm done, 2 QKV done, 3 barrier passed,
+        4 attention done, 5 barrier passed, 6 o_proj done, 7 second norm done, 8 gate/up done, 9 down done)."""
+        self.timing = torch.zeros(self._args.n_layers * 10 + 1, dtype=torch.int64, device=self.device)
+        self._args.timing = self.timing.data_ptr()
+        return self.timing
 
     def takes(self, step) -> bool:
         G = self.nh // self.nkv
