@@ -254,21 +254,28 @@ def d64_dir(tmp_path_factory):
     return write_random_model(tmp_path_factory.mktemp("d64"), cfg, seed=9)
 
 
-@pytest.mark.parametrize("mode", ["tail", "mixed", "many"])
+@pytest.mark.parametrize("mode", ["tail", "mixed", "many", "tail-whole", "mixed-whole", "long-whole"])
 def test_whole_step_decode_kernel_matches_plain(d64_dir, mode, tmp_path, plain_cache, monkeypatch):
     """Decode steps of at most 16 tokens run as ONE kernel (norms, projections, attention, feed-forward of
     every layer). Logits must match the plain implementation like every other path: one request decoded for
-    300 steps across page edges and the key cut at 256; several requests decoding side by side while others
-    still feed prompt portions; and twelve requests decoding together."""
+    300 steps across page edges; several requests decoding side by side while others still feed prompt
+    portions; twelve requests decoding together (a request's keys are split across blocks, the partials merged by
+    the last block to finish); the same with one block attending all keys of a request; and that with a
+    context so long that a warp takes its keys in several rounds."""
     from tokenmill_b200.engine import runner as runner_mod
     from replay_util import mixed_steps
     made = []
     real = runner_mod.fused.FusedDecoder
     monkeypatch.setattr(runner_mod.fused, "FusedDecoder", lambda *a, **k: made.append(real(*a, **k)) or made[-1])
-    if mode == "tail":
+    if mode.endswith("whole"):       # one block attends all keys of a (request, kv head): no partials
+        monkeypatch.setattr(real, "split_for", lambda self, n, kv: 4096)
+    if mode.startswith("tail"):
         reqs = make_requests(500, [310], seed=2)
         steps, max_tokens = tail_decode_steps(reqs, tail=300)
-    elif mode == "mixed":
+    elif mode.startswith("long"):
+        reqs = make_requests(500, [1000], seed=3)
+        steps, max_tokens = tail_decode_steps(reqs, tail=40)
+    elif mode.startswith("mixed"):
         reqs = make_requests(500, [70, 133, 45, 200, 96, 61], seed=11)
         steps, max_tokens = mixed_steps(reqs, seed=7, decode_tail=20)
     else:
@@ -281,7 +288,7 @@ def test_whole_step_decode_kernel_matches_plain(d64_dir, mode, tmp_path, plain_c
         max_tokens = sum(-(-len(t) // 64) * 64 for t in reqs.values())
     outputs = run_trace(d64_dir, "bfloat16", steps, max_tokens, tmp_path / "o")
     check_against_plain(steps, outputs, reqs, plain_for(d64_dir, reqs, plain_cache), "bfloat16")
-    assert made and made[0].launches >= (290 if mode == "tail" else 6)
+    assert made and made[0].launches >= {"tail": 290, "tail-whole": 290, "long-whole": 36}.get(mode, 6)
     made[0].check()
     assert made[0].bar.item() == 0 and int(made[0].attn_count.abs().sum()) == 0      # left clean for the next launch
 

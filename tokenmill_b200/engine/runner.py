@@ -52,7 +52,7 @@ class ModelRunner:
         # One kernel per decode step when the model is the arrangement that kernel implements.
         self.fused = None
         if fused.eligible(model) and len(self.layout.groups) == 1:
-            self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len, fused.SPLIT_KEYS)
+            self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len)
         if self.graph_max_batch:
             if any(s < 0 for s in pools.sink):
                 raise RuntimeError("decode graphs need pools built with a sink page")

@@ -112,6 +112,9 @@ def build(verbose: bool = True, force: bool = False) -> Path:
         tmp = out_dir / f".{lib.name}.{os.getpid()}.tmp"
         _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in objs], "-lcuda"])
         os.replace(tmp, lib)  # atomic: a concurrent builder never sees half a library
+        for stale in out_dir.glob("libtokenmill_kernels_*.so"):     # libraries of earlier source states
+            if stale != lib:
+                stale.unlink(missing_ok=True)   # a process that has one mapped keeps its copy
     finally:
         done.set()
         shutil.rmtree(obj_dir, ignore_errors=True)

@@ -19,7 +19,7 @@ import torch
 from . import lib
 
 MAX_TOKENS = 16
-SPLIT_KEYS = 64          # one 64-key block per attention unit: all of a request's keys are read in parallel
+SPLIT_KEYS = 64          # granularity of the key split of attention (a block attends a multiple of this)
 _ENABLED = os.environ.get("TOKENMILL_FUSED_DECODE", "1") != "0"
 
 
@@ -40,7 +40,8 @@ class _Args(ctypes.Structure):
         + [(n, c_void_p) for n in ("cu_q", "kv_before", "want_rows")]
         + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
         + [(n, c_void_p) for n in ("resid", "q", "part_acc", "part_ml", "attn", "act", "attn_count", "bar",
-                                   "error", "hidden_out", "timing")]
+                                   "error", "hidden_out")]
+        + [("smem_bytes", c_int), ("timing", c_void_p)]
     )
 
 
@@ -80,8 +81,21 @@ def eligible(model) -> bool:
             and first.q_size % 8 == 0 and first.nh // first.nkv <= 16 and len(model.cache_layout().groups) == 1)
 
 
+def pack_rows(w: torch.Tensor) -> torch.Tensor:
+    """The copy of a [N, K] weight matrix the fused kernel streams: [N/8 row groups][K/32 chunks][8 rows]
+    [4 pieces][8 elements], padded with zeros, so that the 32 lanes of a warp, lane 4 g + t holding row g and
+    columns 8 t .. 8 t + 7 of a chunk, read 512 contiguous bytes."""
+    N, K = w.shape
+    Np, Kp = -(-N // 8) * 8, -(-K // 32) * 32
+    if (Np, Kp) != (N, K):
+        padded = torch.zeros((Np, Kp), dtype=w.dtype, device=w.device)
+        padded[:N, :K] = w
+        w = padded
+    return w.view(Np // 8, 8, Kp // 32, 4, 8).permute(0, 2, 1, 3, 4).contiguous()
+
+
 class FusedDecoder:
-    def __init__(self, model, layer_caches, max_model_len: int, split_keys: int):
+    def __init__(self, model, layer_caches, max_model_len: int):
         assert ctypes.sizeof(_Args) == lib.load().tm_decode_fused_args_size(), "FusedArgs layout mismatch"
         assert ctypes.sizeof(_Layer) == lib.load().tm_decode_fused_layer_size(), "FusedLayer layout mismatch"
         self.model, self.device = model, model.device
@@ -90,16 +104,19 @@ class FusedDecoder:
         first = model.blocks[order[0].layer]
         m0, f0 = first.mixer, first.feed_forward
         self.H, self.nh, self.nkv, self.D, self.I = model.spec.hidden_size, m0.nh, m0.nkv, m0.D, f0.intermediate_size
-        self.split_keys = split_keys
-        self.max_splits_cap = -(-max_model_len // split_keys)
+        self.max_splits_cap = -(-max_model_len // SPLIT_KEYS)
         layers = (_Layer * len(order))()
+        self._packed: dict[int, tuple[torch.Tensor, ...]] = {}      # by layer: a layer run twice is packed once
         for i, e in enumerate(order):
             b, lc = model.blocks[e.layer], layer_caches[i]
-            layers[i] = _Layer(b.mixer_norm.weight.data_ptr(), b.mixer.w_qkv.data_ptr(),
+            if e.layer not in self._packed:
+                self._packed[e.layer] = tuple(pack_rows(w) for w in (b.mixer.w_qkv, b.mixer.w_o,
+                                                                     b.feed_forward.w_gate_up, b.feed_forward.w_down))
+            w_qkv, w_o, w_gu, w_down = self._packed[e.layer]
+            layers[i] = _Layer(b.mixer_norm.weight.data_ptr(), w_qkv.data_ptr(),
                                b.mixer.b_qkv.data_ptr() if b.mixer.b_qkv is not None else None,
-                               lc.k.data_ptr(), lc.v.data_ptr(), b.mixer.w_o.data_ptr(),
-                               b.feed_forward_norm.weight.data_ptr(), b.feed_forward.w_gate_up.data_ptr(),
-                               b.feed_forward.w_down.data_ptr())
+                               lc.k.data_ptr(), lc.v.data_ptr(), w_o.data_ptr(),
+                               b.feed_forward_norm.weight.data_ptr(), w_gu.data_ptr(), w_down.data_ptr())
         self._layers_dev = torch.frombuffer(bytearray(bytes(layers)), dtype=torch.uint8).to(dev)
         self._keep = layer_caches           # the table holds raw pointers into these tensors
         T, rows = MAX_TOKENS, MAX_TOKENS * self.nh * self.max_splits_cap
@@ -128,18 +145,30 @@ class FusedDecoder:
         a.act = self.act.data_ptr()
         a.attn_count, a.bar, a.error = self.attn_count.data_ptr(), self.bar.data_ptr(), self.error.data_ptr()
         a.hidden_out = self.hidden.data_ptr()
-        a.split_keys = split_keys
         self._args = a
+        self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
         self.launches = 0
         self.timing: torch.Tensor | None = None
 
     def enable_timing(self) -> torch.Tensor:
         """Profiling aid: block 0 stamps the nanosecond timer at every phase boundary into the returned
-        int64 tensor [n_layers * 10 + 1] (slots per layer: 0 start, 1 norm done, 2 QKV done, 3 barrier passed,
-        4 attention done, 5 barrier passed, 6 o_proj done, 7 second norm done, 8 gate/up done, 9 down done)."""
-        self.timing = torch.zeros(self._args.n_layers * 10 + 1, dtype=torch.int64, device=self.device)
+        int64 tensor [n_layers * 16 + 1] (slots per layer: 0 start, 1 norm done, 2 QKV done, 3 barrier passed,
+        4 attention done, 5 barrier passed, 6 o_proj done, 7 second norm done, 8 gate/up done, 9 down done;
+        inside block 0's first attention unit: 10 copies issued, 11 copies landed, 12 keys done, 13 all warps
+        done, 14 states merged)."""
+        self.timing = torch.zeros(self._args.n_layers * 16 + 1, dtype=torch.int64, device=self.device)
         self._args.timing = self.timing.data_ptr()
         return self.timing
+
+    def split_for(self, n_seqs: int, max_kv_len: int) -> int:
+        """Keys per attention unit: the finest split (a multiple of SPLIT_KEYS) with which the units
+        (request, kv head, split) still fit the grid in one round. A block takes in data at a fixed rate, so
+        spreading a request's keys over many blocks beats one block streaming them all, until the blocks run out."""
+        blocks = -(-max(1, max_kv_len) // SPLIT_KEYS)
+        per_unit = 1
+        while n_seqs * self.nkv * -(-blocks // per_unit) > self.n_sm and per_unit < blocks:
+            per_unit += 1
+        return per_unit * SPLIT_KEYS
 
     def takes(self, step) -> bool:
         G = self.nh // self.nkv
@@ -154,7 +183,8 @@ class FusedDecoder:
         a.bt_stride = step.block_tables[0].stride(0)
         a.cu_q, a.kv_before, a.want_rows = step.cu_q.data_ptr(), step.kv_before.data_ptr(), step.want_rows.data_ptr()
         a.T, a.S, a.n_want, a.page_size = step.n_tokens, step.n_seqs, step.n_want, page_size
-        a.max_splits = min(self.max_splits_cap, max(1, -(-step.max_kv_len // self.split_keys)))
+        a.split_keys = self.split_for(step.n_seqs, step.max_kv_len)
+        a.max_splits = -(-step.max_kv_len // a.split_keys)
         lib.call("tm_decode_fused", ctypes.addressof(a), torch.cuda.current_stream().cuda_stream)
         self._err_host.copy_(self.error, non_blocking=True)     # looked at by check() after the step's own sync
         self.launches += 1
