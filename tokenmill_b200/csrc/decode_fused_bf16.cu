@@ -10,23 +10,34 @@
 // (one atomic arrival counter in global memory, monotone within a launch), so a phase boundary costs an L2
 // round trip instead of a launch and a drain.
 //
+// Weights never wait for a phase: every block knows from the start which pieces of which matrices it will
+// multiply, in which order, for the whole launch. It streams them through a ring of shared-memory stages with
+// bulk asynchronous copies (cp.async.bulk, completion on an mbarrier per stage), a few stages ahead of the
+// arithmetic and across phase and layer boundaries; the warps that used a stage up ask for the piece that
+// comes next into it. Inputs that other blocks wrote (head outputs, activations) come in the same way, one
+// bulk copy per token row, after the grid barrier that makes them complete. A measurement on this machine decided the form: a warp reading 8 rows x 64 bytes of a
+// row-major matrix gets about 20 GB/s per SM out of L2, 512 contiguous bytes per warp load about 50 GB/s,
+// bulk copies of 14 KB and more about 90 GB/s, bulk copies of a single 1.8 KB row 20 GB/s again. So the
+// matrices are read from a packed copy (see fu_packed_group) in which the 8 rows a warp multiplies at a time
+// are contiguous, in the order the tensor-core fragments want them.
+//
 // Phases per layer (the formulas are those of the separate kernels, which stay the reference for tests:
 // norm.cu, gemm_skinny_bf16.cu, attention_decode_bf16.cu; reference model: src/infer/model/qwen2.py:13-23,
 // src/infer/model/layers.py:127-164):
-//   A  every block computes x = residual (+ the previous layer's down-projection output, or the embedding
-//      rows for the first layer) for all tokens, norms it into shared memory, and block r writes row r of the
-//      new residual; then the blocks share the QKV weight rows (8 + 8 partner rows per unit, K cut across the
-//      8 warps), add bias, rotate, and write q and the cache slots.
-//   B  attention units (request, kv head, key split), two per block at a time (4 warps each); the unit that
-//      finishes a (request, kv head) last merges the splits in index order and writes the head outputs.
-//   C  output projection from the staged head outputs to a 32-bit [T, H] buffer.
-//   D  as A with the attention branch and the second norm, then gate/up + SwiGLU into a [T, I] buffer.
-//   E  down projection to a 32-bit [T, H] buffer, which the next layer's phase A (or the final norm) adds.
+//   A  every block norms the residual stream (the embedding rows in the first layer) for all tokens into
+//      shared memory; then the blocks share the QKV weight rows (8 rows and their 8 rotation partners per
+//      unit, K cut across the 8 warps), add bias, rotate, and write q and the cache slots.
+//   B  attention units (request, kv head, key split), one block each; the block that finishes a (request,
+//      kv head) last merges the splits in index order and writes the head outputs.
+//   C  output projection from the staged head outputs, added into the 32-bit residual stream.
+//   D  as A with the second norm, then gate/up + SwiGLU (a warp per unit) into a [T, I] buffer.
+//   E  down projection, added into the residual stream.
 // Data written by other blocks is read with L2-level loads (ld.global.cg / cp.async.cg), since L1 is not
 // coherent across SMs within a launch; weights are read-only.
 //
-// The barrier's spin is bounded: a block that waits too long raises the error word, stops working and
-// leaves; the others run into the same limit and leave too. The launch is cooperative, so all blocks are
+// Every wait is bounded: a block that waits too long at the grid barrier or for a stage raises the error
+// word, stops working and leaves; the others run into the same limit and leave too. Before leaving, a block
+// waits (bounded again) for the copies it still has in flight. The launch is cooperative, so all blocks are
 // resident together. The arrival counter is put back to zero by the last block to leave.
 #include "mma_util.cuh"
 
@@ -35,10 +46,12 @@ namespace tmk {
 constexpr int kFuThreads = 256;
 constexpr int kFuWarps = 8;
 constexpr uint32_t kFuSpinLimit = 1u << 22;
+constexpr int kFuMaxStages = 8;
+constexpr int kFuMaxLayers = 96;
 
 struct FusedLayer {
   const float* ln1_w;
-  // the four matrices in the packed layout described at fu_packed()
+  // the four matrices in the packed layout described at fu_packed_group()
   const __nv_bfloat16* w_qkv;      // [(nh + 2 nkv) D, H]
   const float* b_qkv;              // [(nh + 2 nkv) D] or null
   __nv_bfloat16* kcache;           // [pages, page_size, nkv, D]
@@ -82,10 +95,10 @@ struct FusedArgs {
   int* error;
   __nv_bfloat16* hidden_out;       // [n_want, H]
   int smem_bytes;                  // dynamic shared memory of the launch (set by the launcher)
+  int stage_bytes;                 // bytes of one stage of the weight ring (set by the launcher)
+  int l2_prefetch;                 // nonzero: ask for the next layer's weights into L2 during attention
   unsigned long long* timing;      // null, or [n_layers * 16 + 1] nanosecond stamps written by block 0 (profiling aid)
 };
-
-enum : int { FU_QKV = 0, FU_SWIGLU = 1, FU_ADD_RESID = 2 };
 
 __device__ __forceinline__ void fu_stamp(const FusedArgs& a, int slot) {
   if (a.timing && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -95,12 +108,6 @@ __device__ __forceinline__ void fu_stamp(const FusedArgs& a, int slot) {
   }
 }
 
-__device__ __forceinline__ uint4 fu_ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
 __device__ __forceinline__ void fu_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -110,8 +117,9 @@ __device__ __forceinline__ void fu_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 }
 
 // Ask for `bytes` at `base` to be brought into L2 (no completion to wait for): the whole grid shares the
-// range in 4 KB pieces, one instruction per piece. The weights of the phase after next stream from HBM
-// while this phase computes and the grid barriers are crossed, so the products read L2.
+// range in 4 KB pieces, one instruction per piece. The ring's stages hold a fraction of what two phases
+// multiply back to back; what lets the copies into the stages keep up is that the weights of the next
+// phases were pulled from HBM into L2 earlier, while the memory system was idle.
 __device__ __forceinline__ void fu_prefetch_l2(const void* base, size_t bytes) {
   if (!base || (reinterpret_cast<uintptr_t>(base) & 15)) return;
   constexpr size_t kPiece = 4096;
@@ -123,14 +131,21 @@ __device__ __forceinline__ void fu_prefetch_l2(const void* base, size_t bytes) {
   }
 }
 
+__device__ __forceinline__ uint4 fu_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
 // The weights are read in a packed copy (made once, when the decoder is set up): for every group of 8 rows
 // and every chunk of 32 columns, the 32 lanes' 16-byte pieces lie one after the other in lane order (lane
 // 4 g + t holds row g, columns 8 t .. 8 t + 7 of the chunk; rows and columns beyond the matrix are zeros).
-// A warp's load is then 512 contiguous bytes. With the plain row-major matrix the same load touches 8 rows
-// with 64 bytes each, which the memory system serves at a quarter of the rate.
+// A group's chunks follow one another, so any range of chunks of a group is one contiguous piece of
+// 512 bytes per chunk: one bulk copy, and in shared memory a warp's fragment load is 512 contiguous bytes.
 constexpr int kFuChunkElems = 32 * 8;
-__device__ __forceinline__ const __nv_bfloat16* fu_packed(const __nv_bfloat16* W, int row0, int n_chunks, int lane) {
-  return W + ((size_t)(row0 >> 3) * n_chunks * 32 + lane) * 8;
+constexpr int kFuChunkBytes = 512;
+__device__ __forceinline__ const __nv_bfloat16* fu_packed_group(const __nv_bfloat16* W, int row0, int n_chunks, int chunk) {
+  return W + ((size_t)(row0 >> 3) * n_chunks + chunk) * kFuChunkElems;
 }
 
 __device__ __forceinline__ int fu_row_bytes(int K) {
@@ -241,173 +256,261 @@ __device__ __noinline__ void fu_norm_rows(int T, int H, const __nv_bfloat16* emb
   }
 }
 
-// ---- The projections ---------------------------------------------------------------------------------------
-// The weight-streaming product of gemm_skinny_bf16.cu, shared out over the resident grid. A UNIT is 8 weight
-// rows and, where the epilogue needs two rows per output (a rotation pair of q/k/v; a gate row and its up
-// row), their 8 partner rows. The units are taken in passes; in a pass every block holds `upc` units (4, 2 or
-// 1: as many as keep all blocks busy) and cuts K across the kw = 8 / upc warps of a unit; partial sums meet in
-// shared memory in warp order, so the result does not depend on timing. A lane keeps kFuSlots pairs of
-// 16-byte weight loads in flight. The first pass's first loads can be issued before a grid barrier is
-// waited for (weights do not depend on other blocks), and an input other blocks wrote is staged by each
-// warp for its own K range, so that neither costs a round trip of its own.
-constexpr int kFuSlots = 7;
-
-struct FuTask {
-  int base, upc, kw;        // the pass: first unit, units per block, warps per unit
-  int u;                    // this warp's unit (may be beyond n_units: then the warp loads nothing)
-  int kpart, c_begin, c_end;
-  const __nv_bfloat16* wa;  // the lane's row of the unit, and of the partner rows (or the same row)
-  const __nv_bfloat16* wb;
-  bool ok_a, ok_b;
+// ---- The weight ring ---------------------------------------------------------------------------------------
+// A TILE is what one stage holds: chunks [c0, c0 + nc) of one group of 8 weight rows, and for the projections
+// whose epilogue needs two rows per output (a rotation pair of q/k/v; a gate row and its up row) the same
+// chunks of the partner group behind it. A UNIT is a row group (with its partner) over all of K: one tile, or
+// several when K does not fit a stage. Block b owns units b, b + grid, ... of every projection. Its tiles of
+// the whole launch form one sequence (layer by layer: QKV, output, gate/up, down; unit by unit; K part by K
+// part); tile i lives in stage i % nst and completes phase (i / nst) & 1 of that stage's barrier. Tile
+// i + nst is asked for by the thread that knows tile i has been used up.
+struct FuTileDesc;
+struct FuRing {
+  uint32_t base, bars;             // shared addresses of stage 0 and of its barrier
+  int stage_bytes, nst;
+  int cpt_pair, cpt_single;        // chunks per tile, with and without a partner group
+  int ch_h, ch_q, ch_i;            // chunks in a row of H, nh D and I columns
+  int nq, kq, no, ko, ng, kg, nd, kd;   // this block's units per projection, and tiles per unit
+  int ng_ring;                     // gate/up units that go through the ring (all, or all but the last: see fu_overlay_issue)
+  uint32_t ov_base, ov_bar;        // the overlay stage and its barrier; ov_base == 0: none
+  int per_layer, n_total;          // this block's tiles per layer and in the launch
+  int* issued;                     // [nst] tiles asked for so far, per stage (for the drain on an early exit)
+  const struct FuTileDesc* tiles;  // [min(per_layer, kFuMaxTiles)] this block's tiles of a layer, in shared memory
 };
 
-template <int MODE>
-__device__ __forceinline__ FuTask fu_task(const FusedArgs& a, const __nv_bfloat16* W, int N, int K, int n_units,
-                                          int base) {
-  constexpr bool PAIR = MODE != FU_ADD_RESID;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  FuTask t;
-  t.base = base;
-  const int per_block = (n_units - base) / (int)gridDim.x;
-  t.upc = per_block >= 4 ? 4 : per_block >= 2 ? 2 : 1;
-  t.kw = kFuWarps / t.upc;
-  const int j = warp / t.kw;
-  t.kpart = warp - j * t.kw;
-  t.u = base + j * (int)gridDim.x + (int)blockIdx.x;
-  const int n_chunks = (K + 31) / 32;
-  const int per = (n_chunks + t.kw - 1) / t.kw;
-  t.c_begin = t.kpart * per;
-  t.c_end = min(n_chunks, t.c_begin + per);
-  int row_a, row_b;
-  if (MODE == FU_QKV) {
-    const int per_head = a.D / 16;
-    const int head = t.u / per_head;
-    row_a = head * a.D + (t.u - head * per_head) * 8;
-    row_b = row_a + a.D / 2;
-  } else if (MODE == FU_SWIGLU) {
-    row_a = t.u * 8;
-    row_b = a.I + t.u * 8;
+__device__ __forceinline__ int fu_units_of_block(int n_units) {
+  return (int)blockIdx.x < n_units ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+}
+
+__device__ __forceinline__ FuRing fu_ring_setup(const FusedArgs& a, uint32_t base, uint32_t bars, int nst, int* issued,
+                                                uint32_t ov_base, uint32_t ov_bar) {
+  FuRing R;
+  R.issued = issued;
+  R.base = base;
+  R.bars = bars;
+  R.stage_bytes = a.stage_bytes;
+  R.nst = nst;
+  R.cpt_pair = a.stage_bytes / (2 * kFuChunkBytes);
+  R.cpt_single = a.stage_bytes / kFuChunkBytes;
+  R.ch_h = (a.H + 31) / 32;
+  R.ch_q = (a.nh * a.D + 31) / 32;
+  R.ch_i = (a.I + 31) / 32;
+  R.nq = fu_units_of_block((a.nh + 2 * a.nkv) * (a.D / 16));
+  R.no = fu_units_of_block((a.H + 7) / 8);
+  R.ng = fu_units_of_block((a.I + 7) / 8);
+  R.nd = R.no;
+  R.kq = (R.ch_h + R.cpt_pair - 1) / R.cpt_pair;
+  R.kg = R.kq;
+  R.ko = (R.ch_q + R.cpt_single - 1) / R.cpt_single;
+  R.kd = (R.ch_i + R.cpt_single - 1) / R.cpt_single;
+  const bool overlay = ov_base != 0 && R.kg == 1 && R.ng >= 1;
+  R.ov_base = overlay ? ov_base : 0;
+  R.ov_bar = ov_bar;
+  R.ng_ring = R.ng - (overlay ? 1 : 0);
+  R.per_layer = R.nq * R.kq + R.no * R.ko + R.ng_ring * R.kg + R.nd * R.kd;
+  R.n_total = R.per_layer * a.n_layers;
+  return R;
+}
+
+// Tile r of a layer, for this block: which matrix, where its chunks start (in chunks of the packed copy),
+// how many there are, and whether a partner group follows.
+struct FuTileDesc {
+  uint32_t chunk_a, chunk_b;       // first chunk of the group and of the partner group, counted from the matrix start
+  uint16_t nc;
+  uint8_t matrix;                  // 0 QKV, 1 output, 2 gate/up, 3 down
+  uint8_t pair;
+};
+constexpr int kFuMaxTiles = 64;    // table entries; a block with more tiles per layer works the rest out each time
+
+__device__ __forceinline__ FuTileDesc fu_tile_desc(const FusedArgs& a, const FuRing& R, int r) {
+  const int b = blockIdx.x, grid = gridDim.x;
+  FuTileDesc d;
+  if (r < R.nq * R.kq) {
+    const int j = r / R.kq, kp = r - j * R.kq, u = b + j * grid;
+    const int per_head = a.D / 16, head = u / per_head;
+    const int row_a = head * a.D + (u - head * per_head) * 8, c0 = kp * R.cpt_pair;
+    d.nc = (uint16_t)min(R.cpt_pair, R.ch_h - c0);
+    d.chunk_a = (uint32_t)(row_a >> 3) * R.ch_h + c0;
+    d.chunk_b = (uint32_t)((row_a + a.D / 2) >> 3) * R.ch_h + c0;
+    d.matrix = 0;
+    d.pair = 1;
+  } else if ((r -= R.nq * R.kq) < R.no * R.ko) {
+    const int j = r / R.ko, kp = r - j * R.ko, u = b + j * grid, c0 = kp * R.cpt_single;
+    d.nc = (uint16_t)min(R.cpt_single, R.ch_q - c0);
+    d.chunk_a = d.chunk_b = (uint32_t)u * R.ch_q + c0;
+    d.matrix = 1;
+    d.pair = 0;
+  } else if ((r -= R.no * R.ko) < R.ng_ring * R.kg) {
+    const int j = r / R.kg, kp = r - j * R.kg, u = b + j * grid, c0 = kp * R.cpt_pair;
+    d.nc = (uint16_t)min(R.cpt_pair, R.ch_h - c0);
+    d.chunk_a = (uint32_t)u * R.ch_h + c0;
+    d.chunk_b = (uint32_t)(a.I / 8 + u) * R.ch_h + c0;
+    d.matrix = 2;
+    d.pair = 1;
   } else {
-    row_a = row_b = t.u * 8;
+    r -= R.ng_ring * R.kg;
+    const int j = r / R.kd, kp = r - j * R.kd, u = b + j * grid, c0 = kp * R.cpt_single;
+    d.nc = (uint16_t)min(R.cpt_single, R.ch_i - c0);
+    d.chunk_a = d.chunk_b = (uint32_t)u * R.ch_i + c0;
+    d.matrix = 3;
+    d.pair = 0;
   }
-  t.ok_a = t.ok_b = t.u < n_units;
-  t.wa = fu_packed(W, t.ok_a ? row_a : 0, n_chunks, lane);
-  t.wb = fu_packed(W, t.ok_b ? row_b : 0, n_chunks, lane);
-  (void)PAIR;
-  (void)N;
-  return t;
+  return d;
 }
 
-// Slot s of a task: the two 16-byte loads that travel together. With partner rows they are the same K chunk of
-// both rows; without, two neighbouring chunks of the one row.
-template <int MODE>
-__device__ __forceinline__ void fu_slot_chunks(const FuTask& t, int s, int& ca, int& cb) {
-  if (MODE != FU_ADD_RESID) {
-    ca = cb = t.c_begin + s;
-  } else {
-    ca = t.c_begin + 2 * s;
-    cb = ca + 1;
+// Ask for tile i (one thread). The caller knows that the stage is free.
+__device__ __forceinline__ void fu_tile_issue(const FusedArgs& a, const FuRing& R, const FusedLayer* layers, int i) {
+  if (i >= R.n_total) return;
+  const int l = i / R.per_layer, r = i - l * R.per_layer;
+  const FuTileDesc d = r < kFuMaxTiles ? R.tiles[r] : fu_tile_desc(a, R, r);
+  const FusedLayer& L = layers[l];
+  const __nv_bfloat16* W = d.matrix == 0 ? L.w_qkv : d.matrix == 1 ? L.w_o : d.matrix == 2 ? L.w_gu : L.w_down;
+  const int s = i % R.nst;
+  R.issued[s] = i / R.nst + 1;
+  const uint32_t bar = R.bars + s * 8, dst = R.base + s * R.stage_bytes, bytes = (uint32_t)d.nc * kFuChunkBytes;
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(d.pair ? 2 * bytes : bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(W + (size_t)d.chunk_a * kFuChunkElems), "r"(bytes), "r"(bar) : "memory");
+  if (d.pair)
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst + bytes), "l"(W + (size_t)d.chunk_b * kFuChunkElems), "r"(bytes), "r"(bar) : "memory");
+}
+
+// The overlay stage. While a layer's attention, output projection and gate/up run, most of the staging area
+// (sized for the down projection's input) lies idle; one more stage is laid over its upper part, and the
+// block's LAST gate/up unit of each layer goes there instead of through the ring, asked for as soon as the
+// previous layer's down projection has read its input. A block whose gate/up units outnumber the ring's
+// stages would otherwise start its last unit only after the first one has freed a stage.
+__device__ __forceinline__ void fu_overlay_issue(const FusedArgs& a, const FuRing& R, const FusedLayer* layers, int l) {
+  if (!R.ov_base || l >= a.n_layers) return;
+  const int u = (int)blockIdx.x + (R.ng - 1) * (int)gridDim.x;
+  const __nv_bfloat16* W = layers[l].w_gu;
+  const uint32_t bytes = (uint32_t)R.ch_h * kFuChunkBytes;
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(R.ov_bar), "r"(2 * bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(R.ov_base), "l"(W + (size_t)u * R.ch_h * kFuChunkElems), "r"(bytes), "r"(R.ov_bar) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(R.ov_base + bytes), "l"(W + (size_t)(a.I / 8 + u) * R.ch_h * kFuChunkElems), "r"(bytes), "r"(R.ov_bar) : "memory");
+}
+
+// Wait until tile i has landed. When the wait runs out the error word is raised and the block goes on with
+// whatever the stage holds (every address it forms is in bounds whatever the data), so that no thread leaves
+// the common path and the synchronisations that follow still pair up; the next grid barrier ends the launch.
+__device__ __forceinline__ void fu_bar_wait(const FusedArgs& a, uint32_t bar, uint32_t parity, int* s_ok) {
+  for (uint32_t spins = 0; spins < kFuSpinLimit; ++spins) {
+    uint32_t done;
+    asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return;
+    if (spins > 256) {
+      if (*reinterpret_cast<volatile int*>(s_ok) == 0) return;       // already failed: do not wait again
+      __nanosleep(20);
+    }
   }
+  atomicCAS(a.error, 0, 1000);
+  *reinterpret_cast<volatile int*>(s_ok) = 0;
+}
+__device__ __forceinline__ void fu_tile_wait(const FusedArgs& a, const FuRing& R, int i, int* s_ok) {
+  fu_bar_wait(a, R.bars + (i % R.nst) * 8, (uint32_t)(i / R.nst) & 1u, s_ok);
 }
 
-template <int MODE>
-__device__ __forceinline__ void fu_slot_load(const FuTask& t, int K, int s, uint4& ra, uint4& rb) {
-  int ca, cb;
-  fu_slot_chunks<MODE>(t, s, ca, cb);
-  (void)K;
-  ra = (t.ok_a && ca < t.c_end) ? fu_ldg_stream(t.wa + (size_t)ca * kFuChunkElems) : make_uint4(0u, 0u, 0u, 0u);
-  rb = (t.ok_b && cb < t.c_end) ? fu_ldg_stream(t.wb + (size_t)cb * kFuChunkElems) : make_uint4(0u, 0u, 0u, 0u);
-}
+// ---- The projections ---------------------------------------------------------------------------------------
+enum : int { FU_QKV = 0, FU_ADD_RESID = 1 };
 
-// The first loads of a projection's first pass; call it between a barrier's arrival and its wait.
-template <int MODE>
-__device__ __forceinline__ void fu_project_preload(const FusedArgs& a, const __nv_bfloat16* W, int N, int K,
-                                                   int n_units, uint4 (&ra)[kFuSlots], uint4 (&rb)[kFuSlots]) {
-  const FuTask t = fu_task<MODE>(a, W, N, K, n_units, 0);
-#pragma unroll
-  for (int i = 0; i < kFuSlots; ++i) fu_slot_load<MODE>(t, K, i, ra[i], rb[i]);
-}
-
+// A projection whose units a block takes one at a time, all 8 warps on a tile, each with an eighth of the
+// tile's chunks; the partial sums meet in shared memory in warp order, so the result does not depend on
+// timing. FU_QKV: units of 8 rows and their 8 rotation partners; bias, rotation and the writes of q and of
+// the cache slots follow on the sums. FU_ADD_RESID: units of 8 rows; the sums are added into the residual
+// stream (each element has one owner, so the update is in place).
 // `stage_src`: null when the block's shared memory already holds the input (the norm wrote it), else the
-// [T, K] bfloat16 matrix other blocks wrote (rows beyond T stay as they are: they only feed accumulator rows
-// nobody reads). `preloaded`: ra / rb hold the first pass's first loads.
+// [T, K] bfloat16 matrix other blocks wrote, brought in row by row with bulk copies that complete on
+// `stage_bar` (phase parity `stage_parity`); rows beyond T stay as they are: they only feed accumulator rows
+// nobody reads.
 template <int MODE>
-__device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer& L, const __nv_bfloat16* W, int N,
-                                           int K, int n_units, const __nv_bfloat16* stage_src, unsigned char* xs,
-                                           int row_bytes, float* red, bool preloaded, uint4 (&ra)[kFuSlots],
-                                           uint4 (&rb)[kFuSlots]) {
-  constexpr bool PAIR = MODE != FU_ADD_RESID;
-  constexpr int U = kFuSlots;
+__device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer& L, const FuRing& R,
+                                           const FusedLayer* layers, int tile0, int n_mine, int kparts, int cpt,
+                                           int n_chunks, int N, int K, const __nv_bfloat16* stage_src,
+                                           uint32_t stage_bar, uint32_t stage_parity, unsigned char* xs,
+                                           int row_bytes, float* red, int* s_ok) {
+  constexpr bool PAIR = MODE == FU_QKV;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned char* xrow = xs + (lane >> 2) * row_bytes + (lane & 3) * 16;
-  // With at most 8 tokens only 8 rows are staged; the fragment rows 8..15 then read rows 0..7 again and
-  // feed accumulator rows nobody reads.
+  // With at most 8 tokens only 8 rows are staged; the fragment rows 8..15 then repeat rows 0..7 and feed
+  // accumulator rows nobody reads.
   const size_t hi_off = a.T > 8 ? (size_t)8 * row_bytes : 0;
-  for (int base = 0; base < n_units;) {
-    const FuTask t = fu_task<MODE>(a, W, N, K, n_units, base);
-    if (!(preloaded && base == 0)) {
-#pragma unroll
-      for (int i = 0; i < U; ++i) fu_slot_load<MODE>(t, K, i, ra[i], rb[i]);
-    }
-    if (stage_src && base == 0) {
-      // Warp w brings in the K range that is its own when 8 warps share a unit.
-      const int n_chunks = (K + 31) / 32;
-      const int per8 = (n_chunks + kFuWarps - 1) / kFuWarps;
-      const int c0 = warp * per8, c1 = min(n_chunks, c0 + per8);
-      const uint32_t sbase = smem_u32(xs);
-      const int pieces = max(0, c1 - c0) * 4;
-      for (int idx = lane; idx < a.T * pieces; idx += 32) {
-        const int r = idx / pieces, pc = idx - r * pieces;
-        const int k = c0 * 32 + pc * 8;
-        const bool ok = k < K;
-        cp_async16(sbase + r * row_bytes + k * 2, ok ? stage_src + (size_t)r * K + k : stage_src, ok);
-      }
-      cp_async_commit();
-    }
-    // The residual element this thread will add to, asked for before the products (one owner per element).
-    float resid_in = 0.f;
-    if (!PAIR && tid < t.upc * a.T * 8) {
-      const int j = tid / (a.T * 8), rem = tid - j * (a.T * 8);
-      const int n = (base + j * (int)gridDim.x + (int)blockIdx.x) * 8 + (rem & 7);
-      if (n < N) resid_in = __ldcg(a.resid + (size_t)(rem >> 3) * N + n);
-    }
-    float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
-    const int n_slots = PAIR ? t.c_end - t.c_begin : (t.c_end - t.c_begin + 1) / 2;
-    for (int s0 = 0; s0 < n_slots || s0 == 0; s0 += U) {
-      uint4 ca[U], cb[U];
-#pragma unroll
-      for (int i = 0; i < U; ++i) {
-        ca[i] = ra[i];
-        cb[i] = rb[i];
-      }
-      if (s0 + U < n_slots) {
-#pragma unroll
-        for (int i = 0; i < U; ++i) fu_slot_load<MODE>(t, K, s0 + U + i, ra[i], rb[i]);
-      }
-      if (stage_src && base == 0 && s0 == 0) {             // the staged input is needed only now
-        cp_async_wait<0>();
-        if (t.kw == kFuWarps) __syncwarp(); else __syncthreads();   // uniform over the block
-      }
-#pragma unroll
-      for (int i = 0; i < U; ++i) {
-        if (s0 + i < n_slots) {
-          int xa, xb;
-          fu_slot_chunks<MODE>(t, s0 + i, xa, xb);
-          const uint4 lo = *reinterpret_cast<const uint4*>(xrow + xa * 64);
-          const uint4 hi = *reinterpret_cast<const uint4*>(xrow + hi_off + xa * 64);
-          fu_mma(acc_a, lo.x, hi.x, lo.y, hi.y, ca[i].x, ca[i].y);
-          fu_mma(acc_a, lo.z, hi.z, lo.w, hi.w, ca[i].z, ca[i].w);
-          if (PAIR) {
-            fu_mma(acc_b, lo.x, hi.x, lo.y, hi.y, cb[i].x, cb[i].y);
-            fu_mma(acc_b, lo.z, hi.z, lo.w, hi.w, cb[i].z, cb[i].w);
-          } else if (xb < t.c_end) {                       // uniform over the warp
-            const uint4 lo2 = *reinterpret_cast<const uint4*>(xrow + xb * 64);
-            const uint4 hi2 = *reinterpret_cast<const uint4*>(xrow + hi_off + xb * 64);
-            fu_mma(acc_a, lo2.x, hi2.x, lo2.y, hi2.y, cb[i].x, cb[i].y);
-            fu_mma(acc_a, lo2.z, hi2.z, lo2.w, hi2.w, cb[i].z, cb[i].w);
-          }
+  for (int j = 0; j < n_mine; ++j) {
+    const int u = (int)blockIdx.x + j * (int)gridDim.x;
+    if (stage_src && j == 0) {
+      // One bulk copy per token row (warp 0 asks; everybody waits on the staging barrier below). The columns
+      // between K and the end of the last chunk are not part of the copy: they are zeroed by hand, since
+      // whatever they hold is multiplied (by the packed matrix's zero padding).
+      const int kpad = n_chunks * 32;
+      if (warp == 0) {
+        if (lane == 0) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier plain accesses to the rows come first
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(stage_bar), "r"(a.T * K * 2) : "memory");
         }
+        __syncwarp();
+        if (lane < a.T)
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(smem_u32(xs) + lane * row_bytes), "l"(stage_src + (size_t)lane * K), "r"(K * 2), "r"(stage_bar) : "memory");
       }
+      if (kpad != K) {
+        const int pieces = (kpad - K) / 8;
+        for (int idx = tid; idx < a.T * pieces; idx += kFuThreads) {
+          const int r = idx / pieces, pc = idx - r * pieces;
+          *reinterpret_cast<uint4*>(xs + (size_t)r * row_bytes + (size_t)(K + pc * 8) * 2) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncthreads();
+      }
+    }
+    // The residual element this thread will add to, asked for before the products.
+    float resid_in = 0.f;
+    if (!PAIR && tid < a.T * 8) {
+      const int n = u * 8 + (tid & 7);
+      if (n < N) resid_in = __ldcg(a.resid + (size_t)(tid >> 3) * N + n);
+    }
+    // Two accumulator sets per row group, for even and odd chunks: the tensor-core pipeline then has two
+    // independent chains to work on; they are added at the end.
+    float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc_a2[4] = {0.f, 0.f, 0.f, 0.f}, acc_b2[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int kp = 0; kp < kparts; ++kp) {
+      const int i = tile0 + j * kparts + kp;
+      fu_tile_wait(a, R, i, s_ok);
+      const int c0 = kp * cpt, nc = min(cpt, n_chunks - c0), per = (nc + kFuWarps - 1) / kFuWarps;
+      const int w0 = warp * per, w1 = min(nc, w0 + per);
+      if (stage_src && j == 0 && kp == 0) {                // the staged input is needed only now
+        fu_bar_wait(a, stage_bar, stage_parity, s_ok);
+      }
+      const uint32_t st = R.base + (i % R.nst) * R.stage_bytes + lane * 16;
+      auto chunk = [&](int c, float (&da)[4], float (&db)[4]) {
+        const uint4 wa = fu_lds128(st + c * kFuChunkBytes);
+        const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c0 + c) * 64);
+        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;   // uniform
+        fu_mma(da, lo.x, hi.x, lo.y, hi.y, wa.x, wa.y);
+        fu_mma(da, lo.z, hi.z, lo.w, hi.w, wa.z, wa.w);
+        if (PAIR) {
+          const uint4 wb = fu_lds128(st + (nc + c) * kFuChunkBytes);
+          fu_mma(db, lo.x, hi.x, lo.y, hi.y, wb.x, wb.y);
+          fu_mma(db, lo.z, hi.z, lo.w, hi.w, wb.z, wb.w);
+        }
+      };
+      int c = w0;
+#pragma unroll 2
+      for (; c + 1 < w1; c += 2) {
+        chunk(c, acc_a, acc_b);
+        chunk(c + 1, acc_a2, acc_b2);
+      }
+      if (c < w1) chunk(c, acc_a, acc_b);
+      if (kp + 1 < kparts) {                               // the stage is free once every warp is through
+        __syncthreads();
+        if (tid == 0) fu_tile_issue(a, R, layers, i + R.nst);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      acc_a[e] += acc_a2[e];
+      acc_b[e] += acc_b2[e];
     }
     // Partial sums: red[warp][row group][token][feature].
     {
@@ -421,117 +524,49 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
       }
     }
     __syncthreads();
-    const int kw = t.kw;
-    auto total = [&](int j, int grp, int tok, int f) -> float {
+    if (tid == 0) fu_tile_issue(a, R, layers, tile0 + j * kparts + kparts - 1 + R.nst);
+    auto total = [&](int grp, int tok, int f) -> float {
       float sum = 0.f;
-      for (int p = 0; p < kw; ++p) sum += red[(((size_t)(j * kw + p) * 2 + grp) * 16 + tok) * 8 + f];
+#pragma unroll
+      for (int w = 0; w < kFuWarps; ++w) sum += red[(((size_t)w * 2 + grp) * 16 + tok) * 8 + f];
       return sum;
     };
-    for (int idx = tid; idx < t.upc * a.T * 8; idx += kFuThreads) {
-      const int j = idx / (a.T * 8), rem = idx - j * (a.T * 8);
-      const int tok = rem >> 3, f = rem & 7;
-      const int u = base + j * (int)gridDim.x + (int)blockIdx.x;
-      if (u >= n_units) continue;
-      {
-        // residual + branch, in 32-bit; each element has one owner, so the update is in place
-        const int n = u * 8 + f;
-        if (n < N) a.resid[(size_t)tok * N + n] = (idx == tid ? resid_in : __ldcg(a.resid + (size_t)tok * N + n)) + total(j, 0, tok, f);
-      }
-    }
-    __syncthreads();   // `red` is reused by the next pass
-    base += t.upc * (int)gridDim.x;
-  }
-}
-
-// The QKV projection: a unit is 8 rows of one head and their 8 rotation partners (half a head further); a
-// block takes one unit at a time, 4 warps per row group cutting K between them; bias, rotation and the
-// writes of q and of the cache slots follow on the summed partials.
-__device__ __forceinline__ void fu_qkv_units(const FusedArgs& a, const FusedLayer& L, const __nv_bfloat16* W, int N,
-                                             int K, int n_units, const unsigned char* xs, int row_bytes, float* red) {
-  constexpr int ng = 2;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int kw = kFuWarps / ng;
-  const int g = warp / kw, kpart = warp - g * kw;
-  const int n_chunks = (K + 31) / 32;
-  const int per = (n_chunks + kw - 1) / kw;
-  const int c_begin = kpart * per, c_end = min(n_chunks, c_begin + per);
-  const unsigned char* xrow = xs + (lane >> 2) * row_bytes + (lane & 3) * 16;
-  // With at most 8 tokens only 8 rows are staged; the fragment rows 8..15 then read rows 0..7 again and
-  // feed accumulator rows nobody reads.
-  const size_t hi_off = a.T > 8 ? (size_t)8 * row_bytes : 0;
-  constexpr int U = 8;
-  for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
-    const int per_head = a.D / 16;
-    const int row0 = (u / per_head) * a.D + (u % per_head) * 8 + g * (a.D / 2);
-    const __nv_bfloat16* wp = fu_packed(W, row0, n_chunks, lane);
-    auto load_w = [&](int c) -> uint4 {
-      if (c < c_end) return fu_ldg_stream(wp + (size_t)c * kFuChunkElems);
-      return make_uint4(0u, 0u, 0u, 0u);
-    };
-    uint4 wreg[U];
-#pragma unroll
-    for (int i = 0; i < U; ++i) wreg[i] = load_w(c_begin + i);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = c_begin; c < c_end; c += U) {
-      uint4 cur[U];
-#pragma unroll
-      for (int i = 0; i < U; ++i) cur[i] = wreg[i];
-#pragma unroll
-      for (int i = 0; i < U; ++i) wreg[i] = load_w(c + U + i);
-#pragma unroll
-      for (int i = 0; i < U; ++i) {
-        if (c + i < c_end) {
-          const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c + i) * 64);
-          const uint4 hi = *reinterpret_cast<const uint4*>(xrow + hi_off + (c + i) * 64);
-          fu_mma(acc, lo.x, hi.x, lo.y, hi.y, cur[i].x, cur[i].y);
-          fu_mma(acc, lo.z, hi.z, lo.w, hi.w, cur[i].z, cur[i].w);
-        }
-      }
-    }
-    {
-      const int t0 = lane >> 2, f = (lane & 3) * 2;
-      *reinterpret_cast<float2*>(red + ((size_t)warp * 16 + t0) * 8 + f) = make_float2(acc[0], acc[1]);
-      *reinterpret_cast<float2*>(red + ((size_t)warp * 16 + t0 + 8) * 8 + f) = make_float2(acc[2], acc[3]);
-    }
-    __syncthreads();
-    auto total = [&](int t, int grp, int f) -> float {
-      float s = 0.f;
-      for (int p = 0; p < kw; ++p) s += red[((size_t)(grp * kw + p) * 16 + t) * 8 + f];
-      return s;
-    };
-    {
-      const int half = a.D / 2;
-      const int head = u / per_head, i0 = (u - head * per_head) * 8;
-      for (int idx = tid; idx < a.T * 8; idx += kFuThreads) {
-        const int t = idx >> 3, j = idx & 7, i = i0 + j;
+    for (int idx = tid; idx < a.T * 8; idx += kFuThreads) {
+      const int tok = idx >> 3, f = idx & 7;
+      if (MODE == FU_QKV) {
+        const int per_head = a.D / 16, half = a.D / 2;
+        const int head = u / per_head, i = (u - head * per_head) * 8 + f;
         const int c0 = head * a.D + i, c1 = c0 + half;
-        float x1 = total(t, 0, j), x2 = total(t, 1, j);
+        float x1 = total(0, tok, f), x2 = total(1, tok, f);
         if (L.b_qkv) {
           x1 += L.b_qkv[c0];
           x2 += L.b_qkv[c1];
         }
         float o1 = x1, o2 = x2;
         if (head < a.nh + a.nkv) {
-          int pos = a.positions[t];
+          int pos = a.positions[tok];
           pos = pos < 0 ? 0 : (pos >= a.n_pos ? a.n_pos - 1 : pos);
           const float cs = a.cos_t[(size_t)pos * half + i], sn = a.sin_t[(size_t)pos * half + i];
           o1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
           o2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
         }
+        __nv_bfloat16* dst = nullptr;
         if (head < a.nh) {
-          __nv_bfloat16* dst = a.q + ((size_t)t * a.nh + head) * a.D;
-          dst[i] = __float2bfloat16_rn(o1);
-          dst[i + half] = __float2bfloat16_rn(o2);
+          dst = a.q + ((size_t)tok * a.nh + head) * a.D;
         } else {
-          const int slot = a.slot_map[t];
+          const int slot = a.slot_map[tok];
           if (slot >= 0) {
             const bool is_k = head < a.nh + a.nkv;
-            const int kh = is_k ? head - a.nh : head - a.nh - a.nkv;
-            __nv_bfloat16* dst = (is_k ? L.kcache : L.vcache) + ((size_t)slot * a.nkv + kh) * a.D;
-            dst[i] = __float2bfloat16_rn(o1);
-            dst[i + half] = __float2bfloat16_rn(o2);
+            dst = (is_k ? L.kcache : L.vcache) + ((size_t)slot * a.nkv + (is_k ? head - a.nh : head - a.nh - a.nkv)) * a.D;
           }
         }
+        if (dst) {
+          dst[i] = __float2bfloat16_rn(o1);
+          dst[i + half] = __float2bfloat16_rn(o2);
+        }
+      } else {
+        const int n = u * 8 + f;
+        if (n < N) a.resid[(size_t)tok * N + n] = (idx == tid ? resid_in : __ldcg(a.resid + (size_t)tok * N + n)) + total(0, tok, f);
       }
     }
     __syncthreads();   // `red` is reused by the next unit
@@ -540,74 +575,62 @@ __device__ __forceinline__ void fu_qkv_units(const FusedArgs& a, const FusedLaye
 
 // The gate/up projection with SwiGLU: one WARP owns a unit of 8 gate rows and their 8 up rows over the whole K
 // range, so there is no partial sum to meet in shared memory and no block-wide synchronisation; the
-// activation is computed on the accumulator registers. (Streaming is bound by the loads a block keeps in
-// flight; cutting K across warps to use the idle ones was tried and lost more to the extra pass and its
-// synchronisation than it gained.)
-__device__ __forceinline__ void fu_gate_up_units(const FusedArgs& a, const __nv_bfloat16* W, int N, int K, int n_units,
-                                                 const unsigned char* xs, int row_bytes) {
+// activation is computed on the accumulator registers, and the warp itself asks for the tile that follows
+// into the stage it has used up.
+__device__ __forceinline__ void fu_gate_up(const FusedArgs& a, const FuRing& R, const FusedLayer* layers, int tile0,
+                                           int layer, const unsigned char* xs, int row_bytes, int* s_ok) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t2 = (lane & 3) * 2;
-  const int n_chunks = (K + 31) / 32;
   const unsigned char* xrow = xs + g * row_bytes + (lane & 3) * 16;
-  // With at most 8 tokens only 8 rows are staged; the fragment rows 8..15 then read rows 0..7 again and
-  // feed accumulator rows nobody reads.
   const size_t hi_off = a.T > 8 ? (size_t)8 * row_bytes : 0;
-  constexpr int U = 6;
-  // Unit u goes to warp (u / grid) of block (u % grid): consecutive units land on different SMs.
-  for (int u = warp * gridDim.x + blockIdx.x; u < n_units; u += kFuWarps * gridDim.x) {
-    const int row_a = u * 8, row_b = a.I + u * 8;
-    const bool ok_a = true, ok_b = true;
-    const __nv_bfloat16* wa = fu_packed(W, row_a, n_chunks, lane);
-    const __nv_bfloat16* wb = fu_packed(W, row_b, n_chunks, lane);
-    auto load = [&](const __nv_bfloat16* p, bool ok, int c) -> uint4 {
-      if (ok && c < n_chunks) return fu_ldg_stream(p + (size_t)c * kFuChunkElems);
-      return make_uint4(0u, 0u, 0u, 0u);
-    };
-    uint4 ra[U], rb[U];
-#pragma unroll
-    for (int i = 0; i < U; ++i) {
-      ra[i] = load(wa, ok_a, i);
-      rb[i] = load(wb, ok_b, i);
+  for (int j = warp; j < R.ng; j += kFuWarps) {
+    const int u = (int)blockIdx.x + j * (int)gridDim.x;
+    float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};       // even chunks
+    float acc_a2[4] = {0.f, 0.f, 0.f, 0.f}, acc_b2[4] = {0.f, 0.f, 0.f, 0.f};     // odd chunks
+    const bool overlay = R.ov_base != 0 && j == R.ng - 1;    // (then R.kg == 1)
+    for (int kp = 0; kp < R.kg; ++kp) {
+      const int i = tile0 + j * R.kg + kp;
+      if (overlay) fu_bar_wait(a, R.ov_bar, (uint32_t)layer & 1u, s_ok);
+      else fu_tile_wait(a, R, i, s_ok);
+      const int c0 = kp * R.cpt_pair, nc = min(R.cpt_pair, R.ch_h - c0);
+      const uint32_t st = (overlay ? R.ov_base : R.base + (i % R.nst) * R.stage_bytes) + lane * 16;
+      auto chunk = [&](int c, float (&da)[4], float (&db)[4]) {
+        const uint4 wa = fu_lds128(st + c * kFuChunkBytes);
+        const uint4 wb = fu_lds128(st + (nc + c) * kFuChunkBytes);
+        const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c0 + c) * 64);
+        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;   // uniform
+        fu_mma(da, lo.x, hi.x, lo.y, hi.y, wa.x, wa.y);
+        fu_mma(da, lo.z, hi.z, lo.w, hi.w, wa.z, wa.w);
+        fu_mma(db, lo.x, hi.x, lo.y, hi.y, wb.x, wb.y);
+        fu_mma(db, lo.z, hi.z, lo.w, hi.w, wb.z, wb.w);
+      };
+      int c = 0;
+#pragma unroll 2
+      for (; c + 1 < nc; c += 2) {
+        chunk(c, acc_a, acc_b);
+        chunk(c + 1, acc_a2, acc_b2);
+      }
+      if (c < nc) chunk(c, acc_a, acc_b);
+      __syncwarp();                                        // every lane has its fragments: the stage is free
+      if (lane == 0 && !overlay) fu_tile_issue(a, R, layers, i + R.nst);
     }
-    float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = 0; c < n_chunks; c += U) {
-      uint4 ca[U], cb[U];
 #pragma unroll
-      for (int i = 0; i < U; ++i) {
-        ca[i] = ra[i];
-        cb[i] = rb[i];
-      }
-#pragma unroll
-      for (int i = 0; i < U; ++i) {
-        ra[i] = load(wa, ok_a, c + U + i);
-        rb[i] = load(wb, ok_b, c + U + i);
-      }
-#pragma unroll
-      for (int i = 0; i < U; ++i) {
-        if (c + i < n_chunks) {
-          const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c + i) * 64);
-          const uint4 hi = *reinterpret_cast<const uint4*>(xrow + hi_off + (c + i) * 64);
-          fu_mma(acc_a, lo.x, hi.x, lo.y, hi.y, ca[i].x, ca[i].y);
-          fu_mma(acc_a, lo.z, hi.z, lo.w, hi.w, ca[i].z, ca[i].w);
-          fu_mma(acc_b, lo.x, hi.x, lo.y, hi.y, cb[i].x, cb[i].y);
-          fu_mma(acc_b, lo.z, hi.z, lo.w, hi.w, cb[i].z, cb[i].w);
-        }
-      }
+    for (int e = 0; e < 4; ++e) {
+      acc_a[e] += acc_a2[e];
+      acc_b[e] += acc_b2[e];
     }
     // Accumulator layout: [0], [1] = token g, features t2, t2 + 1; [2], [3] = token g + 8, same features.
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int t = g + hh * 8;
       if (t >= a.T) continue;
-      float v1[2] = {acc_a[2 * hh], acc_a[2 * hh + 1]}, v2[2] = {acc_b[2 * hh], acc_b[2 * hh + 1]};
-      {
-        const int n = u * 8 + t2;
-        if (n + 1 < a.I) {
-          *reinterpret_cast<uint32_t*>(a.act + (size_t)t * a.I + n) =
-              pack_bf16(v1[0] / (1.0f + expf(-v1[0])) * v2[0], v1[1] / (1.0f + expf(-v1[1])) * v2[1]);
-        } else if (n < a.I) {
-          a.act[(size_t)t * a.I + n] = __float2bfloat16_rn(v1[0] / (1.0f + expf(-v1[0])) * v2[0]);
-        }
+      const float g0 = acc_a[2 * hh], g1 = acc_a[2 * hh + 1], u0 = acc_b[2 * hh], u1 = acc_b[2 * hh + 1];
+      const int n = u * 8 + t2;
+      if (n + 1 < a.I) {
+        *reinterpret_cast<uint32_t*>(a.act + (size_t)t * a.I + n) =
+            pack_bf16(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+      } else if (n < a.I) {
+        a.act[(size_t)t * a.I + n] = __float2bfloat16_rn(g0 / (1.0f + expf(-g0)) * u0);
       }
     }
   }
@@ -622,6 +645,12 @@ __device__ __forceinline__ void fu_gate_up_units(const FusedArgs& a, const __nv_
 // the host splits only long contexts) the block writes the head outputs itself; with more, it writes a
 // partial and the block that finishes a (request, kv head) last merges the partials in split order.
 constexpr int kFuKeyCap = 96;      // keys per warp whose cache slots are looked up once per launch
+
+// Attention's working memory (the staging area of the projections): at least 16 keys per warp in flight, and
+// room for the 8 warps' states.
+template <int D> constexpr int fu_attn_min_bytes() {
+  return kFuWarps * 16 * (D + 2) * 4 > kFuWarps * 16 * 4 * D ? kFuWarps * 16 * (D + 2) * 4 : kFuWarps * 16 * 4 * D;
+}
 
 struct FuAttnUnit {
   int s, kvh, z, q_start, q_len, before, n_rows;
@@ -893,31 +922,58 @@ template <int D>
 __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  const int kmax = max(a.H, max(a.nh * a.D, a.I));
-  const int xs_bytes = (a.T > 8 ? 16 : 8) * fu_row_bytes(kmax);
-  unsigned char* xs = smem;
-  float* red = reinterpret_cast<float*>(smem + xs_bytes);            // [8 warps][2 row groups][16][8]
-  const int rb_h = fu_row_bytes(a.H), rb_q = fu_row_bytes(a.nh * a.D), rb_i = fu_row_bytes(a.I);
-  unsigned k = 0;
-  bool ok = true;
-  const int qkv_rows = (a.nh + 2 * a.nkv) * a.D;
-  __syncthreads();
-
-  auto packed_bytes = [](int n, int kk) { return (size_t)((n + 7) / 8 * 8) * ((kk + 31) / 32 * 32) * 2; };
-  const size_t qkv_bytes = packed_bytes(qkv_rows, a.H), o_bytes = packed_bytes(a.H, a.nh * a.D);
-  const size_t gu_bytes = packed_bytes(2 * a.I, a.H), down_bytes = packed_bytes(a.H, a.I);
-  uint4 ra[kFuSlots], rb[kFuSlots];          // the projections' weight loads in flight
-  __shared__ FusedLayer s_layer[2];          // this layer's pointers and the next one's, fetched a phase early
-  if (threadIdx.x == 0 && a.n_layers > 0) s_layer[0] = a.layers[0];
+  __shared__ __align__(8) unsigned long long s_full[kFuMaxStages + 2];   // the stages' barriers, the staging barrier, the overlay's
+  __shared__ int s_issued[kFuMaxStages];
+  __shared__ FuTileDesc s_tiles[kFuMaxTiles];
+  __shared__ FusedLayer s_layers[kFuMaxLayers];
   // The requests' lengths, and the cache slots of this block's first attention unit, are the same in every
   // layer: look them up once, so that each layer can ask for its keys and values a phase before it reads
   // them and starts its copies without a table lookup.
   __shared__ int s_cu_q[17], s_before[16];
   __shared__ int s_slot[kFuWarps][kFuKeyCap];
+  const int kmax = max(a.H, max(a.nh * a.D, a.I));
+  const int xs_bytes = (a.T > 8 ? 16 : 8) * fu_row_bytes(kmax);
+  const int red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
+  unsigned char* xs = smem;                                          // staged inputs; attention's working memory
+  float* red = reinterpret_cast<float*>(smem + xs_bytes);            // [8 warps][2 row groups][16][8]
+  const int work_bytes = max(xs_bytes + red_bytes, fu_attn_min_bytes<D>());
+  const int ring_off = (work_bytes + 127) / 128 * 128;
+  const int nst = min(kFuMaxStages, (a.smem_bytes - ring_off) / a.stage_bytes);
+  // The overlay stage lies in the staging area, above what attention and the narrower projections use of it.
+  const int rows = a.T > 8 ? 16 : 8;
+  const int ov_off = (max(fu_attn_min_bytes<D>(), rows * max(fu_row_bytes(a.H), fu_row_bytes(a.nh * a.D))) + 127) / 128 * 128;
+  const bool ov_fits = ov_off + a.stage_bytes <= xs_bytes;
+  FuRing R = fu_ring_setup(a, smem_u32(smem + ring_off), smem_u32(s_full), nst, s_issued,
+                           ov_fits ? smem_u32(smem + ov_off) : 0u, smem_u32(&s_full[kFuMaxStages + 1]));
+  R.tiles = s_tiles;
+  const int attn_bytes = R.ov_base ? ov_off : work_bytes;   // attention's working memory ends where the overlay begins
+  const int rb_h = fu_row_bytes(a.H), rb_q = fu_row_bytes(a.nh * a.D), rb_i = fu_row_bytes(a.I);
+  unsigned k = 0;
+  bool ok = true;
+  const uint32_t stage_bar = smem_u32(&s_full[kFuMaxStages]);
+  uint32_t n_staged = 0;                      // uses of the staging barrier so far (its phase parity)
+  int ov_issued = 0;                          // tiles asked for into the overlay stage so far
+
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    for (int s = 0; s < kFuMaxStages; ++s) s_issued[s] = 0;
+    for (int s = 0; s < nst; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(R.bars + s * 8));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_full[kFuMaxStages])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_full[kFuMaxStages + 1])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < a.n_layers * (int)(sizeof(FusedLayer) / sizeof(void*)); i += kFuThreads)
+    reinterpret_cast<const void**>(s_layers)[i] = reinterpret_cast<const void* const*>(a.layers)[i];
+  if ((int)threadIdx.x < min(R.per_layer, kFuMaxTiles)) s_tiles[threadIdx.x] = fu_tile_desc(a, R, threadIdx.x);
   if (threadIdx.x <= a.S) s_cu_q[threadIdx.x] = a.cu_q[threadIdx.x];
   if (threadIdx.x < a.S) s_before[threadIdx.x] = a.kv_before[threadIdx.x];
   __syncthreads();
+  if (threadIdx.x == 0)
+  {
+    for (int i = 0; i < nst; ++i) fu_tile_issue(a, R, s_layers, i);
+    fu_overlay_issue(a, R, s_layers, 0);
+  }
+  if (R.ov_base && a.n_layers > 0) ov_issued = 1;
   int first_kvh = 0;
   {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -931,11 +987,11 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   }
   __syncthreads();
 
+  auto packed_bytes = [](int n, int kk) { return (size_t)((n + 7) / 8 * 8) * ((kk + 31) / 32 * 32) * 2; };
   for (int l = 0; l < a.n_layers && ok; ++l) {
-    const FusedLayer& L = s_layer[l & 1];
+    const FusedLayer& L = s_layers[l];
+    const int t_qkv = l * R.per_layer, t_o = t_qkv + R.nq * R.kq, t_gu = t_o + R.no * R.ko, t_down = t_gu + R.ng_ring * R.kg;
     fu_stamp(a, l * 16 + 0);
-    fu_prefetch_l2(L.w_o, o_bytes);
-    fu_prefetch_l2(L.w_gu, gu_bytes);
     for (int i = threadIdx.x & 31; i < kFuKeyCap; i += 32) {
       const int slot = s_slot[threadIdx.x >> 5][i];
       if (slot >= 0) {
@@ -952,37 +1008,43 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
     fu_norm_rows(a.T, a.H, l == 0 ? a.embedding : nullptr, a.token_ids, a.resid, L.ln1_w, a.eps1, xs, rb_h);
     __syncthreads();
     fu_stamp(a, l * 16 + 1);
-    fu_qkv_units(a, L, L.w_qkv, qkv_rows, a.H, (a.nh + 2 * a.nkv) * (a.D / 16), xs, rb_h, red);
+    fu_project<FU_QKV>(a, L, R, s_layers, t_qkv, R.nq, R.kq, R.cpt_pair, R.ch_h, (a.nh + 2 * a.nkv) * a.D, a.H, nullptr,
+                       0, 0, xs, rb_h, red, &s_ok);
     fu_stamp(a, l * 16 + 2);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     fu_stamp(a, l * 16 + 3);
-    // B: attention
-    fu_attention<D>(a, L, smem, a.smem_bytes, s_cu_q, s_before, s_slot, l);
-    fu_stamp(a, l * 16 + 4);
-    // C: output projection; its first weights are asked for while the barrier fills up
-    fu_grid_arrive(a);
-    fu_project_preload<FU_ADD_RESID>(a, L.w_o, a.H, a.nh * a.D, (a.H + 7) / 8, ra, rb);
-    fu_prefetch_l2(L.w_down, down_bytes);
-    if (l + 1 < a.n_layers) {
-      if (threadIdx.x == 0) s_layer[(l + 1) & 1] = a.layers[l + 1];
-      fu_prefetch_l2(a.layers[l + 1].w_qkv, qkv_bytes);
+    // B: attention (its working memory is the staging area; the ring's stages stay untouched). The memory
+    // system has little to do meanwhile: the next layer's weights are asked into L2 now.
+    if (a.l2_prefetch && l + 1 < a.n_layers) {
+      const FusedLayer& Ln = s_layers[l + 1];
+      fu_prefetch_l2(Ln.w_qkv, packed_bytes((a.nh + 2 * a.nkv) * a.D, a.H));
+      fu_prefetch_l2(Ln.w_o, packed_bytes(a.H, a.nh * a.D));
+      fu_prefetch_l2(Ln.w_gu, packed_bytes(2 * a.I, a.H));
+      fu_prefetch_l2(Ln.w_down, packed_bytes(a.H, a.I));
     }
-    if (!(ok = fu_grid_wait(a, k, &s_ok))) break;
+    fu_attention<D>(a, L, xs, attn_bytes, s_cu_q, s_before, s_slot, l);
+    fu_stamp(a, l * 16 + 4);
+    if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     fu_stamp(a, l * 16 + 5);
-    fu_project<FU_ADD_RESID>(a, L, L.w_o, a.H, a.nh * a.D, (a.H + 7) / 8, a.attn, xs, rb_q, red, true, ra, rb);
+    // C: output projection
+    fu_project<FU_ADD_RESID>(a, L, R, s_layers, t_o, R.no, R.ko, R.cpt_single, R.ch_q, a.H, a.nh * a.D, a.attn, stage_bar,
+                             n_staged & 1u, xs, rb_q, red, &s_ok);
+    if (R.no > 0) ++n_staged;
     fu_stamp(a, l * 16 + 6);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     // D: norm + gate/up + SwiGLU
     fu_norm_rows(a.T, a.H, nullptr, a.token_ids, a.resid, L.ln2_w, a.eps2, xs, rb_h);
     __syncthreads();
     fu_stamp(a, l * 16 + 7);
-    fu_gate_up_units(a, L.w_gu, 2 * a.I, a.H, (a.I + 7) / 8, xs, rb_h);
+    fu_gate_up(a, R, s_layers, t_gu, l, xs, rb_h, &s_ok);
     fu_stamp(a, l * 16 + 8);
-    // E: down projection, begun the same way
-    fu_grid_arrive(a);
-    fu_project_preload<FU_ADD_RESID>(a, L.w_down, a.H, a.I, (a.H + 7) / 8, ra, rb);
-    if (!(ok = fu_grid_wait(a, k, &s_ok))) break;
-    fu_project<FU_ADD_RESID>(a, L, L.w_down, a.H, a.I, (a.H + 7) / 8, a.act, xs, rb_i, red, true, ra, rb);
+    if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
+    // E: down projection
+    fu_project<FU_ADD_RESID>(a, L, R, s_layers, t_down, R.nd, R.kd, R.cpt_single, R.ch_i, a.H, a.I, a.act, stage_bar,
+                             n_staged & 1u, xs, rb_i, red, &s_ok);
+    if (R.nd > 0) ++n_staged;
+    if (threadIdx.x == 0) fu_overlay_issue(a, R, s_layers, l + 1);   // the staging area has been read: it is free again
+    if (R.ov_base && l + 1 < a.n_layers) ov_issued = l + 2;
     fu_stamp(a, l * 16 + 9);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
   }
@@ -1007,6 +1069,25 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
         a.hidden_out[(size_t)w * a.H + i] = __float2bfloat16_rn(a.final_ln_w[i] * __bfloat162float(normed));
       }
     }
+  } else {
+    // Leaving early: copies may still be on their way into this block's shared memory. Give each stage's
+    // barrier a bounded chance to complete its current phase (either parity counts) before the block ends.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int s = 0; s <= nst + 1; ++s) {                 // the stages, the staging barrier, the overlay's
+        const int issued = s < nst ? s_issued[s] : s == nst ? (int)n_staged : ov_issued;
+        if (!issued) continue;
+        const uint32_t bar = s < nst ? R.bars + s * 8 : s == nst ? stage_bar : R.ov_bar;
+        const uint32_t parity = (uint32_t)(issued - 1) & 1u;
+        for (uint32_t spins = 0; spins < (1u << 20); ++spins) {
+          uint32_t done;
+          asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+          if (done) break;
+          __nanosleep(100);
+        }
+      }
+    }
   }
   // Leave: the last block to get here puts the arrival counter back to zero (nobody waits on it any more).
   __syncthreads();
@@ -1023,13 +1104,14 @@ int launch_decode_fused(const FusedArgs& a, cudaStream_t stream) {
   const int kmax = a.H > a.I ? (a.H > a.nh * a.D ? a.H : a.nh * a.D) : (a.I > a.nh * a.D ? a.I : a.nh * a.D);
   const int kpad = (kmax + 31) / 32 * 32;
   const int row_bytes = kpad * 2 + ((64 - (kpad * 2) % 128) + 128) % 128;
-  // Less shared memory leaves more L1, and with it more loads in flight: steps of at most 8 tokens stage 8 rows.
-  const int need = (a.T > 8 ? 16 : 8) * row_bytes + kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
-  // The attention warps use the same memory for keys in flight (at least 16 keys per warp) and then for
-  // the 8 warps' states.
-  constexpr int kAttnMin = kFuWarps * 16 * (D + 2) * 4 > kFuWarps * 16 * 4 * D ? kFuWarps * 16 * (D + 2) * 4 : kFuWarps * 16 * 4 * D;
-  const int smem = need > kAttnMin ? need : kAttnMin;
-  if (smem > 216 * 1024) return TM_ERR_UNSUPPORTED_SHAPE;
+  const int xs_bytes = (a.T > 8 ? 16 : 8) * row_bytes, red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
+  const int work_bytes = xs_bytes + red_bytes > fu_attn_min_bytes<D>() ? xs_bytes + red_bytes : fu_attn_min_bytes<D>();
+  // A stage holds a row group and its partner over all of H when that fits 32 KB, else 32 KB worth of chunks.
+  const int ch_h = (a.H + 31) / 32;
+  const int stage_bytes = 2 * ch_h * 512 <= 32768 ? 2 * ch_h * 512 : 32768;
+  const int smem = 212 * 1024;
+  const int ring_off = (work_bytes + 127) / 128 * 128;
+  if (ring_off + stage_bytes > smem || a.n_layers > kFuMaxLayers) return TM_ERR_UNSUPPORTED_SHAPE;
   static int n_sm = 0, per_sm = 0, smem_set = 0;
   if (smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1047,6 +1129,7 @@ int launch_decode_fused(const FusedArgs& a, cudaStream_t stream) {
   }
   FusedArgs args = a;
   args.smem_bytes = smem;
+  args.stage_bytes = stage_bytes;
   void* params[] = {&args};
   return (int)cudaLaunchCooperativeKernel((void*)kern, dim3(n_sm), dim3(kFuThreads), params, (size_t)smem, stream);
 }

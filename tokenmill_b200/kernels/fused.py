@@ -19,6 +19,7 @@ import torch
 from . import lib
 
 MAX_TOKENS = 16
+MAX_LAYERS = 96          # entries of the kernel's layer table in shared memory
 SPLIT_KEYS = 64          # granularity of the key split of attention (a block attends a multiple of this)
 _ENABLED = os.environ.get("TOKENMILL_FUSED_DECODE", "1") != "0"
 
@@ -41,7 +42,7 @@ class _Args(ctypes.Structure):
         + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
         + [(n, c_void_p) for n in ("resid", "q", "part_acc", "part_ml", "attn", "act", "attn_count", "bar",
                                    "error", "hidden_out")]
-        + [("smem_bytes", c_int), ("timing", c_void_p)]
+        + [("smem_bytes", c_int), ("stage_bytes", c_int), ("l2_prefetch", c_int), ("timing", c_void_p)]
     )
 
 
@@ -54,7 +55,8 @@ def eligible(model) -> bool:
 
     if not _ENABLED or model.dtype != torch.bfloat16 or model.device.type != "cuda":
         return False
-    if not model.spec.run_order or any(e.cache_of is not None for e in model.spec.run_order):
+    if not model.spec.run_order or len(model.spec.run_order) > MAX_LAYERS or \
+            any(e.cache_of is not None for e in model.spec.run_order):
         return False
     first = model.blocks[model.spec.run_order[0].layer].mixer
     if not isinstance(first, GroupedQueryAttention):
@@ -145,6 +147,7 @@ class FusedDecoder:
         a.act = self.act.data_ptr()
         a.attn_count, a.bar, a.error = self.attn_count.data_ptr(), self.bar.data_ptr(), self.error.data_ptr()
         a.hidden_out = self.hidden.data_ptr()
+        a.l2_prefetch = int(os.environ.get("TOKENMILL_FUSED_L2_PREFETCH", "0") != "0")   # measured: not worth it
         self._args = a
         self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
         self.launches = 0
