@@ -179,8 +179,7 @@ def decode_end_to_end(engine, batch: int, steps: int, warmup: int) -> dict:
         n += sum(len(o.new_token_ids) for o in engine.step())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    g = engine.runner._graphs.get(batch)
-    h2d = g.lay.total * 4 if g is not None else 0
+    h2d = engine.runner.stats["h2d_bytes"]          # bytes of the last step's (one) host-to-device copy
     for s in seqs:
         engine.abort_request(s.id)
     return {"tok_s": n / dt, "ms_per_step": 1e3 * dt / steps, "h2d": h2d, "d2h": batch * 4, "tokens": n}

@@ -62,6 +62,8 @@ def tiles_for(q_lens: np.ndarray, group_size: int) -> tuple[np.ndarray, np.ndarr
     return tile_seq.astype(np.int32), tile_row0.astype(np.int32)
 
 
+last_h2d_bytes = 0    # bytes of the most recent step's host-to-device copy (read by the runner's statistics)
+
 PACKED_TILE = 64     # rows of the tensor-core prompt attention's work unit; its tile list has key -G
 
 
@@ -137,6 +139,8 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
         buf[lay.tile_row0[g]] = tile_row0
 
     dev = host.to(device, non_blocking=True)
+    global last_h2d_bytes
+    last_h2d_bytes = lay.total * 4
     max_q = int(q_lens.max())
     use_split = split_keys
     return StepInputs(

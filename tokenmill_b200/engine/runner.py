@@ -26,6 +26,7 @@ from ..kernels import fused, lib, ops
 from ..parts.attention import SPLIT_KEYS, AttentionScratch
 from ..parts.base import StepInputs
 from ..parts.model import DecoderModel
+from . import batch as batch_mod
 from .batch import Layout, StepEntry, build_step_inputs, tiles_for
 
 GRAPH_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64, 128, 256]
@@ -48,7 +49,7 @@ class ModelRunner:
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
         self.kernels_per_graph: dict[int, int] = {}
-        self.stats = {"steps": 0, "graph_steps": 0, "fused_steps": 0, "tokens": 0}
+        self.stats = {"steps": 0, "graph_steps": 0, "fused_steps": 0, "tokens": 0, "h2d_bytes": 0}   # h2d: last step
         # One kernel per decode step when the model is the arrangement that kernel implements.
         self.fused = None
         if fused.eligible(model) and len(self.layout.groups) == 1:
@@ -74,9 +75,15 @@ class ModelRunner:
         self.stats["tokens"] += sum(len(e.tokens) for e in entries)
         if self.fused is not None:
             self.fused.check()
+            if len(entries) <= fused.MAX_TOKENS and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+                self.stats["fused_steps"] += 1
+                hidden = self.fused.run_decode(entries, self.cache.page_size)
+                self.stats["h2d_bytes"] = self.fused.h2d_bytes
+                return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
             if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
                 step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                          split_keys=SPLIT_KEYS)
+                self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
                     hidden = self.fused.run(step, self.cache.page_size)
@@ -87,6 +94,7 @@ class ModelRunner:
             return self._graph_step(entries)
         step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                  split_keys=SPLIT_KEYS)
+        self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
         logits = self.model.forward(step, self.layer_caches)
         if self.model.dtype == torch.bfloat16 and step.n_tokens >= ops.TC_MIN_TOKENS:
             ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
@@ -110,6 +118,7 @@ class ModelRunner:
             g = _DecodeGraph(self, bucket)
             self._graphs[bucket] = g
         self.stats["graph_steps"] += 1
+        self.stats["h2d_bytes"] = g.lay.total * 4
         return g.run(entries)
 
 

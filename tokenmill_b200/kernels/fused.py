@@ -150,6 +150,9 @@ class FusedDecoder:
         a.l2_prefetch = int(os.environ.get("TOKENMILL_FUSED_L2_PREFETCH", "0") != "0")   # measured: not worth it
         self._args = a
         self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.max_model_len = max_model_len
+        self._arange = __import__("numpy").arange(MAX_TOKENS + 1, dtype="int32")
+        self.h2d_bytes = 0
         self.launches = 0
         self.timing: torch.Tensor | None = None
 
@@ -177,6 +180,70 @@ class FusedDecoder:
         G = self.nh // self.nkv
         return (step.n_tokens <= MAX_TOKENS and step.max_q_len * G <= 16 and step.n_want > 0
                 and step.n_want <= MAX_TOKENS and len(step.block_tables) == 1)
+
+    # --- plain decode steps: metadata written straight into a pinned ring, no intermediate objects --------
+
+    _RING = 4
+
+    def _decode_ring(self, page_size: int):
+        if getattr(self, "_ring", None) is None:
+            width = -(-self.max_model_len // page_size)
+            n = 6 * 16 + 4 + MAX_TOKENS * width          # six sections of 16 (cu_q: 20) and the block table
+            self._ring = [(torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                           torch.zeros(n, dtype=torch.int32, device=self.device), torch.cuda.Event())
+                          for _ in range(self._RING)]
+            self._ring_np = [h.numpy() for h, _, _ in self._ring]
+            self._ring_at = 0
+        return self._ring
+
+    def run_decode(self, entries, page_size: int) -> torch.Tensor:
+        """One new token for each of at most 16 requests, logits wanted for every one of them. The step's
+        integers (token, position, cache slot, request offsets, block table) go into one of a few pinned
+        buffers and from there to the device in one copy; ``h2d_bytes`` says how many."""
+        ring = self._decode_ring(page_size)
+        k = self._ring_at
+        self._ring_at = (k + 1) % self._RING
+        host, dev, copied = ring[k]
+        copied.synchronize()                              # the copy that last read this pinned buffer is done
+        buf = self._ring_np[k]
+        S = len(entries)
+        max_kv = max(e.start for e in entries) + 1
+        width = -(-max_kv // page_size)
+        o_tok, o_pos, o_slot, o_cu, o_before, o_want, o_tab = 0, 16, 32, 48, 68, 84, 100
+        tab = buf[o_tab:o_tab + S * width].reshape(S, width)
+        for i, e in enumerate(entries):
+            pos = e.start
+            pages = e.handle.tables[0]
+            need = pos // page_size + 1
+            if len(pages) < need:
+                raise RuntimeError(f"entry {i} holds {len(pages)} pages, its {pos + 1} tokens need {need}")
+            page = pages[pos // page_size]
+            if page < 0:
+                raise RuntimeError(f"entry {i} writes into a page it has already given back")
+            buf[o_tok + i] = e.tokens[0]
+            buf[o_pos + i] = pos
+            buf[o_slot + i] = page * page_size + pos % page_size
+            buf[o_before + i] = pos
+            row = pages[:width]
+            tab[i, :len(row)] = row
+            tab[i, len(row):] = 0
+        buf[o_cu:o_cu + S + 1] = self._arange[:S + 1]
+        buf[o_want:o_want + S] = self._arange[:S]
+        used = o_tab + S * width
+        dev[:used].copy_(host[:used], non_blocking=True)
+        copied.record()
+        self.h2d_bytes = used * 4
+        a, base = self._args, dev.data_ptr()
+        a.token_ids, a.positions, a.slot_map = base + 4 * o_tok, base + 4 * o_pos, base + 4 * o_slot
+        a.cu_q, a.kv_before, a.want_rows = base + 4 * o_cu, base + 4 * o_before, base + 4 * o_want
+        a.block_table, a.bt_stride = base + 4 * o_tab, width
+        a.T, a.S, a.n_want, a.page_size = S, S, S, page_size
+        a.split_keys = self.split_for(S, max_kv)
+        a.max_splits = -(-max_kv // a.split_keys)
+        lib.call("tm_decode_fused", ctypes.addressof(a), torch.cuda.current_stream().cuda_stream)
+        self._err_host.copy_(self.error, non_blocking=True)
+        self.launches += 1
+        return self.hidden[:S]
 
     def run(self, step, page_size: int) -> torch.Tensor:
         """Normed hidden rows [n_want, H] (bfloat16) of the step's wanted places."""
