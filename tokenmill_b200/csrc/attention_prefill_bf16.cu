@@ -1,16 +1,21 @@
 // Causal attention of prompt portions over the paged cache on tensor cores (bfloat16 in, float32
-// softmax and accumulate), one pass, no partial results.
+// softmax and accumulate).
 //
 // Semantics as attention_paged.cu (src/infer/model/layers.py:72-107, src/infer/kv/context.py:63-76):
 // the step's keys and values already sit in the cache; the query at absolute position p of a request
 // reads that request's keys j <= p (and j > p - window if a window is set); query head h reads kv
 // head h / G. Any mix of requests works (a decoded token is a portion of one).
 //
-// Work unit: 64 consecutive (token, head-in-group) rows of one request and one kv head, so the G query
-// heads that share a kv head also share every key/value tile that is staged. Units are listed
-// heaviest first by the host and handed out through an atomic ticket, so blocks that finish a short
-// unit fetch the next one (a causal prompt's last tile has 2T/64 times the work of its first). The
-// ticket and a done-counter live in a two-int scratch; the last block to finish puts both back to 0.
+// Work unit: 64 consecutive (token, head-in-group) rows of one request and one kv head (so the G query
+// heads that share a kv head also share every key/value tile that is staged), times one CHUNK of keys cut
+// at absolute multiples of `chunk_keys`. A causal prompt's last row tile sees 2T/64 times the keys of its
+// first; without the cut the longest tile alone sets the kernel's duration while most SMs idle. Units are
+// listed heaviest first by the host and handed out through an atomic ticket, so blocks that finish a short
+// unit fetch the next one. A row tile with a single chunk writes its output itself; the others write
+// unnormalised sums with their running maximum and denominator into per-(tile, chunk) slots, and the block
+// that finishes a (tile, kv head) last merges them in chunk order. Chunks are anchored at absolute positions, so a row's
+// sums run in the same order however the prompt was cut into portions. The ticket and a done-counter live
+// in a two-int scratch; the last block to finish puts both back to 0.
 //
 // Per unit, keys stream through shared memory in blocks of 64 anchored at absolute positions 0, 64,
 // 128, ... (cp.async ring; one page lookup per key row); each warp multiplies its rows with the whole
@@ -32,8 +37,10 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
-    const int* __restrict__ tile_row0, int n_tiles, int* __restrict__ counters, __nv_bfloat16* __restrict__ out,
-    int nh, int nkv, int page_size, float scale_log2, int window) {
+    const int* __restrict__ tile_row0, const int* __restrict__ tile_slot0, const int* __restrict__ tile_nchunks,
+    const int* __restrict__ unit_tile, const int* __restrict__ unit_chunk, int n_units, int chunk_keys,
+    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ tile_done, int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int nh, int nkv,
+    int page_size, float scale_log2, int window) {
   static_assert(MT * WARPS * 16 == kPfBM, "a unit is 64 rows");
   constexpr int THREADS = WARPS * 32;
   constexpr int CH = D / 8;                    // 16-byte chunks per row
@@ -48,7 +55,7 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = nh / nkv;
   const int cpair = (lane & 3) * 2;
-  const int total_units = n_tiles * nkv;
+  const int total_units = n_units * nkv;
 
   for (;;) {
     __syncthreads();                           // the previous unit is done with shared memory and s_ticket
@@ -56,7 +63,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
     __syncthreads();
     const int unit = s_ticket;
     if (unit >= total_units) break;
-    const int tile = unit / nkv, kvh = unit - tile * nkv;
+    const int ui = unit / nkv, kvh = unit - ui * nkv;
+    const int tile = unit_tile[ui], chunk = unit_chunk[ui], slot0 = tile_slot0[tile];
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
     const int q_start = cu_q[s];
@@ -65,9 +73,10 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
     const int n_rows = min(kPfBM, q_len * G - row0);
     if (n_rows <= 0) continue;
     const int p_min = before + row0 / G, p_max = before + (row0 + n_rows - 1) / G;
-    const int j_lo = window > 0 ? max(0, p_min - window + 1) : 0;
-    const int j_hi = p_max;
+    const int j_lo = max(window > 0 ? max(0, p_min - window + 1) : 0, chunk * chunk_keys);
+    const int j_hi = min(p_max, (chunk + 1) * chunk_keys - 1);
     const int* table = block_table + (size_t)s * bt_stride;
+    const bool empty = j_lo > j_hi;              // (a window that has passed the whole chunk) uniform over the block
 
     // Rows of this thread: tile mt, rows rr and rr + 8.
     uint32_t qa[MT][KS][4];
@@ -111,7 +120,7 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
     }
 
     const int kb_first = (j_lo / kPfBN) * kPfBN;
-    const int n_blocks = (j_hi - kb_first) / kPfBN + 1;
+    const int n_blocks = empty ? 0 : (j_hi - kb_first) / kPfBN + 1;
 
     auto load_block = [&](int stage, int kb) {
       const uint32_t k_dst = smem_base + stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
@@ -263,13 +272,62 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
       for (int hh = 0; hh < 2; ++hh) {
         if (p_row[mt][hh] < 0) continue;
         const float l = l_run[mt][hh];
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        __nv_bfloat16* dst = out + o_off[mt][hh];
+        if (slot0 < 0) {                         // the tile's only chunk: normalise and write the output
+          const float inv = l > 0.f ? 1.0f / l : 0.f;
+          __nv_bfloat16* dst = out + o_off[mt][hh];
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
-          *reinterpret_cast<uint32_t*>(dst + t * 8 + cpair) =
-              pack_bf16(o[mt][t][2 * hh] * inv, o[mt][t][2 * hh + 1] * inv);
+          for (int t = 0; t < NT; ++t)
+            *reinterpret_cast<uint32_t*>(dst + t * 8 + cpair) =
+                pack_bf16(o[mt][t][2 * hh] * inv, o[mt][t][2 * hh + 1] * inv);
+        } else {                                 // one of several: sums, maximum (log2 units) and denominator
+          const int r = (warp * MT + mt) * 16 + (lane >> 2) + hh * 8;
+          const size_t prow = ((size_t)(slot0 + chunk) * nkv + kvh) * kPfBM + r;
+          float* dst = part_acc + prow * D;
+#pragma unroll
+          for (int t = 0; t < NT; ++t)
+            *reinterpret_cast<float2*>(dst + t * 8 + cpair) = make_float2(o[mt][t][2 * hh], o[mt][t][2 * hh + 1]);
+          if ((lane & 3) == 0) *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run[mt][hh], l);
+        }
       }
+    if (slot0 >= 0) {
+      // The block that finishes a (row tile, kv head) last merges its chunks, in chunk order, each weighted by
+      // 2^(its maximum - the maximum so far); rows a chunk had no key for carry a maximum of -inf and a zero
+      // denominator and drop out. The arrival counter is left at zero for the next launch.
+      const int n_chunks = tile_nchunks[tile];
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) s_ticket = atomicAdd(&tile_done[tile * nkv + kvh], 1);
+      __syncthreads();
+      if (s_ticket == n_chunks - 1) {
+        __threadfence();
+        for (int idx = tid; idx < n_rows * (D / 4); idx += THREADS) {
+          const int r = idx / (D / 4), d = (idx - r * (D / 4)) * 4;
+          float mx = -INFINITY, lsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+          for (int c = 0; c < n_chunks; ++c) {
+            const size_t prow = ((size_t)(slot0 + c) * nkv + kvh) * kPfBM + r;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + prow * 2));
+            const float4 pa = __ldcg(reinterpret_cast<const float4*>(part_acc + prow * D + d));
+            const float m_new = fmaxf(mx, ml.x);
+            const float keep = mx == -INFINITY ? 0.f : exp2f(mx - m_new);
+            const float w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_new);
+            lsum = lsum * keep + ml.y * w;
+            acc[0] = acc[0] * keep + pa.x * w;
+            acc[1] = acc[1] * keep + pa.y * w;
+            acc[2] = acc[2] * keep + pa.z * w;
+            acc[3] = acc[3] * keep + pa.w * w;
+            mx = m_new;
+          }
+          const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+          const int row = row0 + r, tok = row / G, g = row - tok * G;
+          uint2 ov;
+          ov.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+          ov.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+          *reinterpret_cast<uint2*>(out + ((size_t)(q_start + tok) * nh + kvh * G + g) * D + d) = ov;
+        }
+        if (tid == 0) tile_done[tile * nkv + kvh] = 0;
+      }
+    }
   }
 
   // The last block to leave puts the ticket and the done-counter back to zero for the next launch.
@@ -287,8 +345,12 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
 template <int D, int MT, int WARPS, int STAGES>
 int launch_prefill_attention(const void* q, const void* kcache, const void* vcache, const int* block_table,
                              int bt_stride, const int* cu_q, const int* kv_before, const int* tile_seq,
-                             const int* tile_row0, int n_tiles, int* counters, void* out, int nh, int nkv,
-                             int page_size, float scale, int window, cudaStream_t stream) {
+                             const int* tile_row0, const int* tile_slot0, const int* tile_nchunks, int n_tiles,
+                             const int* unit_tile, const int* unit_chunk, int n_units, int chunk_keys, int n_slots,
+                             float* part_acc, float* part_ml, int* tile_done, int* counters, void* out, int nh,
+                             int nkv, int page_size, float scale, int window, cudaStream_t stream) {
+  (void)n_tiles;
+  (void)n_slots;
   const int smem = STAGES * 2 * kPfBN * D * 2;
   auto kern = prefill_attention_bf16_kernel<D, MT, WARPS, STAGES>;
   static int blocks_per_sm = 0, n_sm = 0;
@@ -303,35 +365,49 @@ int launch_prefill_attention(const void* q, const void* kcache, const void* vcac
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kern, WARPS * 32, smem);
     if (e != cudaSuccess || blocks_per_sm < 1) blocks_per_sm = 1;
   }
-  const long long units = (long long)n_tiles * nkv;
+  const long long units = (long long)n_units * nkv;
   long long grid = (long long)n_sm * blocks_per_sm;
   if (grid > units) grid = units;
   kern<<<(int)grid, WARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, bt_stride,
-      cu_q, kv_before, tile_seq, tile_row0, n_tiles, counters, (__nv_bfloat16*)out, nh, nkv, page_size,
-      scale * 1.4426950408889634f, window);
+      cu_q, kv_before, tile_seq, tile_row0, tile_slot0, tile_nchunks, unit_tile, unit_chunk, n_units, chunk_keys,
+      part_acc, part_ml, tile_done, counters, (__nv_bfloat16*)out, nh, nkv, page_size, scale * 1.4426950408889634f,
+      window);
   return launch_status();
 }
 
 }  // namespace tmk
 
-// q, out [T, nh, D] bfloat16; caches [pages, page_size, nkv, D] bfloat16; tile_seq / tile_row0 [n_tiles]:
-// request and first (token, head-in-group) row of each 64-row tile, heaviest tiles first; counters: two
-// ints that are zero before the first launch (the kernel leaves them zero). Head sizes 64 and 128.
+// q, out [T, nh, D] bfloat16; caches [pages, page_size, nkv, D] bfloat16. Per row tile of 64 (token,
+// head-in-group) rows [n_tiles]: request, first row, first partial slot (-1: single chunk), number of chunks;
+// per unit [n_units], heaviest first: its tile and its key chunk (keys chunk * chunk_keys ...; chunk_keys a
+// multiple of 64). part_acc [n_slots * nkv, 64, D] and part_ml [n_slots * nkv, 64, 2] float32, tile_done
+// [n_tiles * nkv] ints that are zero before the first launch and left zero (all three may be null when n_slots
+// is 0). counters: two ints that are zero before the first launch (the kernel leaves them zero).
+// Head sizes 64 and 128.
 extern "C" int tm_prefill_attention_bf16(const void* q, const void* kcache, const void* vcache,
                                          const int* block_table, int bt_stride, const int* cu_q,
                                          const int* kv_before, const int* tile_seq, const int* tile_row0,
-                                         int n_tiles, int* counters, void* out, int nh, int nkv, int D,
-                                         int page_size, float scale, int window, cudaStream_t stream) {
-  if (n_tiles <= 0) return 0;
-  if (nkv <= 0 || nh % nkv || page_size <= 0 || !counters) return TM_ERR_UNSUPPORTED_SHAPE;
+                                         const int* tile_slot0, const int* tile_nchunks, int n_tiles,
+                                         const int* unit_tile, const int* unit_chunk, int n_units, int chunk_keys,
+                                         int n_slots, float* part_acc, float* part_ml, int* tile_done, int* counters,
+                                         void* out, int nh, int nkv, int D, int page_size, float scale, int window,
+                                         cudaStream_t stream) {
+  if (n_units <= 0 || n_tiles <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || page_size <= 0 || !counters || chunk_keys <= 0 || chunk_keys % tmk::kPfBN ||
+      (n_slots > 0 && (!part_acc || !part_ml || !tile_done)))
+    return TM_ERR_UNSUPPORTED_SHAPE;
   if (D == 64)
     return tmk::launch_prefill_attention<64, 1, 4, 3>(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before,
-                                                      tile_seq, tile_row0, n_tiles, counters, out, nh, nkv,
-                                                      page_size, scale, window, stream);
+                                                      tile_seq, tile_row0, tile_slot0, tile_nchunks, n_tiles,
+                                                      unit_tile, unit_chunk, n_units, chunk_keys, n_slots, part_acc,
+                                                      part_ml, tile_done, counters, out, nh, nkv, page_size, scale, window,
+                                                      stream);
   if (D == 128)
     return tmk::launch_prefill_attention<128, 1, 4, 2>(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before,
-                                                       tile_seq, tile_row0, n_tiles, counters, out, nh, nkv,
-                                                       page_size, scale, window, stream);
+                                                       tile_seq, tile_row0, tile_slot0, tile_nchunks, n_tiles,
+                                                       unit_tile, unit_chunk, n_units, chunk_keys, n_slots, part_acc,
+                                                       part_ml, tile_done, counters, out, nh, nkv, page_size, scale, window,
+                                                       stream);
   return TM_ERR_UNSUPPORTED_SHAPE;
 }

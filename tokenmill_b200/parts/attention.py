@@ -33,6 +33,9 @@ class AttentionScratch:
         self.part_ml: torch.Tensor | None = None
         self.frozen = False      # set once a graph has captured the pointers
         self._counters: torch.Tensor | None = None
+        self._pf_acc: torch.Tensor | None = None
+        self._pf_ml: torch.Tensor | None = None
+        self._pf_done: torch.Tensor | None = None
 
     def counters(self) -> torch.Tensor:
         """Two zeroed ints the prompt-attention kernel uses as work ticket and done-counter (it leaves
@@ -52,6 +55,21 @@ class AttentionScratch:
     def get(self, rows: int, max_splits: int, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
         self.reserve(rows, max_splits, head_dim)
         return self.part_acc, self.part_ml
+
+    def get_prefill(self, slots: int, head_dim: int, tiles: int):
+        """Scratch for the prompt kernel's per-(row tile, key chunk) partial results: ``slots`` slots of 64
+        rows, and one arrival counter (zero between launches) for each of ``tiles`` (row tile, kv head)
+        pairs. Prompt steps are never captured in a graph, so these may grow at any time."""
+        if slots <= 0:
+            return None, None, None
+        need = slots * 64
+        if self._pf_acc is None or self._pf_acc.numel() < need * head_dim:
+            self._pf_acc = torch.empty(need * head_dim, dtype=torch.float32, device=self.device)
+        if self._pf_ml is None or self._pf_ml.numel() < need * 2:
+            self._pf_ml = torch.empty(need * 2, dtype=torch.float32, device=self.device)
+        if self._pf_done is None or self._pf_done.numel() < tiles:
+            self._pf_done = torch.zeros(max(tiles, 1024), dtype=torch.int32, device=self.device)
+        return self._pf_acc, self._pf_ml, self._pf_done
 
 
 class GroupedQueryAttention:
@@ -144,11 +162,14 @@ class GroupedQueryAttention:
                                       window=self.window, split_keys=step.split_keys, max_splits=step.max_splits,
                                       part_acc=part_acc, part_ml=part_ml)
             return
-        if self.dtype == torch.bfloat16 and self.D in (64, 128) and -G in step.tiles:
-            tile_seq, tile_row0, n_tiles = step.attention_tiles(-G)       # 64-row tiles, heaviest first
+        if self.dtype == torch.bfloat16 and self.D in (64, 128) and G in step.prefill:
+            units = step.prefill[G]                # 64-row tiles cut into key chunks, heaviest first
+            part_acc, part_ml, tile_done = step.scratch.get_prefill(units.n_slots * self.nkv, self.D,
+                                                                    units.n_tiles * self.nkv)
             ops.prefill_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
-                                       step.kv_before, tile_seq, tile_row0, n_tiles, step.scratch.counters(), out,
-                                       scale=self.scale, window=self.window)
+                                       step.kv_before, units, step.scratch.counters(), out,
+                                       scale=self.scale, window=self.window, part_acc=part_acc, part_ml=part_ml,
+                                       tile_done=tile_done)
             return
         tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
         kw = {}

@@ -10,7 +10,7 @@ part knows which model it is in, or which layer.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Protocol
+from typing import Any, NamedTuple, Protocol
 
 import torch
 
@@ -30,6 +30,23 @@ class LayerCache:
     group: int = 0
     writes: bool = True
     state: torch.Tensor | None = None
+
+
+class PrefillUnits(NamedTuple):
+    """Work units of the tensor-core prompt attention for one group size (engine/batch.py packed_units):
+    per 64-row tile its request, first row, first partial slot (-1: writes its output itself) and number
+    of key chunks; per unit its tile and key chunk (of chunk_keys keys), heaviest first."""
+
+    tile_seq: torch.Tensor
+    tile_row0: torch.Tensor
+    tile_slot0: torch.Tensor
+    tile_nchunks: torch.Tensor
+    unit_tile: torch.Tensor
+    unit_chunk: torch.Tensor
+    n_tiles: int
+    n_units: int
+    n_slots: int
+    chunk_keys: int
 
 
 @dataclass
@@ -58,6 +75,7 @@ class StepInputs:
     q_lens: list[int] | None = None
     kv_befores: list[int] | None = None
     tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
+    prefill: dict[int, PrefillUnits] = field(default_factory=dict)     # by group size
     scratch: Any = None                # engine-owned scratch provider (attention partials)
     split_keys: int = 0                # > 0: short-query attention cuts keys at multiples of this
     max_splits: int = 0                # number of such cuts the step may need
