@@ -216,7 +216,7 @@ def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
 def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
     """The bfloat16 prompt kernel: whole prompts, later portions that start off a tile or page edge, short
     portions and single tokens in the same launch; tiles that end inside a key block; windows."""
-    from tokenmill_b200.engine.batch import PREFILL_SECTIONS, packed_units
+    from tokenmill_b200.engine.batch import packed_units
     from tokenmill_b200.parts.base import PrefillUnits
     import numpy as np
     ops = _ops()
@@ -226,19 +226,18 @@ def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
     G = nh // nkv
     counters = torch.zeros(2, dtype=torch.int32, device=DEV)
     for chunk in (512, 64, 128):       # the engine's chunk; then chunks so short that most tiles have several
-        u = packed_units(np.array(q_lens, dtype=np.int32), np.array(befores, dtype=np.int32), G, chunk=chunk)
-        assert len(u["tile_seq"]) == sum(-(-n * G // 64) for n in q_lens)
-        assert len(u["unit_tile"]) == int(u["tile_nchunks"].sum()) and u["n_slots"] == int(u["tile_nchunks"][u["tile_slot0"] >= 0].sum())
-        units = PrefillUnits(*(torch.from_numpy(u[name]).to(DEV) for name in PREFILL_SECTIONS), len(u["tile_seq"]),
-                             len(u["unit_tile"]), u["n_slots"], chunk)
-        part_acc = torch.full((max(1, u["n_slots"]) * nkv * 64 * D,), float("nan"), dtype=torch.float32, device=DEV)
-        part_ml = torch.full((max(1, u["n_slots"]) * nkv * 64 * 2,), float("nan"), dtype=torch.float32, device=DEV)
-        tile_done = torch.zeros(len(u["tile_seq"]) * nkv, dtype=torch.int32, device=DEV)
+        rec, n_tiles, n_slots = packed_units(np.array(q_lens, dtype=np.int32), np.array(befores, dtype=np.int32), G,
+                                             chunk=chunk)
+        assert n_tiles == sum(-(-n * G // 64) for n in q_lens)
+        assert len({(r[4], r[2] & 0xffff) for r in rec.tolist()}) == len(rec)          # every (tile, chunk) once
+        units = PrefillUnits(torch.from_numpy(rec).to(DEV), len(rec), n_tiles, n_slots, chunk)
+        part_acc = torch.full((max(1, n_slots) * nkv * 64 * D,), float("nan"), dtype=torch.float32, device=DEV)
+        part_ml = torch.full((max(1, n_slots) * nkv * 64 * 2,), float("nan"), dtype=torch.float32, device=DEV)
+        tile_done = torch.zeros(n_tiles * nkv, dtype=torch.int32, device=DEV)
         for _ in range(2):                                          # the second launch finds the counters at zero
             out = torch.full_like(c["q"], float("nan"))
-            ops.prefill_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], units, counters, out,
-                                       scale=D ** -0.5, window=window, part_acc=part_acc, part_ml=part_ml,
-                                       tile_done=tile_done)
+            ops.prefill_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], units, counters, out, scale=D ** -0.5,
+                                       window=window, part_acc=part_acc, part_ml=part_ml, tile_done=tile_done)
             diff = (out.float().cpu() - c["ref"]).abs().max()
             assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), (chunk, diff)
             assert counters.tolist() == [0, 0] and int(tile_done.abs().sum()) == 0

@@ -36,11 +36,9 @@ template <int D, int MT, int WARPS, int STAGES>   // MT 16-row tiles per warp; M
 __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int bt_stride,
-    const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int* __restrict__ tile_seq,
-    const int* __restrict__ tile_row0, const int* __restrict__ tile_slot0, const int* __restrict__ tile_nchunks,
-    const int* __restrict__ unit_tile, const int* __restrict__ unit_chunk, int n_units, int chunk_keys,
-    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ tile_done, int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int nh, int nkv,
-    int page_size, float scale_log2, int window) {
+    const int4* __restrict__ unit_rec, int n_units, int chunk_keys, float* __restrict__ part_acc,
+    float* __restrict__ part_ml, int* __restrict__ tile_done, int* __restrict__ counters,
+    __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, float scale_log2, int window) {
   static_assert(MT * WARPS * 16 == kPfBM, "a unit is 64 rows");
   constexpr int THREADS = WARPS * 32;
   constexpr int CH = D / 8;                    // 16-byte chunks per row
@@ -59,17 +57,18 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
 
   for (;;) {
     __syncthreads();                           // the previous unit is done with shared memory and s_ticket
+    // (Asking for the next ticket a unit early would hide its round trip, but a block would then sit on a unit
+    // while others have run out of work; measured slower.)
     if (tid == 0) s_ticket = atomicAdd(&counters[0], 1);
     __syncthreads();
     const int unit = s_ticket;
     if (unit >= total_units) break;
     const int ui = unit / nkv, kvh = unit - ui * nkv;
-    const int tile = unit_tile[ui], chunk = unit_chunk[ui], slot0 = tile_slot0[tile];
-    const int s = tile_seq[tile];
-    const int row0 = tile_row0[tile];
-    const int q_start = cu_q[s];
-    const int q_len = cu_q[s + 1] - q_start;
-    const int before = kv_before[s];
+    // The unit's record: request, first row, chunk | chunks << 16, first slot; tile, first flat row of the
+    // request, its tokens in this step, its tokens already in the cache.
+    const int4 ra = __ldg(unit_rec + 2 * ui), rb = __ldg(unit_rec + 2 * ui + 1);
+    const int s = ra.x, row0 = ra.y, chunk = ra.z & 0xffff, n_chunks = ra.z >> 16, slot0 = ra.w;
+    const int tile = rb.x, q_start = rb.y, q_len = rb.z, before = rb.w;
     const int n_rows = min(kPfBM, q_len * G - row0);
     if (n_rows <= 0) continue;
     const int p_min = before + row0 / G, p_max = before + (row0 + n_rows - 1) / G;
@@ -198,8 +197,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
               ok0 = j <= p_row[mt][0] && j >= lo_row[mt][0];
               ok1 = j <= p_row[mt][1] && j >= lo_row[mt][1];
             }
-            sc[mt][t][e] = ok0 ? sc[mt][t][e] * scale_log2 : -INFINITY;
-            sc[mt][t][2 + e] = ok1 ? sc[mt][t][2 + e] * scale_log2 : -INFINITY;
+            if (!ok0) sc[mt][t][e] = -INFINITY;
+            if (!ok1) sc[mt][t][2 + e] = -INFINITY;
             tmax0 = fmaxf(tmax0, sc[mt][t][e]);
             tmax1 = fmaxf(tmax1, sc[mt][t][2 + e]);
           }
@@ -207,7 +206,9 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
-        const float mn0 = fmaxf(m_run[mt][0], tmax0), mn1 = fmaxf(m_run[mt][1], tmax1);
+        // The maximum is taken over the raw scores and scaled once (the scale is positive); the exponent's
+        // argument is then one fused multiply-add per score.
+        const float mn0 = fmaxf(m_run[mt][0], tmax0 * scale_log2), mn1 = fmaxf(m_run[mt][1], tmax1 * scale_log2);
         const float corr0 = mn0 == -INFINITY ? 1.f : exp2f(m_run[mt][0] - mn0);
         const float corr1 = mn1 == -INFINITY ? 1.f : exp2f(m_run[mt][1] - mn1);
         const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
@@ -219,8 +220,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              p[h][e] = exp2f(sc[mt][2 * kk + h][e] - base0);          // masked entries are -inf: 0
-              p[h][2 + e] = exp2f(sc[mt][2 * kk + h][2 + e] - base1);
+              p[h][e] = exp2f(fmaf(sc[mt][2 * kk + h][e], scale_log2, -base0));          // masked entries are -inf: 0
+              p[h][2 + e] = exp2f(fmaf(sc[mt][2 * kk + h][2 + e], scale_log2, -base1));
               ps0 += p[h][e];
               ps1 += p[h][2 + e];
             }
@@ -293,7 +294,6 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
       // The block that finishes a (row tile, kv head) last merges its chunks, in chunk order, each weighted by
       // 2^(its maximum - the maximum so far); rows a chunk had no key for carry a maximum of -inf and a zero
       // denominator and drop out. The arrival counter is left at zero for the next launch.
-      const int n_chunks = tile_nchunks[tile];
       __threadfence();
       __syncthreads();
       if (tid == 0) s_ticket = atomicAdd(&tile_done[tile * nkv + kvh], 1);
@@ -344,13 +344,9 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
 
 template <int D, int MT, int WARPS, int STAGES>
 int launch_prefill_attention(const void* q, const void* kcache, const void* vcache, const int* block_table,
-                             int bt_stride, const int* cu_q, const int* kv_before, const int* tile_seq,
-                             const int* tile_row0, const int* tile_slot0, const int* tile_nchunks, int n_tiles,
-                             const int* unit_tile, const int* unit_chunk, int n_units, int chunk_keys, int n_slots,
-                             float* part_acc, float* part_ml, int* tile_done, int* counters, void* out, int nh,
-                             int nkv, int page_size, float scale, int window, cudaStream_t stream) {
-  (void)n_tiles;
-  (void)n_slots;
+                             int bt_stride, const int* unit_rec, int n_units, int chunk_keys, float* part_acc,
+                             float* part_ml, int* tile_done, int* counters, void* out, int nh, int nkv,
+                             int page_size, float scale, int window, cudaStream_t stream) {
   const int smem = STAGES * 2 * kPfBN * D * 2;
   auto kern = prefill_attention_bf16_kernel<D, MT, WARPS, STAGES>;
   static int blocks_per_sm = 0, n_sm = 0;
@@ -370,44 +366,37 @@ int launch_prefill_attention(const void* q, const void* kcache, const void* vcac
   if (grid > units) grid = units;
   kern<<<(int)grid, WARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, bt_stride,
-      cu_q, kv_before, tile_seq, tile_row0, tile_slot0, tile_nchunks, unit_tile, unit_chunk, n_units, chunk_keys,
-      part_acc, part_ml, tile_done, counters, (__nv_bfloat16*)out, nh, nkv, page_size, scale * 1.4426950408889634f,
-      window);
+      reinterpret_cast<const int4*>(unit_rec), n_units, chunk_keys, part_acc, part_ml, tile_done, counters,
+      (__nv_bfloat16*)out, nh, nkv, page_size, scale * 1.4426950408889634f, window);
   return launch_status();
 }
 
 }  // namespace tmk
 
-// q, out [T, nh, D] bfloat16; caches [pages, page_size, nkv, D] bfloat16. Per row tile of 64 (token,
-// head-in-group) rows [n_tiles]: request, first row, first partial slot (-1: single chunk), number of chunks;
-// per unit [n_units], heaviest first: its tile and its key chunk (keys chunk * chunk_keys ...; chunk_keys a
-// multiple of 64). part_acc [n_slots * nkv, 64, D] and part_ml [n_slots * nkv, 64, 2] float32, tile_done
-// [n_tiles * nkv] ints that are zero before the first launch and left zero (all three may be null when n_slots
-// is 0). counters: two ints that are zero before the first launch (the kernel leaves them zero).
-// Head sizes 64 and 128.
+// q, out [T, nh, D] bfloat16; caches [pages, page_size, nkv, D] bfloat16. unit_rec [n_units, 8] ints, 16-byte
+// aligned, heaviest first: request, first (token, head-in-group) row of the 64-row tile, key chunk | chunks of
+// the tile << 16 (keys chunk * chunk_keys ...; chunk_keys a multiple of 64), first partial slot of the tile
+// (-1: single chunk), tile index, first flat row of the request, its tokens in this step, its tokens already in
+// the cache. part_acc [slots * nkv, 64, D] and part_ml [slots * nkv, 64, 2] float32, tile_done [tiles * nkv]
+// ints that are zero before the first launch and left zero (all three may be null when no tile has several
+// chunks). counters: two ints that are zero before the first launch (the kernel leaves them zero). The scale
+// must be positive. Head sizes 64 and 128.
 extern "C" int tm_prefill_attention_bf16(const void* q, const void* kcache, const void* vcache,
-                                         const int* block_table, int bt_stride, const int* cu_q,
-                                         const int* kv_before, const int* tile_seq, const int* tile_row0,
-                                         const int* tile_slot0, const int* tile_nchunks, int n_tiles,
-                                         const int* unit_tile, const int* unit_chunk, int n_units, int chunk_keys,
-                                         int n_slots, float* part_acc, float* part_ml, int* tile_done, int* counters,
-                                         void* out, int nh, int nkv, int D, int page_size, float scale, int window,
-                                         cudaStream_t stream) {
-  if (n_units <= 0 || n_tiles <= 0) return 0;
+                                         const int* block_table, int bt_stride, const int* unit_rec, int n_units,
+                                         int chunk_keys, float* part_acc, float* part_ml, int* tile_done,
+                                         int* counters, void* out, int nh, int nkv, int D, int page_size,
+                                         float scale, int window, cudaStream_t stream) {
+  if (n_units <= 0) return 0;
   if (nkv <= 0 || nh % nkv || page_size <= 0 || !counters || chunk_keys <= 0 || chunk_keys % tmk::kPfBN ||
-      (n_slots > 0 && (!part_acc || !part_ml || !tile_done)))
+      !(scale > 0.f) || (reinterpret_cast<uintptr_t>(unit_rec) & 15))
     return TM_ERR_UNSUPPORTED_SHAPE;
   if (D == 64)
-    return tmk::launch_prefill_attention<64, 1, 4, 3>(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before,
-                                                      tile_seq, tile_row0, tile_slot0, tile_nchunks, n_tiles,
-                                                      unit_tile, unit_chunk, n_units, chunk_keys, n_slots, part_acc,
-                                                      part_ml, tile_done, counters, out, nh, nkv, page_size, scale, window,
-                                                      stream);
+    return tmk::launch_prefill_attention<64, 1, 4, 3>(q, kcache, vcache, block_table, bt_stride, unit_rec, n_units,
+                                                      chunk_keys, part_acc, part_ml, tile_done, counters, out, nh,
+                                                      nkv, page_size, scale, window, stream);
   if (D == 128)
-    return tmk::launch_prefill_attention<128, 1, 4, 2>(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before,
-                                                       tile_seq, tile_row0, tile_slot0, tile_nchunks, n_tiles,
-                                                       unit_tile, unit_chunk, n_units, chunk_keys, n_slots, part_acc,
-                                                       part_ml, tile_done, counters, out, nh, nkv, page_size, scale, window,
-                                                       stream);
+    return tmk::launch_prefill_attention<128, 1, 4, 2>(q, kcache, vcache, block_table, bt_stride, unit_rec, n_units,
+                                                       chunk_keys, part_acc, part_ml, tile_done, counters, out, nh,
+                                                       nkv, page_size, scale, window, stream);
   return TM_ERR_UNSUPPORTED_SHAPE;
 }

@@ -35,7 +35,7 @@ class Layout:
     """Offsets of every section inside the packed buffer, for given sizes."""
 
     def __init__(self, T: int, S: int, n_want: int, widths: list[int], tiles: dict[int, int],
-                 units: dict[int, tuple[int, int]] | None = None):
+                 units: dict[int, int] | None = None):
         self.T, self.S, self.n_want, self.widths, self.tiles = T, S, n_want, widths, tiles
         off = 0
 
@@ -52,9 +52,8 @@ class Layout:
         self.block_tables = [take(S * w) for w in widths]
         self.tile_seq = {g: take(n) for g, n in tiles.items()}
         self.tile_row0 = {g: take(n) for g, n in tiles.items()}
-        # prompt-attention units per group size: four per-tile sections, two per-unit sections
-        self.prefill = {g: {name: take(n_tiles if name.startswith("tile_") else n_units) for name in PREFILL_SECTIONS}
-                        for g, (n_tiles, n_units) in (units or {}).items()}
+        # prompt-attention unit records per group size
+        self.prefill = {g: take(n_units * UNIT_FIELDS) for g, n_units in (units or {}).items()}
         self.total = off
 
 
@@ -71,38 +70,45 @@ last_h2d_bytes = 0    # bytes of the most recent step's host-to-device copy (rea
 PACKED_TILE = 64        # rows of the tensor-core prompt attention's row tile
 PREFILL_CHUNK = 512     # keys of one work unit of that kernel (a multiple of its 64-key blocks)
 
-PREFILL_SECTIONS = ("tile_seq", "tile_row0", "tile_slot0", "tile_nchunks", "unit_tile", "unit_chunk")
+UNIT_FIELDS = 8         # ints of one unit record
 
 
 def packed_units(q_lens: np.ndarray, starts: np.ndarray, group_size: int, tile: int = PACKED_TILE,
-                 chunk: int = PREFILL_CHUNK) -> dict:
+                 chunk: int = PREFILL_CHUNK) -> tuple[np.ndarray, int, int]:
     """Work units of the tensor-core prompt attention. A ROW TILE is ``tile`` consecutive (token,
     head-in-group) rows of one request; it sees keys 0 .. the position of its last row. A causal prompt's
     last tile has many times the keys of its first, so a tile's keys are cut at absolute multiples of
     ``chunk`` and every (tile, chunk) is a UNIT of its own, handed out heaviest first. A tile with one chunk
     writes its output itself (slot0 -1); the chunks of the others write partial results into slots
-    slot0 .. slot0 + nchunks - 1 that a second kernel merges in chunk order.
+    slot0 .. slot0 + nchunks - 1, which the last of them to finish merges.
 
-    Returns int32 arrays: per tile ``tile_seq``, ``tile_row0``, ``tile_slot0``, ``tile_nchunks``; per unit
-    ``unit_tile``, ``unit_chunk``; and ``n_slots``."""
+    Returns (records, n_tiles, n_slots); records is int32 [n_units, 8]: request, first row, chunk,
+    number of chunks of the tile, slot0, tile index, first flat row of the request, tokens of the request
+    in this step, tokens of it already in the cache. Everything the kernel needs to start a unit is in its
+    record: one load instead of a chain of lookups."""
     per_seq = (q_lens * group_size + tile - 1) // tile
     n_tiles = int(per_seq.sum())
-    tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), per_seq)
+    tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int64), per_seq)
     first = np.cumsum(per_seq) - per_seq
-    row0 = (np.arange(n_tiles, dtype=np.int32) - np.repeat(first, per_seq).astype(np.int32)) * tile
+    row0 = (np.arange(n_tiles, dtype=np.int64) - np.repeat(first, per_seq)) * tile
     last_pos = starts[tile_seq] + np.minimum(row0 + tile - 1, q_lens[tile_seq] * group_size - 1) // group_size
-    n_chunks = (last_pos // chunk + 1).astype(np.int32)
+    n_chunks = last_pos // chunk + 1
     multi = n_chunks > 1
     counted = np.where(multi, n_chunks, 0)
-    slot0 = np.where(multi, np.cumsum(counted) - counted, -1).astype(np.int32)
-    unit_tile = np.repeat(np.arange(n_tiles, dtype=np.int32), n_chunks)
+    slot0 = np.where(multi, np.cumsum(counted) - counted, -1)
+    unit_tile = np.repeat(np.arange(n_tiles, dtype=np.int64), n_chunks)
     cfirst = np.cumsum(n_chunks) - n_chunks
-    unit_chunk = (np.arange(unit_tile.size, dtype=np.int32) - np.repeat(cfirst, n_chunks)).astype(np.int32)
+    unit_chunk = np.arange(unit_tile.size, dtype=np.int64) - np.repeat(cfirst, n_chunks)
     work = np.minimum(chunk, last_pos[unit_tile] + 1 - unit_chunk * chunk)
     order = np.argsort(-work, kind="stable")
-    return {"tile_seq": tile_seq.astype(np.int32), "tile_row0": row0.astype(np.int32), "tile_slot0": slot0,
-            "tile_nchunks": n_chunks, "unit_tile": unit_tile[order].astype(np.int32),
-            "unit_chunk": unit_chunk[order].astype(np.int32), "n_slots": int(counted.sum())}
+    t, c = unit_tile[order], unit_chunk[order]
+    cu_q = np.cumsum(q_lens) - q_lens
+    sq = tile_seq[t]
+    rec = np.stack([sq, row0[t], c, n_chunks[t], slot0[t], t, cu_q[sq], q_lens[sq], starts[sq]], axis=1)
+    assert rec.shape[1] == UNIT_FIELDS + 1
+    # chunk and number of chunks share one int (both far below 2^16: a chunk is hundreds of keys)
+    packed = np.concatenate([rec[:, :2], (rec[:, 2] | (rec[:, 3] << 16))[:, None], rec[:, 4:]], axis=1)
+    return np.ascontiguousarray(packed, dtype=np.int32), n_tiles, int(counted.sum())
 
 
 def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: torch.device,
@@ -127,7 +133,7 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
     tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
     unit_arrays = {g: packed_units(q_lens, starts, g) for g in group_sizes}
     lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()},
-                 {g: (u["tile_seq"].size, u["unit_tile"].size) for g, u in unit_arrays.items()})
+                 {g: u[0].shape[0] for g, u in unit_arrays.items()})
 
     host = torch.empty(lay.total, dtype=torch.int32, pin_memory=device.type == "cuda")
     buf = host.numpy()
@@ -161,9 +167,8 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
     for g, (tile_seq, tile_row0) in tile_arrays.items():
         buf[lay.tile_seq[g]] = tile_seq
         buf[lay.tile_row0[g]] = tile_row0
-    for g, u in unit_arrays.items():
-        for name in PREFILL_SECTIONS:
-            buf[lay.prefill[g][name]] = u[name]
+    for g, (records, _, _) in unit_arrays.items():
+        buf[lay.prefill[g]] = records.reshape(-1)
 
     dev = host.to(device, non_blocking=True)
     global last_h2d_bytes
@@ -179,6 +184,6 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
         want_rows=dev[lay.want_rows], n_want=len(want_rows), max_q_len=max_q, max_kv_len=max_kv,
         q_lens=q_lens.tolist(), kv_befores=starts.tolist(),
         tiles={g: (dev[lay.tile_seq[g]], dev[lay.tile_row0[g]], a[0].size) for g, a in tile_arrays.items()},
-        prefill={g: PrefillUnits(*(dev[lay.prefill[g][name]] for name in PREFILL_SECTIONS), u["tile_seq"].size,
-                                 u["unit_tile"].size, u["n_slots"], PREFILL_CHUNK) for g, u in unit_arrays.items()},
+        prefill={g: PrefillUnits(dev[lay.prefill[g]], records.shape[0], n_tiles, n_slots, PREFILL_CHUNK)
+                 for g, (records, n_tiles, n_slots) in unit_arrays.items()},
         scratch=scratch, split_keys=use_split, max_splits=-(-max_kv // use_split) if use_split else 0)

@@ -138,29 +138,28 @@ def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
 
 
 def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
-                           cu_q: torch.Tensor, kv_before: torch.Tensor, units, counters: torch.Tensor,
-                           out: torch.Tensor, *, scale: float, window: int = 0, part_acc: torch.Tensor | None = None,
-                           part_ml: torch.Tensor | None = None, tile_done: torch.Tensor | None = None) -> torch.Tensor:
+                           units, counters: torch.Tensor, out: torch.Tensor, *, scale: float, window: int = 0,
+                           part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
+                           tile_done: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core causal attention for prompt portions (bfloat16, head size 64 or 128). ``units``: the
-    step's PrefillUnits for this group size (row tiles of 64 (token, head-in-group) rows, cut into key chunks
-    of units.chunk_keys, heaviest first); part_acc / part_ml: float32 scratch for the tiles with several
-    chunks, at least n_slots * kv_heads * 64 * (head_dim | 2) elements, and tile_done, n_tiles * kv_heads int32
-    zeros (left zero); counters: two int32 zeros the kernel uses as work ticket and leaves zero."""
+    step's PrefillUnits for this group size (records of row tiles of 64 (token, head-in-group) rows cut into
+    key chunks of units.chunk_keys, heaviest first); part_acc / part_ml: float32 scratch for the tiles with
+    several chunks, at least n_slots * kv_heads * 64 * (head_dim | 2) elements, and tile_done, n_tiles *
+    kv_heads int32 zeros (left zero); counters: two int32 zeros the kernel uses as work ticket and leaves zero."""
     T, nh, D = q.shape
     page_size, nkv = kcache.shape[1], kcache.shape[2]
     bf, i32 = torch.bfloat16, torch.int32
     if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
         raise lib.KernelError("prefill_attention_bf16: q / cache / out shapes disagree")
+    if scale <= 0:
+        raise lib.KernelError("prefill_attention_bf16: the score scale must be positive")
     if units.n_slots and (part_acc is None or part_ml is None or tile_done is None
                           or part_acc.numel() < units.n_slots * nkv * 64 * D
                           or part_ml.numel() < units.n_slots * nkv * 64 * 2 or tile_done.numel() < units.n_tiles * nkv):
         raise lib.KernelError("prefill_attention_bf16: scratch for the partial results is missing or too small")
     lib.call("tm_prefill_attention_bf16", _req(q, "q", bf), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf),
-             _req(block_table, "block_table", i32), block_table.stride(0), _req(cu_q, "cu_q", i32),
-             _req(kv_before, "kv_before", i32), _req(units.tile_seq, "tile_seq", i32),
-             _req(units.tile_row0, "tile_row0", i32), _req(units.tile_slot0, "tile_slot0", i32),
-             _req(units.tile_nchunks, "tile_nchunks", i32), units.n_tiles, _req(units.unit_tile, "unit_tile", i32),
-             _req(units.unit_chunk, "unit_chunk", i32), units.n_units, int(units.chunk_keys), units.n_slots,
+             _req(block_table, "block_table", i32), block_table.stride(0), _req(units.records, "unit records", i32),
+             units.n_units, int(units.chunk_keys),
              _req(part_acc, "part_acc", torch.float32) if units.n_slots else None,
              _req(part_ml, "part_ml", torch.float32) if units.n_slots else None,
              _req(tile_done, "tile_done", i32) if units.n_slots else None,

@@ -166,8 +166,8 @@ class GroupedQueryAttention:
             units = step.prefill[G]                # 64-row tiles cut into key chunks, heaviest first
             part_acc, part_ml, tile_done = step.scratch.get_prefill(units.n_slots * self.nkv, self.D,
                                                                     units.n_tiles * self.nkv)
-            ops.prefill_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
-                                       step.kv_before, units, step.scratch.counters(), out,
+            ops.prefill_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], units,
+                                       step.scratch.counters(), out,
                                        scale=self.scale, window=self.window, part_acc=part_acc, part_ml=part_ml,
                                        tile_done=tile_done)
             return

@@ -34,17 +34,12 @@ class LayerCache:
 
 class PrefillUnits(NamedTuple):
     """Work units of the tensor-core prompt attention for one group size (engine/batch.py packed_units):
-    per 64-row tile its request, first row, first partial slot (-1: writes its output itself) and number
-    of key chunks; per unit its tile and key chunk (of chunk_keys keys), heaviest first."""
+    one 8-int record per unit (a 64-row tile of one request times one chunk of chunk_keys keys), heaviest
+    first; n_slots partial-result slots are needed, for n_tiles row tiles."""
 
-    tile_seq: torch.Tensor
-    tile_row0: torch.Tensor
-    tile_slot0: torch.Tensor
-    tile_nchunks: torch.Tensor
-    unit_tile: torch.Tensor
-    unit_chunk: torch.Tensor
-    n_tiles: int
+    records: torch.Tensor
     n_units: int
+    n_tiles: int
     n_slots: int
     chunk_keys: int
 
