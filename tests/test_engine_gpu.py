@@ -311,3 +311,91 @@ def test_whole_step_decode_kernel_through_the_engine(d64_dir):
     finally:
         fused._ENABLED = old
     assert_tokens_are_argmax_of_plain(d64_dir, prompts, outs2, "bfloat16")
+
+
+def _run_requests(eng, prompts, params, abort_after=None):
+    """Drive the step loop by hand; returns per request (token ids, finish reason, tokens seen in outputs)."""
+    seqs = [eng.add_request(f"r{i}", p, sp) for i, (p, sp) in enumerate(zip(prompts, params))]
+    seen = {s.id: [] for s in seqs}
+    reasons = {}
+    steps = 0
+    while eng.has_unfinished():
+        for o in eng.step():
+            seen[o.request_id] += o.new_token_ids
+            if o.finished:
+                reasons[o.request_id] = o.finish_reason
+                assert o.num_output_tokens == len(seen[o.request_id])
+        steps += 1
+        if abort_after and steps == abort_after[1]:
+            out = eng.abort_request(abort_after[0])
+            assert out is not None and out.finished and out.finish_reason == "abort"
+            reasons[abort_after[0]] = "abort"
+    eng.drain()
+    assert eng.cache.all_free and not eng.scheduler.running
+    return [(s.output_ids, reasons.get(s.id), seen[s.id]) for s in seqs]
+
+
+def test_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_dir):
+    """With one decode step in flight (tokens fed on the device, the host one step behind) every request gets
+    the same tokens, stops for the same reason at the same place, and the outputs carry every token once:
+    ends by max_tokens at different lengths, by an end-of-sequence token the host cannot foresee, seeded
+    sampling, an abort while a step is in flight, and a request joining while others decode."""
+    from tokenmill_b200.sampling import SamplingParams
+    prompts = prompts_for(d64_dir, lengths=(3, 17, 40, 5, 64, 9))
+    # pick an end-of-sequence token that the greedy run of request 2 produces in mid-stream
+    probe = engine_for(d64_dir, dtype="bfloat16", async_decode=False)
+    eos = probe.generate([prompts[2]], greedy(30))[0][11]
+    params = [SamplingParams(max_tokens=7, ignore_eos=True), SamplingParams(max_tokens=1, ignore_eos=True),
+              SamplingParams(max_tokens=40), SamplingParams(max_tokens=25, temperature=0.8, top_k=50, seed=11, ignore_eos=True),
+              SamplingParams(max_tokens=33, temperature=1.1, top_p=0.9, seed=5, ignore_eos=True),
+              SamplingParams(max_tokens=30, ignore_eos=True)]
+    results = {}
+    for mode in (False, True):
+        eng = engine_for(d64_dir, dtype="bfloat16", async_decode=mode)
+        eng.eos_ids = {eos}
+        assert eng._pipelining() == mode
+        results[mode] = _run_requests(eng, prompts, params, abort_after=("r5", 9))
+        if mode:
+            assert eng.runner.stats["fused_steps"] >= 30
+    for (ids_s, why_s, seen_s), (ids_a, why_a, seen_a), sp in zip(results[False], results[True], params):
+        if why_s == "abort":          # the abort lands one token apart, by construction; the common part agrees
+            n = min(len(ids_s), len(ids_a))
+            assert why_a == "abort" and ids_s[:n] == ids_a[:n] and -1 not in ids_a
+            continue
+        assert ids_s == ids_a and why_s == why_a and seen_s == ids_s and seen_a == ids_a
+    assert results[False][2][1] == "stop" and results[False][2][0][-1] == eos and len(results[False][2][0]) <= 12
+    assert [r[1] for r in results[False][:2]] == ["length", "length"]
+
+    # a request that arrives while a step is in flight joins after that step; nobody's tokens change
+    late = prompts_for(d64_dir, lengths=(21,))[0]
+    outs = {}
+    for mode in (False, True):
+        eng = engine_for(d64_dir, dtype="bfloat16", async_decode=mode)
+        seqs = [eng.add_request(f"a{i}", p, greedy(20)) for i, p in enumerate(prompts[:3])]
+        for _ in range(6):
+            eng.step()
+        seqs.append(eng.add_request("late", late, greedy(10)))
+        while eng.has_unfinished():
+            eng.step()
+        eng.drain()
+        outs[mode] = [s.output_ids for s in seqs]
+        assert eng.cache.all_free
+    assert outs[False] == outs[True]
+
+
+def test_decode_steps_in_flight_survive_preemption(d64_dir):
+    """A pool so small that decoding preempts: the request thrown out while a step is in flight keeps the
+    token that step chose for it, is recomputed later, and ends with the tokens of the synchronous loop."""
+    prompts = prompts_for(d64_dir, lengths=(30, 33, 28, 35))
+    outs = {}
+    probe = engine_for(d64_dir, dtype="bfloat16")
+    per_token = probe.model.cache_layout().bytes_per_token(2)
+    for mode in (False, True):
+        # 12 pages of 16 tokens: four requests of about 32 + 40 tokens (5 pages each) do not fit together
+        eng = engine_for(d64_dir, dtype="bfloat16", async_decode=mode, max_model_len=128, max_num_seqs=4,
+                         kv_cache_mb=(12 * 16 + 1) * per_token / 2 ** 20)
+        assert eng.cache.num_pages == [12]
+        outs[mode] = eng.generate(prompts, greedy(40))
+        assert eng.scheduler.num_preemptions > 0 and eng.cache.all_free
+    assert outs[False] == outs[True]
+    assert_tokens_are_argmax_of_plain(d64_dir, prompts, outs[True], "bfloat16")

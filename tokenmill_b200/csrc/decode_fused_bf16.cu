@@ -82,6 +82,7 @@ struct FusedArgs {
   const int* cu_q;
   const int* kv_before;
   const int* want_rows;
+  const int* token_rows;           // null, or [T]: token t's id is token_ids[token_rows[t]] (ids left on the device by the previous step's sampling)
   int T, S, n_want, page_size, split_keys, max_splits;
   // workspaces
   float* resid;                    // [T, H] the 32-bit residual stream; the projections add into it
@@ -204,13 +205,14 @@ __device__ __forceinline__ void fu_load_x4(const __nv_bfloat16* erow, const floa
 }
 
 __device__ __noinline__ void fu_norm_rows(int T, int H, const __nv_bfloat16* embedding, const int* token_ids,
+                                          const int* token_rows,
                                           float* resid, const float* ln_w, float eps, unsigned char* xs,
                                           int row_bytes) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n4 = H / 4;                                    // float4 groups per row (H is a multiple of 8)
   for (int r = warp; r < T; r += kFuWarps) {               // rows beyond T feed accumulator rows nobody reads
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)r * row_bytes);
-    const __nv_bfloat16* erow = embedding ? embedding + (size_t)token_ids[r] * H : nullptr;
+    const __nv_bfloat16* erow = embedding ? embedding + (size_t)token_ids[token_rows ? token_rows[r] : r] * H : nullptr;
     const float* rrow = resid + (size_t)r * H;
     const bool one_batch = n4 <= kNormBatch * 32;
     float x[kNormBatch][4], w[kNormBatch][4];
@@ -1005,7 +1007,8 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
       }
     }
     // A: norm + QKV
-    fu_norm_rows(a.T, a.H, l == 0 ? a.embedding : nullptr, a.token_ids, a.resid, L.ln1_w, a.eps1, xs, rb_h);
+    fu_norm_rows(a.T, a.H, l == 0 ? a.embedding : nullptr, a.token_ids, a.token_rows, a.resid, L.ln1_w, a.eps1, xs,
+                 rb_h);
     __syncthreads();
     fu_stamp(a, l * 16 + 1);
     fu_project<FU_QKV>(a, L, R, s_layers, t_qkv, R.nq, R.kq, R.cpt_pair, R.ch_h, (a.nh + 2 * a.nkv) * a.D, a.H, nullptr,
@@ -1033,7 +1036,7 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
     fu_stamp(a, l * 16 + 6);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     // D: norm + gate/up + SwiGLU
-    fu_norm_rows(a.T, a.H, nullptr, a.token_ids, a.resid, L.ln2_w, a.eps2, xs, rb_h);
+    fu_norm_rows(a.T, a.H, nullptr, a.token_ids, nullptr, a.resid, L.ln2_w, a.eps2, xs, rb_h);
     __syncthreads();
     fu_stamp(a, l * 16 + 7);
     fu_gate_up(a, R, s_layers, t_gu, l, xs, rb_h, &s_ok);

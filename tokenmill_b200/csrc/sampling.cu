@@ -161,7 +161,7 @@ __device__ __forceinline__ int block_count(int v, int* red) {
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, int V, long long row_stride, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
-    const int* __restrict__ rows, int* __restrict__ out) {
+    const int* __restrict__ rows, int* __restrict__ out, int scatter) {
   __shared__ float redf[32];
   __shared__ int redi[32];
   __shared__ float warp_tot[32];
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     if (lane == 0) s_token = found >= 0 ? found : last_kept;
   }
   __syncthreads();
-  if (tid == 0) out[rowi] = s_token < 0 ? 0 : s_token;
+  if (tid == 0) out[scatter && rows ? rows[rowi] : rowi] = s_token < 0 ? 0 : s_token;
 }
 
 }  // namespace tmk
@@ -308,13 +308,14 @@ extern "C" int tm_argmax(const float* logits, int n_rows, int V, long long row_s
 }
 
 // temperature [n] (> 0), top_k [n] (<= 0 or >= V: off), top_p [n] (>= 1: off), uniform [n] in [0, 1).
-// rows [n] (or null): which row of `logits` draw i reads; out [n].
+// rows [n] (or null): which row of `logits` draw i reads; out [n], or with `scatter` an array indexed like the
+// logits rows: draw i then lands in out[rows[i]] (the other entries stay as they are).
 extern "C" int tm_sample(const float* logits, int n_rows, int V, long long row_stride, const float* temperature,
                          const int* top_k, const float* top_p, const float* uniform, const int* rows, int* out,
-                         cudaStream_t stream) {
+                         int scatter, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
   tmk::sample_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, temperature, top_k, top_p,
-                                                              uniform, rows, out);
+                                                              uniform, rows, out, scatter);
   return tmk::launch_status();
 }

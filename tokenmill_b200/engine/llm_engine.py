@@ -7,6 +7,15 @@ re-plans the batch, so new requests join at the next step and finished ones leav
 count computed tokens and publish full pages -> append the sampled tokens -> stop checks -> outputs.
 Prompts and outputs are token ids; the text side of the reference (tokenizer, HTTP) is not part of
 this engine.
+
+Decode steps the whole-step kernel takes are pipelined (``EngineConfig.async_decode``): the next step is
+planned and launched, its token ids taken on the device from what the previous step's sampling wrote,
+BEFORE the host reads the previous step's tokens; the host's own work per step (planning, metadata,
+bookkeeping) then runs while the GPU is busy instead of between two launches. ``step()`` returns the
+outputs of the step that was in flight, so a request's tokens arrive one call later than they were
+computed; a request that turns out to have ended (end-of-sequence token) has one surplus token computed
+and thrown away. Ends the engine can foresee (``max_tokens``, ``max_model_len``) cost nothing. Tokens,
+stop reasons and the order of outputs are the same as in the synchronous loop.
 """
 
 from __future__ import annotations
@@ -65,6 +74,20 @@ def kv_budget_bytes(cfg: EngineConfig, model: DecoderModel) -> int:
     return budget
 
 
+PLACEHOLDER = -1        # stands in a request's output list for a token that is chosen but not read yet
+
+
+class _InFlight:
+    """A decode step that has been launched and whose tokens the host has not read."""
+
+    __slots__ = ("seqs", "index", "pending", "row_of", "void", "plan", "t0")
+
+    def __init__(self, seqs, index, pending, plan, t0):
+        self.seqs, self.index, self.pending, self.plan, self.t0 = seqs, index, pending, plan, t0
+        self.row_of = {id(s): i for i, s in enumerate(seqs)}
+        self.void: set[int] = set()        # rows whose request ended with the step before: token thrown away
+
+
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, model: DecoderModel | None = None):
         self.cfg = cfg
@@ -98,6 +121,7 @@ class LLMEngine:
         self.scheduler = Scheduler(cfg, self.cache)
         self.sampler = Sampler(self.device)
         self.seqs: dict[str, Sequence] = {}
+        self._inflight: _InFlight | None = None
         self._rng = random.Random(cfg.seed)
         self._offline_counter = 0
         self.stats = {"steps": 0, "peak_running": 0, "prefill_steps": 0, "decode_steps": 0,
@@ -130,6 +154,9 @@ class LLMEngine:
         seq = self.seqs.pop(request_id, None)
         if seq is None:
             return None
+        while seq.output_ids and seq.output_ids[-1] == PLACEHOLDER:      # tokens of steps still in flight
+            seq.output_ids.pop()
+        seq.finishing = False
         self.scheduler.finish(seq, reason)
         seq.finish_time = time.monotonic()
         return self._output(seq, [])
@@ -137,22 +164,147 @@ class LLMEngine:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 
+    def _pipelining(self) -> bool:
+        """Decode steps may stay in flight: the whole-step kernel is there (it can take token ids from the
+        device), and nothing in the configuration needs a step's token ids on the host at once (prefix
+        caching hashes them; mixed steps re-plan prompt portions)."""
+        return (self.cfg.async_decode and self.runner.fused is not None and not self.cfg.enable_chunked_prefill
+                and not self.cfg.enable_prefix_caching)
+
     # --- one step -------------------------------------------------------------------------------
 
     def step(self) -> list[RequestOutput]:
+        if self._inflight is not None:
+            return self._step_behind()
         outputs: list[RequestOutput] = []
         t0 = time.perf_counter()
         plan = self.scheduler.schedule()
+        outputs += self._drop_ignored(plan)
+        if plan.empty:
+            return outputs
+        if self._pipelining() and self._is_plain_decode(plan):
+            self._inflight = self._launch(plan, None, t0)      # its outputs come with the next call
+            return outputs
+        return outputs + self._run(plan, t0)
+
+    def _drop_ignored(self, plan) -> list[RequestOutput]:
+        outputs = []
         for seq in plan.ignored:
             self.seqs.pop(seq.id, None)
             self.scheduler.finish(seq, "length")
             seq.finish_time = time.monotonic()
             outputs.append(self._output(seq, [], error=None if seq.output_ids else
                                         "prompt does not fit in the KV cache"))
-        if plan.empty:
-            return outputs
+        return outputs
+
+    # --- decode steps in flight -----------------------------------------------------------------
+
+    def _is_plain_decode(self, plan) -> bool:
+        return (not plan.prefill_items and self.runner.can_feed_tokens_on_device(len(plan.items))
+                and all(it.samples and it.num_tokens == 1 for it in plan.items))
+
+    def _launch(self, plan, prev: _InFlight | None, t0: float) -> _InFlight:
+        """Launch the plan's decode step without waiting for anything. With ``prev`` (the step still in
+        flight) a request's token is what that step's sampling left on the device."""
+        seqs = [it.seq for it in plan.items]
+        entries, rows = [], []
+        for it in plan.items:
+            seq = it.seq
+            if prev is None:
+                entries.append(StepEntry(seq.cache, [seq.all_token_ids[it.start]], it.start, [0]))
+            else:
+                entries.append(StepEntry(seq.cache, [0], it.start, [0]))
+                rows.append(prev.row_of[id(seq)])
+        if prev is None:
+            logits = self.runner.step(entries)
+        else:
+            logits = self.runner.step_fed(entries, prev.pending.dev, rows)
+        pending = self.sampler.launch(logits, [s.params for s in seqs], [s.sample_seed for s in seqs],
+                                      [s.num_draws for s in seqs])
+        index = []
+        for it in plan.items:
+            seq = it.seq
+            seq.num_computed_tokens = it.start + 1
+            self.cache.release_behind_window(seq.cache, seq.num_computed_tokens)
+            if not seq.params.greedy:
+                seq.num_draws += 1
+            index.append(len(seq.output_ids))
+            seq.output_ids.append(PLACEHOLDER)
+        return _InFlight(seqs, index, pending, plan, t0)
+
+    def _step_behind(self) -> list[RequestOutput]:
+        """One call while a decode step is in flight: plan and launch the step after it if nothing stands
+        in the way, then read the tokens of the step in flight and do its bookkeeping."""
+        cur = self._inflight
+        outputs: list[RequestOutput] = []
+        nxt, leftover = None, None
+        t0 = time.perf_counter()
+        if not self.scheduler.waiting and self._pipelining():
+            for seq, at in zip(cur.seqs, cur.index):
+                # Ends the host can foresee: the step in flight brings the request's last token.
+                if not seq.is_finished and (at + 1 >= seq.params.max_tokens or
+                                            seq.num_prompt_tokens + at + 1 >= self.cfg.max_model_len):
+                    seq.finishing = True
+            plan = self.scheduler.schedule()
+            outputs += self._drop_ignored(plan)
+            if not plan.empty:
+                if self._is_plain_decode(plan) and all(id(it.seq) in cur.row_of for it in plan.items):
+                    nxt = self._launch(plan, cur, t0)
+                else:
+                    leftover = plan                # planned (pages grown) but not launched: run it below
+        outputs += self._collect(cur, nxt)
+        self._inflight = nxt
+        if leftover is not None:
+            outputs += self._run(leftover, t0)
+        return outputs
+
+    def _collect(self, cur: _InFlight, nxt: _InFlight | None) -> list[RequestOutput]:
+        tokens = self.sampler.collect(cur.pending)
+        now = time.monotonic()
+        outputs = []
+        n_new = 0
+        for row, (seq, at) in enumerate(zip(cur.seqs, cur.index)):
+            if row in cur.void or seq.is_finished:        # ended a step earlier, or aborted meanwhile
+                continue
+            tok = tokens[row]
+            seq.output_ids[at] = tok
+            n_new += 1
+            if seq.first_token_time is None:
+                seq.first_token_time = now
+            n_out = at + 1
+            reason = None
+            if tok in self.eos_ids and not seq.params.ignore_eos:
+                reason = "stop"
+            elif n_out >= seq.params.max_tokens or seq.num_prompt_tokens + n_out >= self.cfg.max_model_len:
+                reason = "length"
+            if reason:
+                del seq.output_ids[n_out:]                # the place kept for the step after this one
+                if nxt is not None and id(seq) in nxt.row_of:
+                    nxt.void.add(nxt.row_of[id(seq)])
+                seq.finishing = False
+                self.scheduler.finish(seq, reason)
+                seq.finish_time = now
+                self.seqs.pop(seq.id, None)
+            outputs.append(self._output(seq, [tok], num_output_tokens=n_out))
+        self._record_step(cur.plan, time.perf_counter() - cur.t0, n_new)
+        return outputs
+
+    def drain(self) -> list[RequestOutput]:
+        """Read the step in flight, if any, without launching another (e.g. before the engine is dropped)."""
+        if self._inflight is None:
+            return []
+        cur, self._inflight = self._inflight, None
+        return self._collect(cur, None)
+
+    # --- one step, start to end -----------------------------------------------------------------
+
+    def _run(self, plan, t0: float) -> list[RequestOutput]:
+        outputs: list[RequestOutput] = []
         entries, sampled = [], []
-        for item in plan.items:
+        items = [it for it in plan.items if not it.seq.is_finished]    # (ended since the plan was made)
+        if not items:
+            return outputs
+        for item in items:
             seq = item.seq
             tokens = seq.all_token_ids[item.start:item.start + item.num_tokens]
             want = [item.num_tokens - 1] if item.samples else []
@@ -163,7 +315,7 @@ class LLMEngine:
         tokens = self.sampler.sample(logits, [s.params for s in sampled], [s.sample_seed for s in sampled],
                                      [s.num_draws for s in sampled]) if sampled else []
         now = time.monotonic()
-        for item in plan.items:
+        for item in items:
             seq = item.seq
             seq.num_computed_tokens = item.start + item.num_tokens
             self.cache.register_computed(seq.cache, seq.all_token_ids, seq.num_computed_tokens)
@@ -190,9 +342,11 @@ class LLMEngine:
             return "length"
         return None
 
-    def _output(self, seq: Sequence, new_tokens: list[int], error: str | None = None) -> RequestOutput:
+    def _output(self, seq: Sequence, new_tokens: list[int], error: str | None = None,
+                num_output_tokens: int | None = None) -> RequestOutput:
+        n_out = seq.num_output_tokens if num_output_tokens is None else num_output_tokens
         return RequestOutput(seq.id, new_tokens, seq.is_finished, seq.finish_reason, seq.num_prompt_tokens,
-                             seq.num_output_tokens, seq.arrival_time, seq.first_token_time, seq.finish_time,
+                             n_out, seq.arrival_time, seq.first_token_time, seq.finish_time,
                              seq.num_preemptions, error)
 
     def _record_step(self, plan, step_time: float, n_generated: int) -> None:

@@ -100,6 +100,28 @@ class ModelRunner:
             ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
         return logits
 
+    def can_feed_tokens_on_device(self, n_entries: int) -> bool:
+        """Whether ``step_fed`` takes a decode step of this many requests."""
+        return self.fused is not None and 0 < n_entries <= fused.MAX_TOKENS
+
+    @torch.inference_mode()
+    def step_fed(self, entries: list[StepEntry], token_src: torch.Tensor, token_rows: list[int]) -> torch.Tensor:
+        """A decode step (one token per entry, logits wanted for each) whose token ids are not known on the
+        host yet: entry i continues with token_src[token_rows[i]], an int32 device tensor the previous step's
+        sampling wrote. Everything else (positions, pages) comes from the entries as usual."""
+        if not self.can_feed_tokens_on_device(len(entries)):
+            raise RuntimeError("this step cannot take its tokens from the device")
+        for e in entries:
+            if e.start + 1 > self.max_model_len:
+                raise ValueError(f"a request would reach {e.start + 1} tokens; max_model_len is {self.max_model_len}")
+        self.fused.check()
+        self.stats["steps"] += 1
+        self.stats["tokens"] += len(entries)
+        self.stats["fused_steps"] += 1
+        hidden = self.fused.run_decode(entries, self.cache.page_size, token_src=token_src, token_rows=token_rows)
+        self.stats["h2d_bytes"] = self.fused.h2d_bytes
+        return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
+
     # --- decode graphs --------------------------------------------------------------------------
 
     def _reserve_scratch(self, batch: int) -> None:

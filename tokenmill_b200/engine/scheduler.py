@@ -130,7 +130,9 @@ class Scheduler:
         return self._decode_steps_since_prefill >= self.cfg.max_waiting_steps
 
     def _oldest_first(self) -> list[Sequence]:
-        return sorted(self.running, key=lambda s: s.admit_order)
+        """Running requests, oldest admission first; without those the engine already knows to end with a
+        step that is still in flight."""
+        return sorted((s for s in self.running if not s.finishing), key=lambda s: s.admit_order)
 
     def _admit(self, seq: Sequence) -> None:
         tokens = seq.all_token_ids

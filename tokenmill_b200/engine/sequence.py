@@ -33,6 +33,7 @@ class Sequence:
     num_preemptions: int = 0
     sample_seed: int = 0                      # key of the request's random stream
     num_draws: int = 0                        # random draws taken so far
+    finishing: bool = False                   # ends with a step already launched: not scheduled again
 
     def __repr__(self) -> str:
         return (f"Sequence({self.id!r}, {self.status.name}, prompt={len(self.prompt_ids)}, "

@@ -17,6 +17,7 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from . import lib
+from .ops import _stream as ops_stream
 
 MAX_TOKENS = 16
 MAX_LAYERS = 96          # entries of the kernel's layer table in shared memory
@@ -38,7 +39,7 @@ class _Args(ctypes.Structure):
         + [("n_pos", c_int)]
         + [(n, c_void_p) for n in ("token_ids", "positions", "slot_map", "block_table")]
         + [("bt_stride", c_int)]
-        + [(n, c_void_p) for n in ("cu_q", "kv_before", "want_rows")]
+        + [(n, c_void_p) for n in ("cu_q", "kv_before", "want_rows", "token_rows")]
         + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
         + [(n, c_void_p) for n in ("resid", "q", "part_acc", "part_ml", "attn", "act", "attn_count", "bar",
                                    "error", "hidden_out")]
@@ -188,7 +189,7 @@ class FusedDecoder:
     def _decode_ring(self, page_size: int):
         if getattr(self, "_ring", None) is None:
             width = -(-self.max_model_len // page_size)
-            n = 6 * 16 + 4 + MAX_TOKENS * width          # six sections of 16 (cu_q: 20) and the block table
+            n = 7 * 16 + 4 + MAX_TOKENS * width          # seven sections of 16 (cu_q: 20) and the block table
             self._ring = [(torch.zeros(n, dtype=torch.int32, pin_memory=True),
                            torch.zeros(n, dtype=torch.int32, device=self.device), torch.cuda.Event())
                           for _ in range(self._RING)]
@@ -196,10 +197,14 @@ class FusedDecoder:
             self._ring_at = 0
         return self._ring
 
-    def run_decode(self, entries, page_size: int) -> torch.Tensor:
+    def run_decode(self, entries, page_size: int, token_src: torch.Tensor | None = None,
+                   token_rows: list[int] | None = None) -> torch.Tensor:
         """One new token for each of at most 16 requests, logits wanted for every one of them. The step's
         integers (token, position, cache slot, request offsets, block table) go into one of a few pinned
-        buffers and from there to the device in one copy; ``h2d_bytes`` says how many."""
+        buffers and from there to the device in one copy; ``h2d_bytes`` says how many. With ``token_src`` (an
+        int32 device tensor, e.g. what the previous step's sampling wrote) entry i's token is
+        token_src[token_rows[i]] and the entries' own token ids are ignored: the step can be launched before
+        the host knows the tokens."""
         ring = self._decode_ring(page_size)
         k = self._ring_at
         self._ring_at = (k + 1) % self._RING
@@ -209,38 +214,49 @@ class FusedDecoder:
         S = len(entries)
         max_kv = max(e.start for e in entries) + 1
         width = -(-max_kv // page_size)
-        o_tok, o_pos, o_slot, o_cu, o_before, o_want, o_tab = 0, 16, 32, 48, 68, 84, 100
+        o_tok, o_pos, o_slot, o_cu, o_before, o_want, o_rows, o_tab = 0, 16, 32, 48, 68, 84, 100, 116
         tab = buf[o_tab:o_tab + S * width].reshape(S, width)
+        toks, poss, slots = [0] * S, [0] * S, [0] * S
         for i, e in enumerate(entries):
             pos = e.start
             pages = e.handle.tables[0]
-            need = pos // page_size + 1
-            if len(pages) < need:
-                raise RuntimeError(f"entry {i} holds {len(pages)} pages, its {pos + 1} tokens need {need}")
-            page = pages[pos // page_size]
+            at = pos // page_size
+            if len(pages) <= at:
+                raise RuntimeError(f"entry {i} holds {len(pages)} pages, its {pos + 1} tokens need {at + 1}")
+            page = pages[at]
             if page < 0:
                 raise RuntimeError(f"entry {i} writes into a page it has already given back")
-            buf[o_tok + i] = e.tokens[0]
-            buf[o_pos + i] = pos
-            buf[o_slot + i] = page * page_size + pos % page_size
-            buf[o_before + i] = pos
-            row = pages[:width]
-            tab[i, :len(row)] = row
-            tab[i, len(row):] = 0
+            toks[i], poss[i], slots[i] = e.tokens[0], pos, page * page_size + pos % page_size
+            n = min(len(pages), width)
+            tab[i, :n] = pages[:n]
+            if n < width:
+                tab[i, n:] = 0
+        buf[o_tok:o_tok + S] = toks
+        buf[o_pos:o_pos + S] = poss
+        buf[o_slot:o_slot + S] = slots
+        buf[o_before:o_before + S] = poss
         buf[o_cu:o_cu + S + 1] = self._arange[:S + 1]
         buf[o_want:o_want + S] = self._arange[:S]
+        if token_src is not None:
+            buf[o_rows:o_rows + S] = token_rows
         used = o_tab + S * width
         dev[:used].copy_(host[:used], non_blocking=True)
         copied.record()
         self.h2d_bytes = used * 4
         a, base = self._args, dev.data_ptr()
         a.token_ids, a.positions, a.slot_map = base + 4 * o_tok, base + 4 * o_pos, base + 4 * o_slot
+        if token_src is not None:
+            if token_src.dtype != torch.int32 or not token_src.is_cuda or len(token_rows) != S:
+                raise lib.KernelError("run_decode: token_src must be int32 on the device, one row index per entry")
+            a.token_ids, a.token_rows = token_src.data_ptr(), base + 4 * o_rows
+        else:
+            a.token_rows = None
         a.cu_q, a.kv_before, a.want_rows = base + 4 * o_cu, base + 4 * o_before, base + 4 * o_want
         a.block_table, a.bt_stride = base + 4 * o_tab, width
         a.T, a.S, a.n_want, a.page_size = S, S, S, page_size
         a.split_keys = self.split_for(S, max_kv)
         a.max_splits = -(-max_kv // a.split_keys)
-        lib.call("tm_decode_fused", ctypes.addressof(a), torch.cuda.current_stream().cuda_stream)
+        lib.call("tm_decode_fused", ctypes.addressof(a), ops_stream())
         self._err_host.copy_(self.error, non_blocking=True)
         self.launches += 1
         return self.hidden[:S]
@@ -252,10 +268,11 @@ class FusedDecoder:
         a.slot_map, a.block_table = step.slot_maps[0].data_ptr(), step.block_tables[0].data_ptr()
         a.bt_stride = step.block_tables[0].stride(0)
         a.cu_q, a.kv_before, a.want_rows = step.cu_q.data_ptr(), step.kv_before.data_ptr(), step.want_rows.data_ptr()
+        a.token_rows = None
         a.T, a.S, a.n_want, a.page_size = step.n_tokens, step.n_seqs, step.n_want, page_size
         a.split_keys = self.split_for(step.n_seqs, step.max_kv_len)
         a.max_splits = -(-step.max_kv_len // a.split_keys)
-        lib.call("tm_decode_fused", ctypes.addressof(a), torch.cuda.current_stream().cuda_stream)
+        lib.call("tm_decode_fused", ctypes.addressof(a), ops_stream())
         self._err_host.copy_(self.error, non_blocking=True)     # looked at by check() after the step's own sync
         self.launches += 1
         return self.hidden[:step.n_want]
