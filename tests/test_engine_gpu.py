@@ -399,3 +399,58 @@ def test_decode_steps_in_flight_survive_preemption(d64_dir):
         assert eng.scheduler.num_preemptions > 0 and eng.cache.all_free
     assert outs[False] == outs[True]
     assert_tokens_are_argmax_of_plain(d64_dir, prompts, outs[True], "bfloat16")
+
+
+@pytest.fixture(scope="module")
+def wide_dir(tmp_path_factory):
+    """Two layers of the Qwen2.5-0.5B layer sizes (hidden 896, 14 query heads over 2 kv heads of 64,
+    feed-forward 4864) with a small vocabulary: the shapes for which the whole-step kernel's work split is
+    made (5 gate/up units on some blocks, a down-projection input of 78 KB per 8 tokens, few ring stages)."""
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    cfg = qwen2_config(vocab_size=1000, hidden_size=896, intermediate_size=4864, num_hidden_layers=2,
+                       num_attention_heads=14, num_key_value_heads=2, head_dim=64, rope_theta=1000000.0,
+                       rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096)
+    return write_random_model(tmp_path_factory.mktemp("wide"), cfg, seed=4)
+
+
+@pytest.mark.parametrize("batch", [1, 5, 8, 9, 13, 16])
+def test_whole_step_kernel_at_model_sizes_equals_the_kernel_per_operation_path(wide_dir, batch):
+    """Same requests, same steps, through the whole-step kernel and through the separate kernels: the logits
+    agree within bfloat16 rounding, at batch sizes on both sides of the 8-token staging limit (above it the
+    kernel runs with a single ring stage)."""
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.kernels import fused
+    rng = random.Random(batch)
+    prompts = [[rng.randrange(1000) for _ in range(rng.randrange(300, 700))] for _ in range(batch)]
+    nxt = [[rng.randrange(1000) for _ in range(batch)] for _ in range(4)]
+
+    def run(use_fused):
+        old = fused._ENABLED
+        fused._ENABLED = use_fused
+        try:
+            eng = engine_for(wide_dir, dtype="bfloat16", max_model_len=1024, max_num_seqs=16, kv_cache_mb=64,
+                             max_num_batched_tokens=4096)
+        finally:
+            fused._ENABLED = old
+        assert (eng.runner.fused is not None) == use_fused
+        r, cache = eng.runner, eng.cache
+        hs = []
+        for p in prompts:
+            h = cache.new_handle()
+            cache.allocate(h, p)
+            hs.append(h)
+        for lo in range(0, batch, 4):
+            r.step([StepEntry(h, p, 0, []) for h, p in zip(hs[lo:lo + 4], prompts[lo:lo + 4])])
+        outs = []
+        for k, toks in enumerate(nxt):
+            for h, p in zip(hs, prompts):
+                cache.grow(h, len(p) + k + 1)
+            outs.append(r.step([StepEntry(h, [t], len(p) + k, [0]) for h, p, t in zip(hs, prompts, toks)]).float().cpu())
+        if use_fused:
+            assert r.stats["fused_steps"] == len(nxt)
+            r.fused.check()
+        return outs
+
+    for a, b in zip(run(True), run(False)):
+        assert torch.isfinite(a).all()
+        assert float((a - b).abs().max()) <= 3e-2 * float(b.abs().max()), float((a - b).abs().max())

@@ -368,7 +368,7 @@ __device__ __forceinline__ void fu_tile_issue(const FusedArgs& a, const FuRing& 
   const FusedLayer& L = layers[l];
   const __nv_bfloat16* W = d.matrix == 0 ? L.w_qkv : d.matrix == 1 ? L.w_o : d.matrix == 2 ? L.w_gu : L.w_down;
   const int s = i % R.nst;
-  R.issued[s] = i / R.nst + 1;
+  *reinterpret_cast<volatile int*>(R.issued + s) = i / R.nst + 1;
   const uint32_t bar = R.bars + s * 8, dst = R.base + s * R.stage_bytes, bytes = (uint32_t)d.nc * kFuChunkBytes;
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(d.pair ? 2 * bytes : bytes) : "memory");
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -413,7 +413,25 @@ __device__ __forceinline__ void fu_bar_wait(const FusedArgs& a, uint32_t bar, ui
   *reinterpret_cast<volatile int*>(s_ok) = 0;
 }
 __device__ __forceinline__ void fu_tile_wait(const FusedArgs& a, const FuRing& R, int i, int* s_ok) {
-  fu_bar_wait(a, R.bars + (i % R.nst) * 8, (uint32_t)(i / R.nst) & 1u, s_ok);
+  // A barrier's phase can be told from the one before or after it, not from one two away: a warp that
+  // polled for tile i while the stage's barrier was still two phases back (tile i - 2 nst not landed yet;
+  // it happens as soon as a block has more tiles to wait for at once than stages) would be told "complete"
+  // at once. So the warp first waits until tile i has been asked for, which happens only after tile
+  // i - nst was used up; from then on the barrier is in tile i's phase or past it.
+  const int s = i % R.nst, round = i / R.nst + 1;
+  const volatile int* issued = R.issued + s;
+  for (uint32_t spins = 0; *issued < round; ++spins) {
+    if (spins > kFuSpinLimit) {
+      atomicCAS(a.error, 0, 2000);
+      *reinterpret_cast<volatile int*>(s_ok) = 0;
+      return;
+    }
+    if (spins > 64) {
+      if (*reinterpret_cast<volatile int*>(s_ok) == 0) return;
+      __nanosleep(20);
+    }
+  }
+  fu_bar_wait(a, R.bars + s * 8, (uint32_t)(round - 1) & 1u, s_ok);
 }
 
 // ---- The projections ---------------------------------------------------------------------------------------
