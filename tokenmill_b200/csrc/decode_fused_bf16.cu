@@ -455,9 +455,9 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
   constexpr bool PAIR = MODE == FU_QKV;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned char* xrow = xs + (lane >> 2) * row_bytes + (lane & 3) * 16;
-  // With at most 8 tokens only 8 rows are staged; the fragment rows 8..15 then repeat rows 0..7 and feed
-  // accumulator rows nobody reads.
-  const size_t hi_off = a.T > 8 ? (size_t)8 * row_bytes : 0;
+  // Only max(8, T) rows are staged; a fragment row beyond them repeats the row 8 below it and feeds an
+  // accumulator row nobody reads.
+  const size_t hi_off = (lane >> 2) + 8 < a.T ? (size_t)8 * row_bytes : 0;
   for (int j = 0; j < n_mine; ++j) {
     const int u = (int)blockIdx.x + j * (int)gridDim.x;
     if (stage_src && j == 0) {
@@ -506,7 +506,7 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
       auto chunk = [&](int c, float (&da)[4], float (&db)[4]) {
         const uint4 wa = fu_lds128(st + c * kFuChunkBytes);
         const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c0 + c) * 64);
-        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;   // uniform
+        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;
         fu_mma(da, lo.x, hi.x, lo.y, hi.y, wa.x, wa.y);
         fu_mma(da, lo.z, hi.z, lo.w, hi.w, wa.z, wa.w);
         if (PAIR) {
@@ -602,7 +602,7 @@ __device__ __forceinline__ void fu_gate_up(const FusedArgs& a, const FuRing& R, 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t2 = (lane & 3) * 2;
   const unsigned char* xrow = xs + g * row_bytes + (lane & 3) * 16;
-  const size_t hi_off = a.T > 8 ? (size_t)8 * row_bytes : 0;
+  const size_t hi_off = (lane >> 2) + 8 < a.T ? (size_t)8 * row_bytes : 0;
   for (int j = warp; j < R.ng; j += kFuWarps) {
     const int u = (int)blockIdx.x + j * (int)gridDim.x;
     float acc_a[4] = {0.f, 0.f, 0.f, 0.f}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};       // even chunks
@@ -618,7 +618,7 @@ __device__ __forceinline__ void fu_gate_up(const FusedArgs& a, const FuRing& R, 
         const uint4 wa = fu_lds128(st + c * kFuChunkBytes);
         const uint4 wb = fu_lds128(st + (nc + c) * kFuChunkBytes);
         const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c0 + c) * 64);
-        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;   // uniform
+        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;
         fu_mma(da, lo.x, hi.x, lo.y, hi.y, wa.x, wa.y);
         fu_mma(da, lo.z, hi.z, lo.w, hi.w, wa.z, wa.w);
         fu_mma(db, lo.x, hi.x, lo.y, hi.y, wb.x, wb.y);
@@ -952,7 +952,8 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   __shared__ int s_cu_q[17], s_before[16];
   __shared__ int s_slot[kFuWarps][kFuKeyCap];
   const int kmax = max(a.H, max(a.nh * a.D, a.I));
-  const int xs_bytes = (a.T > 8 ? 16 : 8) * fu_row_bytes(kmax);
+  const int rows = a.T > 8 ? a.T : 8;                                 // staged rows
+  const int xs_bytes = rows * fu_row_bytes(kmax);
   const int red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
   unsigned char* xs = smem;                                          // staged inputs; attention's working memory
   float* red = reinterpret_cast<float*>(smem + xs_bytes);            // [8 warps][2 row groups][16][8]
@@ -960,7 +961,6 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   const int ring_off = (work_bytes + 127) / 128 * 128;
   const int nst = min(kFuMaxStages, (a.smem_bytes - ring_off) / a.stage_bytes);
   // The overlay stage lies in the staging area, above what attention and the narrower projections use of it.
-  const int rows = a.T > 8 ? 16 : 8;
   const int ov_off = (max(fu_attn_min_bytes<D>(), rows * max(fu_row_bytes(a.H), fu_row_bytes(a.nh * a.D))) + 127) / 128 * 128;
   const bool ov_fits = ov_off + a.stage_bytes <= xs_bytes;
   FuRing R = fu_ring_setup(a, smem_u32(smem + ring_off), smem_u32(s_full), nst, s_issued,
@@ -1125,7 +1125,7 @@ int launch_decode_fused(const FusedArgs& a, cudaStream_t stream) {
   const int kmax = a.H > a.I ? (a.H > a.nh * a.D ? a.H : a.nh * a.D) : (a.I > a.nh * a.D ? a.I : a.nh * a.D);
   const int kpad = (kmax + 31) / 32 * 32;
   const int row_bytes = kpad * 2 + ((64 - (kpad * 2) % 128) + 128) % 128;
-  const int xs_bytes = (a.T > 8 ? 16 : 8) * row_bytes, red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
+  const int xs_bytes = (a.T > 8 ? a.T : 8) * row_bytes, red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
   const int work_bytes = xs_bytes + red_bytes > fu_attn_min_bytes<D>() ? xs_bytes + red_bytes : fu_attn_min_bytes<D>();
   // A stage holds a row group and its partner over all of H when that fits 32 KB, else 32 KB worth of chunks.
   const int ch_h = (a.H + 31) / 32;
