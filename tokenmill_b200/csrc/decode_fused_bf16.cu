@@ -98,6 +98,7 @@ struct FusedArgs {
   int smem_bytes;                  // dynamic shared memory of the launch (set by the launcher)
   int stage_bytes;                 // bytes of one stage of the weight ring (set by the launcher)
   int l2_prefetch;                 // nonzero: ask for the next layer's weights into L2 during attention
+  int halves;                      // nonzero (set by the launcher): the down projection takes its 9..16 input rows 8 at a time
   unsigned long long* timing;      // null, or [n_layers * 16 + 1] nanosecond stamps written by block 0 (profiling aid)
 };
 
@@ -445,22 +446,29 @@ enum : int { FU_QKV = 0, FU_ADD_RESID = 1 };
 // `stage_src`: null when the block's shared memory already holds the input (the norm wrote it), else the
 // [T, K] bfloat16 matrix other blocks wrote, brought in row by row with bulk copies that complete on
 // `stage_bar` (phase parity `stage_parity`); rows beyond T stay as they are: they only feed accumulator rows
-// nobody reads.
+// nobody reads. `halves` (a block then has at most one unit, and all its tiles fit the ring at once): the
+// input's 9 to 16 rows come in two passes of 8, so that the staging area stays as small as for 8 tokens and
+// the ring keeps its stages; the unit's tiles are read twice and given back in the second pass.
 template <int MODE>
 __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer& L, const FuRing& R,
                                            const FusedLayer* layers, int tile0, int n_mine, int kparts, int cpt,
                                            int n_chunks, int N, int K, const __nv_bfloat16* stage_src,
                                            uint32_t stage_bar, uint32_t stage_parity, unsigned char* xs,
-                                           int row_bytes, float* red, int* s_ok) {
+                                           int row_bytes, float* red, int* s_ok, bool halves = false) {
   constexpr bool PAIR = MODE == FU_QKV;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned char* xrow = xs + (lane >> 2) * row_bytes + (lane & 3) * 16;
   // Only max(8, T) rows are staged; a fragment row beyond them repeats the row 8 below it and feeds an
   // accumulator row nobody reads.
   const size_t hi_off = (lane >> 2) + 8 < a.T ? (size_t)8 * row_bytes : 0;
+  const int n_pass = halves ? 2 : 1;
   for (int j = 0; j < n_mine; ++j) {
     const int u = (int)blockIdx.x + j * (int)gridDim.x;
-    if (stage_src && j == 0) {
+    for (int pass = 0; pass < n_pass; ++pass) {
+    const int tok0 = halves ? 8 * pass : 0;                        // first token of this pass
+    const int n_tok = halves ? min(8, a.T - tok0) : a.T;           // tokens of this pass
+    const size_t hi = halves ? 0 : hi_off;
+    if (stage_src && (j == 0 || halves)) {
       // One bulk copy per token row (warp 0 asks; everybody waits on the staging barrier below). The columns
       // between K and the end of the last chunk are not part of the copy: they are zeroed by hand, since
       // whatever they hold is multiplied (by the packed matrix's zero padding).
@@ -468,16 +476,16 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
       if (warp == 0) {
         if (lane == 0) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier plain accesses to the rows come first
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(stage_bar), "r"(a.T * K * 2) : "memory");
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(stage_bar), "r"(n_tok * K * 2) : "memory");
         }
         __syncwarp();
-        if (lane < a.T)
+        if (lane < n_tok)
           asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                       ::"r"(smem_u32(xs) + lane * row_bytes), "l"(stage_src + (size_t)lane * K), "r"(K * 2), "r"(stage_bar) : "memory");
+                       ::"r"(smem_u32(xs) + lane * row_bytes), "l"(stage_src + (size_t)(tok0 + lane) * K), "r"(K * 2), "r"(stage_bar) : "memory");
       }
       if (kpad != K) {
         const int pieces = (kpad - K) / 8;
-        for (int idx = tid; idx < a.T * pieces; idx += kFuThreads) {
+        for (int idx = tid; idx < n_tok * pieces; idx += kFuThreads) {
           const int r = idx / pieces, pc = idx - r * pieces;
           *reinterpret_cast<uint4*>(xs + (size_t)r * row_bytes + (size_t)(K + pc * 8) * 2) = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -486,9 +494,9 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
     }
     // The residual element this thread will add to, asked for before the products.
     float resid_in = 0.f;
-    if (!PAIR && tid < a.T * 8) {
+    if (!PAIR && tid < n_tok * 8) {
       const int n = u * 8 + (tid & 7);
-      if (n < N) resid_in = __ldcg(a.resid + (size_t)(tid >> 3) * N + n);
+      if (n < N) resid_in = __ldcg(a.resid + (size_t)(tok0 + (tid >> 3)) * N + n);
     }
     // Two accumulator sets per row group, for even and odd chunks: the tensor-core pipeline then has two
     // independent chains to work on; they are added at the end.
@@ -499,20 +507,20 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
       fu_tile_wait(a, R, i, s_ok);
       const int c0 = kp * cpt, nc = min(cpt, n_chunks - c0), per = (nc + kFuWarps - 1) / kFuWarps;
       const int w0 = warp * per, w1 = min(nc, w0 + per);
-      if (stage_src && j == 0 && kp == 0) {                // the staged input is needed only now
-        fu_bar_wait(a, stage_bar, stage_parity, s_ok);
+      if (stage_src && (j == 0 || halves) && kp == 0) {    // the staged input is needed only now
+        fu_bar_wait(a, stage_bar, (stage_parity + (uint32_t)pass) & 1u, s_ok);
       }
       const uint32_t st = R.base + (i % R.nst) * R.stage_bytes + lane * 16;
       auto chunk = [&](int c, float (&da)[4], float (&db)[4]) {
         const uint4 wa = fu_lds128(st + c * kFuChunkBytes);
         const uint4 lo = *reinterpret_cast<const uint4*>(xrow + (c0 + c) * 64);
-        const uint4 hi = hi_off ? *reinterpret_cast<const uint4*>(xrow + hi_off + (c0 + c) * 64) : lo;
-        fu_mma(da, lo.x, hi.x, lo.y, hi.y, wa.x, wa.y);
-        fu_mma(da, lo.z, hi.z, lo.w, hi.w, wa.z, wa.w);
+        const uint4 hv = hi ? *reinterpret_cast<const uint4*>(xrow + hi + (c0 + c) * 64) : lo;
+        fu_mma(da, lo.x, hv.x, lo.y, hv.y, wa.x, wa.y);
+        fu_mma(da, lo.z, hv.z, lo.w, hv.w, wa.z, wa.w);
         if (PAIR) {
           const uint4 wb = fu_lds128(st + (nc + c) * kFuChunkBytes);
-          fu_mma(db, lo.x, hi.x, lo.y, hi.y, wb.x, wb.y);
-          fu_mma(db, lo.z, hi.z, lo.w, hi.w, wb.z, wb.w);
+          fu_mma(db, lo.x, hv.x, lo.y, hv.y, wb.x, wb.y);
+          fu_mma(db, lo.z, hv.z, lo.w, hv.w, wb.z, wb.w);
         }
       };
       int c = w0;
@@ -522,7 +530,7 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
         chunk(c + 1, acc_a2, acc_b2);
       }
       if (c < w1) chunk(c, acc_a, acc_b);
-      if (kp + 1 < kparts) {                               // the stage is free once every warp is through
+      if (kp + 1 < kparts && pass == n_pass - 1) {         // the stage is free once every warp is through
         __syncthreads();
         if (tid == 0) fu_tile_issue(a, R, layers, i + R.nst);
       }
@@ -544,14 +552,14 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
       }
     }
     __syncthreads();
-    if (tid == 0) fu_tile_issue(a, R, layers, tile0 + j * kparts + kparts - 1 + R.nst);
+    if (tid == 0 && pass == n_pass - 1) fu_tile_issue(a, R, layers, tile0 + j * kparts + kparts - 1 + R.nst);
     auto total = [&](int grp, int tok, int f) -> float {
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kFuWarps; ++w) sum += red[(((size_t)w * 2 + grp) * 16 + tok) * 8 + f];
       return sum;
     };
-    for (int idx = tid; idx < a.T * 8; idx += kFuThreads) {
+    for (int idx = tid; idx < n_tok * 8; idx += kFuThreads) {
       const int tok = idx >> 3, f = idx & 7;
       if (MODE == FU_QKV) {
         const int per_head = a.D / 16, half = a.D / 2;
@@ -586,10 +594,12 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
         }
       } else {
         const int n = u * 8 + f;
-        if (n < N) a.resid[(size_t)tok * N + n] = (idx == tid ? resid_in : __ldcg(a.resid + (size_t)tok * N + n)) + total(0, tok, f);
+        const size_t at = (size_t)(tok0 + tok) * N + n;
+        if (n < N) a.resid[at] = (idx == tid ? resid_in : __ldcg(a.resid + at)) + total(0, tok, f);
       }
     }
-    __syncthreads();   // `red` is reused by the next unit
+    __syncthreads();   // `red` (and with `halves` the staged rows) are reused by what follows
+    }
   }
 }
 
@@ -953,7 +963,8 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   __shared__ int s_slot[kFuWarps][kFuKeyCap];
   const int kmax = max(a.H, max(a.nh * a.D, a.I));
   const int rows = a.T > 8 ? a.T : 8;                                 // staged rows
-  const int xs_bytes = rows * fu_row_bytes(kmax);
+  const int xs_bytes = a.halves ? max(8 * fu_row_bytes(kmax), rows * max(fu_row_bytes(a.H), fu_row_bytes(a.nh * a.D)))
+                                : rows * fu_row_bytes(kmax);
   const int red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
   unsigned char* xs = smem;                                          // staged inputs; attention's working memory
   float* red = reinterpret_cast<float*>(smem + xs_bytes);            // [8 warps][2 row groups][16][8]
@@ -1062,8 +1073,8 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     // E: down projection
     fu_project<FU_ADD_RESID>(a, L, R, s_layers, t_down, R.nd, R.kd, R.cpt_single, R.ch_i, a.H, a.I, a.act, stage_bar,
-                             n_staged & 1u, xs, rb_i, red, &s_ok);
-    if (R.nd > 0) ++n_staged;
+                             n_staged & 1u, xs, rb_i, red, &s_ok, a.halves != 0);
+    if (R.nd > 0) n_staged += a.halves ? 2 : 1;
     if (threadIdx.x == 0) fu_overlay_issue(a, R, s_layers, l + 1);   // the staging area has been read: it is free again
     if (R.ov_base && l + 1 < a.n_layers) ov_issued = l + 2;
     fu_stamp(a, l * 16 + 9);
@@ -1119,38 +1130,54 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   }
 }
 
+static int fu_host_row_bytes(int K) {           // fu_row_bytes for the host
+  const int kpad = (K + 31) / 32 * 32;
+  return kpad * 2 + ((64 - (kpad * 2) % 128) + 128) % 128;
+}
+
 template <int D>
 int launch_decode_fused(const FusedArgs& a, cudaStream_t stream) {
   auto kern = decode_fused_kernel<D>;
-  const int kmax = a.H > a.I ? (a.H > a.nh * a.D ? a.H : a.nh * a.D) : (a.I > a.nh * a.D ? a.I : a.nh * a.D);
-  const int kpad = (kmax + 31) / 32 * 32;
-  const int row_bytes = kpad * 2 + ((64 - (kpad * 2) % 128) + 128) % 128;
-  const int xs_bytes = (a.T > 8 ? a.T : 8) * row_bytes, red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
-  const int work_bytes = xs_bytes + red_bytes > fu_attn_min_bytes<D>() ? xs_bytes + red_bytes : fu_attn_min_bytes<D>();
-  // A stage holds a row group and its partner over all of H when that fits 32 KB, else 32 KB worth of chunks.
-  const int ch_h = (a.H + 31) / 32;
-  const int stage_bytes = 2 * ch_h * 512 <= 32768 ? 2 * ch_h * 512 : 32768;
-  const int smem = 212 * 1024;
-  const int ring_off = (work_bytes + 127) / 128 * 128;
-  if (ring_off + stage_bytes > smem || a.n_layers > kFuMaxLayers) return TM_ERR_UNSUPPORTED_SHAPE;
-  static int n_sm = 0, per_sm = 0, smem_set = 0;
-  if (smem > smem_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    smem_set = smem;
-    per_sm = 0;
-  }
-  if (!per_sm) {
+  constexpr int smem = 212 * 1024;
+  static int n_sm = 0, per_sm = 0;
+  if (!n_sm) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kFuThreads, smem);
-    if (e != cudaSuccess) return (int)e;
-    if (per_sm < 1) return TM_ERR_UNSUPPORTED_SHAPE;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kFuThreads, smem);
+    if (e != cudaSuccess || per_sm < 1) {
+      n_sm = 0;
+      return e != cudaSuccess ? (int)e : TM_ERR_UNSUPPORTED_SHAPE;
+    }
   }
+  const int rb_h = fu_host_row_bytes(a.H), rb_q = fu_host_row_bytes(a.nh * a.D), rb_i = fu_host_row_bytes(a.I);
+  const int rb_narrow = rb_h > rb_q ? rb_h : rb_q, rb_max = rb_narrow > rb_i ? rb_narrow : rb_i;
+  const int red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
+  // A stage holds a row group and its partner over all of H when that fits 32 KB, else 32 KB worth of chunks.
+  const int ch_h = (a.H + 31) / 32;
+  const int stage_bytes = 2 * ch_h * 512 <= 32768 ? 2 * ch_h * 512 : 32768;
+  auto ring_offset = [&](int xs_bytes) {      // the staging area doubles as attention's working memory
+    const int work = xs_bytes + red_bytes > fu_attn_min_bytes<D>() ? xs_bytes + red_bytes : fu_attn_min_bytes<D>();
+    return (work + 127) / 128 * 128;
+  };
+  const int rows = a.T > 8 ? a.T : 8;
+  // Steps of 9 to 16 tokens: the down projection's input (T rows of I columns) would take the room of most
+  // ring stages. Where every block has at most one down-projection unit and the unit's tiles all fit the ring
+  // at once, the input comes in two passes of 8 rows instead and the staging area stays as for 8 tokens.
+  const int xs_halves = 8 * rb_max > rows * rb_narrow ? 8 * rb_max : rows * rb_narrow;
+  int nst_halves = (smem - ring_offset(xs_halves)) / stage_bytes;
+  if (nst_halves > kFuMaxStages) nst_halves = kFuMaxStages;
+  const int cpt_single = stage_bytes / 512, kd = ((a.I + 31) / 32 + cpt_single - 1) / cpt_single;
+  const int nst_rows = (smem - ring_offset(rows * rb_max)) / stage_bytes;
+  // (Measured at the 0.5B sizes: with two or more stages left, staging all rows in one pass is as fast or faster.)
+  const bool halves = a.T > 8 && nst_rows <= 1 && (a.H + 7) / 8 <= n_sm && kd <= nst_halves;
+  const int xs_bytes = halves ? xs_halves : rows * rb_max;
+  if (ring_offset(xs_bytes) + stage_bytes > smem || a.n_layers > kFuMaxLayers) return TM_ERR_UNSUPPORTED_SHAPE;
   FusedArgs args = a;
   args.smem_bytes = smem;
   args.stage_bytes = stage_bytes;
+  args.halves = halves ? 1 : 0;
   void* params[] = {&args};
   return (int)cudaLaunchCooperativeKernel((void*)kern, dim3(n_sm), dim3(kFuThreads), params, (size_t)smem, stream);
 }

@@ -43,7 +43,8 @@ class _Args(ctypes.Structure):
         + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
         + [(n, c_void_p) for n in ("resid", "q", "part_acc", "part_ml", "attn", "act", "attn_count", "bar",
                                    "error", "hidden_out")]
-        + [("smem_bytes", c_int), ("stage_bytes", c_int), ("l2_prefetch", c_int), ("timing", c_void_p)]
+        + [("smem_bytes", c_int), ("stage_bytes", c_int), ("l2_prefetch", c_int), ("halves", c_int),
+           ("timing", c_void_p)]
     )
 
 
