@@ -97,7 +97,6 @@ struct FusedArgs {
   __nv_bfloat16* hidden_out;       // [n_want, H]
   int smem_bytes;                  // dynamic shared memory of the launch (set by the launcher)
   int stage_bytes;                 // bytes of one stage of the weight ring (set by the launcher)
-  int l2_prefetch;                 // nonzero: ask for the next layer's weights into L2 during attention
   int halves;                      // nonzero (set by the launcher): the down projection takes its 9..16 input rows 8 at a time
   unsigned long long* timing;      // null, or [n_layers * 16 + 1] nanosecond stamps written by block 0 (profiling aid)
 };
@@ -118,21 +117,6 @@ __device__ __forceinline__ void fu_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Ask for `bytes` at `base` to be brought into L2 (no completion to wait for): the whole grid shares the
-// range in 4 KB pieces, one instruction per piece. The ring's stages hold a fraction of what two phases
-// multiply back to back; what lets the copies into the stages keep up is that the weights of the next
-// phases were pulled from HBM into L2 earlier, while the memory system was idle.
-__device__ __forceinline__ void fu_prefetch_l2(const void* base, size_t bytes) {
-  if (!base || (reinterpret_cast<uintptr_t>(base) & 15)) return;
-  constexpr size_t kPiece = 4096;
-  const size_t n_pieces = (bytes + kPiece - 1) / kPiece;
-  for (size_t p = blockIdx.x + (size_t)threadIdx.x * gridDim.x; p < n_pieces; p += (size_t)gridDim.x * kFuThreads) {
-    const size_t off = p * kPiece;
-    const uint32_t sz = (uint32_t)((bytes - off < kPiece ? bytes - off : kPiece) & ~(size_t)15);
-    if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(base) + off), "r"(sz) : "memory");
-  }
-}
-
 __device__ __forceinline__ uint4 fu_lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -148,6 +132,14 @@ constexpr int kFuChunkElems = 32 * 8;
 constexpr int kFuChunkBytes = 512;
 __device__ __forceinline__ const __nv_bfloat16* fu_packed_group(const __nv_bfloat16* W, int row0, int n_chunks, int chunk) {
   return W + ((size_t)(row0 >> 3) * n_chunks + chunk) * kFuChunkElems;
+}
+
+// Where element d of a query row lies in the kernel's own q buffer: lane 4 g + t of the attention phase reads, for
+// every 16-wide step ks of the head dimension, elements 16 ks + 2 t + {0, 1, 8, 9} of its rows; they are stored
+// as t's block [ks][0, 1, 8, 9], so that a lane's fragments of a row are D / 4 contiguous elements.
+__device__ __forceinline__ int fu_q_index(int d, int D) {
+  const int ks = d >> 4, rem = d & 15;
+  return ((rem & 7) >> 1) * (D / 4) + ks * 4 + (rem >> 3) * 2 + (rem & 1);
 }
 
 __device__ __forceinline__ int fu_row_bytes(int K) {
@@ -580,7 +572,10 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
         }
         __nv_bfloat16* dst = nullptr;
         if (head < a.nh) {
-          dst = a.q + ((size_t)tok * a.nh + head) * a.D;
+          // q goes to the attention phase in the order its tensor-core fragments are read (fu_q_index)
+          __nv_bfloat16* qrow = a.q + ((size_t)tok * a.nh + head) * a.D;
+          qrow[fu_q_index(i, a.D)] = __float2bfloat16_rn(o1);
+          qrow[fu_q_index(i + half, a.D)] = __float2bfloat16_rn(o2);
         } else {
           const int slot = a.slot_map[tok];
           if (slot >= 0) {
@@ -732,21 +727,6 @@ __device__ __forceinline__ void fu_attention(const FusedArgs& a, const FusedLaye
     const int w_lo = t.j_lo + warp * t.kpw, w_hi = min(t.j_hi, w_lo + t.kpw - 1);
     const bool cached = u == (int)blockIdx.x;            // the launch-time slot table covers the first unit
 
-    uint32_t qa[KS][4];
-    {
-      const __nv_bfloat16* qr0 = nullptr;
-      const __nv_bfloat16* qr1 = nullptr;
-      if (r0 < t.n_rows) qr0 = a.q + ((size_t)(t.q_start + r0 / G) * a.nh + t.kvh * G + r0 % G) * D;
-      if (r1 < t.n_rows) qr1 = a.q + ((size_t)(t.q_start + r1 / G) * a.nh + t.kvh * G + r1 % G) * D;
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        const int c = ks * 16 + cpair;
-        qa[ks][0] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c)) : 0u;
-        qa[ks][1] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c)) : 0u;
-        qa[ks][2] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c + 8)) : 0u;
-        qa[ks][3] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c + 8)) : 0u;
-      }
-    }
     const int p_r0 = r0 < t.n_rows ? t.before + r0 / G : -1, p_r1 = r1 < t.n_rows ? t.before + r1 / G : -1;
     const int lo_r0 = a.window > 0 ? max(0, p_r0 - a.window + 1) : 0;
     const int lo_r1 = a.window > 0 ? max(0, p_r1 - a.window + 1) : 0;
@@ -755,6 +735,8 @@ __device__ __forceinline__ void fu_attention(const FusedArgs& a, const FusedLaye
 #pragma unroll
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
+    uint32_t qa[KS][4];
+    bool q_loaded = false;
     for (int kb = w_lo; kb <= w_hi; kb += cap) {         // rounds: usually one
       const int nk = min(cap, w_hi - kb + 1);
       const int nk16 = (nk + 15) / 16 * 16;
@@ -770,6 +752,23 @@ __device__ __forceinline__ void fu_attention(const FusedArgs& a, const FusedLaye
       }
       cp_async_commit();
       if (u == (int)blockIdx.x) fu_stamp(a, layer * 16 + 10);
+      if (!q_loaded) {                                     // the query fragments: asked for behind the copies, needed after them
+        q_loaded = true;
+        const int t4 = (lane & 3) * (D / 4);                 // this lane's block of a (permuted) query row
+        const uint4* qr0 = nullptr;
+        const uint4* qr1 = nullptr;
+        if (r0 < t.n_rows)
+          qr0 = reinterpret_cast<const uint4*>(a.q + ((size_t)(t.q_start + r0 / G) * a.nh + t.kvh * G + r0 % G) * D + t4);
+        if (r1 < t.n_rows)
+          qr1 = reinterpret_cast<const uint4*>(a.q + ((size_t)(t.q_start + r1 / G) * a.nh + t.kvh * G + r1 % G) * D + t4);
+#pragma unroll
+        for (int kk = 0; kk < KS / 2; ++kk) {                // 16 bytes hold two steps: [ks][0,1 | 8,9]
+          const uint4 v0 = qr0 ? __ldcg(qr0 + kk) : make_uint4(0u, 0u, 0u, 0u);
+          const uint4 v1 = qr1 ? __ldcg(qr1 + kk) : make_uint4(0u, 0u, 0u, 0u);
+          qa[2 * kk][0] = v0.x; qa[2 * kk][2] = v0.y; qa[2 * kk + 1][0] = v0.z; qa[2 * kk + 1][2] = v0.w;
+          qa[2 * kk][1] = v1.x; qa[2 * kk][3] = v1.y; qa[2 * kk + 1][1] = v1.z; qa[2 * kk + 1][3] = v1.w;
+        }
+      }
       cp_async_wait<0>();
       __syncwarp();
       if (u == (int)blockIdx.x) fu_stamp(a, layer * 16 + 11);
@@ -1018,7 +1017,6 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   }
   __syncthreads();
 
-  auto packed_bytes = [](int n, int kk) { return (size_t)((n + 7) / 8 * 8) * ((kk + 31) / 32 * 32) * 2; };
   for (int l = 0; l < a.n_layers && ok; ++l) {
     const FusedLayer& L = s_layers[l];
     const int t_qkv = l * R.per_layer, t_o = t_qkv + R.nq * R.kq, t_gu = t_o + R.no * R.ko, t_down = t_gu + R.ng_ring * R.kg;
@@ -1045,15 +1043,7 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
     fu_stamp(a, l * 16 + 2);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     fu_stamp(a, l * 16 + 3);
-    // B: attention (its working memory is the staging area; the ring's stages stay untouched). The memory
-    // system has little to do meanwhile: the next layer's weights are asked into L2 now.
-    if (a.l2_prefetch && l + 1 < a.n_layers) {
-      const FusedLayer& Ln = s_layers[l + 1];
-      fu_prefetch_l2(Ln.w_qkv, packed_bytes((a.nh + 2 * a.nkv) * a.D, a.H));
-      fu_prefetch_l2(Ln.w_o, packed_bytes(a.H, a.nh * a.D));
-      fu_prefetch_l2(Ln.w_gu, packed_bytes(2 * a.I, a.H));
-      fu_prefetch_l2(Ln.w_down, packed_bytes(a.H, a.I));
-    }
+    // B: attention (its working memory is the staging area; the ring's stages stay untouched)
     fu_attention<D>(a, L, xs, attn_bytes, s_cu_q, s_before, s_slot, l);
     fu_stamp(a, l * 16 + 4);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;

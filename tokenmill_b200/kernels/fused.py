@@ -43,7 +43,7 @@ class _Args(ctypes.Structure):
         + [(n, c_int) for n in ("T", "S", "n_want", "page_size", "split_keys", "max_splits")]
         + [(n, c_void_p) for n in ("resid", "q", "part_acc", "part_ml", "attn", "act", "attn_count", "bar",
                                    "error", "hidden_out")]
-        + [("smem_bytes", c_int), ("stage_bytes", c_int), ("l2_prefetch", c_int), ("halves", c_int),
+        + [("smem_bytes", c_int), ("stage_bytes", c_int), ("halves", c_int),
            ("timing", c_void_p)]
     )
 
@@ -149,7 +149,6 @@ class FusedDecoder:
         a.act = self.act.data_ptr()
         a.attn_count, a.bar, a.error = self.attn_count.data_ptr(), self.bar.data_ptr(), self.error.data_ptr()
         a.hidden_out = self.hidden.data_ptr()
-        a.l2_prefetch = int(os.environ.get("TOKENMILL_FUSED_L2_PREFETCH", "0") != "0")   # measured: not worth it
         self._args = a
         self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
         self.max_model_len = max_model_len
