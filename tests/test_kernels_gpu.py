@@ -202,7 +202,7 @@ def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
     part_acc = torch.full((T * nh * max_splits * D,), float("nan"), device=DEV)
     part_ml = torch.full((T * nh * max_splits * 2,), float("nan"), device=DEV)
     out = torch.empty_like(c["q"])
-    ops.decode_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["seq_of"], len(q_lens), out,
+    ops.decode_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], len(q_lens), out,
                               scale=D ** -0.5, window=window, split_keys=256, max_splits=max_splits,
                               part_acc=part_acc, part_ml=part_ml)
     diff = (out.float().cpu() - c["ref"]).abs().max()

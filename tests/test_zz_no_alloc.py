@@ -48,7 +48,7 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row(nh, nkv, D,
         ordinary = torch.empty_like(c["q"])
         part_acc = torch.empty(T * nh * max_splits * D, device=DEV)
         part_ml = torch.empty(T * nh * max_splits * 2, device=DEV)
-        ops.decode_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], c["seq_of"], T, ordinary,
+        ops.decode_attention_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], T, ordinary,
                                   scale=D ** -0.5, window=window, split_keys=256, max_splits=max_splits,
                                   part_acc=part_acc, part_ml=part_ml)
         out = torch.full_like(c["q"], float("nan"))

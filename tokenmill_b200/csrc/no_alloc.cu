@@ -4,26 +4,28 @@
 #include "common.cuh"
 
 // The partial results of split-key attention live here instead of in caller- or allocator-provided
-// memory. In host code this name is only a stand-in for the device array: its device address has to be
-// asked for (cudaGetSymbolAddress) and is what the kernels receive.
+// memory, and so do the arrival counters by which the last block of a (request, kv head) knows to merge
+// them (zero in the image, left zero by every launch). In host code these names are only stand-ins for the
+// device arrays: their device addresses have to be asked for (cudaGetSymbolAddress) and are what the kernel
+// receives.
 static __device__ __align__(256) float tm_noalloc_scratch[TM_NOALLOC_SCRATCH_FLOATS];
+constexpr int kNoallocCounters = 4096;
+static __device__ int tm_noalloc_done[kNoallocCounters];
 
 extern "C" int tm_decode_attention_bf16(const void* q, const void* kcache, const void* vcache,
                                         const int* block_table, int bt_stride, const int* cu_q,
-                                        const int* kv_before, int n_seqs, float* part_acc, float* part_ml, int nh,
-                                        int nkv, int D, int page_size, float scale, int window, int split_keys,
-                                        int max_splits, cudaStream_t stream);
-extern "C" int tm_attention_combine(int dtype, const float* part_acc, const float* part_ml, const int* cu_q,
-                                    const int* kv_before, const int* seq_of_token, void* out, int n_tokens, int nh,
-                                    int D, int window, int split_keys, int max_splits, cudaStream_t stream);
+                                        const int* kv_before, int n_seqs, float* part_acc, float* part_ml,
+                                        void* out, int* done, int nh, int nkv, int D, int page_size, float scale,
+                                        int window, int split_keys, int max_splits, cudaStream_t stream);
 
 namespace {
 
 constexpr int kMaxDevices = 64;
 float* g_scratch[kMaxDevices] = {};   // device address of tm_noalloc_scratch, per device, once looked up
+int* g_done[kMaxDevices] = {};        // and of tm_noalloc_done
 
-// The array's address on the current device. The first call per device does the look-up.
-int scratch_for_current_device(float** ptr) {
+// The arrays' addresses on the current device. The first call per device does the look-up.
+int scratch_for_current_device(float** ptr, int** done) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -32,9 +34,14 @@ int scratch_for_current_device(float** ptr) {
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, tm_noalloc_scratch);
     if (e != cudaSuccess) return (int)e;
+    int* d = nullptr;
+    e = cudaGetSymbolAddress((void**)&d, tm_noalloc_done);
+    if (e != cudaSuccess) return (int)e;
+    g_done[dev] = d;
     g_scratch[dev] = p;
   }
   *ptr = g_scratch[dev];
+  *done = g_done[dev];
   return 0;
 }
 
@@ -47,17 +54,18 @@ extern "C" int tm_decode_attention_bf16_noalloc(const void* q, const void* kcach
                                                 float scale, int window, int split_keys, int max_splits,
                                                 cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (nh <= 0 || D <= 0 || max_splits <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (nh <= 0 || nkv <= 0 || D <= 0 || max_splits <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  (void)seq_of_token;                         // (kept in the signature; the merge no longer needs it)
   const long long rows = (long long)n_tokens * nh * max_splits;
-  if (rows * (D + 2) > (long long)TM_NOALLOC_SCRATCH_FLOATS) return TM_ERR_NOALLOC_TOO_LARGE;
+  if (rows * (D + 2) > (long long)TM_NOALLOC_SCRATCH_FLOATS || (long long)n_seqs * nkv > kNoallocCounters)
+    return TM_ERR_NOALLOC_TOO_LARGE;
   float* scratch = nullptr;
-  int status = scratch_for_current_device(&scratch);
+  int* done = nullptr;
+  const int status = scratch_for_current_device(&scratch, &done);
   if (status != 0) return status;
   float* part_acc = scratch;                  // [rows, D]
   float* part_ml = scratch + rows * D;        // [rows, 2]
-  status = tm_decode_attention_bf16(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before, n_seqs, part_acc,
-                                    part_ml, nh, nkv, D, page_size, scale, window, split_keys, max_splits, stream);
-  if (status != 0) return status;
-  return tm_attention_combine(TM_DTYPE_BF16, part_acc, part_ml, cu_q, kv_before, seq_of_token, out, n_tokens, nh, D,
-                              window, split_keys, max_splits, stream);
+  return tm_decode_attention_bf16(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before, n_seqs, part_acc,
+                                  part_ml, out, done, nh, nkv, D, page_size, scale, window, split_keys, max_splits,
+                                  stream);
 }

@@ -8,21 +8,24 @@
 // synchronise the whole device. Such callers can still pass their own inputs and outputs, but they have
 // nowhere to get the scratch that split-key decode attention needs for its partial results.
 //
-// tm_decode_attention_bf16_noalloc is the decode attention of tm_decode_attention_bf16 followed by
-// tm_attention_combine, with the partial results kept in a fixed array that is part of the library image
-// itself (TM_NOALLOC_SCRATCH_FLOATS floats, 8 MiB; every GPU that loads the library holds it until the
-// process exits). It calls no cudaMalloc, cudaFree or allocating library routine.
+// tm_decode_attention_bf16_noalloc is the decode attention of tm_decode_attention_bf16 (its last block per
+// request and kv head merges the key splits), with the partial results and the arrival counters kept in fixed
+// arrays that are part of the library image itself (TM_NOALLOC_SCRATCH_FLOATS floats, 8 MiB, and 4,096
+// counters; every GPU that loads the library holds them until the process exits). It calls no cudaMalloc,
+// cudaFree or allocating library routine.
 //
 // Rules for the caller:
 //  * Sizes: T * nh * max_splits * (D + 2) floats must fit the array (T = tokens in the step, nh = query
-//    heads, D = head size); larger steps are refused with TM_ERR_NOALLOC_TOO_LARGE (90004) before anything
-//    is launched. Batch 64, 14 heads of 64, contexts up to 4096 (16 splits of 256 keys) need 0.95 M floats.
+//    heads, D = head size), and requests x kv heads the 4,096 counters; larger steps are refused with
+//    TM_ERR_NOALLOC_TOO_LARGE (90004) before anything is launched. Batch 64, 14 heads of 64, contexts up to
+//    4096 (16 splits of 256 keys) need 0.95 M floats.
 //  * First call on a device: it looks up the array's device address once (cudaGetSymbolAddress, with that
 //    device current) and remembers it. Make that first call outside any stream capture.
-//  * The array is shared by every call and keeps the last call's contents. Nothing in it has to start at
-//    zero (each call writes every partial it later reads), but two calls that overlap on the GPU (different
-//    streams, or one call racing a graph replay that contains another) would write the same floats: keep
-//    calls to this entry point ordered on one stream.
+//  * The arrays are shared by every call. The floats keep the last call's contents and need not start at
+//    zero (each call writes every partial it later reads); the counters are zero in the image and every call
+//    leaves them zero. Two calls that overlap on the GPU (different streams, or one call racing a graph
+//    replay that contains another) would write the same floats and counters: keep calls to this entry point
+//    ordered on one stream.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -35,7 +38,7 @@ extern "C" {
 #endif
 
 // q, out [T, nh, D] bfloat16; kcache, vcache [pages, page_size, nkv, D] bfloat16; block_table [n_seqs,
-// bt_stride] int; cu_q [n_seqs + 1]; kv_before [n_seqs]; seq_of_token [T]. Each request brings at most
+// bt_stride] int; cu_q [n_seqs + 1]; kv_before [n_seqs]; seq_of_token [T] (unused, kept for callers). Each request brings at most
 // 16 / (nh / nkv) tokens; D is 64 or 128; split_keys a multiple of 64. Returns 0, a TM_ERR_* code, or a
 // cudaError_t.
 int tm_decode_attention_bf16_noalloc(const void* q, const void* kcache, const void* vcache,

@@ -120,11 +120,13 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
 
 
 def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
-                          cu_q: torch.Tensor, kv_before: torch.Tensor, seq_of_token: torch.Tensor, n_seqs: int,
-                          out: torch.Tensor, *, scale: float, window: int, split_keys: int, max_splits: int,
-                          part_acc: torch.Tensor, part_ml: torch.Tensor) -> torch.Tensor:
+                          cu_q: torch.Tensor, kv_before: torch.Tensor, n_seqs: int, out: torch.Tensor, *, scale: float,
+                          window: int, split_keys: int, max_splits: int, part_acc: torch.Tensor, part_ml: torch.Tensor,
+                          done: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core attention for steps whose requests bring at most 16 / (nh / nkv) tokens each
-    (decoding). bfloat16, head size 64 or 128; partials through part_acc / part_ml, then combined."""
+    (decoding). bfloat16, head size 64 or 128; per-split partials through part_acc / part_ml, merged by the
+    last block of each (request, kv head); ``done``: n_seqs * kv_heads int32 zeros (left zero), made here when
+    not given."""
     T, nh, D = q.shape
     page_size, nkv = kcache.shape[1], kcache.shape[2]
     bf = torch.bfloat16
@@ -133,14 +135,15 @@ def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
         raise lib.KernelError("decode_attention_bf16: scratch too small")
     if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
         raise lib.KernelError("decode_attention_bf16: q / cache / out shapes disagree")
+    if done is None:
+        done = torch.zeros(n_seqs * nkv, dtype=torch.int32, device=q.device)
+    elif done.numel() < n_seqs * nkv:
+        raise lib.KernelError("decode_attention_bf16: too few arrival counters")
     lib.call("tm_decode_attention_bf16", _req(q, "q", bf), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf),
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
              _req(kv_before, "kv_before", torch.int32), n_seqs, _req(part_acc, "part_acc", torch.float32),
-             _req(part_ml, "part_ml", torch.float32), nh, nkv, D, page_size, float(scale), int(window),
-             int(split_keys), int(max_splits), _stream())
-    lib.call("tm_attention_combine", BF16, part_acc.data_ptr(), part_ml.data_ptr(), cu_q.data_ptr(),
-             kv_before.data_ptr(), _req(seq_of_token, "seq_of_token", torch.int32), _req(out, "out", bf), T, nh, D,
-             int(window), int(split_keys), int(max_splits), _stream())
+             _req(part_ml, "part_ml", torch.float32), _req(out, "out", bf), _req(done, "done", torch.int32), nh, nkv, D,
+             page_size, float(scale), int(window), int(split_keys), int(max_splits), _stream())
     return out
 
 

@@ -31,6 +31,7 @@ class AttentionScratch:
         self.device = device
         self.part_acc: torch.Tensor | None = None
         self.part_ml: torch.Tensor | None = None
+        self.done: torch.Tensor | None = None     # zero between launches
         self.frozen = False      # set once a graph has captured the pointers
         self._counters: torch.Tensor | None = None
         self._pf_acc: torch.Tensor | None = None
@@ -51,6 +52,10 @@ class AttentionScratch:
                 raise RuntimeError("attention scratch would have to grow after a graph captured it")
             self.part_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
             self.part_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
+        if self.done is None or self.done.numel() < rows:     # arrival counters, one per (request, kv head) at most
+            if self.frozen:
+                raise RuntimeError("attention scratch would have to grow after a graph captured it")
+            self.done = torch.zeros(rows, dtype=torch.int32, device=self.device)
 
     def get(self, rows: int, max_splits: int, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
         self.reserve(rows, max_splits, head_dim)
@@ -158,9 +163,9 @@ class GroupedQueryAttention:
         if step.split_keys and rows <= 16 and self.dtype == torch.bfloat16 and self.D in (64, 128):
             part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, step.max_splits, self.D)
             ops.decode_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
-                                      step.kv_before, step.seq_of_token, step.n_seqs, out, scale=self.scale,
-                                      window=self.window, split_keys=step.split_keys, max_splits=step.max_splits,
-                                      part_acc=part_acc, part_ml=part_ml)
+                                      step.kv_before, step.n_seqs, out, scale=self.scale, window=self.window,
+                                      split_keys=step.split_keys, max_splits=step.max_splits, part_acc=part_acc,
+                                      part_ml=part_ml, done=step.scratch.done)
             return
         if self.dtype == torch.bfloat16 and self.D in (64, 128) and G in step.prefill:
             units = step.prefill[G]                # 64-row tiles cut into key chunks, heaviest first
