@@ -217,6 +217,34 @@ def test_command_line_generates(tiny_a_dir):
     assert rows[0]["output_ids"] == plain_greedy(cfg, w, [5, 6, 7], 5)
 
 
+@pytest.mark.parametrize("switch", ["1", "0"])
+def test_prompt_attention_kernel_choice(tmp_path, monkeypatch, plain_cache, switch):
+    """Heads of 64 in bfloat16 take the tcgen05 prompt-attention kernel (128-row tiles), and the mma.sync one
+    when TOKENMILL_TC_ATTENTION=0; both agree with the plain implementation, also on portions cut anywhere and
+    beside another request's decoded tokens."""
+    from tokenmill_b200.kernels import lib
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    cfg = qwen2_config(vocab_size=300, hidden_size=192, intermediate_size=264, num_hidden_layers=2,
+                       num_attention_heads=3, num_key_value_heads=1, rope_theta=10000.0, tie_word_embeddings=False,
+                       max_position_embeddings=1024)
+    folder = write_random_model(tmp_path / "m", cfg, seed=6)
+    monkeypatch.setenv("TOKENMILL_TC_ATTENTION", switch)
+    calls = []
+    real = lib.call
+    monkeypatch.setattr(lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    reqs = make_requests(300, [340, 150], seed=9)
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": reqs["r0"][:297], "want": list(range(0, 297, 5))}], "end": []},
+             {"step": 1, "entries": [{"id": "r1", "tokens": reqs["r1"][:149], "want": [0, 148]},
+                                     {"id": "r0", "tokens": reqs["r0"][297:299], "want": [0, 1]}], "end": []},
+             {"step": 2, "entries": [{"id": "r0", "tokens": reqs["r0"][299:], "want": list(range(41))},
+                                     {"id": "r1", "tokens": reqs["r1"][149:], "want": [0]}], "end": ["r0", "r1"]}]
+    outputs = run_trace(folder, "bfloat16", steps, 512, tmp_path / "o")
+    check_against_plain(steps, outputs, reqs, plain_for(folder, reqs, plain_cache), "bfloat16")
+    used = "tm_prefill_attention_tc_bf16" if switch == "1" else "tm_prefill_attention_bf16"
+    other = "tm_prefill_attention_bf16" if switch == "1" else "tm_prefill_attention_tc_bf16"
+    assert used in calls and other not in calls
+
+
 def test_prompt_products_on_tcgen05_when_switched_on(tmp_path, monkeypatch, plain_cache):
     """With TOKENMILL_TC_GEMM on, prompt steps of 128 tokens or more run the fused q/k/v projection, the
     gate/up projection with its SwiGLU epilogue and the down projection on the tcgen05 kernel; logits stay

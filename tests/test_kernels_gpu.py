@@ -243,6 +243,65 @@ def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
             assert counters.tolist() == [0, 0] and int(tile_done.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,page,window", [(14, 2, 16, 0), (3, 3, 1, 0), (8, 1, 7, 0), (14, 2, 16, 70), (4, 2, 8, 1)])
+def test_prefill_attention_tcgen05_kernel(nh, nkv, page, window):
+    """The tcgen05 prompt kernel (heads of 64, 128-row tiles, scores and outputs in tensor memory): whole
+    prompts, later portions that start off a tile or page edge, short portions and single tokens in the same
+    launch; tiles that end inside a key block; key chunks so short that most tiles have several; windows."""
+    from tokenmill_b200.engine.batch import packed_units
+    from tokenmill_b200.parts.base import PrefillUnits
+    import numpy as np
+    ops = _ops()
+    D = 64
+    q_lens, befores = [200, 1, 64, 3, 129, 65, 17, 300], [0, 300, 64, 5, 77, 191, 1000, 131]
+    c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=nh + window,
+                    window=window)
+    G = nh // nkv
+    counters = torch.zeros(2, dtype=torch.int32, device=DEV)
+    for chunk in (512, 128, 256):
+        rec, n_tiles, n_slots = packed_units(np.array(q_lens, dtype=np.int32), np.array(befores, dtype=np.int32), G,
+                                             tile=128, chunk=chunk)
+        assert n_tiles == sum(-(-n * G // 128) for n in q_lens)
+        units = PrefillUnits(torch.from_numpy(rec).to(DEV), len(rec), n_tiles, n_slots, chunk, 128)
+        part_acc = torch.full((max(1, n_slots) * nkv * 128 * D,), float("nan"), dtype=torch.float32, device=DEV)
+        part_ml = torch.full((max(1, n_slots) * nkv * 128 * 2,), float("nan"), dtype=torch.float32, device=DEV)
+        tile_done = torch.zeros(n_tiles * nkv, dtype=torch.int32, device=DEV)
+        for _ in range(2):                                          # the second launch finds the counters at zero
+            out = torch.full_like(c["q"], float("nan"))
+            ops.prefill_attention_tc_bf16(c["q"], c["kc"], c["vc"], c["table"], units, counters, out, scale=D ** -0.5,
+                                          window=window, part_acc=part_acc, part_ml=part_ml, tile_done=tile_done)
+            ops.tc_check(torch.device(DEV))
+            diff = (out.float().cpu() - c["ref"]).abs().max()
+            assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), (chunk, diff)
+            assert counters.tolist() == [0, 0] and int(tile_done.abs().sum()) == 0
+
+
+def test_prefill_attention_tcgen05_kernel_merges_more_chunks_than_fit_shared_memory():
+    """A row tile whose keys make so many chunks (57 of 128 keys) that not even 8 rows of all of them fit in
+    shared memory is merged piece by piece from the L2 instead; a tile with 29 chunks takes several passes."""
+    from tokenmill_b200.engine.batch import packed_units
+    from tokenmill_b200.parts.base import PrefillUnits
+    import numpy as np
+    ops = _ops()
+    nh, nkv, D, page = 2, 1, 64, 32
+    q_lens, befores = [3, 70], [7290, 3600]
+    c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=11)
+    counters = torch.zeros(2, dtype=torch.int32, device=DEV)
+    rec, n_tiles, n_slots = packed_units(np.array(q_lens, dtype=np.int32), np.array(befores, dtype=np.int32), nh // nkv,
+                                         tile=128, chunk=128)
+    assert (rec[:, 2] >> 16).max() >= 57
+    units = PrefillUnits(torch.from_numpy(rec).to(DEV), len(rec), n_tiles, n_slots, 128, 128)
+    part_acc = torch.full((n_slots * nkv * 128 * D,), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((n_slots * nkv * 128 * 2,), float("nan"), dtype=torch.float32, device=DEV)
+    tile_done = torch.zeros(n_tiles * nkv, dtype=torch.int32, device=DEV)
+    out = torch.full_like(c["q"], float("nan"))
+    ops.prefill_attention_tc_bf16(c["q"], c["kc"], c["vc"], c["table"], units, counters, out, scale=D ** -0.5,
+                                  part_acc=part_acc, part_ml=part_ml, tile_done=tile_done)
+    ops.tc_check(torch.device(DEV))
+    diff = (out.float().cpu() - c["ref"]).abs().max()
+    assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 32, 33, 100])
 def test_paged_attention_window_edge(dtype, window):

@@ -26,6 +26,7 @@
 // This is the mma.sync ("legacy tensor core") formulation; it reaches a fraction of what a tcgen05
 // kernel with the accumulators in tensor memory would, and is the stand-in until that kernel exists.
 #include "mma_util.cuh"
+#include "attention_merge.cuh"
 
 namespace tmk {
 
@@ -300,31 +301,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_bf16_kernel(
       __syncthreads();
       if (s_ticket == n_chunks - 1) {
         __threadfence();
-        for (int idx = tid; idx < n_rows * (D / 4); idx += THREADS) {
-          const int r = idx / (D / 4), d = (idx - r * (D / 4)) * 4;
-          float mx = -INFINITY, lsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-          for (int c = 0; c < n_chunks; ++c) {
-            const size_t prow = ((size_t)(slot0 + c) * nkv + kvh) * kPfBM + r;
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + prow * 2));
-            const float4 pa = __ldcg(reinterpret_cast<const float4*>(part_acc + prow * D + d));
-            const float m_new = fmaxf(mx, ml.x);
-            const float keep = mx == -INFINITY ? 0.f : exp2f(mx - m_new);
-            const float w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_new);
-            lsum = lsum * keep + ml.y * w;
-            acc[0] = acc[0] * keep + pa.x * w;
-            acc[1] = acc[1] * keep + pa.y * w;
-            acc[2] = acc[2] * keep + pa.z * w;
-            acc[3] = acc[3] * keep + pa.w * w;
-            mx = m_new;
-          }
-          const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-          const int row = row0 + r, tok = row / G, g = row - tok * G;
-          uint2 ov;
-          ov.x = pack_bf16(acc[0] * inv, acc[1] * inv);
-          ov.y = pack_bf16(acc[2] * inv, acc[3] * inv);
-          *reinterpret_cast<uint2*>(out + ((size_t)(q_start + tok) * nh + kvh * G + g) * D + d) = ov;
-        }
+        merge_tile_chunks<D, kPfBM, THREADS, 4>(part_acc, part_ml, slot0, n_chunks, nkv, kvh, n_rows, row0, G, q_start, nh,
+                                                  out, tid);
         if (tid == 0) tile_done[tile * nkv + kvh] = 0;
       }
     }

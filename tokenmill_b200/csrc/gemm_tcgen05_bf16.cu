@@ -19,7 +19,7 @@
 // rest of its work, still frees its tensor memory, and the host reports the failure.
 #include <cuda.h>
 
-#include "common.cuh"
+#include "tcgen05_util.cuh"
 
 namespace tmk {
 
@@ -28,7 +28,6 @@ constexpr int kT5ABytes = kT5BM * kT5BK * 2;            // 16 KB
 constexpr int kT5BBytes = kT5BN * kT5BK * 2;            // 32 KB
 constexpr int kT5StageBytes = kT5ABytes + kT5BBytes;    // 48 KB
 constexpr int kT5Threads = 256;
-constexpr uint32_t kT5SpinLimit = 1u << 24;             // polls (with back-off) before a wait gives up
 enum : int { T5_STORE = 0, T5_SWIGLU = 1, T5_QKV = 2 };
 
 struct T5Args {
@@ -49,86 +48,11 @@ struct T5Args {
   int* error;               // device word, 0 when all is well
 };
 
-// --- PTX wrappers ---------------------------------------------------------------------------------
+// --- PTX wrappers (the rest are in tcgen05_util.cuh) -----------------------------------------------
 
-__device__ __forceinline__ uint32_t t5_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false (and raises the error word) when the limit is reached or another role
-// has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int* error, int code) {
-  for (uint32_t i = 0; i < kT5SpinLimit; ++i) {
-    if (mbar_try(bar, parity)) return true;
-    if (i > 64) {
-      if (*s_abort) return false;
-      __nanosleep(64);
-    }
-  }
-  *s_abort = 1;
-  atomicCAS(error, 0, code);
-  return false;
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void t5_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void t5_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-// 32 lanes x 32 consecutive 32-bit columns: thread = lane (row), v[j] = column j.
-__device__ __forceinline__ void t5_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-#pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-}
-// The registers of earlier t5_ld32 calls may be read only after this.
-__device__ __forceinline__ void t5_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile of 128-byte rows, 128-byte swizzle: rows 128 B apart,
-// groups of 8 rows 1024 B apart (stride offset), leading offset unused (1), descriptor version 1.
-__device__ __forceinline__ uint64_t t5_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;                  // leading byte offset (>> 4)
-  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset (>> 4)
-  d |= (uint64_t)1 << 46;                  // version
-  d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
-  return d;
 }
 
 __device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) {

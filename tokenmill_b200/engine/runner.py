@@ -45,6 +45,10 @@ class ModelRunner:
         self.group_sizes = sorted({b.mixer.nh // b.mixer.nkv for b in model.blocks
                                    if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")})
         self.scratch = AttentionScratch(self.device)
+        # Rows of a prompt-attention work unit: 128 where the tcgen05 kernel takes every attention layer of the
+        # model (bfloat16, heads of 64), else the 64 of the mma.sync kernel.
+        heads = {b.mixer.D for b in model.blocks if hasattr(b.mixer, "D")}
+        self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads == {64}) else 64
         self.graph_max_batch = min(cuda_graph_max_batch, max_num_seqs) if cuda_graphs else 0
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
@@ -82,7 +86,7 @@ class ModelRunner:
                 return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
             if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
                 step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                         split_keys=SPLIT_KEYS)
+                                         split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile)
                 self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
@@ -93,10 +97,10 @@ class ModelRunner:
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return self._graph_step(entries)
         step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                 split_keys=SPLIT_KEYS)
+                                 split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile)
         self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
         logits = self.model.forward(step, self.layer_caches)
-        if self.model.dtype == torch.bfloat16 and step.n_tokens >= ops.TC_MIN_TOKENS:
+        if self.model.dtype == torch.bfloat16 and (step.n_tokens >= ops.TC_MIN_TOKENS or self.prefill_tile == 128):
             ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
         return logits
 

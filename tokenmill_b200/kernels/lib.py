@@ -42,6 +42,8 @@ _SIGNATURES: dict[str, list] = {
     "tm_attention_combine": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "tm_decode_attention_bf16": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "tm_prefill_attention_bf16": [_P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "tm_prefill_attention_tc_timing": [_P],
+    "tm_prefill_attention_tc_bf16": [_P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "tm_swiglu": [_I, _P, _P, _I, _I, _P],
     "tm_skinny_linear": [_P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
     "tm_skinny_qkv_rope_write": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],

@@ -163,6 +163,8 @@ def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         raise lib.KernelError("prefill_attention_bf16: q / cache / out shapes disagree")
     if scale <= 0:
         raise lib.KernelError("prefill_attention_bf16: the score scale must be positive")
+    if units.tile_rows != 64:
+        raise lib.KernelError("prefill_attention_bf16: units of 64-row tiles only")
     if units.n_slots and (part_acc is None or part_ml is None or tile_done is None
                           or part_acc.numel() < units.n_slots * nkv * 64 * D
                           or part_ml.numel() < units.n_slots * nkv * 64 * 2 or tile_done.numel() < units.n_tiles * nkv):
@@ -175,6 +177,42 @@ def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
              _req(tile_done, "tile_done", i32) if units.n_slots else None,
              _req(counters, "counters", i32), _req(out, "out", bf), nh, nkv, D, page_size, float(scale), int(window),
              _stream())
+    return out
+
+
+def tc_attention_enabled() -> bool:
+    """The tcgen05 prompt-attention kernel is used where it applies unless TOKENMILL_TC_ATTENTION=0."""
+    return os.environ.get("TOKENMILL_TC_ATTENTION", "1") != "0"
+
+
+def prefill_attention_tc_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                              units, counters: torch.Tensor, out: torch.Tensor, *, scale: float, window: int = 0,
+                              part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
+                              tile_done: torch.Tensor | None = None) -> torch.Tensor:
+    """As prefill_attention_bf16, on tcgen05 with the scores and outputs in tensor memory: head size 64, units of
+    128-row tiles (units.tile_rows == 128; the scratch holds 128 rows per slot). A block that gives up on a
+    bounded wait raises the device error word that tc_check reads."""
+    T, nh, D = q.shape
+    page_size, nkv = kcache.shape[1], kcache.shape[2]
+    bf, i32 = torch.bfloat16, torch.int32
+    if D != 64 or units.tile_rows != 128:
+        raise lib.KernelError("prefill_attention_tc_bf16: head size 64 and 128-row tiles only")
+    if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
+        raise lib.KernelError("prefill_attention_tc_bf16: q / cache / out shapes disagree")
+    if scale <= 0:
+        raise lib.KernelError("prefill_attention_tc_bf16: the score scale must be positive")
+    if units.n_slots and (part_acc is None or part_ml is None or tile_done is None
+                          or part_acc.numel() < units.n_slots * nkv * 128 * D
+                          or part_ml.numel() < units.n_slots * nkv * 128 * 2 or tile_done.numel() < units.n_tiles * nkv):
+        raise lib.KernelError("prefill_attention_tc_bf16: scratch for the partial results is missing or too small")
+    lib.call("tm_prefill_attention_tc_bf16", _req(q, "q", bf), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf),
+             _req(block_table, "block_table", i32), block_table.stride(0), _req(units.records, "unit records", i32),
+             units.n_units, int(units.chunk_keys),
+             _req(part_acc, "part_acc", torch.float32) if units.n_slots else None,
+             _req(part_ml, "part_ml", torch.float32) if units.n_slots else None,
+             _req(tile_done, "tile_done", i32) if units.n_slots else None,
+             _req(counters, "counters", i32), _req(out, "out", bf), nh, nkv, D, page_size, float(scale), int(window),
+             _tc_flag(q.device).data_ptr(), _stream())
     return out
 
 
@@ -351,8 +389,8 @@ def tc_check(device: torch.device) -> None:
         code = int(flag.item())
         if code:
             flag.zero_()
-            raise lib.KernelError(f"a tcgen05 matrix-product block gave up waiting (code {code}: 1 loader, "
-                                  f"2/3 issuer, 4 epilogue); its results are incomplete")
+            raise lib.KernelError(f"a tcgen05 block gave up waiting (code {code}: matrix product 1 loader, 2/3 issuer, "
+                                  f"4 epilogue; attention 11/13 second product, 12 scores); its results are incomplete")
 
 
 def tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:

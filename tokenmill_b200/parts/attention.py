@@ -61,13 +61,13 @@ class AttentionScratch:
         self.reserve(rows, max_splits, head_dim)
         return self.part_acc, self.part_ml
 
-    def get_prefill(self, slots: int, head_dim: int, tiles: int):
-        """Scratch for the prompt kernel's per-(row tile, key chunk) partial results: ``slots`` slots of 64
-        rows, and one arrival counter (zero between launches) for each of ``tiles`` (row tile, kv head)
+    def get_prefill(self, slots: int, head_dim: int, tiles: int, tile_rows: int = 64):
+        """Scratch for the prompt kernel's per-(row tile, key chunk) partial results: ``slots`` slots of
+        ``tile_rows`` rows, and one arrival counter (zero between launches) for each of ``tiles`` (row tile, kv head)
         pairs. Prompt steps are never captured in a graph, so these may grow at any time."""
         if slots <= 0:
             return None, None, None
-        need = slots * 64
+        need = slots * tile_rows
         if self._pf_acc is None or self._pf_acc.numel() < need * head_dim:
             self._pf_acc = torch.empty(need * head_dim, dtype=torch.float32, device=self.device)
         if self._pf_ml is None or self._pf_ml.numel() < need * 2:
@@ -168,13 +168,12 @@ class GroupedQueryAttention:
                                       part_ml=part_ml, done=step.scratch.done)
             return
         if self.dtype == torch.bfloat16 and self.D in (64, 128) and G in step.prefill:
-            units = step.prefill[G]                # 64-row tiles cut into key chunks, heaviest first
+            units = step.prefill[G]                # row tiles cut into key chunks, heaviest first
             part_acc, part_ml, tile_done = step.scratch.get_prefill(units.n_slots * self.nkv, self.D,
-                                                                    units.n_tiles * self.nkv)
-            ops.prefill_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], units,
-                                       step.scratch.counters(), out,
-                                       scale=self.scale, window=self.window, part_acc=part_acc, part_ml=part_ml,
-                                       tile_done=tile_done)
+                                                                    units.n_tiles * self.nkv, units.tile_rows)
+            kernel = ops.prefill_attention_tc_bf16 if units.tile_rows == 128 and self.D == 64 else ops.prefill_attention_bf16
+            kernel(q, cache.k, cache.v, step.block_tables[cache.group], units, step.scratch.counters(), out,
+                   scale=self.scale, window=self.window, part_acc=part_acc, part_ml=part_ml, tile_done=tile_done)
             return
         tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
         kw = {}

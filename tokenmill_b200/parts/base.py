@@ -34,14 +34,15 @@ class LayerCache:
 
 class PrefillUnits(NamedTuple):
     """Work units of the tensor-core prompt attention for one group size (engine/batch.py packed_units):
-    one 8-int record per unit (a 64-row tile of one request times one chunk of chunk_keys keys), heaviest
-    first; n_slots partial-result slots are needed, for n_tiles row tiles."""
+    one 8-int record per unit (a tile of tile_rows rows of one request times one chunk of chunk_keys keys),
+    heaviest first; n_slots partial-result slots (of tile_rows rows) are needed, for n_tiles row tiles."""
 
     records: torch.Tensor
     n_units: int
     n_tiles: int
     n_slots: int
     chunk_keys: int
+    tile_rows: int = 64
 
 
 @dataclass
