@@ -18,24 +18,30 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   }
 }
 
-// 16 bytes per access: VEC elements (8 bfloat16 or 4 float32).
+// 16 bytes per access: VEC elements (8 bfloat16 or 4 float32). One block works on a piece of one row (the row
+// is the block's x index), so that no thread divides a 64-bit index; with bfloat16 outputs the quotient is a
+// reciprocal and a multiply (2 ulp in float32, far below the output's rounding): with the exact division and the
+// flat index the kernel was bound by instruction issue, not by memory.
 template <typename T, int VEC>
-__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, long long total_vec) {
-  const int per_row = I / VEC;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const long long t = idx / per_row;
-    const int i = (int)(idx - t * per_row) * VEC;
-    const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
-    const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
-    uint4 o;
-    const T* gp = reinterpret_cast<const T*>(&g);
-    const T* up = reinterpret_cast<const T*>(&u);
-    T* op = reinterpret_cast<T*>(&o);
+__global__ void __launch_bounds__(128) swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (i >= I) return;
+  const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+  const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+  uint4 o;
+  const T* gp = reinterpret_cast<const T*>(&g);
+  const T* up = reinterpret_cast<const T*>(&u);
+  T* op = reinterpret_cast<T*>(&o);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) op[e] = from_float<T>(silu_mul(to_float(gp[e]), to_float(up[e])));
-    *reinterpret_cast<uint4*>(out + t * I + i) = o;
+  for (int e = 0; e < VEC; ++e) {
+    const float gf = to_float(gp[e]), uf = to_float(up[e]);
+    if constexpr (sizeof(T) == 2) op[e] = from_float<T>(__fdividef(gf, 1.0f + expf(-gf)) * uf);
+    else op[e] = from_float<T>(silu_mul(gf, uf));
   }
+  *reinterpret_cast<uint4*>(out + t * I + i) = o;
 }
 
 template <typename T>
@@ -44,10 +50,9 @@ int launch_swiglu(const void* gu, void* out, int T_, int I, cudaStream_t stream)
   const int threads = 256;
   const bool aligned = ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   if (I % VEC == 0 && aligned) {
-    const long long total = (long long)T_ * (I / VEC);
-    long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    swiglu_vec_kernel<T, VEC><<<(int)blocks, threads, 0, stream>>>((const T*)gu, (T*)out, I, total);
+    const int per_row = I / VEC;
+    return launch_pdl(swiglu_vec_kernel<T, VEC>, dim3(T_, (per_row + 127) / 128), dim3(128), 0, stream, (const T*)gu,
+                      (T*)out, I);
   } else {
     const long long total = (long long)T_ * I;
     long long blocks = (total + threads - 1) / threads;

@@ -81,6 +81,83 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(
   }
 }
 
+// The same, one WARP per row: the row lives in the warp's registers (CH chunks of 4 elements per lane), so
+// there is no shared memory and no block-level synchronisation, and a few thousand rows are in flight on the
+// chip at once. One block per row left a long prompt's norm bound by the latency of its load, reduce and store
+// chain, two waves deep. Rows up to 128 CH wide whose width is a multiple of 4; the order of the sum of
+// squares (lane-wise over the chunks, then the butterfly across lanes) is fixed by the width alone.
+template <typename T, int CH>
+__global__ void __launch_bounds__(128) add_rmsnorm_warp_kernel(
+    float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ partials,
+    int n_partials, long long partial_stride, const int* __restrict__ ids, const T* __restrict__ table,
+    const int* __restrict__ rows, const float* __restrict__ weight, float eps, T* __restrict__ out, int H,
+    int n_rows) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  float w[CH][4];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {               // the weights depend on no earlier kernel
+    const int i = (c * 32 + lane) * 4;
+    if (i < H) load4<float>(weight + i, w[c]);
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  if (r >= n_rows) return;
+  const int src = rows ? rows[r] : r;
+  const bool write_back = !rows && (ids || branch || partials);
+  float x[CH][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * 32 + lane) * 4;
+    if (i >= H) continue;
+    if (ids) {
+      load4<T>(table + (size_t)ids[src] * H + i, x[c]);
+    } else {
+      load4<float>(resid + (size_t)src * H + i, x[c]);
+      if (branch) {
+        float b[4];
+        load4<T>(branch + (size_t)src * H + i, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[c][e] += b[e];
+      }
+      if (partials) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int p2 = 0; p2 < n_partials; ++p2) {
+          float v[4];
+          load4<float>(partials + (size_t)p2 * partial_stride + (size_t)src * H + i, v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[e] += v[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[c][e] += acc[e];
+      }
+    }
+    if (write_back) store4<float>(resid + (size_t)src * H + i, x[c]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss += x[c][e] * x[c][e];
+  }
+  const float total = warp_sum(ss);
+  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * 32 + lane) * 4;
+    if (i >= H) continue;
+    float y[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) y[e] = w[c][e] * to_float(from_float<T>(x[c][e] * rstd));
+    store4<T>(out + (size_t)r * H + i, y);
+  }
+}
+
+template <typename T, int CH, typename... Args>
+int launch_add_rmsnorm_warp(int n_rows, cudaStream_t stream, Args... args) {
+  // Few rows: one warp per block, so that they spread over the SMs; many: four.
+  const int warps = n_rows >= 1024 ? 4 : 1;
+  return launch_pdl(add_rmsnorm_warp_kernel<T, CH>, dim3((n_rows + warps - 1) / warps), dim3(32 * warps), 0, stream,
+                    args..., n_rows);
+}
+
 template <typename T>
 int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, int n_partials,
                        long long partial_stride, const int* ids, const void* table, const int* rows,
@@ -92,6 +169,18 @@ int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, 
                         reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(table) |
                         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight);
   const bool vec = H % 4 == 0 && (all & 15) == 0 && (partial_stride % 4 == 0);
+  if (vec && H <= 128 * 16) {
+    const int chunks = (H + 127) / 128;
+#define TM_NORM_WARP(CH)                                                                                          \
+  return launch_add_rmsnorm_warp<T, CH>(n_rows, stream, resid, (const T*)branch, partials, n_partials, partial_stride, \
+                                        ids, (const T*)table, rows, weight, eps, (T*)out, H)
+    if (chunks <= 1) TM_NORM_WARP(1);
+    if (chunks <= 2) TM_NORM_WARP(2);
+    if (chunks <= 4) TM_NORM_WARP(4);
+    if (chunks <= 8) TM_NORM_WARP(8);
+    TM_NORM_WARP(16);
+#undef TM_NORM_WARP
+  }
   auto kern = vec ? add_rmsnorm_kernel<T, 4> : add_rmsnorm_kernel<T, 1>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
