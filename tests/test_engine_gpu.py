@@ -217,18 +217,21 @@ def test_command_line_generates(tiny_a_dir):
     assert rows[0]["output_ids"] == plain_greedy(cfg, w, [5, 6, 7], 5)
 
 
+@pytest.mark.parametrize("step_program", ["1", "0"])
 @pytest.mark.parametrize("switch", ["1", "0"])
-def test_prompt_attention_kernel_choice(tmp_path, monkeypatch, plain_cache, switch):
+def test_prompt_attention_kernel_choice(tmp_path, monkeypatch, plain_cache, switch, step_program):
     """Heads of 64 in bfloat16 take the tcgen05 prompt-attention kernel (128-row tiles), and the mma.sync one
     when TOKENMILL_TC_ATTENTION=0; both agree with the plain implementation, also on portions cut anywhere and
-    beside another request's decoded tokens."""
-    from tokenmill_b200.kernels import lib
+    beside another request's decoded tokens. The same with the launches walked by a step program (the default)
+    and made one by one from Python (TOKENMILL_STEP_PROGRAM=0)."""
+    from tokenmill_b200.kernels import lib, program
     from tokenmill_b200.weights import qwen2_config, write_random_model
     cfg = qwen2_config(vocab_size=300, hidden_size=192, intermediate_size=264, num_hidden_layers=2,
                        num_attention_heads=3, num_key_value_heads=1, rope_theta=10000.0, tie_word_embeddings=False,
                        max_position_embeddings=1024)
     folder = write_random_model(tmp_path / "m", cfg, seed=6)
     monkeypatch.setenv("TOKENMILL_TC_ATTENTION", switch)
+    monkeypatch.setenv("TOKENMILL_STEP_PROGRAM", step_program)
     calls = []
     real = lib.call
     monkeypatch.setattr(lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
@@ -238,11 +241,16 @@ def test_prompt_attention_kernel_choice(tmp_path, monkeypatch, plain_cache, swit
                                      {"id": "r0", "tokens": reqs["r0"][297:299], "want": [0, 1]}], "end": []},
              {"step": 2, "entries": [{"id": "r0", "tokens": reqs["r0"][299:], "want": list(range(41))},
                                      {"id": "r1", "tokens": reqs["r1"][149:], "want": [0]}], "end": ["r0", "r1"]}]
+    before = program.kind_launches()
     outputs = run_trace(folder, "bfloat16", steps, 512, tmp_path / "o")
     check_against_plain(steps, outputs, reqs, plain_for(folder, reqs, plain_cache), "bfloat16")
-    used = "tm_prefill_attention_tc_bf16" if switch == "1" else "tm_prefill_attention_bf16"
-    other = "tm_prefill_attention_bf16" if switch == "1" else "tm_prefill_attention_tc_bf16"
-    assert used in calls and other not in calls
+    used, other = ("prefill_attention_tc", "prefill_attention") if switch == "1" else ("prefill_attention", "prefill_attention_tc")
+    if step_program == "1":
+        issued = {k: v - before[k] for k, v in program.kind_launches().items()}
+        assert issued[used] == 6 and issued[other] == 0 and issued["gemm_bf16"] == 3 * (4 * 2 + 1)
+        assert calls.count("tm_program_run") == 3 and not any("attention" in c for c in calls)
+    else:
+        assert f"tm_{used}_bf16" in calls and f"tm_{other}_bf16" not in calls and "tm_program_run" not in calls
 
 
 def test_prompt_products_on_tcgen05_when_switched_on(tmp_path, monkeypatch, plain_cache):
@@ -482,3 +490,47 @@ def test_whole_step_kernel_at_model_sizes_equals_the_kernel_per_operation_path(w
     for a, b in zip(run(True), run(False)):
         assert torch.isfinite(a).all()
         assert float((a - b).abs().max()) <= 3e-2 * float(b.abs().max()), float((a - b).abs().max())
+
+
+def test_step_program_equals_the_launch_by_launch_path(wide_dir, monkeypatch):
+    """The same steps with the launches walked natively from a step program and made one by one from Python:
+    prompt portions of growing size (the program's workspace is rebuilt when a step outgrows it), a mixed step,
+    a step of 20 single tokens (which takes the decode attention kernel inside the program) and a step that
+    wants no logits. Same kernels, same arguments: the logits agree to the last bit wherever the matrix library
+    picks the same algorithm, and within bfloat16 rounding otherwise."""
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.kernels import program
+    rng = random.Random(3)
+    prompts = [[rng.randrange(1000) for _ in range(n)] for n in [700] + [40] * 19]
+
+    def run(use_program):
+        monkeypatch.setenv("TOKENMILL_STEP_PROGRAM", "1" if use_program else "0")
+        eng = engine_for(wide_dir, dtype="bfloat16", max_model_len=1024, max_num_seqs=32, kv_cache_mb=64,
+                         max_num_batched_tokens=4096, cuda_graphs=False)
+        r, cache = eng.runner, eng.cache
+        hs = []
+        for p in prompts:
+            h = cache.new_handle()
+            cache.allocate(h, p + [0])
+            hs.append(h)
+        before = program.kind_launches()
+        outs = [r.step([StepEntry(hs[0], prompts[0][:100], 0, [0, 99])]),                    # capacity 256
+                r.step([StepEntry(hs[0], prompts[0][100:130], 100, [])]),                    # no logits wanted
+                r.step([StepEntry(hs[0], prompts[0][130:], 130, [569])] +                    # capacity 1024, mixed
+                       [StepEntry(h, p, 0, [39]) for h, p in zip(hs[1:], prompts[1:])]),
+                r.step([StepEntry(hs[0], [5], 700, [0])] +                                   # 20 decoded tokens
+                       [StepEntry(h, [7 + i], 40, [0]) for i, h in enumerate(hs[1:])])]
+        issued = {k: v - before[k] for k, v in program.kind_launches().items()}
+        if use_program:
+            assert r.stats["program_steps"] == 4 and r._program.capacity == 2048
+            assert issued["decode_attention"] == 2 and issued["prefill_attention_tc"] == 6 and issued["prefill_attention"] == 0
+        else:
+            assert r.stats["program_steps"] == 0 and sum(issued.values()) == 0
+        return [o.float().cpu() for o in outs]
+
+    a, b = run(True), run(False)
+    assert a[1].shape == (0, 1000) and b[1].shape == (0, 1000)
+    for x, y in zip(a, b):
+        assert x.shape == y.shape and torch.isfinite(x).all()
+        if x.numel():
+            assert float((x - y).abs().max()) <= 3e-2 * float(y.abs().max()), float((x - y).abs().max())

@@ -113,7 +113,8 @@ def packed_units(q_lens: np.ndarray, starts: np.ndarray, group_size: int, tile: 
 
 def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: torch.device,
                       group_sizes: list[int], *, scratch=None, split_keys: int = 0,
-                      min_table_width: int = 0, prefill_tile: int = PACKED_TILE) -> StepInputs:
+                      min_table_width: int = 0, prefill_tile: int = PACKED_TILE,
+                      prefill_chunk: int = PREFILL_CHUNK) -> StepInputs:
     S = len(entries)
     ps = cache.page_size
     q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
@@ -131,7 +132,7 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
         if any(not (0 <= w < len(e.tokens)) for w in e.want):
             raise ValueError(f"entry {i}: a wanted place lies outside its {len(e.tokens)} tokens")
     tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
-    unit_arrays = {g: packed_units(q_lens, starts, g, tile=prefill_tile) for g in group_sizes}
+    unit_arrays = {g: packed_units(q_lens, starts, g, tile=prefill_tile, chunk=prefill_chunk) for g in group_sizes}
     lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()},
                  {g: u[0].shape[0] for g, u in unit_arrays.items()})
 
@@ -184,6 +185,6 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
         want_rows=dev[lay.want_rows], n_want=len(want_rows), max_q_len=max_q, max_kv_len=max_kv,
         q_lens=q_lens.tolist(), kv_befores=starts.tolist(),
         tiles={g: (dev[lay.tile_seq[g]], dev[lay.tile_row0[g]], a[0].size) for g, a in tile_arrays.items()},
-        prefill={g: PrefillUnits(dev[lay.prefill[g]], records.shape[0], n_tiles, n_slots, PREFILL_CHUNK, prefill_tile)
+        prefill={g: PrefillUnits(dev[lay.prefill[g]], records.shape[0], n_tiles, n_slots, prefill_chunk, prefill_tile)
                  for g, (records, n_tiles, n_slots) in unit_arrays.items()},
         scratch=scratch, split_keys=use_split, max_splits=-(-max_kv // use_split) if use_split else 0)

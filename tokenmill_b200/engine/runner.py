@@ -16,6 +16,7 @@ never hands out.
 from __future__ import annotations
 
 import bisect
+import os
 
 import numpy as np
 import torch
@@ -23,6 +24,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.pool import CachePools
 from ..kernels import fused, lib, ops
+from ..kernels import program as program_mod
 from ..parts.attention import SPLIT_KEYS, AttentionScratch
 from ..parts.base import StepInputs
 from ..parts.model import DecoderModel
@@ -49,11 +51,16 @@ class ModelRunner:
         # model (bfloat16, heads of 64), else the 64 of the mma.sync kernel.
         heads = {b.mixer.D for b in model.blocks if hasattr(b.mixer, "D")}
         self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads == {64}) else 64
+        self.prefill_chunk = batch_mod.PREFILL_CHUNK     # keys of a work unit
+        # Steps of more than 16 tokens run as a step program (one native call walks the launches) where every
+        # part of the model can write its launches down; TOKENMILL_STEP_PROGRAM=0 keeps the per-launch path.
+        self._program = None
+        self._no_program = os.environ.get("TOKENMILL_STEP_PROGRAM", "1") == "0"
         self.graph_max_batch = min(cuda_graph_max_batch, max_num_seqs) if cuda_graphs else 0
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
         self.kernels_per_graph: dict[int, int] = {}
-        self.stats = {"steps": 0, "graph_steps": 0, "fused_steps": 0, "tokens": 0, "h2d_bytes": 0}   # h2d: last step
+        self.stats = {"steps": 0, "graph_steps": 0, "fused_steps": 0, "program_steps": 0, "tokens": 0, "h2d_bytes": 0}   # h2d: last step
         # One kernel per decode step when the model is the arrangement that kernel implements.
         self.fused = None
         if fused.eligible(model) and len(self.layout.groups) == 1:
@@ -86,7 +93,8 @@ class ModelRunner:
                 return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
             if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
                 step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                         split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile)
+                                         split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
+                                 prefill_chunk=self.prefill_chunk)
                 self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
@@ -97,12 +105,33 @@ class ModelRunner:
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return self._graph_step(entries)
         step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                 split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile)
+                                 split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
+                                 prefill_chunk=self.prefill_chunk)
         self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
-        logits = self.model.forward(step, self.layer_caches)
+        prog = self._step_program(step.n_tokens)
+        if prog is not None and prog.takes(step):
+            self.stats["program_steps"] += 1
+            step.logits_out = torch.empty((step.n_want, self.model.spec.vocab_size), dtype=torch.float32,
+                                          device=self.device)
+            prog.run(step)
+            logits = step.logits_out
+        else:
+            logits = self.model.forward(step, self.layer_caches)
         if self.model.dtype == torch.bfloat16 and (step.n_tokens >= ops.TC_MIN_TOKENS or self.prefill_tile == 128):
             ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
         return logits
+
+    def _step_program(self, n_tokens: int):
+        """The model's step program with room for ``n_tokens`` (built on first need, rebuilt with a larger
+        workspace when a step outgrows it), or None where there is none."""
+        if self._no_program or n_tokens < program_mod.MIN_TOKENS or ops._TC_ENABLED:
+            return None
+        if self._program is None or self._program.capacity < n_tokens:
+            capacity = max(256, 1 << (n_tokens - 1).bit_length())
+            self._program = self.model.program(self.layer_caches, capacity)
+            if self._program is None:
+                self._no_program = True
+        return self._program
 
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
         """Whether ``step_fed`` takes a decode step of this many requests."""

@@ -110,7 +110,7 @@ def build(verbose: bool = True, force: bool = False) -> Path:
             for j in jobs:
                 j.result()
         tmp = out_dir / f".{lib.name}.{os.getpid()}.tmp"
-        _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in objs], "-lcuda"])
+        _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in objs], "-lcuda", "-ldl"])
         os.replace(tmp, lib)  # atomic: a concurrent builder never sees half a library
         for stale in out_dir.glob("libtokenmill_kernels_*.so"):     # libraries of earlier source states
             if stale != lib:

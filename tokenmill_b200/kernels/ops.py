@@ -23,6 +23,9 @@ def _code(dtype: torch.dtype) -> int:
     raise lib.KernelError(f"kernels run in float32 or bfloat16, got {dtype}")
 
 
+dtype_code = _code
+
+
 def _stream() -> int:
     """The raw handle of the stream torch launches on right now (captured graphs included). The private
     C call is a fraction of a microsecond; the public ``torch.cuda.current_stream()`` builds objects on
@@ -380,6 +383,9 @@ def _tc_flag(device: torch.device) -> torch.Tensor:
     if device not in _tc_error:
         _tc_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
     return _tc_error[device]
+
+
+tc_error_word = _tc_flag
 
 
 def tc_check(device: torch.device) -> None:

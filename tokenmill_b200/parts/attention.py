@@ -154,24 +154,107 @@ class GroupedQueryAttention:
             return ops.skinny_linear(flat, self.w_o, k_splits=ops.skinny_k_splits(T, self.q_size))
         return ops.linear(flat, self.w_o)
 
+    def attention_path(self, step: StepInputs) -> str:
+        """Which attention kernel this step's shape takes: "decode" (tensor cores, every request brings at most
+        16 query rows per kv head), "prefill_tc" / "prefill" (tensor cores, tcgen05 or mma.sync, row tiles cut
+        into key chunks) or "generic" (any head size and dtype)."""
+        G = self.nh // self.nkv
+        if self.dtype != torch.bfloat16 or self.D not in (64, 128):
+            return "generic"
+        if step.split_keys and step.max_q_len * G <= 16:
+            return "decode"
+        if G in step.prefill:
+            return "prefill_tc" if step.prefill[G].tile_rows == 128 and self.D == 64 else "prefill"
+        return "generic"
+
+    def emit(self, b, x, cache: LayerCache):
+        """The prompt-step launches (library product, bias + rotation + cache write, attention, library
+        product) written into a step program (kernels/program.py). ``x`` is a workspace buffer; returns the
+        output buffer. The attention kernel is chosen per step as in ``attend``: all candidates are in the
+        program, each under a step parameter that says whether it runs."""
+        from ..kernels.program import (OP_DECODE_ATTENTION, OP_GEMM_BF16, OP_PREFILL_ATTENTION, OP_PREFILL_ATTENTION_TC,
+                                       OP_QKV_ROPE_WRITE, Float)
+        if self.dtype != torch.bfloat16 or self.D not in (64, 128) or self.position is None:
+            raise NotImplementedError("step programs are built for bfloat16 attention with heads of 64 or 128")
+        T, g, G, nh, nkv, D = b.tokens(), cache.group, self.nh // self.nkv, self.nh, self.nkv, self.D
+        code = ops.dtype_code(self.dtype)
+        n_qkv = self.q_size + 2 * self.kv_size
+        qkv = b.buffer("qkv", n_qkv * 2)
+        q = b.buffer("q", self.q_size * 2)
+        out = b.buffer("attention_out", self.q_size * 2)
+        branch = b.buffer("mixer_out", self.hidden_size * 2)
+        positions = b.param("positions", lambda s: s.positions.data_ptr())
+        slot_map = b.param(f"slot_map{g}", lambda s: s.slot_maps[g].data_ptr()) if cache.writes else None
+        kc, vc = (cache.k, cache.v) if cache.writes else (None, None)
+        b.emit(OP_GEMM_BF16, [x, self.w_qkv, qkv, T, n_qkv, self.hidden_size, 0])
+        b.emit(OP_QKV_ROPE_WRITE, [code, code, qkv, self.b_qkv, positions, self.cos, self.sin, slot_map, q, kc, vc, T,
+                                   nh, nkv, D, self.cos.shape[0]])
+
+        path = self.attention_path
+        b.guard(lambda s: path(s) != "generic")
+        key = f"G{G}_D{D}_kv{nkv}"
+        table = b.param(f"block_table{g}", lambda s: s.block_tables[g].data_ptr())
+        bt_stride = b.param(f"block_table_stride{g}", lambda s: s.block_tables[g].stride(0))
+        page, scale, window = cache.k.shape[1], Float(self.scale), self.window
+
+        # decode kernel: scratch for T * nh rows of max_splits partial results, n_seqs * nkv arrival counters
+        def dec(i):
+            return lambda s: s.scratch.get(s.n_tokens * nh, s.max_splits, D)[i].data_ptr() if path(s) == "decode" else 0
+        def dec_done(s):
+            if path(s) != "decode":
+                return 0
+            s.scratch.get(s.n_tokens * nh, s.max_splits, D)
+            return s.scratch.done.data_ptr()
+        b.emit(OP_DECODE_ATTENTION,
+               [q, cache.k, cache.v, table, bt_stride, b.param("cu_q", lambda s: s.cu_q.data_ptr()),
+                b.param("kv_before", lambda s: s.kv_before.data_ptr()), b.param("n_seqs", lambda s: s.n_seqs),
+                b.param(f"decode_acc_{key}", dec(0)), b.param(f"decode_ml_{key}", dec(1)), out,
+                b.param(f"decode_done_{key}", dec_done), nh, nkv, D, page, scale, window,
+                b.param("split_keys", lambda s: s.split_keys), b.param("max_splits", lambda s: s.max_splits)],
+               cond=b.param(f"attention_decode_{key}", lambda s: int(path(s) == "decode")))
+
+        # prompt kernels: the step's work units for this group size, scratch for the tiles with several chunks
+        def pf(i):
+            def fn(s):
+                if not path(s).startswith("prefill"):
+                    return 0
+                u = s.prefill[G]
+                t = s.scratch.get_prefill(u.n_slots * nkv, D, u.n_tiles * nkv, u.tile_rows)[i]
+                return t.data_ptr() if t is not None else 0
+            return fn
+        units = [b.param(f"units_{G}", lambda s: s.prefill[G].records.data_ptr() if G in s.prefill else 0),
+                 b.param(f"n_units_{G}", lambda s: s.prefill[G].n_units if G in s.prefill else 0),
+                 b.param(f"chunk_keys_{G}", lambda s: s.prefill[G].chunk_keys if G in s.prefill else 0)]
+        scratch = [b.param(f"prefill_acc_{key}", pf(0)), b.param(f"prefill_ml_{key}", pf(1)),
+                   b.param(f"prefill_done_{key}", pf(2)), b.param("prefill_counters", lambda s: s.scratch.counters().data_ptr())]
+        common = [q, cache.k, cache.v, table, bt_stride, *units, *scratch, out, nh, nkv, D, page, scale, window]
+        if D == 64:
+            b.uses_tc_attention = True
+            b.emit(OP_PREFILL_ATTENTION_TC, common + [ops.tc_error_word(self.device)],
+                   cond=b.param(f"attention_prefill_tc_{key}", lambda s: int(path(s) == "prefill_tc")))
+        b.emit(OP_PREFILL_ATTENTION, common,
+               cond=b.param(f"attention_prefill_{key}", lambda s: int(path(s) == "prefill")))
+        b.emit(OP_GEMM_BF16, [out, self.w_o, branch, T, self.hidden_size, self.q_size, 0])
+        return branch
+
     def attend(self, q: torch.Tensor, step: StepInputs, cache: LayerCache, out: torch.Tensor) -> None:
-        """Pick the attention kernel for this step's shape: the tensor-core decode kernel when every
-        request brings at most 16 query rows per kv head (bfloat16, head size 64 or 128), else the
-        shape-generic kernel, with its keys split when the queries are few and the contexts long."""
+        """Run the attention kernel that ``attention_path`` names; the shape-generic kernel has its keys split
+        when the queries are few and the contexts long."""
         G = self.nh // self.nkv
         rows = step.max_q_len * G
-        if step.split_keys and rows <= 16 and self.dtype == torch.bfloat16 and self.D in (64, 128):
+        path = self.attention_path(step)
+        if path == "decode":
             part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, step.max_splits, self.D)
             ops.decode_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
                                       step.kv_before, step.n_seqs, out, scale=self.scale, window=self.window,
                                       split_keys=step.split_keys, max_splits=step.max_splits, part_acc=part_acc,
                                       part_ml=part_ml, done=step.scratch.done)
             return
-        if self.dtype == torch.bfloat16 and self.D in (64, 128) and G in step.prefill:
+        if path in ("prefill_tc", "prefill"):
             units = step.prefill[G]                # row tiles cut into key chunks, heaviest first
             part_acc, part_ml, tile_done = step.scratch.get_prefill(units.n_slots * self.nkv, self.D,
                                                                     units.n_tiles * self.nkv, units.tile_rows)
-            kernel = ops.prefill_attention_tc_bf16 if units.tile_rows == 128 and self.D == 64 else ops.prefill_attention_bf16
+            kernel = ops.prefill_attention_tc_bf16 if path == "prefill_tc" else ops.prefill_attention_bf16
             kernel(q, cache.k, cache.v, step.block_tables[cache.group], units, step.scratch.counters(), out,
                    scale=self.scale, window=self.window, part_acc=part_acc, part_ml=part_ml, tile_done=tile_done)
             return

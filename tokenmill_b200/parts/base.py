@@ -73,6 +73,7 @@ class StepInputs:
     tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
     prefill: dict[int, PrefillUnits] = field(default_factory=dict)     # by group size
     scratch: Any = None                # engine-owned scratch provider (attention partials)
+    logits_out: torch.Tensor | None = None   # where a step program writes the logits ([n_want, vocab] float32)
     split_keys: int = 0                # > 0: short-query attention cuts keys at multiples of this
     max_splits: int = 0                # number of such cuts the step may need
 

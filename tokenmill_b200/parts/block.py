@@ -48,4 +48,15 @@ class PreNormBlock:
         return Pending.of(self.feed_forward.forward(normed, step))
 
 
+    def emit(self, b, resid, pending: dict, cache: LayerCache) -> dict:
+        """The block's launches written into a step program (kernels/program.py). ``pending`` holds what the
+        first norm still has to add to the stream (``branch``: a workspace buffer, or ``ids`` and ``table``);
+        returns the same for the norm that follows the block."""
+        T = b.tokens()
+        normed = self.mixer_norm.emit(b, resid, n_rows=T, **pending)
+        mixed = self.mixer.emit(b, normed, cache)
+        normed = self.feed_forward_norm.emit(b, resid, n_rows=T, branch=mixed)
+        return {"branch": self.feed_forward.emit(b, normed)}
+
+
 register_block("pre_norm", PreNormBlock)

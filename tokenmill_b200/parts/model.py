@@ -117,6 +117,32 @@ class DecoderModel:
 
     # --- run ------------------------------------------------------------------------------------
 
+    def program(self, caches: list[LayerCache], capacity: int):
+        """The whole forward pass as a step program for steps of up to ``capacity`` tokens
+        (kernels/program.py), or None when the model is not bfloat16 or one of its parts cannot write its
+        launches down (it has no ``emit``). The program's last launch writes the logits to the address in the
+        step parameter "logits" ([n_want, vocab] float32, which the caller allocates)."""
+        from ..kernels.program import OP_GEMM_BF16, ProgramBuilder
+        s = self.spec
+        parts = [p for blk in self.blocks for p in (blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm)]
+        if self.dtype != torch.bfloat16 or not all(hasattr(p, "emit") for p in parts + [self.final_norm]):
+            return None
+        b = ProgramBuilder(self.device, self.dtype)
+        try:
+            resid = b.buffer("residual", s.hidden_size * 4)
+            pending = {"ids": b.param("token_ids", lambda st: st.token_ids.data_ptr()), "table": self.embedding}
+            for pos, entry in enumerate(s.run_order):
+                pending = self.blocks[entry.layer].emit(b, resid, pending, caches[pos])
+            n_want = b.param("n_want", lambda st: st.n_want)
+            hidden = self.final_norm.emit(b, resid, n_rows=n_want, out_tag="wanted_rows",
+                                          rows=b.param("want_rows", lambda st: st.want_rows.data_ptr()), cond=n_want,
+                                          **pending)
+            b.emit(OP_GEMM_BF16, [hidden, self.output_weight, b.param("logits", lambda st: st.logits_out.data_ptr()),
+                                  n_want, s.vocab_size, s.hidden_size, 1], cond=n_want)
+        except NotImplementedError:
+            return None
+        return b.finish(capacity)
+
     def forward(self, step: StepInputs, caches: list[LayerCache]) -> torch.Tensor:
         """Run the step's tokens; returns logits [n_want, vocab] float32."""
         s = self.spec

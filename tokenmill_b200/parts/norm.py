@@ -40,4 +40,15 @@ class RMSNorm:
                                table=table, rows=rows)
 
 
+    def emit(self, b, resid, *, n_rows, out_tag: str = "normed", branch=None, ids=None, table=None, rows=None,
+             cond=None):
+        """The same launch, written into a step program (kernels/program.py): ``resid`` and ``branch`` are
+        workspace buffers, ``ids`` / ``rows`` / ``n_rows`` step parameters. Returns the output buffer."""
+        from ..kernels.program import OP_ADD_RMSNORM, Float
+        out = b.buffer(out_tag, self.hidden_size * (torch.finfo(self.dtype).bits // 8))
+        b.emit(OP_ADD_RMSNORM, [ops.dtype_code(self.dtype), resid, branch, ids, table, rows, self.weight, Float(self.eps), out,
+                                n_rows, self.hidden_size], cond=cond)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)

@@ -47,4 +47,20 @@ class SwiGLUFeedForward:
         return ops.linear(act, self.w_down)
 
 
+    def emit(self, b, x):
+        """The prompt-step launches (library product, activation, library product) written into a step program
+        (kernels/program.py); ``x`` is a workspace buffer. Returns the output buffer."""
+        from ..kernels.program import OP_GEMM_BF16, OP_SWIGLU
+        if self.dtype != torch.bfloat16:
+            raise NotImplementedError("step programs are built for the bfloat16 path")
+        H, I, T = self.hidden_size, self.intermediate_size, b.tokens()
+        gu = b.buffer("gate_up", 2 * I * 2)
+        act = b.buffer("act", I * 2)
+        out = b.buffer("feed_forward_out", H * 2)
+        b.emit(OP_GEMM_BF16, [x, self.w_gate_up, gu, T, 2 * I, H, 0])
+        b.emit(OP_SWIGLU, [ops.dtype_code(self.dtype), gu, act, T, I])
+        b.emit(OP_GEMM_BF16, [act, self.w_down, out, T, H, I, 0])
+        return out
+
+
 register_feed_forward("swiglu", SwiGLUFeedForward)
