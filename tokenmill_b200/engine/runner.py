@@ -51,7 +51,10 @@ class ModelRunner:
         # model (bfloat16, heads of 64), else the 64 of the mma.sync kernel.
         heads = {b.mixer.D for b in model.blocks if hasattr(b.mixer, "D")}
         self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads == {64}) else 64
-        self.prefill_chunk = batch_mod.PREFILL_CHUNK     # keys of a work unit
+        # keys of a work unit: chosen per step (0) for the tcgen05 kernel, fixed for the mma.sync one
+        self.prefill_chunk = 0 if self.prefill_tile == 128 else batch_mod.PREFILL_CHUNK
+        self.kv_heads_of = {b.mixer.nh // b.mixer.nkv: b.mixer.nkv for b in model.blocks
+                            if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")}
         # Steps of more than 16 tokens run as a step program (one native call walks the launches) where every
         # part of the model can write its launches down; TOKENMILL_STEP_PROGRAM=0 keeps the per-launch path.
         self._program = None
@@ -94,7 +97,7 @@ class ModelRunner:
             if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
                 step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                          split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
-                                 prefill_chunk=self.prefill_chunk)
+                                 prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
                 self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
@@ -106,7 +109,7 @@ class ModelRunner:
             return self._graph_step(entries)
         step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                  split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
-                                 prefill_chunk=self.prefill_chunk)
+                                 prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
         self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
         prog = self._step_program(step.n_tokens)
         if prog is not None and prog.takes(step):
