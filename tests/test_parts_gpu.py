@@ -118,10 +118,12 @@ def _model_from(spec, dtype, seed):
     return model, {k: v.float() for k, v in stored.items()}
 
 
+@pytest.mark.parametrize("wide_heads", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_run_order_runs_a_layer_twice_and_shares_a_cache(dtype):
+def test_run_order_runs_a_layer_twice_and_shares_a_cache(dtype, wide_heads):
     """Layers 0, 1, 1 again (a cache of its own), then 0 again reading the first run's cache: the plain
-    model is the same walk, the shared-cache run attending over the first run's keys and values."""
+    model is the same walk, the shared-cache run attending over the first run's keys and values. With heads of
+    64 the bfloat16 prompt portion runs as a step program (an entry that reads another's cache writes none)."""
     from tokenmill_b200.cache import CacheManager
     from tokenmill_b200.cache.pool import CachePools
     from tokenmill_b200.config import Qwen2Config
@@ -133,6 +135,10 @@ def test_run_order_runs_a_layer_twice_and_shares_a_cache(dtype):
     from plain_qwen2 import plain_apply_rope, plain_causal_attention, plain_qkv
 
     raw = {**named_config("tiny-a"), "num_hidden_layers": 2, "max_position_embeddings": 256}
+    nh, nkv, D = 4, 2, 16
+    if wide_heads:
+        nh, nkv, D = 2, 1, 64
+        raw.update(hidden_size=128, num_attention_heads=nh, num_key_value_heads=nkv, head_dim=D)
     spec = qwen2_spec(Qwen2Config.from_dict(raw))
     spec = replace(spec, run_order=[RunEntry(0), RunEntry(1), RunEntry(1), RunEntry(0, cache_of=0)])
     model, w = _model_from(spec, dtype, seed=4)
@@ -146,8 +152,9 @@ def test_run_order_runs_a_layer_twice_and_shares_a_cache(dtype):
     cache.allocate(h, ids)
     got = torch.cat([runner.step([StepEntry(h, ids[a:b], a, list(range(b - a)))]) for a, b in [(0, 33), (33, 49), (49, 50)]])
 
-    cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": raw["rms_norm_eps"], "layers": 2}
-    cos, sin = plain_rope_tables(50, 16, raw["rope_theta"])
+    assert runner.stats["program_steps"] == (1 if wide_heads and dtype == torch.bfloat16 else 0)
+    cfg = {"heads": nh, "kv_heads": nkv, "head_dim": D, "eps": raw["rms_norm_eps"], "layers": 2}
+    cos, sin = plain_rope_tables(50, D, raw["rope_theta"])
     x = plain_embedding(ids, w["model.embed_tokens.weight"])
     first_kv = None
     for entry in spec.run_order:
@@ -162,8 +169,8 @@ def test_run_order_runs_a_layer_twice_and_shares_a_cache(dtype):
             normed = plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], cfg["eps"])
             q, _, _ = plain_qkv(normed, w, f"{p}.self_attn", cfg)
             q = plain_apply_rope(q, cos, sin, range(50))
-            att = plain_causal_attention(q, first_kv[0], first_kv[1], 16 ** -0.5)
-            x = x + att.reshape(50, 64) @ w[f"{p}.self_attn.o_proj.weight"].T
+            att = plain_causal_attention(q, first_kv[0], first_kv[1], D ** -0.5)
+            x = x + att.reshape(50, nh * D) @ w[f"{p}.self_attn.o_proj.weight"].T
             x = x + plain_swiglu(plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], cfg["eps"]), w, f"{p}.mlp")
     ref = plain_rmsnorm(x, w["model.norm.weight"], cfg["eps"]) @ w["model.embed_tokens.weight"].T
     assert (got.cpu() - ref).abs().max() <= tol(dtype, ref)
