@@ -534,3 +534,30 @@ def test_step_program_equals_the_launch_by_launch_path(wide_dir, monkeypatch):
         assert x.shape == y.shape and torch.isfinite(x).all()
         if x.numel():
             assert float((x - y).abs().max()) <= 3e-2 * float(y.abs().max()), float((x - y).abs().max())
+
+
+def test_output_matrix_kernel_in_the_decode_step(wide_dir, monkeypatch):
+    """With TOKENMILL_LM_HEAD=1 the whole-step decode path multiplies by the output matrix with this library's
+    streaming kernel instead of the library product: same logits within float32 summation order."""
+    from tokenmill_b200.engine.batch import StepEntry
+    rng = random.Random(11)
+    prompts = [[rng.randrange(1000) for _ in range(rng.randrange(20, 90))] for _ in range(5)]
+
+    def run(switch):
+        monkeypatch.setenv("TOKENMILL_LM_HEAD", switch)
+        eng = engine_for(wide_dir, dtype="bfloat16", max_model_len=256, max_num_seqs=8, kv_cache_mb=32,
+                         max_num_batched_tokens=1024)
+        r, cache = eng.runner, eng.cache
+        assert (r._packed_output is not None) == (switch == "1")
+        hs = []
+        for p in prompts:
+            h = cache.new_handle()
+            cache.allocate(h, p + [0, 0])
+            hs.append(h)
+        r.step([StepEntry(h, p, 0, []) for h, p in zip(hs, prompts)])
+        outs = [r.step([StepEntry(h, [3 + k], len(p) + k, [0]) for h, p in zip(hs, prompts)]).float().cpu() for k in range(2)]
+        r.fused.check()
+        return outs
+
+    for a, b in zip(run("1"), run("0")):
+        assert a.shape == (5, 1000) and float((a - b).abs().max()) <= 1e-4 * float(b.abs().max())

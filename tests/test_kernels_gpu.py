@@ -541,3 +541,24 @@ def test_kernels_refuse_what_they_cannot_do():
         ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
     with pytest.raises(KernelError, match="float32 or bfloat16"):
         ops.swiglu(torch.zeros(2, 4, device=DEV, dtype=torch.float16), torch.zeros(2, 2, device=DEV, dtype=torch.float16))
+
+
+@pytest.mark.parametrize("T", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(1000, 896), (151, 64), (4099, 136), (33000, 1024), (16, 32)])
+def test_output_matrix_streaming_kernel(T, N, K):
+    """The decode step's output matrix product from the packed copy of the matrix: vocabularies that are no
+    multiple of 8 or 16 rows, widths that are no multiple of 32, more row-group pairs than blocks and fewer;
+    rows 8..15 of the token tile unused or used. One weight row is made to stand out for one token."""
+    from tokenmill_b200.kernels.fused import pack_rows
+    ops = _ops()
+    g = torch.Generator().manual_seed(N + T)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    w[N - 1] = (x[T - 1].float() * 0.5).bfloat16()                      # the last row answers the last token
+    ref = x.float() @ w.float().t()
+    out = ops.lm_head(x.to(DEV), pack_rows(w.to(DEV)), N)
+    ops.tc_check(torch.device(DEV))
+    assert out.shape == (T, N) and out.dtype == torch.float32
+    diff = (out.cpu() - ref).abs().max()
+    assert diff <= 1e-5 * max(1.0, float(ref.abs().max())), diff
+    assert int(out[T - 1].argmax()) == N - 1

@@ -1,0 +1,192 @@
+// The output matrix product of a decode step: logits[T, N] = x[T, K] . w[N, K]^T for T <= 16 tokens and a
+// vocabulary-sized N (src/infer/model/qwen2.py:50-52: the output matrix, tied to the embedding or its own),
+// bfloat16 in, float32 accumulation and output.
+//
+// The product reads every weight once and does next to no arithmetic, so it runs at the speed of the memory:
+// 272 MB for a vocabulary of 151,936 by 896. Measured on a B200: 52 us with a clean L2 and 64 us behind a
+// kernel that left the L2 full of written lines, against 50 and 64 us for the library's kernel: both sit at
+// the rate at which the memory can be read (5.2 to 5.4 TB/s), so the engine keeps the library product unless
+// asked otherwise, and saves the packed copy. This kernel streams the weights through a ring of shared-memory stages with bulk asynchronous copies
+// that complete on mbarriers, several stages ahead of the arithmetic, from the PACKED copy of the matrix
+// ([N/8 row groups][K/32 chunks][8 rows][4 pieces][8 elements]: a stage is one contiguous range, and a
+// warp's fragment load from it is 512 contiguous bytes).
+//
+// One persistent block per SM, 8 warps. A stage holds two row groups (16 vocabulary rows). Warp w works on row
+// group w / 4 and on the quarter w % 4 of the K range, with the tokens' activations for that quarter in its
+// registers for the whole kernel (tokens are the M side of mma.m16n8k16, the 8 rows of the group its N side;
+// the k index inside a 32-element chunk is permuted the same way on both sides, so that a lane's 16-byte
+// weight load is two instructions' worth of B fragments). The four quarters of a row group meet in shared
+// memory in a fixed order, and 256 threads write the 2 x 16 x 8 results of the stage.
+//
+// The stages of the ring are filled before the kernel waits for the kernel in front of it on the stream
+// (programmatic dependent launch): the weights depend on nothing. Every mbarrier wait is bounded; a block whose
+// wait runs out raises the error word and leaves.
+#include "tcgen05_util.cuh"
+#include "mma_util.cuh"
+
+namespace tmk {
+
+constexpr int kLhThreads = 256;
+constexpr int kLhMaxChunksPerWarp = 8;      // K <= 4 * 8 * 32 = 1024
+
+struct LmHeadArgs {
+  const __nv_bfloat16* x;      // [T, K]
+  const __nv_bfloat16* w;      // packed
+  float* out;                  // [T, N]
+  int T, N, K;
+  int chunks;                  // K / 32 rounded up
+  int n_stages_total;          // row-group pairs
+  int ring;                    // stages in shared memory
+  int* error;
+};
+
+template <int CPW>   // chunks of 32 k per warp
+__global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs a) {
+  extern __shared__ __align__(1024) unsigned char lh_smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = warp >> 2, quarter = warp & 3;
+  const uint32_t group_bytes = (uint32_t)a.chunks * 512u, stage_bytes = 2u * group_bytes;
+  const uint32_t base = t5_smem(lh_smem);
+  // shared memory: ring stages, then the partial sums (2 buffers x 8 warps x 32 lanes x 4 floats), then barriers
+  float* red = reinterpret_cast<float*>(lh_smem + (size_t)a.ring * stage_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 2 * 8 * 128);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + a.ring);
+  const int n_groups = (a.N + 7) >> 3;
+
+  if (tid == 0) {
+    *s_abort = 0;
+    for (int s = 0; s < a.ring; ++s) mbar_init(t5_smem(&bars[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // this block's stages: blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int my_stages = a.n_stages_total > (int)blockIdx.x ? (a.n_stages_total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  auto issue = [&](int it) {                 // one thread: stage `it` of this block into ring slot it % ring
+    const int st = (int)blockIdx.x + it * (int)gridDim.x;
+    const int groups_here = min(2, n_groups - 2 * st);
+    const uint32_t bytes = (uint32_t)groups_here * group_bytes;
+    const uint32_t bar = t5_smem(&bars[it % a.ring]);
+    mbar_expect_tx(bar, bytes);
+    bulk_load(base + (uint32_t)(it % a.ring) * stage_bytes, reinterpret_cast<const unsigned char*>(a.w) + (size_t)st * stage_bytes,
+              bytes, bar);
+  };
+  if (tid == 0)
+    for (int it = 0; it < a.ring && it < my_stages; ++it) issue(it);
+
+  pdl_launch_dependents();
+  pdl_wait();                                // the activations come from the kernel before
+
+  // The tokens' activations for this warp's quarter of K: chunk c of the quarter, tokens g and g + 8, columns
+  // 8 t .. 8 t + 7 of the chunk.
+  uint32_t xlo[CPW][4], xhi[CPW][4];
+#pragma unroll
+  for (int c = 0; c < CPW; ++c) {
+    const int k = ((quarter * CPW + c) * 32) + 8 * t;
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+    if (quarter * CPW + c < a.chunks && k < a.K) {       // K is a multiple of 8: a piece is whole or absent
+      if (g < a.T) lo = *reinterpret_cast<const uint4*>(a.x + (size_t)g * a.K + k);
+      if (g + 8 < a.T) hi = *reinterpret_cast<const uint4*>(a.x + (size_t)(g + 8) * a.K + k);
+    }
+    xlo[c][0] = lo.x; xlo[c][1] = lo.y; xlo[c][2] = lo.z; xlo[c][3] = lo.w;
+    xhi[c][0] = hi.x; xhi[c][1] = hi.y; xhi[c][2] = hi.z; xhi[c][3] = hi.w;
+  }
+
+  int it = 0;
+  for (; it < my_stages; ++it) {
+    const int slot = it % a.ring;
+    // (A wait that runs out sets the block's abort flag; the block leaves together after the barrier below.)
+    const bool ok = mbar_wait(t5_smem(&bars[slot]), (uint32_t)(it / a.ring) & 1u, s_abort, a.error, 21);
+    float c4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ok) {
+      const uint32_t wbase = base + (uint32_t)slot * stage_bytes + (uint32_t)group * group_bytes + (uint32_t)lane * 16u;
+#pragma unroll
+      for (int c = 0; c < CPW; ++c) {
+        const int chunk = quarter * CPW + c;
+        if (chunk < a.chunks) {
+          uint32_t w0, w1, w2, w3;
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(wbase + (uint32_t)chunk * 512u));
+          const uint32_t a0[4] = {xlo[c][0], xhi[c][0], xlo[c][1], xhi[c][1]};
+          const uint32_t a1[4] = {xlo[c][2], xhi[c][2], xlo[c][3], xhi[c][3]};
+          mma_bf16_16816(c4, a0, w0, w1);
+          mma_bf16_16816(c4, a1, w2, w3);
+        }
+      }
+    }
+    float* mine = red + ((it & 1) * 8 + warp) * 128;
+    *reinterpret_cast<float4*>(mine + lane * 4) = make_float4(c4[0], c4[1], c4[2], c4[3]);
+    __syncthreads();                         // the stage has been read by everyone; the partial sums are visible
+    if (*s_abort) break;                     // the same for every thread: the flag was set before the barrier
+    if (tid == 0 && it + a.ring < my_stages) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the reads of the slot come before its refill
+      issue(it + a.ring);
+    }
+    // thread -> (row group of the stage, token, row of the group); the four quarters of K in order
+    const int grp = tid >> 7, tok = (tid >> 3) & 15, col = tid & 7;
+    const int src_lane = (tok & 7) * 4 + (col >> 1), src_reg = (tok >> 3) * 2 + (col & 1);
+    const float* p = red + ((it & 1) * 8 + grp * 4) * 128 + src_lane * 4 + src_reg;
+    const float sum = ((p[0] + p[128]) + p[256]) + p[384];
+    const int st = (int)blockIdx.x + it * (int)gridDim.x;
+    const int n = (2 * st + grp) * 8 + col;
+    if (tok < a.T && n < a.N) a.out[(size_t)tok * a.N + n] = sum;
+  }
+  // After an abort: the copies still on their way into this block's shared memory are waited for (bounded)
+  // before the block gives the memory up.
+  if (it < my_stages && tid == 0) {
+    for (int j = it + 1; j < my_stages && j < it + a.ring; ++j) {
+      const uint32_t bar = t5_smem(&bars[j % a.ring]);
+      for (uint32_t spin = 0; spin < (1u << 20) && !mbar_try(bar, (uint32_t)(j / a.ring) & 1u); ++spin) __nanosleep(64);
+    }
+  }
+}
+
+}  // namespace tmk
+
+// x [T, K] bfloat16 (T <= 16, K a multiple of 8, at most 1024), w_packed the packed copy of w [N, K] (rows
+// padded to a multiple of 8, K to a multiple of 32), out [T, N] float32. `error`: a device int that must be
+// zero; a block whose wait runs out writes 21 there instead of hanging.
+extern "C" int tm_lm_head_bf16(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error,
+                               cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (T > 16 || K <= 0 || K % 8 || !error) return TM_ERR_UNSUPPORTED_SHAPE;
+  const int chunks = (K + 31) / 32;
+  const int cpw = (chunks + 3) / 4;
+  if (cpw > tmk::kLhMaxChunksPerWarp) return TM_ERR_UNSUPPORTED_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_packed)) & 15) return TM_ERR_UNSUPPORTED_SHAPE;
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  }
+  tmk::LmHeadArgs a{};
+  a.x = (const __nv_bfloat16*)x; a.w = (const __nv_bfloat16*)w_packed; a.out = out;
+  a.T = T; a.N = N; a.K = K; a.chunks = chunks; a.error = error;
+  const int n_groups = (N + 7) / 8;
+  a.n_stages_total = (n_groups + 1) / 2;
+  const size_t stage_bytes = (size_t)2 * chunks * 512;
+  const size_t fixed = 2 * 8 * 128 * sizeof(float) + 64 * sizeof(uint64_t) + 64;
+  int ring = (int)((200 * 1024 - fixed) / stage_bytes);
+  if (ring > 32) ring = 32;
+  if (ring < 2) return TM_ERR_UNSUPPORTED_SHAPE;
+  a.ring = ring;
+  const size_t smem = (size_t)ring * stage_bytes + fixed;
+  const int grid = a.n_stages_total < n_sm ? a.n_stages_total : n_sm;
+#define LH_CASE(C)                                                                                               \
+  {                                                                                                              \
+    auto kern = tmk::lm_head_kernel<C>;                                                                          \
+    static bool set = false;                                                                                     \
+    if (!set) {                                                                                                  \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);       \
+      if (e != cudaSuccess) return (int)e;                                                                       \
+      set = true;                                                                                                \
+    }                                                                                                            \
+    return tmk::launch_pdl(kern, dim3(grid), dim3(tmk::kLhThreads), smem, stream, a);                            \
+  }
+  if (cpw <= 1) LH_CASE(1)
+  if (cpw <= 2) LH_CASE(2)
+  if (cpw <= 4) LH_CASE(4)
+  if (cpw <= 7) LH_CASE(7)
+  LH_CASE(8)
+#undef LH_CASE
+}

@@ -68,6 +68,13 @@ class ModelRunner:
         self.fused = None
         if fused.eligible(model) and len(self.layout.groups) == 1:
             self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len)
+        # The output matrix of those steps is the library product. With TOKENMILL_LM_HEAD=1 this library's own
+        # streaming kernel takes it from a packed copy of the matrix (as much memory again); both run at the
+        # memory's read rate (50 us against 52 us for 272 MB), so the copy is not made by default.
+        self._packed_output = None
+        if self.fused is not None and ops.lm_head_ok(1, model.spec.hidden_size) and \
+                os.environ.get("TOKENMILL_LM_HEAD", "0") == "1":
+            self._packed_output = fused.pack_rows(model.output_weight)
         if self.graph_max_batch:
             if any(s < 0 for s in pools.sink):
                 raise RuntimeError("decode graphs need pools built with a sink page")
@@ -93,7 +100,7 @@ class ModelRunner:
                 self.stats["fused_steps"] += 1
                 hidden = self.fused.run_decode(entries, self.cache.page_size)
                 self.stats["h2d_bytes"] = self.fused.h2d_bytes
-                return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
+                return self._decode_logits(hidden)
             if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
                 step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                          split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
@@ -102,7 +109,7 @@ class ModelRunner:
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
                     hidden = self.fused.run(step, self.cache.page_size)
-                    return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
+                    return self._decode_logits(hidden)
                 return self.model.forward(step, self.layer_caches)
         if self.graph_max_batch and len(entries) <= self.graph_max_batch and \
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
@@ -123,6 +130,12 @@ class ModelRunner:
         if self.model.dtype == torch.bfloat16 and (step.n_tokens >= ops.TC_MIN_TOKENS or self.prefill_tile == 128):
             ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
         return logits
+
+    def _decode_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Logits of a whole-step decode: hidden [T <= 16, H] times the output matrix."""
+        if self._packed_output is not None and ops.lm_head_ok(hidden.shape[0], hidden.shape[1]):
+            return ops.lm_head(hidden, self._packed_output, self.model.spec.vocab_size, error=self.fused.error)
+        return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
 
     def _step_program(self, n_tokens: int):
         """The model's step program with room for ``n_tokens`` (built on first need, rebuilt with a larger
@@ -156,7 +169,7 @@ class ModelRunner:
         self.stats["fused_steps"] += 1
         hidden = self.fused.run_decode(entries, self.cache.page_size, token_src=token_src, token_rows=token_rows)
         self.stats["h2d_bytes"] = self.fused.h2d_bytes
-        return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
+        return self._decode_logits(hidden)
 
     # --- decode graphs --------------------------------------------------------------------------
 

@@ -287,5 +287,6 @@ class FusedDecoder:
             self.error.zero_()
             self.bar.zero_()
             self.attn_count.zero_()
-            raise lib.KernelError(f"the fused decode kernel gave up at grid barrier {code - 100}; the step's "
-                                  f"results are incomplete")
+            what = "the output matrix kernel gave up waiting for its weights" if code == 21 else \
+                f"the fused decode kernel gave up at grid barrier {code - 100}"
+            raise lib.KernelError(f"{what}; the step's results are incomplete")

@@ -346,6 +346,30 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None
     return out
 
 
+LM_HEAD_MAX_TOKENS, LM_HEAD_MAX_K = 16, 1024
+
+
+def lm_head_ok(T: int, K: int) -> bool:
+    """Whether the streaming output-matrix kernel takes a product of T tokens over K columns."""
+    return 0 < T <= LM_HEAD_MAX_TOKENS and K % 8 == 0 and K <= LM_HEAD_MAX_K
+
+
+def lm_head(x: torch.Tensor, w_packed: torch.Tensor, n_rows: int, error: torch.Tensor | None = None) -> torch.Tensor:
+    """x [T, K] bfloat16 (T <= 16) times the output matrix, given as its packed copy (kernels/fused.py
+    pack_rows of w [n_rows, K]) -> logits [T, n_rows] float32. The weights stream through shared memory at
+    memory speed; the kernel's waits are bounded and report (code 21) through ``error``, an int32 device word
+    that is zero, by default the word that tc_check reads."""
+    T, K = x.shape
+    if not lm_head_ok(T, K) or x.dtype != torch.bfloat16 or w_packed.dtype != torch.bfloat16:
+        raise lib.KernelError(f"lm_head: {T} tokens of {K} columns in {x.dtype} are not taken")
+    if w_packed.dim() != 5 or w_packed.shape[0] * 8 < n_rows or w_packed.shape[1] * 32 < K or not w_packed.is_contiguous():
+        raise lib.KernelError("lm_head: the packed matrix does not fit the sizes given")
+    out = torch.empty((T, n_rows), dtype=torch.float32, device=x.device)
+    lib.call("tm_lm_head_bf16", _req(x, "x", torch.bfloat16), w_packed.data_ptr(), out.data_ptr(), T, n_rows, K,
+             (error if error is not None else _tc_flag(x.device)).data_ptr(), _stream())
+    return out
+
+
 def skinny_qkv_rope_write(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor,
                           cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
                           kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, D: int) -> None:
@@ -396,7 +420,8 @@ def tc_check(device: torch.device) -> None:
         if code:
             flag.zero_()
             raise lib.KernelError(f"a tcgen05 block gave up waiting (code {code}: matrix product 1 loader, 2/3 issuer, "
-                                  f"4 epilogue; attention 11/13 second product, 12 scores); its results are incomplete")
+                                  f"4 epilogue; attention 11/13 second product, 12 scores, 14 merge; 21 output matrix stream); "
+                                  f"its results are incomplete")
 
 
 def tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
