@@ -561,3 +561,55 @@ def test_output_matrix_kernel_in_the_decode_step(wide_dir, monkeypatch):
 
     for a, b in zip(run("1"), run("0")):
         assert a.shape == (5, 1000) and float((a - b).abs().max()) <= 1e-4 * float(b.abs().max())
+
+
+@pytest.mark.parametrize("inter,expect", [(8960, "some"), (13312, "none")])
+def test_whole_step_kernel_leaves_wide_models_to_the_other_kernels(tmp_path, inter, expect):
+    """A feed-forward so wide that the staged activations of many tokens leave no room for a ring stage: the
+    whole-step kernel says how many tokens it takes at these sizes (none at all for the widest), steps beyond
+    that run through the separate kernels, and the logits agree either way."""
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.kernels import fused
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    cfg = qwen2_config(vocab_size=500, hidden_size=256, intermediate_size=inter, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=128, rope_theta=10000.0,
+                       tie_word_embeddings=True, max_position_embeddings=512)
+    folder = write_random_model(tmp_path / "m", cfg, seed=2)
+    rng = random.Random(inter)
+    prompts = [[rng.randrange(500) for _ in range(rng.randrange(5, 60))] for _ in range(16)]
+
+    def run(use_fused, batches):
+        old = fused._ENABLED
+        fused._ENABLED = use_fused
+        try:
+            eng = engine_for(folder, dtype="bfloat16", max_model_len=128, max_num_seqs=16, kv_cache_mb=16,
+                             max_num_batched_tokens=1024)
+        finally:
+            fused._ENABLED = old
+        r, cache = eng.runner, eng.cache
+        hs = []
+        for p in prompts:
+            h = cache.new_handle()
+            cache.allocate(h, p + [0] * len(batches))
+            hs.append(h)
+        r.step([StepEntry(h, p, 0, []) for h, p in zip(hs, prompts)])
+        outs = [r.step([StepEntry(h, [3 + k], len(p) + k, [0]) for h, p in list(zip(hs, prompts))[:b]]).float().cpu()
+                for k, b in enumerate(batches)]
+        if r.fused is not None:
+            r.fused.check()
+        return r, outs
+
+    r0, _ = run(True, [])
+    if expect == "none":
+        assert r0.fused is None
+        batches = [1, 8]
+    else:
+        limit = r0.fused.max_tokens
+        assert 1 <= limit < 16
+        batches = [1, limit, limit + 1, 16]
+    ra, a = run(True, batches)
+    rb, b = run(False, batches)
+    if expect == "some":
+        assert ra.stats["fused_steps"] == 2 and rb.stats["fused_steps"] == 0
+    for x, y in zip(a, b):
+        assert torch.isfinite(x).all() and float((x - y).abs().max()) <= 3e-2 * float(y.abs().max())

@@ -1125,6 +1125,39 @@ static int fu_host_row_bytes(int K) {           // fu_row_bytes for the host
   return kpad * 2 + ((64 - (kpad * 2) % 128) + 128) % 128;
 }
 
+// How a step of T tokens is laid out in the block's shared memory: the bytes of a ring stage and whether the
+// down projection's input comes in two passes of 8 rows. False when the sizes leave no room for a ring stage
+// beside the staged activations (wide models at many tokens): such steps are not for this kernel.
+template <int D>
+bool fu_plan(int H, int nh, int I, int T, int n_sm, int smem, int* stage_bytes_out, bool* halves_out) {
+  const int rb_h = fu_host_row_bytes(H), rb_q = fu_host_row_bytes(nh * D), rb_i = fu_host_row_bytes(I);
+  const int rb_narrow = rb_h > rb_q ? rb_h : rb_q, rb_max = rb_narrow > rb_i ? rb_narrow : rb_i;
+  const int red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
+  // A stage holds a row group and its partner over all of H when that fits 32 KB, else 32 KB worth of chunks.
+  const int ch_h = (H + 31) / 32;
+  const int stage_bytes = 2 * ch_h * 512 <= 32768 ? 2 * ch_h * 512 : 32768;
+  auto ring_offset = [&](int xs_bytes) {      // the staging area doubles as attention's working memory
+    const int work = xs_bytes + red_bytes > fu_attn_min_bytes<D>() ? xs_bytes + red_bytes : fu_attn_min_bytes<D>();
+    return (work + 127) / 128 * 128;
+  };
+  const int rows = T > 8 ? T : 8;
+  // Steps of 9 to 16 tokens: the down projection's input (T rows of I columns) would take the room of most
+  // ring stages. Where every block has at most one down-projection unit and the unit's tiles all fit the ring
+  // at once, the input comes in two passes of 8 rows instead and the staging area stays as for 8 tokens.
+  const int xs_halves = 8 * rb_max > rows * rb_narrow ? 8 * rb_max : rows * rb_narrow;
+  int nst_halves = (smem - ring_offset(xs_halves)) / stage_bytes;
+  if (nst_halves > kFuMaxStages) nst_halves = kFuMaxStages;
+  const int cpt_single = stage_bytes / 512, kd = ((I + 31) / 32 + cpt_single - 1) / cpt_single;
+  const int nst_rows = (smem - ring_offset(rows * rb_max)) / stage_bytes;
+  // (Measured at the 0.5B sizes: with two or more stages left, staging all rows in one pass is as fast or faster.)
+  const bool halves = T > 8 && nst_rows <= 1 && (H + 7) / 8 <= n_sm && kd <= nst_halves;
+  const int xs_bytes = halves ? xs_halves : rows * rb_max;
+  if (ring_offset(xs_bytes) + stage_bytes > smem) return false;
+  *stage_bytes_out = stage_bytes;
+  *halves_out = halves;
+  return true;
+}
+
 template <int D>
 int launch_decode_fused(const FusedArgs& a, cudaStream_t stream) {
   auto kern = decode_fused_kernel<D>;
@@ -1141,29 +1174,10 @@ int launch_decode_fused(const FusedArgs& a, cudaStream_t stream) {
       return e != cudaSuccess ? (int)e : TM_ERR_UNSUPPORTED_SHAPE;
     }
   }
-  const int rb_h = fu_host_row_bytes(a.H), rb_q = fu_host_row_bytes(a.nh * a.D), rb_i = fu_host_row_bytes(a.I);
-  const int rb_narrow = rb_h > rb_q ? rb_h : rb_q, rb_max = rb_narrow > rb_i ? rb_narrow : rb_i;
-  const int red_bytes = kFuWarps * 2 * 16 * 8 * (int)sizeof(float);
-  // A stage holds a row group and its partner over all of H when that fits 32 KB, else 32 KB worth of chunks.
-  const int ch_h = (a.H + 31) / 32;
-  const int stage_bytes = 2 * ch_h * 512 <= 32768 ? 2 * ch_h * 512 : 32768;
-  auto ring_offset = [&](int xs_bytes) {      // the staging area doubles as attention's working memory
-    const int work = xs_bytes + red_bytes > fu_attn_min_bytes<D>() ? xs_bytes + red_bytes : fu_attn_min_bytes<D>();
-    return (work + 127) / 128 * 128;
-  };
-  const int rows = a.T > 8 ? a.T : 8;
-  // Steps of 9 to 16 tokens: the down projection's input (T rows of I columns) would take the room of most
-  // ring stages. Where every block has at most one down-projection unit and the unit's tiles all fit the ring
-  // at once, the input comes in two passes of 8 rows instead and the staging area stays as for 8 tokens.
-  const int xs_halves = 8 * rb_max > rows * rb_narrow ? 8 * rb_max : rows * rb_narrow;
-  int nst_halves = (smem - ring_offset(xs_halves)) / stage_bytes;
-  if (nst_halves > kFuMaxStages) nst_halves = kFuMaxStages;
-  const int cpt_single = stage_bytes / 512, kd = ((a.I + 31) / 32 + cpt_single - 1) / cpt_single;
-  const int nst_rows = (smem - ring_offset(rows * rb_max)) / stage_bytes;
-  // (Measured at the 0.5B sizes: with two or more stages left, staging all rows in one pass is as fast or faster.)
-  const bool halves = a.T > 8 && nst_rows <= 1 && (a.H + 7) / 8 <= n_sm && kd <= nst_halves;
-  const int xs_bytes = halves ? xs_halves : rows * rb_max;
-  if (ring_offset(xs_bytes) + stage_bytes > smem || a.n_layers > kFuMaxLayers) return TM_ERR_UNSUPPORTED_SHAPE;
+  int stage_bytes = 0;
+  bool halves = false;
+  if (!fu_plan<D>(a.H, a.nh, a.I, a.T, n_sm, smem, &stage_bytes, &halves) || a.n_layers > kFuMaxLayers)
+    return TM_ERR_UNSUPPORTED_SHAPE;
   FusedArgs args = a;
   args.smem_bytes = smem;
   args.stage_bytes = stage_bytes;
@@ -1186,6 +1200,21 @@ extern "C" int tm_decode_fused(const void* args, cudaStream_t stream) {
   if (a.D == 64) return tmk::launch_decode_fused<64>(a, stream);
   if (a.D == 128) return tmk::launch_decode_fused<128>(a, stream);
   return TM_ERR_UNSUPPORTED_SHAPE;
+}
+
+// The largest number of tokens (0 to 16) a step of these sizes may have for tm_decode_fused: every count up to
+// it has room in shared memory for its staged activations and at least one ring stage. `n_sm`: the device's SMs.
+extern "C" int tm_decode_fused_max_tokens(int H, int nh, int nkv, int D, int I, int n_sm) {
+  if (H % 8 || I % 8 || (nh * D) % 8 || nkv <= 0 || nh % nkv || nh / nkv > 16 || (D != 64 && D != 128)) return 0;
+  int best = 0, stage = 0;
+  bool halves = false;
+  for (int T = 1; T <= 16; ++T) {
+    const bool ok = D == 64 ? tmk::fu_plan<64>(H, nh, I, T, n_sm, 212 * 1024, &stage, &halves)
+                            : tmk::fu_plan<128>(H, nh, I, T, n_sm, 212 * 1024, &stage, &halves);
+    if (!ok) break;
+    best = T;
+  }
+  return best;
 }
 
 extern "C" int tm_decode_fused_args_size() { return (int)sizeof(tmk::FusedArgs); }

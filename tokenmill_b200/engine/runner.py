@@ -68,6 +68,8 @@ class ModelRunner:
         self.fused = None
         if fused.eligible(model) and len(self.layout.groups) == 1:
             self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len)
+            if self.fused.max_tokens == 0:          # not even one token fits beside a ring stage at these sizes
+                self.fused = None
         # The output matrix of those steps is the library product. With TOKENMILL_LM_HEAD=1 this library's own
         # streaming kernel takes it from a packed copy of the matrix (as much memory again); both run at the
         # memory's read rate (50 us against 52 us for 272 MB), so the copy is not made by default.
@@ -96,12 +98,12 @@ class ModelRunner:
         self.stats["tokens"] += sum(len(e.tokens) for e in entries)
         if self.fused is not None:
             self.fused.check()
-            if len(entries) <= fused.MAX_TOKENS and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+            if len(entries) <= self.fused.max_tokens and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
                 self.stats["fused_steps"] += 1
                 hidden = self.fused.run_decode(entries, self.cache.page_size)
                 self.stats["h2d_bytes"] = self.fused.h2d_bytes
                 return self._decode_logits(hidden)
-            if sum(len(e.tokens) for e in entries) <= fused.MAX_TOKENS:
+            if sum(len(e.tokens) for e in entries) <= self.fused.max_tokens:
                 step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                          split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
                                  prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
@@ -151,7 +153,7 @@ class ModelRunner:
 
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
         """Whether ``step_fed`` takes a decode step of this many requests."""
-        return self.fused is not None and 0 < n_entries <= fused.MAX_TOKENS
+        return self.fused is not None and 0 < n_entries <= self.fused.max_tokens
 
     @torch.inference_mode()
     def step_fed(self, entries: list[StepEntry], token_src: torch.Tensor, token_rows: list[int]) -> torch.Tensor:

@@ -85,6 +85,10 @@ def eligible(model) -> bool:
             and first.q_size % 8 == 0 and first.nh // first.nkv <= 16 and len(model.cache_layout().groups) == 1)
 
 
+def dev_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
 def pack_rows(w: torch.Tensor) -> torch.Tensor:
     """The copy of a [N, K] weight matrix the fused kernel streams: [N/8 row groups][K/32 chunks][8 rows]
     [4 pieces][8 elements], padded with zeros, so that the 32 lanes of a warp, lane 4 g + t holding row g and
@@ -109,6 +113,10 @@ class FusedDecoder:
         m0, f0 = first.mixer, first.feed_forward
         self.H, self.nh, self.nkv, self.D, self.I = model.spec.hidden_size, m0.nh, m0.nkv, m0.D, f0.intermediate_size
         self.max_splits_cap = -(-max_model_len // SPLIT_KEYS)
+        # Tokens a step may bring at these sizes: wide models leave no room for a ring stage beside the staged
+        # activations of many tokens (the fallback is the kernel-per-operation path).
+        n_sm = torch.cuda.get_device_properties(dev_index(model.device)).multi_processor_count
+        self.max_tokens = int(lib.load().tm_decode_fused_max_tokens(self.H, self.nh, self.nkv, self.D, self.I, n_sm))
         layers = (_Layer * len(order))()
         self._packed: dict[int, tuple[torch.Tensor, ...]] = {}      # by layer: a layer run twice is packed once
         for i, e in enumerate(order):
@@ -179,8 +187,8 @@ class FusedDecoder:
 
     def takes(self, step) -> bool:
         G = self.nh // self.nkv
-        return (step.n_tokens <= MAX_TOKENS and step.max_q_len * G <= 16 and step.n_want > 0
-                and step.n_want <= MAX_TOKENS and len(step.block_tables) == 1)
+        return (step.n_tokens <= self.max_tokens and step.max_q_len * G <= 16 and step.n_want > 0
+                and step.n_want <= self.max_tokens and len(step.block_tables) == 1)
 
     # --- plain decode steps: metadata written straight into a pinned ring, no intermediate objects --------
 

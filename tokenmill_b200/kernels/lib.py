@@ -52,6 +52,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_tc_gate_up_swiglu": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "tm_tc_qkv_rope_write": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "tm_decode_fused": [_P, _P],
+    "tm_decode_fused_max_tokens": [_I, _I, _I, _I, _I, _I],
     "tm_lm_head_bf16": [_P, _P, _P, _I, _I, _I, _P, _P],
     "tm_gemm_f32_nt": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "tm_argmax": [_P, _I, _I, _LL, _P, _P, _P, _P],
