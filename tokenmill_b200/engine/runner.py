@@ -51,8 +51,7 @@ class ModelRunner:
         # model (bfloat16, heads of 64), else the 64 of the mma.sync kernel.
         heads = {b.mixer.D for b in model.blocks if hasattr(b.mixer, "D")}
         self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads == {64}) else 64
-        # keys of a work unit: chosen per step (0) for the tcgen05 kernel, fixed for the mma.sync one
-        self.prefill_chunk = 0 if self.prefill_tile == 128 else batch_mod.PREFILL_CHUNK
+        self.prefill_chunk = 0          # keys of a work unit: chosen per step (batch.choose_chunk)
         self.kv_heads_of = {b.mixer.nh // b.mixer.nkv: b.mixer.nkv for b in model.blocks
                             if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")}
         # Steps of more than 16 tokens run as a step program (one native call walks the launches) where every
