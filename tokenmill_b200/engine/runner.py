@@ -150,9 +150,17 @@ class ModelRunner:
                 self._no_program = True
         return self._program
 
+    @property
+    def feeds_tokens_on_device(self) -> bool:
+        """Whether some decode steps can take their token ids from the device (``step_fed``)."""
+        return self.fused is not None or self.graph_max_batch > 0
+
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
-        """Whether ``step_fed`` takes a decode step of this many requests."""
-        return self.fused is not None and 0 < n_entries <= self.fused.max_tokens
+        """Whether ``step_fed`` takes a decode step of this many requests: the whole-step kernel reads the ids
+        itself, a captured graph has them gathered into its static input buffer."""
+        if self.fused is not None and 0 < n_entries <= self.fused.max_tokens:
+            return True
+        return 0 < n_entries <= self.graph_max_batch
 
     @torch.inference_mode()
     def step_fed(self, entries: list[StepEntry], token_src: torch.Tensor, token_rows: list[int]) -> torch.Tensor:
@@ -164,9 +172,11 @@ class ModelRunner:
         for e in entries:
             if e.start + 1 > self.max_model_len:
                 raise ValueError(f"a request would reach {e.start + 1} tokens; max_model_len is {self.max_model_len}")
-        self.fused.check()
         self.stats["steps"] += 1
         self.stats["tokens"] += len(entries)
+        if self.fused is None or len(entries) > self.fused.max_tokens:
+            return self._graph_step(entries, token_src, token_rows)
+        self.fused.check()
         self.stats["fused_steps"] += 1
         hidden = self.fused.run_decode(entries, self.cache.page_size, token_src=token_src, token_rows=token_rows)
         self.stats["h2d_bytes"] = self.fused.h2d_bytes
@@ -181,7 +191,8 @@ class ModelRunner:
             if hasattr(m, "nh"):
                 self.scratch.reserve(batch * m.nh, max_splits, m.D)
 
-    def _graph_step(self, entries: list[StepEntry]) -> torch.Tensor:
+    def _graph_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
+                    token_rows: list[int] | None = None) -> torch.Tensor:
         n = len(entries)
         sizes = [b for b in GRAPH_BATCH_SIZES if b < self.graph_max_batch] + [self.graph_max_batch]
         bucket = sizes[bisect.bisect_left(sizes, n)]
@@ -191,7 +202,7 @@ class ModelRunner:
             self._graphs[bucket] = g
         self.stats["graph_steps"] += 1
         self.stats["h2d_bytes"] = g.lay.total * 4
-        return g.run(entries)
+        return g.run(entries, token_src, token_rows)
 
 
 class _DecodeGraph:
@@ -200,6 +211,8 @@ class _DecodeGraph:
     def __init__(self, runner: ModelRunner, bucket: int):
         self.r, self.bucket = runner, bucket
         self._copied: torch.cuda.Event | None = None
+        self._rows_host: torch.Tensor | None = None
+        self._rows_dev: torch.Tensor | None = None
         cache, dev = runner.cache, runner.device
         ps = cache.page_size
         self.width = -(-runner.max_model_len // ps)
@@ -275,11 +288,23 @@ class _DecodeGraph:
                     raise RuntimeError("a decoded token would be written into a page already given back")
                 slots[i] = page * ps + e.start % ps
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor:
+    def run(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
+            token_rows: list[int] | None = None) -> torch.Tensor:
+        """Replay the step. With ``token_src`` (int32, on the device) entry i's token is
+        token_src[token_rows[i]], gathered into the static input buffer behind the metadata copy: the host
+        need not know the ids yet."""
         if self._copied is not None:
-            self._copied.synchronize()       # the pinned buffer is about to be rewritten
+            self._copied.synchronize()       # the pinned buffers are about to be rewritten
         self._fill(entries)
         self.dev.copy_(self.host, non_blocking=True)
+        if token_src is not None:
+            n = len(entries)
+            if self._rows_host is None:
+                self._rows_host = torch.zeros(self.bucket, dtype=torch.int64, pin_memory=True)
+                self._rows_dev = torch.zeros(self.bucket, dtype=torch.int64, device=self.dev.device)
+            self._rows_host[:n] = torch.as_tensor(token_rows, dtype=torch.int64)
+            self._rows_dev.copy_(self._rows_host, non_blocking=True)
+            torch.index_select(token_src, 0, self._rows_dev[:n], out=self.dev[self.lay.token_ids][:n])
         if self._copied is None:
             self._copied = torch.cuda.Event()
         self._copied.record()
