@@ -240,7 +240,7 @@ class LLMEngine:
         outputs: list[RequestOutput] = []
         nxt, leftover = None, None
         t0 = time.perf_counter()
-        if not self.scheduler.waiting and self._pipelining():
+        if self._pipelining():
             for seq, at in zip(cur.seqs, cur.index):
                 # Ends the host can foresee: the step in flight brings the request's last token.
                 if not seq.is_finished and (at + 1 >= seq.params.max_tokens or
