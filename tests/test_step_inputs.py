@@ -1,0 +1,79 @@
+"""Host-side planning of a step's attention work and of step programs (no GPU needed)."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from tokenmill_b200.engine.batch import PREFILL_CHUNK, choose_chunk, packed_units
+
+
+def _keys_per_tile(q_lens, starts, G, tile):
+    out = []
+    for n, s in zip(q_lens, starts):
+        rows = n * G
+        for r0 in range(0, rows, tile):
+            out.append(s + (min(r0 + tile, rows) - 1) // G + 1)
+    return out
+
+
+def test_chunk_choice_is_a_power_of_two_multiple_of_512_and_follows_the_step():
+    G, nkv = 7, 2
+    picks = {}
+    for T in (1024, 2048, 4096, 8192):
+        for tile in (64, 128):
+            c = choose_chunk(np.array([T]), np.array([0]), G, nkv, tile=tile)
+            assert c % PREFILL_CHUNK == 0 and (c // PREFILL_CHUNK) & (c // PREFILL_CHUNK - 1) == 0
+            picks[T, tile] = c
+    # a short prompt keeps short chunks (few tiles: they must spread), long prompts take long ones
+    assert picks[1024, 128] == 512 and picks[2048, 128] == 1024 and picks[8192, 128] == 8192
+    assert picks[1024, 64] == 512 and picks[8192, 64] >= 4096
+    # a late portion of a long prompt: few tiles, every one with thousands of keys -> cut, but not finely
+    assert choose_chunk(np.array([1024]), np.array([3072]), G, nkv, tile=128) == 2048
+    # nothing but single tokens and a tiny prompt: the base size
+    assert choose_chunk(np.array([1, 1, 5]), np.array([900, 30, 0]), G, nkv, tile=128) == PREFILL_CHUNK
+    assert choose_chunk(np.zeros(0, dtype=np.int64), np.zeros(0, dtype=np.int64), G, nkv) == PREFILL_CHUNK
+
+
+def test_units_cover_every_tile_s_keys_once_for_any_chunk():
+    rng = np.random.default_rng(0)
+    for _ in range(20):
+        S = int(rng.integers(1, 5))
+        q_lens = rng.integers(1, 400, S)
+        starts = rng.integers(0, 3000, S)
+        G = int(rng.choice([1, 3, 7]))
+        tile = int(rng.choice([64, 128]))
+        chunk = int(rng.choice([128, 512, 1024, 4096]))
+        rec, n_tiles, n_slots = packed_units(q_lens, starts, G, tile=tile, chunk=chunk)
+        keys = _keys_per_tile(q_lens.tolist(), starts.tolist(), G, tile)
+        assert n_tiles == len(keys)
+        covered = {}
+        for seq, row0, packed, slot0, t, q_start, q_len, before in rec.tolist():
+            c, n = packed & 0xffff, packed >> 16
+            assert n == -(-keys[t] // chunk) and 0 <= c < n and q_len == q_lens[seq] and before == starts[seq]
+            assert (slot0 == -1) == (n == 1)
+            covered.setdefault(t, []).append(c)
+        assert all(sorted(v) == list(range(len(v))) for v in covered.values()) and len(covered) == n_tiles
+        assert n_slots == sum(len(v) for v in covered.values() if len(v) > 1)
+        # heaviest first
+        work = [min(chunk, keys[t] - (p & 0xffff) * chunk) for _, _, p, _, t, _, _, _ in rec.tolist()]
+        assert work == sorted(work, reverse=True)
+
+
+def test_program_builder_shares_parameters_and_buffers_by_name():
+    from tokenmill_b200.kernels.program import OP_SWIGLU, Buffer, Param, ProgramBuilder
+    b = ProgramBuilder(torch.device("cpu"), torch.bfloat16)
+    t1, t2 = b.tokens(), b.tokens()
+    assert t1 == t2 == Param(0) and len(b.providers) == 1
+    p = b.param("n_want", lambda s: s.n_want)
+    assert p == Param(1) and b.param("n_want", lambda s: -1) == p and len(b.providers) == 2
+    x = b.buffer("act", 64)
+    y = b.buffer("act", 128)            # the same buffer, grown to the larger row
+    assert x.tag == y.tag == "act" and b.buffers["act"] == Buffer("act", 128)
+    b.emit(OP_SWIGLU, [2, x, y, t1, 32], cond=p)
+    assert b.ops == [(OP_SWIGLU, p, [2, x, y, t1, 32])]
+    try:
+        b.emit(OP_SWIGLU, list(range(25)))
+        assert False, "a record of 25 values must be refused"
+    except ValueError:
+        pass
