@@ -176,3 +176,63 @@ def test_run_order_runs_a_layer_twice_and_shares_a_cache(dtype, wide_heads):
     assert (got.cpu() - ref).abs().max() <= tol(dtype, ref)
     cache.free(h)
     assert cache.all_free
+
+
+@pytest.mark.parametrize("case", ["tiny-one-layer", "wide-one-layer", "wide-all-layers"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_windowed_mixers_through_the_runner(dtype, case):
+    """Attention with a window of 40 keys in one layer (a cache group of its own beside the full-attention
+    layer's) or in every layer (one group; with heads of 64 in bfloat16 the tcgen05 prompt kernel, the step
+    program and the whole-step decode kernel all see the window): prompt portions, then tokens one by one, with
+    the pages behind the window given back after every step, against the plain walk with the same window."""
+    from tokenmill_b200.cache import CacheManager
+    from tokenmill_b200.cache.pool import CachePools
+    from tokenmill_b200.config import Qwen2Config
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.engine.runner import ModelRunner
+    from tokenmill_b200.models.qwen2 import qwen2_spec
+    from tokenmill_b200.weights import named_config
+
+    W, n = 40, 150
+    raw = {**named_config("tiny-a"), "num_hidden_layers": 2, "max_position_embeddings": 256}
+    nh, nkv, D = 4, 2, 16
+    if case.startswith("wide"):
+        nh, nkv, D = 2, 1, 64
+        raw.update(hidden_size=128, num_attention_heads=nh, num_key_value_heads=nkv, head_dim=D)
+    spec = qwen2_spec(Qwen2Config.from_dict(raw))
+    windowed = [0, 1] if case.endswith("all-layers") else [1]
+    layers = [replace(l, mixer=replace(l.mixer, params={**l.mixer.params, "window": W})) if i in windowed else l
+              for i, l in enumerate(spec.layers)]
+    spec = replace(spec, layers=layers)
+    model, w = _model_from(spec, dtype, seed=9)
+    layout = model.cache_layout()
+    assert len(layout.groups) == (1 if case.endswith("all-layers") else 2)
+    pages = [14] * len(layout.groups)
+    cache = CacheManager(pages, 16, windows=[g.need.window for g in layout.groups], watermark=0.0)
+    pools = CachePools(layout, pages, 16, dtype, DEV, run_order_cache_of=[e.cache_of for e in spec.run_order])
+    runner = ModelRunner(model, cache, pools, max_model_len=256)
+    ids = torch.randint(0, 256, (n,), generator=torch.Generator().manual_seed(2)).tolist()
+    h = cache.new_handle()
+    cache.allocate(h, ids)
+    cuts = [(0, 70), (70, 101)] + [(i, i + 1) for i in range(101, n)]
+    got, freed = [], 0
+    for a, b in cuts:
+        got.append(runner.step([StepEntry(h, ids[a:b], a, list(range(b - a)))]))
+        freed += cache.release_behind_window(h, b)
+    got = torch.cat(got)
+    assert freed >= (n - W) // 16 - 1              # the windowed group gave its old pages back on the way
+    if case == "wide-all-layers" and dtype == torch.bfloat16:
+        assert runner.fused is not None and runner.stats["fused_steps"] == n - 101 and runner.stats["program_steps"] == 2
+
+    cfg = {"heads": nh, "kv_heads": nkv, "head_dim": D, "eps": raw["rms_norm_eps"], "layers": 2}
+    cos, sin = plain_rope_tables(n, D, raw["rope_theta"])
+    x = plain_embedding(ids, w["model.embed_tokens.weight"])
+    for i in range(2):
+        p = f"model.layers.{i}"
+        x = x + plain_attention_block(plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], cfg["eps"]), w,
+                                      f"{p}.self_attn", cfg, cos, sin, window=W if i in windowed else None)
+        x = x + plain_swiglu(plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], cfg["eps"]), w, f"{p}.mlp")
+    ref = plain_rmsnorm(x, w["model.norm.weight"], cfg["eps"]) @ w["model.embed_tokens.weight"].T
+    assert (got.cpu() - ref).abs().max() <= tol(dtype, ref)
+    cache.free(h)
+    assert cache.all_free
