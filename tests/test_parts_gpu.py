@@ -236,3 +236,48 @@ def test_windowed_mixers_through_the_runner(dtype, case):
     assert (got.cpu() - ref).abs().max() <= tol(dtype, ref)
     cache.free(h)
     assert cache.all_free
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layers_with_different_mixers_and_feed_forwards(dtype):
+    """One model, three layers that differ: 2 query heads over 1 kv head, then 2 over 2 (another group size and
+    another cache group), then 2 over 1 with a feed-forward twice as wide. Each part takes its sizes from its own
+    parameters; in bfloat16 (heads of 64) the step program holds all three."""
+    from tokenmill_b200.cache import CacheManager
+    from tokenmill_b200.cache.pool import CachePools
+    from tokenmill_b200.config import Qwen2Config
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.engine.runner import ModelRunner
+    from tokenmill_b200.models.qwen2 import qwen2_spec
+    from tokenmill_b200.weights import named_config
+
+    raw = {**named_config("tiny-a"), "num_hidden_layers": 3, "max_position_embeddings": 256, "hidden_size": 128,
+           "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 136}
+    spec = qwen2_spec(Qwen2Config.from_dict(raw))
+    kv_heads, inter = [1, 2, 1], [136, 136, 272]
+    layers = [replace(l, mixer=replace(l.mixer, params={**l.mixer.params, "num_kv_heads": kv_heads[i]}),
+                      feed_forward=replace(l.feed_forward, params={**l.feed_forward.params, "intermediate_size": inter[i]}))
+              for i, l in enumerate(spec.layers)]
+    spec = replace(spec, layers=layers)
+    model, w = _model_from(spec, dtype, seed=12)
+    layout = model.cache_layout()
+    assert [g.entries for g in layout.groups] == [[0, 2], [1]]
+    cache = CacheManager([8, 8], 16, windows=[None, None], watermark=0.0)
+    pools = CachePools(layout, [8, 8], 16, dtype, DEV, run_order_cache_of=[e.cache_of for e in spec.run_order])
+    runner = ModelRunner(model, cache, pools, max_model_len=256)
+    assert runner.fused is None                      # the whole-step kernel wants every layer alike
+    ids = torch.randint(0, 256, (90,), generator=torch.Generator().manual_seed(4)).tolist()
+    h = cache.new_handle()
+    cache.allocate(h, ids)
+    got = torch.cat([runner.step([StepEntry(h, ids[a:b], a, list(range(b - a)))])
+                     for a, b in [(0, 41), (41, 80), (80, 82)] + [(i, i + 1) for i in range(82, 90)]])
+    assert runner.stats["program_steps"] == (2 if dtype == torch.bfloat16 else 0)
+    cos, sin = plain_rope_tables(90, 64, raw["rope_theta"])
+    x = plain_embedding(ids, w["model.embed_tokens.weight"])
+    for i in range(3):
+        cfg = {"heads": 2, "kv_heads": kv_heads[i], "head_dim": 64, "eps": raw["rms_norm_eps"], "layers": 3}
+        x = plain_decoder_layer(x, w, i, cfg, cos, sin)
+    ref = plain_rmsnorm(x, w["model.norm.weight"], raw["rms_norm_eps"]) @ w["model.embed_tokens.weight"].T
+    assert (got.cpu() - ref).abs().max() <= tol(dtype, ref)
+    cache.free(h)
+    assert cache.all_free
