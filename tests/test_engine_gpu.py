@@ -615,10 +615,11 @@ def test_whole_step_kernel_leaves_wide_models_to_the_other_kernels(tmp_path, int
         assert torch.isfinite(x).all() and float((x - y).abs().max()) <= 3e-2 * float(y.abs().max())
 
 
-@pytest.mark.parametrize("max_seqs", [32, 10])
-def test_graph_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_dir, max_seqs):
+@pytest.mark.parametrize("max_seqs,graphs", [(32, True), (10, True), (32, False)])
+def test_graph_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_dir, max_seqs, graphs):
     """(With room for 10 requests the others wait and join as requests end: steps stay in flight while the
-    queue is not empty.) More requests than the whole-step kernel takes: their decode steps replay captured graphs, and with
+    queue is not empty. Without decode graphs the steps of 17 and more requests run as step programs, with the
+    ids gathered into the step's input buffer.) More requests than the whole-step kernel takes: their decode steps replay captured graphs, and with
     steps in flight the token ids are gathered on the device into the graph's static input. Same tokens, same
     ends as the synchronous loop: greedy and seeded sampling, ends at different lengths (the batch shrinks
     through the graph buckets down into the whole-step kernel's range)."""
@@ -631,10 +632,11 @@ def test_graph_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_di
     results = {}
     for mode in (False, True):
         eng = engine_for(d64_dir, dtype="bfloat16", async_decode=mode, max_num_seqs=max_seqs, max_num_batched_tokens=1024,
-                         kv_cache_mb=16, cuda_graphs=True, cuda_graph_max_batch=32)
+                         kv_cache_mb=16, cuda_graphs=graphs, cuda_graph_max_batch=32)
         assert eng._pipelining() == mode
         results[mode] = _run_requests(eng, prompts, params)
-        assert eng.runner.stats["fused_steps"] >= 3 and (max_seqs < 17 or eng.runner.stats["graph_steps"] >= 3)
+        st = eng.runner.stats
+        assert st["fused_steps"] >= 3 and (max_seqs < 17 or st["graph_steps" if graphs else "program_steps"] >= 3)
     for (ids_s, why_s, seen_s), (ids_a, why_a, seen_a), sp in zip(results[False], results[True], params):
         assert ids_s == ids_a and why_s == why_a == "length" and seen_s == ids_s and seen_a == ids_a
         assert len(ids_s) == sp.max_tokens and -1 not in ids_a

@@ -115,10 +115,20 @@ class ModelRunner:
         if self.graph_max_batch and len(entries) <= self.graph_max_batch and \
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return self._graph_step(entries)
+        return self._general_step(entries)
+
+    def _general_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
+                      token_rows: list[int] | None = None) -> torch.Tensor:
+        """Any step, through the step program where the model has one, else through the parts' forward
+        methods. With ``token_src`` (int32, on the device) the entries bring one token each and entry i's is
+        token_src[token_rows[i]], gathered into the step's input buffer behind its copy."""
         step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
                                  split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
                                  prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
         self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
+        if token_src is not None:
+            rows = torch.as_tensor(token_rows, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+            torch.index_select(token_src, 0, rows, out=step.token_ids)
         prog = self._step_program(step.n_tokens)
         if prog is not None and prog.takes(step):
             self.stats["program_steps"] += 1
@@ -128,8 +138,10 @@ class ModelRunner:
             logits = step.logits_out
         else:
             logits = self.model.forward(step, self.layer_caches)
-        if self.model.dtype == torch.bfloat16 and (step.n_tokens >= ops.TC_MIN_TOKENS or self.prefill_tile == 128):
-            ops.tc_check(self.device)       # a tcgen05 block that gave up on a wait must not pass silently
+        # A tcgen05 block that gave up on a wait must not pass silently: steps with prompt portions (the only
+        # ones that launch such kernels) read the error word back; the caller reads their logits at once anyway.
+        if self.model.dtype == torch.bfloat16 and (step.max_q_len > 1 or ops._TC_ENABLED):
+            ops.tc_check(self.device)
         return logits
 
     def _decode_logits(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -153,14 +165,16 @@ class ModelRunner:
     @property
     def feeds_tokens_on_device(self) -> bool:
         """Whether some decode steps can take their token ids from the device (``step_fed``)."""
-        return self.fused is not None or self.graph_max_batch > 0
+        return self.fused is not None or self.graph_max_batch > 0 or self._step_program(program_mod.MIN_TOKENS) is not None
 
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
         """Whether ``step_fed`` takes a decode step of this many requests: the whole-step kernel reads the ids
         itself, a captured graph has them gathered into its static input buffer."""
         if self.fused is not None and 0 < n_entries <= self.fused.max_tokens:
             return True
-        return 0 < n_entries <= self.graph_max_batch
+        if 0 < n_entries <= self.graph_max_batch:
+            return True
+        return n_entries >= program_mod.MIN_TOKENS and self._step_program(n_entries) is not None
 
     @torch.inference_mode()
     def step_fed(self, entries: list[StepEntry], token_src: torch.Tensor, token_rows: list[int]) -> torch.Tensor:
@@ -175,7 +189,9 @@ class ModelRunner:
         self.stats["steps"] += 1
         self.stats["tokens"] += len(entries)
         if self.fused is None or len(entries) > self.fused.max_tokens:
-            return self._graph_step(entries, token_src, token_rows)
+            if len(entries) <= self.graph_max_batch:
+                return self._graph_step(entries, token_src, token_rows)
+            return self._general_step(entries, token_src, token_rows)
         self.fused.check()
         self.stats["fused_steps"] += 1
         hidden = self.fused.run_decode(entries, self.cache.page_size, token_src=token_src, token_rows=token_rows)
