@@ -174,9 +174,11 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
             raise ValueError(f"entry {i}: a wanted place lies outside its {len(e.tokens)} tokens")
     tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
     # keys per work unit: the given number, or (0) chosen for this step's shape
+    # (A step in which every request brings so few rows that the decode kernel takes it needs no prompt units.)
+    unit_groups = [g for g in group_sizes if not (split_keys and int(q_lens.max()) * g <= 16)]
     chunks = {g: prefill_chunk or choose_chunk(q_lens, starts, g, (kv_heads_of or {}).get(g, 1), tile=prefill_tile)
-              for g in group_sizes}
-    unit_arrays = {g: packed_units(q_lens, starts, g, tile=prefill_tile, chunk=chunks[g]) for g in group_sizes}
+              for g in unit_groups}
+    unit_arrays = {g: packed_units(q_lens, starts, g, tile=prefill_tile, chunk=chunks[g]) for g in unit_groups}
     lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()},
                  {g: u[0].shape[0] for g, u in unit_arrays.items()})
 
@@ -191,22 +193,30 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
     buf[lay.kv_before] = starts
     buf[lay.state_slots] = [e.handle.state_slot for e in entries]
     buf[lay.want_rows] = want_rows
+    cu_list = cu_q.tolist()
     for g in range(cache.num_groups):
         w = widths[g]
         table = np.zeros((S, w), dtype=np.int32)
         slots = np.empty(T, dtype=np.int32)
         for i, e in enumerate(entries):
-            row = np.asarray(e.handle.tables[g], dtype=np.int32)
-            need = -(-int(kv_after[i]) // ps)
-            if row.size < need:
-                raise RuntimeError(f"entry {i} holds {row.size} pages in group {g}, its {int(kv_after[i])} "
-                                   f"tokens need {need}")
-            table[i, :min(row.size, w)] = row[:w]
-            p = positions[cu_q[i]:cu_q[i + 1]]
+            pages_of = e.handle.tables[g]
+            have, start, n_new = len(pages_of), e.start, len(e.tokens)
+            need = -(-(start + n_new) // ps)
+            if have < need:
+                raise RuntimeError(f"entry {i} holds {have} pages in group {g}, its {start + n_new} tokens need {need}")
+            table[i, :min(have, w)] = pages_of[:w]
+            if n_new == 1:                       # a decoded token: no arrays for one slot
+                page = pages_of[start // ps]
+                if page < 0:
+                    raise RuntimeError(f"entry {i} writes into a page it has already given back")
+                slots[cu_list[i]] = page * ps + start % ps
+                continue
+            row = np.asarray(pages_of, dtype=np.int32)
+            p = positions[cu_list[i]:cu_list[i + 1]]
             pages = row[p // ps]
             if (pages < 0).any():
                 raise RuntimeError(f"entry {i} writes into a page it has already given back")
-            slots[cu_q[i]:cu_q[i + 1]] = pages * ps + p % ps
+            slots[cu_list[i]:cu_list[i + 1]] = pages * ps + p % ps
         buf[lay.block_tables[g]] = table.reshape(-1)
         buf[lay.slot_maps[g]] = slots
     for g, (tile_seq, tile_row0) in tile_arrays.items():
