@@ -4,14 +4,15 @@
 // attention_prefill_bf16.cu (src/infer/model/layers.py:72-107, src/infer/kv/context.py:63-76); what differs
 // is the row tile (128 rows of (token, head-in-group) instead of 64) and where the products run.
 //
-// One block of 128 threads per work unit (row tile, kv head, chunk of keys); thread r owns row r, which is
-// lane r of tensor memory. Per block of 128 keys:
+// One block of 256 threads per work unit (row tile, kv head, chunk of keys); threads r and r + 128 share row r,
+// which is lane r of tensor memory: the first takes keys 0..63 of a block and output columns 0..31, the second
+// the other halves, and they agree on the block's reference maximum through shared memory. Per block of 128 keys:
 //   1. keys and values arrive by cp.async into 128-byte-swizzled tiles, two stages deep (8 neighbouring threads
 //      bring the 8 16-byte pieces of a row; the rows' cache slots are looked up one tile ahead, stepping
 //      through the pages with one division a tile);
 //   2. one thread issues S = Q K^T (M 128 rows, N 128 keys, K 64) as 4 tcgen05.mma into 128 columns of tensor
 //      memory and commits to an mbarrier;
-//   3. every thread reads its row of S back (tcgen05.ld), masks, takes the row maximum, turns the scores into
+//   3. every thread reads its half of its row of S back (tcgen05.ld), masks, takes the maximum, turns the scores into
 //      probabilities (one fused multiply-add and exp2 each), keeps the running maximum and denominator, and
 //      writes the probabilities as bfloat16 into a swizzled shared-memory tile; when the maximum moved, the
 //      row's partial output in tensor memory is rescaled (tcgen05.ld / st);
@@ -33,8 +34,9 @@ constexpr int kTaBM = 128;                 // rows per work unit
 constexpr int kTaBN = 128;                 // keys per block
 constexpr int kTaD = 64;                   // head size
 constexpr int kTaTile = kTaBN * kTaD * 2;  // 16 KB: a Q, K or V tile; half of the P tile
-constexpr int kTaSmem = kTaTile * (1 + 2 + 2 + 2) + 64;     // Q, K x2, V x2, P (two 64-key halves), barriers and flags
-constexpr int kTaThreads = 128;
+constexpr int kTaXch = 512;                // the two halves' block maxima, bfloat16, [row][half]
+constexpr int kTaSmem = kTaTile * (1 + 2 + 2 + 2) + 64 + kTaXch;   // Q, K x2, V x2, P (two 64-key halves), barriers and flags, maxima
+constexpr int kTaThreads = 256;             // two threads per row: thread t and t + 128 share row t, 64 keys each
 constexpr int kTaCols = 256;               // tensor-memory columns: S 0..127, O 128..191
 
 // Profiling aid: when set (tm_prefill_attention_tc_timing), the first thread of block 0's second warp (a warp
@@ -75,6 +77,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(tail + 16);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(tail + 20);
   int& s_ticket = *reinterpret_cast<int*>(tail + 24);
+  __nv_bfloat16* xch = reinterpret_cast<__nv_bfloat16*>(tail + 64);
   const uint32_t bar_s = t5_smem(&bars[0]), bar_pv = t5_smem(&bars[1]), bar_m = t5_smem(&bars[4]);
   if (base & 1023u) {                        // (never seen; without it the products would read garbage)
     if (threadIdx.x == 0) atomicCAS(error, 0, 19);
@@ -98,7 +101,10 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
   t5_fence_before();
   __syncthreads();
   t5_fence_after();
-  const uint32_t tmem_row = s_tmem_base + ((uint32_t)(warp * 32) << 16);   // this thread's lane, column 0
+  // Thread t and thread t + 128 work on row t (tensor-memory lane t; a warp reaches the 32 lanes of its index
+  // modulo 4): the first on keys 0..63 of a block and output columns 0..31, the second on the other halves.
+  const int rt = tid & 127, half = tid >> 7;
+  const uint32_t tmem_row = s_tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // this thread's lane, column 0
   const uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + kTaBN;
   constexpr uint32_t idesc_qk = t5_idesc(kTaBM, kTaBN, false), idesc_pv = t5_idesc(kTaBM, D, true);
   uint32_t n_s = 0, n_pv = 0, n_m = 0;                // completed phases of the two barriers (uniform over the block)
@@ -127,35 +133,35 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     const int n_blocks = j_lo > j_hi ? 0 : (j_hi - kb_first) / kTaBN + 1;
 
     // This thread's row.
-    const bool row_ok = tid < n_rows;
-    const int row = row0 + (row_ok ? tid : 0);
+    const bool row_ok = rt < n_rows;
+    const int row = row0 + (row_ok ? rt : 0);
     const int tok = row / G, g = row - tok * G;
     const size_t o_off = ((size_t)(q_start + tok) * nh + kvh * G + g) * D;
     const int p_row = row_ok ? before + tok : -1;
     const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
-    const uint32_t sw = (uint32_t)(tid & 7);
+    const uint32_t sw = (uint32_t)(rt & 7);
 
     // Loading a tile: 8 neighbouring threads bring the 8 16-byte chunks of one row (a full 128-byte line), a
-    // warp 4 rows per instruction, the block 16 rows per pass, 8 passes; chunk c of row r goes to (c ^ (r % 8)).
+    // warp 4 rows per instruction, the block 32 rows per pass, 4 passes; chunk c of row r goes to (c ^ (r % 8)).
     // The pages of a tile's rows are looked up one tile ahead, so that no copy waits for a table read.
     const int l_row = tid >> 3;                          // this thread's row within a pass
     const uint32_t l_chunk = (uint32_t)(tid & 7);
-    int slots[8];                                        // cache slots of rows l_row + 16 i of the tile to load next
+    int slots[4];                                        // cache slots of rows l_row + 32 i of the tile to load next
     auto look_up = [&](int kb) {                         // one division a tile: the rows step through the pages
       const int j0 = kb + l_row;
       int pg = j0 / page_size, off = j0 - pg * page_size;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int j = j0 + 16 * i;
+      for (int i = 0; i < 4; ++i) {
+        const int j = j0 + 32 * i;
         slots[i] = (j >= j_lo && j <= j_hi) ? table[pg] * page_size + off : -1;
-        off += 16;
+        off += 32;
         while (off >= page_size) { off -= page_size; ++pg; }
       }
     };
     auto load_kv = [&](int stage) {                      // uses `slots`, looked up for the tile to load
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int r = l_row + 16 * i;
+      for (int i = 0; i < 4; ++i) {
+        const int r = l_row + 32 * i;
         const bool has = slots[i] >= 0;
         const size_t src = has ? ((size_t)slots[i] * nkv + kvh) * D + l_chunk * 8 : 0;
         const uint32_t off = (uint32_t)r * 128 + ((l_chunk ^ (uint32_t)(r & 7)) << 4);
@@ -172,8 +178,8 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     };
     if (n_blocks > 0) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {                      // the queries: row r of the tile is row row0 + r
-        const int r = l_row + 16 * i;
+      for (int i = 0; i < 4; ++i) {                      // the queries: row r of the tile is row row0 + r
+        const int r = l_row + 32 * i;
         const bool has = r < n_rows;
         const int qrow = row0 + (has ? r : 0), qtok = qrow / G, qg = qrow - qtok * G;
         cp_async16(q_s + (uint32_t)r * 128 + ((l_chunk ^ (uint32_t)(r & 7)) << 4),
@@ -211,61 +217,66 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
       t5_fence_after();
       ta_stamp(stamp_at, 3);
 
-      // The row's 128 scores come into registers at once (four reads in flight, one wait).
-      const int last = min(j_hi, p_row) - kb, first = max(j_lo, lo_row) - kb;   // visible columns: first..last
-      float sv[4][32];
+      // This thread's 64 scores of the row come into registers at once (two reads in flight, one wait).
+      const int col0 = half * 64;
+      const int last = min(j_hi, p_row) - kb - col0, first = max(j_lo, lo_row) - kb - col0;   // visible: first..last
+      float sv[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) t5_ld32(tmem_row + c * 32, sv[c]);
+      for (int c = 0; c < 2; ++c) t5_ld32(tmem_row + col0 + c * 32, sv[c]);
       t5_ld_wait();
       // Most blocks lie wholly inside every row's visible range: only the others pay for the mask.
-      if (!(first <= 0 && last >= kTaBN - 1)) {
+      if (!(first <= 0 && last >= 63)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i < first || c * 32 + i > last) sv[c][i] = -INFINITY;
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one of 64
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[c][i]);
-      const float m_new = fmaxf(m_run, mx * scale_log2);
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[c][i]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // The row's two threads agree on one reference value: each leaves its own maximum, rounded UP to
+      // bfloat16 (any value at or above the true maximum will do, as long as both use the same), and takes the
+      // larger of the two.
+      xch[rt * 2 + half] = __float2bfloat16_ru(mx * scale_log2);
+      __syncthreads();
+      const __nv_bfloat162 both = *reinterpret_cast<const __nv_bfloat162*>(xch + rt * 2);
+      const float m_new = fmaxf(m_run, fmaxf(__bfloat162float(both.x), __bfloat162float(both.y)));
       const float mbase = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = m_new == -INFINITY ? 1.f : ta_exp2(m_run - m_new);
-      // Probabilities, their sum, and the bfloat16 tile for the second product.
-      float psum = 0.f;
+      // Probabilities, their sum, and this thread's half of the bfloat16 tile for the second product.
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t half_tile = p_s + half * kTaTile + rt * 128;        // 64 keys per 128-byte row
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           sv[c][i] = ta_exp2(fmaf(sv[c][i], scale_log2, -mbase));      // a masked score is -inf: 0
-          psum += sv[c][i];
+          ps4[i & 3] += sv[c][i];
         }
-        const uint32_t half_tile = p_s + (c >> 1) * kTaTile + tid * 128;        // 64 keys per 128-byte row
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           const uint32_t w0 = pack_bf16(sv[c][i], sv[c][i + 1]), w1 = pack_bf16(sv[c][i + 2], sv[c][i + 3]);
           const uint32_t w2 = pack_bf16(sv[c][i + 4], sv[c][i + 5]), w3 = pack_bf16(sv[c][i + 6], sv[c][i + 7]);
-          const uint32_t ch = (uint32_t)((((c & 1) * 32) + i) >> 3);
+          const uint32_t ch = (uint32_t)((c * 32 + i) >> 3);
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(half_tile + ((ch ^ sw) << 4)), "r"(w0), "r"(w1),
                        "r"(w2), "r"(w3) : "memory");
         }
       }
       ta_stamp(stamp_at, 4);
-      l_run = l_run * alpha + psum;
+      l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
       m_run = m_new;
       // The row's partial output follows the maximum (the first block of a unit starts it afresh).
       if (b > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          float v[32];
-          t5_ld32(tmem_row + kTaBN + c0, v);
-          t5_ld_wait();
+        float v[32];                           // this thread's 32 of the row's 64 output columns
+        t5_ld32(tmem_row + kTaBN + half * 32, v);
+        t5_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= alpha;
-          t5_st32(tmem_row + kTaBN + c0, v);
-        }
+        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+        t5_st32(tmem_row + kTaBN + half * 32, v);
         t5_st_wait();
       }
       ta_stamp(stamp_at, 5);
@@ -294,21 +305,26 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     t5_fence_after();
 
     // The row's result: normalised output when the tile has one chunk, else sums, maximum and denominator.
-    // (Every thread takes part in the tensor-memory reads; only the stores depend on the row being real.)
+    // The row's two threads add up their halves of the denominator (through the P tile, free by now) and each
+    // writes its 32 output columns. (Every thread takes part in the tensor-memory reads; only the stores depend
+    // on the row being real.)
     {
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      const size_t prow = slot0 < 0 ? 0 : ((size_t)(slot0 + chunk) * nkv + kvh) * kTaBM + tid;
-#pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float v[32];
-        if (n_blocks > 0) {                  // uniform over the block
-          t5_ld32(tmem_row + kTaBN + c0, v);
-          t5_ld_wait();
-        } else {
+      float* lx = reinterpret_cast<float*>(ta_smem_raw + 5 * kTaTile);      // [half][row]
+      lx[half * kTaBM + rt] = l_run;
+      __syncthreads();
+      const float l_row_sum = lx[rt] + lx[kTaBM + rt];
+      const float inv = l_row_sum > 0.f ? 1.0f / l_row_sum : 0.f;
+      const size_t prow = slot0 < 0 ? 0 : ((size_t)(slot0 + chunk) * nkv + kvh) * kTaBM + rt;
+      const int c0 = half * 32;
+      float v[32];
+      if (n_blocks > 0) {                    // uniform over the block
+        t5_ld32(tmem_row + kTaBN + c0, v);
+        t5_ld_wait();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-        }
-        if (!row_ok) continue;
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      if (row_ok) {
         if (slot0 < 0) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -323,9 +339,9 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<float4*>(part_acc + prow * D + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          if (half == 0) *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run, l_row_sum);
         }
       }
-      if (row_ok && slot0 >= 0) *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run, l_run);
     }
     t5_fence_before();
     if (slot0 >= 0) {
