@@ -243,16 +243,17 @@ def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
             assert counters.tolist() == [0, 0] and int(tile_done.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("nh,nkv,page,window", [(14, 2, 16, 0), (3, 3, 1, 0), (8, 1, 7, 0), (14, 2, 16, 70), (4, 2, 8, 1)])
-def test_prefill_attention_tcgen05_kernel(nh, nkv, page, window):
-    """The tcgen05 prompt kernel (heads of 64, 128-row tiles, scores and outputs in tensor memory): whole
+def test_prefill_attention_tcgen05_kernel(nh, nkv, page, window, D):
+    """The tcgen05 prompt kernel (heads of 64 on blocks of 128 keys, heads of 128 on blocks of 64; 128-row
+    tiles, scores and outputs in tensor memory): whole
     prompts, later portions that start off a tile or page edge, short portions and single tokens in the same
     launch; tiles that end inside a key block; key chunks so short that most tiles have several; windows."""
     from tokenmill_b200.engine.batch import packed_units
     from tokenmill_b200.parts.base import PrefillUnits
     import numpy as np
     ops = _ops()
-    D = 64
     q_lens, befores = [200, 1, 64, 3, 129, 65, 17, 300], [0, 300, 64, 5, 77, 191, 1000, 131]
     c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=nh + window,
                     window=window)

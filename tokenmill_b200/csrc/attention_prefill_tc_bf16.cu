@@ -1,6 +1,7 @@
 // Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores (tcgen05):
 // bfloat16 in, scores and outputs accumulated in float32 in tensor memory, softmax in float32 registers.
-// Head size 64. Semantics, work units and the merge of a row tile's key chunks are those of
+// Head sizes 64 (blocks of 128 keys) and 128 (blocks of 64 keys: the same 112 KB of shared memory and 192
+// columns of tensor memory either way). Semantics, work units and the merge of a row tile's key chunks are those of
 // attention_prefill_bf16.cu (src/infer/model/layers.py:72-107, src/infer/kv/context.py:63-76); what differs
 // is the row tile (128 rows of (token, head-in-group) instead of 64) and where the products run.
 //
@@ -31,13 +32,13 @@
 namespace tmk {
 
 constexpr int kTaBM = 128;                 // rows per work unit
-constexpr int kTaBN = 128;                 // keys per block
-constexpr int kTaD = 64;                   // head size
-constexpr int kTaTile = kTaBN * kTaD * 2;  // 16 KB: a Q, K or V tile; half of the P tile
+// Head size 64 works on blocks of 128 keys, head size 128 on blocks of 64: either way a K or V stage is 16 KB,
+// Q and P together 48 KB (16 + 32, or 32 + 16), S and O together 192 columns of tensor memory.
+constexpr int kTaTile = 16384;             // a panel: 128 rows of 128 bytes (64 bfloat16)
 constexpr int kTaXch = 512;                // the two halves' block maxima, bfloat16, [row][half]
-constexpr int kTaSmem = kTaTile * (1 + 2 + 2 + 2) + 64 + kTaXch;   // Q, K x2, V x2, P (two 64-key halves), barriers and flags, maxima
+constexpr int kTaSmem = kTaTile * 7 + 64 + kTaXch;   // Q, K x2, V x2, P; barriers and flags; maxima
 constexpr int kTaThreads = 256;             // two threads per row: thread t and t + 128 share row t, 64 keys each
-constexpr int kTaCols = 256;               // tensor-memory columns: S 0..127, O 128..191
+constexpr int kTaCols = 256;               // tensor-memory columns: S first, then O (192 of them used)
 
 // Profiling aid: when set (tm_prefill_attention_tc_timing), the first thread of block 0's second warp (a warp
 // that issues no products) stamps the nanosecond timer at the stations of its first units' key blocks: 8 stamps
@@ -59,19 +60,28 @@ __device__ __forceinline__ void ta_stamp(int& at, int station) {
   }
 }
 
+template <int D>
 __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int bt_stride,
     const int4* __restrict__ unit_rec, int n_units, int chunk_keys, float* __restrict__ part_acc,
     float* __restrict__ part_ml, int* __restrict__ tile_done, int* __restrict__ counters,
     __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, float scale_log2, int window, int* error) {
-  constexpr int D = kTaD;
+  constexpr int BN = D == 64 ? 128 : 64;     // keys per block
+  constexpr int QP = D / 64;                 // 64-column panels of a Q, K or V tile
+  constexpr int PP = BN / 64;                // 64-key panels of the P tile
+  constexpr int CPR = D / 8;                 // 16-byte pieces of a row
+  constexpr int RPP = kTaThreads / CPR;      // rows the block copies per pass
+  static_assert(D == 64 || D == 128, "head size 64 or 128");
   // All shared memory is the dynamic region (no static variables, no slack): two blocks then fit an SM. The
   // tiles need 1024-byte alignment (the swizzle pattern repeats every 1024 B); with nothing in front of it
   // the region starts aligned, which is checked below.
   extern __shared__ __align__(1024) unsigned char ta_smem_raw[];
   const uint32_t base = t5_smem(ta_smem_raw);
-  const uint32_t q_s = base, k_s = base + kTaTile, v_s = base + 3 * kTaTile, p_s = base + 5 * kTaTile;
+  // Tiles are stored as panels of [rows][128 bytes] with the 128-byte swizzle: Q [QP][128 rows], a K or V stage
+  // [QP][BN rows] (16 KB either way), P [PP][128 rows].
+  const uint32_t q_s = base, k_s = base + QP * kTaTile, v_s = k_s + 2 * kTaTile, p_s = v_s + 2 * kTaTile;
+  constexpr uint32_t kPanelKV = BN * 128;    // bytes of one panel of a K or V stage
   unsigned char* tail = ta_smem_raw + 7 * kTaTile;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(tail + 16);
@@ -105,8 +115,8 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
   // modulo 4): the first on keys 0..63 of a block and output columns 0..31, the second on the other halves.
   const int rt = tid & 127, half = tid >> 7;
   const uint32_t tmem_row = s_tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // this thread's lane, column 0
-  const uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + kTaBN;
-  constexpr uint32_t idesc_qk = t5_idesc(kTaBM, kTaBN, false), idesc_pv = t5_idesc(kTaBM, D, true);
+  const uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + BN;
+  constexpr uint32_t idesc_qk = t5_idesc(kTaBM, BN, false), idesc_pv = t5_idesc(kTaBM, 64, true);
   uint32_t n_s = 0, n_pv = 0, n_m = 0;                // completed phases of the two barriers (uniform over the block)
   int stamp_at = 0;
   bool ok = true;
@@ -129,8 +139,8 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     const int j_lo = max(window > 0 ? max(0, p_min - window + 1) : 0, chunk * chunk_keys);
     const int j_hi = min(p_max, (chunk + 1) * chunk_keys - 1);
     const int* table = block_table + (size_t)s * bt_stride;
-    const int kb_first = (j_lo / kTaBN) * kTaBN;
-    const int n_blocks = j_lo > j_hi ? 0 : (j_hi - kb_first) / kTaBN + 1;
+    const int kb_first = (j_lo / BN) * BN;
+    const int n_blocks = j_lo > j_hi ? 0 : (j_hi - kb_first) / BN + 1;
 
     // This thread's row.
     const bool row_ok = rt < n_rows;
@@ -141,53 +151,56 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
     const uint32_t sw = (uint32_t)(rt & 7);
 
-    // Loading a tile: 8 neighbouring threads bring the 8 16-byte chunks of one row (a full 128-byte line), a
-    // warp 4 rows per instruction, the block 32 rows per pass, 4 passes; chunk c of row r goes to (c ^ (r % 8)).
-    // The pages of a tile's rows are looked up one tile ahead, so that no copy waits for a table read.
-    const int l_row = tid >> 3;                          // this thread's row within a pass
-    const uint32_t l_chunk = (uint32_t)(tid & 7);
-    int slots[4];                                        // cache slots of rows l_row + 32 i of the tile to load next
+    // Loading a tile: CPR neighbouring threads bring the 16-byte pieces of one row (whole 128-byte lines), the
+    // block RPP rows per pass, four passes for a stage of BN rows; piece c of row r goes to panel c / 8, place
+    // ((c % 8) ^ (r % 8)) of the row. The cache slots of a tile's rows are looked up one tile ahead, so that no
+    // copy waits for a table read.
+    const int l_row = tid / CPR;                         // this thread's row within a pass
+    const uint32_t l_piece = (uint32_t)(tid % CPR);
+    const uint32_t l_panel = l_piece >> 3, l_chunk = l_piece & 7;
+    int slots[4];                                        // cache slots of rows l_row + RPP i of the tile to load next
     auto look_up = [&](int kb) {                         // one division a tile: the rows step through the pages
       const int j0 = kb + l_row;
       int pg = j0 / page_size, off = j0 - pg * page_size;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int j = j0 + 32 * i;
+        const int j = j0 + RPP * i;
         slots[i] = (j >= j_lo && j <= j_hi) ? table[pg] * page_size + off : -1;
-        off += 32;
+        off += RPP;
         while (off >= page_size) { off -= page_size; ++pg; }
       }
     };
     auto load_kv = [&](int stage) {                      // uses `slots`, looked up for the tile to load
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int r = l_row + 32 * i;
+        const int r = l_row + RPP * i;
         const bool has = slots[i] >= 0;
-        const size_t src = has ? ((size_t)slots[i] * nkv + kvh) * D + l_chunk * 8 : 0;
-        const uint32_t off = (uint32_t)r * 128 + ((l_chunk ^ (uint32_t)(r & 7)) << 4);
+        const size_t src = has ? ((size_t)slots[i] * nkv + kvh) * D + l_piece * 8 : 0;
+        const uint32_t off = l_panel * kPanelKV + (uint32_t)r * 128 + ((l_chunk ^ (uint32_t)(r & 7)) << 4);
         cp_async16(k_s + stage * kTaTile + off, kcache + src, has);        // rows without a key are zeros
         cp_async16(v_s + stage * kTaTile + off, vcache + src, has);
       }
     };
-    auto issue_qk = [&](int stage) {                     // one thread
+    auto issue_qk = [&](int stage) {                     // one thread: S = Q K^T, D / 16 steps of 16 columns
       t5_fence_after();
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks)
-        t5_mma(tmem_s, t5_desc(q_s + ks * 32), t5_desc(k_s + stage * kTaTile + ks * 32), idesc_qk, ks ? 1u : 0u);
+        t5_mma(tmem_s, t5_desc(q_s + (ks >> 2) * kTaTile + (ks & 3) * 32),
+               t5_desc(k_s + stage * kTaTile + (ks >> 2) * kPanelKV + (ks & 3) * 32), idesc_qk, ks ? 1u : 0u);
       t5_commit(bar_s);
     };
     if (n_blocks > 0) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {                      // the queries: row r of the tile is row row0 + r
-        const int r = l_row + 32 * i;
+      for (int i = 0; i < kTaBM / RPP; ++i) {            // the queries: row r of the tile is row row0 + r
+        const int r = l_row + RPP * i;
         const bool has = r < n_rows;
         const int qrow = row0 + (has ? r : 0), qtok = qrow / G, qg = qrow - qtok * G;
-        cp_async16(q_s + (uint32_t)r * 128 + ((l_chunk ^ (uint32_t)(r & 7)) << 4),
-                   q + ((size_t)(q_start + qtok) * nh + kvh * G + qg) * D + l_chunk * 8, has);
+        cp_async16(q_s + l_panel * kTaTile + (uint32_t)r * 128 + ((l_chunk ^ (uint32_t)(r & 7)) << 4),
+                   q + ((size_t)(q_start + qtok) * nh + kvh * G + qg) * D + l_piece * 8, has);
       }
       look_up(kb_first);
       load_kv(0);
-      look_up(kb_first + kTaBN);
+      look_up(kb_first + BN);
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -197,7 +210,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
 
     float m_run = -INFINITY, l_run = 0.f;    // running maximum (scaled, log2 units) and denominator of the row
     for (int b = 0; b < n_blocks && ok; ++b) {
-      const int kb = kb_first + b * kTaBN, stage = b & 1;
+      const int kb = kb_first + b * BN, stage = b & 1;
       ta_stamp(stamp_at, 0);
       if (b > 0) {                           // the products before are done: P, the other stage and O are free
         ok = mbar_wait(bar_pv, n_pv & 1u, &s_abort, error, 11);
@@ -207,7 +220,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
       ta_stamp(stamp_at, 1);
       if (b + 1 < n_blocks) {
         load_kv(stage ^ 1);
-        look_up(kb + 2 * kTaBN);
+        look_up(kb + 2 * BN);
       }
       cp_async_commit();
       ta_stamp(stamp_at, 2);
@@ -217,24 +230,25 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
       t5_fence_after();
       ta_stamp(stamp_at, 3);
 
-      // This thread's 64 scores of the row come into registers at once (two reads in flight, one wait).
-      const int col0 = half * 64;
+      // This thread's BN / 2 scores of the row come into registers at once (all reads in flight, one wait).
+      constexpr int SC = BN / 64;            // 32-column reads per thread
+      const int col0 = half * (BN / 2);
       const int last = min(j_hi, p_row) - kb - col0, first = max(j_lo, lo_row) - kb - col0;   // visible: first..last
-      float sv[2][32];
+      float sv[SC][32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) t5_ld32(tmem_row + col0 + c * 32, sv[c]);
+      for (int c = 0; c < SC; ++c) t5_ld32(tmem_row + col0 + c * 32, sv[c]);
       t5_ld_wait();
       // Most blocks lie wholly inside every row's visible range: only the others pay for the mask.
-      if (!(first <= 0 && last >= 63)) {
+      if (!(first <= 0 && last >= BN / 2 - 1)) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int c = 0; c < SC; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i < first || c * 32 + i > last) sv[c][i] = -INFINITY;
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one of 64
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one long one
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < SC; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[c][i]);
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
@@ -247,11 +261,11 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
       const float m_new = fmaxf(m_run, fmaxf(__bfloat162float(both.x), __bfloat162float(both.y)));
       const float mbase = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = m_new == -INFINITY ? 1.f : ta_exp2(m_run - m_new);
-      // Probabilities, their sum, and this thread's half of the bfloat16 tile for the second product.
+      // Probabilities, their sum, and this thread's part of the bfloat16 tile for the second product: key j of
+      // the block lies in panel j / 64, piece (j % 64) / 8 of the row.
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-      const uint32_t half_tile = p_s + half * kTaTile + rt * 128;        // 64 keys per 128-byte row
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < SC; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           sv[c][i] = ta_exp2(fmaf(sv[c][i], scale_log2, -mbase));      // a masked score is -inf: 0
@@ -261,9 +275,10 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
         for (int i = 0; i < 32; i += 8) {
           const uint32_t w0 = pack_bf16(sv[c][i], sv[c][i + 1]), w1 = pack_bf16(sv[c][i + 2], sv[c][i + 3]);
           const uint32_t w2 = pack_bf16(sv[c][i + 4], sv[c][i + 5]), w3 = pack_bf16(sv[c][i + 6], sv[c][i + 7]);
-          const uint32_t ch = (uint32_t)((c * 32 + i) >> 3);
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(half_tile + ((ch ^ sw) << 4)), "r"(w0), "r"(w1),
-                       "r"(w2), "r"(w3) : "memory");
+          const uint32_t j = (uint32_t)(col0 + c * 32 + i);
+          const uint32_t row_s = p_s + (j >> 6) * kTaTile + rt * 128;
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_s + ((((j & 63) >> 3) ^ sw) << 4)), "r"(w0),
+                       "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
       }
       ta_stamp(stamp_at, 4);
@@ -271,12 +286,15 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
       m_run = m_new;
       // The row's partial output follows the maximum (the first block of a unit starts it afresh).
       if (b > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        float v[32];                           // this thread's 32 of the row's 64 output columns
-        t5_ld32(tmem_row + kTaBN + half * 32, v);
-        t5_ld_wait();
+#pragma unroll 1
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {   // this thread's half of the columns
+          float v[32];
+          t5_ld32(tmem_row + BN + c0, v);
+          t5_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= alpha;
-        t5_st32(tmem_row + kTaBN + half * 32, v);
+          for (int i = 0; i < 32; ++i) v[i] *= alpha;
+          t5_st32(tmem_row + BN + c0, v);
+        }
         t5_st_wait();
       }
       ta_stamp(stamp_at, 5);
@@ -287,10 +305,13 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
       ta_stamp(stamp_at, 6);
       if (tid == 0) {
         t5_fence_after();
+        // O += P V, 64 output columns (one panel of V) at a time, BN / 16 steps of 16 keys each
 #pragma unroll
-        for (int ks = 0; ks < kTaBN / 16; ++ks)
-          t5_mma(tmem_o, t5_desc(p_s + (ks >> 2) * kTaTile + (ks & 3) * 32),
-                 t5_desc(v_s + stage * kTaTile + ks * 2048), idesc_pv, (b | ks) ? 1u : 0u);
+        for (int dp = 0; dp < QP; ++dp)
+#pragma unroll
+          for (int ks = 0; ks < BN / 16; ++ks)
+            t5_mma(tmem_o + dp * 64, t5_desc(p_s + (ks >> 2) * kTaTile + (ks & 3) * 32),
+                   t5_desc(v_s + stage * kTaTile + dp * kPanelKV + ks * 2048), idesc_pv, (b | ks) ? 1u : 0u);
         t5_commit(bar_pv);
         if (b + 1 < n_blocks) issue_qk(stage ^ 1);       // the next block's scores follow at once
       }
@@ -309,22 +330,23 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
     // writes its 32 output columns. (Every thread takes part in the tensor-memory reads; only the stores depend
     // on the row being real.)
     {
-      float* lx = reinterpret_cast<float*>(ta_smem_raw + 5 * kTaTile);      // [half][row]
+      float* lx = reinterpret_cast<float*>(ta_smem_raw + (QP + 4) * kTaTile);      // [half][row], in the P tile
       lx[half * kTaBM + rt] = l_run;
       __syncthreads();
       const float l_row_sum = lx[rt] + lx[kTaBM + rt];
       const float inv = l_row_sum > 0.f ? 1.0f / l_row_sum : 0.f;
       const size_t prow = slot0 < 0 ? 0 : ((size_t)(slot0 + chunk) * nkv + kvh) * kTaBM + rt;
-      const int c0 = half * 32;
-      float v[32];
-      if (n_blocks > 0) {                    // uniform over the block
-        t5_ld32(tmem_row + kTaBN + c0, v);
-        t5_ld_wait();
-      } else {
+#pragma unroll 1
+      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+        float v[32];
+        if (n_blocks > 0) {                  // uniform over the block
+          t5_ld32(tmem_row + BN + c0, v);
+          t5_ld_wait();
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0.f;
-      }
-      if (row_ok) {
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        }
+        if (!row_ok) continue;
         if (slot0 < 0) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -339,9 +361,9 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<float4*>(part_acc + prow * D + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-          if (half == 0) *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run, l_row_sum);
         }
       }
+      if (row_ok && slot0 >= 0 && half == 0) *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run, l_row_sum);
     }
     t5_fence_before();
     if (slot0 >= 0) {
@@ -441,8 +463,8 @@ extern "C" int tm_prefill_attention_tc_timing(unsigned long long* stamps) {
   return (int)cudaMemcpyToSymbol(tmk::g_ta_timing, &stamps, sizeof(stamps));
 }
 
-// As tm_prefill_attention_bf16, for head size 64, with row tiles of 128 rows (the unit records and the
-// partial-result slots are made for 128-row tiles: part_acc [slots * nkv, 128, 64], part_ml [slots * nkv,
+// As tm_prefill_attention_bf16, for head sizes 64 and 128, with row tiles of 128 rows (the unit records and the
+// partial-result slots are made for 128-row tiles: part_acc [slots * nkv, 128, D], part_ml [slots * nkv,
 // 128, 2]). `error`: a device int that must be zero; a block whose wait runs out writes a non-zero code there
 // instead of hanging.
 extern "C" int tm_prefill_attention_tc_bf16(const void* q, const void* kcache, const void* vcache,
@@ -451,12 +473,13 @@ extern "C" int tm_prefill_attention_tc_bf16(const void* q, const void* kcache, c
                                             int* counters, void* out, int nh, int nkv, int D, int page_size,
                                             float scale, int window, int* error, cudaStream_t stream) {
   if (n_units <= 0) return 0;
-  if (D != tmk::kTaD || nkv <= 0 || nh % nkv || page_size <= 0 || !counters || !error || chunk_keys <= 0 ||
-      chunk_keys % tmk::kTaBN || !(scale > 0.f) || (reinterpret_cast<uintptr_t>(unit_rec) & 15))
+  if ((D != 64 && D != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || !counters || !error || chunk_keys <= 0 ||
+      chunk_keys % 128 || !(scale > 0.f) || (reinterpret_cast<uintptr_t>(unit_rec) & 15))
     return TM_ERR_UNSUPPORTED_SHAPE;
-  auto kern = tmk::prefill_attention_tc_kernel;
-  static int blocks_per_sm = 0, n_sm = 0;
-  if (blocks_per_sm == 0) {
+  auto kern = D == 64 ? tmk::prefill_attention_tc_kernel<64> : tmk::prefill_attention_tc_kernel<128>;
+  static int n_sm = 0;
+  static bool prepared[2] = {false, false};
+  if (!prepared[D == 128]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tmk::kTaSmem);
     if (e != cudaSuccess) return (int)e;
     // Two blocks of 112 KB per SM need nearly all of the SM's memory as shared memory.
@@ -465,11 +488,12 @@ extern "C" int tm_prefill_attention_tc_bf16(const void* q, const void* kcache, c
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    // Two blocks per SM: by shared memory (2 x 112 KB), registers and tensor memory (2 x 256 columns) they fit,
-    // although the occupancy query answers 1 here. Should an SM take only one at a time, the others start
-    // when it leaves and find the ticket counter exhausted: slower, never wrong.
-    blocks_per_sm = 2;
+    prepared[D == 128] = true;
   }
+  // Two blocks per SM: by shared memory (2 x 112 KB), registers and tensor memory (2 x 256 columns) they fit,
+  // although the occupancy query answers 1 here. Should an SM take only one at a time, the others start when
+  // it leaves and find the ticket counter exhausted: slower, never wrong.
+  const int blocks_per_sm = 2;
   const long long units = (long long)n_units * nkv;
   long long grid = (long long)n_sm * blocks_per_sm;
   if (grid > units) grid = units;

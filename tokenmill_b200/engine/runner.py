@@ -48,9 +48,10 @@ class ModelRunner:
                                    if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")})
         self.scratch = AttentionScratch(self.device)
         # Rows of a prompt-attention work unit: 128 where the tcgen05 kernel takes every attention layer of the
-        # model (bfloat16, heads of 64), else the 64 of the mma.sync kernel.
+        # model (bfloat16, heads of 64 or 128), else the 64 of the mma.sync kernel.
         heads = {b.mixer.D for b in model.blocks if hasattr(b.mixer, "D")}
-        self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads == {64}) else 64
+        self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads
+                                    and heads <= {64, 128}) else 64
         self.prefill_chunk = 0          # keys of a work unit: chosen per step (batch.choose_chunk)
         self.kv_heads_of = {b.mixer.nh // b.mixer.nkv: b.mixer.nkv for b in model.blocks
                             if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")}

@@ -192,14 +192,14 @@ def prefill_attention_tc_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: tor
                               units, counters: torch.Tensor, out: torch.Tensor, *, scale: float, window: int = 0,
                               part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
                               tile_done: torch.Tensor | None = None) -> torch.Tensor:
-    """As prefill_attention_bf16, on tcgen05 with the scores and outputs in tensor memory: head size 64, units of
+    """As prefill_attention_bf16, on tcgen05 with the scores and outputs in tensor memory: head size 64 or 128, units of
     128-row tiles (units.tile_rows == 128; the scratch holds 128 rows per slot). A block that gives up on a
     bounded wait raises the device error word that tc_check reads."""
     T, nh, D = q.shape
     page_size, nkv = kcache.shape[1], kcache.shape[2]
     bf, i32 = torch.bfloat16, torch.int32
-    if D != 64 or units.tile_rows != 128:
-        raise lib.KernelError("prefill_attention_tc_bf16: head size 64 and 128-row tiles only")
+    if D not in (64, 128) or units.tile_rows != 128:
+        raise lib.KernelError("prefill_attention_tc_bf16: head size 64 or 128 and 128-row tiles only")
     if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
         raise lib.KernelError("prefill_attention_tc_bf16: q / cache / out shapes disagree")
     if scale <= 0:

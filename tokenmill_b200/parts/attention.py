@@ -164,7 +164,7 @@ class GroupedQueryAttention:
         if step.split_keys and step.max_q_len * G <= 16:
             return "decode"
         if G in step.prefill:
-            return "prefill_tc" if step.prefill[G].tile_rows == 128 and self.D == 64 else "prefill"
+            return "prefill_tc" if step.prefill[G].tile_rows == 128 else "prefill"
         return "generic"
 
     def emit(self, b, x, cache: LayerCache):
@@ -228,10 +228,9 @@ class GroupedQueryAttention:
         scratch = [b.param(f"prefill_acc_{key}", pf(0)), b.param(f"prefill_ml_{key}", pf(1)),
                    b.param(f"prefill_done_{key}", pf(2)), b.param("prefill_counters", lambda s: s.scratch.counters().data_ptr())]
         common = [q, cache.k, cache.v, table, bt_stride, *units, *scratch, out, nh, nkv, D, page, scale, window]
-        if D == 64:
-            b.uses_tc_attention = True
-            b.emit(OP_PREFILL_ATTENTION_TC, common + [ops.tc_error_word(self.device)],
-                   cond=b.param(f"attention_prefill_tc_{key}", lambda s: int(path(s) == "prefill_tc")))
+        b.uses_tc_attention = True
+        b.emit(OP_PREFILL_ATTENTION_TC, common + [ops.tc_error_word(self.device)],
+               cond=b.param(f"attention_prefill_tc_{key}", lambda s: int(path(s) == "prefill_tc")))
         b.emit(OP_PREFILL_ATTENTION, common,
                cond=b.param(f"attention_prefill_{key}", lambda s: int(path(s) == "prefill")))
         b.emit(OP_GEMM_BF16, [out, self.w_o, branch, T, self.hidden_size, self.q_size, 0])
