@@ -59,6 +59,14 @@ class ModelRunner:
         # part of the model can write its launches down; TOKENMILL_STEP_PROGRAM=0 keeps the per-launch path.
         self._program = None
         self._no_program = os.environ.get("TOKENMILL_STEP_PROGRAM", "1") == "0"
+        # Small steps (up to 16 tokens) of a model whose matrices the weight-streaming kernels take keep the
+        # launch-by-launch path, where those kernels are; with large matrices the products are the library's
+        # anyway, and the program takes steps of any size.
+        mats = [w for b in model.blocks for w in (getattr(b.mixer, "w_qkv", None), getattr(b.mixer, "w_o", None),
+                                                  getattr(b.feed_forward, "w_gate_up", None),
+                                                  getattr(b.feed_forward, "w_down", None)) if w is not None]
+        streams_all = all(w.numel() * 2 <= ops.SKINNY_MAX_WEIGHT_BYTES for w in mats)
+        self._program_min_tokens = program_mod.MIN_TOKENS if streams_all else 1
         self.graph_max_batch = min(cuda_graph_max_batch, max_num_seqs) if cuda_graphs else 0
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
@@ -131,7 +139,7 @@ class ModelRunner:
             rows = torch.as_tensor(token_rows, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
             torch.index_select(token_src, 0, rows, out=step.token_ids)
         prog = self._step_program(step.n_tokens)
-        if prog is not None and prog.takes(step):
+        if prog is not None and prog.takes(step, self._program_min_tokens):
             self.stats["program_steps"] += 1
             step.logits_out = torch.empty((step.n_want, self.model.spec.vocab_size), dtype=torch.float32,
                                           device=self.device)
@@ -154,7 +162,7 @@ class ModelRunner:
     def _step_program(self, n_tokens: int):
         """The model's step program with room for ``n_tokens`` (built on first need, rebuilt with a larger
         workspace when a step outgrows it), or None where there is none."""
-        if self._no_program or n_tokens < program_mod.MIN_TOKENS or ops._TC_ENABLED:
+        if self._no_program or n_tokens < self._program_min_tokens or ops._TC_ENABLED:
             return None
         if self._program is None or self._program.capacity < n_tokens:
             capacity = max(256, 1 << (n_tokens - 1).bit_length())
@@ -175,7 +183,7 @@ class ModelRunner:
             return True
         if 0 < n_entries <= self.graph_max_batch:
             return True
-        return n_entries >= program_mod.MIN_TOKENS and self._step_program(n_entries) is not None
+        return n_entries >= self._program_min_tokens and self._step_program(n_entries) is not None
 
     @torch.inference_mode()
     def step_fed(self, entries: list[StepEntry], token_src: torch.Tensor, token_rows: list[int]) -> torch.Tensor:

@@ -21,6 +21,10 @@ from .ops import _stream as ops_stream
 
 MAX_TOKENS = 16
 MAX_LAYERS = 96          # entries of the kernel's layer table in shared memory
+# Layers beyond this many bytes of weights are left to the separate kernels: the whole-step kernel is made for
+# steps that are bound by latency (0.5B layer sizes, 30 MB a layer: 30 us against 53 us); at the 1.5B sizes (93 MB
+# a layer) its two remaining ring stages stream at 0.8 TB/s and the library products are faster (117 vs 86 us).
+MAX_LAYER_WEIGHT_BYTES = 48 << 20
 SPLIT_KEYS = 64          # granularity of the key split of attention (a block attends a multiple of this)
 _ENABLED = os.environ.get("TOKENMILL_FUSED_DECODE", "1") != "0"
 
@@ -81,6 +85,8 @@ def eligible(model) -> bool:
                 b.feed_forward_norm.eps != model.blocks[model.spec.run_order[0].layer].feed_forward_norm.eps:
             return False
     H, I = model.spec.hidden_size, model.blocks[0].feed_forward.intermediate_size
+    if 2 * (H * (first.q_size + 2 * first.kv_size) + first.q_size * H + 3 * H * I) > MAX_LAYER_WEIGHT_BYTES:
+        return False
     return (type(model.final_norm) is RMSNorm and first.D in (64, 128) and H % 8 == 0 and I % 8 == 0
             and first.q_size % 8 == 0 and first.nh // first.nkv <= 16 and len(model.cache_layout().groups) == 1)
 

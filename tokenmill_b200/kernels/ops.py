@@ -306,6 +306,10 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 # --- weight-streaming products for decode steps (bfloat16, at most 64 tokens) -------------------------
 
 SKINNY_MAX_TOKENS = 16             # the kernel takes up to 64; beyond 16 the library product is faster today
+# Matrices beyond this size go to the library product at every token count: the weight-streaming kernel tops out
+# near 1.2 to 2.1 TB/s, which is what a small matrix gets anyway (its time is latency) but half of what the
+# library reaches on a large one (7B layer sizes, 8 tokens: gate/up 127 vs 66 us, down 116 vs 42 us).
+SKINNY_MAX_WEIGHT_BYTES = 20 << 20
 _SKINNY_X_BYTES = 200 * 1024       # shared memory the staged activations may take
 
 
@@ -317,7 +321,8 @@ def skinny_ok(x: torch.Tensor, w: torch.Tensor, allow_split: bool = False) -> bo
     """Whether the weight-streaming kernel takes this product (else the library product does).
     A product with a fused epilogue cannot cut its K range, so its activations must fit shared memory."""
     if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
-            and x.shape[0] <= SKINNY_MAX_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.shape[0] <= SKINNY_MAX_TOKENS and w.numel() * 2 <= SKINNY_MAX_WEIGHT_BYTES
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()):
         return False
     return allow_split or _padded_tokens(x.shape[0]) * (x.shape[1] + 64) * 2 <= _SKINNY_X_BYTES

@@ -177,8 +177,8 @@ class StepProgram:
         ws = StepProgram._cublas_workspace
         lib.call("tm_program_setup", ws.data_ptr(), ws.numel())
 
-    def takes(self, step: "StepInputs") -> bool:
-        return MIN_TOKENS <= step.n_tokens <= self.capacity and all(g(step) for g in self.guards)
+    def takes(self, step: "StepInputs", min_tokens: int = MIN_TOKENS) -> bool:
+        return min_tokens <= step.n_tokens <= self.capacity and all(g(step) for g in self.guards)
 
     def run(self, step: "StepInputs") -> None:
         """Launch the step. What the providers read from ``step`` must stay alive until the launches have
