@@ -207,12 +207,60 @@ def prefill_timed(engine, tokens: int, reps: int = 5) -> dict:
     return {"ms": statistics.median(times)}
 
 
+def products_timed(tokens: int = 8) -> list[dict]:
+    """Profiling aid (--only products): a decode step's matrix products at the Qwen2.5 0.5B / 1.5B / 7B layer
+    sizes, through this library's weight-streaming kernels and through the library product (plus the SwiGLU
+    kernel for gate/up), each after an L2 flush. It is what the size limits of kernels/ops.py
+    (SKINNY_MAX_WEIGHT_BYTES) and kernels/fused.py (MAX_LAYER_WEIGHT_BYTES) were read from."""
+    import torch
+    from tokenmill_b200.kernels import ops
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, n=12):
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1000)
+        return sorted(ts)[n // 2]
+
+    rows = []
+    for name, (H, QKV, I) in {"0.5B": (896, 1152, 4864), "1.5B": (1536, 2048, 8960), "7B": (3584, 4608, 18944)}.items():
+        x = torch.randn(tokens, H, device="cuda").bfloat16()
+        xi = torch.randn(tokens, I, device="cuda").bfloat16()
+        w_qkv = (torch.randn(QKV, H, device="cuda") * 0.02).bfloat16()
+        w_gu = (torch.randn(2 * I, H, device="cuda") * 0.02).bfloat16()
+        w_d = (torch.randn(H, I, device="cuda") * 0.02).bfloat16()
+        act = torch.empty(tokens, I, device="cuda", dtype=torch.bfloat16)
+        gu = torch.empty(tokens, 2 * I, device="cuda", dtype=torch.bfloat16)
+        ks = ops.skinny_k_splits(tokens, I)
+
+        def lib_gate_up():
+            torch.mm(x, w_gu.t(), out=gu)
+            ops.swiglu(gu, act)
+        for what, ours, theirs, nbytes in (
+                ("qkv", lambda: ops.skinny_linear(x, w_qkv), lambda: torch.mm(x, w_qkv.t()), QKV * H * 2),
+                ("gate_up+swiglu", lambda: ops.skinny_gate_up_swiglu(x, w_gu, act), lib_gate_up, 2 * I * H * 2),
+                ("down", lambda: ops.skinny_linear(xi, w_d, k_splits=ks), lambda: torch.mm(xi, w_d.t()), H * I * 2)):
+            t_ours, t_lib = timed(ours), timed(theirs)
+            rows.append({"sizes": name, "tokens": tokens, "product": what, "weight_mb": round(nbytes / 2 ** 20, 1),
+                         "streaming_us": round(t_ours, 1), "streaming_tb_s": round(nbytes / t_ours / 1e6, 2),
+                         "library_us": round(t_lib, 1), "library_tb_s": round(nbytes / t_lib / 1e6, 2)})
+    return rows
+
+
+
 def run_ours(args) -> dict:
     import torch
     from tokenmill_b200 import EngineConfig
     from tokenmill_b200.engine import LLMEngine
     from tokenmill_b200.kernels import lib
 
+    if args.only == "products":
+        for row in products_timed():
+            print(json.dumps(row))
+        return {}
     layers = args.layers or SIZES["num_hidden_layers"]
     pk, pk_kind = peaks()
     info = model_flops_bytes(SIZES, layers)
@@ -363,7 +411,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
-    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill' or 'decode_b<batch>' and print its time")
+    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>' or 'products' and print its time")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     args = ap.parse_args()
