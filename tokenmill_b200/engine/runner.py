@@ -112,10 +112,7 @@ class ModelRunner:
                 self.stats["h2d_bytes"] = self.fused.h2d_bytes
                 return self._decode_logits(hidden)
             if sum(len(e.tokens) for e in entries) <= self.fused.max_tokens:
-                step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                         split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
-                                 prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
-                self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
+                step = self._inputs(entries)
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
                     hidden = self.fused.run(step, self.cache.page_size)
@@ -126,15 +123,20 @@ class ModelRunner:
             return self._graph_step(entries)
         return self._general_step(entries)
 
+    def _inputs(self, entries: list[StepEntry]) -> StepInputs:
+        """The step's batch on the device (one packed buffer, one copy)."""
+        step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
+                                 split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
+                                 prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
+        self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
+        return step
+
     def _general_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
                       token_rows: list[int] | None = None) -> torch.Tensor:
         """Any step, through the step program where the model has one, else through the parts' forward
         methods. With ``token_src`` (int32, on the device) the entries bring one token each and entry i's is
         token_src[token_rows[i]], gathered into the step's input buffer behind its copy."""
-        step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                 split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
-                                 prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
-        self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
+        step = self._inputs(entries)
         if token_src is not None:
             rows = torch.as_tensor(token_rows, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
             torch.index_select(token_src, 0, rows, out=step.token_ids)
@@ -149,7 +151,7 @@ class ModelRunner:
             logits = self.model.forward(step, self.layer_caches)
         # A tcgen05 block that gave up on a wait must not pass silently: steps with prompt portions (the only
         # ones that launch such kernels) read the error word back; the caller reads their logits at once anyway.
-        if self.model.dtype == torch.bfloat16 and (step.max_q_len > 1 or ops._TC_ENABLED):
+        if self.model.dtype == torch.bfloat16 and (step.max_q_len > 1 or ops.tc_gemm_enabled()):
             ops.tc_check(self.device)
         return logits
 
@@ -162,7 +164,7 @@ class ModelRunner:
     def _step_program(self, n_tokens: int):
         """The model's step program with room for ``n_tokens`` (built on first need, rebuilt with a larger
         workspace when a step outgrows it), or None where there is none."""
-        if self._no_program or n_tokens < self._program_min_tokens or ops._TC_ENABLED:
+        if self._no_program or n_tokens < self._program_min_tokens or ops.tc_gemm_enabled():
             return None
         if self._program is None or self._program.capacity < n_tokens:
             capacity = max(256, 1 << (n_tokens - 1).bit_length())

@@ -408,6 +408,11 @@ _TC_ENABLED = os.environ.get("TOKENMILL_TC_GEMM", "0") == "1"
 _tc_error: dict[torch.device, torch.Tensor] = {}
 
 
+def tc_gemm_enabled() -> bool:
+    """Whether prompt-step products go to the tcgen05 kernels (TOKENMILL_TC_GEMM=1) instead of the library."""
+    return _TC_ENABLED
+
+
 def _tc_flag(device: torch.device) -> torch.Tensor:
     if device not in _tc_error:
         _tc_error[device] = torch.zeros(1, dtype=torch.int32, device=device)
