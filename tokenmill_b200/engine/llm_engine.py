@@ -29,6 +29,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.pool import CachePools
 from ..config.engine_config import EngineConfig
+from ..kernels import ops
 from ..parts.model import DecoderModel
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -293,9 +294,12 @@ class LLMEngine:
     def drain(self) -> list[RequestOutput]:
         """Read the step in flight, if any, without launching another (e.g. before the engine is dropped)."""
         if self._inflight is None:
+            ops.tc_check(self.runner.device)     # (errors of prompt steps that nobody has looked at yet)
             return []
         cur, self._inflight = self._inflight, None
-        return self._collect(cur, None)
+        outputs = self._collect(cur, None)
+        ops.tc_check(self.runner.device)
+        return outputs
 
     # --- one step, start to end -----------------------------------------------------------------
 
@@ -374,4 +378,5 @@ class LLMEngine:
             seqs.append(self.add_request(f"offline-{self._offline_counter}", p, sp))
         while self.has_unfinished():
             self.step()
+        ops.tc_check(self.runner.device)         # a prompt step's kernel that gave up must not pass silently
         return [s.output_ids for s in seqs]

@@ -104,6 +104,7 @@ class ModelRunner:
                                  f"{self.max_model_len}")
         self.stats["steps"] += 1
         self.stats["tokens"] += sum(len(e.tokens) for e in entries)
+        ops.tc_poll(self.device)
         if self.fused is not None:
             self.fused.check()
             if len(entries) <= self.fused.max_tokens and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
@@ -149,10 +150,12 @@ class ModelRunner:
             logits = step.logits_out
         else:
             logits = self.model.forward(step, self.layer_caches)
-        # A tcgen05 block that gave up on a wait must not pass silently: steps with prompt portions (the only
-        # ones that launch such kernels) read the error word back; the caller reads their logits at once anyway.
+        # A tcgen05 block that gave up on a wait must not pass silently: after steps with prompt portions (the
+        # only ones that launch such kernels) the error word travels to the host behind the step, and the next
+        # step (or whoever has synchronised: trace replay, drain) looks at it. Nothing waits here: a prompt cut
+        # into portions keeps the host one step ahead of the GPU.
         if self.model.dtype == torch.bfloat16 and (step.max_q_len > 1 or ops.tc_gemm_enabled()):
-            ops.tc_check(self.device)
+            ops.tc_post(self.device)
         return logits
 
     def _decode_logits(self, hidden: torch.Tensor) -> torch.Tensor:

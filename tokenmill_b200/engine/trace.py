@@ -28,6 +28,7 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
         device: str = "cuda:0", page_size: int = PAGE_SIZE) -> int:
     from ..cache.manager import CacheManager
     from ..cache.pool import CachePools
+    from ..kernels import ops
     from ..weights.loader import load_model, resolve_dtype
     from .batch import StepEntry
     from .runner import ModelRunner
@@ -80,6 +81,7 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
             logits = runner.step(entries)
             if logits.shape[0] > 0:
                 arr = logits.detach().to("cpu", torch.float32).contiguous().numpy()
+                ops.tc_check(runner.device)          # (the copy above has waited for the step)
                 arr.astype("<f4", copy=False).tofile(out / f"{step_no}.f32")
             for e in entries:
                 cache.release_behind_window(e.handle, e.start + len(e.tokens))

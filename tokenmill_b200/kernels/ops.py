@@ -422,8 +422,31 @@ def _tc_flag(device: torch.device) -> torch.Tensor:
 tc_error_word = _tc_flag
 
 
+_tc_host: dict[torch.device, torch.Tensor] = {}
+
+
+def tc_post(device: torch.device) -> None:
+    """Send the error word on its way to pinned host memory behind the work launched so far, without waiting;
+    ``tc_poll`` looks at the copy."""
+    flag = _tc_error.get(device)
+    if flag is not None:
+        if device not in _tc_host:
+            _tc_host[device] = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        _tc_host[device].copy_(flag, non_blocking=True)
+
+
+def tc_poll(device: torch.device) -> None:
+    """Raise if the last copy ``tc_post`` made that has arrived holds an error (no synchronisation: a failure
+    shows once the stream has been synchronised, at the latest one step later)."""
+    host = _tc_host.get(device)
+    if host is not None and int(host[0]):
+        host.zero_()
+        tc_check(device)
+
+
 def tc_check(device: torch.device) -> None:
-    """Raise if a tcgen05 kernel gave up on a bounded wait since the last check (reads one int back)."""
+    """Raise if a tcgen05 kernel gave up on a bounded wait since the last check (reads one int back, which
+    waits for the device)."""
     flag = _tc_error.get(device)
     if flag is not None:
         code = int(flag.item())
