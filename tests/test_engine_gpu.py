@@ -645,3 +645,46 @@ def test_graph_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_di
     for (ids_s, why_s, seen_s), (ids_a, why_a, seen_a), sp in zip(results[False], results[True], params):
         assert ids_s == ids_a and why_s == why_a == "length" and seen_s == ids_s and seen_a == ids_a
         assert len(ids_s) == sp.max_tokens and -1 not in ids_a
+
+
+@pytest.mark.parametrize("trial", [0, 3, 4])
+def test_random_workloads_with_tiny_pools(d64_dir, trial):
+    """Sixty requests of random lengths and sampling settings arriving at random times into a pool so small
+    that requests are preempted again and again, with decode graphs, chunked prompts in one trial, steps in
+    flight or not: every request gets exactly its tokens, no placeholder survives, no page is lost, and in
+    float32 the loop with steps in flight produces the synchronous loop's tokens. (Between graph replays a
+    mixed step of many short portions needs more attention scratch than the graphs captured.)"""
+    from tokenmill_b200.sampling import SamplingParams
+    vocab = json.loads((Path(d64_dir) / "config.json").read_text())["vocab_size"]
+    rng = random.Random(trial)
+    n = 60
+    prompts = [[rng.randrange(vocab) for _ in range(rng.choice([1, 2, 5, 17, 40, 90, 150]))] for _ in range(n)]
+    params = [SamplingParams(max_tokens=rng.choice([1, 3, 10, 40, 90]), ignore_eos=True) if rng.random() < 0.6 else
+              SamplingParams(max_tokens=rng.choice([5, 30, 60]), temperature=0.8, top_k=20, seed=rng.randrange(1000),
+                             ignore_eos=True) for _ in range(n)]
+
+    def drive(eng):
+        arrivals = random.Random(trial)
+        pending = list(range(n))
+        seqs, steps = {}, 0
+        while pending or eng.has_unfinished():
+            for _ in range(min(arrivals.choice([0, 0, 1, 2, 5]) if steps else 6, len(pending))):
+                i = pending.pop(0)
+                seqs[i] = eng.add_request(f"r{i}", prompts[i], params[i])
+            eng.step()
+            steps += 1
+            assert steps < 20000
+        eng.drain()
+        assert eng.cache.all_free and not eng.scheduler.running
+        return [seqs[i].output_ids for i in range(n)]
+
+    outs = {}
+    for dtype, kv_mb in (("float32", 1.2), ("bfloat16", 0.6)):        # room for 400 tokens: any request alone fits
+        for mode in (False, True):
+            eng = engine_for(d64_dir, dtype=dtype, max_model_len=512, max_num_seqs=24, max_num_batched_tokens=256,
+                             kv_cache_mb=kv_mb, async_decode=mode, cuda_graphs=True, cuda_graph_max_batch=32,
+                             enable_chunked_prefill=(trial % 3 == 0))
+            outs[dtype, mode] = drive(eng)
+            for ids, sp in zip(outs[dtype, mode], params):
+                assert len(ids) == sp.max_tokens and all(0 <= t < vocab for t in ids)
+    assert outs["float32", False] == outs["float32", True]

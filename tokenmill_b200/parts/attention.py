@@ -31,7 +31,11 @@ class AttentionScratch:
         self.device = device
         self.part_acc: torch.Tensor | None = None
         self.part_ml: torch.Tensor | None = None
-        self.done: torch.Tensor | None = None     # zero between launches
+        self.done: torch.Tensor | None = None     # zero between launches; the counters that go with the last get()
+        self._graph_done: torch.Tensor | None = None
+        self._x_acc: torch.Tensor | None = None   # a second set for steps that outgrow what graphs captured
+        self._x_ml: torch.Tensor | None = None
+        self._x_done: torch.Tensor | None = None
         self.frozen = False      # set once a graph has captured the pointers
         self._counters: torch.Tensor | None = None
         self._pf_acc: torch.Tensor | None = None
@@ -46,20 +50,37 @@ class AttentionScratch:
         return self._counters
 
     def reserve(self, rows: int, max_splits: int, head_dim: int) -> None:
+        """Make the buffers that captured graphs point at large enough (before the first capture)."""
         need_acc, need_ml = rows * max_splits * head_dim, rows * max_splits * 2
         if self.part_acc is None or self.part_acc.numel() < need_acc or self.part_ml.numel() < need_ml:
             if self.frozen:
                 raise RuntimeError("attention scratch would have to grow after a graph captured it")
             self.part_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
             self.part_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
-        if self.done is None or self.done.numel() < rows:     # arrival counters, one per (request, kv head) at most
+        if self._graph_done is None or self._graph_done.numel() < rows:   # arrival counters, one per (request, kv head) at most
             if self.frozen:
                 raise RuntimeError("attention scratch would have to grow after a graph captured it")
-            self.done = torch.zeros(rows, dtype=torch.int32, device=self.device)
+            self._graph_done = torch.zeros(rows, dtype=torch.int32, device=self.device)
+        self.done = self._graph_done
 
     def get(self, rows: int, max_splits: int, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
-        self.reserve(rows, max_splits, head_dim)
-        return self.part_acc, self.part_ml
+        """Buffers for ``rows`` rows of ``max_splits`` partial results; ``self.done`` then holds arrival
+        counters for as many rows. Once a graph has captured the first set, a step that needs more (a mixed
+        step of many tokens between graph replays) gets a second set of its own, which may grow: the graphs
+        keep pointing at the first."""
+        need_acc, need_ml = rows * max_splits * head_dim, rows * max_splits * 2
+        fits = (self.part_acc is not None and self.part_acc.numel() >= need_acc and self.part_ml.numel() >= need_ml
+                and self._graph_done is not None and self._graph_done.numel() >= rows)
+        if fits or not self.frozen:
+            self.reserve(rows, max_splits, head_dim)
+            return self.part_acc, self.part_ml
+        if self._x_acc is None or self._x_acc.numel() < need_acc or self._x_ml.numel() < need_ml:
+            self._x_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
+            self._x_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
+        if self._x_done is None or self._x_done.numel() < rows:
+            self._x_done = torch.zeros(rows, dtype=torch.int32, device=self.device)
+        self.done = self._x_done
+        return self._x_acc, self._x_ml
 
     def get_prefill(self, slots: int, head_dim: int, tiles: int, tile_rows: int = 64):
         """Scratch for the prompt kernel's per-(row tile, key chunk) partial results: ``slots`` slots of
