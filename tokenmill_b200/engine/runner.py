@@ -16,6 +16,7 @@ never hands out.
 from __future__ import annotations
 
 import bisect
+import gc
 import os
 
 import numpy as np
@@ -277,8 +278,18 @@ class _DecodeGraph:
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         launched_before = lib.launch_count
-        with torch.cuda.graph(self.graph, pool=runner._graph_pool):
-            self.logits = runner.model.forward(self.inputs, runner.layer_caches)
+        # No garbage collection while the stream is capturing: collecting an older engine's graphs (a process
+        # that has built several engines) destroys CUDA objects, which is not permitted during a capture and
+        # invalidates it.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=runner._graph_pool):
+                self.logits = runner.model.forward(self.inputs, runner.layer_caches)
+        finally:
+            if gc_was_on:
+                gc.enable()
         runner.kernels_per_graph[bucket] = lib.launch_count - launched_before   # this library's kernels per replay
         if runner._graph_pool is None:
             runner._graph_pool = self.graph.pool()

@@ -74,6 +74,8 @@ class AttentionScratch:
         if fits or not self.frozen:
             self.reserve(rows, max_splits, head_dim)
             return self.part_acc, self.part_ml
+        if torch.cuda.is_current_stream_capturing():     # a graph must never point at the set that may move
+            raise RuntimeError("attention scratch would have to grow after a graph captured it")
         if self._x_acc is None or self._x_acc.numel() < need_acc or self._x_ml.numel() < need_ml:
             self._x_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
             self._x_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
