@@ -688,3 +688,28 @@ def test_random_workloads_with_tiny_pools(d64_dir, trial):
             for ids, sp in zip(outs[dtype, mode], params):
                 assert len(ids) == sp.max_tokens and all(0 <= t < vocab for t in ids)
     assert outs["float32", False] == outs["float32", True]
+
+
+@pytest.mark.parametrize("trial", [0, 1, 2, 3])
+def test_greedy_tokens_survive_preemption_prefix_sharing_and_portions(d64_dir, trial):
+    """Sixteen greedy requests (some sharing a 37-token prefix) through a float32 engine with room for 200
+    tokens and 8 requests at a time, prompts cut into portions of 32 or 128, prefix caching on in half of the
+    trials, decode graphs, steps in flight or not: whatever the scheduler does (preempt and recompute, reuse a
+    prefix's pages, cut a prompt), every request's tokens are the plain implementation's greedy continuation."""
+    from tokenmill_b200.sampling import SamplingParams
+    cfg, w = load_plain(d64_dir)
+    vocab = json.loads((Path(d64_dir) / "config.json").read_text())["vocab_size"]
+    rng = random.Random(trial)
+    shared = [rng.randrange(vocab) for _ in range(rng.choice([0, 37]))]
+    prompts = [shared + [rng.randrange(vocab) for _ in range(rng.choice([1, 4, 20, 50]))] for _ in range(16)]
+    news = [rng.choice([1, 5, 20]) for _ in range(16)]
+    want = [plain_greedy(cfg, w, p, k) for p, k in zip(prompts, news)]
+    budget, block = rng.choice([32, 128]), rng.choice([8, 16])
+    for mode in (False, True):
+        eng = engine_for(d64_dir, dtype="float32", max_model_len=256, max_num_seqs=8, max_num_batched_tokens=budget,
+                         kv_cache_mb=3 * 2 * 64 * 2 * 4 * 200 / 2 ** 20, block_size=block, async_decode=mode,
+                         cuda_graphs=True, cuda_graph_max_batch=8, enable_chunked_prefill=trial % 2 == 0,
+                         enable_prefix_caching=trial >= 2)
+        got = eng.generate(prompts, [SamplingParams(max_tokens=k, ignore_eos=True) for k in news])
+        assert got == want, (mode, [i for i, (a, b) in enumerate(zip(got, want)) if a != b])
+        assert eng.cache.all_free
