@@ -450,7 +450,7 @@ def wide_dir(tmp_path_factory):
 
 
 @pytest.mark.parametrize("batch", [1, 5, 8, 9, 13, 16])
-def test_whole_step_kernel_at_model_sizes_equals_the_kernel_per_operation_path(wide_dir, batch):
+def test_whole_step_kernel_at_model_sizes_equals_the_kernel_per_operation_path(wide_dir, batch, monkeypatch):
     """Same requests, same steps, through the whole-step kernel and through the separate kernels: the logits
     agree within bfloat16 rounding, at batch sizes on both sides of the 8-token staging limit (above it the
     kernel runs with a single ring stage)."""
@@ -463,6 +463,8 @@ def test_whole_step_kernel_at_model_sizes_equals_the_kernel_per_operation_path(w
     def run(use_fused):
         old = fused._ENABLED
         fused._ENABLED = use_fused
+        # (the other path: launch by launch from Python, with the weight-streaming kernels for the decode steps)
+        monkeypatch.setenv("TOKENMILL_STEP_PROGRAM", "1" if use_fused else "0")
         try:
             eng = engine_for(wide_dir, dtype="bfloat16", max_model_len=1024, max_num_seqs=16, kv_cache_mb=64,
                              max_num_batched_tokens=4096)

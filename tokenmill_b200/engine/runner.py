@@ -60,14 +60,11 @@ class ModelRunner:
         # part of the model can write its launches down; TOKENMILL_STEP_PROGRAM=0 keeps the per-launch path.
         self._program = None
         self._no_program = os.environ.get("TOKENMILL_STEP_PROGRAM", "1") == "0"
-        # Small steps (up to 16 tokens) of a model whose matrices the weight-streaming kernels take keep the
-        # launch-by-launch path, where those kernels are; with large matrices the products are the library's
-        # anyway, and the program takes steps of any size.
-        mats = [w for b in model.blocks for w in (getattr(b.mixer, "w_qkv", None), getattr(b.mixer, "w_o", None),
-                                                  getattr(b.feed_forward, "w_gate_up", None),
-                                                  getattr(b.feed_forward, "w_down", None)) if w is not None]
-        streams_all = all(w.numel() * 2 <= ops.SKINNY_MAX_WEIGHT_BYTES for w in mats)
-        self._program_min_tokens = program_mod.MIN_TOKENS if streams_all else 1
+        # Steps of every size: what the whole-step kernel and the decode graphs do not take is still cheaper as
+        # one native walk over library products than as 200 launches from Python with the weight-streaming
+        # kernels (a 16-token prompt at the 0.5B sizes: 1.8 against 2.5 ms). Those kernels serve the captured
+        # decode graphs and models without a program.
+        self._program_min_tokens = 1
         self.graph_max_batch = min(cuda_graph_max_batch, max_num_seqs) if cuda_graphs else 0
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
@@ -119,7 +116,7 @@ class ModelRunner:
                     self.stats["fused_steps"] += 1
                     hidden = self.fused.run(step, self.cache.page_size)
                     return self._decode_logits(hidden)
-                return self.model.forward(step, self.layer_caches)
+                return self._general_step(entries, step=step)      # a short prompt: too many rows per kv head
         if self.graph_max_batch and len(entries) <= self.graph_max_batch and \
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return self._graph_step(entries)
@@ -134,11 +131,12 @@ class ModelRunner:
         return step
 
     def _general_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
-                      token_rows: list[int] | None = None) -> torch.Tensor:
+                      token_rows: list[int] | None = None, step: StepInputs | None = None) -> torch.Tensor:
         """Any step, through the step program where the model has one, else through the parts' forward
         methods. With ``token_src`` (int32, on the device) the entries bring one token each and entry i's is
         token_src[token_rows[i]], gathered into the step's input buffer behind its copy."""
-        step = self._inputs(entries)
+        if step is None:
+            step = self._inputs(entries)
         if token_src is not None:
             rows = torch.as_tensor(token_rows, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
             torch.index_select(token_src, 0, rows, out=step.token_ids)

@@ -37,7 +37,7 @@ if TYPE_CHECKING:
 OP_ADD_RMSNORM, OP_GEMM_BF16, OP_QKV_ROPE_WRITE = 1, 2, 3
 OP_PREFILL_ATTENTION_TC, OP_PREFILL_ATTENTION, OP_DECODE_ATTENTION, OP_SWIGLU = 4, 5, 6, 7
 MAX_ARGS = 24
-MIN_TOKENS = 17           # steps of up to 16 tokens have weight-streaming kernels of their own
+MIN_TOKENS = 1            # (a caller may keep small steps on the launch-by-launch path by asking for more)
 CUBLAS_WORKSPACE = 32 << 20
 
 lib.register_signature("tm_program_op_size", [])
