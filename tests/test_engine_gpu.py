@@ -715,3 +715,29 @@ def test_greedy_tokens_survive_preemption_prefix_sharing_and_portions(d64_dir, t
         got = eng.generate(prompts, [SamplingParams(max_tokens=k, ignore_eos=True) for k in news])
         assert got == want, (mode, [i for i, (a, b) in enumerate(zip(got, want)) if a != b])
         assert eng.cache.all_free
+
+
+def test_short_prompts_go_through_the_whole_step_kernel_in_pieces(d64_dir, tmp_path, plain_cache, monkeypatch):
+    """Prompts of up to 16 tokens (alone, beside other short prompts, beside decoded tokens) have more rows per
+    kv head than one attention unit of the whole-step kernel holds; they enter it as pieces of a few tokens each
+    and the logits at every place are the plain implementation's."""
+    from tokenmill_b200.kernels import lib
+    calls = []
+    real = lib.call
+    monkeypatch.setattr(lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
+    vocab = json.loads((Path(d64_dir) / "config.json").read_text())["vocab_size"]
+    reqs = make_requests(vocab, [30, 20, 12, 40], seed=21)
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": reqs["r0"][:11], "want": [0, 5, 10]}], "end": []},
+             {"step": 1, "entries": [{"id": "r1", "tokens": reqs["r1"][:7], "want": list(range(7))},
+                                     {"id": "r0", "tokens": reqs["r0"][11:12], "want": [0]},
+                                     {"id": "r2", "tokens": reqs["r2"][:3], "want": [2]}], "end": []},
+             {"step": 2, "entries": [{"id": "r3", "tokens": reqs["r3"][:16], "want": [15]}], "end": []},
+             {"step": 3, "entries": [{"id": "r0", "tokens": reqs["r0"][12:18], "want": [0, 5]},
+                                     {"id": "r1", "tokens": reqs["r1"][7:13], "want": [5]},
+                                     {"id": "r2", "tokens": reqs["r2"][3:4], "want": [0]},
+                                     {"id": "r3", "tokens": reqs["r3"][16:17], "want": [0]}], "end": ["r2"]},
+             {"step": 4, "entries": [{"id": "r0", "tokens": reqs["r0"][18:], "want": [11]},
+                                     {"id": "r3", "tokens": reqs["r3"][17:21], "want": [3]}], "end": ["r0", "r1", "r3"]}]
+    outputs = run_trace(d64_dir, "bfloat16", steps, 512, tmp_path / "o")
+    check_against_plain(steps, outputs, reqs, plain_for(d64_dir, reqs, plain_cache), "bfloat16")
+    assert calls.count("tm_decode_fused") == 5 and "tm_program_run" not in calls

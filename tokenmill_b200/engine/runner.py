@@ -111,7 +111,10 @@ class ModelRunner:
                 self.stats["h2d_bytes"] = self.fused.h2d_bytes
                 return self._decode_logits(hidden)
             if sum(len(e.tokens) for e in entries) <= self.fused.max_tokens:
-                step = self._inputs(entries)
+                # A short prompt has more rows per kv head than an attention unit of the kernel holds: it goes in
+                # as several pieces of a few tokens each (same pages, consecutive starts). All keys and values of
+                # a layer are in the cache before its attention begins, so a piece sees the pieces before it.
+                step = self._inputs(self._pieces_for_fused(entries) or entries)
                 if self.fused.takes(step):
                     self.stats["fused_steps"] += 1
                     hidden = self.fused.run(step, self.cache.page_size)
@@ -121,6 +124,22 @@ class ModelRunner:
                 all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return self._graph_step(entries)
         return self._general_step(entries)
+
+    def _pieces_for_fused(self, entries: list[StepEntry]) -> list[StepEntry] | None:
+        """The entries with every run of tokens cut to what one attention unit of the whole-step kernel takes
+        (16 rows of (token, head in group) per kv head), or None where that cannot be done (wanted places out
+        of order, more than 16 pieces)."""
+        rows = 16 // (self.fused.nh // self.fused.nkv)
+        if rows < 1 or all(len(e.tokens) <= rows for e in entries):
+            return None
+        pieces = []
+        for e in entries:
+            if list(e.want) != sorted(e.want):
+                return None
+            for a in range(0, len(e.tokens), rows):
+                b = min(a + rows, len(e.tokens))
+                pieces.append(StepEntry(e.handle, e.tokens[a:b], e.start + a, [w - a for w in e.want if a <= w < b]))
+        return pieces if len(pieces) <= fused.MAX_TOKENS else None
 
     def _inputs(self, entries: list[StepEntry]) -> StepInputs:
         """The step's batch on the device (one packed buffer, one copy)."""
