@@ -77,3 +77,30 @@ def test_program_builder_shares_parameters_and_buffers_by_name():
         assert False, "a record of 25 values must be refused"
     except ValueError:
         pass
+
+
+def test_short_prompts_are_cut_into_pieces_an_attention_unit_holds():
+    from types import SimpleNamespace
+
+    from tokenmill_b200.engine.batch import StepEntry
+    from tokenmill_b200.engine.runner import ModelRunner
+
+    def pieces(entries, nh, nkv):
+        me = SimpleNamespace(fused=SimpleNamespace(nh=nh, nkv=nkv))
+        return ModelRunner._pieces_for_fused(me, entries)
+
+    h1, h2 = object(), object()
+    # 7 heads per kv head: 2 tokens per piece; the wanted places move with their piece
+    got = pieces([StepEntry(h1, [10, 11, 12, 13, 14], 100, [0, 3, 4]), StepEntry(h2, [7], 5, [0])], 14, 2)
+    assert [(p.handle, p.tokens, p.start, p.want) for p in got] == [
+        (h1, [10, 11], 100, [0]), (h1, [12, 13], 102, [1]), (h1, [14], 104, [0]), (h2, [7], 5, [0])]
+    # nothing to cut: every entry already fits
+    assert pieces([StepEntry(h1, [1, 2], 0, [1]), StepEntry(h2, [3], 9, [0])], 14, 2) is None
+    # 3 heads per kv head: 5 tokens per piece
+    got = pieces([StepEntry(h1, list(range(12)), 0, [11])], 6, 2)
+    assert [(p.tokens, p.start, p.want) for p in got] == [(list(range(5)), 0, []), (list(range(5, 10)), 5, []),
+                                                           ([10, 11], 10, [1])]
+    # wanted places out of order, more heads per kv head than rows, or too many pieces: not cut
+    assert pieces([StepEntry(h1, [1, 2, 3, 4], 0, [3, 0])], 14, 2) is None
+    assert pieces([StepEntry(h1, [1, 2, 3], 0, [2])], 32, 1) is None
+    assert pieces([StepEntry(h1, list(range(34)), 0, [33])], 14, 2) is None
