@@ -32,7 +32,20 @@ sys.path.insert(0, str(ROOT))
 SIZES = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
              num_attention_heads=14, num_key_value_heads=2, head_dim=64, rope_theta=1000000.0, rms_norm_eps=1e-6,
              tie_word_embeddings=True, max_position_embeddings=32768)
+MODEL_LABEL = "Qwen2.5-0.5B"
 PROMPT_LEN, CONTEXT, BATCH, PREFILL_TOKENS, PAGE = 512, 4096, 8, 2048, 16
+
+
+def use_sizes(name: str) -> None:
+    """Measure another of the named sizes (--sizes qwen2.5-1.5b | qwen2.5-7b) instead of the default one."""
+    global MODEL_LABEL
+    from tokenmill_b200.weights.random_init import NAMED_SIZES
+    if name.lower() not in NAMED_SIZES:
+        raise SystemExit(f"bench.py: unknown --sizes {name!r}; known: {sorted(NAMED_SIZES)}")
+    named = NAMED_SIZES[name.lower()]
+    SIZES.update(named)
+    SIZES["head_dim"] = named.get("head_dim", named["hidden_size"] // named["num_attention_heads"])
+    MODEL_LABEL = name.replace("qwen", "Qwen").replace("b", "B") if name.lower().startswith("qwen") else name
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -296,14 +309,14 @@ def run_ours(args) -> dict:
     pf_flops = info["prefill_flops"](PREFILL_TOKENS)
     pf_frac = pf_flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12)
     return {
-        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, prompt 512, bf16)", "value": round(main["tok_s"], 1),
+        "metric": f"decode tok/s at batch 8 ({MODEL_LABEL} sizes, prompt 512, bf16)", "value": round(main["tok_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights seed 0", "impl": "ours",
-        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
+        "config": {"model": f"{MODEL_LABEL} sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
                    "hidden": SIZES["hidden_size"], "q_heads": SIZES["num_attention_heads"],
                    "kv_heads": SIZES["num_key_value_heads"], "head_dim": SIZES["head_dim"],
-                   "intermediate": SIZES["intermediate_size"], "vocab": SIZES["vocab_size"], "tied_output": True,
+                   "intermediate": SIZES["intermediate_size"], "vocab": SIZES["vocab_size"], "tied_output": bool(SIZES["tie_word_embeddings"]),
                    "global_batch": BATCH, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "kv_page": PAGE,
                    "mean_decode_context": round(main["mean_ctx"], 1), "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights read per step: %.0f MB)" % (info["weight_bytes"] / 1e6),
@@ -389,11 +402,11 @@ def run_reference(args) -> dict:
         tmp.cleanup()
     pf_ms = statistics.median(pre[2:])
     return {
-        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B sizes, prompt 512, bf16)", "value": round(main["tok_s_dev"], 1),
+        "metric": f"decode tok/s at batch 8 ({MODEL_LABEL} sizes, prompt 512, bf16)", "value": round(main["tok_s_dev"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random weights seed 0", "impl": "reference",
-        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "global_batch": BATCH, "prompt_len": PROMPT_LEN,
+        "config": {"model": f"{MODEL_LABEL} sizes", "layers": layers, "global_batch": BATCH, "prompt_len": PROMPT_LEN,
                    "seq_len": CONTEXT, "kv_page": PAGE, "reference_flags": "paged engine, cuda_graphs=True, max batch 64",
                    "parallelism": "single GPU"},
         "e2e": {"value": round(main["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": None,
@@ -411,6 +424,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
+    ap.add_argument("--sizes", default="", help="another named size (qwen2.5-1.5b, qwen2.5-7b) instead of Qwen2.5-0.5B")
     ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>' or 'products' and print its time")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
@@ -420,6 +434,8 @@ def main() -> int:
             print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.sizes:
+        use_sizes(args.sizes)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result:
         print(json.dumps(result), flush=True)
