@@ -222,11 +222,13 @@ def prefill_timed(engine, tokens: int, reps: int = 5) -> dict:
 
 def products_timed(tokens: int = 8) -> list[dict]:
     """Profiling aid (--only products): a decode step's matrix products at the Qwen2.5 0.5B / 1.5B / 7B layer
-    sizes, through this library's weight-streaming kernels and through the library product (plus the SwiGLU
-    kernel for gate/up), each after an L2 flush. It is what the size limits of kernels/ops.py
+    sizes, through this library's weight-streaming kernels ("streaming": plain loads; "ring": packed weights
+    through a shared-memory ring of bulk copies, the K range cut into slices) and through the library product
+    (plus the SwiGLU kernel for gate/up), each after an L2 flush. It is what the size limits of kernels/ops.py
     (SKINNY_MAX_WEIGHT_BYTES) and kernels/fused.py (MAX_LAYER_WEIGHT_BYTES) were read from."""
     import torch
     from tokenmill_b200.kernels import ops
+    from tokenmill_b200.kernels.fused import pack_rows
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def timed(fn, n=12):
@@ -252,13 +254,20 @@ def products_timed(tokens: int = 8) -> list[dict]:
         def lib_gate_up():
             torch.mm(x, w_gu.t(), out=gu)
             ops.swiglu(gu, act)
-        for what, ours, theirs, nbytes in (
-                ("qkv", lambda: ops.skinny_linear(x, w_qkv), lambda: torch.mm(x, w_qkv.t()), QKV * H * 2),
-                ("gate_up+swiglu", lambda: ops.skinny_gate_up_swiglu(x, w_gu, act), lib_gate_up, 2 * I * H * 2),
-                ("down", lambda: ops.skinny_linear(xi, w_d, k_splits=ks), lambda: torch.mm(xi, w_d.t()), H * I * 2)):
-            t_ours, t_lib = timed(ours), timed(theirs)
+        p_qkv, p_gu, p_d = pack_rows(w_qkv), pack_rows(w_gu), pack_rows(w_d)
+
+        def ring_gate_up():
+            ops.swiglu_partials(ops.stream_linear(x, p_gu, 2 * I), act)
+        for what, ours, ring, theirs, nbytes in (
+                ("qkv", lambda: ops.skinny_linear(x, w_qkv), lambda: ops.stream_linear(x, p_qkv, QKV),
+                 lambda: torch.mm(x, w_qkv.t()), QKV * H * 2),
+                ("gate_up+swiglu", lambda: ops.skinny_gate_up_swiglu(x, w_gu, act), ring_gate_up, lib_gate_up, 2 * I * H * 2),
+                ("down", lambda: ops.skinny_linear(xi, w_d, k_splits=ks), lambda: ops.stream_linear(xi, p_d, H),
+                 lambda: torch.mm(xi, w_d.t()), H * I * 2)):
+            t_ours, t_ring, t_lib = timed(ours), timed(ring), timed(theirs)
             rows.append({"sizes": name, "tokens": tokens, "product": what, "weight_mb": round(nbytes / 2 ** 20, 1),
                          "streaming_us": round(t_ours, 1), "streaming_tb_s": round(nbytes / t_ours / 1e6, 2),
+                         "ring_us": round(t_ring, 1), "ring_tb_s": round(nbytes / t_ring / 1e6, 2),
                          "library_us": round(t_lib, 1), "library_tb_s": round(nbytes / t_lib / 1e6, 2)})
     return rows
 

@@ -563,3 +563,44 @@ def test_output_matrix_streaming_kernel(T, N, K):
     diff = (out.cpu() - ref).abs().max()
     assert diff <= 1e-5 * max(1.0, float(ref.abs().max())), diff
     assert int(out[T - 1].argmax()) == N - 1
+
+
+@pytest.mark.parametrize("T", [1, 8, 13, 16])
+@pytest.mark.parametrize("N,K", [(1536, 8960), (3584, 18944), (17920, 1536), (200, 1032), (24, 4104)])
+def test_streaming_product_with_a_cut_k_range(T, N, K):
+    """The streaming product for K beyond what a warp's registers hold of the activations: the K range is cut
+    into slices of at most 1024 columns (the last shorter, or ending inside a 32-column chunk), every slice's
+    sums come back separately, and their sum in index order is the product."""
+    from tokenmill_b200.kernels.fused import pack_rows
+    ops = _ops()
+    g = torch.Generator().manual_seed(N + K + T)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.03).bfloat16()
+    ref = x.double() @ w.double().t()
+    parts = ops.stream_linear(x.to(DEV), pack_rows(w.to(DEV)), N)
+    ops.tc_check(torch.device(DEV))
+    S = -(-(-(-K // 32)) // 32)
+    assert parts.shape == (S, T, N) and parts.dtype == torch.float32
+    total = parts[0].clone()
+    for s in range(1, S):
+        total += parts[s]
+    assert (total.cpu().double() - ref).abs().max() <= 2e-5 * max(1.0, float(ref.abs().max()))
+    # a slice holds its own columns only: slice 0 is the product over the first columns
+    if S > 1:
+        width = -(-(-(-K // 32)) // S) * 32
+        first = x[:, :width].double() @ w[:, :width].double().t()
+        assert (parts[0].cpu().double() - first).abs().max() <= 2e-5 * max(1.0, float(first.abs().max()))
+
+
+@pytest.mark.parametrize("S,T,I", [(1, 3, 160), (9, 8, 8960), (4, 16, 44)])
+def test_swiglu_over_partial_sums(S, T, I):
+    ops = _ops()
+    g = torch.Generator().manual_seed(S + I)
+    parts = torch.randn(S, T, 2 * I, generator=g)
+    total = parts[0].clone()
+    for s in range(1, S):
+        total += parts[s]
+    gate, up = total[:, :I].bfloat16().float(), total[:, I:].bfloat16().float()
+    ref = (gate * torch.sigmoid(gate) * up)
+    out = ops.swiglu_partials(parts.to(DEV), torch.empty(T, I, dtype=torch.bfloat16, device=DEV))
+    assert (out.float().cpu() - ref).abs().max() <= 1e-2 * max(1.0, float(ref.abs().max()))

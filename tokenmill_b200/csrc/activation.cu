@@ -44,6 +44,34 @@ __global__ void __launch_bounds__(128) swiglu_vec_kernel(const T* __restrict__ g
   *reinterpret_cast<uint4*>(out + t * I + i) = o;
 }
 
+// SwiGLU over a gate/up product that arrives as float32 partial sums [S, T, 2 I] (a product whose K range was
+// cut): the slices are added in index order, gate and up are rounded to bfloat16 as a library product would have
+// left them, and out [T, I] = silu(gate) * up in bfloat16. I a multiple of 4.
+__global__ void __launch_bounds__(256) swiglu_partials_kernel(const float* __restrict__ parts, int S, long long stride,
+                                                              __nv_bfloat16* __restrict__ out, int I, long long total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int per_row = I / 4;
+  const long long t = idx / per_row;
+  const int i = (int)(idx - t * per_row) * 4;
+  float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < S; ++s) {
+    const float* row = parts + (size_t)s * stride + (size_t)t * 2 * I;
+    const float4 a = *reinterpret_cast<const float4*>(row + i), b = *reinterpret_cast<const float4*>(row + I + i);
+    g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+    u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
+  }
+  float o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float gf = to_float(from_float<__nv_bfloat16>(g[e])), uf = to_float(from_float<__nv_bfloat16>(u[e]));
+    o[e] = silu_mul(gf, uf);
+  }
+  store4<__nv_bfloat16>(out + t * I + i, o);
+}
+
 template <typename T>
 int launch_swiglu(const void* gu, void* out, int T_, int I, cudaStream_t stream) {
   constexpr int VEC = 16 / sizeof(T);
@@ -69,4 +97,15 @@ extern "C" int tm_swiglu(int dtype, const void* gu, void* out, int T, int I, cud
   if (dtype == TM_DTYPE_F32) return tmk::launch_swiglu<float>(gu, out, T, I, stream);
   if (dtype == TM_DTYPE_BF16) return tmk::launch_swiglu<__nv_bfloat16>(gu, out, T, I, stream);
   return TM_ERR_BAD_DTYPE;
+}
+
+// parts [S, T, 2 I] float32 (slice stride `stride` floats) -> out [T, I] bfloat16; I a multiple of 4.
+extern "C" int tm_swiglu_partials(const float* parts, int S, long long stride, void* out, int T, int I,
+                                  cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (S <= 0 || I % 4 || ((reinterpret_cast<uintptr_t>(parts) | reinterpret_cast<uintptr_t>(out)) & 15) || stride % 4)
+    return TM_ERR_UNSUPPORTED_SHAPE;
+  const long long total = (long long)T * (I / 4);
+  return tmk::launch_pdl(tmk::swiglu_partials_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, parts, S,
+                         stride, (__nv_bfloat16*)out, I, total);
 }

@@ -37,6 +37,9 @@ struct LmHeadArgs {
   int chunks;                  // K / 32 rounded up
   int n_stages_total;          // row-group pairs
   int ring;                    // stages in shared memory
+  int n_slices;                // cuts of the K range; a block works on one of them (blockIdx.x % n_slices)
+  int slice_chunks;            // chunks of a slice (the last may have fewer)
+  long long slice_stride;      // floats between two slices' outputs (T * N), 0 with one slice
   int* error;
 };
 
@@ -46,7 +49,12 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int group = warp >> 2, quarter = warp & 3;
-  const uint32_t group_bytes = (uint32_t)a.chunks * 512u, stage_bytes = 2u * group_bytes;
+  // A wide K range is cut into slices of at most 1024 columns (what a warp's registers hold of the
+  // activations); a block keeps one slice for all its row groups and writes that slice's partial sums.
+  const int slice = (int)blockIdx.x % a.n_slices;
+  const int my_chunks = min(a.slice_chunks, a.chunks - slice * a.slice_chunks);
+  const int pair0 = (int)blockIdx.x / a.n_slices, pair_step = (int)gridDim.x / a.n_slices;
+  const uint32_t group_bytes = (uint32_t)a.slice_chunks * 512u, stage_bytes = 2u * group_bytes;
   const uint32_t base = t5_smem(lh_smem);
   // shared memory: ring stages, then the partial sums (2 buffers x 8 warps x 32 lanes x 4 floats), then barriers
   float* red = reinterpret_cast<float*>(lh_smem + (size_t)a.ring * stage_bytes);
@@ -60,16 +68,18 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // this block's stages: blockIdx.x, blockIdx.x + gridDim.x, ...
-  const int my_stages = a.n_stages_total > (int)blockIdx.x ? (a.n_stages_total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  // this block's stages: row-group pairs pair0, pair0 + pair_step, ... (all of its own slice)
+  const int my_stages = a.n_stages_total > pair0 ? (a.n_stages_total - 1 - pair0) / pair_step + 1 : 0;
   auto issue = [&](int it) {                 // one thread: stage `it` of this block into ring slot it % ring
-    const int st = (int)blockIdx.x + it * (int)gridDim.x;
+    const int st = pair0 + it * pair_step;
     const int groups_here = min(2, n_groups - 2 * st);
-    const uint32_t bytes = (uint32_t)groups_here * group_bytes;
+    const uint32_t bytes = (uint32_t)my_chunks * 512u;
     const uint32_t bar = t5_smem(&bars[it % a.ring]);
-    mbar_expect_tx(bar, bytes);
-    bulk_load(base + (uint32_t)(it % a.ring) * stage_bytes, reinterpret_cast<const unsigned char*>(a.w) + (size_t)st * stage_bytes,
-              bytes, bar);
+    mbar_expect_tx(bar, (uint32_t)groups_here * bytes);
+    for (int gi = 0; gi < groups_here; ++gi)       // a group's chunks of this slice are one contiguous range
+      bulk_load(base + (uint32_t)(it % a.ring) * stage_bytes + (uint32_t)gi * group_bytes,
+                reinterpret_cast<const unsigned char*>(a.w) +
+                    ((size_t)(2 * st + gi) * a.chunks + (size_t)slice * a.slice_chunks) * 512, bytes, bar);
   };
   if (tid == 0)
     for (int it = 0; it < a.ring && it < my_stages; ++it) issue(it);
@@ -82,9 +92,9 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
   uint32_t xlo[CPW][4], xhi[CPW][4];
 #pragma unroll
   for (int c = 0; c < CPW; ++c) {
-    const int k = ((quarter * CPW + c) * 32) + 8 * t;
+    const int k = ((slice * a.slice_chunks + quarter * CPW + c) * 32) + 8 * t;
     uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-    if (quarter * CPW + c < a.chunks && k < a.K) {       // K is a multiple of 8: a piece is whole or absent
+    if (quarter * CPW + c < my_chunks && k < a.K) {      // K is a multiple of 8: a piece is whole or absent
       if (g < a.T) lo = *reinterpret_cast<const uint4*>(a.x + (size_t)g * a.K + k);
       if (g + 8 < a.T) hi = *reinterpret_cast<const uint4*>(a.x + (size_t)(g + 8) * a.K + k);
     }
@@ -103,7 +113,7 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
 #pragma unroll
       for (int c = 0; c < CPW; ++c) {
         const int chunk = quarter * CPW + c;
-        if (chunk < a.chunks) {
+        if (chunk < my_chunks) {
           uint32_t w0, w1, w2, w3;
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(wbase + (uint32_t)chunk * 512u));
           const uint32_t a0[4] = {xlo[c][0], xhi[c][0], xlo[c][1], xhi[c][1]};
@@ -126,9 +136,9 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
     const int src_lane = (tok & 7) * 4 + (col >> 1), src_reg = (tok >> 3) * 2 + (col & 1);
     const float* p = red + ((it & 1) * 8 + grp * 4) * 128 + src_lane * 4 + src_reg;
     const float sum = ((p[0] + p[128]) + p[256]) + p[384];
-    const int st = (int)blockIdx.x + it * (int)gridDim.x;
+    const int st = pair0 + it * pair_step;
     const int n = (2 * st + grp) * 8 + col;
-    if (tok < a.T && n < a.N) a.out[(size_t)tok * a.N + n] = sum;
+    if (tok < a.T && n < a.N) a.out[(size_t)slice * a.slice_stride + (size_t)tok * a.N + n] = sum;
   }
   // After an abort: the copies still on their way into this block's shared memory are waited for (bounded)
   // before the block gives the memory up.
@@ -142,16 +152,22 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
 
 }  // namespace tmk
 
-// x [T, K] bfloat16 (T <= 16, K a multiple of 8, at most 1024), w_packed the packed copy of w [N, K] (rows
-// padded to a multiple of 8, K to a multiple of 32), out [T, N] float32. `error`: a device int that must be
-// zero; a block whose wait runs out writes 21 there instead of hanging.
-extern "C" int tm_lm_head_bf16(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error,
-                               cudaStream_t stream) {
+// How many slices of the K range tm_stream_linear_bf16 cuts a product of K columns into (each at most 1024
+// columns, all but the last equally long): the caller sizes the output by it.
+extern "C" int tm_stream_linear_slices(int K) {
+  const int chunks = (K + 31) / 32;
+  return (chunks + 31) / 32;
+}
+
+// x [T, K] bfloat16 (T <= 16, K a multiple of 8), w_packed the packed copy of w [N, K] (rows padded to a
+// multiple of 8, K to a multiple of 32), out [n_slices, T, N] float32 with n_slices = tm_stream_linear_slices(K):
+// slice s holds the sums over its part of the K range (the caller, or the norm kernel that follows, adds the
+// slices in index order). `error`: a device int that must be zero; a block whose wait runs out writes 21 there
+// instead of hanging.
+extern "C" int tm_stream_linear_bf16(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error,
+                                     cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (T > 16 || K <= 0 || K % 8 || !error) return TM_ERR_UNSUPPORTED_SHAPE;
-  const int chunks = (K + 31) / 32;
-  const int cpw = (chunks + 3) / 4;
-  if (cpw > tmk::kLhMaxChunksPerWarp) return TM_ERR_UNSUPPORTED_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_packed)) & 15) return TM_ERR_UNSUPPORTED_SHAPE;
   static int n_sm = 0;
   if (!n_sm) {
@@ -159,19 +175,28 @@ extern "C" int tm_lm_head_bf16(const void* x, const void* w_packed, float* out, 
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
   }
+  const int chunks = (K + 31) / 32;
+  const int n_slices = tm_stream_linear_slices(K);
+  if (n_slices > n_sm) return TM_ERR_UNSUPPORTED_SHAPE;
+  const int slice_chunks = (chunks + n_slices - 1) / n_slices;
+  const int cpw = (slice_chunks + 3) / 4;
+  if (cpw > tmk::kLhMaxChunksPerWarp || (long long)slice_chunks * (n_slices - 1) >= chunks) return TM_ERR_UNSUPPORTED_SHAPE;
   tmk::LmHeadArgs a{};
   a.x = (const __nv_bfloat16*)x; a.w = (const __nv_bfloat16*)w_packed; a.out = out;
   a.T = T; a.N = N; a.K = K; a.chunks = chunks; a.error = error;
+  a.n_slices = n_slices; a.slice_chunks = slice_chunks; a.slice_stride = n_slices > 1 ? (long long)T * N : 0;
   const int n_groups = (N + 7) / 8;
   a.n_stages_total = (n_groups + 1) / 2;
-  const size_t stage_bytes = (size_t)2 * chunks * 512;
+  const size_t stage_bytes = (size_t)2 * slice_chunks * 512;
   const size_t fixed = 2 * 8 * 128 * sizeof(float) + 64 * sizeof(uint64_t) + 64;
   int ring = (int)((200 * 1024 - fixed) / stage_bytes);
   if (ring > 32) ring = 32;
   if (ring < 2) return TM_ERR_UNSUPPORTED_SHAPE;
   a.ring = ring;
   const size_t smem = (size_t)ring * stage_bytes + fixed;
-  const int grid = a.n_stages_total < n_sm ? a.n_stages_total : n_sm;
+  int per_slice = n_sm / n_slices;                       // blocks per slice: the grid is a multiple of n_slices
+  if (per_slice > a.n_stages_total) per_slice = a.n_stages_total;
+  const int grid = per_slice * n_slices;
 #define LH_CASE(C)                                                                                               \
   {                                                                                                              \
     auto kern = tmk::lm_head_kernel<C>;                                                                          \
@@ -189,4 +214,11 @@ extern "C" int tm_lm_head_bf16(const void* x, const void* w_packed, float* out, 
   if (cpw <= 7) LH_CASE(7)
   LH_CASE(8)
 #undef LH_CASE
+}
+
+// The output matrix of a decode step: tm_stream_linear_bf16 for a K of at most 1024 columns (one slice), out [T, N].
+extern "C" int tm_lm_head_bf16(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error,
+                               cudaStream_t stream) {
+  if (K > 1024) return TM_ERR_UNSUPPORTED_SHAPE;
+  return tm_stream_linear_bf16(x, w_packed, out, T, N, K, error, stream);
 }

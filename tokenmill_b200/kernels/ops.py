@@ -375,6 +375,38 @@ def lm_head(x: torch.Tensor, w_packed: torch.Tensor, n_rows: int, error: torch.T
     return out
 
 
+def stream_linear_ok(T: int, K: int) -> bool:
+    """Whether the streaming kernel takes a product of T tokens over K columns (any number of rows)."""
+    return 0 < T <= LM_HEAD_MAX_TOKENS and K % 8 == 0 and -(-K // 1024) <= 128
+
+
+def stream_linear(x: torch.Tensor, w_packed: torch.Tensor, n_rows: int, error: torch.Tensor | None = None) -> torch.Tensor:
+    """x [T, K] bfloat16 (T <= 16) times a matrix given as its packed copy (kernels/fused.py pack_rows of
+    w [n_rows, K]) -> float32 partial products [S, T, n_rows], one per slice of at most 1024 columns of K
+    (S = 1 for K <= 1024): the weights stream through shared memory at the memory's rate. The norm kernel adds
+    such slices in index order (``Pending.partials``), ``swiglu_partials`` does for a gate/up product."""
+    T, K = x.shape
+    if not stream_linear_ok(T, K) or x.dtype != torch.bfloat16 or w_packed.dtype != torch.bfloat16:
+        raise lib.KernelError(f"stream_linear: {T} tokens of {K} columns in {x.dtype} are not taken")
+    if w_packed.dim() != 5 or w_packed.shape[0] * 8 < n_rows or w_packed.shape[1] * 32 < K or not w_packed.is_contiguous():
+        raise lib.KernelError("stream_linear: the packed matrix does not fit the sizes given")
+    S = int(lib.load().tm_stream_linear_slices(K))
+    out = torch.empty((S, T, n_rows), dtype=torch.float32, device=x.device)
+    lib.call("tm_stream_linear_bf16", _req(x, "x", torch.bfloat16), w_packed.data_ptr(), out.data_ptr(), T, n_rows, K,
+             (error if error is not None else _tc_flag(x.device)).data_ptr(), _stream())
+    return out
+
+
+def swiglu_partials(parts: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """parts [S, T, 2 I] float32 partial gate/up products -> out [T, I] bfloat16 = silu(gate) * up."""
+    S, T, two_i = parts.shape
+    if two_i % 8 or out.shape != (T, two_i // 2) or out.dtype != torch.bfloat16:
+        raise lib.KernelError(f"swiglu_partials: parts {tuple(parts.shape)} and out {tuple(out.shape)} do not fit")
+    lib.call("tm_swiglu_partials", _req(parts, "parts", torch.float32), S, parts.stride(0), _req(out, "out", torch.bfloat16),
+             T, two_i // 2, _stream())
+    return out
+
+
 def skinny_qkv_rope_write(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor,
                           cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
                           kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, D: int) -> None:
