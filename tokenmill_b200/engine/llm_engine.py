@@ -168,10 +168,9 @@ class LLMEngine:
     def _pipelining(self) -> bool:
         """Decode steps may stay in flight: the runner can take token ids from the device (the whole-step
         kernel reads them, a captured graph has them gathered), and nothing in the configuration needs a
-        step's token ids on the host at once (prefix caching hashes them; mixed steps re-plan prompt
-        portions)."""
-        return (self.cfg.async_decode and self.runner.feeds_tokens_on_device and not self.cfg.enable_chunked_prefill
-                and not self.cfg.enable_prefix_caching)
+        step's token ids on the host at once (prefix caching hashes them). With chunked prompts a plan that
+        holds a prompt portion is simply not launched ahead: it runs once the step in flight has been read."""
+        return self.cfg.async_decode and self.runner.feeds_tokens_on_device and not self.cfg.enable_prefix_caching
 
     # --- one step -------------------------------------------------------------------------------
 
