@@ -37,7 +37,7 @@ from ..weights.loader import load_model, resolve_dtype
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import Scheduler
-from .sequence import RequestOutput, Sequence
+from .sequence import PLACEHOLDER, RequestOutput, Sequence, Status
 
 log = logging.getLogger("tokenmill_b200.engine")
 
@@ -75,7 +75,6 @@ def kv_budget_bytes(cfg: EngineConfig, model: DecoderModel) -> int:
     return budget
 
 
-PLACEHOLDER = -1        # stands in a request's output list for a token that is chosen but not read yet
 
 
 class _InFlight:
@@ -168,9 +167,11 @@ class LLMEngine:
     def _pipelining(self) -> bool:
         """Decode steps may stay in flight: the runner can take token ids from the device (the whole-step
         kernel reads them, a captured graph has them gathered), and nothing in the configuration needs a
-        step's token ids on the host at once (prefix caching hashes them). With chunked prompts a plan that
-        holds a prompt portion is simply not launched ahead: it runs once the step in flight has been read."""
-        return self.cfg.async_decode and self.runner.feeds_tokens_on_device and not self.cfg.enable_prefix_caching
+        step's token ids on the host at once. With chunked prompts a plan that holds a prompt portion is simply
+        not launched ahead: it runs once the step in flight has been read. With prefix caching a page is
+        published when the step that filled it has been read (its ids are known then), and a preempted request
+        whose last token is still on the device waits for it before it is admitted again."""
+        return self.cfg.async_decode and self.runner.feeds_tokens_on_device
 
     # --- one step -------------------------------------------------------------------------------
 
@@ -270,6 +271,9 @@ class LLMEngine:
             tok = tokens[row]
             seq.output_ids[at] = tok
             n_new += 1
+            if seq.status == Status.RUNNING:              # (a preempted request holds no pages to publish)
+                self.cache.register_computed(seq.cache, seq.prompt_ids + seq.output_ids[:at + 1],
+                                             seq.num_prompt_tokens + at)
             if seq.first_token_time is None:
                 seq.first_token_time = now
             n_out = at + 1

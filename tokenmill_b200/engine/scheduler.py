@@ -146,6 +146,8 @@ class Scheduler:
         """The head of the waiting queue if it can be admitted now; drops heads that never fit."""
         while self.waiting and len(self.running) < self.cfg.max_num_seqs:
             seq = self.waiting[0]
+            if seq.awaits_token:          # preempted with a step in flight: its last id is not on the host yet
+                return None
             status = self.cache.admission_status(seq.cache, seq.all_token_ids)
             if status == AllocStatus.NEVER:
                 self.waiting.popleft()

@@ -9,6 +9,9 @@ from ..cache.manager import CacheHandle
 from ..sampling.params import SamplingParams
 
 
+PLACEHOLDER = -1        # stands in a request's output list for a token that is chosen but not read yet
+
+
 class Status(Enum):
     WAITING = 0
     RUNNING = 1
@@ -63,6 +66,11 @@ class Sequence:
     def num_new_tokens(self) -> int:
         """Tokens the next forward pass has to run for this request: the whole uncached tail."""
         return self.length - self.num_computed_tokens
+
+    @property
+    def awaits_token(self) -> bool:
+        """Its last token is still on the device (a decode step in flight): the ids are not all known."""
+        return bool(self.output_ids) and self.output_ids[-1] == PLACEHOLDER
 
     @property
     def is_finished(self) -> bool:
