@@ -234,3 +234,22 @@ def test_random_workloads_always_drain_and_return_every_page():
             cache.check_invariants()
         assert not sched.has_unfinished(), f"seed {seed} did not drain"
         assert cache.all_free and all(s.is_finished for s in seqs)
+
+
+def test_a_request_whose_last_token_is_still_on_the_device_is_not_admitted():
+    """Preempted while a decode step was in flight: its output list ends in a placeholder. Until the engine
+    has read that token the request stays at the head of the queue (nothing behind it jumps ahead), and it is
+    admitted as soon as the id is known."""
+    from tokenmill_b200.engine.sequence import PLACEHOLDER
+    for chunked in (False, True):
+        sched, cache = make(enable_chunked_prefill=chunked, enable_prefix_caching=True)
+        a = seq(sched, cache, "a", 6)
+        b = seq(sched, cache, "b", 3, first=50)
+        a.output_ids += [9, PLACEHOLDER]
+        assert a.awaits_token and not b.awaits_token
+        plan = sched.schedule()
+        assert plan.empty and a.status == Status.WAITING and b.status == Status.WAITING
+        assert not a.cache.page_hashes                     # nothing was hashed over an unknown id
+        a.output_ids[-1] = 11
+        plan = sched.schedule()
+        assert [i.seq.id for i in plan.items][0] == "a" and a.status == Status.RUNNING
