@@ -11,7 +11,7 @@ from tokenmill_b200.config import ConfigError, EngineConfig, Qwen2Config, add_en
 from tokenmill_b200.parts.model import DecoderModel
 from tokenmill_b200.registry import RegistryError, architecture_names, get_architecture, get_part
 from tokenmill_b200.weights import WeightError, named_config, read_spec, write_random_model
-from tokenmill_b200.weights.loader import limit_positions, load_tensors
+from tokenmill_b200.weights.loader import load_tensors
 
 BASE = named_config("tiny-a")
 
@@ -157,11 +157,21 @@ def test_no_safetensors_and_unknown_architecture(tmp_path):
 
 
 def test_limit_positions_sizes_the_tables(tmp_path):
+    """The engine's own limit reaches the position tables through the parts' hooks, and the model reports the
+    shortest table as the longest sequence it serves."""
+    from tokenmill_b200.parts.model import DecoderModel
     d = write_random_model(tmp_path / "a", named_config("tiny-a"), seed=0)
     spec, _ = read_spec(d)
-    cut = limit_positions(spec, 100)
-    assert cut.max_positions == 100 and cut.layers[0].mixer.params["position"].params["max_positions"] == 100
-    assert limit_positions(spec, 10 ** 9).max_positions == spec.max_positions
+    model = DecoderModel(spec, torch.float32, torch.device("cpu"))
+    assert model.max_positions() == spec.max_positions == 1024
+    model.limit_positions(100)
+    assert model.max_positions() == 100
+    assert all(b.mixer.position.max_positions == 100 for b in model.blocks)
+    model.limit_positions(10 ** 9)                     # a larger limit never grows the tables
+    assert model.max_positions() == 100
+    model.bind({w.name: torch.zeros(w.shape) for w in model.weight_specs()})
+    assert model.blocks[0].mixer.cos.shape == (100, spec.layers[0].mixer.params["head_dim"] // 2)
+    assert model.activation_bytes(10) > 10 * spec.hidden_size * 8
 
 
 def test_cache_layout_groups_layers_and_shared_caches():

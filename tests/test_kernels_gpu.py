@@ -11,6 +11,8 @@ import torch
 from plain_qwen2 import (plain_apply_rope, plain_causal_attention, plain_filtered_probs, plain_inverse_cdf,
                          plain_rmsnorm, plain_rope_tables, plain_silu)
 
+from kernel_cases import paged_case as _paged_case
+
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
@@ -105,49 +107,6 @@ def test_qkv_rope_write(dtype, nh, nkv, D, page):
     assert float(flat_k[untouched.to(DEV)].abs().max()) == 0      # nothing written elsewhere
 
 
-def _paged_case(nh, nkv, D, page, q_lens, befores, dtype, seed, window=0):
-    """Random requests laid out in a shuffled paged cache; returns device tensors and the plain result."""
-    from tokenmill_b200.engine.batch import tiles_for
-    import numpy as np
-
-    g = torch.Generator().manual_seed(seed)
-    S = len(q_lens)
-    G = nh // nkv
-    totals = [b + n for b, n in zip(befores, q_lens)]
-    n_pages = sum(-(-t // page) for t in totals) + 3
-    perm = torch.randperm(n_pages, generator=g).tolist()
-    kc = torch.randn(n_pages, page, nkv, D, generator=g).to(dtype)     # stale noise in every unused slot
-    vc = torch.randn(n_pages, page, nkv, D, generator=g).to(dtype)
-    W = max(-(-t // page) for t in totals)
-    table = torch.zeros(S, W, dtype=torch.int32)
-    qs, refs = [], []
-    for s in range(S):
-        k = torch.randn(totals[s], nkv, D, generator=g).to(dtype)
-        v = torch.randn(totals[s], nkv, D, generator=g).to(dtype)
-        q = torch.randn(q_lens[s], nh, D, generator=g).to(dtype)
-        if totals[s] > 40:                                           # one far key dominates one query head
-            q[-1, 0] = 0
-            q[-1, 0, 0] = 6.0
-            k[3, 0] = 0
-            k[3, 0, 0] = 6.0 * math.sqrt(D) / 1.5
-        for i in range(-(-totals[s] // page)):
-            table[s, i] = perm.pop()
-            lo, hi = i * page, min((i + 1) * page, totals[s])
-            kc[table[s, i], :hi - lo] = k[lo:hi]
-            vc[table[s, i], :hi - lo] = v[lo:hi]
-        qs.append(q)
-        refs.append(plain_causal_attention(q.float(), k.float(), v.float(), D ** -0.5, window=window or None))
-    q_all = torch.cat(qs)
-    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
-    tile_seq, tile_row0 = tiles_for(np.array(q_lens, dtype=np.int32), G)
-    seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), torch.tensor(q_lens))
-    dev = lambda t: t.to(DEV)
-    return dict(q=dev(q_all), kc=dev(kc), vc=dev(vc), table=dev(table), cu=dev(cu),
-                before=dev(torch.tensor(befores, dtype=torch.int32)), tile_seq=dev(torch.from_numpy(tile_seq)),
-                tile_row0=dev(torch.from_numpy(tile_row0)), n_tiles=len(tile_seq), seq_of=dev(seq_of),
-                ref=torch.cat(refs))
-
-
 ATTN_SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (14, 2, 64, 16), (6, 3, 48, 5), (12, 2, 128, 32), (40, 1, 16, 16),
                (2, 2, 256, 16), (5, 1, 80, 1)]
 
@@ -216,7 +175,7 @@ def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
 def test_prefill_attention_tensor_core_kernel(nh, nkv, D, page, window):
     """The bfloat16 prompt kernel: whole prompts, later portions that start off a tile or page edge, short
     portions and single tokens in the same launch; tiles that end inside a key block; windows."""
-    from tokenmill_b200.engine.batch import packed_units
+    from tokenmill_b200.parts.attention_plan import packed_units
     from tokenmill_b200.parts.base import PrefillUnits
     import numpy as np
     ops = _ops()
@@ -250,7 +209,7 @@ def test_prefill_attention_tcgen05_kernel(nh, nkv, page, window, D):
     tiles, scores and outputs in tensor memory): whole
     prompts, later portions that start off a tile or page edge, short portions and single tokens in the same
     launch; tiles that end inside a key block; key chunks so short that most tiles have several; windows."""
-    from tokenmill_b200.engine.batch import packed_units
+    from tokenmill_b200.parts.attention_plan import packed_units
     from tokenmill_b200.parts.base import PrefillUnits
     import numpy as np
     ops = _ops()
@@ -280,7 +239,7 @@ def test_prefill_attention_tcgen05_kernel(nh, nkv, page, window, D):
 def test_prefill_attention_tcgen05_kernel_merges_more_chunks_than_fit_shared_memory():
     """A row tile whose keys make so many chunks (57 of 128 keys) that not even 8 rows of all of them fit in
     shared memory is merged piece by piece from the L2 instead; a tile with 29 chunks takes several passes."""
-    from tokenmill_b200.engine.batch import packed_units
+    from tokenmill_b200.parts.attention_plan import packed_units
     from tokenmill_b200.parts.base import PrefillUnits
     import numpy as np
     ops = _ops()

@@ -33,11 +33,11 @@ def rand_weights(part, seed, dtype):
     return dev, cpu
 
 
-def step_for(cache, entries):
-    from tokenmill_b200.engine.batch import build_step_inputs
-    from tokenmill_b200.parts.attention import AttentionScratch
-    return build_step_inputs(entries, cache, DEV, group_sizes=[1, 2, 3, 4, 7], scratch=AttentionScratch(DEV),
-                             split_keys=256)
+def step_for(cache, entries, parts=()):
+    """The step's inputs with the metadata the given parts ask for, and a workspace for their scratch."""
+    from tokenmill_b200.engine.batch import build_step_inputs, metadata_providers
+    from tokenmill_b200.engine.workspace import Workspace
+    return build_step_inputs(entries, cache, DEV, metadata_providers(parts), workspace=Workspace(DEV))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -88,7 +88,7 @@ def test_attention_mixer_through_the_cache(dtype, H, nh, nkv, D, page):
     cache.allocate(h, list(range(n)))
     outs = []
     for start, size in [(0, 30), (30, 14), (44, 1)]:                       # whole part, later portion, one token
-        step = step_for(cache, [StepEntry(h, list(range(size)), start)])
+        step = step_for(cache, [StepEntry(h, list(range(size)), start)], [mixer])
         outs.append(mixer.forward(x[start:start + size].to(DEV), step, lc))
     got = torch.cat(outs).float().cpu()
     assert (got - ref).abs().max() <= tol(dtype, ref)

@@ -5,7 +5,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from tokenmill_b200.engine.batch import PREFILL_CHUNK, choose_chunk, packed_units
+from tokenmill_b200.parts.attention_plan import PREFILL_CHUNK, choose_chunk, packed_units
 
 
 def _keys_per_tile(q_lens, starts, G, tile):

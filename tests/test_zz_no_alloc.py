@@ -36,7 +36,7 @@ def _call_noalloc(c, nh, nkv, D, page, n_seqs, window, max_splits, out):
 
 @pytest.mark.parametrize("nh,nkv,D,page", [(14, 2, 64, 16), (8, 2, 128, 8)])
 def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row(nh, nkv, D, page):
-    from test_kernels_gpu import _paged_case
+    from kernel_cases import paged_case as _paged_case
     from tokenmill_b200.kernels import ops
 
     for call, (befores, window) in enumerate([([0, 255, 256, 700, 1000, 63, 511], 0), ([900, 3, 300, 64, 1, 513, 128], 150)]):
@@ -63,7 +63,7 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row(nh, nkv, D,
 
 
 def test_noalloc_entry_point_refuses_what_does_not_fit():
-    from test_kernels_gpu import _paged_case
+    from kernel_cases import paged_case as _paged_case
 
     c = _paged_case(14, 2, 64, 16, q_lens=[1, 1], befores=[10, 20], dtype=torch.bfloat16, seed=1)
     out = torch.empty_like(c["q"])

@@ -3,8 +3,8 @@
 One tensor per group, ``[entries, 2 (K and V), pages, page_size, kv_heads, head_dim]`` in the run's
 dtype (the reference keeps one such tensor for all layers, src/infer/kv/paged_cache.py:25-34), and
 one tensor per stateful run-order entry, ``[slots, *shape]``. A ``sink`` page may be appended to each
-group: padded rows of a captured decode graph write there, and the manager never hands it out
-(src/infer/engine/cuda_graphs.py:56-58).
+group, and a sink slot to the state tensors: padded rows of a captured decode graph write there, and the
+manager never hands them out (src/infer/engine/cuda_graphs.py:56-58).
 """
 
 from __future__ import annotations
@@ -28,7 +28,8 @@ class CachePools:
         self.kv = [torch.zeros((len(g.entries), 2, n + extra, page_size, g.need.kv_heads, g.need.head_dim),
                                dtype=dtype, device=device)
                    for g, n in zip(layout.groups, num_pages)]
-        self.state = {pos: torch.zeros((max(num_state_slots, 1), *need.shape), dtype=_STATE_DTYPES[need.dtype],
+        self.state_sink = num_state_slots if sink_page else -1        # index of the sink state slot
+        self.state = {pos: torch.zeros((max(num_state_slots, 1) + extra, *need.shape), dtype=_STATE_DTYPES[need.dtype],
                                        device=device)
                       for pos, need in layout.entry_state.items()}
         self._cache_of = run_order_cache_of or []

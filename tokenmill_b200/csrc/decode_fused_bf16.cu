@@ -565,7 +565,10 @@ __device__ __forceinline__ void fu_project(const FusedArgs& a, const FusedLayer&
         float o1 = x1, o2 = x2;
         if (head < a.nh + a.nkv) {
           int pos = a.positions[tok];
-          pos = pos < 0 ? 0 : (pos >= a.n_pos ? a.n_pos - 1 : pos);
+          if (pos < 0 || pos >= a.n_pos) {                 // never read outside the tables; tell the host
+            atomicCAS(a.error, 0, 31);
+            pos = pos < 0 ? 0 : a.n_pos - 1;
+          }
           const float cs = a.cos_t[(size_t)pos * half + i], sn = a.sin_t[(size_t)pos * half + i];
           o1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
           o2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));

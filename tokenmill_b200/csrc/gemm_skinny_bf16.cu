@@ -47,6 +47,7 @@ struct SkinnyArgs {
   __nv_bfloat16* kcache;
   __nv_bfloat16* vcache;
   int nh, nkv, D, n_pos;
+  int* error;                 // QKV: set to 31 when a position lies outside the tables (may be null)
   int inter;                  // SWIGLU: I
 };
 
@@ -184,7 +185,10 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(const Skinny
       float o1 = x1, o2 = x2;
       if (head < a.nh + a.nkv) {
         int pos = a.positions[t];
-        pos = pos < 0 ? 0 : (pos >= a.n_pos ? a.n_pos - 1 : pos);
+        if (pos < 0 || pos >= a.n_pos) {                   // never read outside the tables; tell the host
+          if (a.error) atomicCAS(a.error, 0, 31);
+          pos = pos < 0 ? 0 : a.n_pos - 1;
+        }
         const float cs = a.cos_t[(size_t)pos * half + i], sn = a.sin_t[(size_t)pos * half + i];
         o1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
         o2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
@@ -292,7 +296,7 @@ extern "C" int tm_skinny_linear(const void* x, int ldx, const void* w, const flo
 extern "C" int tm_skinny_qkv_rope_write(const void* x, int ldx, const void* w, const float* bias,
                                         const int* positions, const float* cos_t, const float* sin_t,
                                         const int* slot_map, void* q_out, void* kcache, void* vcache, int T, int K,
-                                        int nh, int nkv, int D, int n_pos, cudaStream_t stream) {
+                                        int nh, int nkv, int D, int n_pos, int* error, cudaStream_t stream) {
   if (D % 16) return TM_ERR_UNSUPPORTED_SHAPE;
   tmk::SkinnyArgs a{};
   a.x = (const __nv_bfloat16*)x;
@@ -301,7 +305,7 @@ extern "C" int tm_skinny_qkv_rope_write(const void* x, int ldx, const void* w, c
   a.k_per_block = K;
   a.bias = bias; a.positions = positions; a.cos_t = cos_t; a.sin_t = sin_t; a.slot_map = slot_map;
   a.q_out = (__nv_bfloat16*)q_out; a.kcache = (__nv_bfloat16*)kcache; a.vcache = (__nv_bfloat16*)vcache;
-  a.nh = nh; a.nkv = nkv; a.D = D; a.n_pos = n_pos;
+  a.nh = nh; a.nkv = nkv; a.D = D; a.n_pos = n_pos; a.error = error;
   return tmk::sk_launch(a, (nh + 2 * nkv) * (D / 16), 1, stream);
 }
 

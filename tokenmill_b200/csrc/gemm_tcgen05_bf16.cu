@@ -230,7 +230,10 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
         int pos = 0, slot = -1;
         if (row_ok) {
           pos = a.positions[t];
-          pos = pos < 0 ? 0 : (pos >= a.n_pos ? a.n_pos - 1 : pos);
+          if (pos < 0 || pos >= a.n_pos) {                 // never read outside the tables; tell the host
+            if (a.error) atomicCAS(a.error, 0, 31);
+            pos = pos < 0 ? 0 : a.n_pos - 1;
+          }
           slot = a.slot_map ? a.slot_map[t] : -1;
         }
 #pragma unroll 1

@@ -27,7 +27,7 @@ int tm_add_rmsnorm(int dtype, float* resid, const void* branch, const float* par
                    float eps, void* out, int n_rows, int H, cudaStream_t stream);
 int tm_qkv_rope_write(int in_dtype, int dtype, const void* qkv, const float* bias, const int* positions,
                       const float* cos_t, const float* sin_t, const int* slot_map, void* q_out, void* kcache,
-                      void* vcache, int T, int nh, int nkv, int D, int n_pos, cudaStream_t stream);
+                      void* vcache, int T, int nh, int nkv, int D, int n_pos, int* error, cudaStream_t stream);
 int tm_swiglu(int dtype, const void* gu, void* out, int T, int I, cudaStream_t stream);
 int tm_prefill_attention_tc_bf16(const void* q, const void* kcache, const void* vcache, const int* block_table,
                                  int bt_stride, const int* unit_rec, int n_units, int chunk_keys, float* part_acc,
@@ -145,12 +145,13 @@ static int run_op(const ProgramOp& op, const int64_t* a, cudaStream_t s) {
       if (op.n_args != 7) return TM_ERR_PROGRAM;
       return gemm_bf16(as_ptr<const void>(a[0]), as_ptr<const void>(a[1]), as_ptr<void>(a[2]), (int)a[3], (int)a[4], (int)a[5],
                        (int)a[6], s);
-    case kOpQkvRopeWrite:  // in_dtype, dtype, qkv, bias, positions, cos, sin, slot_map, q_out, kcache, vcache, T, nh, nkv, D, n_pos
-      if (op.n_args != 16) return TM_ERR_PROGRAM;
+    case kOpQkvRopeWrite:  // in_dtype, dtype, qkv, bias, positions, cos, sin, slot_map, q_out, kcache, vcache, T, nh, nkv, D,
+                           // n_pos, error
+      if (op.n_args != 17) return TM_ERR_PROGRAM;
       return tm_qkv_rope_write((int)a[0], (int)a[1], as_ptr<const void>(a[2]), as_ptr<const float>(a[3]), as_ptr<const int>(a[4]),
                                as_ptr<const float>(a[5]), as_ptr<const float>(a[6]), as_ptr<const int>(a[7]), as_ptr<void>(a[8]),
                                as_ptr<void>(a[9]), as_ptr<void>(a[10]), (int)a[11], (int)a[12], (int)a[13], (int)a[14],
-                               (int)a[15], s);
+                               (int)a[15], as_ptr<int>(a[16]), s);
     case kOpPrefillAttentionTc:  // q, k, v, table, bt_stride, units, n_units, chunk, acc, ml, tile_done, counters, out,
                                  // nh, nkv, D, page, scale, window, error
       if (op.n_args != 20) return TM_ERR_PROGRAM;

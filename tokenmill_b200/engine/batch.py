@@ -4,20 +4,22 @@ The reference builds five int64 tensors from Python lists over every token and c
 (src/infer/engine/model_runner.py:30-32,40-74). Here the same information (token ids, absolute
 positions, cache slots, block tables, per-request offsets, rows whose logits are wanted) is laid out
 with numpy in a single pinned buffer; the device tensors the kernels read are views of one
-allocation.
+allocation. The parts of the model add their own sections to that buffer: each part that has a
+``step_metadata`` hook is asked once per step (parts with the same ``metadata_key()`` share one answer),
+and its integer arrays travel in the same copy (``StepInputs.meta``). The engine does not know what
+they mean.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from typing import Hashable
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheHandle, CacheManager
-from ..parts.base import PrefillUnits, StepInputs
-
-TILE_ROWS = 32       # rows of (token, head-in-group) one attention tile covers
+from ..parts.base import PartMeta, StepInputs, StepMetadata, StepShape, part_metadata_key
 
 
 @dataclass
@@ -31,12 +33,38 @@ class StepEntry:
     want: list[int] = field(default_factory=list)
 
 
-class Layout:
-    """Offsets of every section inside the packed buffer, for given sizes."""
+def metadata_providers(parts) -> dict[Hashable, object]:
+    """The parts that ask for step metadata, one per distinct key, in first-seen order."""
+    out: dict[Hashable, object] = {}
+    for p in parts:
+        key = part_metadata_key(p)
+        if key is not None and key not in out:
+            out[key] = p
+    return out
 
-    def __init__(self, T: int, S: int, n_want: int, widths: list[int], tiles: dict[int, int],
-                 units: dict[int, int] | None = None):
-        self.T, self.S, self.n_want, self.widths, self.tiles = T, S, n_want, widths, tiles
+
+def collect_metadata(providers: dict[Hashable, object], shape: StepShape) -> dict[Hashable, StepMetadata]:
+    """Ask every provider for its arrays and numbers for this step."""
+    out = {}
+    for key, part in providers.items():
+        md = part.step_metadata(shape)
+        if md is None:
+            md = StepMetadata()
+        for name, arr in md.arrays.items():
+            if not isinstance(arr, np.ndarray) or arr.dtype != np.int32:
+                raise TypeError(f"step metadata {key!r}/{name}: arrays are int32 numpy arrays, got "
+                                f"{getattr(arr, 'dtype', type(arr))}")
+        out[key] = md
+    return out
+
+
+class Layout:
+    """Offsets of every section inside the packed buffer, for given sizes. ``extra`` names the parts'
+    own sections: {(key, name): number of ints}."""
+
+    def __init__(self, T: int, S: int, n_want: int, widths: list[int],
+                 extra: dict[tuple[Hashable, str], int] | None = None):
+        self.T, self.S, self.n_want, self.widths = T, S, n_want, widths
         off = 0
 
         def take(n: int) -> slice:
@@ -50,112 +78,37 @@ class Layout:
         self.want_rows = take(n_want)
         self.slot_maps = [take(T) for _ in widths]
         self.block_tables = [take(S * w) for w in widths]
-        self.tile_seq = {g: take(n) for g, n in tiles.items()}
-        self.tile_row0 = {g: take(n) for g, n in tiles.items()}
-        # prompt-attention unit records per group size
-        self.prefill = {g: take(n_units * UNIT_FIELDS) for g, n_units in (units or {}).items()}
+        self.extra = {k: take(n) for k, n in (extra or {}).items()}
         self.total = off
 
 
-def tiles_for(q_lens: np.ndarray, group_size: int) -> tuple[np.ndarray, np.ndarray]:
-    per_seq = (q_lens * group_size + TILE_ROWS - 1) // TILE_ROWS
-    tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), per_seq)
-    first = np.cumsum(per_seq) - per_seq
-    tile_row0 = (np.arange(tile_seq.size, dtype=np.int32) - np.repeat(first, per_seq).astype(np.int32)) * TILE_ROWS
-    return tile_seq.astype(np.int32), tile_row0.astype(np.int32)
+def extra_sizes(metadata: dict[Hashable, StepMetadata]) -> dict[tuple[Hashable, str], int]:
+    return {(key, name): int(arr.size) for key, md in metadata.items() for name, arr in md.arrays.items()}
+
+
+def write_extra(buf: np.ndarray, lay: Layout, metadata: dict[Hashable, StepMetadata]) -> None:
+    for key, md in metadata.items():
+        for name, arr in md.arrays.items():
+            sl = lay.extra[(key, name)]
+            if sl.stop - sl.start != arr.size:
+                raise RuntimeError(f"step metadata {key!r}/{name} changed its size ({arr.size} ints, the buffer "
+                                   f"has room for {sl.stop - sl.start})")
+            buf[sl] = arr.reshape(-1)
+
+
+def device_meta(dev: torch.Tensor, lay: Layout, metadata: dict[Hashable, StepMetadata]) -> dict[Hashable, PartMeta]:
+    """The parts' sections as views of the device buffer, shaped as the parts shaped them."""
+    return {key: PartMeta({name: dev[lay.extra[(key, name)]].view(arr.shape) for name, arr in md.arrays.items()},
+                          dict(md.host))
+            for key, md in metadata.items()}
 
 
 last_h2d_bytes = 0    # bytes of the most recent step's host-to-device copy (read by the runner's statistics)
 
-PACKED_TILE = 64        # rows of the tensor-core prompt attention's row tile
-PREFILL_CHUNK = 512     # keys of one work unit of that kernel (a multiple of its 64-key blocks)
-
-UNIT_FIELDS = 8         # ints of one unit record
-
-
-def packed_units(q_lens: np.ndarray, starts: np.ndarray, group_size: int, tile: int = PACKED_TILE,
-                 chunk: int = PREFILL_CHUNK) -> tuple[np.ndarray, int, int]:
-    """Work units of the tensor-core prompt attention. A ROW TILE is ``tile`` consecutive (token,
-    head-in-group) rows of one request; it sees keys 0 .. the position of its last row. A causal prompt's
-    last tile has many times the keys of its first, so a tile's keys are cut at absolute multiples of
-    ``chunk`` and every (tile, chunk) is a UNIT of its own, handed out heaviest first. A tile with one chunk
-    writes its output itself (slot0 -1); the chunks of the others write partial results into slots
-    slot0 .. slot0 + nchunks - 1, which the last of them to finish merges.
-
-    Returns (records, n_tiles, n_slots); records is int32 [n_units, 8]: request, first row, chunk,
-    number of chunks of the tile, slot0, tile index, first flat row of the request, tokens of the request
-    in this step, tokens of it already in the cache. Everything the kernel needs to start a unit is in its
-    record: one load instead of a chain of lookups."""
-    per_seq = (q_lens * group_size + tile - 1) // tile
-    n_tiles = int(per_seq.sum())
-    tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int64), per_seq)
-    first = np.cumsum(per_seq) - per_seq
-    row0 = (np.arange(n_tiles, dtype=np.int64) - np.repeat(first, per_seq)) * tile
-    last_pos = starts[tile_seq] + np.minimum(row0 + tile - 1, q_lens[tile_seq] * group_size - 1) // group_size
-    n_chunks = last_pos // chunk + 1
-    multi = n_chunks > 1
-    counted = np.where(multi, n_chunks, 0)
-    slot0 = np.where(multi, np.cumsum(counted) - counted, -1)
-    unit_tile = np.repeat(np.arange(n_tiles, dtype=np.int64), n_chunks)
-    cfirst = np.cumsum(n_chunks) - n_chunks
-    unit_chunk = np.arange(unit_tile.size, dtype=np.int64) - np.repeat(cfirst, n_chunks)
-    work = np.minimum(chunk, last_pos[unit_tile] + 1 - unit_chunk * chunk)
-    order = np.argsort(-work, kind="stable")
-    t, c = unit_tile[order], unit_chunk[order]
-    cu_q = np.cumsum(q_lens) - q_lens
-    sq = tile_seq[t]
-    rec = np.stack([sq, row0[t], c, n_chunks[t], slot0[t], t, cu_q[sq], q_lens[sq], starts[sq]], axis=1)
-    assert rec.shape[1] == UNIT_FIELDS + 1
-    # chunk and number of chunks share one int (both far below 2^16: a chunk is hundreds of keys)
-    packed = np.concatenate([rec[:, :2], (rec[:, 2] | (rec[:, 3] << 16))[:, None], rec[:, 4:]], axis=1)
-    return np.ascontiguousarray(packed, dtype=np.int32), n_tiles, int(counted.sum())
-
-
-def choose_chunk(q_lens: np.ndarray, starts: np.ndarray, group_size: int, kv_heads: int, tile: int = 128,
-                 key_block: int = 128, n_sm: int = 148) -> int:
-    """Keys per work unit of the prompt attention kernels, chosen for the step at hand. For the tcgen05 kernel
-    (128-row tiles): Long units spare the
-    per-unit costs (ticket, queries, first tile, writing and merging partial results: about 4 us of an SM's time
-    against 1.4 us per block of 128 keys, two blocks of threads sharing the SM), short ones spread a few heavy
-    tiles over the chip; the estimate is the larger of the work divided over the SMs and the longest unit running
-    alone (1.8 us a block plus 8 us), over chunks of 512, 1024, 2048, ... keys. Measured at 14 query heads
-    over 2 kv heads of 64 against a fixed 512: 2,048-token prompt 3.92 vs 4.21 ms for 24 layers, 4,096 tokens
-    6.97 vs 8.38 ms, 8,192 tokens 15.7 vs 20.4 ms, 1,024 tokens behind 3,072 cached 3.70 vs 4.01 ms."""
-    per_seq = (q_lens * group_size + tile - 1) // tile
-    rows_end = np.minimum((np.concatenate([np.arange(n) for n in per_seq]) + 1) * tile,
-                          np.repeat(q_lens * group_size, per_seq)) if len(per_seq) else np.zeros(0, dtype=np.int64)
-    keys = np.repeat(starts, per_seq) + (rows_end - 1) // group_size + 1        # keys each row tile sees
-    if keys.size == 0:
-        return PREFILL_CHUNK
-    longest = int(keys.max())
-    if tile != 128:
-        # The mma.sync kernel (64-row tiles, three blocks of threads per SM): the longest chunk that still leaves
-        # three units per SM. Measured at 12 query heads over 2 kv heads of 128 against a fixed 512: 4,096-token
-        # prompt 6.37 vs 6.94 ms for 8 layers, 8,192 tokens 17.2 vs 19.6 ms, 1,024 and 2,048 tokens unchanged.
-        best, chunk = PREFILL_CHUNK, PREFILL_CHUNK
-        while chunk < longest and chunk < (1 << 15):
-            chunk *= 2
-            if float(np.sum((keys + chunk - 1) // chunk)) * kv_heads >= 3 * n_sm:
-                best = chunk
-        return best
-    blocks = float(np.sum((keys + key_block - 1) // key_block))
-    best, best_cost, chunk = PREFILL_CHUNK, None, PREFILL_CHUNK
-    while True:
-        units = float(np.sum((keys + chunk - 1) // chunk))
-        spread = (blocks * 1.37 + units * 4.0) * kv_heads / n_sm
-        alone = -(-min(chunk, longest) // key_block) * 1.8 + 8.0
-        cost = max(spread, alone)
-        if best_cost is None or cost <= best_cost:
-            best, best_cost = chunk, cost
-        if chunk >= longest or chunk >= (1 << 15):
-            return best
-        chunk *= 2
-
 
 def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: torch.device,
-                      group_sizes: list[int], *, scratch=None, split_keys: int = 0,
-                      min_table_width: int = 0, prefill_tile: int = PACKED_TILE,
-                      prefill_chunk: int = PREFILL_CHUNK, kv_heads_of: dict[int, int] | None = None) -> StepInputs:
+                      providers: dict[Hashable, object] | None = None, *, workspace=None,
+                      min_table_width: int = 0) -> StepInputs:
     S = len(entries)
     ps = cache.page_size
     q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
@@ -172,15 +125,8 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
     for i, e in enumerate(entries):
         if any(not (0 <= w < len(e.tokens)) for w in e.want):
             raise ValueError(f"entry {i}: a wanted place lies outside its {len(e.tokens)} tokens")
-    tile_arrays = {g: tiles_for(q_lens, g) for g in group_sizes}
-    # keys per work unit: the given number, or (0) chosen for this step's shape
-    # (A step in which every request brings so few rows that the decode kernel takes it needs no prompt units.)
-    unit_groups = [g for g in group_sizes if not (split_keys and int(q_lens.max()) * g <= 16)]
-    chunks = {g: prefill_chunk or choose_chunk(q_lens, starts, g, (kv_heads_of or {}).get(g, 1), tile=prefill_tile)
-              for g in unit_groups}
-    unit_arrays = {g: packed_units(q_lens, starts, g, tile=prefill_tile, chunk=chunks[g]) for g in unit_groups}
-    lay = Layout(T, S, len(want_rows), widths, {g: a[0].size for g, a in tile_arrays.items()},
-                 {g: u[0].shape[0] for g, u in unit_arrays.items()})
+    metadata = collect_metadata(providers or {}, StepShape(q_lens, starts, ps, max_kv))
+    lay = Layout(T, S, len(want_rows), widths, extra_sizes(metadata))
 
     host = torch.empty(lay.total, dtype=torch.int32, pin_memory=device.type == "cuda")
     buf = host.numpy()
@@ -219,26 +165,17 @@ def build_step_inputs(entries: list[StepEntry], cache: CacheManager, device: tor
             slots[cu_list[i]:cu_list[i + 1]] = pages * ps + p % ps
         buf[lay.block_tables[g]] = table.reshape(-1)
         buf[lay.slot_maps[g]] = slots
-    for g, (tile_seq, tile_row0) in tile_arrays.items():
-        buf[lay.tile_seq[g]] = tile_seq
-        buf[lay.tile_row0[g]] = tile_row0
-    for g, (records, _, _) in unit_arrays.items():
-        buf[lay.prefill[g]] = records.reshape(-1)
+    write_extra(buf, lay, metadata)
 
     dev = host.to(device, non_blocking=True)
     global last_h2d_bytes
     last_h2d_bytes = lay.total * 4
-    max_q = int(q_lens.max())
-    use_split = split_keys
     return StepInputs(
         n_tokens=T, n_seqs=S, token_ids=dev[lay.token_ids], positions=dev[lay.positions],
         seq_of_token=dev[lay.seq_of_token], cu_q=dev[lay.cu_q], kv_before=dev[lay.kv_before],
         state_slots=dev[lay.state_slots],
         block_tables=[dev[lay.block_tables[g]].view(S, widths[g]) for g in range(cache.num_groups)],
         slot_maps=[dev[lay.slot_maps[g]] for g in range(cache.num_groups)],
-        want_rows=dev[lay.want_rows], n_want=len(want_rows), max_q_len=max_q, max_kv_len=max_kv,
-        q_lens=q_lens.tolist(), kv_befores=starts.tolist(),
-        tiles={g: (dev[lay.tile_seq[g]], dev[lay.tile_row0[g]], a[0].size) for g, a in tile_arrays.items()},
-        prefill={g: PrefillUnits(dev[lay.prefill[g]], records.shape[0], n_tiles, n_slots, chunks[g], prefill_tile)
-                 for g, (records, n_tiles, n_slots) in unit_arrays.items()},
-        scratch=scratch, split_keys=use_split, max_splits=-(-max_kv // use_split) if use_split else 0)
+        want_rows=dev[lay.want_rows], n_want=len(want_rows), max_q_len=int(q_lens.max()), max_kv_len=max_kv,
+        q_lens=q_lens.tolist(), kv_befores=starts.tolist(), meta=device_meta(dev, lay, metadata),
+        workspace=workspace)

@@ -52,29 +52,25 @@ def _element_size(dtype: torch.dtype) -> int:
 
 def kv_budget_bytes(cfg: EngineConfig, model: DecoderModel) -> int:
     """Bytes for the cache pool: ``kv_cache_mb`` if given, else what is left of
-    ``gpu_memory_utilization`` x device memory after what is already allocated (the weights) and an
-    allowance for the largest step's activations (src/infer/engine/engine.py:44-61; the reference
-    measures the activation peak with a dummy forward, here it is computed from the layer sizes)."""
+    ``gpu_memory_utilization`` x device memory after what is already allocated (the weights), what the
+    runner will allocate for good (the whole-step kernel's packed copy of the layer matrices), and an
+    allowance for the largest step's activations and logits (src/infer/engine/engine.py:44-61; the reference
+    measures the activation peak with a dummy forward, here the parts are asked: ``activation_bytes``)."""
     if cfg.kv_cache_mb is not None:
         return int(cfg.kv_cache_mb * 2 ** 20)
+    from ..kernels import fused
+
     dev = model.device
     total = torch.cuda.get_device_properties(dev).total_memory
     used = torch.cuda.memory_allocated(dev)
-    s = model.spec
-    widest = 0
-    for b in model.blocks:
-        ffn, mixer = b.feed_forward, b.mixer
-        widest = max(widest, 3 * getattr(ffn, "intermediate_size", s.hidden_size),
-                     2 * (getattr(mixer, "q_size", s.hidden_size) + 2 * getattr(mixer, "kv_size", 0)))
-    act = cfg.max_num_batched_tokens * (8 * s.hidden_size + 4 * widest)
-    logits = 3 * min(cfg.max_num_seqs, cfg.max_num_batched_tokens) * s.vocab_size * 4
-    budget = int(total * cfg.gpu_memory_utilization) - used - act - logits - (512 << 20)
+    act = 2 * model.activation_bytes(cfg.max_num_batched_tokens)          # twice: temporaries of the library products
+    logits = 3 * min(cfg.max_num_seqs, cfg.max_num_batched_tokens) * model.spec.vocab_size * 4
+    runner = fused.persistent_bytes(model)
+    budget = int(total * cfg.gpu_memory_utilization) - used - runner - act - logits - (512 << 20)
     if budget <= 0:
         raise RuntimeError("no memory left for the cache; lower --max-batched-tokens or raise "
                            "--gpu-memory-utilization")
     return budget
-
-
 
 
 class _InFlight:
@@ -98,6 +94,9 @@ class LLMEngine:
                                max_positions=cfg.max_model_len)
         self.model = model
         self.device, self.dtype = model.device, model.dtype
+        if cfg.max_model_len > model.max_positions():
+            raise ValueError(f"max_model_len is {cfg.max_model_len}, but the model serves {model.max_positions()} "
+                             f"positions (max_position_embeddings): lower --max-model-len")
         self.eos_ids = set(model.spec.eos_token_ids)
         layout = model.cache_layout()
         per_token = layout.bytes_per_token(_element_size(self.dtype))

@@ -26,11 +26,12 @@ from ..cache.manager import CacheManager
 from ..cache.pool import CachePools
 from ..kernels import fused, lib, ops
 from ..kernels import program as program_mod
-from ..parts.attention import SPLIT_KEYS, AttentionScratch
-from ..parts.base import StepInputs
+from ..parts.base import StepInputs, StepShape
 from ..parts.model import DecoderModel
 from . import batch as batch_mod
-from .batch import Layout, StepEntry, build_step_inputs, tiles_for
+from .batch import (Layout, StepEntry, build_step_inputs, collect_metadata, device_meta, extra_sizes,
+                    metadata_providers, write_extra)
+from .workspace import Workspace
 
 GRAPH_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64, 128, 256]
 
@@ -42,20 +43,17 @@ class ModelRunner:
             raise RuntimeError(f"the engine runs on a CUDA device only, not on {model.device}")
         self.model, self.cache, self.pools = model, cache, pools
         self.device = model.device
+        limit = model.max_positions()
+        if max_model_len > limit:
+            raise ValueError(f"max_model_len is {max_model_len}, but the model serves {limit} positions (its position "
+                             f"tables end there): tokens beyond them would be encoded wrongly")
         self.max_model_len = max_model_len
         self.layout = model.cache_layout()
         self.layer_caches = pools.layer_caches(len(model.spec.run_order))
-        self.group_sizes = sorted({b.mixer.nh // b.mixer.nkv for b in model.blocks
-                                   if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")})
-        self.scratch = AttentionScratch(self.device)
-        # Rows of a prompt-attention work unit: 128 where the tcgen05 kernel takes every attention layer of the
-        # model (bfloat16, heads of 64 or 128), else the 64 of the mma.sync kernel.
-        heads = {b.mixer.D for b in model.blocks if hasattr(b.mixer, "D")}
-        self.prefill_tile = 128 if (ops.tc_attention_enabled() and model.dtype == torch.bfloat16 and heads
-                                    and heads <= {64, 128}) else 64
-        self.prefill_chunk = 0          # keys of a work unit: chosen per step (batch.choose_chunk)
-        self.kv_heads_of = {b.mixer.nh // b.mixer.nkv: b.mixer.nkv for b in model.blocks
-                            if hasattr(b.mixer, "nh") and hasattr(b.mixer, "nkv")}
+        # Parts that want arrays of their own in every step's input buffer (by their metadata key), and the
+        # scratch buffers parts ask for while they run.
+        self.providers = metadata_providers(model.parts())
+        self.workspace = Workspace(self.device)
         # Steps of more than 16 tokens run as a step program (one native call walks the launches) where every
         # part of the model can write its launches down; TOKENMILL_STEP_PROGRAM=0 keeps the per-launch path.
         self._program = None
@@ -84,9 +82,8 @@ class ModelRunner:
                 os.environ.get("TOKENMILL_LM_HEAD", "0") == "1":
             self._packed_output = fused.pack_rows(model.output_weight)
         if self.graph_max_batch:
-            if any(s < 0 for s in pools.sink):
-                raise RuntimeError("decode graphs need pools built with a sink page")
-            self._reserve_scratch(self.graph_max_batch)
+            if any(s < 0 for s in pools.sink) or (pools.state and pools.state_sink < 0):
+                raise RuntimeError("decode graphs need pools built with a sink page (and a sink state slot)")
 
     # --- the step -------------------------------------------------------------------------------
 
@@ -143,9 +140,7 @@ class ModelRunner:
 
     def _inputs(self, entries: list[StepEntry]) -> StepInputs:
         """The step's batch on the device (one packed buffer, one copy)."""
-        step = build_step_inputs(entries, self.cache, self.device, self.group_sizes, scratch=self.scratch,
-                                 split_keys=SPLIT_KEYS, prefill_tile=self.prefill_tile,
-                                 prefill_chunk=self.prefill_chunk, kv_heads_of=self.kv_heads_of)
+        step = build_step_inputs(entries, self.cache, self.device, self.providers, workspace=self.workspace)
         self.stats["h2d_bytes"] = batch_mod.last_h2d_bytes
         return step
 
@@ -232,18 +227,15 @@ class ModelRunner:
 
     # --- decode graphs --------------------------------------------------------------------------
 
-    def _reserve_scratch(self, batch: int) -> None:
-        max_splits = -(-self.max_model_len // SPLIT_KEYS)
-        for b in self.model.blocks:
-            m = b.mixer
-            if hasattr(m, "nh"):
-                self.scratch.reserve(batch * m.nh, max_splits, m.D)
-
     def _graph_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
                     token_rows: list[int] | None = None) -> torch.Tensor:
         n = len(entries)
         sizes = [b for b in GRAPH_BATCH_SIZES if b < self.graph_max_batch] + [self.graph_max_batch]
         bucket = sizes[bisect.bisect_left(sizes, n)]
+        if not self._graphs and bucket != sizes[-1]:
+            # The largest batch is captured first: its warm-up makes every scratch buffer as large as any
+            # graph will need, so the smaller graphs share those buffers instead of getting sets of their own.
+            self._graphs[sizes[-1]] = _DecodeGraph(self, sizes[-1])
         g = self._graphs.get(bucket)
         if g is None:
             g = _DecodeGraph(self, bucket)
@@ -265,15 +257,20 @@ class _DecodeGraph:
         ps = cache.page_size
         self.width = -(-runner.max_model_len // ps)
         B = bucket
-        q_lens = np.ones(B, dtype=np.int32)
-        self.tile_arrays = {g: tiles_for(q_lens, g) for g in runner.group_sizes}
-        self.lay = Layout(B, B, B, [self.width] * cache.num_groups, {g: a[0].size for g, a in self.tile_arrays.items()})
+        # The parts' own arrays, as they are for B single tokens at any context up to the limit. Those that
+        # depend on where the requests stand are written again at every replay (same sizes, or it is an error).
+        self.shape = StepShape(np.ones(B, dtype=np.int32), np.zeros(B, dtype=np.int32), ps, runner.max_model_len,
+                               for_graph=True)
+        metadata = collect_metadata(runner.providers, self.shape)
+        self.refill = {k: p for k, p in runner.providers.items() if not metadata[k].constant_in_graph}
+        self.host_meta = {k: dict(md.host) for k, md in metadata.items()}
+        self.lay = Layout(B, B, B, [self.width] * cache.num_groups, extra_sizes(metadata))
         self.dev = torch.zeros(self.lay.total, dtype=torch.int32, device=dev)
         self.host = torch.zeros(self.lay.total, dtype=torch.int32, pin_memory=True)
+        write_extra(self.host.numpy(), self.lay, metadata)
         self._fill([], first=True)
         self.dev.copy_(self.host)
         lay, d = self.lay, self.dev
-        max_splits = -(-runner.max_model_len // SPLIT_KEYS)
         self.inputs = StepInputs(
             n_tokens=B, n_seqs=B, token_ids=d[lay.token_ids], positions=d[lay.positions],
             seq_of_token=d[lay.seq_of_token], cu_q=d[lay.cu_q], kv_before=d[lay.kv_before],
@@ -281,9 +278,7 @@ class _DecodeGraph:
             block_tables=[d[lay.block_tables[g]].view(B, self.width) for g in range(cache.num_groups)],
             slot_maps=[d[lay.slot_maps[g]] for g in range(cache.num_groups)],
             want_rows=d[lay.want_rows], n_want=B, max_q_len=1, max_kv_len=runner.max_model_len,
-            tiles={g: (d[lay.tile_seq[g]], d[lay.tile_row0[g]], a[0].size) for g, a in self.tile_arrays.items()},
-            scratch=runner.scratch, split_keys=SPLIT_KEYS, max_splits=max_splits)
-        runner._reserve_scratch(B)
+            meta=device_meta(d, lay, metadata), workspace=runner.workspace)
         # Warm up outside capture (library handles and workspaces), then capture.
         torch.cuda.synchronize(dev)
         side = torch.cuda.Stream(device=dev)
@@ -310,7 +305,7 @@ class _DecodeGraph:
         runner.kernels_per_graph[bucket] = lib.launch_count - launched_before   # this library's kernels per replay
         if runner._graph_pool is None:
             runner._graph_pool = self.graph.pool()
-        runner.scratch.frozen = True
+        runner.workspace.freeze()
 
     def _fill(self, entries: list[StepEntry], first: bool = False) -> None:
         lay, buf, B = self.lay, self.host.numpy(), self.bucket
@@ -320,17 +315,17 @@ class _DecodeGraph:
             buf[lay.seq_of_token] = np.arange(B, dtype=np.int32)
             buf[lay.cu_q] = np.arange(B + 1, dtype=np.int32)
             buf[lay.want_rows] = np.arange(B, dtype=np.int32)
-            for g, (tile_seq, tile_row0) in self.tile_arrays.items():
-                buf[lay.tile_seq[g]] = tile_seq
-                buf[lay.tile_row0[g]] = tile_row0
         tok, pos, slot_state = buf[lay.token_ids], buf[lay.positions], buf[lay.state_slots]
         before = buf[lay.kv_before]
         tok[:] = 0
         pos[:] = 0
         before[:] = 0
-        slot_state[:] = 0
+        # Padded rows update the sink state slot, never a live request's.
+        slot_state[:] = max(self.r.pools.state_sink, 0)
         for i, e in enumerate(entries):
-            tok[i], pos[i], before[i], slot_state[i] = e.tokens[0], e.start, e.start, max(e.handle.state_slot, 0)
+            tok[i], pos[i], before[i] = e.tokens[0], e.start, e.start
+            if e.handle.state_slot >= 0:
+                slot_state[i] = e.handle.state_slot
         for g in range(cache.num_groups):
             sink = self.r.pools.sink[g]
             table = buf[lay.block_tables[g]].reshape(B, self.width)
@@ -345,6 +340,15 @@ class _DecodeGraph:
                 if page < 0:
                     raise RuntimeError("a decoded token would be written into a page already given back")
                 slots[i] = page * ps + e.start % ps
+        if self.refill and not first:
+            self.shape.starts[:] = 0
+            self.shape.starts[:n] = [e.start for e in entries]
+            metadata = collect_metadata(self.refill, self.shape)
+            for key, md in metadata.items():
+                if md.host != self.host_meta[key]:
+                    raise RuntimeError(f"step metadata {key!r}: the numbers a graph captured ({self.host_meta[key]}) "
+                                       f"differ at replay ({md.host})")
+            write_extra(buf, lay, metadata)
 
     def run(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
             token_rows: list[int] | None = None) -> torch.Tensor:

@@ -21,11 +21,12 @@ from pathlib import Path
 
 import torch
 
-PAGE_SIZE = 16
+PAGE_SIZE = 16           # tokens per cache page unless --page-size says otherwise
+LIVE_REQUESTS = 4        # requests that may be live at a time (state slots are kept for twice as many)
 
 
 def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=None, stdout=None,
-        device: str = "cuda:0", page_size: int = PAGE_SIZE) -> int:
+        device: str = "cuda:0", page_size: int = PAGE_SIZE, state_slots: int = 2 * LIVE_REQUESTS) -> int:
     from ..cache.manager import CacheManager
     from ..cache.pool import CachePools
     from ..kernels import ops
@@ -45,14 +46,16 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, stdin=No
     layout = model.cache_layout()
     # The pool holds exactly the pages max_tokens needs (live requests each rounded up to 64 tokens,
     # a multiple of the page size), so pages freed by one request are reused by the next.
+    if page_size < 1 or 64 % page_size:
+        raise ValueError(f"--page-size must divide 64 (requests are counted in units of 64 tokens), got {page_size}")
     num_pages = max(1, -(-max_tokens // page_size))
     n_groups = len(layout.groups)
-    n_state = 8 if layout.entry_state else 0
+    n_state = state_slots if layout.entry_state else 0
     cache = CacheManager([num_pages] * n_groups, page_size, layout.windows, watermark=0.0,
                          enable_prefix_caching=False, num_state_slots=n_state)
     pools = CachePools(layout, [num_pages] * n_groups, page_size, dtype, dev, num_state_slots=n_state,
                        run_order_cache_of=[e.cache_of for e in model.spec.run_order])
-    runner = ModelRunner(model, cache, pools, max_model_len=model.spec.max_positions)
+    runner = ModelRunner(model, cache, pools, max_model_len=model.max_positions())
     vocab = model.spec.vocab_size
 
     live: dict[str, tuple] = {}         # id -> (handle, tokens held)
@@ -102,8 +105,12 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page (a divisor of 64)")
+    ap.add_argument("--state-slots", type=int, default=2 * LIVE_REQUESTS,
+                    help="slots for fixed-size per-request state, for models whose mixers keep some")
     args = ap.parse_args(argv)
-    return run(args.model, args.dtype, args.out, args.max_tokens, device=args.device)
+    return run(args.model, args.dtype, args.out, args.max_tokens, device=args.device, page_size=args.page_size,
+               state_slots=args.state_slots)
 
 
 if __name__ == "__main__":

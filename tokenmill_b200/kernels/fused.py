@@ -77,7 +77,7 @@ def eligible(model) -> bool:
         if (m.nh, m.nkv, m.D, m.window, m.scale, m.hidden_size) != (first.nh, first.nkv, first.D, first.window,
                                                                    first.scale, first.hidden_size):
             return False
-        if m.position is None or m.cos.data_ptr() != first.cos.data_ptr():
+        if m.cos is None or first.cos is None or m.cos.data_ptr() != first.cos.data_ptr():
             return False
         if f.intermediate_size != model.blocks[model.spec.run_order[0].layer].feed_forward.intermediate_size:
             return False
@@ -89,6 +89,22 @@ def eligible(model) -> bool:
         return False
     return (type(model.final_norm) is RMSNorm and first.D in (64, 128) and H % 8 == 0 and I % 8 == 0
             and first.q_size % 8 == 0 and first.nh // first.nkv <= 16 and len(model.cache_layout().groups) == 1)
+
+
+def persistent_bytes(model) -> int:
+    """Device memory a FusedDecoder for this model keeps for good beyond the model's own weights: the packed
+    copy of every layer's four matrices (0 when the model gets no whole-step kernel)."""
+    if not eligible(model):
+        return 0
+    total, seen = 0, set()
+    for e in model.spec.run_order:
+        if e.layer in seen:
+            continue
+        seen.add(e.layer)
+        b = model.blocks[e.layer]
+        total += sum(w.numel() * w.element_size() for w in (b.mixer.w_qkv, b.mixer.w_o, b.feed_forward.w_gate_up,
+                                                            b.feed_forward.w_down))
+    return total + (64 << 20)
 
 
 def dev_index(device: torch.device) -> int:
@@ -302,5 +318,7 @@ class FusedDecoder:
             self.bar.zero_()
             self.attn_count.zero_()
             what = "the output matrix kernel gave up waiting for its weights" if code == 21 else \
-                f"the fused decode kernel gave up at grid barrier {code - 100}"
+                "a token's position lies outside the position tables" if code == 31 else \
+                f"the fused decode kernel gave up at a bounded wait (code {code}: 100 + n grid barrier n, 1000 / 2000 " \
+                f"weight ring, 3000 + n readiness counter n)"
             raise lib.KernelError(f"{what}; the step's results are incomplete")

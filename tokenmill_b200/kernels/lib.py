@@ -36,7 +36,8 @@ _P, _I, _F, _LL = c_void_p, c_int, c_float, c_longlong
 # name -> argument types (the trailing stream pointer included)
 _SIGNATURES: dict[str, list] = {
     "tm_add_rmsnorm": [_I, _P, _P, _P, _I, _LL, _P, _P, _P, _P, _F, _P, _I, _I, _P],
-    "tm_qkv_rope_write": [_I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tm_qkv_rope_write": [_I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "tm_kv_cache_write": [_I, _P, _P, _P, _P, _P, _I, _I, _P],
     "tm_paged_attention": [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
                            _I, _P],
     "tm_attention_combine": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -46,7 +47,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_prefill_attention_tc_bf16": [_P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "tm_swiglu": [_I, _P, _P, _I, _I, _P],
     "tm_skinny_linear": [_P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
-    "tm_skinny_qkv_rope_write": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "tm_skinny_qkv_rope_write": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "tm_skinny_gate_up_swiglu": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
     "tm_tc_linear": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "tm_tc_gate_up_swiglu": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],

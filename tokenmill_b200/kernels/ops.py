@@ -76,20 +76,39 @@ def add_rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torc
     return out
 
 
-def qkv_rope_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, cos: torch.Tensor,
-                   sin: torch.Tensor, slot_map: torch.Tensor | None, q_out: torch.Tensor,
+def qkv_rope_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, cos: torch.Tensor | None,
+                   sin: torch.Tensor | None, slot_map: torch.Tensor | None, q_out: torch.Tensor,
                    kcache: torch.Tensor | None, vcache: torch.Tensor | None, nh: int, nkv: int, D: int) -> None:
-    """qkv [T, (nh + 2 nkv) D]; cos/sin [P, D/2] float32; q_out [T, nh, D]; caches [pages, page, nkv, D]."""
+    """qkv [T, (nh + 2 nkv) D]; cos/sin [P, D/2] float32 (both None: no rotation); q_out [T, nh, D]; caches
+    [pages, page, nkv, D]. Without a slot map but with "caches" of T rows, token t's k and v go to row t. A
+    position outside the tables raises the device error word (``position_check``) instead of reading them."""
     T = qkv.shape[0]
-    if qkv.shape[1] != (nh + 2 * nkv) * D or cos.shape[1] * 2 != D or positions.numel() < T:
+    if qkv.shape[1] != (nh + 2 * nkv) * D or positions.numel() < T or (cos is None) != (sin is None) or \
+            (cos is not None and cos.shape[1] * 2 != D):
         raise lib.KernelError(f"qkv_rope_write: shapes do not fit (qkv {tuple(qkv.shape)}, nh {nh}, nkv {nkv}, D {D})")
     if slot_map is not None and (kcache is None or vcache is None):
         raise lib.KernelError("qkv_rope_write: a slot map needs both caches")
+    if slot_map is None and kcache is not None and (kcache.numel() < T * nkv * D or vcache is None
+                                                    or vcache.numel() < T * nkv * D):
+        raise lib.KernelError("qkv_rope_write: dense k / v outputs need a row per token")
     dt = q_out.dtype
     lib.call("tm_qkv_rope_write", _code(qkv.dtype), _code(dt), _req(qkv, "qkv"), _opt(bias, "bias", torch.float32),
-             _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32),
-             _req(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out"),
-             _opt(kcache, "kcache", dt), _opt(vcache, "vcache", dt), T, nh, nkv, D, cos.shape[0], _stream())
+             _req(positions, "positions", torch.int32), _opt(cos, "cos", torch.float32),
+             _opt(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out"),
+             _opt(kcache, "kcache", dt), _opt(vcache, "vcache", dt), T, nh, nkv, D, cos.shape[0] if cos is not None else 1,
+             _tc_flag(qkv.device).data_ptr(), _stream())
+
+
+def kv_cache_write(k: torch.Tensor, v: torch.Tensor, slot_map: torch.Tensor, kcache: torch.Tensor,
+                   vcache: torch.Tensor) -> None:
+    """k, v [T, nkv, D] -> rows slot_map[t] of the caches [pages, page, nkv, D] (negative slots are skipped)."""
+    T = k.shape[0]
+    width = k.numel() // max(T, 1)
+    if v.shape != k.shape or kcache.shape[2:] != k.shape[1:] or vcache.shape != kcache.shape or slot_map.numel() < T:
+        raise lib.KernelError("kv_cache_write: k / v / cache shapes disagree")
+    dt = kcache.dtype
+    lib.call("tm_kv_cache_write", _code(dt), _req(k, "k", dt), _req(v, "v", dt), _req(slot_map, "slot_map", torch.int32),
+             _req(kcache, "kcache"), _req(vcache, "vcache", dt), T, width, _stream())
 
 
 def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
@@ -419,7 +438,8 @@ def skinny_qkv_rope_write(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor |
     lib.call("tm_skinny_qkv_rope_write", x.data_ptr(), x.stride(0), _req(w, "w", bf), _opt(bias, "bias", torch.float32),
              _req(positions, "positions", torch.int32), _req(cos, "cos", torch.float32),
              _req(sin, "sin", torch.float32), _opt(slot_map, "slot_map", torch.int32), _req(q_out, "q_out", bf),
-             _opt(kcache, "kcache", bf), _opt(vcache, "vcache", bf), T, K, nh, nkv, D, cos.shape[0], _stream())
+             _opt(kcache, "kcache", bf), _opt(vcache, "vcache", bf), T, K, nh, nkv, D, cos.shape[0],
+             _tc_flag(x.device).data_ptr(), _stream())
 
 
 def skinny_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -477,13 +497,17 @@ def tc_poll(device: torch.device) -> None:
 
 
 def tc_check(device: torch.device) -> None:
-    """Raise if a tcgen05 kernel gave up on a bounded wait since the last check (reads one int back, which
-    waits for the device)."""
+    """Raise if a kernel reported through the device error word since the last check: a tcgen05 block that gave
+    up on a bounded wait, or a position outside the rotary tables (reads one int back, which waits for the
+    device)."""
     flag = _tc_error.get(device)
     if flag is not None:
         code = int(flag.item())
         if code:
             flag.zero_()
+            if code == 31:
+                raise lib.KernelError("a token's position lies outside the position tables (the rotation was not "
+                                      "applied as asked; the step's results are wrong)")
             raise lib.KernelError(f"a tcgen05 block gave up waiting (code {code}: matrix product 1 loader, 2/3 issuer, "
                                   f"4 epilogue; attention 11/13 second product, 12 scores, 14 merge; 21 output matrix stream); "
                                   f"its results are incomplete")

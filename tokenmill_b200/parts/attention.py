@@ -1,103 +1,37 @@
 """Grouped-query attention mixer over the paged cache.
 
 Order of operations (src/infer/model/layers.py:127-150, src/infer/kv/context.py:63-80): fused
-q/k/v projection with bias; rotate-half position encoding of q and k; the step's k and v are
-written to their cache slots BEFORE attention, so a prompt portion reads its own keys back from the
-cache; causal attention of every query over its own request's keys; output projection without bias.
-The projection weights are stored fused, rows [q; k; v], from the checkpoint's q_proj / k_proj /
-v_proj tensors (src/infer/model/loader.py:45,68-70,111-113).
+q/k/v projection with bias; position encoding of q and k; the step's k and v are written to their
+cache slots BEFORE attention, so a prompt portion reads its own keys back from the cache; causal
+attention of every query over its own request's keys; output projection without bias. The projection
+weights are stored fused, rows [q; k; v], from the checkpoint's q_proj / k_proj / v_proj tensors
+(src/infer/model/loader.py:45,68-70,111-113).
 
 Every size and constant is a constructor parameter: head counts, head size, whether q/k/v carry a
 bias, the softmax scale, an optional window, and the position encoding (itself a part, looked up by
-kind). A window of w keys means a query at position p reads keys p-w+1..p.
+kind). A window of w keys means a query at position p reads keys p-w+1..p. The position encoding may
+give rotate-half tables (applied inside the projection's epilogue), bring a kernel of its own
+(``apply(q, k, positions)``, run between the bias and the cache write), or be absent.
+
+What the attention kernels need per step beyond the engine's own arrays (row tiles, work units cut into
+key chunks, the key split of short-query steps) is planned in ``step_metadata`` (parts/attention_plan.py)
+and reaches the device in the step's one copy; scratch for partial results comes from the step's
+workspace.
 """
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..kernels import ops
 from ..registry import get_part, register_mixer
-from .base import LayerCache, StepInputs
+from .attention_plan import choose_chunk, packed_units, tiles_for
+from .base import (LayerCache, PartMeta, PrefillUnits, StepInputs, StepMetadata, StepShape, part_limit_positions,
+                   part_max_positions)
 from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
 
 SPLIT_KEYS = 128     # decode attention cuts each request's keys at absolute multiples of this (batch 64 at contexts near 600: 1.27 ms a step against 1.31 with 256 and 1.38 with 64)
-
-
-class AttentionScratch:
-    """Scratch for split-key attention partials, sized once for the largest decode step."""
-
-    def __init__(self, device: torch.device):
-        self.device = device
-        self.part_acc: torch.Tensor | None = None
-        self.part_ml: torch.Tensor | None = None
-        self.done: torch.Tensor | None = None     # zero between launches; the counters that go with the last get()
-        self._graph_done: torch.Tensor | None = None
-        self._x_acc: torch.Tensor | None = None   # a second set for steps that outgrow what graphs captured
-        self._x_ml: torch.Tensor | None = None
-        self._x_done: torch.Tensor | None = None
-        self.frozen = False      # set once a graph has captured the pointers
-        self._counters: torch.Tensor | None = None
-        self._pf_acc: torch.Tensor | None = None
-        self._pf_ml: torch.Tensor | None = None
-        self._pf_done: torch.Tensor | None = None
-
-    def counters(self) -> torch.Tensor:
-        """Two zeroed ints the prompt-attention kernel uses as work ticket and done-counter (it leaves
-        them zero again)."""
-        if self._counters is None:
-            self._counters = torch.zeros(2, dtype=torch.int32, device=self.device)
-        return self._counters
-
-    def reserve(self, rows: int, max_splits: int, head_dim: int) -> None:
-        """Make the buffers that captured graphs point at large enough (before the first capture)."""
-        need_acc, need_ml = rows * max_splits * head_dim, rows * max_splits * 2
-        if self.part_acc is None or self.part_acc.numel() < need_acc or self.part_ml.numel() < need_ml:
-            if self.frozen:
-                raise RuntimeError("attention scratch would have to grow after a graph captured it")
-            self.part_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
-            self.part_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
-        if self._graph_done is None or self._graph_done.numel() < rows:   # arrival counters, one per (request, kv head) at most
-            if self.frozen:
-                raise RuntimeError("attention scratch would have to grow after a graph captured it")
-            self._graph_done = torch.zeros(rows, dtype=torch.int32, device=self.device)
-        self.done = self._graph_done
-
-    def get(self, rows: int, max_splits: int, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """Buffers for ``rows`` rows of ``max_splits`` partial results; ``self.done`` then holds arrival
-        counters for as many rows. Once a graph has captured the first set, a step that needs more (a mixed
-        step of many tokens between graph replays) gets a second set of its own, which may grow: the graphs
-        keep pointing at the first."""
-        need_acc, need_ml = rows * max_splits * head_dim, rows * max_splits * 2
-        fits = (self.part_acc is not None and self.part_acc.numel() >= need_acc and self.part_ml.numel() >= need_ml
-                and self._graph_done is not None and self._graph_done.numel() >= rows)
-        if fits or not self.frozen:
-            self.reserve(rows, max_splits, head_dim)
-            return self.part_acc, self.part_ml
-        if torch.cuda.is_current_stream_capturing():     # a graph must never point at the set that may move
-            raise RuntimeError("attention scratch would have to grow after a graph captured it")
-        if self._x_acc is None or self._x_acc.numel() < need_acc or self._x_ml.numel() < need_ml:
-            self._x_acc = torch.empty(need_acc, dtype=torch.float32, device=self.device)
-            self._x_ml = torch.empty(need_ml, dtype=torch.float32, device=self.device)
-        if self._x_done is None or self._x_done.numel() < rows:
-            self._x_done = torch.zeros(rows, dtype=torch.int32, device=self.device)
-        self.done = self._x_done
-        return self._x_acc, self._x_ml
-
-    def get_prefill(self, slots: int, head_dim: int, tiles: int, tile_rows: int = 64):
-        """Scratch for the prompt kernel's per-(row tile, key chunk) partial results: ``slots`` slots of
-        ``tile_rows`` rows, and one arrival counter (zero between launches) for each of ``tiles`` (row tile, kv head)
-        pairs. Prompt steps are never captured in a graph, so these may grow at any time."""
-        if slots <= 0:
-            return None, None, None
-        need = slots * tile_rows
-        if self._pf_acc is None or self._pf_acc.numel() < need * head_dim:
-            self._pf_acc = torch.empty(need * head_dim, dtype=torch.float32, device=self.device)
-        if self._pf_ml is None or self._pf_ml.numel() < need * 2:
-            self._pf_ml = torch.empty(need * 2, dtype=torch.float32, device=self.device)
-        if self._pf_done is None or self._pf_done.numel() < tiles:
-            self._pf_done = torch.zeros(max(tiles, 1024), dtype=torch.int32, device=self.device)
-        return self._pf_acc, self._pf_ml, self._pf_done
 
 
 class GroupedQueryAttention:
@@ -120,6 +54,13 @@ class GroupedQueryAttention:
         self.w_qkv: torch.Tensor | None = None
         self.b_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
+        self.cos: torch.Tensor | None = None      # rotate-half tables, when the position encoding has them
+        self.sin: torch.Tensor | None = None
+        # The tensor-core kernels take bfloat16 heads of 64 or 128; everything else runs the shape-generic kernel.
+        self.fast = dtype == torch.bfloat16 and head_dim in (64, 128)
+        # Rows of a prompt-attention work unit: 128 for the tcgen05 kernel, 64 for the mma.sync kernel.
+        self.prefill_tile = 128 if (self.fast and ops.tc_attention_enabled()) else 64
+        self.prefill_chunk = 0          # keys of a work unit; 0: chosen per step (attention_plan.choose_chunk)
 
     # --- declarations ---------------------------------------------------------------------------
 
@@ -139,6 +80,20 @@ class GroupedQueryAttention:
     def state_need(self) -> StateNeed | None:
         return None
 
+    def max_positions(self) -> int | None:
+        """How far the position encoding reaches (None: it has no limit, or there is none)."""
+        return part_max_positions(self.position) if self.position is not None else None
+
+    def limit_positions(self, n: int) -> None:
+        """No position >= n will be asked for: the encoding may size its tables so (before ``bind``)."""
+        if self.position is not None:
+            part_limit_positions(self.position, n)
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        """q/k/v product, q, head outputs and the branch output of one step."""
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * (3 * self.q_size + 2 * self.kv_size + self.hidden_size) * elt
+
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
                                dim=0).contiguous()
@@ -146,8 +101,53 @@ class GroupedQueryAttention:
             self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]],
                                    dim=0).contiguous()
         self.w_o = tensors["o_proj.weight"]
-        if self.position is not None:
-            self.cos, self.sin = self.position.tables(self.device)
+        tables = self.position.tables(self.device) if callable(getattr(self.position, "tables", None)) else None
+        if tables is not None:
+            self.cos, self.sin = tables
+        elif self.position is not None and not callable(getattr(self.position, "apply", None)):
+            raise TypeError(f"position encoding {type(self.position).__name__} has neither tables nor apply()")
+
+    # --- what the kernels need per step ---------------------------------------------------------
+
+    def metadata_key(self):
+        """Mixers with the same head grouping and kernels share one plan per step."""
+        return ("gqa_attention", self.nh // self.nkv, self.nkv, self.prefill_tile, self.fast)
+
+    def step_metadata(self, shape: StepShape) -> StepMetadata:
+        """The step's attention work as integer arrays. ``path`` names the kernel the step's shape takes:
+        "decode" (tensor cores, every request brings at most 16 query rows per kv head: keys cut at absolute
+        multiples of ``split_keys`` across blocks), "prefill_tc" / "prefill" (tensor cores, tcgen05 or
+        mma.sync: ``units`` are row tiles cut into key chunks, heaviest first) or "generic" (any head size and
+        dtype: tiles of 32 rows, keys split when the queries are few)."""
+        G = self.nh // self.nkv
+        q_lens, starts = shape.q_lens, shape.starts
+        max_q = int(q_lens.max()) if q_lens.size else 0
+        host = {"split_keys": SPLIT_KEYS, "max_splits": max(1, -(-int(shape.max_kv_len) // SPLIT_KEYS))}
+        arrays: dict[str, np.ndarray] = {}
+        if self.fast and max_q * G <= 16:
+            host["path"] = "decode"
+        elif self.fast:
+            chunk = self.prefill_chunk or choose_chunk(q_lens, starts, G, self.nkv, tile=self.prefill_tile)
+            records, n_tiles, n_slots = packed_units(q_lens, starts, G, tile=self.prefill_tile, chunk=chunk)
+            arrays["units"] = records
+            host.update(path="prefill_tc" if self.prefill_tile == 128 else "prefill", n_units=records.shape[0],
+                        n_tiles=n_tiles, n_slots=n_slots, chunk_keys=chunk, tile_rows=self.prefill_tile)
+        else:
+            tile_seq, tile_row0 = tiles_for(q_lens, G)
+            arrays["tile_seq"], arrays["tile_row0"] = tile_seq, tile_row0
+            host.update(path="generic", n_tiles32=int(tile_seq.size))
+        return StepMetadata(arrays, host, constant_in_graph=True)      # (a graph replays q_lens of 1: nothing depends on starts)
+
+    def _meta(self, step: StepInputs) -> PartMeta:
+        return step.meta[self.metadata_key()]
+
+    def attention_path(self, step: StepInputs) -> str:
+        return self._meta(step).host["path"]
+
+    @staticmethod
+    def _units(meta: PartMeta) -> PrefillUnits:
+        h = meta.host
+        return PrefillUnits(meta.arrays["units"], h["n_units"], h["n_tiles"], h["n_slots"], h["chunk_keys"], h["tile_rows"])
 
     # --- run ------------------------------------------------------------------------------------
 
@@ -156,39 +156,35 @@ class GroupedQueryAttention:
         q = torch.empty((T, self.nh, self.D), dtype=self.dtype, device=x.device)
         slot_map = step.slot_maps[cache.group] if cache.writes else None
         kc, vc = (cache.k, cache.v) if cache.writes else (None, None)
-        if self.position is None:
-            raise NotImplementedError("an attention mixer without position encoding is not built")
-        if ops.skinny_ok(x, self.w_qkv):
+        rotary = self.cos is not None
+        if rotary and ops.skinny_ok(x, self.w_qkv):
             # decode step: one kernel streams the fused weight and finishes bias, rotation and cache write
             ops.skinny_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
                                       kc, vc, self.nh, self.nkv, self.D)
-        elif self.D in (64, 128, 256) and ops.tc_ok(x, self.w_qkv):
+        elif rotary and self.D in (64, 128, 256) and ops.tc_ok(x, self.w_qkv):
             # prompt step: the tcgen05 kernel keeps the product in tensor memory and finishes it the same way
             ops.tc_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
                                   kc, vc, self.nh, self.nkv, self.D)
-        else:
+        elif rotary or self.position is None:
+            # library (or 32-bit) product, then bias + rotation (none without an encoding) + cache write
             qkv = ops.linear(x, self.w_qkv)
             ops.qkv_rope_write(qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q, kc, vc,
                                self.nh, self.nkv, self.D)
+        else:
+            # an encoding with a kernel of its own: bias and split into dense q, k, v; the encoding; the cache write
+            qkv = ops.linear(x, self.w_qkv)
+            k = torch.empty((T, self.nkv, self.D), dtype=self.dtype, device=x.device)
+            v = torch.empty_like(k)
+            ops.qkv_rope_write(qkv, self.b_qkv, step.positions, None, None, None, q, k, v, self.nh, self.nkv, self.D)
+            self.position.apply(q, k, step.positions)
+            if cache.writes:
+                ops.kv_cache_write(k, v, slot_map, cache.k, cache.v)
         out = torch.empty_like(q)
         self.attend(q, step, cache, out)
         flat = out.view(T, self.q_size)
         if ops.skinny_ok(flat, self.w_o, allow_split=True):
             return ops.skinny_linear(flat, self.w_o, k_splits=ops.skinny_k_splits(T, self.q_size))
         return ops.linear(flat, self.w_o)
-
-    def attention_path(self, step: StepInputs) -> str:
-        """Which attention kernel this step's shape takes: "decode" (tensor cores, every request brings at most
-        16 query rows per kv head), "prefill_tc" / "prefill" (tensor cores, tcgen05 or mma.sync, row tiles cut
-        into key chunks) or "generic" (any head size and dtype)."""
-        G = self.nh // self.nkv
-        if self.dtype != torch.bfloat16 or self.D not in (64, 128):
-            return "generic"
-        if step.split_keys and step.max_q_len * G <= 16:
-            return "decode"
-        if G in step.prefill:
-            return "prefill_tc" if step.prefill[G].tile_rows == 128 else "prefill"
-        return "generic"
 
     def emit(self, b, x, cache: LayerCache):
         """The prompt-step launches (library product, bias + rotation + cache write, attention, library
@@ -197,8 +193,8 @@ class GroupedQueryAttention:
         program, each under a step parameter that says whether it runs."""
         from ..kernels.program import (OP_DECODE_ATTENTION, OP_GEMM_BF16, OP_PREFILL_ATTENTION, OP_PREFILL_ATTENTION_TC,
                                        OP_QKV_ROPE_WRITE, Float)
-        if self.dtype != torch.bfloat16 or self.D not in (64, 128) or self.position is None:
-            raise NotImplementedError("step programs are built for bfloat16 attention with heads of 64 or 128")
+        if not self.fast or self.cos is None:
+            raise NotImplementedError("step programs are built for bfloat16 rotary attention with heads of 64 or 128")
         T, g, G, nh, nkv, D = b.tokens(), cache.group, self.nh // self.nkv, self.nh, self.nkv, self.D
         code = ops.dtype_code(self.dtype)
         n_qkv = self.q_size + 2 * self.kv_size
@@ -211,45 +207,51 @@ class GroupedQueryAttention:
         kc, vc = (cache.k, cache.v) if cache.writes else (None, None)
         b.emit(OP_GEMM_BF16, [x, self.w_qkv, qkv, T, n_qkv, self.hidden_size, 0])
         b.emit(OP_QKV_ROPE_WRITE, [code, code, qkv, self.b_qkv, positions, self.cos, self.sin, slot_map, q, kc, vc, T,
-                                   nh, nkv, D, self.cos.shape[0]])
+                                   nh, nkv, D, self.cos.shape[0], ops.tc_error_word(self.device)])
 
-        path = self.attention_path
-        b.guard(lambda s: path(s) != "generic")
+        mkey = self.metadata_key()
+        meta = lambda s: s.meta[mkey]                                   # noqa: E731
+        path = lambda s: s.meta[mkey].host["path"]                      # noqa: E731
+        b.guard(lambda s: mkey in s.meta and path(s) != "generic")
         key = f"G{G}_D{D}_kv{nkv}"
         table = b.param(f"block_table{g}", lambda s: s.block_tables[g].data_ptr())
         bt_stride = b.param(f"block_table_stride{g}", lambda s: s.block_tables[g].stride(0))
         page, scale, window = cache.k.shape[1], Float(self.scale), self.window
+        i32 = torch.int32
 
         # decode kernel: scratch for T * nh rows of max_splits partial results, n_seqs * nkv arrival counters
+        # (buffers named for this head shape: a later launch record's buffer never moves an earlier one's)
         def dec(i):
-            return lambda s: s.scratch.get(s.n_tokens * nh, s.max_splits, D)[i].data_ptr() if path(s) == "decode" else 0
-        def dec_done(s):
-            if path(s) != "decode":
-                return 0
-            s.scratch.get(s.n_tokens * nh, s.max_splits, D)
-            return s.scratch.done.data_ptr()
+            def fn(s):
+                if path(s) != "decode":
+                    return 0
+                return self._decode_scratch(s.workspace, s.n_tokens, s.n_seqs, meta(s).host["max_splits"],
+                                            "_" + key)[i].data_ptr()
+            return fn
         b.emit(OP_DECODE_ATTENTION,
                [q, cache.k, cache.v, table, bt_stride, b.param("cu_q", lambda s: s.cu_q.data_ptr()),
                 b.param("kv_before", lambda s: s.kv_before.data_ptr()), b.param("n_seqs", lambda s: s.n_seqs),
-                b.param(f"decode_acc_{key}", dec(0)), b.param(f"decode_ml_{key}", dec(1)), out,
-                b.param(f"decode_done_{key}", dec_done), nh, nkv, D, page, scale, window,
-                b.param("split_keys", lambda s: s.split_keys), b.param("max_splits", lambda s: s.max_splits)],
+                b.param(f"decode_acc_{key}", dec(0)), b.param(f"decode_ml_{key}", dec(1)),
+                out, b.param(f"decode_done_{key}", dec(2)), nh, nkv, D, page, scale, window,
+                b.param(f"split_keys_{key}", lambda s: meta(s).host["split_keys"]),
+                b.param(f"max_splits_{key}", lambda s: meta(s).host["max_splits"])],
                cond=b.param(f"attention_decode_{key}", lambda s: int(path(s) == "decode")))
 
-        # prompt kernels: the step's work units for this group size, scratch for the tiles with several chunks
+        # prompt kernels: the step's work units for this head grouping, scratch for the tiles with several chunks
         def pf(i):
             def fn(s):
                 if not path(s).startswith("prefill"):
                     return 0
-                u = s.prefill[G]
-                t = s.scratch.get_prefill(u.n_slots * nkv, D, u.n_tiles * nkv, u.tile_rows)[i]
+                t = self._prefill_scratch(s.workspace, self._units(meta(s)), key)[i]
                 return t.data_ptr() if t is not None else 0
             return fn
-        units = [b.param(f"units_{G}", lambda s: s.prefill[G].records.data_ptr() if G in s.prefill else 0),
-                 b.param(f"n_units_{G}", lambda s: s.prefill[G].n_units if G in s.prefill else 0),
-                 b.param(f"chunk_keys_{G}", lambda s: s.prefill[G].chunk_keys if G in s.prefill else 0)]
+        prefill = lambda s: path(s).startswith("prefill")               # noqa: E731
+        units = [b.param(f"units_{key}", lambda s: meta(s).arrays["units"].data_ptr() if prefill(s) else 0),
+                 b.param(f"n_units_{key}", lambda s: meta(s).host["n_units"] if prefill(s) else 0),
+                 b.param(f"chunk_keys_{key}", lambda s: meta(s).host["chunk_keys"] if prefill(s) else 0)]
         scratch = [b.param(f"prefill_acc_{key}", pf(0)), b.param(f"prefill_ml_{key}", pf(1)),
-                   b.param(f"prefill_done_{key}", pf(2)), b.param("prefill_counters", lambda s: s.scratch.counters().data_ptr())]
+                   b.param(f"prefill_done_{key}", pf(2)),
+                   b.param("prefill_counters", lambda s: s.workspace.get("attn_pf_counters", 2, i32, zeroed=True).data_ptr())]
         common = [q, cache.k, cache.v, table, bt_stride, *units, *scratch, out, nh, nkv, D, page, scale, window]
         b.uses_tc_attention = True
         b.emit(OP_PREFILL_ATTENTION_TC, common + [ops.tc_error_word(self.device)],
@@ -259,32 +261,54 @@ class GroupedQueryAttention:
         b.emit(OP_GEMM_BF16, [out, self.w_o, branch, T, self.hidden_size, self.q_size, 0])
         return branch
 
+    def _decode_scratch(self, ws, n_tokens: int, n_seqs: int, max_splits: int, suffix: str = ""):
+        """(part_acc, part_ml, done) for split-key attention: n_tokens * heads rows of max_splits partial results,
+        and an arrival counter (zero between launches) per (request, kv head)."""
+        rows = n_tokens * self.nh * max_splits
+        return (ws.get("attn_part_acc" + suffix, rows * self.D, torch.float32),
+                ws.get("attn_part_ml" + suffix, rows * 2, torch.float32),
+                ws.get("attn_done" + suffix, n_seqs * self.nkv, torch.int32, zeroed=True))
+
+    def _prefill_scratch(self, ws, units: PrefillUnits, suffix: str = ""):
+        """(part_acc, part_ml, tile_done) for the prompt kernels' per-(row tile, key chunk) partial results:
+        n_slots * kv_heads slots of tile_rows rows, and one arrival counter (zero between launches) for each
+        (row tile, kv head) pair. Nothing when no tile of the step has more than one chunk."""
+        slots = units.n_slots * self.nkv
+        if slots <= 0:
+            return None, None, None
+        need = slots * units.tile_rows
+        sfx = f"_{suffix}" if suffix else ""
+        return (ws.get("attn_pf_acc" + sfx, need * self.D, torch.float32),
+                ws.get("attn_pf_ml" + sfx, need * 2, torch.float32),
+                ws.get("attn_pf_done" + sfx, max(units.n_tiles * self.nkv, 1024), torch.int32, zeroed=True))
+
     def attend(self, q: torch.Tensor, step: StepInputs, cache: LayerCache, out: torch.Tensor) -> None:
-        """Run the attention kernel that ``attention_path`` names; the shape-generic kernel has its keys split
+        """Run the attention kernel the step's plan names; the shape-generic kernel has its keys split
         when the queries are few and the contexts long."""
         G = self.nh // self.nkv
-        rows = step.max_q_len * G
-        path = self.attention_path(step)
+        meta = self._meta(step)
+        path, ws = meta.host["path"], step.workspace
+        split_keys, max_splits = meta.host["split_keys"], meta.host["max_splits"]
         if path == "decode":
-            part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, step.max_splits, self.D)
+            part_acc, part_ml, done = self._decode_scratch(ws, q.shape[0], step.n_seqs, max_splits)
             ops.decode_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
                                       step.kv_before, step.n_seqs, out, scale=self.scale, window=self.window,
-                                      split_keys=step.split_keys, max_splits=step.max_splits, part_acc=part_acc,
-                                      part_ml=part_ml, done=step.scratch.done)
+                                      split_keys=split_keys, max_splits=max_splits, part_acc=part_acc,
+                                      part_ml=part_ml, done=done)
             return
         if path in ("prefill_tc", "prefill"):
-            units = step.prefill[G]                # row tiles cut into key chunks, heaviest first
-            part_acc, part_ml, tile_done = step.scratch.get_prefill(units.n_slots * self.nkv, self.D,
-                                                                    units.n_tiles * self.nkv, units.tile_rows)
+            units = self._units(meta)              # row tiles cut into key chunks, heaviest first
+            part_acc, part_ml, tile_done = self._prefill_scratch(ws, units)
             kernel = ops.prefill_attention_tc_bf16 if path == "prefill_tc" else ops.prefill_attention_bf16
-            kernel(q, cache.k, cache.v, step.block_tables[cache.group], units, step.scratch.counters(), out,
+            kernel(q, cache.k, cache.v, step.block_tables[cache.group], units,
+                   ws.get("attn_pf_counters", 2, torch.int32, zeroed=True), out,
                    scale=self.scale, window=self.window, part_acc=part_acc, part_ml=part_ml, tile_done=tile_done)
             return
-        tile_seq, tile_row0, n_tiles = step.attention_tiles(G)
+        tile_seq, tile_row0, n_tiles = meta.arrays["tile_seq"], meta.arrays["tile_row0"], meta.host["n_tiles32"]
         kw = {}
-        if step.split_keys and rows <= 32 and step.max_splits > 1:
-            part_acc, part_ml = step.scratch.get(q.shape[0] * self.nh, step.max_splits, self.D)
-            kw = dict(split_keys=step.split_keys, max_splits=step.max_splits, part_acc=part_acc, part_ml=part_ml,
+        if step.max_q_len * G <= 32 and max_splits > 1:
+            part_acc, part_ml, _ = self._decode_scratch(ws, q.shape[0], step.n_seqs, max_splits)
+            kw = dict(split_keys=split_keys, max_splits=max_splits, part_acc=part_acc, part_ml=part_ml,
                       seq_of_token=step.seq_of_token)
         ops.paged_attention(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q, step.kv_before,
                             tile_seq, tile_row0, n_tiles, out, scale=self.scale, window=self.window, **kw)

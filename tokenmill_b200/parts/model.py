@@ -16,7 +16,7 @@ import torch
 
 from ..kernels import ops
 from ..registry import get_part
-from .base import LayerCache, StepInputs
+from .base import (LayerCache, StepInputs, part_activation_bytes, part_limit_positions, part_max_positions)
 from .block import Pending
 from .spec import LayerSpec, ModelSpec, PagedKVNeed, PartSpec, StateNeed, WeightSpec
 
@@ -87,6 +87,35 @@ class DecoderModel:
         self.output_weight = self.embedding if s.lm_head_name is None else tensors[s.lm_head_name]
         for prefix, part in self._named:
             part.bind({w.name: tensors[f"{prefix}.{w.name}"] for w in part.weight_specs()})
+
+    # --- what the engine asks the parts -----------------------------------------------------------
+
+    def parts(self) -> list:
+        """Every part of the model, layer by layer (mixer, feed-forward, the two norms), then the final norm."""
+        out = []
+        for blk in self.blocks:
+            out += [blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm]
+        return out + [self.final_norm]
+
+    def max_positions(self) -> int:
+        """The longest sequence the model can serve: the architecture's own limit, or less where a part's
+        position tables are shorter."""
+        limits = [self.spec.max_positions] + [n for n in (part_max_positions(p) for p in self.parts()) if n is not None]
+        return min(limits)
+
+    def limit_positions(self, n: int) -> None:
+        """Tell the parts, before the weights are bound, that no position >= n will be asked for, so that
+        position tables are sized for the engine's own limit (src/infer/model/qwen2.py:34)."""
+        for p in self.parts():
+            part_limit_positions(p, n)
+
+    def activation_bytes(self, n_tokens: int) -> int:
+        """Working memory of a step of n_tokens: the 32-bit residual stream, a normed copy, and the largest
+        layer's own need (layers run one after another and reuse the memory)."""
+        H = self.spec.hidden_size
+        per_layer = max((part_activation_bytes(b.mixer, n_tokens, H) + part_activation_bytes(b.feed_forward, n_tokens, H)
+                         for b in self.blocks), default=0)
+        return n_tokens * H * 8 + per_layer
 
     # --- cache needs ----------------------------------------------------------------------------
 

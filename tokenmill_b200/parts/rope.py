@@ -23,6 +23,11 @@ class RotaryEmbedding:
         self.theta = float(theta)
         self.max_positions = int(max_positions)
 
+    def limit_positions(self, n: int) -> None:
+        """No position >= n will be asked for: the tables are built that short
+        (src/infer/model/qwen2.py:34: min(max_positions, max_position_embeddings))."""
+        self.max_positions = max(1, min(self.max_positions, int(n)))
+
     def tables(self, device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
         """(cos, sin), each [max_positions, head_dim / 2] float32 on ``device``; shared between layers."""
         key = (self.head_dim, self.theta, self.max_positions, str(device))

@@ -26,6 +26,11 @@ class SwiGLUFeedForward:
         return [WeightSpec("gate_proj.weight", (I, H)), WeightSpec("up_proj.weight", (I, H)),
                 WeightSpec("down_proj.weight", (H, I))]
 
+    def activation_bytes(self, n_tokens: int) -> int:
+        """The [T, 2 I] product, the [T, I] activation and the branch output of one step."""
+        elt = 4 if self.dtype == torch.float32 else 2
+        return n_tokens * (3 * self.intermediate_size + self.hidden_size) * elt
+
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]

@@ -1,5 +1,5 @@
-from .loader import WeightError, limit_positions, load_model, load_tensors, read_spec, resolve_dtype
+from .loader import WeightError, load_model, load_tensors, read_spec, resolve_dtype
 from .random_init import named_config, qwen2_config, write_random_model
 
-__all__ = ["WeightError", "limit_positions", "load_model", "load_tensors", "read_spec", "resolve_dtype",
+__all__ = ["WeightError", "load_model", "load_tensors", "read_spec", "resolve_dtype",
            "named_config", "qwen2_config", "write_random_model"]

@@ -116,28 +116,8 @@ def load_model(folder: str | Path, dtype: torch.dtype | str = torch.bfloat16,
         dtype = resolve_dtype(dtype)
     device = torch.device(device)
     spec, _cfg = read_spec(folder)
-    if max_positions is not None:
-        spec = limit_positions(spec, max_positions)
     model = DecoderModel(spec, dtype, device)
+    if max_positions is not None:
+        model.limit_positions(max_positions)
     model.bind(load_tensors(folder, model.weight_specs(), dtype, device, spec.ignored_name_patterns))
     return model
-
-
-def limit_positions(spec: ModelSpec, max_positions: int) -> ModelSpec:
-    """Size position tables for the engine's max_model_len instead of the model's maximum
-    (src/infer/model/qwen2.py:34: min(max_positions, max_position_embeddings))."""
-    from dataclasses import replace
-
-    from ..parts.spec import PartSpec
-
-    n = min(int(max_positions), spec.max_positions)
-
-    def cut(part: PartSpec) -> PartSpec:
-        params = dict(part.params)
-        pos = params.get("position")
-        if isinstance(pos, PartSpec) and "max_positions" in pos.params:
-            params["position"] = PartSpec(pos.kind, {**pos.params, "max_positions": min(n, pos.params["max_positions"])})
-        return PartSpec(part.kind, params)
-
-    layers = [replace(layer, mixer=cut(layer.mixer)) for layer in spec.layers]
-    return replace(spec, layers=layers, max_positions=n)
