@@ -110,13 +110,15 @@ def mixed_steps(reqs: dict[str, list[int]], seed: int, max_live: int = 4, decode
     return steps, peak
 
 
-def run_trace(model_dir: Path, dtype: str, steps: list[dict], max_tokens: int, out_dir: Path) -> dict[int, np.ndarray]:
-    from tokenmill_b200.engine.trace import run
+def run_trace(model_dir: Path, dtype: str, steps: list[dict], max_tokens: int, out_dir: Path,
+              page_size: int | None = None) -> dict[int, np.ndarray]:
+    from tokenmill_b200.engine.trace import PAGE_SIZE, run
 
     out_dir.mkdir(parents=True, exist_ok=True)
     stdin = io.StringIO("".join(json.dumps(s) + "\n" for s in steps))
     stdout = io.StringIO()
-    assert run(str(model_dir), dtype, str(out_dir), max_tokens, stdin=stdin, stdout=stdout) == 0
+    assert run(str(model_dir), dtype, str(out_dir), max_tokens, stdin=stdin, stdout=stdout,
+               page_size=page_size or PAGE_SIZE) == 0
     done = [line for line in stdout.getvalue().splitlines() if line.startswith("done ")]
     assert [int(d.split()[1]) for d in done] == [s["step"] for s in steps]
     vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]

@@ -43,6 +43,58 @@ def test_replay_matches_plain(tiny_dir, dtype, mode, tmp_path, plain_cache):
     print(f"{Path(tiny_dir).name} {dtype} {mode}: worst |engine - plain| = {worst:.3e}")
 
 
+def _steps_for(mode, reqs):
+    if mode == "whole":
+        return whole_steps(reqs)
+    if mode == "tail":
+        return tail_decode_steps(reqs)
+    if mode == "portions":
+        return portion_steps(reqs, seed=5)
+    return mixed_steps(reqs, seed=7)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["tail", "mixed"])
+def test_replay_with_pages_of_8_tokens(tiny_b_dir, dtype, mode, tmp_path, plain_cache):
+    """The second tiny configuration with the page size its benchmark configuration names (8): twice as many
+    page edges, block tables twice as wide, the same logits."""
+    reqs = make_requests(_vocab(tiny_b_dir), LENGTHS, seed=13)
+    steps, max_tokens = _steps_for(mode, reqs)
+    outputs = run_trace(tiny_b_dir, dtype, steps, max_tokens, tmp_path / "out", page_size=8)
+    check_against_plain(steps, outputs, reqs, plain_for(tiny_b_dir, reqs, plain_cache), dtype)
+
+
+@pytest.mark.parametrize("page", [8, 32])
+@pytest.mark.parametrize("mode", ["tail", "mixed", "portions"])
+def test_heads_of_64_replay_at_other_page_sizes(d64_dir, page, mode, tmp_path, plain_cache):
+    """The kernels serving uses for heads of 64 (whole-step decode kernel, tensor-core decode and prompt
+    attention) over pages of 8 and of 32 tokens, against the plain implementation."""
+    from tokenmill_b200.kernels import lib
+    reqs = make_requests(_vocab(d64_dir), [70, 133, 45, 200, 96, 61], seed=17)
+    steps, max_tokens = _steps_for(mode, reqs)
+    before = lib.launch_count
+    outputs = run_trace(d64_dir, "bfloat16", steps, max_tokens, tmp_path / "out", page_size=page)
+    assert lib.launch_count > before
+    check_against_plain(steps, outputs, reqs, plain_for(d64_dir, reqs, plain_cache), "bfloat16")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("size", ["0.5b", "1.5b", "7b"])
+def test_replay_at_the_real_layer_sizes(real_size_dir, size, dtype, tmp_path, plain_cache):
+    """Two layers of the Qwen2.5-0.5B, 1.5B and 7B layer sizes (small vocabulary), each request whole, in
+    portions and mixed with others over a pool with no spare page, in float32 and in bfloat16, against the
+    plain implementation: the widths, head counts and groupings that serving meets, through the kernels that
+    serving picks for them."""
+    folder = real_size_dir(size)
+    reqs = make_requests(_vocab(folder), [70, 133, 45, 96], seed=19)
+    plain = plain_for(folder, reqs, plain_cache)
+    for mode in ("whole", "portions", "mixed"):
+        steps, max_tokens = _steps_for(mode, reqs)
+        outputs = run_trace(folder, dtype, steps, max_tokens, tmp_path / mode)
+        worst = check_against_plain(steps, outputs, reqs, plain, dtype)
+        print(f"{size} {dtype} {mode}: worst |engine - plain| = {worst:.3e}")
+
+
 def test_modes_agree_in_float32(tiny_b_dir, tmp_path):
     """The same position's logits under different cuts differ by rounding only."""
     reqs = make_requests(_vocab(tiny_b_dir), [150, 77], seed=3)

@@ -37,7 +37,7 @@ from ..weights.loader import load_model, resolve_dtype
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import Scheduler
-from .sequence import PLACEHOLDER, RequestOutput, Sequence, Status
+from .request import TOKEN_IN_FLIGHT, Phase, Request, RequestOutput
 
 log = logging.getLogger("tokenmill_b200.engine")
 
@@ -76,11 +76,11 @@ def kv_budget_bytes(cfg: EngineConfig, model: DecoderModel) -> int:
 class _InFlight:
     """A decode step that has been launched and whose tokens the host has not read."""
 
-    __slots__ = ("seqs", "index", "pending", "row_of", "void", "plan", "t0")
+    __slots__ = ("reqs", "index", "pending", "row_of", "void", "plan", "t0")
 
-    def __init__(self, seqs, index, pending, plan, t0):
-        self.seqs, self.index, self.pending, self.plan, self.t0 = seqs, index, pending, plan, t0
-        self.row_of = {id(s): i for i, s in enumerate(seqs)}
+    def __init__(self, reqs, index, pending, plan, t0):
+        self.reqs, self.index, self.pending, self.plan, self.t0 = reqs, index, pending, plan, t0
+        self.row_of = {id(r): i for i, r in enumerate(reqs)}
         self.void: set[int] = set()        # rows whose request ended with the step before: token thrown away
 
 
@@ -119,10 +119,14 @@ class LLMEngine:
                                   max_num_seqs=cfg.max_num_seqs)
         self.scheduler = Scheduler(cfg, self.cache)
         self.sampler = Sampler(self.device)
-        self.seqs: dict[str, Sequence] = {}
+        self.requests: dict[str, Request] = {}          # live requests by id
         self._inflight: _InFlight | None = None
         self._rng = random.Random(cfg.seed)
         self._offline_counter = 0
+        # A tap for whoever wants to see the numbers behind the tokens (tests, log-probability tooling):
+        # called after every step that samples with ([(request id, position of the row's token)], logits
+        # [n, vocab] float32 on the device); the logits are only valid during the call.
+        self.on_logits = None
         self.stats = {"steps": 0, "peak_running": 0, "prefill_steps": 0, "decode_steps": 0,
                       "generated_tokens": 0, "busy_time": 0.0}
         log.info("engine ready: %d pages of %d tokens in %d group(s) (%.0f MiB), dtype %s, device %s", num_pages,
@@ -131,44 +135,60 @@ class LLMEngine:
     # --- requests -------------------------------------------------------------------------------
 
     def add_request(self, request_id: str, prompt_ids: list[int], params: SamplingParams,
-                    arrival_time: float | None = None) -> Sequence:
-        if not prompt_ids:
-            raise RequestRejected("prompt is empty")
-        if len(prompt_ids) >= self.cfg.max_model_len:
-            raise RequestRejected(f"prompt has {len(prompt_ids)} tokens; max_model_len is {self.cfg.max_model_len}")
-        if request_id in self.seqs:
-            raise RequestRejected(f"duplicate request id {request_id}")
-        vocab = self.model.spec.vocab_size
-        if any(not (0 <= t < vocab) for t in prompt_ids):
-            raise RequestRejected(f"a prompt token id lies outside the vocabulary of {vocab}")
-        seq = Sequence(request_id, list(prompt_ids), params, self.cache.new_handle(),
-                       arrival_time=time.monotonic() if arrival_time is None else arrival_time)
+                    arrival_time: float | None = None) -> Request:
+        """Queue a request. Refused at once (``RequestRejected``) when it could never be served."""
+        n, limit, vocab = len(prompt_ids), self.cfg.max_model_len, self.model.spec.vocab_size
+        problem = None
+        if request_id in self.requests:
+            problem = f"request id {request_id!r} is already in use"
+        elif n == 0:
+            problem = "the prompt holds no tokens"
+        elif n >= limit:
+            problem = f"the prompt's {n} tokens leave no room to generate under max_model_len = {limit}"
+        elif min(prompt_ids) < 0 or max(prompt_ids) >= vocab:
+            problem = f"the prompt holds a token id outside the vocabulary of {vocab}"
+        if problem:
+            raise RequestRejected(problem)
+        req = Request(request_id, list(prompt_ids), params, self.cache.new_handle())
+        if arrival_time is not None:
+            req.times.arrival = arrival_time
         if not params.greedy:
-            seq.sample_seed = params.seed if params.seed is not None else self._rng.getrandbits(62)
-        self.seqs[request_id] = seq
-        self.scheduler.add(seq)
-        return seq
+            req.sample_seed = params.seed if params.seed is not None else self._rng.getrandbits(62)
+        self.requests[request_id] = req
+        self.scheduler.submit(req)
+        return req
 
     def abort_request(self, request_id: str, reason: str = "abort") -> RequestOutput | None:
-        seq = self.seqs.pop(request_id, None)
-        if seq is None:
+        """End a request wherever it stands; None if the id is not live."""
+        req = self.requests.get(request_id)
+        if req is None:
             return None
-        while seq.output_ids and seq.output_ids[-1] == PLACEHOLDER:      # tokens of steps still in flight
-            seq.output_ids.pop()
-        seq.finishing = False
-        self.scheduler.finish(seq, reason)
-        seq.finish_time = time.monotonic()
-        return self._output(seq, [])
+        req.output_ids = [t for t in req.output_ids if t != TOKEN_IN_FLIGHT]    # a step in flight: its token is dropped
+        return self._retire(req, reason, time.monotonic())
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.busy
+
+    def _retire(self, req: Request, reason: str, now: float, new_tokens=(), error: str | None = None) -> RequestOutput:
+        req.closing = False
+        self.scheduler.retire(req, reason)
+        req.times.finish = now
+        self.requests.pop(req.id, None)
+        return self._report(req, list(new_tokens), error=error)
+
+    def _end_reason(self, req: Request, token: int, n_output: int) -> str | None:
+        """Why the request ends with ``token`` as its ``n_output``-th output, if it does."""
+        if token in self.eos_ids and not req.params.ignore_eos:
+            return "stop"
+        full = req.n_prompt + n_output >= self.cfg.max_model_len
+        return "length" if full or n_output >= req.params.max_tokens else None
 
     def _pipelining(self) -> bool:
         """Decode steps may stay in flight: the runner can take token ids from the device (the whole-step
         kernel reads them, a captured graph has them gathered), and nothing in the configuration needs a
         step's token ids on the host at once. With chunked prompts a plan that holds a prompt portion is simply
         not launched ahead: it runs once the step in flight has been read. With prefix caching a page is
-        published when the step that filled it has been read (its ids are known then), and a preempted request
+        published when the step that filled it has been read (its ids are known then), and an evicted request
         whose last token is still on the device waits for it before it is admitted again."""
         return self.cfg.async_decode and self.runner.feeds_tokens_on_device
 
@@ -177,10 +197,9 @@ class LLMEngine:
     def step(self) -> list[RequestOutput]:
         if self._inflight is not None:
             return self._step_behind()
-        outputs: list[RequestOutput] = []
         t0 = time.perf_counter()
-        plan = self.scheduler.schedule()
-        outputs += self._drop_ignored(plan)
+        plan = self.scheduler.plan_step()
+        outputs = self._reject(plan)
         if plan.empty:
             return outputs
         if self._pipelining() and self._is_plain_decode(plan):
@@ -188,50 +207,53 @@ class LLMEngine:
             return outputs
         return outputs + self._run(plan, t0)
 
-    def _drop_ignored(self, plan) -> list[RequestOutput]:
-        outputs = []
-        for seq in plan.ignored:
-            self.seqs.pop(seq.id, None)
-            self.scheduler.finish(seq, "length")
-            seq.finish_time = time.monotonic()
-            outputs.append(self._output(seq, [], error=None if seq.output_ids else
-                                        "prompt does not fit in the KV cache"))
-        return outputs
+    def _reject(self, plan) -> list[RequestOutput]:
+        """Requests the plan found could never fit the pool end here, with an error unless they had already
+        produced something (an evicted request that outgrew the pool)."""
+        now = time.monotonic()
+        return [self._retire(req, "length", now,
+                             error=None if req.output_ids else "prompt does not fit in the KV cache")
+                for req in plan.rejected]
+
+    def _tap(self, rows: list[tuple[str, int]], logits: torch.Tensor) -> None:
+        if self.on_logits is not None and rows:
+            self.on_logits(rows, logits)
 
     # --- decode steps in flight -----------------------------------------------------------------
 
     def _is_plain_decode(self, plan) -> bool:
-        return (not plan.prefill_items and self.runner.can_feed_tokens_on_device(len(plan.items))
-                and all(it.samples and it.num_tokens == 1 for it in plan.items))
+        return (not plan.prompt_items and self.runner.can_feed_tokens_on_device(len(plan.items))
+                and all(it.samples and it.count == 1 for it in plan.items))
 
     def _launch(self, plan, prev: _InFlight | None, t0: float) -> _InFlight:
         """Launch the plan's decode step without waiting for anything. With ``prev`` (the step still in
         flight) a request's token is what that step's sampling left on the device."""
-        seqs = [it.seq for it in plan.items]
+        reqs = [it.req for it in plan.items]
         entries, rows = [], []
         for it in plan.items:
-            seq = it.seq
+            req = it.req
             if prev is None:
-                entries.append(StepEntry(seq.cache, [seq.all_token_ids[it.start]], it.start, [0]))
+                entries.append(StepEntry(req.cache, [req.tokens[it.start]], it.start, [0]))
             else:
-                entries.append(StepEntry(seq.cache, [0], it.start, [0]))
-                rows.append(prev.row_of[id(seq)])
+                entries.append(StepEntry(req.cache, [0], it.start, [0]))
+                rows.append(prev.row_of[id(req)])
         if prev is None:
             logits = self.runner.step(entries)
         else:
             logits = self.runner.step_fed(entries, prev.pending.dev, rows)
-        pending = self.sampler.launch(logits, [s.params for s in seqs], [s.sample_seed for s in seqs],
-                                      [s.num_draws for s in seqs])
+        self._tap([(it.req.id, it.start) for it in plan.items], logits)
+        pending = self.sampler.launch(logits, [r.params for r in reqs], [r.sample_seed for r in reqs],
+                                      [r.draws for r in reqs])
         index = []
         for it in plan.items:
-            seq = it.seq
-            seq.num_computed_tokens = it.start + 1
-            self.cache.release_behind_window(seq.cache, seq.num_computed_tokens)
-            if not seq.params.greedy:
-                seq.num_draws += 1
-            index.append(len(seq.output_ids))
-            seq.output_ids.append(PLACEHOLDER)
-        return _InFlight(seqs, index, pending, plan, t0)
+            req = it.req
+            req.cached_tokens = it.start + 1
+            self.cache.release_behind_window(req.cache, req.cached_tokens)
+            if not req.params.greedy:
+                req.draws += 1
+            index.append(len(req.output_ids))
+            req.output_ids.append(TOKEN_IN_FLIGHT)
+        return _InFlight(reqs, index, pending, plan, t0)
 
     def _step_behind(self) -> list[RequestOutput]:
         """One call while a decode step is in flight: plan and launch the step after it if nothing stands
@@ -241,15 +263,15 @@ class LLMEngine:
         nxt, leftover = None, None
         t0 = time.perf_counter()
         if self._pipelining():
-            for seq, at in zip(cur.seqs, cur.index):
+            for req, at in zip(cur.reqs, cur.index):
                 # Ends the host can foresee: the step in flight brings the request's last token.
-                if not seq.is_finished and (at + 1 >= seq.params.max_tokens or
-                                            seq.num_prompt_tokens + at + 1 >= self.cfg.max_model_len):
-                    seq.finishing = True
-            plan = self.scheduler.schedule()
-            outputs += self._drop_ignored(plan)
+                if not req.done and (at + 1 >= req.params.max_tokens or
+                                     req.n_prompt + at + 1 >= self.cfg.max_model_len):
+                    req.closing = True
+            plan = self.scheduler.plan_step()
+            outputs += self._reject(plan)
             if not plan.empty:
-                if self._is_plain_decode(plan) and all(id(it.seq) in cur.row_of for it in plan.items):
+                if self._is_plain_decode(plan) and all(id(it.req) in cur.row_of for it in plan.items):
                     nxt = self._launch(plan, cur, t0)
                 else:
                     leftover = plan                # planned (pages grown) but not launched: run it below
@@ -264,32 +286,25 @@ class LLMEngine:
         now = time.monotonic()
         outputs = []
         n_new = 0
-        for row, (seq, at) in enumerate(zip(cur.seqs, cur.index)):
-            if row in cur.void or seq.is_finished:        # ended a step earlier, or aborted meanwhile
+        for row, (req, at) in enumerate(zip(cur.reqs, cur.index)):
+            if row in cur.void or req.done:               # ended a step earlier, or aborted meanwhile
                 continue
             tok = tokens[row]
-            seq.output_ids[at] = tok
+            req.output_ids[at] = tok
             n_new += 1
-            if seq.status == Status.RUNNING:              # (a preempted request holds no pages to publish)
-                self.cache.register_computed(seq.cache, seq.prompt_ids + seq.output_ids[:at + 1],
-                                             seq.num_prompt_tokens + at)
-            if seq.first_token_time is None:
-                seq.first_token_time = now
+            if req.phase is Phase.RUNNING:                # (an evicted request holds no pages to publish)
+                self.cache.register_computed(req.cache, req.prompt_ids + req.output_ids[:at + 1], req.n_prompt + at)
+            if req.times.first_token is None:
+                req.times.first_token = now
             n_out = at + 1
-            reason = None
-            if tok in self.eos_ids and not seq.params.ignore_eos:
-                reason = "stop"
-            elif n_out >= seq.params.max_tokens or seq.num_prompt_tokens + n_out >= self.cfg.max_model_len:
-                reason = "length"
+            reason = self._end_reason(req, tok, n_out)
             if reason:
-                del seq.output_ids[n_out:]                # the place kept for the step after this one
-                if nxt is not None and id(seq) in nxt.row_of:
-                    nxt.void.add(nxt.row_of[id(seq)])
-                seq.finishing = False
-                self.scheduler.finish(seq, reason)
-                seq.finish_time = now
-                self.seqs.pop(seq.id, None)
-            outputs.append(self._output(seq, [tok], num_output_tokens=n_out))
+                del req.output_ids[n_out:]                # the place kept for the step after this one
+                if nxt is not None and id(req) in nxt.row_of:
+                    nxt.void.add(nxt.row_of[id(req)])
+                outputs.append(self._retire(req, reason, now, [tok]))
+            else:
+                outputs.append(self._report(req, [tok], n_output=n_out))
         self._record_step(cur.plan, time.perf_counter() - cur.t0, n_new)
         return outputs
 
@@ -306,79 +321,61 @@ class LLMEngine:
     # --- one step, start to end -----------------------------------------------------------------
 
     def _run(self, plan, t0: float) -> list[RequestOutput]:
-        outputs: list[RequestOutput] = []
-        entries, sampled = [], []
-        items = [it for it in plan.items if not it.seq.is_finished]    # (ended since the plan was made)
+        items = [it for it in plan.items if not it.req.done]    # (ended since the plan was made)
         if not items:
-            return outputs
-        for item in items:
-            seq = item.seq
-            tokens = seq.all_token_ids[item.start:item.start + item.num_tokens]
-            want = [item.num_tokens - 1] if item.samples else []
-            entries.append(StepEntry(seq.cache, tokens, item.start, want))
-            if item.samples:
-                sampled.append(seq)
+            return []
+        entries = [StepEntry(it.req.cache, it.req.tokens[it.start:it.start + it.count], it.start,
+                             [it.count - 1] if it.samples else []) for it in items]
+        sampling = [it.req for it in items if it.samples]
         logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, [s.params for s in sampled], [s.sample_seed for s in sampled],
-                                     [s.num_draws for s in sampled]) if sampled else []
+        self._tap([(it.req.id, it.start + it.count - 1) for it in items if it.samples], logits)
+        tokens = self.sampler.sample(logits, [r.params for r in sampling], [r.sample_seed for r in sampling],
+                                     [r.draws for r in sampling]) if sampling else []
         now = time.monotonic()
-        for item in items:
-            seq = item.seq
-            seq.num_computed_tokens = item.start + item.num_tokens
-            self.cache.register_computed(seq.cache, seq.all_token_ids, seq.num_computed_tokens)
-            self.cache.release_behind_window(seq.cache, seq.num_computed_tokens)
-        for seq, tok in zip(sampled, tokens):
-            seq.output_ids.append(tok)
-            if not seq.params.greedy:
-                seq.num_draws += 1
-            if seq.first_token_time is None:
-                seq.first_token_time = now
-            reason = self._stop_reason(seq, tok)
-            if reason:
-                self.scheduler.finish(seq, reason)
-                seq.finish_time = now
-                self.seqs.pop(seq.id, None)
-            outputs.append(self._output(seq, [tok]))
-        self._record_step(plan, time.perf_counter() - t0, len(sampled))
+        for it in items:
+            req = it.req
+            req.cached_tokens = it.start + it.count
+            self.cache.register_computed(req.cache, req.tokens, req.cached_tokens)
+            self.cache.release_behind_window(req.cache, req.cached_tokens)
+        outputs = []
+        for req, tok in zip(sampling, tokens):
+            req.output_ids.append(tok)
+            req.draws += 0 if req.params.greedy else 1
+            if req.times.first_token is None:
+                req.times.first_token = now
+            reason = self._end_reason(req, tok, req.n_output)
+            outputs.append(self._retire(req, reason, now, [tok]) if reason else self._report(req, [tok]))
+        self._record_step(plan, time.perf_counter() - t0, len(sampling))
         return outputs
 
-    def _stop_reason(self, seq: Sequence, tok: int) -> str | None:
-        if tok in self.eos_ids and not seq.params.ignore_eos:
-            return "stop"
-        if seq.num_output_tokens >= seq.params.max_tokens or seq.length >= self.cfg.max_model_len:
-            return "length"
-        return None
-
-    def _output(self, seq: Sequence, new_tokens: list[int], error: str | None = None,
-                num_output_tokens: int | None = None) -> RequestOutput:
-        n_out = seq.num_output_tokens if num_output_tokens is None else num_output_tokens
-        return RequestOutput(seq.id, new_tokens, seq.is_finished, seq.finish_reason, seq.num_prompt_tokens,
-                             n_out, seq.arrival_time, seq.first_token_time, seq.finish_time,
-                             seq.num_preemptions, error)
+    def _report(self, req: Request, new_tokens: list[int], error: str | None = None,
+                n_output: int | None = None) -> RequestOutput:
+        return RequestOutput(req.id, new_tokens, req.done, req.finish_reason, error, req.n_prompt,
+                             req.n_output if n_output is None else n_output, req.evictions, req.times)
 
     def _record_step(self, plan, step_time: float, n_generated: int) -> None:
         s = self.stats
         s["steps"] += 1
         s["busy_time"] += step_time
-        s["prefill_steps" if plan.prefill_items else "decode_steps"] += 1
+        s["prefill_steps" if plan.prompt_items else "decode_steps"] += 1
         s["generated_tokens"] += n_generated
         s["peak_running"] = max(s["peak_running"], len(self.scheduler.running))
         if self.cfg.debug_steps:
             log.info("step=%d batch=%d prefill_tokens=%d decode_tokens=%d step_ms=%.2f kv_usage=%.3f waiting=%d "
-                     "running=%d preempted=%d", s["steps"], len(plan.items), plan.num_prefill_tokens,
-                     len(plan.decode_items), step_time * 1e3, self.cache.usage(), len(self.scheduler.waiting),
-                     len(self.scheduler.running), len(plan.preempted))
+                     "running=%d preempted=%d", s["steps"], len(plan.items), plan.n_prompt_tokens,
+                     len(plan.decode_items), step_time * 1e3, self.cache.usage(), len(self.scheduler.queue),
+                     len(self.scheduler.running), len(plan.evicted))
 
     # --- offline helper -------------------------------------------------------------------------
 
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[list[int]]:
         """Run every prompt to completion through the step loop; output token ids in prompt order."""
         plist = params if isinstance(params, list) else [params] * len(prompts)
-        seqs = []
+        reqs = []
         for p, sp in zip(prompts, plist):
             self._offline_counter += 1
-            seqs.append(self.add_request(f"offline-{self._offline_counter}", p, sp))
+            reqs.append(self.add_request(f"offline-{self._offline_counter}", p, sp))
         while self.has_unfinished():
             self.step()
         ops.tc_check(self.runner.device)         # a prompt step's kernel that gave up must not pass silently
-        return [s.output_ids for s in seqs]
+        return [r.output_ids for r in reqs]

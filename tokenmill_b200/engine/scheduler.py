@@ -1,24 +1,26 @@
-"""Decides, every step, which requests run how many tokens, and who is preempted. Host only.
+"""Plans every step: which requests run how many tokens, who is admitted, who gives pages back. Host only.
 
-The decisions are the reference scheduler's (src/infer/engine/scheduler.py:56-242):
+The policy is the reference scheduler's (src/infer/engine/scheduler.py:56-242), restated:
 
-* first come, first served, no skipping: only the head of the waiting queue is considered;
+* first come, first served, no skipping: only the head of the queue is ever considered for admission;
 * a step's tokens stay under ``max_num_batched_tokens`` (a prompt longer than the whole budget runs
-  alone) and its requests under ``max_num_seqs``;
-* admission asks the cache manager OK / LATER / NEVER: LATER stops admission for this step, NEVER
-  takes the request out with an error ("ignored");
-* without chunked prefill a step is either a prefill step or a decode step (``prefill_first``:
-  prefill whenever something can be admitted; ``decode_first``: decode while anything runs, prefill
-  after ``max_waiting_steps`` decode steps);
-* with chunked prefill a step is mixed: every running request decodes, then prompts already in
-  progress and then new prompts get portions from what is left of the budget;
-* when a decoding request needs a page and none is free, the request admitted LAST is preempted
-  (its pages are released, its computed count reset, and it goes to the FRONT of the waiting queue to
-  be recomputed: prompt and generated tokens), repeated until the page is there; the request asking
-  is the last to go.
+  alone) and the running requests under ``max_num_seqs``;
+* admission asks the cache manager OK / LATER / NEVER: LATER ends admission for this step, NEVER takes
+  the request out with an error (``StepPlan.rejected``);
+* without chunked prefill a step either admits whole prompts or decodes (``prefill_first``: admit
+  whenever the head fits; ``decode_first``: decode while anything runs, admit after
+  ``max_waiting_steps`` decode steps);
+* with chunked prefill a step is mixed: every running request that is through its prompt decodes, then
+  prompts in progress and after them new prompts get portions of what is left of the budget;
+* when a decoding request needs a page and none is free, the request admitted LAST gives way (pages
+  released, nothing cached any more, FRONT of the queue, recomputed from prompt and outputs when it is
+  admitted again), repeated until the page is there; the request that asks is the last to go.
 
-The plan is a flat list of (request, first token, number of tokens) items, prompt portions first and
-single decoded tokens after them, which is the layout of the step's batch.
+Here the plan is one flat list of (request, first token, count) items, prompt portions before single
+decoded tokens, which is the layout of the step's batch; both modes are built from the same three
+passes (decode, continue, admit). A request whose newest token is still on the device (a decode step in
+flight) is not admitted until the host knows it, and one the engine already knows to end with the step in
+flight is planned no further.
 """
 
 from __future__ import annotations
@@ -28,223 +30,195 @@ from dataclasses import dataclass, field
 
 from ..cache.manager import AllocStatus, CacheManager
 from ..config.engine_config import EngineConfig
-from .sequence import Sequence, Status
+from .request import Phase, Request
 
 
 @dataclass
 class PlanItem:
-    seq: Sequence
-    start: int            # first position this step computes (= tokens already in the cache)
-    num_tokens: int
-    is_decode: bool
+    req: Request
+    start: int            # first position this step computes (= tokens the cache already holds)
+    count: int
+    decode: bool
 
     @property
     def samples(self) -> bool:
-        """True when the item reaches the request's last known token, so a token is sampled."""
-        return self.start + self.num_tokens == self.seq.length
+        """The item reaches the request's last known token: the step samples the next one."""
+        return self.start + self.count == self.req.n_tokens
 
 
 @dataclass
 class StepPlan:
     items: list[PlanItem] = field(default_factory=list)
-    preempted: list[Sequence] = field(default_factory=list)
-    ignored: list[Sequence] = field(default_factory=list)       # can never fit in the pool
+    evicted: list[Request] = field(default_factory=list)
+    rejected: list[Request] = field(default_factory=list)        # would not fit an empty pool
 
     @property
     def empty(self) -> bool:
         return not self.items
 
     @property
-    def prefill_items(self) -> list[PlanItem]:
-        return [i for i in self.items if not i.is_decode]
+    def prompt_items(self) -> list[PlanItem]:
+        return [i for i in self.items if not i.decode]
 
     @property
     def decode_items(self) -> list[PlanItem]:
-        return [i for i in self.items if i.is_decode]
+        return [i for i in self.items if i.decode]
 
     @property
-    def num_batched_tokens(self) -> int:
-        return sum(i.num_tokens for i in self.items)
+    def n_tokens(self) -> int:
+        return sum(i.count for i in self.items)
 
     @property
-    def num_prefill_tokens(self) -> int:
-        return sum(i.num_tokens for i in self.items if not i.is_decode)
+    def n_prompt_tokens(self) -> int:
+        return sum(i.count for i in self.items if not i.decode)
 
 
 class Scheduler:
     def __init__(self, cfg: EngineConfig, cache: CacheManager):
-        self.cfg = cfg
-        self.cache = cache
-        self.waiting: deque[Sequence] = deque()      # FCFS; preempted requests return to the front
-        self.running: list[Sequence] = []            # admission order, oldest first
-        self.num_preemptions = 0
-        self._admit_counter = 0
-        self._decode_steps_since_prefill = 0
+        self.cfg, self.cache = cfg, cache
+        self.queue: deque[Request] = deque()      # arrival order; evicted requests re-enter at the front
+        self.running: list[Request] = []
+        self.evictions = 0
+        self._next_seat = 0
+        self._decodes_since_admission = 0         # decode_first: decode steps taken while the queue waited
 
-    # --- queues ---------------------------------------------------------------------------------
+    # --- requests come and go -------------------------------------------------------------------
 
-    def add(self, seq: Sequence) -> None:
-        seq.status = Status.WAITING
-        self.waiting.append(seq)
+    def submit(self, req: Request) -> None:
+        req.phase = Phase.QUEUED
+        self.queue.append(req)
 
-    def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+    @property
+    def busy(self) -> bool:
+        return bool(self.queue) or bool(self.running)
 
-    def finish(self, seq: Sequence, reason: str) -> None:
-        """Release everything the request holds. Safe for a request in any queue."""
-        if seq.status == Status.FINISHED:
+    def retire(self, req: Request, reason: str) -> None:
+        """The request is over (wherever it stands): what it holds goes back to the cache manager."""
+        if req.done:
             return
-        if seq in self.running:
-            self.running.remove(seq)
-            self.cache.free(seq.cache)
-        else:
-            try:
-                self.waiting.remove(seq)
-            except ValueError:
-                pass
-        seq.status = Status.FINISHED
-        seq.finish_reason = reason
+        if req.phase is Phase.RUNNING:
+            self.running.remove(req)
+            self.cache.free(req.cache)
+        elif req in self.queue:
+            self.queue.remove(req)
+        req.phase, req.finish_reason = Phase.DONE, reason
 
-    # --- one step's plan ------------------------------------------------------------------------
+    # --- the plan -------------------------------------------------------------------------------
 
-    def schedule(self) -> StepPlan:
+    def plan_step(self) -> StepPlan:
         plan = StepPlan()
+        budget = self.cfg.max_num_batched_tokens
         if self.cfg.enable_chunked_prefill:
-            self._schedule_mixed(plan)
+            decodes, midway = self._decode_pass(plan)
+            budget -= len(decodes)
+            portions = self._continue_pass(midway, budget)
+            budget -= sum(p.count for p in portions)
+            portions += self._admit_pass(plan, budget, whole_prompts=False)
+            plan.items = portions + decodes
             return plan
-        if self._should_prefill():
-            self._schedule_prefills(plan)
+        if self._admission_turn():
+            plan.items = self._admit_pass(plan, budget, whole_prompts=True)
             if plan.items:
-                self._decode_steps_since_prefill = 0
+                self._decodes_since_admission = 0
                 return plan
-        self._schedule_decodes(plan, self._oldest_first())
-        if self.waiting:
-            self._decode_steps_since_prefill += 1
+        plan.items, _ = self._decode_pass(plan)
+        if self.queue:
+            self._decodes_since_admission += 1
         return plan
 
-    def _should_prefill(self) -> bool:
-        if not self.waiting:
+    def _admission_turn(self) -> bool:
+        """Whole-prompt mode: is this step one that admits?"""
+        if not self.queue:
             return False
         if self.cfg.policy == "prefill_first" or not self.running:
             return True
-        return self._decode_steps_since_prefill >= self.cfg.max_waiting_steps
+        return self._decodes_since_admission >= self.cfg.max_waiting_steps
 
-    def _oldest_first(self) -> list[Sequence]:
-        """Running requests, oldest admission first; without those the engine already knows to end with a
-        step that is still in flight."""
-        return sorted((s for s in self.running if not s.finishing), key=lambda s: s.admit_order)
+    # --- the three passes -----------------------------------------------------------------------
 
-    def _admit(self, seq: Sequence) -> None:
-        tokens = seq.all_token_ids
-        seq.num_computed_tokens = self.cache.allocate(seq.cache, tokens)
-        seq.status = Status.RUNNING
-        seq.admit_order = self._admit_counter
-        self._admit_counter += 1
-        self.running.append(seq)
+    def _decode_pass(self, plan: StepPlan) -> tuple[list[PlanItem], list[Request]]:
+        """Running requests in admission order. One that is through its prompt decodes one token, after its
+        page is secured; one still inside its prompt is set aside for the continue pass. Returns both."""
+        order = deque(sorted((r for r in self.running if not r.closing), key=lambda r: r.seat))
+        decodes: list[PlanItem] = []
+        midway: list[Request] = []
+        while order:
+            req = order.popleft()
+            if req.backlog > 1:
+                midway.append(req)
+            elif self._secure_page(req, order, plan):
+                decodes.append(PlanItem(req, req.n_tokens - 1, 1, True))
+        return decodes, midway
 
-    def _head_status(self, plan: StepPlan) -> Sequence | None:
-        """The head of the waiting queue if it can be admitted now; drops heads that never fit."""
-        while self.waiting and len(self.running) < self.cfg.max_num_seqs:
-            seq = self.waiting[0]
-            if seq.awaits_token:          # preempted with a step in flight: its last id is not on the host yet
-                return None
-            status = self.cache.admission_status(seq.cache, seq.all_token_ids)
-            if status == AllocStatus.NEVER:
-                self.waiting.popleft()
-                plan.ignored.append(seq)
-                continue
-            return seq if status == AllocStatus.OK else None
-        return None
+    def _secure_page(self, req: Request, younger: deque[Request], plan: StepPlan) -> bool:
+        """Room for ``req``'s next token. While there is none, the youngest request this step has not
+        looked at yet is evicted (it may be a prompt in progress; never one older than ``req``), and when
+        no such request is left, ``req`` itself. False when ``req`` had to go."""
+        while not self.cache.can_grow(req.cache, req.n_tokens):
+            victim = younger.pop() if younger else req
+            self._evict(victim, plan)
+            if victim is req:
+                return False
+        self.cache.grow(req.cache, req.n_tokens)
+        return True
 
-    def _schedule_prefills(self, plan: StepPlan) -> None:
-        budget = self.cfg.max_num_batched_tokens
-        while True:
-            seq = self._head_status(plan)
-            if seq is None:
-                break
-            # A prompt that does not fit the budget waits, except that one larger than the whole
-            # budget runs alone.
-            if seq.length > budget and plan.items:
-                break
-            self.waiting.popleft()
-            self._admit(seq)
-            n = seq.num_new_tokens
-            plan.items.append(PlanItem(seq, seq.num_computed_tokens, n, False))
-            budget -= n
+    @staticmethod
+    def _continue_pass(midway: list[Request], budget: int) -> list[PlanItem]:
+        """Prompts in progress, oldest first, take what the budget still holds."""
+        portions = []
+        for req in midway:
             if budget <= 0:
                 break
+            n = min(req.backlog, budget)
+            portions.append(PlanItem(req, req.cached_tokens, n, False))
+            budget -= n
+        return portions
 
-    def _schedule_decodes(self, plan: StepPlan, queue: list[Sequence]) -> list[PlanItem]:
-        """Every request of ``queue`` (oldest first) that is ready decodes one token; growth that
-        finds no free page preempts from the newest end. Returns the decode items in order."""
+    def _admit_pass(self, plan: StepPlan, budget: int, *, whole_prompts: bool) -> list[PlanItem]:
+        """Admit from the head of the queue while the budget lasts. ``whole_prompts``: a prompt is never cut,
+        one that does not fit what is left waits for the next step, and one longer than a whole step's budget
+        gets a step to itself. Otherwise the last one admitted takes a portion. Pages for all of a request's
+        tokens are taken at admission either way."""
         items: list[PlanItem] = []
-        queue = list(queue)
-        while queue:
-            seq = queue.pop(0)
-            preempted_self = False
-            while not self.cache.can_grow(seq.cache, seq.length):
-                victim = queue.pop() if queue else seq
-                self._preempt(victim, plan)
-                if victim is seq:
-                    preempted_self = True
-                    break
-            if preempted_self:
-                continue
-            self.cache.grow(seq.cache, seq.length)
-            items.append(PlanItem(seq, seq.length - 1, 1, True))
-        plan.items += items
+        while budget > 0:
+            req = self._admissible_head(plan)
+            if req is None or (whole_prompts and items and req.n_tokens > budget):
+                break
+            self.queue.popleft()
+            self._seat(req)
+            n = req.backlog if whole_prompts else min(req.backlog, budget)
+            items.append(PlanItem(req, req.cached_tokens, n, False))
+            budget -= n
         return items
 
-    def _schedule_mixed(self, plan: StepPlan) -> None:
-        budget = self.cfg.max_num_batched_tokens
-        # 1. Running requests, oldest first: ready ones decode, ones still inside their prompt wait
-        #    for step 2. A victim comes from the newest end of what has not been visited yet, so it
-        #    may be a prompt in progress, never one older than the request that needs the page.
-        queue = self._oldest_first()
-        partial: list[Sequence] = []
-        decodes: list[PlanItem] = []
-        while queue:
-            seq = queue.pop(0)
-            if seq.num_new_tokens > 1:
-                partial.append(seq)
-                continue
-            preempted_self = False
-            while not self.cache.can_grow(seq.cache, seq.length):
-                victim = queue.pop() if queue else seq
-                self._preempt(victim, plan)
-                if victim is seq:
-                    preempted_self = True
-                    break
-            if preempted_self:
-                continue
-            self.cache.grow(seq.cache, seq.length)
-            decodes.append(PlanItem(seq, seq.length - 1, 1, True))
-        budget -= len(decodes)
-        # 2. Prompts already in progress, oldest first. 3. New prompts, first come first served.
-        prefills: list[PlanItem] = []
-        for seq in partial:
-            if budget <= 0:
-                break
-            n = min(seq.num_new_tokens, budget)
-            prefills.append(PlanItem(seq, seq.num_computed_tokens, n, False))
-            budget -= n
-        while budget > 0:
-            seq = self._head_status(plan)
-            if seq is None:
-                break
-            self.waiting.popleft()
-            self._admit(seq)                               # pages for the whole prompt up front
-            n = min(seq.num_new_tokens, budget)
-            prefills.append(PlanItem(seq, seq.num_computed_tokens, n, False))
-            budget -= n
-        plan.items = prefills + decodes
+    def _admissible_head(self, plan: StepPlan) -> Request | None:
+        """The head of the queue if it can be admitted now. Heads that can never fit are rejected on the way."""
+        while self.queue and len(self.running) < self.cfg.max_num_seqs:
+            head = self.queue[0]
+            if head.awaits_token:          # evicted with a step in flight: its newest id is not on the host yet
+                return None
+            verdict = self.cache.admission_status(head.cache, head.tokens)
+            if verdict is AllocStatus.OK:
+                return head
+            if verdict is AllocStatus.LATER:
+                return None
+            plan.rejected.append(self.queue.popleft())
+        return None
 
-    def _preempt(self, seq: Sequence, plan: StepPlan) -> None:
-        self.running.remove(seq)
-        self.cache.free(seq.cache)
-        seq.num_computed_tokens = 0              # recompute prompt + generated tokens on resume
-        seq.status = Status.PREEMPTED
-        seq.num_preemptions += 1
-        self.num_preemptions += 1
-        self.waiting.appendleft(seq)             # front of the queue
-        plan.preempted.append(seq)
+    # --- state changes --------------------------------------------------------------------------
+
+    def _seat(self, req: Request) -> None:
+        req.cached_tokens = self.cache.allocate(req.cache, req.tokens)      # > 0 after a prefix hit
+        req.phase, req.seat = Phase.RUNNING, self._next_seat
+        self._next_seat += 1
+        self.running.append(req)
+
+    def _evict(self, req: Request, plan: StepPlan) -> None:
+        self.running.remove(req)
+        self.cache.free(req.cache)
+        req.cached_tokens = 0
+        req.phase = Phase.EVICTED
+        req.evictions += 1
+        self.evictions += 1
+        self.queue.appendleft(req)
+        plan.evicted.append(req)

@@ -23,6 +23,7 @@ from .config.engine_config import add_engine_args, engine_config_from_args
 def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(prog="python -m tokenmill_b200.generate", description=__doc__.split("\n\n")[0])
     add_engine_args(ap)
+    ap.set_defaults(max_model_len=None)      # unless given: the engine's default, or the model's own limit if that is less
     ap.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids (repeatable)")
     ap.add_argument("--prompt-file", help="file with one JSON list of token ids per line")
     ap.add_argument("--max-tokens", type=int, default=16)
@@ -55,6 +56,11 @@ def main(argv: list[str] | None = None) -> int:
         args.model = tmp.name
     if not args.model:
         ap.error("give --model or --random-weights")
+    if args.max_model_len is None:
+        from .config.engine_config import EngineConfig
+        from .weights.loader import read_spec
+
+        args.max_model_len = min(EngineConfig().max_model_len, read_spec(args.model)[0].max_positions)
     try:
         engine = LLMEngine(engine_config_from_args(args))
         params = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
