@@ -5,7 +5,8 @@ the two tiny test configurations with this repository's random-weights writer, l
 folders with the reference's loader, runs its whole-sequence forward pass (no cache) and its
 single-sequence greedy path, and records a few logits and the greedy tokens. The recorded file
 (tests/golden/tiny_golden.json) is committed; tests/test_plain.py compares the plain implementation
-with it, and re-runs this comparison live when the reference is importable.
+with it, and re-runs this comparison live (test_plain_matches_the_reference_live) when the reference's
+package is present (baseline/_ref of the checkout, or $TOKENMILL_REFERENCE_SRC).
 
     python tests/golden/make_golden.py --reference-src <reference checkout>/src
 

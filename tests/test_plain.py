@@ -33,6 +33,40 @@ def test_plain_matches_the_reference_recording(name, tmp_path):
         assert row["max_abs_diff_vs_reference"] < 1e-5
 
 
+def _reference_src() -> Path | None:
+    """Where the reference's ``infer`` package can be imported from: $TOKENMILL_REFERENCE_SRC, or the offline
+    install under baseline/_ref of this checkout."""
+    import os
+    for cand in (os.environ.get("TOKENMILL_REFERENCE_SRC"), Path(__file__).resolve().parents[1] / "baseline" / "_ref"):
+        if cand and (Path(cand) / "infer" / "model" / "qwen2.py").is_file():
+            return Path(cand)
+    return None
+
+
+@pytest.mark.skipif(_reference_src() is None, reason="the reference's model code is not present in this checkout")
+def test_plain_matches_the_reference_live(tmp_path):
+    """The anchor again, not from the recording: the reference's own loader and whole-sequence forward pass on
+    the CPU against the plain implementation, on a tiny random model (logits and greedy tokens)."""
+    import sys
+    sys.path.insert(0, str(Path(__file__).parent / "golden"))
+    sys.path.insert(0, str(_reference_src()))
+    try:
+        import make_golden
+        from tokenmill_b200.weights import named_config
+        cfg_json = named_config("tiny-b")
+        folder = write_random_model(tmp_path / "tiny-b", cfg_json, seed=5, store_dtype="float32")
+        prompts = make_golden.prompts_for("tiny-b", cfg_json["vocab_size"])[:3]
+        ref = make_golden.reference_outputs(folder, prompts, 6)
+    finally:
+        sys.path.remove(str(_reference_src()))
+        for name in [m for m in sys.modules if m == "infer" or m.startswith("infer.")]:
+            del sys.modules[name]
+    cfg, w = load_plain(folder)
+    for p, r in zip(prompts, ref):
+        assert float((plain_logits(cfg, w, p) - r["logits"]).abs().max()) < 1e-5
+        assert plain_greedy(cfg, w, p, 6) == r["greedy"]
+
+
 def test_rmsnorm_formula():
     x = torch.randn(5, 12)
     w = torch.rand(12) + 0.5

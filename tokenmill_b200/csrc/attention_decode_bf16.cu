@@ -29,13 +29,19 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_bf16_kernel(
     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_before, float* __restrict__ part_acc,
     float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int* __restrict__ done, int nh, int nkv,
-    int page_size, float scale_log2, int window, int split_keys, int max_splits) {
+    int page_size, float scale_log2, int window, int split_keys, int max_splits, int* __restrict__ error) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_last;
   pdl_launch_dependents();
   pdl_wait();                                  // q and this step's keys and values come from the kernel before
   const int s = blockIdx.x, kvh = blockIdx.y;
   const int q_start = cu_q[s], q_len = cu_q[s + 1] - q_start, before = kv_before[s];
+  // What the host cannot check (the lengths live on the device): a request with more rows than a tile holds,
+  // or with keys beyond the last split of the launch grid. Such a request's output would be incomplete; the
+  // error word says so (32), the splits that exist are still merged and the counters still end at zero.
+  if (threadIdx.x == 0 && blockIdx.z == 0 && kvh == 0 && error &&
+      (q_len * (nh / nkv) > 16 || (q_len > 0 && (before + q_len - 1) / split_keys >= max_splits)))
+    atomicCAS(error, 0, 32);
   const bool worked = decode_attention_unit<D>(q, kcache, vcache, block_table + (size_t)s * bt_stride, q_start, q_len,
                                                before, kvh, blockIdx.z, part_acc, part_ml, nh, nkv, page_size,
                                                scale_log2, window, split_keys, max_splits, smem, threadIdx.x,
@@ -46,7 +52,8 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_bf16_kernel(
   const int n_rows = min(q_len * G, 16);
   const int p_max = before + (n_rows - 1) / G;
   const int lo_all = window > 0 ? max(0, before - window + 1) : 0;
-  const int expected = p_max / split_keys - lo_all / split_keys + 1;
+  const int z_last = min(p_max / split_keys, max_splits - 1);        // splits beyond the grid do not exist
+  const int expected = z_last - lo_all / split_keys + 1;
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(&done[s * nkv + kvh], 1) == expected - 1;
@@ -58,7 +65,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_bf16_kernel(
     const size_t orow = (size_t)(q_start + r / G) * nh + kvh * G + r % G;
     const int p = before + r / G;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int z0 = lo / split_keys, z1 = p / split_keys;
+    const int z0 = lo / split_keys, z1 = min(p / split_keys, max_splits - 1);
     // One pass in split order: the running maximum rescales what has been summed so far. The loads do not
     // depend on the running state, so several splits are in flight at a time.
     float mx = -INFINITY, lsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -89,7 +96,7 @@ template <int D>
 int launch_decode_attention(const void* q, const void* kcache, const void* vcache, const int* block_table,
                             int bt_stride, const int* cu_q, const int* kv_before, int n_seqs, float* part_acc,
                             float* part_ml, void* out, int* done, int nh, int nkv, int page_size, float scale,
-                            int window, int split_keys, int max_splits, cudaStream_t stream) {
+                            int window, int split_keys, int max_splits, int* error, cudaStream_t stream) {
   const int kv_bytes = 2 * 2 * kDecBN * D * 2;
   const int merge_bytes = kDecWarps * 16 * (D + 2) * 4;
   const int smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
@@ -102,7 +109,7 @@ int launch_decode_attention(const void* q, const void* kcache, const void* vcach
   return launch_pdl(kern, grid, dim3(kDecWarps * 32), (size_t)smem, stream, (const __nv_bfloat16*)q,
                     (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, bt_stride, cu_q,
                     kv_before, part_acc, part_ml, (__nv_bfloat16*)out, done, nh, nkv, page_size,
-                    scale * 1.4426950408889634f, window, split_keys, max_splits);
+                    scale * 1.4426950408889634f, window, split_keys, max_splits, error);
 }
 
 }  // namespace tmk
@@ -110,12 +117,15 @@ int launch_decode_attention(const void* q, const void* kcache, const void* vcach
 // q, out [T, nh, D] bfloat16; caches [pages, page_size, nkv, D] bfloat16. Every request must bring at most
 // 16 / (nh / nkv) tokens. Scratch: part_acc [T*nh, max_splits, D], part_ml [T*nh, max_splits, 2] float32, and
 // done [n_seqs * nkv] ints that are zero before the first launch (the kernel leaves them zero). Head sizes 64
-// and 128.
+// and 128. max_splits * split_keys must exceed the longest context of the step; where it does not, or a request
+// brings more rows than a tile, `error` (a device int that is zero; may be null) is set to 32 and that request's
+// output is incomplete.
 extern "C" int tm_decode_attention_bf16(const void* q, const void* kcache, const void* vcache,
                                         const int* block_table, int bt_stride, const int* cu_q,
                                         const int* kv_before, int n_seqs, float* part_acc, float* part_ml,
                                         void* out, int* done, int nh, int nkv, int D, int page_size, float scale,
-                                        int window, int split_keys, int max_splits, cudaStream_t stream) {
+                                        int window, int split_keys, int max_splits, int* error,
+                                        cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (nkv <= 0 || nh % nkv || nh / nkv > 16 || page_size <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
   if (split_keys <= 0 || split_keys % tmk::kDecBN || max_splits <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
@@ -123,10 +133,10 @@ extern "C" int tm_decode_attention_bf16(const void* q, const void* kcache, const
   if (D == 64)
     return tmk::launch_decode_attention<64>(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before, n_seqs,
                                             part_acc, part_ml, out, done, nh, nkv, page_size, scale, window,
-                                            split_keys, max_splits, stream);
+                                            split_keys, max_splits, error, stream);
   if (D == 128)
     return tmk::launch_decode_attention<128>(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before, n_seqs,
                                              part_acc, part_ml, out, done, nh, nkv, page_size, scale, window,
-                                             split_keys, max_splits, stream);
+                                             split_keys, max_splits, error, stream);
   return TM_ERR_UNSUPPORTED_SHAPE;
 }

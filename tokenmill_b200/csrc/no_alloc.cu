@@ -11,21 +11,24 @@
 static __device__ __align__(256) float tm_noalloc_scratch[TM_NOALLOC_SCRATCH_FLOATS];
 constexpr int kNoallocCounters = 4096;
 static __device__ int tm_noalloc_done[kNoallocCounters];
+static __device__ int tm_noalloc_error;       // raised (32) by a launch whose requests broke the rules on sizes
 
 extern "C" int tm_decode_attention_bf16(const void* q, const void* kcache, const void* vcache,
                                         const int* block_table, int bt_stride, const int* cu_q,
                                         const int* kv_before, int n_seqs, float* part_acc, float* part_ml,
                                         void* out, int* done, int nh, int nkv, int D, int page_size, float scale,
-                                        int window, int split_keys, int max_splits, cudaStream_t stream);
+                                        int window, int split_keys, int max_splits, int* error,
+                                        cudaStream_t stream);
 
 namespace {
 
 constexpr int kMaxDevices = 64;
 float* g_scratch[kMaxDevices] = {};   // device address of tm_noalloc_scratch, per device, once looked up
 int* g_done[kMaxDevices] = {};        // and of tm_noalloc_done
+int* g_error[kMaxDevices] = {};       // and of tm_noalloc_error
 
 // The arrays' addresses on the current device. The first call per device does the look-up.
-int scratch_for_current_device(float** ptr, int** done) {
+int scratch_for_current_device(float** ptr, int** done, int** error) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -37,11 +40,16 @@ int scratch_for_current_device(float** ptr, int** done) {
     int* d = nullptr;
     e = cudaGetSymbolAddress((void**)&d, tm_noalloc_done);
     if (e != cudaSuccess) return (int)e;
+    int* w = nullptr;
+    e = cudaGetSymbolAddress((void**)&w, tm_noalloc_error);
+    if (e != cudaSuccess) return (int)e;
+    g_error[dev] = w;
     g_done[dev] = d;
     g_scratch[dev] = p;
   }
   *ptr = g_scratch[dev];
   *done = g_done[dev];
+  *error = g_error[dev];
   return 0;
 }
 
@@ -61,11 +69,38 @@ extern "C" int tm_decode_attention_bf16_noalloc(const void* q, const void* kcach
     return TM_ERR_NOALLOC_TOO_LARGE;
   float* scratch = nullptr;
   int* done = nullptr;
-  const int status = scratch_for_current_device(&scratch, &done);
+  int* error = nullptr;
+  const int status = scratch_for_current_device(&scratch, &done, &error);
   if (status != 0) return status;
   float* part_acc = scratch;                  // [rows, D]
   float* part_ml = scratch + rows * D;        // [rows, 2]
   return tm_decode_attention_bf16(q, kcache, vcache, block_table, bt_stride, cu_q, kv_before, n_seqs, part_acc,
                                   part_ml, out, done, nh, nkv, D, page_size, scale, window, split_keys, max_splits,
-                                  stream);
+                                  error, stream);
+}
+
+// Puts the arrival counters and the error word back to zero, on `stream` (cudaMemsetAsync at the arrays' own
+// addresses: nothing is allocated). For after a launch that failed or was cut short.
+extern "C" int tm_decode_attention_bf16_noalloc_reset(cudaStream_t stream) {
+  float* scratch = nullptr;
+  int* done = nullptr;
+  int* error = nullptr;
+  const int status = scratch_for_current_device(&scratch, &done, &error);
+  if (status != 0) return status;
+  cudaError_t e = cudaMemsetAsync(done, 0, sizeof(int) * kNoallocCounters, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(error, 0, sizeof(int), stream);
+  return (int)e;
+}
+
+// Reads the error word of the current device into *code (0: every launch so far kept the rules; 32: some
+// request had more rows than a tile holds, or keys beyond max_splits * split_keys). Waits for `stream`.
+extern "C" int tm_decode_attention_bf16_noalloc_status(int* code, cudaStream_t stream) {
+  float* scratch = nullptr;
+  int* done = nullptr;
+  int* error = nullptr;
+  const int status = scratch_for_current_device(&scratch, &done, &error);
+  if (status != 0) return status;
+  cudaError_t e = cudaMemcpyAsync(code, error, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return (int)e;
 }

@@ -19,11 +19,17 @@
 //    heads, D = head size), and requests x kv heads the 4,096 counters; larger steps are refused with
 //    TM_ERR_NOALLOC_TOO_LARGE (90004) before anything is launched. Batch 64, 14 heads of 64, contexts up to
 //    4096 (16 splits of 256 keys) need 0.95 M floats.
+//  * What the host cannot see (the requests' lengths are device arrays): max_splits * split_keys must exceed
+//    the longest context of the step, and no request may bring more than 16 / (nh / nkv) tokens. A launch
+//    that meets a request beyond either limit leaves that request's output incomplete and raises an error
+//    word inside the library, which tm_decode_attention_bf16_noalloc_status reads (32); the counters still
+//    end at zero.
 //  * First call on a device: it looks up the array's device address once (cudaGetSymbolAddress, with that
 //    device current) and remembers it. Make that first call outside any stream capture.
 //  * The arrays are shared by every call. The floats keep the last call's contents and need not start at
 //    zero (each call writes every partial it later reads); the counters are zero in the image and every call
-//    leaves them zero. Two calls that overlap on the GPU (different streams, or one call racing a graph
+//    leaves them zero. A call that returned a CUDA error (a failed launch, a fault in an earlier kernel of the
+//    stream) leaves them undefined: call tm_decode_attention_bf16_noalloc_reset before the next one. Two calls that overlap on the GPU (different streams, or one call racing a graph
 //    replay that contains another) would write the same floats and counters: keep calls to this entry point
 //    ordered on one stream.
 #pragma once
@@ -46,6 +52,13 @@ int tm_decode_attention_bf16_noalloc(const void* q, const void* kcache, const vo
                                      const int* seq_of_token, int n_seqs, int n_tokens, void* out, int nh, int nkv,
                                      int D, int page_size, float scale, int window, int split_keys, int max_splits,
                                      cudaStream_t stream);
+
+// Zeroes the arrival counters and the error word on `stream` (no allocation). Use after a failed launch.
+int tm_decode_attention_bf16_noalloc_reset(cudaStream_t stream);
+
+// Copies the current device's error word to *code (host memory) and waits for `stream`: 0, or 32 after a launch
+// that met a request beyond the size rules above.
+int tm_decode_attention_bf16_noalloc_status(int* code, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -40,7 +40,7 @@ int tm_prefill_attention_bf16(const void* q, const void* kcache, const void* vca
 int tm_decode_attention_bf16(const void* q, const void* kcache, const void* vcache, const int* block_table,
                              int bt_stride, const int* cu_q, const int* kv_before, int n_seqs, float* part_acc,
                              float* part_ml, void* out, int* done, int nh, int nkv, int D, int page_size, float scale,
-                             int window, int split_keys, int max_splits, cudaStream_t stream);
+                             int window, int split_keys, int max_splits, int* error, cudaStream_t stream);
 }
 
 #define TM_ERR_PROGRAM 90010          // a malformed record (unknown kind, parameter index out of range)
@@ -168,13 +168,13 @@ static int run_op(const ProgramOp& op, const int64_t* a, cudaStream_t s) {
                                        as_ptr<void>(a[12]), (int)a[13], (int)a[14], (int)a[15], (int)a[16], as_float(a[17]),
                                        (int)a[18], s);
     case kOpDecodeAttention:     // q, k, v, table, bt_stride, cu_q, kv_before, n_seqs, acc, ml, out, done, nh, nkv, D, page,
-                                 // scale, window, split_keys, max_splits
-      if (op.n_args != 20) return TM_ERR_PROGRAM;
+                                 // scale, window, split_keys, max_splits, error
+      if (op.n_args != 21) return TM_ERR_PROGRAM;
       return tm_decode_attention_bf16(as_ptr<const void>(a[0]), as_ptr<const void>(a[1]), as_ptr<const void>(a[2]),
                                       as_ptr<const int>(a[3]), (int)a[4], as_ptr<const int>(a[5]), as_ptr<const int>(a[6]),
                                       (int)a[7], as_ptr<float>(a[8]), as_ptr<float>(a[9]), as_ptr<void>(a[10]), as_ptr<int>(a[11]),
                                       (int)a[12], (int)a[13], (int)a[14], (int)a[15], as_float(a[16]), (int)a[17], (int)a[18],
-                                      (int)a[19], s);
+                                      (int)a[19], as_ptr<int>(a[20]), s);
     case kOpSwiglu:       // dtype, gu, out, T, I
       if (op.n_args != 5) return TM_ERR_PROGRAM;
       return tm_swiglu((int)a[0], as_ptr<const void>(a[1]), as_ptr<void>(a[2]), (int)a[3], (int)a[4], s);

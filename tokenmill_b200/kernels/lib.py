@@ -41,7 +41,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_paged_attention": [_I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
                            _I, _P],
     "tm_attention_combine": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "tm_decode_attention_bf16": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "tm_decode_attention_bf16": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
     "tm_prefill_attention_bf16": [_P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "tm_prefill_attention_tc_timing": [_P],
     "tm_prefill_attention_tc_bf16": [_P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],

@@ -165,7 +165,8 @@ def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
              _req(block_table, "block_table", torch.int32), block_table.stride(0), _req(cu_q, "cu_q", torch.int32),
              _req(kv_before, "kv_before", torch.int32), n_seqs, _req(part_acc, "part_acc", torch.float32),
              _req(part_ml, "part_ml", torch.float32), _req(out, "out", bf), _req(done, "done", torch.int32), nh, nkv, D,
-             page_size, float(scale), int(window), int(split_keys), int(max_splits), _stream())
+             page_size, float(scale), int(window), int(split_keys), int(max_splits), _tc_flag(q.device).data_ptr(),
+             _stream())
     return out
 
 
@@ -505,6 +506,9 @@ def tc_check(device: torch.device) -> None:
         code = int(flag.item())
         if code:
             flag.zero_()
+            if code == 32:
+                raise lib.KernelError("decode attention met a request with more rows than a tile holds or with keys "
+                                      "beyond max_splits * split_keys; its output is incomplete")
             if code == 31:
                 raise lib.KernelError("a token's position lies outside the position tables (the rotation was not "
                                       "applied as asked; the step's results are wrong)")

@@ -234,7 +234,7 @@ class GroupedQueryAttention:
                 b.param(f"decode_acc_{key}", dec(0)), b.param(f"decode_ml_{key}", dec(1)),
                 out, b.param(f"decode_done_{key}", dec(2)), nh, nkv, D, page, scale, window,
                 b.param(f"split_keys_{key}", lambda s: meta(s).host["split_keys"]),
-                b.param(f"max_splits_{key}", lambda s: meta(s).host["max_splits"])],
+                b.param(f"max_splits_{key}", lambda s: meta(s).host["max_splits"]), ops.tc_error_word(self.device)],
                cond=b.param(f"attention_decode_{key}", lambda s: int(path(s) == "decode")))
 
         # prompt kernels: the step's work units for this head grouping, scratch for the tiles with several chunks
