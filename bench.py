@@ -1,15 +1,26 @@
 """Decode and prefill throughput of the engine at the Qwen2.5-0.5B layer sizes, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+    python bench.py --workload 1.5b-mixed | 7b-prefix [--impl ours|reference] [--layers L]
 
-One JSON line on standard output. A "step" is one decode step of a batch of 8 requests (prompt 512,
-context limit 4096). ``value`` is decoded tokens per second timed on the device with CUDA events around
-exactly K steps of the engine's step function (one metadata copy, the captured decode graph and the
-arg-max kernel per step); ``e2e`` is the same quantity through the Python entry point
-(``LLMEngine.step``: scheduler, pinned host-to-device metadata copy, decode graph, sampling, token ids
-read back to the host every step), timed on the host between two device synchronisations. ``prefill``
-times one 2,048-token prompt; ``roofline`` relates the decode step to the memory bandwidth it needs
-(every weight once plus the live requests' cache); ``points`` holds decode at batch 1 and 64.
+One JSON line on standard output. A "step" is one decode step of a batch of 8 requests (prompt 512, 512 new
+tokens, context limit 4096): after the prompts, decode steps run untimed until the K timed steps lie in the
+middle of the 512 new tokens (mean context 768). ``value`` is decoded tokens per second timed on the device
+with CUDA events around exactly K steps of the engine's step function (one metadata copy, the whole-step decode
+kernel, the output matrix and the arg-max kernel per step); ``e2e`` is the same quantity through the Python
+entry point (``LLMEngine.step``: scheduler, pinned host-to-device metadata copy, kernels, sampling, token ids
+read back to the host every step), timed on the host between two device synchronisations. ``prefill`` times
+one 2,048-token prompt; ``roofline`` relates the decode step to the memory bandwidth it needs (every weight
+once plus the live requests' cache); ``points`` holds decode at batch 1 and 64 (device-timed and end to end);
+``fp32`` the float32 engine's decode step at batch 8 and its 2,048-token prompt.
+
+``--workload`` runs one of the two other workloads the baseline names, through ``LLMEngine`` with every
+request submitted at once and stepped to completion (the reference's bench/common.py:58-76 method), and prints
+one JSON line with generated tokens per second, preemptions and the prefix-cache hit rate:
+``1.5b-mixed``: Qwen2.5-1.5B sizes, 64 requests, prompt lengths uniform in [128, 2048], 256 new tokens,
+chunked prefill with a 2,048-token budget; ``7b-prefix``: Qwen2.5-7B sizes, context 8192, 32 requests of
+4,096-token prompts that share their first 1,024 tokens, 512 new tokens, prefix caching, a pool too small for
+all of them so that requests are preempted.
 
 The engine runs on one GPU: for --gpus N > 1 a line says so and the exit code is 2.
 """
@@ -33,7 +44,7 @@ SIZES = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hid
              num_attention_heads=14, num_key_value_heads=2, head_dim=64, rope_theta=1000000.0, rms_norm_eps=1e-6,
              tie_word_embeddings=True, max_position_embeddings=32768)
 MODEL_LABEL = "Qwen2.5-0.5B"
-PROMPT_LEN, CONTEXT, BATCH, PREFILL_TOKENS, PAGE = 512, 4096, 8, 2048, 16
+PROMPT_LEN, NEW_TOKENS, CONTEXT, BATCH, PREFILL_TOKENS, PAGE = 512, 512, 4096, 8, 2048, 16
 
 
 def use_sizes(name: str) -> None:
@@ -130,7 +141,7 @@ def prompts(batch: int, length: int, seed: int = 0) -> list[list[int]]:
     return [[rng.randrange(1000, 150000) for _ in range(length)] for _ in range(batch)]
 
 
-def decode_device_timed(engine, batch: int, steps: int, warmup: int) -> dict:
+def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead: bool = True) -> dict:
     """K decode steps of the step function, CUDA events on the launching stream."""
     import torch
     from tokenmill_b200.engine.batch import StepEntry
@@ -146,6 +157,8 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int) -> dict:
         runner.step([StepEntry(h, p, 0, []) for h, p in handles[lo:lo + 4]])
     length = PROMPT_LEN
     tok = [p[-1] for _, p in handles]
+    # The timed steps lie in the middle of the NEW_TOKENS new tokens; the steps before them run untimed.
+    forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup) if skip_ahead else 0
 
     def one():
         nonlocal length
@@ -155,7 +168,7 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int) -> dict:
         ops.argmax(logits)
         length += 1
 
-    for _ in range(warmup):
+    for _ in range(forward + warmup):
         one()
     torch.cuda.synchronize()
     launches0 = lib.launch_count
@@ -179,11 +192,12 @@ def decode_end_to_end(engine, batch: int, steps: int, warmup: int) -> dict:
     import torch
     from tokenmill_b200.sampling import SamplingParams
 
-    sp = SamplingParams(max_tokens=steps + warmup + 2, ignore_eos=True)
+    forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup)
+    sp = SamplingParams(max_tokens=forward + steps + warmup + 4, ignore_eos=True)
     seqs = [engine.add_request(f"e2e-{batch}-{i}", p, sp) for i, p in enumerate(prompts(batch, PROMPT_LEN, seed=99))]
-    while any(s.num_output_tokens == 0 for s in seqs):
+    while any(s.n_output == 0 for s in seqs):
         engine.step()
-    for _ in range(warmup):
+    for _ in range(forward + warmup):
         engine.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -273,9 +287,31 @@ def products_timed(tokens: int = 8) -> list[dict]:
 
 
 
+def bench_config(layers: int, mean_ctx: float, extra: dict) -> dict:
+    """The ``config`` object of the JSON line (flat, at most 20 keys), the same keys in both arms."""
+    cfg = {"model": f"{MODEL_LABEL} sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
+           "hidden": SIZES["hidden_size"], "q_heads": SIZES["num_attention_heads"],
+           "kv_heads": SIZES["num_key_value_heads"], "head_dim": SIZES["head_dim"],
+           "intermediate": SIZES["intermediate_size"], "vocab": SIZES["vocab_size"],
+           "tied_output": bool(SIZES["tie_word_embeddings"]), "global_batch": BATCH, "prompt_len": PROMPT_LEN,
+           "new_tokens": NEW_TOKENS, "seq_len": CONTEXT, "kv_page": PAGE, "mean_decode_context": round(mean_ctx, 1),
+           "parallelism": "single GPU"}
+    cfg.update(extra)
+    assert len(cfg) <= 20
+    return cfg
+
+
+def engine_config(model_dir: str, dtype: str, info: dict, graphs: bool):
+    from tokenmill_b200 import EngineConfig
+    elt = 2 if dtype == "bfloat16" else 4
+    return EngineConfig(model=model_dir, dtype=dtype, block_size=PAGE, max_model_len=CONTEXT, max_num_seqs=64,
+                        max_num_batched_tokens=4 * PROMPT_LEN,
+                        kv_cache_mb=64 * (PROMPT_LEN + NEW_TOKENS + 64) * info["kv_bytes_per_token"] * (elt // 2) / 2 ** 20,
+                        watermark=0.0, cuda_graphs=graphs, cuda_graph_max_batch=64)
+
+
 def run_ours(args) -> dict:
     import torch
-    from tokenmill_b200 import EngineConfig
     from tokenmill_b200.engine import LLMEngine
     from tokenmill_b200.kernels import lib
 
@@ -287,49 +323,60 @@ def run_ours(args) -> dict:
     pk, pk_kind = peaks()
     info = model_flops_bytes(SIZES, layers)
     tmp = make_model_dir(layers)
+    fp32 = None
     try:
-        cfg = EngineConfig(model=tmp.name, dtype="bfloat16", block_size=PAGE, max_model_len=CONTEXT, max_num_seqs=64,
-                           max_num_batched_tokens=4 * PROMPT_LEN, kv_cache_mb=64 * CONTEXT * info["kv_bytes_per_token"]
-                           / 2 ** 20, watermark=0.0, cuda_graphs=not args.no_graphs, cuda_graph_max_batch=64)
-        engine = LLMEngine(cfg)
+        engine = LLMEngine(engine_config(tmp.name, "bfloat16", info, not args.no_graphs))
         lib.load()
         if args.only:                                             # a small case for profilers: no JSON contract
             if args.only == "prefill":
                 print(json.dumps({"only": "prefill", **prefill_timed(engine, args.prefill_tokens, reps=args.steps)}))
             else:
                 batch = int(args.only.split("_b")[1])
-                r = decode_device_timed(engine, batch, args.steps, args.warmup)
-                print(json.dumps({"only": args.only, "ms_per_step": r["ms_per_step"], "tok_s": r["tok_s"]}))
+                r = decode_device_timed(engine, batch, args.steps, args.warmup, skip_ahead=not args.no_skip)
+                print(json.dumps({"only": args.only, "ms_per_step": r["ms_per_step"], "tok_s": r["tok_s"],
+                                  "mean_ctx": r["mean_ctx"]}))
             return {}
         sampler = ClockSampler()
         # warm every path once before the clocks are sampled
-        decode_device_timed(engine, BATCH, 4, 3)
+        decode_device_timed(engine, BATCH, 4, 3, skip_ahead=False)
         sampler.start()
         main = decode_device_timed(engine, BATCH, args.steps, args.warmup)
         e2e = decode_end_to_end(engine, BATCH, args.steps, args.warmup)
-        b1 = decode_device_timed(engine, 1, max(16, args.steps // 2), args.warmup)
-        b64 = decode_device_timed(engine, 64, max(16, args.steps // 2), args.warmup)
+        side = max(16, args.steps // 2)
+        b1 = decode_device_timed(engine, 1, side, args.warmup)
+        b64 = decode_device_timed(engine, 64, side, args.warmup)
+        e1 = decode_end_to_end(engine, 1, side, args.warmup)
+        e64 = decode_end_to_end(engine, 64, side, args.warmup)
         pre = prefill_timed(engine, PREFILL_TOKENS)
         clocks = sampler.stop()
+        if not args.no_fp32:
+            # The float32 engine (true 32-bit products on CUDA cores): one decode point and the prompt, so that a
+            # regression of that path shows. Not part of the clock record above.
+            del engine
+            torch.cuda.empty_cache()
+            engine = LLMEngine(engine_config(tmp.name, "float32", info, False))
+            d32 = decode_device_timed(engine, BATCH, min(args.steps, 16), 3)
+            p32 = prefill_timed(engine, PREFILL_TOKENS, reps=2)
+            fp32 = {"decode_b8": round(d32["tok_s"], 1), "decode_b8_ms": round(d32["ms_per_step"], 4),
+                    "prefill_ms": round(p32["ms"], 3), "prefill_tok_s": round(PREFILL_TOKENS / (p32["ms"] / 1e3), 1)}
     finally:
         tmp.cleanup()
     step_bytes = info["weight_bytes"] + BATCH * main["mean_ctx"] * info["kv_bytes_per_token"]
     achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
     pf_flops = info["prefill_flops"](PREFILL_TOKENS)
     pf_frac = pf_flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12)
-    return {
+
+    def hbm_frac(batch, r):
+        return round((info["weight_bytes"] + batch * r["mean_ctx"] * info["kv_bytes_per_token"])
+                     / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+    out = {
         "metric": f"decode tok/s at batch 8 ({MODEL_LABEL} sizes, prompt 512, bf16)", "value": round(main["tok_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights seed 0", "impl": "ours",
-        "config": {"model": f"{MODEL_LABEL} sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
-                   "hidden": SIZES["hidden_size"], "q_heads": SIZES["num_attention_heads"],
-                   "kv_heads": SIZES["num_key_value_heads"], "head_dim": SIZES["head_dim"],
-                   "intermediate": SIZES["intermediate_size"], "vocab": SIZES["vocab_size"], "tied_output": bool(SIZES["tie_word_embeddings"]),
-                   "global_batch": BATCH, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "kv_page": PAGE,
-                   "mean_decode_context": round(main["mean_ctx"], 1), "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (weights read per step: %.0f MB)" % (info["weight_bytes"] / 1e6),
-                   "peaks": pk_kind},
+        "config": bench_config(layers, main["mean_ctx"], {
+            "l2": "inputs larger than L2 (weights read per step: %.0f MB)" % (info["weight_bytes"] / 1e6),
+            "peaks": pk_kind, "cuda_graphs": not args.no_graphs}),
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms_per_step"], 4),
                 "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": int(main["launches"]),
@@ -338,9 +385,97 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1),
-                   "decode_b1_ms": round(b1["ms_per_step"], 4), "decode_b64_ms": round(b64["ms_per_step"], 4)},
+                   "decode_b1_ms": round(b1["ms_per_step"], 4), "decode_b64_ms": round(b64["ms_per_step"], 4),
+                   "decode_b1_hbm_frac": hbm_frac(1, b1), "decode_b64_hbm_frac": hbm_frac(64, b64),
+                   "e2e_b1": round(e1["tok_s"], 1), "e2e_b64": round(e64["tok_s"], 1)},
         "clocks": clocks,
     }
+    if fp32 is not None:
+        out["fp32"] = fp32
+    return out
+
+
+# --- the two other workloads the baseline names --------------------------------------------------------------
+
+WORKLOADS = {
+    # sizes, context, requests, prompt lengths, shared prefix, new tokens, engine options, share of the need the pool holds
+    "1.5b-mixed": dict(sizes="qwen2.5-1.5b", context=4096, n=64, prompt=(128, 2048), shared=0, new=256,
+                       engine=dict(enable_chunked_prefill=True, max_num_batched_tokens=2048), pool_share=1.0),
+    "7b-prefix": dict(sizes="qwen2.5-7b", context=8192, n=32, prompt=(4096, 4096), shared=1024, new=512,
+                      engine=dict(enable_prefix_caching=True, max_num_batched_tokens=8192), pool_share=0.6),
+}
+
+
+def workload_prompts(w: dict, seed: int = 0) -> list[list[int]]:
+    import random
+    rng = random.Random(seed)
+    shared = [rng.randrange(1000, 150000) for _ in range(w["shared"])]
+    lo, hi = w["prompt"]
+    return [shared + [rng.randrange(1000, 150000) for _ in range(rng.randint(lo, hi) - w["shared"])] for _ in range(w["n"])]
+
+
+def run_workload(args) -> dict:
+    """Everything submitted at once and stepped to completion; generated tokens / wall time."""
+    import torch
+    w = WORKLOADS[args.workload]
+    use_sizes(w["sizes"])
+    layers = args.layers or SIZES["num_hidden_layers"]
+    info = model_flops_bytes(SIZES, layers)
+    prompts_ = workload_prompts(w)
+    need_tokens = sum(len(p) for p in prompts_) + w["n"] * w["new"]
+    pool_mb = w["pool_share"] * need_tokens * info["kv_bytes_per_token"] / 2 ** 20
+    tmp = make_model_dir(layers)
+    base = dict(model=tmp.name, dtype="bfloat16", block_size=PAGE, max_model_len=w["context"], max_num_seqs=w["n"],
+                kv_cache_mb=pool_mb, **w["engine"])
+    try:
+        if args.impl == "reference":
+            ref = ROOT / "baseline" / "_ref"
+            if not (ref / "infer").is_dir():
+                return {"impl": "reference", "unavailable": "baseline/_ref/infer is not installed on this machine"}
+            sys.path.insert(0, str(ref))
+            from infer.config import EngineConfig
+            from infer.engine.engine import LLMEngine
+            from infer.engine.sequence import SamplingParams
+            from infer.model.loader import load_model
+            model = load_model(tmp.name, torch.bfloat16, torch.device("cuda:0"), max_positions=w["context"])
+            engine = LLMEngine(EngineConfig(device="cuda:0", cuda_graphs=True, request_timeout=None, **base), model=model)
+        else:
+            from tokenmill_b200 import EngineConfig
+            from tokenmill_b200.engine import LLMEngine
+            from tokenmill_b200.sampling import SamplingParams
+            engine = LLMEngine(EngineConfig(**base))
+        sp = SamplingParams(max_tokens=w["new"], ignore_eos=True)
+        warm = engine.generate([prompts_[0][:64]], SamplingParams(max_tokens=4, ignore_eos=True))    # compile / warm paths
+        assert len(warm[0]) == 4
+        for i, p in enumerate(prompts_):
+            engine.add_request(f"w{i}", p, sp)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n_out = 0
+        while engine.has_unfinished():
+            n_out += sum(len(o.new_token_ids) for o in engine.step())
+        if hasattr(engine, "drain"):
+            n_out += sum(len(o.new_token_ids) for o in engine.drain())
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        sched, cache = engine.scheduler, engine.cache
+        preempted = getattr(sched, "evictions", getattr(sched, "num_preemptions", 0))
+        hit = getattr(cache, "prefix_hit_tokens", None)
+        asked = getattr(cache, "prefix_query_tokens", None)
+        if hit is None:                                           # the reference's counters live on its block manager
+            hit, asked = getattr(cache, "hit_tokens", 0), getattr(cache, "query_tokens", 0)
+        stats = engine.stats
+    finally:
+        tmp.cleanup()
+    return {"workload": args.workload, "impl": args.impl, "metric": "generated tok/s, all requests submitted at once",
+            "value": round(n_out / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3), "generated_tokens": n_out,
+            "prompt_tokens": sum(len(p) for p in prompts_), "requests": w["n"], "new_tokens": w["new"],
+            "preemptions": int(preempted), "prefix_hit_rate": round(hit / asked, 4) if asked else 0.0,
+            "steps": stats.get("steps"), "peak_running": stats.get("peak_running"),
+            "config": {"model": f"{MODEL_LABEL} sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
+                       "context": w["context"], "kv_page": PAGE, "kv_pool_mb": round(pool_mb, 1),
+                       "pool_share_of_need": w["pool_share"], **{k: v for k, v in w["engine"].items()}},
+            "dtype": "bf16", "data": "synthetic token ids, random weights seed 0"}
 
 
 def run_reference(args) -> dict:
@@ -372,12 +507,13 @@ def run_reference(args) -> dict:
         sampler = ClockSampler()
 
         def timed(batch, steps, warmup):
-            sp = SamplingParams(max_tokens=steps + warmup + 2, ignore_eos=True)
+            forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup)      # the timed steps: the middle of the new tokens
+            sp = SamplingParams(max_tokens=forward + steps + warmup + 4, ignore_eos=True)
             seqs = [engine.add_request(f"r-{batch}-{i}-{time.time_ns()}", p, sp)
                     for i, p in enumerate(prompts(batch, PROMPT_LEN, seed=99))]
             while any(s.num_output_tokens == 0 for s in seqs):
                 engine.step()
-            for _ in range(warmup):
+            for _ in range(forward + warmup):
                 engine.step()
             torch.cuda.synchronize()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -389,9 +525,11 @@ def run_reference(args) -> dict:
             end.record()
             torch.cuda.synchronize()
             dt = time.perf_counter() - t0
+            ctx = statistics.mean(s.length for s in seqs) - steps / 2
             for s in seqs:
                 engine.abort_request(s.id)
-            return {"tok_s_dev": n / (start.elapsed_time(end) / 1e3), "tok_s": n / dt, "ms": 1e3 * dt / steps}
+            return {"tok_s_dev": n / (start.elapsed_time(end) / 1e3), "tok_s": n / dt, "ms": 1e3 * dt / steps,
+                    "mean_ctx": ctx}
 
         timed(BATCH, 4, 3)
         sampler.start()
@@ -415,13 +553,14 @@ def run_reference(args) -> dict:
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random weights seed 0", "impl": "reference",
-        "config": {"model": f"{MODEL_LABEL} sizes", "layers": layers, "global_batch": BATCH, "prompt_len": PROMPT_LEN,
-                   "seq_len": CONTEXT, "kv_page": PAGE, "reference_flags": "paged engine, cuda_graphs=True, max batch 64",
-                   "parallelism": "single GPU"},
+        "config": bench_config(layers, main["mean_ctx"], {
+            "l2": "inputs larger than L2 (weights read per step: %.0f MB)" % (info["weight_bytes"] / 1e6),
+            "peaks": peaks()[1], "cuda_graphs": True}),
         "e2e": {"value": round(main["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": None,
                 "d2h_bytes_per_step": BATCH * 8},
         "prefill": {"value": round(PREFILL_TOKENS / (pf_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3)},
-        "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)},
+        "points": {"decode_b1": round(b1["tok_s_dev"], 1), "decode_b64": round(b64["tok_s_dev"], 1),
+                   "e2e_b1": round(b1["tok_s"], 1), "e2e_b64": round(b64["tok_s"], 1)},
         "clocks": clocks,
     }
 
@@ -437,6 +576,10 @@ def main() -> int:
     ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>' or 'products' and print its time")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--no-skip", action="store_true", help="profiling aid: time the decode steps right behind the prompt")
+    ap.add_argument("--no-fp32", action="store_true", help="leave out the float32 engine's points")
+    ap.add_argument("--workload", default="", choices=["", *WORKLOADS],
+                    help="run one of the other baseline workloads through LLMEngine instead of the headline bench")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
@@ -445,7 +588,10 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.sizes:
         use_sizes(args.sizes)
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload:
+        result = run_workload(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result:
         print(json.dumps(result), flush=True)
     return 0
