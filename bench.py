@@ -160,12 +160,18 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead:
     # The timed steps lie in the middle of the NEW_TOKENS new tokens; the steps before them run untimed.
     forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup) if skip_ahead else 0
 
+    greedy = runner.takes_greedy_steps(batch)      # the arg-max comes out of the output matrix's own kernel
+    chosen = torch.zeros(max(batch, 16), dtype=torch.int32, device=runner.device)
+
     def one():
         nonlocal length
         for h, _ in handles:
             cache.grow(h, length + 1)
-        logits = runner.step([StepEntry(h, [t], length, [0]) for (h, _), t in zip(handles, tok)])
-        ops.argmax(logits)
+        entries = [StepEntry(h, [t], length, [0]) for (h, _), t in zip(handles, tok)]
+        if greedy:
+            runner.step_greedy(entries, chosen)
+        else:
+            ops.argmax(runner.step(entries), out=chosen[:batch])
         length += 1
 
     for _ in range(forward + warmup):

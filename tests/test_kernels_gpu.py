@@ -524,6 +524,40 @@ def test_output_matrix_streaming_kernel(T, N, K):
     assert int(out[T - 1].argmax()) == N - 1
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 16])
+@pytest.mark.parametrize("N,K", [(1000, 896), (151, 64), (4099, 136), (151936, 896), (16, 32)])
+def test_output_matrix_kernel_finds_the_arg_max_in_its_epilogue(T, N, K):
+    """The same product with each token's arg-max taken in the epilogue, three calls in a row on the same
+    scratch (the arrival counter must end at zero): with and without the logits being written; equal logits
+    (exact ties) at several indices must give the lowest of them, in the same block and across blocks; one
+    token's winner is made to sit in the last, partly filled row group."""
+    from tokenmill_b200.kernels.fused import pack_rows
+    ops = _ops()
+    g = torch.Generator().manual_seed(N * 3 + T)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    if T > 1:
+        w[N - 1] = (x[T - 1].float() * 0.5).bfloat16()                  # the last row answers the last token
+    if N > 600:                                                          # identical rows: identical logits
+        w[17] = w[577] = w[N // 2 + 3] = (x[0].float() * 0.7).bfloat16()  # ... that win for token 0
+    packed = pack_rows(w.to(DEV))
+    logits = ops.lm_head(x.to(DEV), packed, N)
+    want = logits.argmax(-1).to(torch.int32)
+    if N > 600:
+        assert float(logits[0, 17]) == float(logits[0, 577]) == float(logits[0, N // 2 + 3]) and int(want[0]) == 17
+    if T > 1:
+        assert int(want[T - 1]) == N - 1
+    for call in range(3):
+        tokens = torch.full((16,), -7, dtype=torch.int32, device=DEV)
+        out = torch.full((T, N), float("nan"), device=DEV) if call == 1 else None
+        ops.lm_head_argmax(x.to(DEV), packed, N, tokens, logits=out)
+        ops.tc_check(torch.device(DEV))
+        assert torch.equal(tokens[:T], want), (call, tokens[:T].tolist(), want.tolist())
+        assert int((tokens[T:] == -7).sum()) == 16 - T
+        if out is not None:
+            assert torch.equal(out, logits)
+
+
 @pytest.mark.parametrize("T", [1, 8, 13, 16])
 @pytest.mark.parametrize("N,K", [(1536, 8960), (3584, 18944), (17920, 1536), (200, 1032), (24, 4104)])
 def test_streaming_product_with_a_cut_k_range(T, N, K):

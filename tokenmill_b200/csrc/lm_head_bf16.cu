@@ -41,7 +41,23 @@ struct LmHeadArgs {
   int slice_chunks;            // chunks of a slice (the last may have fewer)
   long long slice_stride;      // floats between two slices' outputs (T * N), 0 with one slice
   int* error;
+  // Arg-max in the epilogue (one slice only; all null when not asked for): every block keeps, per token, the
+  // largest of the logits it computed (the lowest index on ties) and writes it to best_val / best_idx
+  // [grid, 16]; the block that finishes last (arrival counter `done`, zero between launches) picks each
+  // token's winner over the blocks in index order and writes argmax_out [T].
+  int* argmax_out;
+  float* best_val;
+  int* best_idx;
+  int* done;
 };
+
+// (value, index) pairs: the larger value wins, the lower index on equal values (torch.argmax's rule).
+__device__ __forceinline__ void lh_better(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) {
+    v = ov;
+    i = oi;
+  }
+}
 
 template <int CPW>   // chunks of 32 k per warp
 __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs a) {
@@ -102,6 +118,8 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
     xhi[c][0] = hi.x; xhi[c][1] = hi.y; xhi[c][2] = hi.z; xhi[c][3] = hi.w;
   }
 
+  float best = -INFINITY;                    // this thread's largest logit so far (its token: (tid >> 3) & 15)
+  int best_n = 0x7fffffff;
   int it = 0;
   for (; it < my_stages; ++it) {
     const int slot = it % a.ring;
@@ -138,7 +156,60 @@ __global__ void __launch_bounds__(kLhThreads, 1) lm_head_kernel(const LmHeadArgs
     const float sum = ((p[0] + p[128]) + p[256]) + p[384];
     const int st = pair0 + it * pair_step;
     const int n = (2 * st + grp) * 8 + col;
-    if (tok < a.T && n < a.N) a.out[(size_t)slice * a.slice_stride + (size_t)tok * a.N + n] = sum;
+    if (tok < a.T && n < a.N) {
+      if (a.out) a.out[(size_t)slice * a.slice_stride + (size_t)tok * a.N + n] = sum;
+      if (sum > best) {                      // (n grows from stage to stage: the first of equal values stays)
+        best = sum;
+        best_n = n;
+      }
+    }
+  }
+  if (a.argmax_out && it == my_stages) {
+    // A token's 16 threads: 8 neighbouring lanes (the rows of a group) in each of two warps (the two groups).
+    __shared__ float s_val[2][16];
+    __shared__ int s_idx[2][16];
+    __shared__ int s_last;
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_n, o);
+      lh_better(best, best_n, ov, oi);
+    }
+    __syncthreads();
+    if ((tid & 7) == 0) {
+      s_val[tid >> 7][(tid >> 3) & 15] = best;
+      s_idx[tid >> 7][(tid >> 3) & 15] = best_n;
+    }
+    __syncthreads();
+    if (tid < 16) {
+      float v = s_val[0][tid];
+      int i = s_idx[0][tid];
+      lh_better(v, i, s_val[1][tid], s_idx[1][tid]);
+      a.best_val[(size_t)blockIdx.x * 16 + tid] = v;
+      a.best_idx[(size_t)blockIdx.x * 16 + tid] = i;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(a.done, 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      // 16 threads per token, each over every 16th block, then the lowest index among equal values again
+      // (the rule is symmetric, so the order in which pairs meet does not matter).
+      const int tok = tid >> 4, part = tid & 15;
+      float v = -INFINITY;
+      int i = 0x7fffffff;
+      for (int b = part; b < (int)gridDim.x; b += 16)
+        lh_better(v, i, __ldcg(a.best_val + (size_t)b * 16 + tok), __ldcg(a.best_idx + (size_t)b * 16 + tok));
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        lh_better(v, i, ov, oi);
+      }
+      if (part == 0 && tok < a.T) a.argmax_out[tok] = i;
+      if (tid == 0) *a.done = 0;
+    }
   }
   // After an abort: the copies still on their way into this block's shared memory are waited for (bounded)
   // before the block gives the memory up.
@@ -164,8 +235,17 @@ extern "C" int tm_stream_linear_slices(int K) {
 // slice s holds the sums over its part of the K range (the caller, or the norm kernel that follows, adds the
 // slices in index order). `error`: a device int that must be zero; a block whose wait runs out writes 21 there
 // instead of hanging.
+static int lh_launch(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error, int* argmax_out,
+                     float* best_val, int* best_idx, int* done, cudaStream_t stream);
+
 extern "C" int tm_stream_linear_bf16(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error,
                                      cudaStream_t stream) {
+  if (!out) return TM_ERR_UNSUPPORTED_SHAPE;
+  return lh_launch(x, w_packed, out, T, N, K, error, nullptr, nullptr, nullptr, nullptr, stream);
+}
+
+static int lh_launch(const void* x, const void* w_packed, float* out, int T, int N, int K, int* error, int* argmax_out,
+                     float* best_val, int* best_idx, int* done, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (T > 16 || K <= 0 || K % 8 || !error) return TM_ERR_UNSUPPORTED_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_packed)) & 15) return TM_ERR_UNSUPPORTED_SHAPE;
@@ -184,6 +264,8 @@ extern "C" int tm_stream_linear_bf16(const void* x, const void* w_packed, float*
   tmk::LmHeadArgs a{};
   a.x = (const __nv_bfloat16*)x; a.w = (const __nv_bfloat16*)w_packed; a.out = out;
   a.T = T; a.N = N; a.K = K; a.chunks = chunks; a.error = error;
+  a.argmax_out = argmax_out; a.best_val = best_val; a.best_idx = best_idx; a.done = done;
+  if (argmax_out && (n_slices != 1 || !best_val || !best_idx || !done)) return TM_ERR_UNSUPPORTED_SHAPE;
   a.n_slices = n_slices; a.slice_chunks = slice_chunks; a.slice_stride = n_slices > 1 ? (long long)T * N : 0;
   const int n_groups = (N + 7) / 8;
   a.n_stages_total = (n_groups + 1) / 2;
@@ -221,4 +303,15 @@ extern "C" int tm_lm_head_bf16(const void* x, const void* w_packed, float* out, 
                                cudaStream_t stream) {
   if (K > 1024) return TM_ERR_UNSUPPORTED_SHAPE;
   return tm_stream_linear_bf16(x, w_packed, out, T, N, K, error, stream);
+}
+
+// The same product with the arg-max of every token's logits found in the epilogue: tokens [T] int32 receives the
+// index of the largest logit (the lowest index on ties), so a greedy decode step neither writes nor re-reads
+// [T, N] logits (the reference computes logits.argmax(-1) as a separate pass, src/infer/sampling.py:30-33).
+// `logits` may be null (nothing is written) or [T, N] float32. Scratch: best_val, best_idx [148 * 16] (one row per
+// block; any number of blocks up to the device's SMs), done: one int that is zero (left zero).
+extern "C" int tm_lm_head_argmax_bf16(const void* x, const void* w_packed, float* logits, int* tokens, float* best_val,
+                                      int* best_idx, int* done, int T, int N, int K, int* error, cudaStream_t stream) {
+  if (K > 1024 || !tokens) return TM_ERR_UNSUPPORTED_SHAPE;
+  return lh_launch(x, w_packed, logits, T, N, K, error, tokens, best_val, best_idx, done, stream);
 }

@@ -237,13 +237,20 @@ class LLMEngine:
             else:
                 entries.append(StepEntry(req.cache, [0], it.start, [0]))
                 rows.append(prev.row_of[id(req)])
-        if prev is None:
-            logits = self.runner.step(entries)
+        if self.on_logits is None and all(r.params.greedy for r in reqs) and self.runner.takes_greedy_steps(len(entries)):
+            # Every request wants its most likely token and nobody looks at the logits: the output matrix's
+            # kernel finds the arg-max itself and no logits are written.
+            src = None if prev is None else prev.pending.dev
+            pending = self.sampler.launch_filled(
+                len(entries), lambda dev: self.runner.step_greedy(entries, dev, src, rows if prev is not None else None))
         else:
-            logits = self.runner.step_fed(entries, prev.pending.dev, rows)
-        self._tap([(it.req.id, it.start) for it in plan.items], logits)
-        pending = self.sampler.launch(logits, [r.params for r in reqs], [r.sample_seed for r in reqs],
-                                      [r.draws for r in reqs])
+            if prev is None:
+                logits = self.runner.step(entries)
+            else:
+                logits = self.runner.step_fed(entries, prev.pending.dev, rows)
+            self._tap([(it.req.id, it.start) for it in plan.items], logits)
+            pending = self.sampler.launch(logits, [r.params for r in reqs], [r.sample_seed for r in reqs],
+                                          [r.draws for r in reqs])
         index = []
         for it in plan.items:
             req = it.req

@@ -74,12 +74,14 @@ class ModelRunner:
             self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len)
             if self.fused.max_tokens == 0:          # not even one token fits beside a ring stage at these sizes
                 self.fused = None
-        # The output matrix of those steps is the library product. With TOKENMILL_LM_HEAD=1 this library's own
-        # streaming kernel takes it from a packed copy of the matrix (as much memory again); both run at the
-        # memory's read rate (50 us against 52 us for 272 MB), so the copy is not made by default.
+        # The output matrix of those steps goes through this library's own streaming kernel, from a packed copy of
+        # the matrix (as much memory again; hidden sizes up to 1024). It runs at the memory's read rate like the
+        # library's kernel (52 against 50 us for 272 MB), and it finds the arg-max of greedy rows in its epilogue,
+        # which saves writing and re-reading the logits and two launches (15 to 20 us a step). TOKENMILL_LM_HEAD=0
+        # keeps the library product and saves the copy.
         self._packed_output = None
         if self.fused is not None and ops.lm_head_ok(1, model.spec.hidden_size) and \
-                os.environ.get("TOKENMILL_LM_HEAD", "0") == "1":
+                os.environ.get("TOKENMILL_LM_HEAD", "1") != "0":
             self._packed_output = fused.pack_rows(model.output_weight)
         if self.graph_max_batch:
             if any(s < 0 for s in pools.sink) or (pools.state and pools.state_sink < 0):
@@ -176,6 +178,33 @@ class ModelRunner:
         if self._packed_output is not None and ops.lm_head_ok(hidden.shape[0], hidden.shape[1]):
             return ops.lm_head(hidden, self._packed_output, self.model.spec.vocab_size, error=self.fused.error)
         return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
+
+    def takes_greedy_steps(self, n_entries: int) -> bool:
+        """Whether ``step_greedy`` takes a decode step of this many requests."""
+        return (self.fused is not None and self._packed_output is not None and 0 < n_entries <= self.fused.max_tokens
+                and ops.lm_head_ok(n_entries, self.model.spec.hidden_size))
+
+    @torch.inference_mode()
+    def step_greedy(self, entries: list[StepEntry], out: torch.Tensor, token_src: torch.Tensor | None = None,
+                    token_rows: list[int] | None = None) -> None:
+        """A decode step (one token per entry) of which only each entry's most likely next token is wanted:
+        out[:n] (int32, on the device) receives the arg-max of entry i's logits, the lowest index on ties, and no
+        logits are written. With ``token_src`` the entries' tokens come from the device as in ``step_fed``. For
+        steps the whole-step kernel takes (``takes_greedy_steps``)."""
+        n = len(entries)
+        if not self.takes_greedy_steps(n) or any(len(e.tokens) != 1 for e in entries):
+            raise RuntimeError("this step cannot have its arg-max taken in the output matrix's epilogue")
+        for e in entries:
+            if e.start + 1 > self.max_model_len:
+                raise ValueError(f"a request would reach {e.start + 1} tokens; max_model_len is {self.max_model_len}")
+        self.stats["steps"] += 1
+        self.stats["tokens"] += n
+        self.stats["fused_steps"] += 1
+        ops.tc_poll(self.device)
+        self.fused.check()
+        hidden = self.fused.run_decode(entries, self.cache.page_size, token_src=token_src, token_rows=token_rows)
+        self.stats["h2d_bytes"] = self.fused.h2d_bytes
+        ops.lm_head_argmax(hidden, self._packed_output, self.model.spec.vocab_size, out, error=self.fused.error)
 
     def _step_program(self, n_tokens: int):
         """The model's step program with room for ``n_tokens`` (built on first need, rebuilt with a larger

@@ -104,6 +104,9 @@ def persistent_bytes(model) -> int:
         b = model.blocks[e.layer]
         total += sum(w.numel() * w.element_size() for w in (b.mixer.w_qkv, b.mixer.w_o, b.feed_forward.w_gate_up,
                                                             b.feed_forward.w_down))
+    from . import ops
+    if ops.lm_head_ok(1, model.spec.hidden_size) and os.environ.get("TOKENMILL_LM_HEAD", "1") != "0":
+        total += model.output_weight.numel() * model.output_weight.element_size()      # the output matrix's packed copy
     return total + (64 << 20)
 
 
@@ -220,11 +223,16 @@ class FusedDecoder:
         if getattr(self, "_ring", None) is None:
             width = -(-self.max_model_len // page_size)
             n = 7 * 16 + 4 + MAX_TOKENS * width          # seven sections of 16 (cu_q: 20) and the block table
+            # per slot: pinned buffer, device buffer, "copy has run" and "the kernel that read it has run" events
             self._ring = [(torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                           torch.zeros(n, dtype=torch.int32, device=self.device), torch.cuda.Event())
+                           torch.zeros(n, dtype=torch.int32, device=self.device), torch.cuda.Event(), torch.cuda.Event())
                           for _ in range(self._RING)]
-            self._ring_np = [h.numpy() for h, _, _ in self._ring]
+            self._ring_np = [h.numpy() for h, _, _, _ in self._ring]
             self._ring_at = 0
+            # The step's integers travel on a stream of their own, so that the copy runs beside the step before
+            # it instead of between two kernels; the error word goes back the same way behind the kernel.
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._launched = torch.cuda.Event()
         return self._ring
 
     def run_decode(self, entries, page_size: int, token_src: torch.Tensor | None = None,
@@ -238,7 +246,7 @@ class FusedDecoder:
         ring = self._decode_ring(page_size)
         k = self._ring_at
         self._ring_at = (k + 1) % self._RING
-        host, dev, copied = ring[k]
+        host, dev, copied, consumed = ring[k]
         copied.synchronize()                              # the copy that last read this pinned buffer is done
         buf = self._ring_np[k]
         S = len(entries)
@@ -270,8 +278,12 @@ class FusedDecoder:
         if token_src is not None:
             buf[o_rows:o_rows + S] = token_rows
         used = o_tab + S * width
-        dev[:used].copy_(host[:used], non_blocking=True)
-        copied.record()
+        main, side = torch.cuda.current_stream(self.device), self._copy_stream
+        side.wait_event(consumed)                         # (the kernel that read this slot four steps ago is through)
+        with torch.cuda.stream(side):
+            dev[:used].copy_(host[:used], non_blocking=True)
+            copied.record(side)
+        main.wait_event(copied)
         self.h2d_bytes = used * 4
         a, base = self._args, dev.data_ptr()
         a.token_ids, a.positions, a.slot_map = base + 4 * o_tok, base + 4 * o_pos, base + 4 * o_slot
@@ -287,7 +299,10 @@ class FusedDecoder:
         a.split_keys = self.split_for(S, max_kv)
         a.max_splits = -(-max_kv // a.split_keys)
         lib.call("tm_decode_fused", ctypes.addressof(a), ops_stream())
-        self._err_host.copy_(self.error, non_blocking=True)
+        consumed.record(main)
+        side.wait_event(consumed)
+        with torch.cuda.stream(side):
+            self._err_host.copy_(self.error, non_blocking=True)
         self.launches += 1
         return self.hidden[:S]
 

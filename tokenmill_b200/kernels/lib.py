@@ -56,6 +56,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_decode_fused_max_tokens": [_I, _I, _I, _I, _I, _I],
     "tm_lm_head_bf16": [_P, _P, _P, _I, _I, _I, _P, _P],
     "tm_stream_linear_bf16": [_P, _P, _P, _I, _I, _I, _P, _P],
+    "tm_lm_head_argmax_bf16": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P],
     "tm_stream_linear_slices": [_I],
     "tm_swiglu_partials": [_P, _I, _LL, _P, _I, _I, _P],
     "tm_gemm_f32_nt": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],

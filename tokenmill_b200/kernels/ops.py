@@ -395,6 +395,34 @@ def lm_head(x: torch.Tensor, w_packed: torch.Tensor, n_rows: int, error: torch.T
     return out
 
 
+_lm_head_scratch: dict[torch.device, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+
+
+def lm_head_argmax(x: torch.Tensor, w_packed: torch.Tensor, n_rows: int, tokens: torch.Tensor,
+                   logits: torch.Tensor | None = None, error: torch.Tensor | None = None) -> torch.Tensor:
+    """``lm_head`` with the arg-max found in its epilogue: tokens[:T] (int32, on the device) receives the index
+    of each token's largest logit, the lowest index on ties. ``logits`` [T, n_rows] float32 is written as well
+    when given; without it no logits reach memory at all."""
+    T, K = x.shape
+    if not lm_head_ok(T, K) or x.dtype != torch.bfloat16 or w_packed.dtype != torch.bfloat16:
+        raise lib.KernelError(f"lm_head_argmax: {T} tokens of {K} columns in {x.dtype} are not taken")
+    if w_packed.dim() != 5 or w_packed.shape[0] * 8 < n_rows or w_packed.shape[1] * 32 < K or not w_packed.is_contiguous():
+        raise lib.KernelError("lm_head_argmax: the packed matrix does not fit the sizes given")
+    if tokens.dtype != torch.int32 or tokens.numel() < T or (logits is not None and logits.shape != (T, n_rows)):
+        raise lib.KernelError("lm_head_argmax: tokens are int32 [T], logits float32 [T, rows]")
+    if x.device not in _lm_head_scratch:       # per-block winners (one row of 16 per block) and the arrival counter
+        n_blocks = torch.cuda.get_device_properties(x.device).multi_processor_count
+        _lm_head_scratch[x.device] = (torch.empty(n_blocks * 16, dtype=torch.float32, device=x.device),
+                                      torch.empty(n_blocks * 16, dtype=torch.int32, device=x.device),
+                                      torch.zeros(1, dtype=torch.int32, device=x.device))
+    best_val, best_idx, done = _lm_head_scratch[x.device]
+    lib.call("tm_lm_head_argmax_bf16", _req(x, "x", torch.bfloat16), w_packed.data_ptr(),
+             _opt(logits, "logits", torch.float32), _req(tokens, "tokens", torch.int32), best_val.data_ptr(),
+             best_idx.data_ptr(), done.data_ptr(), T, n_rows, K,
+             (error if error is not None else _tc_flag(x.device)).data_ptr(), _stream())
+    return tokens
+
+
 def stream_linear_ok(T: int, K: int) -> bool:
     """Whether the streaming kernel takes a product of T tokens over K columns (any number of rows)."""
     return 0 < T <= LM_HEAD_MAX_TOKENS and K % 8 == 0 and -(-K // 1024) <= 128

@@ -89,6 +89,15 @@ class Sampler:
         event.record()
         return PendingSample(dev, host, event, n)
 
+    def launch_filled(self, n: int, fill) -> PendingSample:
+        """As ``launch`` for a step whose tokens a kernel writes itself: ``fill(dev)`` is called with the int32
+        device array to write its n tokens into (the output matrix's arg-max epilogue does)."""
+        dev, host, event = self._slot(n)
+        fill(dev)
+        host[:n].copy_(dev[:n], non_blocking=True)
+        event.record()
+        return PendingSample(dev, host, event, n)
+
     def collect(self, pending: PendingSample) -> list[int]:
         pending.event.synchronize()
         return pending.host[:pending.n].tolist()
