@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_bf16_kernel(
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_last;
   pdl_launch_dependents();
-  pdl_wait();                                  // q and this step's keys and values come from the kernel before
+  // (The request's lengths and block table are the step's inputs, copied before its first kernel: they and the
+  // older keys and values may be read before the kernel in front of this one has finished.)
   const int s = blockIdx.x, kvh = blockIdx.y;
   const int q_start = cu_q[s], q_len = cu_q[s + 1] - q_start, before = kv_before[s];
   // What the host cannot check (the lengths live on the device): a request with more rows than a tile holds,
@@ -45,8 +46,11 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_bf16_kernel(
   const bool worked = decode_attention_unit<D>(q, kcache, vcache, block_table + (size_t)s * bt_stride, q_start, q_len,
                                                before, kvh, blockIdx.z, part_acc, part_ml, nh, nkv, page_size,
                                                scale_log2, window, split_keys, max_splits, smem, threadIdx.x,
-                                               [] { __syncthreads(); });
-  if (!worked) return;                         // no key of this request in this split (uniform over the block)
+                                               [] { __syncthreads(); }, [] { pdl_wait(); });
+  if (!worked) {                               // no key of this request in this split (uniform over the block)
+    pdl_wait();                                // (every kernel of the chain waits before it exits)
+    return;
+  }
   // How many splits hold keys for this (request, kv head): the last of them to finish merges all.
   const int G = nh / nkv;
   const int n_rows = min(q_len * G, 16);

@@ -1,7 +1,11 @@
 // The body of split-key decode attention for one (request, kv head, key split): 4 warps, 128 threads.
-// Shared by the stand-alone kernel (attention_decode_bf16.cu) and the fused decode-step kernel
-// (decode_fused_bf16.cu), which differ only in how the 128 threads synchronise and where their shared
-// memory lies. See attention_decode_bf16.cu for the method. Returns false when the unit has no keys.
+// See attention_decode_bf16.cu for the method. Returns false when the unit has no keys.
+//
+// `wait_for_step` is called once, before the unit touches anything the kernel in front of it on the stream
+// wrote: the queries, and the keys and values of the step's own tokens (positions >= `before`). Keys and
+// values of older positions were written by earlier steps, so their copies are asked for BEFORE that call:
+// launched with programmatic dependent launch, the kernel gets its table lookups and most of its data on
+// the way while the kernel in front of it is still running.
 #pragma once
 
 #include "mma_util.cuh"
@@ -17,12 +21,13 @@ template <int D> constexpr int decode_unit_smem_bytes() {
                                                                      : (kDecWarps * 16 * (D + 2) * 4);
 }
 
-template <int D, typename Sync>
+template <int D, typename Sync, typename Wait>
 __device__ __forceinline__ bool decode_attention_unit(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ table, int q_start, int q_len, int before,
     int kvh, int z, float* __restrict__ part_acc, float* __restrict__ part_ml, int nh, int nkv, int page_size,
-    float scale_log2, int window, int split_keys, int max_splits, unsigned char* smem, int tid, Sync sync) {
+    float scale_log2, int window, int split_keys, int max_splits, unsigned char* smem, int tid, Sync sync,
+    Wait wait_for_step) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int KS = D / 16;                // k-steps of the score product
   constexpr int NT = D / 8;                 // 8-wide output tiles
@@ -43,22 +48,7 @@ __device__ __forceinline__ bool decode_attention_unit(
   const int r0 = lane >> 2, r1 = r0 + 8;    // the two tile rows this thread's accumulators belong to
   const int cpair = (lane & 3) * 2;
 
-  // Query fragments straight from global memory (rows beyond n_rows are zero).
   uint32_t qa[KS][4];
-  {
-    const __nv_bfloat16* qr0 = nullptr;
-    const __nv_bfloat16* qr1 = nullptr;
-    if (r0 < n_rows) qr0 = q + ((size_t)(q_start + r0 / G) * nh + kvh * G + r0 % G) * D;
-    if (r1 < n_rows) qr1 = q + ((size_t)(q_start + r1 / G) * nh + kvh * G + r1 % G) * D;
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      const int c = ks * 16 + cpair;
-      qa[ks][0] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c)) : 0u;
-      qa[ks][1] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c)) : 0u;
-      qa[ks][2] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c + 8)) : 0u;
-      qa[ks][3] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c + 8)) : 0u;
-    }
-  }
   const int p_r0 = r0 < n_rows ? before + r0 / G : -1, p_r1 = r1 < n_rows ? before + r1 / G : -1;
   const int lo_r0 = window > 0 ? max(0, p_r0 - window + 1) : 0, lo_r1 = window > 0 ? max(0, p_r1 - window + 1) : 0;
 
@@ -87,14 +77,44 @@ __device__ __forceinline__ bool decode_attention_unit(
     }
   };
 
-  load_block(0, kb_first);
-  cp_async_commit();
+  // Block k of the unit into stage k & 1. A block that holds keys of the step's own tokens has to wait for the
+  // kernel that wrote them; all the others are asked for at once.
+  bool waited = false;
+  auto issue = [&](int k) {
+    const int kb = kb_first + k * kDecBN;
+    if (!waited && kb + kDecBN > before) {
+      wait_for_step();
+      waited = true;
+    }
+    load_block(k & 1, kb);
+    cp_async_commit();
+  };
+  issue(0);
+  if (n_blocks > 1) issue(1);
+  if (!waited) {
+    wait_for_step();
+    waited = true;
+  }
+  // Query fragments straight from global memory (rows beyond n_rows are zero).
+  {
+    const __nv_bfloat16* qr0 = nullptr;
+    const __nv_bfloat16* qr1 = nullptr;
+    if (r0 < n_rows) qr0 = q + ((size_t)(q_start + r0 / G) * nh + kvh * G + r0 % G) * D;
+    if (r1 < n_rows) qr1 = q + ((size_t)(q_start + r1 / G) * nh + kvh * G + r1 % G) * D;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int c = ks * 16 + cpair;
+      qa[ks][0] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c)) : 0u;
+      qa[ks][1] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c)) : 0u;
+      qa[ks][2] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c + 8)) : 0u;
+      qa[ks][3] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c + 8)) : 0u;
+    }
+  }
   for (int b = 0; b < n_blocks; ++b) {
     const int kb = kb_first + b * kDecBN;
     const int stage = b & 1;
+    if (b >= 1 && b + 1 < n_blocks) issue(b + 1);      // (its stage was given back at the end of the last trip)
     if (b + 1 < n_blocks) {
-      load_block(stage ^ 1, kb + kDecBN);
-      cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();

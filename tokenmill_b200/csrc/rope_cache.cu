@@ -33,6 +33,7 @@ __global__ void qkv_rope_write_kernel(const TIn* __restrict__ qkv, const float* 
                                       const float* __restrict__ sin_t, const int* __restrict__ slot_map,
                                       T* __restrict__ q_out, T* __restrict__ kcache, T* __restrict__ vcache,
                                       int nh, int nkv, int D, int n_pos, int* __restrict__ error) {
+  pdl_launch_dependents();                     // (the kernel behind this one may start its own preparations)
   const int t = blockIdx.x;
   const int half = D >> 1;
   const int heads = nh + 2 * nkv;
@@ -75,6 +76,7 @@ __global__ void qkv_rope_write_vec_kernel(const TIn* __restrict__ qkv, const flo
                                           const float* __restrict__ sin_t, const int* __restrict__ slot_map,
                                           T* __restrict__ q_out, T* __restrict__ kcache, T* __restrict__ vcache,
                                           int nh, int nkv, int D, int n_pos, int* __restrict__ error) {
+  pdl_launch_dependents();                     // (the kernel behind this one may start its own preparations)
   const int t = blockIdx.x;
   const int half = D >> 1, quads = half >> 2;
   const int heads = nh + 2 * nkv;
