@@ -314,7 +314,7 @@ def test_prompt_products_on_tcgen05_when_switched_on(tmp_path, monkeypatch, plai
                        num_attention_heads=2, num_key_value_heads=1, rope_theta=10000.0, tie_word_embeddings=False,
                        max_position_embeddings=1024)
     folder = write_random_model(tmp_path / "m", cfg, seed=5)
-    monkeypatch.setattr(ops, "_TC_ENABLED", True)
+    monkeypatch.setattr(ops, "_TC_MODE", "1")
     calls = []
     real = lib.call
     monkeypatch.setattr(lib, "call", lambda name, *a: (calls.append(name), real(name, *a))[1])
@@ -327,6 +327,30 @@ def test_prompt_products_on_tcgen05_when_switched_on(tmp_path, monkeypatch, plai
     outputs = run_trace(folder, "bfloat16", steps, 512, tmp_path / "o")
     check_against_plain(steps, outputs, reqs, plain_for(folder, reqs, plain_cache), "bfloat16")
     assert {"tm_tc_qkv_rope_write", "tm_tc_gate_up_swiglu", "tm_tc_linear"} <= set(calls)
+
+
+def test_fused_qkv_and_narrow_products_on_tcgen05_inside_step_programs(d64_dir, tmp_path, monkeypatch, plain_cache):
+    """TOKENMILL_TC_GEMM=qkv: in prompt steps long enough, the q/k/v projection runs as one tcgen05 kernel with bias,
+    rotation and cache write in its epilogue (tiles of 128 columns: one wave) and the output projection on the same
+    kernel, both as launches of the step program; shorter steps of the same program keep the library products. The
+    logits are the plain implementation's, and decoding afterwards reads the keys that epilogue wrote."""
+    from tokenmill_b200.kernels import ops, program
+    monkeypatch.setattr(ops, "_TC_MODE", "qkv")
+    vocab = json.loads((Path(d64_dir) / "config.json").read_text())["vocab_size"]
+    reqs = make_requests(vocab, [1130, 420], seed=8)
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": reqs["r0"][:1100], "want": list(range(0, 1100, 37))}], "end": []},
+             {"step": 1, "entries": [{"id": "r1", "tokens": reqs["r1"][:400], "want": [0, 399]},
+                                     {"id": "r0", "tokens": reqs["r0"][1100:1110], "want": list(range(10))}], "end": []},
+             {"step": 2, "entries": [{"id": "r0", "tokens": reqs["r0"][1110:], "want": list(range(20))},
+                                     {"id": "r1", "tokens": reqs["r1"][400:], "want": list(range(20))}], "end": ["r0", "r1"]}]
+    before = program.kind_launches()
+    outputs = run_trace(d64_dir, "bfloat16", steps, 2048, tmp_path / "o")
+    after = program.kind_launches()
+    check_against_plain(steps, outputs, reqs, plain_for(d64_dir, reqs, plain_cache), "bfloat16")
+    took = {k: after[k] - before[k] for k in after}
+    # 3 layers: step 0 (1,100 tokens) takes both tcgen05 launches, step 1 (410 tokens) the fused projection only,
+    # step 2 (40 tokens) neither
+    assert took["tc_qkv_rope_write"] == 6 and took["tc_linear"] == 3 and took["qkv_rope_write"] == 3
 
 
 @pytest.mark.parametrize("mode", ["tail", "mixed", "many", "tail-whole", "mixed-whole", "long-whole"])

@@ -23,10 +23,14 @@
 
 namespace tmk {
 
-constexpr int kT5BM = 128, kT5BN = 256, kT5BK = 64, kT5Stages = 4;
+// The tile is 128 tokens by BN weight rows: 256 where the projection has many tiles (gate/up, down, o_proj), 128
+// where 256 would leave most SMs without a tile (the q/k/v projection of a 2,048-token prompt at 14 + 2 x 2
+// heads of 64 has 80 tiles of 256 columns and 144 of 128: one wave that fills the chip).
+constexpr int kT5BM = 128, kT5BK = 64;
 constexpr int kT5ABytes = kT5BM * kT5BK * 2;            // 16 KB
-constexpr int kT5BBytes = kT5BN * kT5BK * 2;            // 32 KB
-constexpr int kT5StageBytes = kT5ABytes + kT5BBytes;    // 48 KB
+template <int BN> constexpr int t5_b_bytes() { return BN * kT5BK * 2; }                       // 32 or 16 KB
+template <int BN> constexpr int t5_stage_bytes() { return kT5ABytes + t5_b_bytes<BN>(); }     // 48 or 32 KB
+template <int BN> constexpr int t5_stages() { return BN == 256 ? 4 : 6; }
 constexpr int kT5Threads = 256;
 enum : int { T5_STORE = 0, T5_SWIGLU = 1, T5_QKV = 2 };
 
@@ -64,20 +68,23 @@ __device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) 
   *reinterpret_cast<uint4*>(dst) = o;
 }
 
-// First weight row of each 128-row half of tile column `tn`.
+// First weight row of each 128-row half of tile column `tn` (a tile of 128 columns has only the first).
+template <int BN>
 __device__ __forceinline__ void t5_tile_rows(const T5Args& a, int tn, int& row_lo, int& row_hi) {
   if (a.mode == T5_SWIGLU) {
     row_lo = tn * 128;              // gate rows
     row_hi = a.inter + tn * 128;    // the matching up rows
   } else {
-    row_lo = tn * kT5BN;
+    row_lo = tn * BN;
     row_hi = row_lo + 128;
   }
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                      const __grid_constant__ CUtensorMap map_w,
                                                                      const T5Args a) {
+  constexpr int kT5BN = BN, kT5Stages = t5_stages<BN>(), kT5BBytes = t5_b_bytes<BN>(), kT5StageBytes = t5_stage_bytes<BN>();
   extern __shared__ __align__(1024) unsigned char t5_smem_raw[];
   // The dynamic region is used from the next 1024-byte boundary (the swizzle pattern repeats every 1024 B).
   const uint32_t ring = (t5_smem(t5_smem_raw) + 1023u) & ~1023u;
@@ -123,7 +130,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       const int tn = tile / a.n_tiles_m, tm = tile - tn * a.n_tiles_m;
       int row_lo, row_hi;
-      t5_tile_rows(a, tn, row_lo, row_hi);
+      t5_tile_rows<BN>(a, tn, row_lo, row_hi);
       for (int kb = 0; kb < n_kb && ok; ++kb) {
         ok = mbar_wait(empty_bar(stage), phase ^ 1u, &s_abort, a.error, 1);
         if (!ok) break;
@@ -131,7 +138,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
         mbar_expect_tx(full_bar(stage), kT5StageBytes);
         tma_load_2d(dst, &map_x, kb * kT5BK, tm * kT5BM, full_bar(stage));
         tma_load_2d(dst + kT5ABytes, &map_w, kb * kT5BK, row_lo, full_bar(stage));
-        tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, kb * kT5BK, row_hi, full_bar(stage));
+        if (BN == 256) tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, kb * kT5BK, row_hi, full_bar(stage));
         if (++stage == kT5Stages) {
           stage = 0;
           phase ^= 1u;
@@ -140,7 +147,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
-    // Instruction descriptor: D float32, A and B bfloat16, both K-major, N = 256, M = 128.
+    // Instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128.
     constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kT5BN >> 3) << 17) |
                                ((uint32_t)(kT5BM >> 4) << 24);
     int stage = 0;
@@ -336,6 +343,17 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static int t5_sm_count() {
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n_sm;
+}
+
+template <int BN>
 static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream_t stream) {
   if (a.T <= 0) return 0;
   if (a.K % 8 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -344,22 +362,17 @@ static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, x, a.T, a.K, ldx) || !make_map(&map_w, w, a.N, a.K, a.K)) return 90006;
   a.n_tiles_m = (a.T + kT5BM - 1) / kT5BM;
-  static int n_sm = 0;
-  if (!n_sm) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-  }
-  const int smem = kT5Stages * kT5StageBytes + 1024;
+  const int n_sm = t5_sm_count();
+  const int smem = t5_stages<BN>() * t5_stage_bytes<BN>() + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   const int tiles = a.n_tiles_m * a.n_tiles_n;
   const int grid = tiles < n_sm ? tiles : n_sm;
-  gemm_tcgen05_kernel<<<grid, kT5Threads, smem, stream>>>(map_x, map_w, a);
+  gemm_tcgen05_kernel<BN><<<grid, kT5Threads, smem, stream>>>(map_x, map_w, a);
   return launch_status();
 }
 
@@ -371,10 +384,15 @@ extern "C" int tm_tc_linear(const void* x, int ldx, const void* w, void* out, in
                             int* error, cudaStream_t stream) {
   tmk::T5Args a{};
   a.T = T; a.N = N; a.K = K; a.mode = tmk::T5_STORE;
-  a.n_tiles_n = (N + tmk::kT5BN - 1) / tmk::kT5BN;
   a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.error = error;
   if (ldo % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return TM_ERR_UNSUPPORTED_SHAPE;
-  return tmk::t5_launch(a, x, ldx, w, stream);
+  // Tiles of 128 columns while tiles of 256 would not fill the chip once (a narrow projection such as o_proj).
+  if (((T + tmk::kT5BM - 1) / tmk::kT5BM) * ((N + 255) / 256) < tmk::t5_sm_count()) {
+    a.n_tiles_n = (N + 127) / 128;
+    return tmk::t5_launch<128>(a, x, ldx, w, stream);
+  }
+  a.n_tiles_n = (N + 255) / 256;
+  return tmk::t5_launch<256>(a, x, ldx, w, stream);
 }
 
 // out [T, I] = silu(x . gate^T) * (x . up^T); w [2 I, K] with the gate rows first; I a multiple of 8.
@@ -385,7 +403,7 @@ extern "C" int tm_tc_gate_up_swiglu(const void* x, int ldx, const void* w, void*
   a.n_tiles_n = (inter + 127) / 128;
   a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.error = error;
   if (ldo % 8 || inter % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return TM_ERR_UNSUPPORTED_SHAPE;
-  return tmk::t5_launch(a, x, ldx, w, stream);
+  return tmk::t5_launch<256>(a, x, ldx, w, stream);
 }
 
 // Fused q/k/v projection with bias, rotate-half position encoding and cache write (see rope_cache.cu for the
@@ -397,9 +415,15 @@ extern "C" int tm_tc_qkv_rope_write(const void* x, int ldx, const void* w, const
   if (D != 64 && D != 128 && D != 256) return TM_ERR_UNSUPPORTED_SHAPE;
   tmk::T5Args a{};
   a.T = T; a.N = (nh + 2 * nkv) * D; a.K = K; a.mode = tmk::T5_QKV;
-  a.n_tiles_n = (a.N + tmk::kT5BN - 1) / tmk::kT5BN;
   a.bias = bias; a.positions = positions; a.cos_t = cos_t; a.sin_t = sin_t; a.slot_map = slot_map;
   a.q_out = (__nv_bfloat16*)q_out; a.kcache = (__nv_bfloat16*)kcache; a.vcache = (__nv_bfloat16*)vcache;
   a.nh = nh; a.nkv = nkv; a.D = D; a.n_pos = n_pos; a.error = error;
-  return tmk::t5_launch(a, x, ldx, w, stream);
+  // Tiles of 128 columns (whole heads of 64 or 128) while tiles of 256 would not fill the chip once.
+  const int tiles_m = (T + tmk::kT5BM - 1) / tmk::kT5BM;
+  if (D <= 128 && tiles_m * ((a.N + 255) / 256) < tmk::t5_sm_count()) {
+    a.n_tiles_n = (a.N + 127) / 128;
+    return tmk::t5_launch<128>(a, x, ldx, w, stream);
+  }
+  a.n_tiles_n = (a.N + 255) / 256;
+  return tmk::t5_launch<256>(a, x, ldx, w, stream);
 }

@@ -29,6 +29,11 @@ int tm_qkv_rope_write(int in_dtype, int dtype, const void* qkv, const float* bia
                       const float* cos_t, const float* sin_t, const int* slot_map, void* q_out, void* kcache,
                       void* vcache, int T, int nh, int nkv, int D, int n_pos, int* error, cudaStream_t stream);
 int tm_swiglu(int dtype, const void* gu, void* out, int T, int I, cudaStream_t stream);
+int tm_tc_linear(const void* x, int ldx, const void* w, void* out, int ldo, int T, int N, int K, int* error,
+                 cudaStream_t stream);
+int tm_tc_qkv_rope_write(const void* x, int ldx, const void* w, const float* bias, const int* positions,
+                         const float* cos_t, const float* sin_t, const int* slot_map, void* q_out, void* kcache,
+                         void* vcache, int T, int K, int nh, int nkv, int D, int n_pos, int* error, cudaStream_t stream);
 int tm_prefill_attention_tc_bf16(const void* q, const void* kcache, const void* vcache, const int* block_table,
                                  int bt_stride, const int* unit_rec, int n_units, int chunk_keys, float* part_acc,
                                  float* part_ml, int* tile_done, int* counters, void* out, int nh, int nkv, int D,
@@ -56,7 +61,10 @@ enum ProgramOpKind : int32_t {
   kOpPrefillAttention = 5,
   kOpDecodeAttention = 6,
   kOpSwiglu = 7,
+  kOpTcQkvRopeWrite = 8,
+  kOpTcLinear = 9,
 };
+constexpr int kOpKinds = 16;
 
 constexpr int kProgramArgs = 24;
 
@@ -131,10 +139,10 @@ static inline float as_float(int64_t v) {
 }
 template <typename T> static inline T* as_ptr(int64_t v) { return reinterpret_cast<T*>(static_cast<uintptr_t>(v)); }
 
-static long long g_kind_launches[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // launches issued per kind since the library was loaded
+static long long g_kind_launches[kOpKinds] = {};   // launches issued per kind since the library was loaded
 
 static int run_op(const ProgramOp& op, const int64_t* a, cudaStream_t s) {
-  if (op.kind > 0 && op.kind < 8) ++g_kind_launches[op.kind];
+  if (op.kind > 0 && op.kind < kOpKinds) ++g_kind_launches[op.kind];
   switch (op.kind) {
     case kOpAddRmsNorm:   // dtype, resid, branch, ids, table, rows, weight, eps, out, n_rows, H
       if (op.n_args != 11) return TM_ERR_PROGRAM;
@@ -178,6 +186,16 @@ static int run_op(const ProgramOp& op, const int64_t* a, cudaStream_t s) {
     case kOpSwiglu:       // dtype, gu, out, T, I
       if (op.n_args != 5) return TM_ERR_PROGRAM;
       return tm_swiglu((int)a[0], as_ptr<const void>(a[1]), as_ptr<void>(a[2]), (int)a[3], (int)a[4], s);
+    case kOpTcQkvRopeWrite:  // x, ldx, w, bias, positions, cos, sin, slot_map, q_out, kcache, vcache, T, K, nh, nkv, D, n_pos, error
+      if (op.n_args != 18) return TM_ERR_PROGRAM;
+      return tm_tc_qkv_rope_write(as_ptr<const void>(a[0]), (int)a[1], as_ptr<const void>(a[2]), as_ptr<const float>(a[3]),
+                                  as_ptr<const int>(a[4]), as_ptr<const float>(a[5]), as_ptr<const float>(a[6]),
+                                  as_ptr<const int>(a[7]), as_ptr<void>(a[8]), as_ptr<void>(a[9]), as_ptr<void>(a[10]),
+                                  (int)a[11], (int)a[12], (int)a[13], (int)a[14], (int)a[15], (int)a[16], as_ptr<int>(a[17]), s);
+    case kOpTcLinear:     // x, ldx, w, out, ldo, T, N, K, error
+      if (op.n_args != 9) return TM_ERR_PROGRAM;
+      return tm_tc_linear(as_ptr<const void>(a[0]), (int)a[1], as_ptr<const void>(a[2]), as_ptr<void>(a[3]), (int)a[4],
+                          (int)a[5], (int)a[6], (int)a[7], as_ptr<int>(a[8]), s);
     default:
       return TM_ERR_PROGRAM;
   }
@@ -193,10 +211,10 @@ extern "C" int tm_program_setup(void* workspace, long long workspace_bytes) {
   return tmk::cublas_setup(workspace, (size_t)workspace_bytes);
 }
 
-// How many launches of each kind (index = kind, 8 values) programs have issued in this process: lets a caller
+// How many launches of each kind (index = kind, 16 values) programs have issued in this process: lets a caller
 // check which kernels a step took.
 extern "C" int tm_program_kind_launches(long long* out) {
-  for (int i = 0; i < 8; ++i) out[i] = tmk::g_kind_launches[i];
+  for (int i = 0; i < tmk::kOpKinds; ++i) out[i] = tmk::g_kind_launches[i];
   return 0;
 }
 

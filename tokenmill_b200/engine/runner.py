@@ -210,7 +210,7 @@ class ModelRunner:
         """The model's step program with room for ``n_tokens`` (built on first need, rebuilt with a larger
         workspace when a step outgrows it), or None where there is none."""
         if self._no_program or n_tokens < self._program_min_tokens or ops.tc_gemm_enabled():
-            return None
+            return None      # (with every prompt product on the tcgen05 kernels the parts' forward methods run)
         if self._program is None or self._program.capacity < n_tokens:
             capacity = max(256, 1 << (n_tokens - 1).bit_length())
             self._program = self.model.program(self.layer_caches, capacity)

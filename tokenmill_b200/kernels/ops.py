@@ -483,15 +483,41 @@ def skinny_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.T
 # --- prompt-step products on tcgen05 tensor cores (bfloat16) ------------------------------------------
 
 TC_MIN_TOKENS = 128                # below this the 128-token tiles are mostly padding
-# Off unless TOKENMILL_TC_GEMM=1: with one SM per tile the kernel is bound by L2-to-shared-memory traffic and
-# the library's two-SM tiles are faster at these sizes, so prompt products go to the library by default.
-_TC_ENABLED = os.environ.get("TOKENMILL_TC_GEMM", "0") == "1"
+# Which prompt-step products run on this library's tcgen05 kernels (TOKENMILL_TC_GEMM): "0" (default) none: they
+# go to the library product, as in the reference; "qkv": the q/k/v projection with bias, rotation and cache write in
+# its epilogue, and narrow plain products (o_proj), both while tiles of 128 columns fill the chip in one wave; "1"
+# every prompt product. Measured inside the prompt step at the 0.5B layer sizes (24 layers, 2,048 tokens): 3.83 ms
+# with "0", 4.07 ms with "qkv" (at 512 tokens 2.16 against 2.45 ms; 1.5B sizes, 8 layers: 2.69 against 2.90 ms):
+# one wave of tiles with its epilogue exposed, two tensor maps encoded per launch and the kernel's set-up cost more
+# than the rotary kernel and the launch they save, so the default stays with the library. (A loop of Python-driven
+# launches shows the opposite, 21 against 34 us, because there the library path pays two interpreter round trips.)
+_TC_MODE = os.environ.get("TOKENMILL_TC_GEMM", "0")
+if _TC_MODE == "auto":
+    _TC_MODE = "qkv"
+if _TC_MODE not in ("qkv", "0", "1"):
+    _TC_MODE = "0"
+TC_QKV_MIN_TOKENS = 384            # fused q/k/v projection: tokens from which it beats library product + rotary kernel
+TC_NARROW_MIN_TOKENS = 1024        # plain narrow product: tokens from which it beats the library product
 _tc_error: dict[torch.device, torch.Tensor] = {}
+_sm_count: dict[int, int] = {}
 
 
 def tc_gemm_enabled() -> bool:
-    """Whether prompt-step products go to the tcgen05 kernels (TOKENMILL_TC_GEMM=1) instead of the library."""
-    return _TC_ENABLED
+    """Whether EVERY prompt-step product goes to the tcgen05 kernels (TOKENMILL_TC_GEMM=1)."""
+    return _TC_MODE == "1"
+
+
+def _sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def tc_one_wave(T: int, N: int, device: torch.device) -> bool:
+    """Whether the tcgen05 kernel takes the product in tiles of 128 columns that fill the chip in one wave (it does
+    so while tiles of 256 columns would leave SMs without a tile)."""
+    return -(-T // 128) * -(-N // 256) < _sms(device)
 
 
 def _tc_flag(device: torch.device) -> torch.Tensor:
@@ -545,12 +571,30 @@ def tc_check(device: torch.device) -> None:
                                   f"its results are incomplete")
 
 
-def tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 kernels take this product: switched on (TOKENMILL_TC_GEMM=1), bfloat16, a
-    prompt-sized batch, 16-byte aligned rows."""
-    return (_TC_ENABLED and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
+def _tc_operands_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
             and x.shape[0] >= TC_MIN_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0)
+
+
+def tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether a wide prompt product (gate/up, down) goes to the tcgen05 kernels: only with TOKENMILL_TC_GEMM=1."""
+    return _TC_MODE == "1" and _tc_operands_ok(x, w)
+
+
+def tc_qkv_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the q/k/v projection of a prompt step runs as ONE tcgen05 kernel with bias, rotation and cache write
+    in its epilogue (else: library product, then the rotary kernel)."""
+    if _TC_MODE == "0" or not _tc_operands_ok(x, w):
+        return False
+    return _TC_MODE == "1" or (x.shape[0] >= TC_QKV_MIN_TOKENS and tc_one_wave(x.shape[0], w.shape[0], x.device))
+
+
+def tc_narrow_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether a plain narrow prompt product (o_proj) runs on the tcgen05 kernel."""
+    if _TC_MODE == "0" or not _tc_operands_ok(x, w):
+        return False
+    return _TC_MODE == "1" or (x.shape[0] >= TC_NARROW_MIN_TOKENS and tc_one_wave(x.shape[0], w.shape[0], x.device))
 
 
 def tc_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -161,7 +161,7 @@ class GroupedQueryAttention:
             # decode step: one kernel streams the fused weight and finishes bias, rotation and cache write
             ops.skinny_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
                                       kc, vc, self.nh, self.nkv, self.D)
-        elif rotary and self.D in (64, 128, 256) and ops.tc_ok(x, self.w_qkv):
+        elif rotary and self.D in (64, 128, 256) and ops.tc_qkv_ok(x, self.w_qkv):
             # prompt step: the tcgen05 kernel keeps the product in tensor memory and finishes it the same way
             ops.tc_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
                                   kc, vc, self.nh, self.nkv, self.D)
@@ -184,6 +184,8 @@ class GroupedQueryAttention:
         flat = out.view(T, self.q_size)
         if ops.skinny_ok(flat, self.w_o, allow_split=True):
             return ops.skinny_linear(flat, self.w_o, k_splits=ops.skinny_k_splits(T, self.q_size))
+        if ops.tc_narrow_ok(flat, self.w_o):
+            return ops.tc_linear(flat, self.w_o)
         return ops.linear(flat, self.w_o)
 
     def emit(self, b, x, cache: LayerCache):
@@ -192,7 +194,7 @@ class GroupedQueryAttention:
         output buffer. The attention kernel is chosen per step as in ``attend``: all candidates are in the
         program, each under a step parameter that says whether it runs."""
         from ..kernels.program import (OP_DECODE_ATTENTION, OP_GEMM_BF16, OP_PREFILL_ATTENTION, OP_PREFILL_ATTENTION_TC,
-                                       OP_QKV_ROPE_WRITE, Float)
+                                       OP_QKV_ROPE_WRITE, OP_TC_LINEAR, OP_TC_QKV_ROPE_WRITE, Float)
         if not self.fast or self.cos is None:
             raise NotImplementedError("step programs are built for bfloat16 rotary attention with heads of 64 or 128")
         T, g, G, nh, nkv, D = b.tokens(), cache.group, self.nh // self.nkv, self.nh, self.nkv, self.D
@@ -205,9 +207,21 @@ class GroupedQueryAttention:
         positions = b.param("positions", lambda s: s.positions.data_ptr())
         slot_map = b.param(f"slot_map{g}", lambda s: s.slot_maps[g].data_ptr()) if cache.writes else None
         kc, vc = (cache.k, cache.v) if cache.writes else (None, None)
-        b.emit(OP_GEMM_BF16, [x, self.w_qkv, qkv, T, n_qkv, self.hidden_size, 0])
+        # The projection: ONE tcgen05 kernel with bias, rotation and cache write in its epilogue where that wins (see
+        # ops.tc_qkv_ok: prompts long enough, tiles that fill the chip in one wave), else the library product and
+        # the rotary kernel behind it. Both are in the program; a step parameter says which runs.
+        H = self.hidden_size
+        err = ops.tc_error_word(self.device)
+        fused_qkv = (lambda s: int(ops._TC_MODE != "0" and s.n_tokens >= ops.TC_MIN_TOKENS and H % 8 == 0 and
+                                   (ops._TC_MODE == "1" or (s.n_tokens >= ops.TC_QKV_MIN_TOKENS and
+                                                            ops.tc_one_wave(s.n_tokens, n_qkv, self.device)))))
+        use_tc = b.param(f"tc_qkv_{n_qkv}_{H}", fused_qkv)
+        use_lib = b.param(f"lib_qkv_{n_qkv}_{H}", lambda s: 1 - fused_qkv(s))
+        b.emit(OP_TC_QKV_ROPE_WRITE, [x, H, self.w_qkv, self.b_qkv, positions, self.cos, self.sin, slot_map, q, kc, vc, T,
+                                      H, nh, nkv, D, self.cos.shape[0], err], cond=use_tc)
+        b.emit(OP_GEMM_BF16, [x, self.w_qkv, qkv, T, n_qkv, H, 0], cond=use_lib)
         b.emit(OP_QKV_ROPE_WRITE, [code, code, qkv, self.b_qkv, positions, self.cos, self.sin, slot_map, q, kc, vc, T,
-                                   nh, nkv, D, self.cos.shape[0], ops.tc_error_word(self.device)])
+                                   nh, nkv, D, self.cos.shape[0], err], cond=use_lib)
 
         mkey = self.metadata_key()
         meta = lambda s: s.meta[mkey]                                   # noqa: E731
@@ -258,7 +272,13 @@ class GroupedQueryAttention:
                cond=b.param(f"attention_prefill_tc_{key}", lambda s: int(path(s) == "prefill_tc")))
         b.emit(OP_PREFILL_ATTENTION, common,
                cond=b.param(f"attention_prefill_{key}", lambda s: int(path(s) == "prefill")))
-        b.emit(OP_GEMM_BF16, [out, self.w_o, branch, T, self.hidden_size, self.q_size, 0])
+        # The output projection: a narrow product, on the tcgen05 kernel where its 128-column tiles fill the chip.
+        qs = self.q_size
+        tc_o = (lambda s: int(ops._TC_MODE != "0" and s.n_tokens >= ops.TC_MIN_TOKENS and qs % 8 == 0 and H % 8 == 0 and
+                              (ops._TC_MODE == "1" or (s.n_tokens >= ops.TC_NARROW_MIN_TOKENS and
+                                                       ops.tc_one_wave(s.n_tokens, H, self.device)))))
+        b.emit(OP_TC_LINEAR, [out, qs, self.w_o, branch, H, T, H, qs, err], cond=b.param(f"tc_o_{H}_{qs}", tc_o))
+        b.emit(OP_GEMM_BF16, [out, self.w_o, branch, T, H, qs, 0], cond=b.param(f"lib_o_{H}_{qs}", lambda s: 1 - tc_o(s)))
         return branch
 
     def _decode_scratch(self, ws, n_tokens: int, n_seqs: int, max_splits: int, suffix: str = ""):
