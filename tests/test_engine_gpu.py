@@ -577,7 +577,8 @@ def test_step_program_equals_the_launch_by_launch_path(wide_dir, monkeypatch):
         issued = {k: v - before[k] for k, v in program.kind_launches().items()}
         if use_program:
             assert r.stats["program_steps"] == 4 and r._program.capacity == 2048
-            assert issued["decode_attention"] == 2 and issued["prefill_attention_tc"] == 6 and issued["prefill_attention"] == 0
+            assert issued["decode_attention_units"] == 2 and issued["decode_attention"] == 0
+            assert issued["prefill_attention_tc"] == 6 and issued["prefill_attention"] == 0
         else:
             assert r.stats["program_steps"] == 0 and sum(issued.values()) == 0
         return [o.float().cpu() for o in outs]

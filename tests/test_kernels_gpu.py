@@ -168,6 +168,44 @@ def test_decode_attention_tensor_core_kernel(nh, nkv, D, page, q_lens, window):
     assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
 
 
+@pytest.mark.parametrize("nh,nkv,D,page,q_lens,window,cap,slots", [
+    (14, 2, 64, 16, [1] * 8, 0, 16, 592), (12, 2, 128, 16, [1] * 8, 0, 16, 444), (16, 1, 64, 8, [1] * 8, 0, 16, 5),
+    (4, 4, 128, 64, [1] * 8, 0, 3, 7), (14, 2, 64, 32, [2, 1, 2, 1, 1, 2, 1, 2], 0, 16, 592),
+    (8, 4, 64, 8, [4, 1, 3, 1, 1, 2, 4, 1], 0, 4, 3), (14, 2, 64, 16, [1] * 8, 100, 16, 592),
+    (6, 2, 128, 32, [4, 1, 1, 5, 1, 2, 1, 1], 300, 16, 11), (28, 4, 128, 16, [1] * 8, 0, 16, 444),
+])
+def test_decode_attention_by_units_kernel(nh, nkv, D, page, q_lens, window, cap, slots):
+    """The persistent decode kernel with its host-made list of units: contexts on and around the stage and page
+    edges and one of thousands of keys, one far key that dominates, windows, several query tokens a request; few
+    slots and a low cap so that blocks take several units each and units are long; the list padded as a captured
+    graph pads it. Twice: the second launch finds the counters at zero."""
+    import numpy as np
+    from tokenmill_b200.parts.attention_plan import decode_units
+    ops = _ops()
+    befores = [0, 63, 64, 255, 256, 1000, 5000, 127]
+    c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=D + nh, window=window)
+    T, S = sum(q_lens), len(q_lens)
+    for rows in (None, S * 32):
+        rec, n_units, max_parts = decode_units(np.array(q_lens), np.array(befores), window, kv_heads=nkv, slots=slots,
+                                               cap=cap, head_dim=D, rows=rows)
+        assert max_parts <= cap and int((rec[:, 2] - rec[:, 1]).max()) <= 32
+        units = torch.from_numpy(rec).to(DEV)
+        n_work = torch.tensor([n_units * nkv], dtype=torch.int32, device=DEV)
+        part_acc = torch.full((T * nh * max_parts * D,), float("nan"), device=DEV)
+        part_ml = torch.full((T * nh * max_parts * 2,), float("nan"), device=DEV)
+        done = torch.zeros(S * nkv, dtype=torch.int32, device=DEV)
+        for _ in range(2):
+            out = torch.full_like(c["q"], float("nan"))
+            ops.decode_attention_units_bf16(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["before"], units, n_work, out,
+                                            scale=D ** -0.5, window=window, max_parts=max_parts,
+                                            grid=min(slots, rec.shape[0] * nkv), part_acc=part_acc, part_ml=part_ml,
+                                            done=done)
+            ops.tc_check(torch.device(DEV))
+            diff = (out.float().cpu() - c["ref"]).abs().max()
+            assert diff <= tol(torch.bfloat16, c["ref"], bf16=1e-2), diff
+            assert int(done.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("nh,nkv,D,page,window", [
     (14, 2, 64, 16, 0), (12, 2, 128, 16, 0), (3, 3, 64, 1, 0), (4, 1, 128, 7, 0), (14, 2, 64, 16, 70), (4, 2, 64, 8, 1),
     (6, 2, 128, 32, 200),

@@ -104,3 +104,37 @@ def test_short_prompts_are_cut_into_pieces_an_attention_unit_holds():
     assert pieces([StepEntry(h1, [1, 2, 3, 4], 0, [3, 0])], 14, 2) is None
     assert pieces([StepEntry(h1, [1, 2, 3], 0, [2])], 32, 1) is None
     assert pieces([StepEntry(h1, list(range(34)), 0, [33])], 14, 2) is None
+
+
+def test_decode_units_cover_every_stage_once_and_fill_the_slots():
+    """The decode kernel's plan: every request's stages (from its window's start to its last key) lie in exactly
+    one unit, parts are numbered 0 .. parts - 1, no unit is longer than the kernel takes, no request has more
+    parts than the cap; the list is sorted longest first and padded with empty rows when asked."""
+    import numpy as np
+    from tokenmill_b200.parts.attention_plan import DECODE_MAX_UNIT_STAGES, decode_parts_cap, decode_units
+    rng = np.random.default_rng(0)
+    for trial in range(50):
+        S = int(rng.integers(1, 40))
+        q_lens = rng.integers(1, 3, S)
+        starts = rng.integers(0, int(rng.choice([100, 3000, 40000])), S)
+        window = int(rng.choice([0, 0, 70, 1000]))
+        cap = int(rng.choice([decode_parts_cap(int(starts.max()) + 2), 64]))
+        slots = int(rng.choice([3, 444, 592]))
+        rows = S * cap if trial % 2 else None
+        rec, n, max_parts = decode_units(q_lens, starts, window, kv_heads=2, slots=slots, cap=cap, rows=rows)
+        assert max_parts <= cap and rec.shape[0] == (rows if rows else n)
+        assert not rec[n:].any()
+        sizes = rec[:n, 2] - rec[:n, 1]
+        assert (sizes >= 1).all() and (sizes <= DECODE_MAX_UNIT_STAGES).all() and (np.diff(sizes) <= 0).all()
+        for s in range(S):
+            mine = rec[:n][rec[:n, 0] == s]
+            mine = mine[np.argsort(mine[:, 3] & 0xffff)]
+            parts = int(mine[0, 3]) >> 16
+            assert len(mine) == parts and (mine[:, 3] >> 16 == parts).all()
+            assert (mine[:, 3] & 0xffff).tolist() == list(range(parts))
+            lo = max(0, int(starts[s]) - window + 1) if window else 0
+            assert mine[0, 1] == lo // 64 and mine[-1, 2] == (int(starts[s]) + int(q_lens[s]) - 1) // 64 + 1
+            assert (mine[1:, 1] == mine[:-1, 2]).all()
+    # the example of the docstring: two rounds, not three
+    rec, n, _ = decode_units(np.ones(27, int), np.full(27, 4400), 0, kv_heads=4, slots=444, cap=16)
+    assert n * 4 <= 2 * 444

@@ -1,0 +1,565 @@
+// Decode attention over the paged cache, driven by a list of work units, with the keys and values brought in by
+// the tensor memory accelerator (bfloat16, head size 64 or 128, pages of 8, 16, 32 or 64 tokens). The arithmetic
+// is that of src/infer/model/layers.py:100-124 over the cache of src/infer/kv/context.py:77-79: every query row
+// sees the keys up to its own position (and not older than the window), softmax in 32-bit.
+//
+// The host cuts each request's keys into UNITS of whole 64-key stages (parts/attention_plan.py decode_units: as many
+// units as keep every block of the grid busy for the same time, however the step's requests differ in length) and
+// writes them as records {request, first stage, end stage, part | parts << 16}. The grid is persistent: block b
+// takes work items b, b + gridDim.x, ... of the list, an item being (unit, kv head). A block is two warps.
+//
+//   * The PRODUCER warp walks the block's items and fills a ring of stages with `cp.async.bulk.tensor`: a page's
+//     keys of one kv head are one box of a 2-D tensor map over the cache ([slots, kv_heads * head_dim], box = page
+//     rows x 64 columns, 128-byte swizzle: the layout ldmatrix reads without bank conflicts), one lane per box.
+//     It only waits for a ring slot to be given back, so it runs ahead of the arithmetic, across item borders.
+//   * The CONSUMER warp takes the stages in order: scores of 16 query rows against 64 keys on the tensor cores
+//     (mma.sync m16n8k16), an online softmax, the values; at an item's end its state is the unit's PARTIAL, written
+//     straight from the registers. The block that writes the last partial of a (request, kv head) merges them in
+//     part order. (One consumer per ring: a ring slot is always read by the same warp, so the parity it waits for
+//     cannot be mistaken for that of a fill it has not seen.)
+//
+// Every wait is bounded (tcgen05_util.cuh mbar_wait): a block that gives up raises the error word, waits (bounded)
+// for the copies it asked for and leaves. A stage's rows beyond the unit's keys are filled from the nearest page
+// inside the unit (their scores are masked; what matters is that they hold finite numbers: the pool starts zeroed
+// and only finite values are ever written).
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <vector>
+
+#include "attention_decode_core.cuh"
+#include "tcgen05_util.cuh"
+
+namespace tmk {
+
+constexpr int kTdMaxPages = 256;           // pages of one unit: at most 32 stages of 64 keys in pages of 8
+constexpr int kTdMaxStages = 32;           // stages of one unit (attention_plan.py DECODE_MAX_UNIT_STAGES)
+template <int D> __host__ __device__ constexpr int td_stage_bytes() { return 2 * kDecBN * D * 2; }   // K and V tiles
+template <int D> __host__ __device__ constexpr int td_stages() { return D == 64 ? 3 : 2; }
+template <int D> __host__ __device__ constexpr int td_blocks_per_sm() { return D == 64 ? 4 : 3; }
+
+__device__ __forceinline__ void td_tma_load(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Where 16-byte piece `chunk` of key row `key` lies in a tile of 64 keys: halves of 64 columns one after the other,
+// rows of 128 bytes, pieces XOR-swizzled by the row (what the 128-byte swizzle of the tensor map writes).
+__device__ __forceinline__ uint32_t td_tile_addr(uint32_t base, int key, int chunk) {
+  return base + (uint32_t)(chunk >> 3) * (kDecBN * 128) + (uint32_t)key * 128 + (uint32_t)(((chunk & 7) ^ (key & 7)) << 4);
+}
+
+// 2^x by the hardware's approximation (2 ulp; the argument is at most 0, and -inf gives 0).
+__device__ __forceinline__ float td_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Profiling aid: when set (tm_decode_attention_units_timing), block 0 writes the global timer at its stations,
+// 8 a work item for its first 7 items ([64] unsigned 64-bit): 0 entry, 1 set up; then from 2 + 8 * item:
+// queries loaded, first stage landed, last stage done, partial written, merged (if it was the last); producer:
+// first copy asked for, last copy asked for; consumer again: counted.
+__device__ unsigned long long* g_td_timing = nullptr;
+
+__device__ __forceinline__ void td_stamp(unsigned long long* at, int station) {
+  if (at && station < 64) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    at[station] = t;
+  }
+}
+
+// What a work item covers, worked out the same way by both warps.
+struct TdItem {
+  int s, kvh, part, parts;
+  int q_start, n_rows, before, p_max;
+  int j_lo, j_hi;            // first and last key of the item
+  int kb_first, n_stages;    // first key of its first stage, stages (0: nothing to do)
+};
+
+__device__ __forceinline__ TdItem td_item(const int4* __restrict__ units, int w, const int* __restrict__ cu_q,
+                                          const int* __restrict__ kv_before, int nh, int nkv, int window) {
+  TdItem it;
+  const int4 rec = units[w / nkv];
+  it.s = rec.x;
+  it.kvh = w % nkv;
+  it.part = rec.w & 0xffff;
+  it.parts = rec.w >> 16;
+  it.q_start = cu_q[it.s];
+  const int q_len = cu_q[it.s + 1] - it.q_start;
+  const int G = nh / nkv;
+  it.before = kv_before[it.s];
+  it.n_rows = min(q_len * G, 16);
+  it.p_max = it.before + (it.n_rows - 1) / G;
+  const int lo = window > 0 ? max(0, it.before - window + 1) : 0;
+  it.j_lo = max(lo, rec.y * kDecBN);
+  it.j_hi = min(it.p_max, rec.z * kDecBN - 1);
+  it.kb_first = (it.j_lo / kDecBN) * kDecBN;
+  it.n_stages = (it.n_rows <= 0 || it.j_lo > it.j_hi) ? 0 : (it.j_hi - it.kb_first) / kDecBN + 1;
+  return it;
+}
+
+template <int D>
+__global__ void __launch_bounds__(64) decode_attention_units_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+    const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_table, int bt_stride,
+    const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int4* __restrict__ units,
+    const int* __restrict__ n_work_ptr, int max_work, float* __restrict__ part_acc, float* __restrict__ part_ml,
+    __nv_bfloat16* __restrict__ out, int* __restrict__ done, int nh, int nkv, int page_size, float scale_log2,
+    int window, int max_parts, int* __restrict__ error) {
+  constexpr int KS = D / 16, NT = D / 8, NS = td_stages<D>(), STAGE = td_stage_bytes<D>(), TILE = kDecBN * D * 2;
+  extern __shared__ __align__(1024) unsigned char td_raw[];
+  __shared__ __align__(8) uint64_t s_full[NS], s_empty[NS];
+  __shared__ int s_pages[kTdMaxPages];       // (the producer's own: the pages of the item it is filling)
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t ring = (t5_smem(td_raw) + 1023u) & ~1023u;
+  pdl_launch_dependents();
+  // (The unit list, the requests' lengths and the block table are the step's inputs, copied before its first
+  // kernel: they and the older keys and values may be read before the kernel in front of this one has finished.)
+  unsigned long long* stamps = (g_td_timing && blockIdx.x == 0 && lane == 0) ? g_td_timing : nullptr;
+  td_stamp(warp == 0 ? stamps : nullptr, 0);
+  const int n_work = min(*n_work_ptr, max_work);
+  const int G = nh / nkv;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(t5_smem(&s_full[i]), 1);
+      mbar_init(t5_smem(&s_empty[i]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  td_stamp(warp == 0 ? stamps : nullptr, 1);
+
+  bool ok = true;
+  int issued = 0;                            // (producer) stages asked for so far, over all items
+  if (warp == 1) {
+    // ---- producer: the copies of a stage are spread over the lanes: lane = (box, half head, K or V), at most 8 x 2 x 2 ----
+    const int page_log = 31 - __clz(page_size);                 // (page sizes are powers of two)
+    const int rows = min(page_size, kDecBN);                    // rows of a box
+    const int boxes = kDecBN / rows;
+    constexpr int HALVES = D / 64;
+    const int my_box = lane / (2 * HALVES), my_half = (lane / 2) % HALVES, my_v = lane & 1;
+    const bool copies = my_box < boxes;
+    const CUtensorMap* my_map = my_v ? &map_v : &map_k;
+    const uint32_t my_off = (uint32_t)my_v * TILE + (uint32_t)my_half * (kDecBN * 128) + (uint32_t)(my_box * rows) * 128;
+    bool waited = false;
+    int item = 0;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++item) {
+      const TdItem it = td_item(units, w, cu_q, kv_before, nh, nkv, window);
+      if (it.n_stages <= 0) continue;
+      if (it.n_stages > kTdMaxStages) {      // (a plan this kernel cannot hold: say so and stop)
+        if (lane == 0) atomicCAS(error, 0, 32);
+        s_abort = 1;
+        ok = false;
+        break;
+      }
+      const int page0 = it.kb_first >> page_log;
+      const int n_pages = (it.j_hi >> page_log) - page0 + 1;
+      __syncwarp();                          // the copies of the item before have been asked for: its pages may go
+      for (int i = lane; i < n_pages; i += 32) s_pages[i] = block_table[(size_t)it.s * bt_stride + page0 + i];
+      __syncwarp();
+      const int j_first = it.j_lo & ~(rows - 1), j_last = it.j_hi & ~(rows - 1);
+      const int x = it.kvh * D + my_half * 64;
+      for (int k = 0; k < it.n_stages; ++k) {
+        const int slot = issued % NS;
+        if (issued >= NS) {
+          ok = mbar_wait(t5_smem(&s_empty[slot]), (uint32_t)(issued / NS - 1) & 1u, &s_abort, error, 34);
+          if (!ok) break;
+        }
+        const int kb = it.kb_first + k * kDecBN;
+        if (!waited && kb + kDecBN > it.before) {               // keys of the step's own tokens: written by the
+          pdl_wait();                                           // kernel in front of this one
+          waited = true;
+        }
+        const uint32_t bar = t5_smem(&s_full[slot]);
+        if (k == 0 && item < 7) td_stamp(stamps, 2 + 8 * item + 5);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)STAGE);
+        __syncwarp();
+        if (copies) {
+          const int j0 = min(max(kb + my_box * rows, j_first), j_last);
+          const int y = (s_pages[(j0 >> page_log) - page0] << page_log) + (j0 & (page_size - 1));
+          td_tma_load(ring + (uint32_t)slot * STAGE + my_off, my_map, x, y, bar);
+        }
+        ++issued;
+      }
+      if (item < 7) td_stamp(stamps, 2 + 8 * item + 6);
+    }
+    pdl_wait();                              // (every thread of the chain waits before it exits)
+  } else {
+    // ---- consumer: the stages in order, 64 keys at a time, one online softmax per item ----
+    pdl_wait();                              // the queries come from the kernel in front of this one
+    const int r0 = lane >> 2, r1 = r0 + 8;   // the two tile rows this thread's accumulators belong to
+    const int cpair = (lane & 3) * 2;
+    const int k_key = (lane & 7) + ((lane >> 4) << 3), k_sel = (lane >> 3) & 1;     // ldmatrix rows: keys, not transposed
+    const int v_key = (lane & 7) + (((lane >> 3) & 1) << 3), v_sel = lane >> 4;     // and transposed, for the values
+    int taken = 0;                           // stages read so far, over all items
+    int item = 0;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++item) {
+      const TdItem it = td_item(units, w, cu_q, kv_before, nh, nkv, window);
+      if (it.n_stages <= 0) continue;
+      if (it.n_stages > kTdMaxStages) break;
+      const int n_rows = it.n_rows, before = it.before;
+      uint32_t qa[KS][4];                    // query fragments straight from global memory (rows beyond n_rows are zero)
+      {
+        const __nv_bfloat16* qr0 = nullptr;
+        const __nv_bfloat16* qr1 = nullptr;
+        if (r0 < n_rows) qr0 = q + ((size_t)(it.q_start + r0 / G) * nh + it.kvh * G + r0 % G) * D;
+        if (r1 < n_rows) qr1 = q + ((size_t)(it.q_start + r1 / G) * nh + it.kvh * G + r1 % G) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int c = ks * 16 + cpair;
+          qa[ks][0] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c)) : 0u;
+          qa[ks][1] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c)) : 0u;
+          qa[ks][2] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c + 8)) : 0u;
+          qa[ks][3] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c + 8)) : 0u;
+        }
+      }
+      if (item < 7) td_stamp(stamps, 2 + 8 * item);
+      const int p_r0 = r0 < n_rows ? before + r0 / G : -1, p_r1 = r1 < n_rows ? before + r1 / G : -1;
+      const int lo_r0 = window > 0 ? max(0, p_r0 - window + 1) : 0, lo_r1 = window > 0 ? max(0, p_r1 - window + 1) : 0;
+      const int lo_max = window > 0 ? max(0, it.p_max - window + 1) : 0;
+      float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // running max (log2 units) and sum per row
+      float o[NT][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+      for (int b = 0; b < it.n_stages; ++b) {
+        const int kb = it.kb_first + b * kDecBN;
+        const int slot = taken % NS;
+        ok = mbar_wait(t5_smem(&s_full[slot]), (uint32_t)(taken / NS) & 1u, &s_abort, error, 33);
+        if (!ok) break;
+        if (b == 0 && item < 7) td_stamp(stamps, 2 + 8 * item + 1);
+        const uint32_t k_base = ring + (uint32_t)slot * STAGE, v_base = k_base + TILE;
+        float sc[8][4];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(td_tile_addr(k_base, g * 16 + k_key, 2 * ks + k_sel), b0, b1, b2, b3);
+            mma_bf16_16816(sc[2 * g], qa[ks], b0, b1);
+            mma_bf16_16816(sc[2 * g + 1], qa[ks], b2, b3);
+          }
+        // Scale into log2 units; mask where the stage reaches beyond the keys a row may see (uniform over the warp;
+        // rows beyond n_rows are never written out).
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+        if (kb >= it.j_lo && kb >= lo_max && kb + kDecBN - 1 <= min(it.j_hi, before)) {
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[t][e] *= scale_log2;
+            tmax0 = fmaxf(tmax0, fmaxf(sc[t][0], sc[t][1]));
+            tmax1 = fmaxf(tmax1, fmaxf(sc[t][2], sc[t][3]));
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int j = kb + t * 8 + cpair + e;
+              const bool in = j >= it.j_lo && j <= it.j_hi;
+              sc[t][e] = (in && j <= p_r0 && j >= lo_r0) ? sc[t][e] * scale_log2 : -INFINITY;
+              sc[t][2 + e] = (in && j <= p_r1 && j >= lo_r1) ? sc[t][2 + e] * scale_log2 : -INFINITY;
+              tmax0 = fmaxf(tmax0, sc[t][e]);
+              tmax1 = fmaxf(tmax1, sc[t][2 + e]);
+            }
+        }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
+        // (A row that has seen no key yet subtracts 0 instead of -inf: its scores are all -inf and come out as 0.)
+        const float sub0 = mn0 == -INFINITY ? 0.f : mn0, sub1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float corr0 = td_exp2(m0 - sub0), corr1 = td_exp2(m1 - sub1);
+        float ps0 = 0.f, ps1 = 0.f;
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float p[2][4];
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              p[t][e] = td_exp2(sc[2 * g + t][e] - sub0);
+              p[t][2 + e] = td_exp2(sc[2 * g + t][2 + e] - sub1);
+              ps0 += p[t][e];
+              ps1 += p[t][2 + e];
+            }
+          pa[g][0] = pack_bf16(p[0][0], p[0][1]);
+          pa[g][1] = pack_bf16(p[0][2], p[0][3]);
+          pa[g][2] = pack_bf16(p[1][0], p[1][1]);
+          pa[g][3] = pack_bf16(p[1][2], p[1][3]);
+        }
+        ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1);
+        ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
+        ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1);
+        ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
+        l0 = l0 * corr0 + ps0;
+        l1 = l1 * corr1 + ps1;
+        m0 = mn0;
+        m1 = mn1;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          o[t][0] *= corr0;
+          o[t][1] *= corr0;
+          o[t][2] *= corr1;
+          o[t][3] *= corr1;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+          for (int dt = 0; dt < NT / 2; ++dt) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(td_tile_addr(v_base, g * 16 + v_key, 2 * dt + v_sel), b0, b1, b2, b3);
+            mma_bf16_16816(o[2 * dt], pa[g], b0, b1);
+            mma_bf16_16816(o[2 * dt + 1], pa[g], b2, b3);
+          }
+        __syncwarp();                                                   // the warp has read the stage
+        if (lane == 0) mbar_arrive(t5_smem(&s_empty[slot]));
+        ++taken;
+      }
+      if (!ok) break;
+      if (item < 7) td_stamp(stamps, 2 + 8 * item + 2);
+
+      if (it.parts == 1) {
+        // The request's only unit: its state is the result.
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = half ? r1 : r0;
+          if (r < n_rows) {
+            const size_t orow = (size_t)(it.q_start + r / G) * nh + it.kvh * G + r % G;
+            const float l = half ? l1 : l0;
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __nv_bfloat16* dst = out + orow * D + cpair;
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+              *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16(o[t][2 * half] * inv, o[t][2 * half + 1] * inv);
+          }
+        }
+        if (item < 7) td_stamp(stamps, 2 + 8 * item + 3);
+      } else {
+        // The item's state is the unit's partial (max in log2 units, sum, unnormalised values).
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = half ? r1 : r0;
+          if (r < n_rows) {
+            const size_t orow = (size_t)(it.q_start + r / G) * nh + it.kvh * G + r % G;
+            float* dst = part_acc + (orow * max_parts + it.part) * D + cpair;
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+              *reinterpret_cast<float2*>(dst + t * 8) = make_float2(o[t][2 * half], o[t][2 * half + 1]);
+            if ((lane & 3) == 0)
+              *reinterpret_cast<float2*>(part_ml + (orow * max_parts + it.part) * 2) =
+                  make_float2(half ? m1 : m0, half ? l1 : l0);
+          }
+        }
+        if (item < 7) td_stamp(stamps, 2 + 8 * item + 3);
+        // The last of a (request, kv head)'s units to finish merges them, in part order.
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(&done[it.s * nkv + it.kvh], 1) == it.parts - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (item < 7) td_stamp(stamps, 2 + 8 * item + 7);
+        if (last) {
+          __threadfence();
+          // A lane owns 4 columns of up to 8 rows at a time and takes the parts two by two: the loads of a pass
+          // (up to 32 a lane) are all asked for before the first is used, so a pass costs one trip to the L2.
+          constexpr int GROUPS = D / 4, LANE_ROWS = 32 / GROUPS;
+          const int d = (lane % GROUPS) * 4;
+          for (int rb = 0; rb < n_rows; rb += 8 * LANE_ROWS) {
+            int orow[8];
+            float mx[8], lsum[8], acc[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = rb + i * LANE_ROWS + lane / GROUPS;
+              orow[i] = r < n_rows ? (it.q_start + r / G) * nh + it.kvh * G + r % G : -1;
+              mx[i] = -INFINITY;
+              lsum[i] = 0.f;
+              acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+            }
+            for (int z0 = 0; z0 < it.parts; z0 += 2) {
+              float2 ml[8][2];
+              float4 pv[8][2];
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const bool have = orow[i] >= 0 && z0 + u < it.parts;
+                  const size_t at = (size_t)max(orow[i], 0) * max_parts + min(z0 + u, it.parts - 1);
+                  ml[i][u] = have ? __ldcg(reinterpret_cast<const float2*>(part_ml + at * 2)) : make_float2(-INFINITY, 0.f);
+                  pv[i][u] = have ? __ldcg(reinterpret_cast<const float4*>(part_acc + at * D + d))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+              for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float m_new = fmaxf(mx[i], ml[i][u].x);
+                  const float sub = m_new == -INFINITY ? 0.f : m_new;      // (no key yet on either side: both weigh 0)
+                  const float keep = td_exp2(mx[i] - sub), wgt = td_exp2(ml[i][u].x - sub);
+                  lsum[i] = lsum[i] * keep + ml[i][u].y * wgt;
+                  acc[i][0] = acc[i][0] * keep + pv[i][u].x * wgt;
+                  acc[i][1] = acc[i][1] * keep + pv[i][u].y * wgt;
+                  acc[i][2] = acc[i][2] * keep + pv[i][u].z * wgt;
+                  acc[i][3] = acc[i][3] * keep + pv[i][u].w * wgt;
+                  mx[i] = m_new;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (orow[i] >= 0) {
+                const float inv = lsum[i] > 0.f ? 1.0f / lsum[i] : 0.f;
+                uint2 ov;
+                ov.x = pack_bf16(acc[i][0] * inv, acc[i][1] * inv);
+                ov.y = pack_bf16(acc[i][2] * inv, acc[i][3] * inv);
+                *reinterpret_cast<uint2*>(out + (size_t)orow[i] * D + d) = ov;
+              }
+          }
+          if (lane == 0) done[it.s * nkv + it.kvh] = 0;
+        }
+      }
+      if (item < 7) td_stamp(stamps, 2 + 8 * item + 4);
+    }
+  }
+  __syncthreads();                           // both warps: all copies have been asked for, all stages read, or one gave up
+  if (s_abort && warp == 1 && lane == 0) {
+    // Leaving early: give the copies still on their way into this block's shared memory a bounded chance to land
+    // (the producer knows which fills it asked for: the last one of each slot, by its parity).
+    for (int k = max(0, issued - NS); k < issued; ++k)
+      for (uint32_t spin = 0; spin < (1u << 18) && !mbar_try(t5_smem(&s_full[k % NS]), (uint32_t)(k / NS) & 1u); ++spin)
+        __nanosleep(64);
+  }
+}
+
+// --- host -----------------------------------------------------------------------------------------------------
+
+using TdEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static TdEncodeFn td_encode_fn() {
+  static TdEncodeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TdEncodeFn>(p);
+  }
+  return fn;
+}
+
+struct TdMapKey {
+  const void* base;
+  long long slots;
+  int page_size, nkv, D;
+  bool operator==(const TdMapKey& o) const {
+    return base == o.base && slots == o.slots && page_size == o.page_size && nkv == o.nkv && D == o.D;
+  }
+};
+
+// The tensor map of one cache tensor ([slots, nkv * D] bfloat16, boxes of min(page, 64) rows x 64 columns, 128-byte
+// swizzle). Encoding takes microseconds on the host, and a layer's cache never moves: maps are kept by address.
+static bool td_map_for(const void* base, long long slots, int page_size, int nkv, int D, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::vector<std::pair<TdMapKey, CUtensorMap>> maps;
+  const TdMapKey key{base, slots, page_size, nkv, D};
+  std::lock_guard<std::mutex> lock(mu);
+  for (auto& kv : maps)
+    if (kv.first == key) {
+      *out = kv.second;
+      return true;
+    }
+  TdEncodeFn fn = td_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)nkv * D, (cuuint64_t)slots};
+  const cuuint64_t strides[1] = {(cuuint64_t)nkv * D * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)(page_size < kDecBN ? page_size : kDecBN)};
+  const cuuint32_t elem[2] = {1u, 1u};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (maps.size() >= 4096) maps.clear();     // (engines come and go in one process: do not grow without bound)
+  maps.emplace_back(key, m);
+  *out = m;
+  return true;
+}
+
+template <int D>
+int launch_decode_attention_units(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* block_table,
+                                  int bt_stride, const int* cu_q, const int* kv_before, const int* units,
+                                  const int* n_work, int max_work, int grid_blocks, float* part_acc, float* part_ml,
+                                  void* out, int* done, int nh, int nkv, int page_size, float scale, int window,
+                                  int max_parts, int* error, cudaStream_t stream) {
+  const int smem = td_stages<D>() * td_stage_bytes<D>() + 1024;
+  auto kern = decode_attention_units_kernel<D>;
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    set = true;
+  }
+  return launch_pdl(kern, dim3(grid_blocks), dim3(64), (size_t)smem, stream, mk, mv, (const __nv_bfloat16*)q,
+                    block_table, bt_stride, cu_q, kv_before, reinterpret_cast<const int4*>(units), n_work, max_work,
+                    part_acc, part_ml, (__nv_bfloat16*)out, done, nh, nkv, page_size,
+                    scale * 1.4426950408889634f, window, max_parts, error);
+}
+
+}  // namespace tmk
+
+// Where block 0 writes its stations (device memory, [64] unsigned 64-bit; null turns it off).
+extern "C" int tm_decode_attention_units_timing(unsigned long long* stamps) {
+  return (int)cudaMemcpyToSymbol(tmk::g_td_timing, &stamps, sizeof(stamps));
+}
+
+// Blocks of the persistent grid that are resident at once on a chip of `sm_count` multiprocessors: what the host's
+// plan of units should fill evenly.
+extern "C" int tm_decode_attention_units_slots(int D, int sm_count) {
+  return sm_count * (D == 64 ? tmk::td_blocks_per_sm<64>() : tmk::td_blocks_per_sm<128>());
+}
+
+// Decode attention by a list of units. q, out: [T, nh, D] bfloat16; caches [n_pages, page_size, nkv, D] bfloat16
+// (16-byte aligned, for the tensor maps); block_table [n_seqs, bt_stride]; cu_q [n_seqs + 1]; kv_before [n_seqs];
+// units: int32 [.., 4] records {request, first stage, end stage, part | parts << 16} (16-byte aligned), of which
+// *n_work / nkv are valid (n_work on the device, at most max_work); every request with query rows has `parts` units
+// that together cover its keys, part numbers 0 .. parts - 1 < max_parts, at most 32 stages a unit. part_acc
+// [T * nh * max_parts * D] and part_ml [T * nh * max_parts * 2] float32 scratch; done: n_seqs * nkv zeroed counters
+// (left zeroed). Every request brings at most 16 / (nh / nkv) query tokens. `error` (required) receives 32 for a
+// plan the kernel cannot hold, 33 / 34 for a wait that ran out. Page sizes 8, 16, 32, 64; head sizes 64 and 128;
+// anything else returns TM_ERR_UNSUPPORTED_SHAPE.
+extern "C" int tm_decode_attention_units_bf16(const void* q, const void* kcache, const void* vcache, long long n_pages,
+                                              const int* block_table, int bt_stride, const int* cu_q,
+                                              const int* kv_before, const int* units, const int* n_work, int max_work,
+                                              int grid_blocks, float* part_acc, float* part_ml, void* out, int* done,
+                                              int nh, int nkv, int D, int page_size, float scale, int window,
+                                              int max_parts, int* error, cudaStream_t stream) {
+  if (max_work <= 0 || grid_blocks <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || nh / nkv > 16 || n_pages <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (max_parts <= 0 || max_parts > 0x7fff) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (D != 64 && D != 128) return TM_ERR_UNSUPPORTED_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(kcache) | reinterpret_cast<uintptr_t>(vcache) | reinterpret_cast<uintptr_t>(units)) & 15)
+    return TM_ERR_UNSUPPORTED_SHAPE;
+  if (!part_acc || !part_ml || !done || !out || !error || !units || !n_work) return TM_ERR_SCRATCH_TOO_SMALL;
+  CUtensorMap mk, mv;
+  if (!tmk::td_map_for(kcache, n_pages * page_size, page_size, nkv, D, &mk) ||
+      !tmk::td_map_for(vcache, n_pages * page_size, page_size, nkv, D, &mv))
+    return 90006;
+  if (D == 64)
+    return tmk::launch_decode_attention_units<64>(mk, mv, q, block_table, bt_stride, cu_q, kv_before, units, n_work,
+                                                  max_work, grid_blocks, part_acc, part_ml, out, done, nh, nkv,
+                                                  page_size, scale, window, max_parts, error, stream);
+  return tmk::launch_decode_attention_units<128>(mk, mv, q, block_table, bt_stride, cu_q, kv_before, units, n_work,
+                                                 max_work, grid_blocks, part_acc, part_ml, out, done, nh, nkv,
+                                                 page_size, scale, window, max_parts, error, stream);
+}

@@ -46,6 +46,11 @@ int tm_decode_attention_bf16(const void* q, const void* kcache, const void* vcac
                              int bt_stride, const int* cu_q, const int* kv_before, int n_seqs, float* part_acc,
                              float* part_ml, void* out, int* done, int nh, int nkv, int D, int page_size, float scale,
                              int window, int split_keys, int max_splits, int* error, cudaStream_t stream);
+int tm_decode_attention_units_bf16(const void* q, const void* kcache, const void* vcache, long long n_pages,
+                                   const int* block_table, int bt_stride, const int* cu_q, const int* kv_before,
+                                   const int* units, const int* n_work, int max_work, int grid_blocks, float* part_acc,
+                                   float* part_ml, void* out, int* done, int nh, int nkv, int D, int page_size,
+                                   float scale, int window, int max_parts, int* error, cudaStream_t stream);
 }
 
 #define TM_ERR_PROGRAM 90010          // a malformed record (unknown kind, parameter index out of range)
@@ -63,6 +68,7 @@ enum ProgramOpKind : int32_t {
   kOpSwiglu = 7,
   kOpTcQkvRopeWrite = 8,
   kOpTcLinear = 9,
+  kOpDecodeAttentionUnits = 10,
 };
 constexpr int kOpKinds = 16;
 
@@ -183,6 +189,15 @@ static int run_op(const ProgramOp& op, const int64_t* a, cudaStream_t s) {
                                       (int)a[7], as_ptr<float>(a[8]), as_ptr<float>(a[9]), as_ptr<void>(a[10]), as_ptr<int>(a[11]),
                                       (int)a[12], (int)a[13], (int)a[14], (int)a[15], as_float(a[16]), (int)a[17], (int)a[18],
                                       (int)a[19], as_ptr<int>(a[20]), s);
+    case kOpDecodeAttentionUnits:  // q, k, v, n_pages, table, bt_stride, cu_q, kv_before, units, n_work, max_work, grid, acc, ml,
+                                   // out, done, nh, nkv, D, page, scale, window, max_parts, error
+      if (op.n_args != 24) return TM_ERR_PROGRAM;
+      return tm_decode_attention_units_bf16(
+          as_ptr<const void>(a[0]), as_ptr<const void>(a[1]), as_ptr<const void>(a[2]), (long long)a[3],
+          as_ptr<const int>(a[4]), (int)a[5], as_ptr<const int>(a[6]), as_ptr<const int>(a[7]), as_ptr<const int>(a[8]),
+          as_ptr<const int>(a[9]), (int)a[10], (int)a[11], as_ptr<float>(a[12]), as_ptr<float>(a[13]), as_ptr<void>(a[14]),
+          as_ptr<int>(a[15]), (int)a[16], (int)a[17], (int)a[18], (int)a[19], as_float(a[20]), (int)a[21], (int)a[22],
+          as_ptr<int>(a[23]), s);
     case kOpSwiglu:       // dtype, gu, out, T, I
       if (op.n_args != 5) return TM_ERR_PROGRAM;
       return tm_swiglu((int)a[0], as_ptr<const void>(a[1]), as_ptr<void>(a[2]), (int)a[3], (int)a[4], s);

@@ -170,6 +170,62 @@ def decode_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
     return out
 
 
+_DECODE_UNITS = os.environ.get("TOKENMILL_DECODE_UNITS", "1") != "0"
+
+
+def decode_units_ok(page_size: int, head_dim: int) -> bool:
+    """Whether decode attention runs as a persistent grid over a host-made list of units, with the keys and values
+    brought in by tensor-map copies (attention_decode_tma_bf16.cu: pages of 8, 16, 32 or 64 tokens, heads of 64 or
+    128). TOKENMILL_DECODE_UNITS=0 keeps the kernel with one block per (request, kv head, fixed split)."""
+    return _DECODE_UNITS and page_size in (8, 16, 32, 64) and head_dim in (64, 128)
+
+
+_units_slots: dict[tuple[int, int], int] = {}
+
+
+def decode_units_slots(head_dim: int, device: torch.device | None = None) -> int:
+    """Blocks of the unit-driven decode attention that are resident at once: what a plan of units should fill
+    evenly (multiprocessors of the device; 148 where there is none to ask)."""
+    sms = 148
+    if device is not None and device.type == "cuda":
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+    key = (head_dim, sms)
+    if key not in _units_slots:
+        _units_slots[key] = sms * (4 if head_dim == 64 else 3)
+    return _units_slots[key]
+
+
+def decode_attention_units_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                                cu_q: torch.Tensor, kv_before: torch.Tensor, units: torch.Tensor, n_work: torch.Tensor,
+                                out: torch.Tensor, *, scale: float, window: int, max_parts: int, grid: int,
+                                part_acc: torch.Tensor, part_ml: torch.Tensor, done: torch.Tensor) -> torch.Tensor:
+    """Tensor-core attention for steps whose requests bring at most 16 / (nh / nkv) tokens each (decoding), by a
+    list of units (parts/attention_plan.py decode_units): ``units`` int32 [rows, 4] on the device, of which
+    ``n_work`` (one int32 on the device) / kv_heads are valid; per-unit partials through part_acc / part_ml
+    (``max_parts`` a request), merged by the block that writes a (request, kv head)'s last; ``done``:
+    n_seqs * kv_heads int32 zeros (left zero); ``grid``: blocks to launch."""
+    T, nh, D = q.shape
+    page_size, nkv = kcache.shape[1], kcache.shape[2]
+    bf, i32 = torch.bfloat16, torch.int32
+    n_seqs = kv_before.numel()
+    need = T * nh * max_parts
+    if part_acc.numel() < need * D or part_ml.numel() < need * 2:
+        raise lib.KernelError("decode_attention_units_bf16: scratch too small")
+    if kcache.shape[3] != D or vcache.shape != kcache.shape or out.shape != q.shape:
+        raise lib.KernelError("decode_attention_units_bf16: q / cache / out shapes disagree")
+    if done.numel() < n_seqs * nkv:
+        raise lib.KernelError("decode_attention_units_bf16: too few arrival counters")
+    if units.dim() != 2 or units.shape[1] != 4 or units.data_ptr() % 16:
+        raise lib.KernelError("decode_attention_units_bf16: units must be 16-byte aligned int32 records of 4")
+    lib.call("tm_decode_attention_units_bf16", _req(q, "q", bf), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf),
+             kcache.shape[0], _req(block_table, "block_table", i32), block_table.stride(0), _req(cu_q, "cu_q", i32),
+             _req(kv_before, "kv_before", i32), _req(units, "units", i32), _req(n_work, "n_work", i32),
+             units.shape[0] * nkv, int(grid), _req(part_acc, "part_acc", torch.float32),
+             _req(part_ml, "part_ml", torch.float32), _req(out, "out", bf), _req(done, "done", i32), nh, nkv, D, page_size,
+             float(scale), int(window), int(max_parts), _tc_flag(q.device).data_ptr(), _stream())
+    return out
+
+
 def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                            units, counters: torch.Tensor, out: torch.Tensor, *, scale: float, window: int = 0,
                            part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
@@ -561,8 +617,12 @@ def tc_check(device: torch.device) -> None:
         if code:
             flag.zero_()
             if code == 32:
-                raise lib.KernelError("decode attention met a request with more rows than a tile holds or with keys "
-                                      "beyond max_splits * split_keys; its output is incomplete")
+                raise lib.KernelError("decode attention met a request with more rows than a tile holds, keys beyond "
+                                      "max_splits * split_keys or a unit of more stages than it takes; its output is "
+                                      "incomplete")
+            if code in (33, 34):
+                raise lib.KernelError(f"decode attention gave up waiting for {'a stage of keys' if code == 33 else 'a free stage'}"
+                                      f" (code {code}); its output is incomplete")
             if code == 31:
                 raise lib.KernelError("a token's position lies outside the position tables (the rotation was not "
                                       "applied as asked; the step's results are wrong)")

@@ -36,7 +36,7 @@ if TYPE_CHECKING:
 
 OP_ADD_RMSNORM, OP_GEMM_BF16, OP_QKV_ROPE_WRITE = 1, 2, 3
 OP_PREFILL_ATTENTION_TC, OP_PREFILL_ATTENTION, OP_DECODE_ATTENTION, OP_SWIGLU = 4, 5, 6, 7
-OP_TC_QKV_ROPE_WRITE, OP_TC_LINEAR = 8, 9
+OP_TC_QKV_ROPE_WRITE, OP_TC_LINEAR, OP_DECODE_ATTENTION_UNITS = 8, 9, 10
 MAX_ARGS = 24
 MIN_TOKENS = 1            # (a caller may keep small steps on the launch-by-launch path by asking for more)
 CUBLAS_WORKSPACE = 32 << 20
@@ -51,7 +51,7 @@ lib.register_signature("tm_program_kind_launches", [ctypes.c_void_p])
 KIND_NAMES = {OP_ADD_RMSNORM: "add_rmsnorm", OP_GEMM_BF16: "gemm_bf16", OP_QKV_ROPE_WRITE: "qkv_rope_write",
               OP_PREFILL_ATTENTION_TC: "prefill_attention_tc", OP_PREFILL_ATTENTION: "prefill_attention",
               OP_DECODE_ATTENTION: "decode_attention", OP_SWIGLU: "swiglu", OP_TC_QKV_ROPE_WRITE: "tc_qkv_rope_write",
-              OP_TC_LINEAR: "tc_linear"}
+              OP_TC_LINEAR: "tc_linear", OP_DECODE_ATTENTION_UNITS: "decode_attention_units"}
 
 
 def kind_launches() -> dict[str, int]:

@@ -26,12 +26,25 @@ import torch
 
 from ..kernels import ops
 from ..registry import get_part, register_mixer
-from .attention_plan import choose_chunk, packed_units, tiles_for
+from .attention_plan import choose_chunk, decode_parts_cap, decode_units, packed_units, tiles_for
 from .base import (LayerCache, PartMeta, PrefillUnits, StepInputs, StepMetadata, StepShape, part_limit_positions,
                    part_max_positions)
 from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
 
 SPLIT_KEYS = 128     # decode attention cuts each request's keys at absolute multiples of this (batch 64 at contexts near 600: 1.27 ms a step against 1.31 with 256 and 1.38 with 64)
+MAX_SPLIT_KEYS = 512  # (the kernel with one block per split)
+SPLIT_UNITS = 256    # ... or of a larger power-of-two multiple while the step still has this many (request, kv head, split) units
+
+
+def choose_split(kv_lens: np.ndarray, kv_heads: int) -> int:
+    """Keys per split of the decode attention for a step whose requests hold ``kv_lens`` keys: the base size, doubled
+    while enough units are left to fill the chip. Every split costs a partial result written and merged, so long
+    contexts in large batches want few, long splits (27 requests of 4,400 keys over 4 kv heads of 128: 140 us a layer
+    with 128 keys a split, 95 us with 512); short ones want many (what a block takes in per second is limited)."""
+    split = SPLIT_KEYS
+    while split < MAX_SPLIT_KEYS and int(np.sum(-(-kv_lens // (2 * split)))) * kv_heads >= SPLIT_UNITS:
+        split *= 2
+    return split
 
 
 class GroupedQueryAttention:
@@ -122,10 +135,26 @@ class GroupedQueryAttention:
         G = self.nh // self.nkv
         q_lens, starts = shape.q_lens, shape.starts
         max_q = int(q_lens.max()) if q_lens.size else 0
-        host = {"split_keys": SPLIT_KEYS, "max_splits": max(1, -(-int(shape.max_kv_len) // SPLIT_KEYS))}
+        # (a captured graph serves every context up to the limit with the launch grid it was captured with: base size)
+        split = SPLIT_KEYS if shape.for_graph or not self.fast else choose_split(starts.astype(np.int64) + q_lens, self.nkv)
+        host = {"split_keys": split, "max_splits": max(1, -(-int(shape.max_kv_len) // split))}
         arrays: dict[str, np.ndarray] = {}
+        constant = True                           # (a graph replays q_lens of 1: nothing else depends on starts)
         if self.fast and max_q * G <= 16:
             host["path"] = "decode"
+            if ops.decode_units_ok(shape.page_size, self.D):
+                # The persistent kernel's list of units, made anew for every step (a captured graph has room for
+                # the most units its requests can have, and is told at each replay how many there are).
+                S = int(q_lens.size)
+                cap = decode_parts_cap(shape.max_kv_len)
+                slots = ops.decode_units_slots(self.D, self.device)
+                records, n_units, max_parts = decode_units(q_lens, starts, self.window, kv_heads=self.nkv, slots=slots,
+                                                           cap=cap, head_dim=self.D, rows=S * cap if shape.for_graph else None)
+                arrays["decode_units"] = records
+                arrays["decode_n_work"] = np.array([n_units * self.nkv], dtype=np.int32)
+                host.update(max_parts=cap if shape.for_graph else max_parts,
+                            decode_grid=min(slots, records.shape[0] * self.nkv))
+                constant = False
         elif self.fast:
             chunk = self.prefill_chunk or choose_chunk(q_lens, starts, G, self.nkv, tile=self.prefill_tile)
             records, n_tiles, n_slots = packed_units(q_lens, starts, G, tile=self.prefill_tile, chunk=chunk)
@@ -136,7 +165,7 @@ class GroupedQueryAttention:
             tile_seq, tile_row0 = tiles_for(q_lens, G)
             arrays["tile_seq"], arrays["tile_row0"] = tile_seq, tile_row0
             host.update(path="generic", n_tiles32=int(tile_seq.size))
-        return StepMetadata(arrays, host, constant_in_graph=True)      # (a graph replays q_lens of 1: nothing depends on starts)
+        return StepMetadata(arrays, host, constant_in_graph=constant)
 
     def _meta(self, step: StepInputs) -> PartMeta:
         return step.meta[self.metadata_key()]
@@ -193,7 +222,7 @@ class GroupedQueryAttention:
         product) written into a step program (kernels/program.py). ``x`` is a workspace buffer; returns the
         output buffer. The attention kernel is chosen per step as in ``attend``: all candidates are in the
         program, each under a step parameter that says whether it runs."""
-        from ..kernels.program import (OP_DECODE_ATTENTION, OP_GEMM_BF16, OP_PREFILL_ATTENTION, OP_PREFILL_ATTENTION_TC,
+        from ..kernels.program import (OP_DECODE_ATTENTION, OP_DECODE_ATTENTION_UNITS, OP_GEMM_BF16, OP_PREFILL_ATTENTION, OP_PREFILL_ATTENTION_TC,
                                        OP_QKV_ROPE_WRITE, OP_TC_LINEAR, OP_TC_QKV_ROPE_WRITE, Float)
         if not self.fast or self.cos is None:
             raise NotImplementedError("step programs are built for bfloat16 rotary attention with heads of 64 or 128")
@@ -235,21 +264,37 @@ class GroupedQueryAttention:
 
         # decode kernel: scratch for T * nh rows of max_splits partial results, n_seqs * nkv arrival counters
         # (buffers named for this head shape: a later launch record's buffer never moves an earlier one's)
-        def dec(i):
+        by_units = lambda s: path(s) == "decode" and "decode_units" in meta(s).arrays      # noqa: E731
+        by_splits = lambda s: path(s) == "decode" and "decode_units" not in meta(s).arrays  # noqa: E731
+
+        def dec(i, units):
             def fn(s):
-                if path(s) != "decode":
+                if not (by_units(s) if units else by_splits(s)):
                     return 0
-                return self._decode_scratch(s.workspace, s.n_tokens, s.n_seqs, meta(s).host["max_splits"],
-                                            "_" + key)[i].data_ptr()
+                parts = meta(s).host["max_parts" if units else "max_splits"]
+                return self._decode_scratch(s.workspace, s.n_tokens, s.n_seqs, parts,
+                                            ("_units_" if units else "_") + key)[i].data_ptr()
             return fn
+        cu_q = b.param("cu_q", lambda s: s.cu_q.data_ptr())
+        kv_before = b.param("kv_before", lambda s: s.kv_before.data_ptr())
+        b.emit(OP_DECODE_ATTENTION_UNITS,
+               [q, cache.k, cache.v, cache.k.shape[0], table, bt_stride, cu_q, kv_before,
+                b.param(f"decode_units_{key}", lambda s: meta(s).arrays["decode_units"].data_ptr() if by_units(s) else 0),
+                b.param(f"decode_n_work_{key}", lambda s: meta(s).arrays["decode_n_work"].data_ptr() if by_units(s) else 0),
+                b.param(f"decode_max_work_{key}", lambda s: meta(s).arrays["decode_units"].shape[0] * nkv if by_units(s) else 0),
+                b.param(f"decode_grid_{key}", lambda s: meta(s).host["decode_grid"] if by_units(s) else 0),
+                b.param(f"decode_units_acc_{key}", dec(0, True)), b.param(f"decode_units_ml_{key}", dec(1, True)),
+                out, b.param(f"decode_units_done_{key}", dec(2, True)), nh, nkv, D, page, scale, window,
+                b.param(f"decode_max_parts_{key}", lambda s: meta(s).host["max_parts"] if by_units(s) else 0),
+                ops.tc_error_word(self.device)],
+               cond=b.param(f"attention_decode_units_{key}", lambda s: int(by_units(s))))
         b.emit(OP_DECODE_ATTENTION,
-               [q, cache.k, cache.v, table, bt_stride, b.param("cu_q", lambda s: s.cu_q.data_ptr()),
-                b.param("kv_before", lambda s: s.kv_before.data_ptr()), b.param("n_seqs", lambda s: s.n_seqs),
-                b.param(f"decode_acc_{key}", dec(0)), b.param(f"decode_ml_{key}", dec(1)),
-                out, b.param(f"decode_done_{key}", dec(2)), nh, nkv, D, page, scale, window,
+               [q, cache.k, cache.v, table, bt_stride, cu_q, kv_before, b.param("n_seqs", lambda s: s.n_seqs),
+                b.param(f"decode_acc_{key}", dec(0, False)), b.param(f"decode_ml_{key}", dec(1, False)),
+                out, b.param(f"decode_done_{key}", dec(2, False)), nh, nkv, D, page, scale, window,
                 b.param(f"split_keys_{key}", lambda s: meta(s).host["split_keys"]),
                 b.param(f"max_splits_{key}", lambda s: meta(s).host["max_splits"]), ops.tc_error_word(self.device)],
-               cond=b.param(f"attention_decode_{key}", lambda s: int(path(s) == "decode")))
+               cond=b.param(f"attention_decode_{key}", lambda s: int(by_splits(s))))
 
         # prompt kernels: the step's work units for this head grouping, scratch for the tiles with several chunks
         def pf(i):
@@ -309,6 +354,15 @@ class GroupedQueryAttention:
         meta = self._meta(step)
         path, ws = meta.host["path"], step.workspace
         split_keys, max_splits = meta.host["split_keys"], meta.host["max_splits"]
+        if path == "decode" and "decode_units" in meta.arrays:
+            max_parts = meta.host["max_parts"]
+            part_acc, part_ml, done = self._decode_scratch(ws, q.shape[0], step.n_seqs, max_parts, "_units")
+            ops.decode_attention_units_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
+                                            step.kv_before, meta.arrays["decode_units"], meta.arrays["decode_n_work"],
+                                            out, scale=self.scale, window=self.window, max_parts=max_parts,
+                                            grid=meta.host["decode_grid"], part_acc=part_acc, part_ml=part_ml,
+                                            done=done)
+            return
         if path == "decode":
             part_acc, part_ml, done = self._decode_scratch(ws, q.shape[0], step.n_seqs, max_splits)
             ops.decode_attention_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,

@@ -103,3 +103,73 @@ def choose_chunk(q_lens: np.ndarray, starts: np.ndarray, group_size: int, kv_hea
         if chunk >= longest or chunk >= (1 << 15):
             return best
         chunk *= 2
+
+
+# --- decode: units of whole 64-key stages for the persistent kernel ------------------------------------------------
+
+DECODE_STAGE_KEYS = 64          # keys of a stage of the decode kernel
+DECODE_MAX_UNIT_STAGES = 32     # most stages the kernel takes in one unit
+DECODE_MIN_PARTS = 16           # partial results a request may have at least (the scratch is sized by the cap)
+_UNIT_CANDIDATES = np.array([1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 20, 24, 28, 32], dtype=np.int64)
+
+
+def decode_parts_cap(max_kv_len: int) -> int:
+    """The most units a request of up to ``max_kv_len`` keys is ever cut into: what the scratch for the partial
+    results is sized by where it cannot follow the step (a captured graph)."""
+    stages = -(-max(int(max_kv_len), 1) // DECODE_STAGE_KEYS)
+    return max(DECODE_MIN_PARTS, -(-stages // DECODE_MAX_UNIT_STAGES))
+
+
+def decode_units(q_lens: np.ndarray, starts: np.ndarray, window: int, *, kv_heads: int, slots: int, cap: int,
+                 head_dim: int = 128, rows: int | None = None) -> tuple[np.ndarray, int, int]:
+    """Cut every request's keys into units for the persistent decode kernel. Returns (records, n_units, max_parts):
+    records int32 [n, 4] = {request, first stage, end stage, part | parts << 16}, longest first, padded with zero
+    rows to ``rows`` when given.
+
+    A request whose rows see keys lo .. p (lo the window's start) has the stages lo // 64 .. p // 64; they are
+    divided evenly among ``parts`` units. The unit length is the one (of a short list) for which the step takes
+    the least time by this model: the grid's ``slots`` blocks take the (unit, kv head) items round-robin, so a
+    step of ``items`` takes ceil(items / slots) rounds of the longest unit's stages (2 us a stage of 128-wide
+    heads) plus a fixed cost per unit (its first copies' latency and its partial result: about 3 us), and the
+    merge of a request's partials at the end costs 1.5 us and 0.75 us a part (measured: 4 parts 4.5 us, 7 parts
+    6.7 us; a request in one unit writes its result itself). Short units fill the last
+    round better and cost more partials; the model picks between them (27 requests of 4,400 keys,
+    4 kv heads, 444 slots: 9 stages a unit, 864 items in 2 rounds, where 8 stages would need 3)."""
+    q_lens = np.asarray(q_lens, dtype=np.int64)
+    starts = np.asarray(starts, dtype=np.int64)
+    S = int(q_lens.size)
+    p_max = starts + np.maximum(q_lens, 1) - 1
+    lo = np.maximum(0, starts - window + 1) if window > 0 else np.zeros(S, dtype=np.int64)
+    first = lo // DECODE_STAGE_KEYS
+    n = p_max // DECODE_STAGE_KEYS + 1 - first
+    n_max = int(n.max()) if S else 1
+    u_min = max(1, -(-n_max // cap))
+    if u_min > DECODE_MAX_UNIT_STAGES:
+        raise ValueError(f"a request of {n_max} stages of keys does not fit {cap} units of {DECODE_MAX_UNIT_STAGES} stages")
+    stage_us = 2.0 * head_dim / 128          # a stage of 64 keys when every block of a multiprocessor streams
+    cand = _UNIT_CANDIDATES[(_UNIT_CANDIDATES >= u_min) & (_UNIT_CANDIDATES < n_max)]
+    cand = np.append(cand, min(max(n_max, u_min), DECODE_MAX_UNIT_STAGES))          # (one unit a request, if it may be)
+    parts_c = -(-n[None, :] // cand[:, None])                                       # [candidates, requests]
+    items = parts_c.sum(axis=1) * kv_heads
+    longest = (-(-n[None, :] // parts_c)).max(axis=1)
+    most = parts_c.max(axis=1)
+    merge_us = np.where(most > 1, 1.5 + 0.75 * most, 0.0)                           # the last unit counts and merges
+    cost = -(-items // slots) * (longest * stage_us + 3.0) + merge_us
+    best_u = int(cand[len(cost) - 1 - int(np.argmin(cost[::-1]))])                  # (ties: the longer unit)
+    parts = -(-n // best_u)
+    total = int(parts.sum())
+    req = np.repeat(np.arange(S, dtype=np.int64), parts)
+    j = np.arange(total, dtype=np.int64) - np.repeat(np.cumsum(parts) - parts, parts)
+    base, extra = (n // parts)[req], (n % parts)[req]
+    begin = first[req] + j * base + np.minimum(j, extra)
+    size = base + (j < extra)
+    records = np.stack([req, begin, begin + size, j | (parts[req] << 16)], axis=1).astype(np.int32)
+    records = records[np.argsort(-size, kind="stable")]
+    max_parts = int(parts.max()) if S else 1
+    if rows is not None:
+        if total > rows:
+            raise ValueError(f"{total} units, room for {rows}")
+        padded = np.zeros((rows, 4), dtype=np.int32)
+        padded[:total] = records
+        records = padded
+    return records, total, max_parts
