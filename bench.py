@@ -293,6 +293,80 @@ def products_timed(tokens: int = 8) -> list[dict]:
 
 
 
+ATTENTION_CASES = {      # requests, keys a request, heads, kv heads, head size
+    "0.5b_b64": (64, 768, 14, 2, 64), "0.5b_b256": (256, 1000, 14, 2, 64), "1.5b_b64": (64, 1200, 12, 2, 128),
+    "7b_b27_long": (27, 4400, 28, 4, 128), "7b_b8_long": (8, 4400, 28, 4, 128), "7b_b64_ragged": (64, 4000, 28, 4, 128),
+}
+
+
+def decode_attention_timed(case: str, reps: int = 5, page: int = 16) -> dict:
+    """Profiling aid (--only decode_attention:<case>): the decode attention kernel alone over a shuffled paged cache,
+    one new token a request, by host-made units (the engine's plan) and by fixed splits of 512 keys; ten launches
+    in a captured graph a repetition, so that the time is the device's. "ragged" cases draw the lengths from a
+    quarter of the named one up to it."""
+    import numpy as np
+    import torch
+    from tokenmill_b200.kernels import ops
+    from tokenmill_b200.parts.attention_plan import decode_parts_cap, decode_units
+    S, ctx, nh, nkv, D = ATTENTION_CASES[case]
+    dev = torch.device("cuda:0")
+    lens = np.random.default_rng(0).integers(ctx // 4, ctx, S) if "ragged" in case else np.full(S, ctx)
+    pages_seq = -(-(ctx + 1) // page)
+    n_pages = S * pages_seq + 1
+    kc = (torch.randn(n_pages, page, nkv, D, device=dev) * 0.5).bfloat16()
+    vc = (torch.randn(n_pages, page, nkv, D, device=dev) * 0.5).bfloat16()
+    table = (torch.randperm(n_pages - 1, device=dev).int() + 1)[: S * pages_seq].view(S, pages_seq).contiguous()
+    q = torch.randn(S, nh, D, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    cu = torch.arange(S + 1, device=dev, dtype=torch.int32)
+    before = torch.from_numpy(lens.astype(np.int32)).to(dev)
+    done = torch.zeros(S * nkv, dtype=torch.int32, device=dev)
+    slots = ops.decode_units_slots(D, dev)
+    rec, n_units, max_parts = decode_units(np.ones(S, int), lens, 0, kv_heads=nkv, slots=slots,
+                                           cap=decode_parts_cap(ctx + 1), head_dim=D)
+    units = torch.from_numpy(rec).to(dev)
+    n_work = torch.tensor([n_units * nkv], dtype=torch.int32, device=dev)
+    split, max_splits = 512, -(-(ctx + 1) // 512)
+    parts = max(max_parts, max_splits)
+    acc = torch.empty(S * nh * parts * D, device=dev)
+    ml = torch.empty(S * nh * parts * 2, device=dev)
+
+    def by_units():
+        ops.decode_attention_units_bf16(q, kc, vc, table, cu, before, units, n_work, out, scale=D ** -0.5, window=0,
+                                        max_parts=max_parts, grid=min(slots, n_units * nkv), part_acc=acc, part_ml=ml,
+                                        done=done)
+
+    def by_splits():
+        ops.decode_attention_bf16(q, kc, vc, table, cu, before, S, out, scale=D ** -0.5, window=0, split_keys=split,
+                                  max_splits=max_splits, part_acc=acc, part_ml=ml, done=done)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ops.tc_check(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(10):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); g.replay(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 100)
+        return sorted(ts)[reps // 2]
+
+    nbytes = int((lens + 1).sum()) * nkv * D * 2 * 2
+    t_units, t_splits = timed(by_units), timed(by_splits)
+    return {"only": "decode_attention", "case": case, "requests": S, "keys": ctx, "heads": nh, "kv_heads": nkv,
+            "head_dim": D, "page": page, "kv_mb": round(nbytes / 1e6, 1), "units": n_units, "parts_a_request": max_parts,
+            "stages_a_unit": int((rec[:, 2] - rec[:, 1]).max()), "units_us": round(t_units, 1),
+            "units_tb_s": round(nbytes / t_units / 1e6, 2), "splits_of_512_us": round(t_splits, 1),
+            "splits_tb_s": round(nbytes / t_splits / 1e6, 2)}
+
+
 def bench_config(layers: int, mean_ctx: float, extra: dict) -> dict:
     """The ``config`` object of the JSON line (flat, at most 20 keys), the same keys in both arms."""
     cfg = {"model": f"{MODEL_LABEL} sizes", "layers": layers, "layers_in_named_config": SIZES["num_hidden_layers"],
@@ -324,6 +398,11 @@ def run_ours(args) -> dict:
     if args.only == "products":
         for row in products_timed():
             print(json.dumps(row))
+        return {}
+    if args.only.startswith("decode_attention"):
+        cases = [args.only.split(":", 1)[1]] if ":" in args.only else list(ATTENTION_CASES)
+        for case in cases:
+            print(json.dumps(decode_attention_timed(case)))
         return {}
     layers = args.layers or SIZES["num_hidden_layers"]
     pk, pk_kind = peaks()
@@ -579,7 +658,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
     ap.add_argument("--sizes", default="", help="another named size (qwen2.5-1.5b, qwen2.5-7b) instead of Qwen2.5-0.5B")
-    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>' or 'products' and print its time")
+    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>', 'products' or "
+                         "'decode_attention[:<case>]' and print its time")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--no-skip", action="store_true", help="profiling aid: time the decode steps right behind the prompt")
