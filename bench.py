@@ -299,11 +299,12 @@ ATTENTION_CASES = {      # requests, keys a request, heads, kv heads, head size
 }
 
 
-def decode_attention_timed(case: str, reps: int = 5, page: int = 16) -> dict:
+def decode_attention_timed(case: str, reps: int = 5, page: int = 16, sequential: bool = False) -> dict:
     """Profiling aid (--only decode_attention:<case>): the decode attention kernel alone over a shuffled paged cache,
     one new token a request, by host-made units (the engine's plan) and by fixed splits of 512 keys; ten launches
     in a captured graph a repetition, so that the time is the device's. "ragged" cases draw the lengths from a
-    quarter of the named one up to it."""
+    quarter of the named one up to it. ``decode_attention:<case>:sequential`` lays each request's pages one after
+    the other in the pool instead of shuffling them."""
     import numpy as np
     import torch
     from tokenmill_b200.kernels import ops
@@ -313,9 +314,14 @@ def decode_attention_timed(case: str, reps: int = 5, page: int = 16) -> dict:
     lens = np.random.default_rng(0).integers(ctx // 4, ctx, S) if "ragged" in case else np.full(S, ctx)
     pages_seq = -(-(ctx + 1) // page)
     n_pages = S * pages_seq + 1
-    kc = (torch.randn(n_pages, page, nkv, D, device=dev) * 0.5).bfloat16()
-    vc = (torch.randn(n_pages, page, nkv, D, device=dev) * 0.5).bfloat16()
-    table = (torch.randperm(n_pages - 1, device=dev).int() + 1)[: S * pages_seq].view(S, pages_seq).contiguous()
+    nbytes = int((lens + 1).sum()) * nkv * D * 2 * 2
+    # As many caches as exceed the L2 together, one after the other through the ten launches of a repetition (a
+    # model's layers each have their own): every launch reads its keys and values from memory.
+    copies = min(10, max(1, -(-(300 << 20) // nbytes)))
+    caches = [((torch.randn(n_pages, page, nkv, D, device=dev) * 0.5).bfloat16(),
+               (torch.randn(n_pages, page, nkv, D, device=dev) * 0.5).bfloat16()) for _ in range(copies)]
+    order = torch.arange(n_pages - 1, device=dev) if sequential else torch.randperm(n_pages - 1, device=dev)
+    table = (order.int() + 1)[: S * pages_seq].view(S, pages_seq).contiguous()
     q = torch.randn(S, nh, D, device=dev).bfloat16()
     out = torch.empty_like(q)
     cu = torch.arange(S + 1, device=dev, dtype=torch.int32)
@@ -331,24 +337,24 @@ def decode_attention_timed(case: str, reps: int = 5, page: int = 16) -> dict:
     acc = torch.empty(S * nh * parts * D, device=dev)
     ml = torch.empty(S * nh * parts * 2, device=dev)
 
-    def by_units():
+    def by_units(kc, vc):
         ops.decode_attention_units_bf16(q, kc, vc, table, cu, before, units, n_work, out, scale=D ** -0.5, window=0,
                                         max_parts=max_parts, grid=min(slots, n_units * nkv), part_acc=acc, part_ml=ml,
                                         done=done)
 
-    def by_splits():
+    def by_splits(kc, vc):
         ops.decode_attention_bf16(q, kc, vc, table, cu, before, S, out, scale=D ** -0.5, window=0, split_keys=split,
                                   max_splits=max_splits, part_acc=acc, part_ml=ml, done=done)
 
     def timed(fn):
-        for _ in range(3):
-            fn()
+        for kc, vc in caches:
+            fn(kc, vc)
         torch.cuda.synchronize()
         ops.tc_check(dev)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            for _ in range(10):
-                fn()
+            for i in range(10):
+                fn(*caches[i % copies])
         g.replay()
         torch.cuda.synchronize()
         ts = []
@@ -358,10 +364,10 @@ def decode_attention_timed(case: str, reps: int = 5, page: int = 16) -> dict:
             ts.append(a.elapsed_time(b) * 100)
         return sorted(ts)[reps // 2]
 
-    nbytes = int((lens + 1).sum()) * nkv * D * 2 * 2
     t_units, t_splits = timed(by_units), timed(by_splits)
     return {"only": "decode_attention", "case": case, "requests": S, "keys": ctx, "heads": nh, "kv_heads": nkv,
-            "head_dim": D, "page": page, "kv_mb": round(nbytes / 1e6, 1), "units": n_units, "parts_a_request": max_parts,
+            "head_dim": D, "page": page, "pages": "sequential" if sequential else "shuffled", "kv_mb": round(nbytes / 1e6, 1),
+            "caches": copies, "units": n_units, "parts_a_request": max_parts,
             "stages_a_unit": int((rec[:, 2] - rec[:, 1]).max()), "units_us": round(t_units, 1),
             "units_tb_s": round(nbytes / t_units / 1e6, 2), "splits_of_512_us": round(t_splits, 1),
             "splits_tb_s": round(nbytes / t_splits / 1e6, 2)}
@@ -400,9 +406,10 @@ def run_ours(args) -> dict:
             print(json.dumps(row))
         return {}
     if args.only.startswith("decode_attention"):
-        cases = [args.only.split(":", 1)[1]] if ":" in args.only else list(ATTENTION_CASES)
+        parts = args.only.split(":")
+        cases = [parts[1]] if len(parts) > 1 and parts[1] else list(ATTENTION_CASES)
         for case in cases:
-            print(json.dumps(decode_attention_timed(case)))
+            print(json.dumps(decode_attention_timed(case, sequential="sequential" in parts[2:])))
         return {}
     layers = args.layers or SIZES["num_hidden_layers"]
     pk, pk_kind = peaks()

@@ -259,7 +259,18 @@ class ModelRunner:
     def _graph_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
                     token_rows: list[int] | None = None) -> torch.Tensor:
         n = len(entries)
-        sizes = [b for b in GRAPH_BATCH_SIZES if b < self.graph_max_batch] + [self.graph_max_batch]
+        if self.fused is not None:
+            # Steps of up to 16 tokens take the whole-step kernel, so graphs serve 17 and more requests: ONE graph of
+            # the largest batch for all of them. Padding costs little at these sizes, and a second captured graph
+            # costs more: once a process has captured library products twice, the kernels of every captured
+            # graph stop overlapping with the library kernels in front of them (measured on B200, CUDA 12.9: the
+            # same graph of 64 rows replays in 1.18 ms before and 1.29 ms after a graph of 32 rows is captured,
+            # which is its time with programmatic dependent launch switched off; an eager step, or a captured
+            # graph without library products, does not do that). With the one graph 17 / 32 / 64 requests take
+            # 1.18 / 1.22 / 1.26 ms a step; with graphs of 32 and 64 rows they took 1.33 / 1.36 / 1.37.
+            sizes = [self.graph_max_batch]
+        else:
+            sizes = [b for b in GRAPH_BATCH_SIZES if b < self.graph_max_batch] + [self.graph_max_batch]
         bucket = sizes[bisect.bisect_left(sizes, n)]
         if not self._graphs and bucket != sizes[-1]:
             # The largest batch is captured first: its warm-up makes every scratch buffer as large as any
