@@ -434,6 +434,30 @@ def test_tcgen05_linear(T, N, K):
     assert (out.float().cpu() - ref).abs().max() <= 1e-2 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("T,N,K", [(64, 896, 4864), (17, 896, 896), (100, 1536, 8960), (128, 3584, 18944), (33, 100, 72),
+                                   (64, 132, 200), (48, 896, 64)])
+def test_tcgen05_linear_added_into_a_float32_stream(T, N, K):
+    """The product of a step of a few dozen tokens, its K range cut over the chip and every piece added into the
+    32-bit stream: the stream's own values stay, rows beyond T stay untouched, twice in a row adds twice."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(T + N + K)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    base = torch.randn(T + 3, N, generator=g)
+    ref = base[:T] + x.float() @ w.float().T
+    stream = base.to(DEV)
+    assert ops.tc_add_ok(x.to(DEV), w.to(DEV), stream[:T]) == (K >= ops.TC_ADD_MIN_K)    # (the kernel takes short rows too)
+    ops.tc_linear_add(x.to(DEV), w.to(DEV), stream[:T])
+    ops.tc_check(stream.device)
+    got = stream.cpu()
+    assert (got[:T] - ref).abs().max() <= 1e-3 * float(ref.abs().max()) + 1e-5
+    assert torch.equal(got[T:], base[T:])
+    ops.tc_linear_add(x.to(DEV), w.to(DEV), stream[:T])
+    ops.tc_check(stream.device)
+    twice = base[:T] + 2 * (x.float() @ w.float().T)
+    assert (stream[:T].cpu() - twice).abs().max() <= 2e-3 * float(twice.abs().max()) + 1e-5
+
+
 @pytest.mark.parametrize("T,H,I", [(128, 64, 128), (2048, 896, 4864), (333, 1536, 8960), (200, 96, 160), (130, 72, 1000)])
 def test_tcgen05_gate_up_swiglu(T, H, I):
     ops = _ops()

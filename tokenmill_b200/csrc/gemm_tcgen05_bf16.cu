@@ -32,11 +32,13 @@ template <int BN> constexpr int t5_b_bytes() { return BN * kT5BK * 2; }         
 template <int BN> constexpr int t5_stage_bytes() { return kT5ABytes + t5_b_bytes<BN>(); }     // 48 or 32 KB
 template <int BN> constexpr int t5_stages() { return BN == 256 ? 4 : 6; }
 constexpr int kT5Threads = 256;
-enum : int { T5_STORE = 0, T5_SWIGLU = 1, T5_QKV = 2 };
+enum : int { T5_STORE = 0, T5_SWIGLU = 1, T5_QKV = 2, T5_ADD_F32 = 3 };
 
 struct T5Args {
   int T, N, K, mode;
   int n_tiles_m, n_tiles_n;
+  int n_splits, kb_per_split;   // the K range cut into n_splits pieces of kb_per_split blocks of 64 (1 piece: all of K)
+  float* out_f32;           // ADD_F32: [T, N] float32 that the product is added into (one atomic add per piece)
   __nv_bfloat16* out;       // STORE: [T, N]; SWIGLU: [T, inter]
   int ldo, inter;
   // QKV
@@ -80,6 +82,27 @@ __device__ __forceinline__ void t5_tile_rows(const T5Args& a, int tn, int& row_l
   }
 }
 
+// Tile number -> (row tile of tokens, tile column of weights, first and end block of its K range).
+struct T5Tile {
+  int tm, tn, kb0, kb1;
+};
+__device__ __forceinline__ T5Tile t5_tile(const T5Args& a, int tile, int n_kb) {
+  T5Tile t;
+  t.tm = tile % a.n_tiles_m;
+  const int rest = tile / a.n_tiles_m;
+  const int ks = rest % a.n_splits;
+  t.tn = rest / a.n_splits;
+  t.kb0 = ks * a.kb_per_split;
+  t.kb1 = a.n_splits > 1 ? min(n_kb, t.kb0 + a.kb_per_split) : n_kb;
+  return t;
+}
+
+// 16 bytes of float32 added to memory in one instruction.
+__device__ __forceinline__ void t5_red_add4(float* dst, const float* v) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+               "f"(v[3]) : "memory");
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                      const __grid_constant__ CUtensorMap map_w,
@@ -118,20 +141,47 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
   __syncthreads();
   t5_fence_after();
   const uint32_t tmem_base = s_tmem_base;
+  // (Launched with programmatic dependent launch where it follows a kernel of this library in a decode step: what
+  // stands above depends on no earlier kernel, and neither do the weights: the producer asks for its first tile's
+  // weight blocks before it waits for the kernel in front. Everything else may read what that kernel wrote.)
+  pdl_launch_dependents();
+  const bool producer = warp == 0 && lane == 0;
+  if (!producer) pdl_wait();
 
-  const int n_tiles = a.n_tiles_m * a.n_tiles_n;
+  const int n_tiles = a.n_tiles_m * a.n_tiles_n * a.n_splits;
   const int n_kb = (a.K + kT5BK - 1) / kT5BK;
 
-  if (warp == 0 && lane == 0) {
+  if (producer) {
     // ---- TMA producer ----
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    int pre = 0;                               // k-blocks of the first tile asked for ahead of the wait
+    if ((int)blockIdx.x < n_tiles) {
+      const T5Tile tl = t5_tile(a, blockIdx.x, n_kb);
+      int row_lo, row_hi;
+      t5_tile_rows<BN>(a, tl.tn, row_lo, row_hi);
+      pre = min(tl.kb1 - tl.kb0, kT5Stages);
+      for (int i = 0; i < pre; ++i) {          // (every stage is free at the start)
+        const uint32_t dst = ring + i * kT5StageBytes;
+        mbar_expect_tx(full_bar(i), kT5StageBytes);
+        tma_load_2d(dst + kT5ABytes, &map_w, (tl.kb0 + i) * kT5BK, row_lo, full_bar(i));
+        if (BN == 256) tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, (tl.kb0 + i) * kT5BK, row_hi, full_bar(i));
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(ring + i * kT5StageBytes, &map_x, (tl.kb0 + i) * kT5BK, tl.tm * kT5BM, full_bar(i));
+      stage = pre % kT5Stages;
+      if (pre == kT5Stages) phase ^= 1u;
+    } else {
+      pdl_wait();
+    }
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      const int tn = tile / a.n_tiles_m, tm = tile - tn * a.n_tiles_m;
+      const T5Tile tl = t5_tile(a, tile, n_kb);
+      const int tn = tl.tn, tm = tl.tm;
       int row_lo, row_hi;
       t5_tile_rows<BN>(a, tn, row_lo, row_hi);
-      for (int kb = 0; kb < n_kb && ok; ++kb) {
+      for (int kb = tl.kb0 + (tile == (int)blockIdx.x ? pre : 0); kb < tl.kb1 && ok; ++kb) {
         ok = mbar_wait(empty_bar(stage), phase ^ 1u, &s_abort, a.error, 1);
         if (!ok) break;
         const uint32_t dst = ring + stage * kT5StageBytes;
@@ -160,14 +210,15 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
       if (!ok) break;
       t5_fence_after();
       const uint32_t d_tmem = tmem_base + acc * kT5BN;
-      for (int kb = 0; kb < n_kb && ok; ++kb) {
+      const T5Tile tl = t5_tile(a, tile, n_kb);
+      for (int kb = tl.kb0; kb < tl.kb1 && ok; ++kb) {
         ok = mbar_wait(full_bar(stage), phase, &s_abort, a.error, 3);
         if (!ok) break;
         t5_fence_after();
         const uint32_t sa = ring + stage * kT5StageBytes, sb = sa + kT5ABytes;
 #pragma unroll
         for (int k = 0; k < kT5BK / 16; ++k)
-          t5_mma(d_tmem, t5_desc(sa + k * 32), t5_desc(sb + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          t5_mma(d_tmem, t5_desc(sa + k * 32), t5_desc(sb + k * 32), idesc, (kb != tl.kb0 || k != 0) ? 1u : 0u);
         t5_commit(empty_bar(stage));                   // the stage is free once these products are done
         if (++stage == kT5Stages) {
           stage = 0;
@@ -187,7 +238,8 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      const int tn = tile / a.n_tiles_m, tm = tile - tn * a.n_tiles_m;
+      const T5Tile tl = t5_tile(a, tile, n_kb);
+      const int tn = tl.tn, tm = tl.tm;
       ok = mbar_wait(tfull_bar(acc), acc_phase, &s_abort, a.error, 4);
       if (!ok) break;
       t5_fence_after();
@@ -209,6 +261,22 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
             } else {
               for (int j = 0; j < 32 && n + j < a.N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
             }
+          }
+        }
+      } else if (a.mode == T5_ADD_F32) {
+        // One piece of the K range: its sums are added into the 32-bit output (the residual stream), 16 bytes an
+        // instruction. (N is a multiple of 4 and the rows are 16-byte aligned: the launcher checks.)
+#pragma unroll 1
+        for (int c = 0; c < kT5BN; c += 32) {
+          float v[32];
+          t5_ld32(taddr + c, v);
+          t5_ld_wait();
+          const int n = tn * kT5BN + c;
+          if (row_ok && n < a.N) {
+            float* dst = a.out_f32 + (size_t)t * a.ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (n + j < a.N) t5_red_add4(dst + j, v + j);
           }
         }
       } else if (a.mode == T5_SWIGLU) {
@@ -362,6 +430,10 @@ static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, x, a.T, a.K, ldx) || !make_map(&map_w, w, a.N, a.K, a.K)) return 90006;
   a.n_tiles_m = (a.T + kT5BM - 1) / kT5BM;
+  if (a.n_splits <= 0) {
+    a.n_splits = 1;
+    a.kb_per_split = (a.K + kT5BK - 1) / kT5BK;
+  }
   const int n_sm = t5_sm_count();
   const int smem = t5_stages<BN>() * t5_stage_bytes<BN>() + 1024;
   static bool attr_set = false;
@@ -370,8 +442,10 @@ static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const int tiles = a.n_tiles_m * a.n_tiles_n;
+  const int tiles = a.n_tiles_m * a.n_tiles_n * a.n_splits;
   const int grid = tiles < n_sm ? tiles : n_sm;
+  if (a.mode == T5_ADD_F32)      // a decode step's product between kernels of this library
+    return launch_pdl(gemm_tcgen05_kernel<BN>, dim3(grid), dim3(kT5Threads), (size_t)smem, stream, map_x, map_w, a);
   gemm_tcgen05_kernel<BN><<<grid, kT5Threads, smem, stream>>>(map_x, map_w, a);
   return launch_status();
 }
@@ -393,6 +467,27 @@ extern "C" int tm_tc_linear(const void* x, int ldx, const void* w, void* out, in
   }
   a.n_tiles_n = (N + 255) / 256;
   return tmk::t5_launch<256>(a, x, ldx, w, stream);
+}
+
+// out [T, N] (float32, row stride ldo) += x [T, K] . w [N, K]^T: a projection added into the 32-bit residual stream
+// (src/infer/model/qwen2.py:20-22), for steps of a few dozen tokens, where a product is one pass over the weights
+// and has too few tiles of 128 columns to fill the chip: the K range is cut so that about one (tile, piece) falls
+// to every multiprocessor, and every piece adds its sums with vector atomics (so the order of the sum, and with
+// it the last bits, varies from run to run). N a multiple of 4; out 16-byte aligned, ldo a multiple of 4.
+extern "C" int tm_tc_linear_add_f32(const void* x, int ldx, const void* w, float* out, int ldo, int T, int N, int K,
+                                    int* error, cudaStream_t stream) {
+  tmk::T5Args a{};
+  a.T = T; a.N = N; a.K = K; a.mode = tmk::T5_ADD_F32;
+  a.out_f32 = out; a.ldo = ldo; a.error = error;
+  if (N % 4 || ldo % 4 || (reinterpret_cast<uintptr_t>(out) & 15)) return TM_ERR_UNSUPPORTED_SHAPE;
+  a.n_tiles_n = (N + 127) / 128;
+  const int tiles = ((T + tmk::kT5BM - 1) / tmk::kT5BM) * a.n_tiles_n;
+  const int n_kb = (K + tmk::kT5BK - 1) / tmk::kT5BK;
+  int splits = tmk::t5_sm_count() / (tiles > 0 ? tiles : 1);
+  splits = splits < 1 ? 1 : (splits > n_kb ? n_kb : splits);
+  a.kb_per_split = (n_kb + splits - 1) / splits;
+  a.n_splits = (n_kb + a.kb_per_split - 1) / a.kb_per_split;
+  return tmk::t5_launch<128>(a, x, ldx, w, stream);
 }
 
 // out [T, I] = silu(x . gate^T) * (x . up^T); w [2 I, K] with the gate rows first; I a multiple of 8.

@@ -54,6 +54,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_skinny_qkv_rope_write": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "tm_skinny_gate_up_swiglu": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
     "tm_tc_linear": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
+    "tm_tc_linear_add_f32": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "tm_tc_gate_up_swiglu": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "tm_tc_qkv_rope_write": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "tm_decode_fused": [_P, _P],

@@ -668,6 +668,34 @@ def tc_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None)
     return out
 
 
+_TC_ADD = os.environ.get("TOKENMILL_TC_ADD", "1") != "0"
+_TC_ADD_ALL = os.environ.get("TOKENMILL_TC_ADD", "1") == "all"
+TC_ADD_MIN_TOKENS, TC_ADD_MAX_TOKENS = 17, 128
+TC_ADD_MIN_K = 2048     # shorter rows: the library's kernel is as fast (o_proj of 896: 4.9 us against 6 us here)
+
+
+def tc_add_ok(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor | None) -> bool:
+    """Whether ``tc_linear_add`` takes this projection: a step of 17 to 128 tokens (below, the weight-streaming
+    kernels; above, the library product is one pass over the weights at full tiles anyway), rows long enough
+    that cutting them pays (the down projection: 7.9 us against the library's 9.5 at 64 x 4864 -> 896), bfloat16
+    operands, a 32-bit residual stream of the product's shape. TOKENMILL_TC_ADD=0 switches it off; =all takes
+    short rows too."""
+    return (_TC_ADD and resid is not None and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.dim() == 2 and TC_ADD_MIN_TOKENS <= x.shape[0] <= TC_ADD_MAX_TOKENS and x.shape[1] % 8 == 0
+            and (x.shape[1] >= TC_ADD_MIN_K or _TC_ADD_ALL)
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
+            and w.data_ptr() % 16 == 0 and w.shape[0] % 4 == 0 and resid.dtype == torch.float32
+            and resid.shape == (x.shape[0], w.shape[0]) and resid.stride(1) == 1 and resid.stride(0) % 4 == 0
+            and resid.data_ptr() % 16 == 0)
+
+
+def tc_linear_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor) -> None:
+    """resid [T, N] float32 += x [T, K] . w [N, K]^T on tcgen05, the K range cut over the chip (atomic adds)."""
+    T, K = x.shape
+    lib.call("tm_tc_linear_add_f32", x.data_ptr(), x.stride(0), w.data_ptr(), _req(resid, "resid", torch.float32),
+             resid.stride(0), T, w.shape[0], K, _tc_flag(x.device).data_ptr(), _stream())
+
+
 def tc_gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out [T, I] = silu(x . gate^T) * (x . up^T) on tcgen05; the [T, 2I] product stays in tensor memory."""
     T, K = x.shape

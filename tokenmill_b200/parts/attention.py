@@ -180,7 +180,10 @@ class GroupedQueryAttention:
 
     # --- run ------------------------------------------------------------------------------------
 
-    def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache) -> torch.Tensor:
+    adds_to_residual = True      # forward(..., residual=stream) may add its output into the stream and return None
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: LayerCache,
+                residual: torch.Tensor | None = None) -> torch.Tensor | None:
         T = x.shape[0]
         q = torch.empty((T, self.nh, self.D), dtype=self.dtype, device=x.device)
         slot_map = step.slot_maps[cache.group] if cache.writes else None
@@ -215,6 +218,10 @@ class GroupedQueryAttention:
             return ops.skinny_linear(flat, self.w_o, k_splits=ops.skinny_k_splits(T, self.q_size))
         if ops.tc_narrow_ok(flat, self.w_o):
             return ops.tc_linear(flat, self.w_o)
+        if ops.tc_add_ok(flat, self.w_o, residual):
+            # a few dozen tokens: the output projection cut along K over the whole chip, added into the stream
+            ops.tc_linear_add(flat, self.w_o, residual)
+            return None
         return ops.linear(flat, self.w_o)
 
     def emit(self, b, x, cache: LayerCache):

@@ -29,7 +29,10 @@ class Pending:
     @classmethod
     def of(cls, y: torch.Tensor) -> "Pending":
         """A part's output: [T, H] in the activation dtype, or [n, T, H] float32 partial products of a
-        matrix product whose K range was cut (the norm that follows adds them up in index order)."""
+        matrix product whose K range was cut (the norm that follows adds them up in index order), or None
+        when the part has added its output into the stream itself."""
+        if y is None:
+            return cls()
         return cls(partials=y) if y.dim() == 3 else cls(branch=y)
 
     def kwargs(self) -> dict:
@@ -42,10 +45,14 @@ class PreNormBlock:
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
 
     def forward(self, resid: torch.Tensor, pending: Pending, step: StepInputs, cache: LayerCache) -> Pending:
+        # A part that says ``adds_to_residual`` is offered the stream: it may add its output there itself (its
+        # last product's epilogue) and return None; the norm that follows then has nothing left to add.
         normed = self.mixer_norm.forward(resid, **pending.kwargs())
-        mixed = Pending.of(self.mixer.forward(normed, step, cache))
+        offer = {"residual": resid} if getattr(self.mixer, "adds_to_residual", False) else {}
+        mixed = Pending.of(self.mixer.forward(normed, step, cache, **offer))
         normed = self.feed_forward_norm.forward(resid, **mixed.kwargs())
-        return Pending.of(self.feed_forward.forward(normed, step))
+        offer = {"residual": resid} if getattr(self.feed_forward, "adds_to_residual", False) else {}
+        return Pending.of(self.feed_forward.forward(normed, step, **offer))
 
 
     def emit(self, b, resid, pending: dict, cache: LayerCache) -> dict:

@@ -35,7 +35,10 @@ class SwiGLUFeedForward:
         self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
-    def forward(self, x: torch.Tensor, step: StepInputs | None = None) -> torch.Tensor:
+    adds_to_residual = True      # forward(..., residual=stream) may add its output into the stream and return None
+
+    def forward(self, x: torch.Tensor, step: StepInputs | None = None,
+                residual: torch.Tensor | None = None) -> torch.Tensor | None:
         T = x.shape[0]
         act = torch.empty((T, self.intermediate_size), dtype=self.dtype, device=x.device)
         if ops.skinny_ok(x, self.w_gate_up) and ops.skinny_ok(act, self.w_down, allow_split=True):
@@ -49,6 +52,10 @@ class SwiGLUFeedForward:
             return ops.tc_linear(act, self.w_down) if ops.tc_ok(act, self.w_down) else ops.linear(act, self.w_down)
         gu = ops.linear(x, self.w_gate_up)
         ops.swiglu(gu, act)
+        if ops.tc_add_ok(act, self.w_down, residual):
+            # a few dozen tokens: the down projection cut along K over the whole chip, added into the stream
+            ops.tc_linear_add(act, self.w_down, residual)
+            return None
         return ops.linear(act, self.w_down)
 
 
