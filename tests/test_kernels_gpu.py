@@ -458,7 +458,8 @@ def test_tcgen05_linear_added_into_a_float32_stream(T, N, K):
     assert (stream[:T].cpu() - twice).abs().max() <= 2e-3 * float(twice.abs().max()) + 1e-5
 
 
-@pytest.mark.parametrize("T,H,I", [(128, 64, 128), (2048, 896, 4864), (333, 1536, 8960), (200, 96, 160), (130, 72, 1000)])
+@pytest.mark.parametrize("T,H,I", [(128, 64, 128), (2048, 896, 4864), (333, 1536, 8960), (200, 96, 160), (130, 72, 1000),
+                                   (64, 896, 4864), (17, 1536, 8960), (100, 3584, 18944), (33, 72, 200), (128, 96, 40)])
 def test_tcgen05_gate_up_swiglu(T, H, I):
     ops = _ops()
     g = torch.Generator().manual_seed(T + H + I)

@@ -28,9 +28,9 @@ namespace tmk {
 // heads of 64 has 80 tiles of 256 columns and 144 of 128: one wave that fills the chip).
 constexpr int kT5BM = 128, kT5BK = 64;
 constexpr int kT5ABytes = kT5BM * kT5BK * 2;            // 16 KB
-template <int BN> constexpr int t5_b_bytes() { return BN * kT5BK * 2; }                       // 32 or 16 KB
-template <int BN> constexpr int t5_stage_bytes() { return kT5ABytes + t5_b_bytes<BN>(); }     // 48 or 32 KB
-template <int BN> constexpr int t5_stages() { return BN == 256 ? 4 : 6; }
+template <int BN> constexpr int t5_b_bytes() { return BN * kT5BK * 2; }                       // 32, 16 or 8 KB
+template <int BN> constexpr int t5_stage_bytes() { return kT5ABytes + t5_b_bytes<BN>(); }     // 48, 32 or 24 KB
+template <int BN> constexpr int t5_stages() { return BN == 256 ? 4 : (BN == 128 ? 6 : 8); }
 constexpr int kT5Threads = 256;
 enum : int { T5_STORE = 0, T5_SWIGLU = 1, T5_QKV = 2, T5_ADD_F32 = 3 };
 
@@ -52,6 +52,7 @@ struct T5Args {
   __nv_bfloat16* vcache;
   int nh, nkv, D, n_pos;
   int* error;               // device word, 0 when all is well
+  int pdl;                  // launched with programmatic dependent launch (a decode step's product)
 };
 
 // --- PTX wrappers (the rest are in tcgen05_util.cuh) -----------------------------------------------
@@ -70,12 +71,13 @@ __device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float* v) 
   *reinterpret_cast<uint4*>(dst) = o;
 }
 
-// First weight row of each 128-row half of tile column `tn` (a tile of 128 columns has only the first).
+// First weight row of each half of tile column `tn` (a plain tile of 128 columns has only the first). A SwiGLU
+// tile is BN / 2 gate rows and the matching up rows.
 template <int BN>
 __device__ __forceinline__ void t5_tile_rows(const T5Args& a, int tn, int& row_lo, int& row_hi) {
   if (a.mode == T5_SWIGLU) {
-    row_lo = tn * 128;              // gate rows
-    row_hi = a.inter + tn * 128;    // the matching up rows
+    row_lo = tn * (BN / 2);              // gate rows
+    row_hi = a.inter + tn * (BN / 2);    // the matching up rows
   } else {
     row_lo = tn * BN;
     row_hi = row_lo + 128;
@@ -157,6 +159,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
     uint32_t phase = 0;
     bool ok = true;
     int pre = 0;                               // k-blocks of the first tile asked for ahead of the wait
+    const bool two_boxes = BN == 256 || a.mode == T5_SWIGLU;   // the weight tile is two boxes of BN / 2 rows
     if ((int)blockIdx.x < n_tiles) {
       const T5Tile tl = t5_tile(a, blockIdx.x, n_kb);
       int row_lo, row_hi;
@@ -166,7 +169,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
         const uint32_t dst = ring + i * kT5StageBytes;
         mbar_expect_tx(full_bar(i), kT5StageBytes);
         tma_load_2d(dst + kT5ABytes, &map_w, (tl.kb0 + i) * kT5BK, row_lo, full_bar(i));
-        if (BN == 256) tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, (tl.kb0 + i) * kT5BK, row_hi, full_bar(i));
+        if (two_boxes) tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, (tl.kb0 + i) * kT5BK, row_hi, full_bar(i));
       }
       pdl_wait();
       for (int i = 0; i < pre; ++i)
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
         mbar_expect_tx(full_bar(stage), kT5StageBytes);
         tma_load_2d(dst, &map_x, kb * kT5BK, tm * kT5BM, full_bar(stage));
         tma_load_2d(dst + kT5ABytes, &map_w, kb * kT5BK, row_lo, full_bar(stage));
-        if (BN == 256) tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, kb * kT5BK, row_hi, full_bar(stage));
+        if (two_boxes) tma_load_2d(dst + kT5ABytes + kT5BBytes / 2, &map_w, kb * kT5BK, row_hi, full_bar(stage));
         if (++stage == kT5Stages) {
           stage = 0;
           phase ^= 1u;
@@ -280,13 +283,14 @@ __global__ void __launch_bounds__(kT5Threads, 1) gemm_tcgen05_kernel(const __gri
           }
         }
       } else if (a.mode == T5_SWIGLU) {
+        constexpr int HALF = BN / 2;       // gate columns, then as many up columns
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
+        for (int c = 0; c < HALF; c += 32) {
           float g[32], u[32];
           t5_ld32(taddr + c, g);
-          t5_ld32(taddr + 128 + c, u);
+          t5_ld32(taddr + HALF + c, u);
           t5_ld_wait();
-          const int n = tn * 128 + c;
+          const int n = tn * HALF + c;
           if (row_ok && n < a.inter) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) g[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
@@ -397,14 +401,15 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A [rows, K] bfloat16 row-major matrix viewed through boxes of 128 rows x 64 columns, 128-byte swizzle;
+// A [rows, K] bfloat16 row-major matrix viewed through boxes of 128 (or box_rows) rows x 64 columns, 128-byte swizzle;
 // parts of a box outside the matrix read as zero.
-static bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long row_stride_elems) {
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long row_stride_elems,
+                     int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kT5BK, 128u};
+  const cuuint32_t box[2] = {(cuuint32_t)kT5BK, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1u, 1u};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -428,7 +433,7 @@ static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream
     return TM_ERR_UNSUPPORTED_SHAPE;     // TMA wants 16-byte aligned rows
   if (!a.error) return TM_ERR_SCRATCH_TOO_SMALL;
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, x, a.T, a.K, ldx) || !make_map(&map_w, w, a.N, a.K, a.K)) return 90006;
+  if (!make_map(&map_x, x, a.T, a.K, ldx) || !make_map(&map_w, w, a.N, a.K, a.K, BN == 64 ? 32 : 128)) return 90006;
   a.n_tiles_m = (a.T + kT5BM - 1) / kT5BM;
   if (a.n_splits <= 0) {
     a.n_splits = 1;
@@ -444,7 +449,7 @@ static int t5_launch(T5Args a, const void* x, int ldx, const void* w, cudaStream
   }
   const int tiles = a.n_tiles_m * a.n_tiles_n * a.n_splits;
   const int grid = tiles < n_sm ? tiles : n_sm;
-  if (a.mode == T5_ADD_F32)      // a decode step's product between kernels of this library
+  if (a.mode == T5_ADD_F32 || a.pdl)      // a decode step's product between kernels of this library
     return launch_pdl(gemm_tcgen05_kernel<BN>, dim3(grid), dim3(kT5Threads), (size_t)smem, stream, map_x, map_w, a);
   gemm_tcgen05_kernel<BN><<<grid, kT5Threads, smem, stream>>>(map_x, map_w, a);
   return launch_status();
@@ -495,9 +500,16 @@ extern "C" int tm_tc_gate_up_swiglu(const void* x, int ldx, const void* w, void*
                                     int inter, int* error, cudaStream_t stream) {
   tmk::T5Args a{};
   a.T = T; a.N = 2 * inter; a.K = K; a.mode = tmk::T5_SWIGLU; a.inter = inter;
-  a.n_tiles_n = (inter + 127) / 128;
   a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.error = error;
   if (ldo % 8 || inter % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (T <= tmk::kT5BM) {
+    // One row tile of tokens (a decode step): tiles of 32 gate and 32 up rows, so that there is one for every
+    // multiprocessor (152 for 4,864 rows), launched with programmatic dependent launch.
+    a.n_tiles_n = (inter + 31) / 32;
+    a.pdl = 1;
+    return tmk::t5_launch<64>(a, x, ldx, w, stream);
+  }
+  a.n_tiles_n = (inter + 127) / 128;
   return tmk::t5_launch<256>(a, x, ldx, w, stream);
 }
 

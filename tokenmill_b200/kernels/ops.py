@@ -668,8 +668,8 @@ def tc_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None)
     return out
 
 
-_TC_ADD = os.environ.get("TOKENMILL_TC_ADD", "1") != "0"
-_TC_ADD_ALL = os.environ.get("TOKENMILL_TC_ADD", "1") == "all"
+_TC_ADD = os.environ.get("TOKENMILL_TC_DECODE", "1") != "0"
+_TC_ADD_ALL = os.environ.get("TOKENMILL_TC_DECODE", "1") == "all"
 TC_ADD_MIN_TOKENS, TC_ADD_MAX_TOKENS = 17, 128
 TC_ADD_MIN_K = 2048     # shorter rows: the library's kernel is as fast (o_proj of 896: 4.9 us against 6 us here)
 
@@ -678,7 +678,7 @@ def tc_add_ok(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor | None) -> b
     """Whether ``tc_linear_add`` takes this projection: a step of 17 to 128 tokens (below, the weight-streaming
     kernels; above, the library product is one pass over the weights at full tiles anyway), rows long enough
     that cutting them pays (the down projection: 7.9 us against the library's 9.5 at 64 x 4864 -> 896), bfloat16
-    operands, a 32-bit residual stream of the product's shape. TOKENMILL_TC_ADD=0 switches it off; =all takes
+    operands, a 32-bit residual stream of the product's shape. TOKENMILL_TC_DECODE=0 switches it off; =all takes
     short rows too."""
     return (_TC_ADD and resid is not None and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and x.dim() == 2 and TC_ADD_MIN_TOKENS <= x.shape[0] <= TC_ADD_MAX_TOKENS and x.shape[1] % 8 == 0
@@ -687,6 +687,18 @@ def tc_add_ok(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor | None) -> b
             and w.data_ptr() % 16 == 0 and w.shape[0] % 4 == 0 and resid.dtype == torch.float32
             and resid.shape == (x.shape[0], w.shape[0]) and resid.stride(1) == 1 and resid.stride(0) % 4 == 0
             and resid.data_ptr() % 16 == 0)
+
+
+def tc_swiglu_decode_ok(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
+    """Whether a step of 17 to 128 tokens takes its gate/up projection with the activation in the epilogue on
+    tcgen05 (tiles of 32 gate and 32 up rows, one for every multiprocessor) instead of the library product and
+    the activation kernel. Only with TOKENMILL_TC_DECODE=all: measured at 64 tokens, 896 -> 2 x 4864, the fused
+    kernel takes about 16 us against the library's 7.0 + 2.8 us (every tile reads all of x again, 14 blocks of K
+    one after the other), so a step of 64 requests takes 1.37 ms with it and 1.21 without."""
+    return (_TC_ADD_ALL and x.is_cuda and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and x.dim() == 2
+            and TC_ADD_MIN_TOKENS <= x.shape[0] <= TC_ADD_MAX_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w_gate_up.is_contiguous()
+            and w_gate_up.data_ptr() % 16 == 0 and (w_gate_up.shape[0] // 2) % 8 == 0)
 
 
 def tc_linear_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor) -> None:

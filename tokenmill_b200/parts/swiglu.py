@@ -50,8 +50,12 @@ class SwiGLUFeedForward:
             # prompt step on tcgen05 (when switched on): the activation is the product's epilogue
             ops.tc_gate_up_swiglu(x, self.w_gate_up, act)
             return ops.tc_linear(act, self.w_down) if ops.tc_ok(act, self.w_down) else ops.linear(act, self.w_down)
-        gu = ops.linear(x, self.w_gate_up)
-        ops.swiglu(gu, act)
+        if ops.tc_swiglu_decode_ok(x, self.w_gate_up):
+            # a few dozen tokens: one tcgen05 tile of 32 gate and 32 up rows for every multiprocessor
+            ops.tc_gate_up_swiglu(x, self.w_gate_up, act)
+        else:
+            gu = ops.linear(x, self.w_gate_up)
+            ops.swiglu(gu, act)
         if ops.tc_add_ok(act, self.w_down, residual):
             # a few dozen tokens: the down projection cut along K over the whole chip, added into the stream
             ops.tc_linear_add(act, self.w_down, residual)
