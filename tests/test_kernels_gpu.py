@@ -206,6 +206,60 @@ def test_decode_attention_by_units_kernel(nh, nkv, D, page, q_lens, window, cap,
             assert int(done.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,D,page,q_lens,window,bias", [
+    (14, 2, 64, 16, [1] * 8, 0, True), (12, 2, 128, 16, [1] * 8, 0, True), (28, 4, 128, 8, [1] * 8, 0, False),
+    (8, 4, 64, 32, [2, 1, 3, 1, 1, 2, 4, 1], 0, True), (6, 2, 128, 64, [1, 1, 2, 5, 1, 2, 1, 1], 300, True),
+    (16, 1, 64, 16, [1] * 8, 90, False),
+])
+def test_decode_attention_by_units_finishing_the_projection_itself(nh, nkv, D, page, q_lens, window, bias):
+    """The unit-driven decode kernel fed with the RAW q/k/v product (bias not added, nothing rotated, nothing in
+    the cache yet) against the two kernels it replaces (rotation + cache write, then attention): the same
+    arithmetic in the same order, so the outputs and the cache are EQUAL, bit for bit. New tokens on a stage's
+    first and last row, several new tokens a request, a window, few slots so that blocks take several units."""
+    import numpy as np
+    from tokenmill_b200.parts.attention_plan import decode_units
+    ops = _ops()
+    befores = [0, 63, 64, 255, 256, 1000, 2047, 127]
+    c = _paged_case(nh, nkv, D, page, q_lens=q_lens, befores=befores, dtype=torch.bfloat16, seed=D + nh, window=window)
+    T, S = sum(q_lens), len(q_lens)
+    g = torch.Generator().manual_seed(nh * D + page)
+    qkv = torch.randn(T, (nh + 2 * nkv) * D, generator=g).bfloat16().to(DEV)
+    b = torch.randn((nh + 2 * nkv) * D, generator=g).to(DEV) if bias else None
+    n_pos = 2100
+    ang = torch.arange(n_pos)[:, None] * (10000.0 ** (-torch.arange(D // 2) / (D // 2)))[None, :]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    positions, slots = [], []
+    table = c["table"].cpu()
+    for s_i, (n, before) in enumerate(zip(q_lens, befores)):
+        for j in range(n):
+            positions.append(before + j)
+            slots.append(int(table[s_i, (before + j) // page]) * page + (before + j) % page)
+    positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    slot_map = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    rec, n_units, max_parts = decode_units(np.array(q_lens), np.array(befores), window, kv_heads=nkv, slots=9, cap=16,
+                                           head_dim=D)
+    units = torch.from_numpy(rec).to(DEV)
+    n_work = torch.tensor([n_units * nkv], dtype=torch.int32, device=DEV)
+    scratch = dict(part_acc=torch.empty(T * nh * max_parts * D, device=DEV), part_ml=torch.empty(T * nh * max_parts * 2, device=DEV),
+                   done=torch.zeros(S * nkv, dtype=torch.int32, device=DEV))
+    common = dict(scale=D ** -0.5, window=window, max_parts=max_parts, grid=min(9, n_units * nkv))
+    # the two kernels
+    kc_a, vc_a = c["kc"].clone(), c["vc"].clone()
+    q = torch.empty(T, nh, D, dtype=torch.bfloat16, device=DEV)
+    ops.qkv_rope_write(qkv, b, positions, cos, sin, slot_map, q, kc_a, vc_a, nh, nkv, D)
+    out_a = torch.full_like(q, float("nan"))
+    ops.decode_attention_units_bf16(q, kc_a, vc_a, c["table"], c["cu"], c["before"], units, n_work, out_a, **common, **scratch)
+    # the one kernel
+    kc_b, vc_b = c["kc"].clone(), c["vc"].clone()
+    out_b = torch.full_like(q, float("nan"))
+    ops.decode_attention_units_rope_bf16(qkv, b, positions, cos, sin, slot_map, kc_b, vc_b, c["table"], c["cu"], c["before"],
+                                         units, n_work, out_b, **common, **scratch)
+    ops.tc_check(torch.device(DEV))
+    assert torch.isfinite(out_a.float()).all()
+    assert torch.equal(kc_a, kc_b) and torch.equal(vc_a, vc_b)
+    assert torch.equal(out_a, out_b)
+
+
 @pytest.mark.parametrize("nh,nkv,D,page,window", [
     (14, 2, 64, 16, 0), (12, 2, 128, 16, 0), (3, 3, 64, 1, 0), (4, 1, 128, 7, 0), (14, 2, 64, 16, 70), (4, 2, 64, 8, 1),
     (6, 2, 128, 32, 200),

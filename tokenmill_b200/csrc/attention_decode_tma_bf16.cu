@@ -101,14 +101,43 @@ __device__ __forceinline__ TdItem td_item(const int4* __restrict__ units, int w,
   return it;
 }
 
-template <int D>
+// What the kernel needs to finish the q/k/v projection itself (ROPE variant): the raw product of the step's tokens,
+// the bias, the rotation tables and where each token's key and value go. Then no kernel stands between the
+// projection and the attention: the consumer warp adds the bias and rotates its query rows while it loads them
+// (rotate-half, src/infer/model/layers.py:60-64, in the arithmetic of rope_cache.cu), and the item whose unit holds
+// a new token's position computes that token's key and value for its kv head, writes them to the cache and puts
+// them into the stage it has just received (where the copy brought the slot's old content).
+struct TdRope {
+  const __nv_bfloat16* qkv;      // [T, (nh + 2 nkv) D]
+  const float* bias;             // [(nh + 2 nkv) D] or null
+  const int* positions;          // [T]
+  const float* cos_t;            // [n_pos, D / 2]
+  const float* sin_t;
+  const int* slot_map;           // [T] cache slot of each token (negative: not written)
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  int n_pos;
+};
+
+__device__ __forceinline__ int td_rope_position(int pos, int n_pos, int* error) {
+  if (pos >= 0 && pos < n_pos) return pos;
+  if (error) atomicCAS(error, 0, 31);          // never read outside the tables; tell the host
+  return pos < 0 ? 0 : n_pos - 1;
+}
+
+__device__ __forceinline__ float2 td_bf16x2(uint32_t v) {
+  __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&v);
+  return __bfloat1622float2(h);
+}
+
+template <int D, bool ROPE>
 __global__ void __launch_bounds__(64) decode_attention_units_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_before, const int4* __restrict__ units,
     const int* __restrict__ n_work_ptr, int max_work, float* __restrict__ part_acc, float* __restrict__ part_ml,
     __nv_bfloat16* __restrict__ out, int* __restrict__ done, int nh, int nkv, int page_size, float scale_log2,
-    int window, int max_parts, int* __restrict__ error) {
+    int window, int max_parts, int* __restrict__ error, const TdRope rp) {
   constexpr int KS = D / 16, NT = D / 8, NS = td_stages<D>(), STAGE = td_stage_bytes<D>(), TILE = kDecBN * D * 2;
   extern __shared__ __align__(1024) unsigned char td_raw[];
   __shared__ __align__(8) uint64_t s_full[NS], s_empty[NS];
@@ -171,9 +200,9 @@ __global__ void __launch_bounds__(64) decode_attention_units_kernel(
           if (!ok) break;
         }
         const int kb = it.kb_first + k * kDecBN;
-        if (!waited && kb + kDecBN > it.before) {               // keys of the step's own tokens: written by the
-          pdl_wait();                                           // kernel in front of this one
-          waited = true;
+        if (!ROPE && !waited && kb + kDecBN > it.before) {      // keys of the step's own tokens: written by the
+          pdl_wait();                                           // kernel in front of this one (with ROPE: by the
+          waited = true;                                        // consumer, into the stage itself)
         }
         const uint32_t bar = t5_smem(&s_full[slot]);
         if (k == 0 && item < 7) td_stamp(stamps, 2 + 8 * item + 5);
@@ -204,7 +233,7 @@ __global__ void __launch_bounds__(64) decode_attention_units_kernel(
       if (it.n_stages > kTdMaxStages) break;
       const int n_rows = it.n_rows, before = it.before;
       uint32_t qa[KS][4];                    // query fragments straight from global memory (rows beyond n_rows are zero)
-      {
+      if constexpr (!ROPE) {
         const __nv_bfloat16* qr0 = nullptr;
         const __nv_bfloat16* qr1 = nullptr;
         if (r0 < n_rows) qr0 = q + ((size_t)(it.q_start + r0 / G) * nh + it.kvh * G + r0 % G) * D;
@@ -216,6 +245,47 @@ __global__ void __launch_bounds__(64) decode_attention_units_kernel(
           qa[ks][1] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c)) : 0u;
           qa[ks][2] = qr0 ? __ldcg(reinterpret_cast<const unsigned int*>(qr0 + c + 8)) : 0u;
           qa[ks][3] = qr1 ? __ldcg(reinterpret_cast<const unsigned int*>(qr1 + c + 8)) : 0u;
+        }
+      } else {
+        // The raw projection's rows: bias added and rotated here. A lane's elements of the first half of a head
+        // (steps ks < KS / 2) and their partners of the second half (ks + KS / 2) are both its own.
+        constexpr int half_d = D / 2;
+        const int width = (nh + 2 * nkv) * D;
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+          const int r = hrow ? r1 : r0;
+          if (r >= n_rows) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) qa[ks][hrow] = qa[ks][2 + hrow] = 0u;
+            continue;
+          }
+          const int tok = it.q_start + r / G, head = it.kvh * G + r % G;
+          const __nv_bfloat16* src = rp.qkv + (size_t)tok * width + head * D;
+          const float* bsrc = rp.bias ? rp.bias + head * D : nullptr;
+          const int pos = td_rope_position(rp.positions[tok], rp.n_pos, error);
+          const float* cs = rp.cos_t + (size_t)pos * half_d;
+          const float* sn = rp.sin_t + (size_t)pos * half_d;
+#pragma unroll
+          for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {           // elements c, c + 1 and c + 8, c + 9
+              const int c = ks * 16 + cpair + part * 8;
+              float2 x1 = td_bf16x2(__ldcg(reinterpret_cast<const unsigned int*>(src + c)));
+              float2 x2 = td_bf16x2(__ldcg(reinterpret_cast<const unsigned int*>(src + c + half_d)));
+              if (bsrc) {
+                const float2 b1 = __ldg(reinterpret_cast<const float2*>(bsrc + c));
+                const float2 b2 = __ldg(reinterpret_cast<const float2*>(bsrc + c + half_d));
+                x1.x += b1.x; x1.y += b1.y; x2.x += b2.x; x2.y += b2.y;
+              }
+              const float2 cc = __ldg(reinterpret_cast<const float2*>(cs + c));
+              const float2 ss = __ldg(reinterpret_cast<const float2*>(sn + c));
+              const float o1x = __fadd_rn(__fmul_rn(x1.x, cc.x), __fmul_rn(-x2.x, ss.x));
+              const float o1y = __fadd_rn(__fmul_rn(x1.y, cc.y), __fmul_rn(-x2.y, ss.y));
+              const float o2x = __fadd_rn(__fmul_rn(x2.x, cc.x), __fmul_rn(x1.x, ss.x));
+              const float o2y = __fadd_rn(__fmul_rn(x2.y, cc.y), __fmul_rn(x1.y, ss.y));
+              qa[ks][hrow + 2 * part] = pack_bf16(o1x, o1y);
+              qa[ks + KS / 2][hrow + 2 * part] = pack_bf16(o2x, o2y);
+            }
         }
       }
       if (item < 7) td_stamp(stamps, 2 + 8 * item);
@@ -234,6 +304,52 @@ __global__ void __launch_bounds__(64) decode_attention_units_kernel(
         if (!ok) break;
         if (b == 0 && item < 7) td_stamp(stamps, 2 + 8 * item + 1);
         const uint32_t k_base = ring + (uint32_t)slot * STAGE, v_base = k_base + TILE;
+        if constexpr (ROPE) {
+          // The step's own tokens whose positions lie in this stage (and in this item's keys): their key and value
+          // for this kv head, finished here, written to the cache and into the stage.
+          const int q_tokens = (n_rows + G - 1) / G;
+          const int t_lo = max(0, max(kb, it.j_lo) - before), t_hi = min(q_tokens - 1, min(kb + kDecBN - 1, it.j_hi) - before);
+          if (t_lo <= t_hi) {
+            constexpr int half_d = D / 2;
+            const int width = (nh + 2 * nkv) * D;
+            unsigned char* stage_ptr = td_raw + (k_base - t5_smem(td_raw));
+            for (int tt = t_lo; tt <= t_hi; ++tt) {
+              const int tok = it.q_start + tt, row = before + tt - kb;
+              const int pos = td_rope_position(rp.positions[tok], rp.n_pos, error);
+              const int cache_slot = rp.slot_map ? rp.slot_map[tok] : -1;
+              const __nv_bfloat16* ksrc = rp.qkv + (size_t)tok * width + (nh + it.kvh) * D;
+              const __nv_bfloat16* vsrc = ksrc + nkv * D;
+              const float* kb_bias = rp.bias ? rp.bias + (nh + it.kvh) * D : nullptr;
+              const float* vb_bias = rp.bias ? kb_bias + nkv * D : nullptr;
+              for (int i = lane; i < half_d; i += 32) {
+                float k1 = __bfloat162float(ksrc[i]), k2 = __bfloat162float(ksrc[i + half_d]);
+                float v1 = __bfloat162float(vsrc[i]), v2 = __bfloat162float(vsrc[i + half_d]);
+                if (kb_bias) {
+                  k1 += kb_bias[i]; k2 += kb_bias[i + half_d];
+                  v1 += vb_bias[i]; v2 += vb_bias[i + half_d];
+                }
+                const float c = rp.cos_t[(size_t)pos * half_d + i], sv = rp.sin_t[(size_t)pos * half_d + i];
+                const __nv_bfloat16 ok1 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(k1, c), __fmul_rn(-k2, sv)));
+                const __nv_bfloat16 ok2 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(k2, c), __fmul_rn(k1, sv)));
+                const __nv_bfloat16 ov1 = __float2bfloat16_rn(v1), ov2 = __float2bfloat16_rn(v2);
+                if (cache_slot >= 0) {
+                  const size_t at = ((size_t)cache_slot * nkv + it.kvh) * D;
+                  rp.kcache[at + i] = ok1; rp.kcache[at + i + half_d] = ok2;
+                  rp.vcache[at + i] = ov1; rp.vcache[at + i + half_d] = ov2;
+                }
+                // element d of key row `row`: piece d / 8 of the row, swizzled as the copies write it
+                auto put = [&](uint32_t tile_off, int d, __nv_bfloat16 val) {
+                  const uint32_t off = td_tile_addr(tile_off, row, d >> 3) + (uint32_t)(d & 7) * 2;
+                  *reinterpret_cast<__nv_bfloat16*>(stage_ptr + off) = val;
+                };
+                put(0u, i, ok1); put(0u, i + half_d, ok2);
+                put((uint32_t)TILE, i, ov1); put((uint32_t)TILE, i + half_d, ov2);
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these writes come before the slot's next copies
+            __syncwarp();
+          }
+        }
         float sc[8][4];
 #pragma unroll
         for (int t = 0; t < 8; ++t) sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
@@ -495,14 +611,14 @@ static bool td_map_for(const void* base, long long slots, int page_size, int nkv
   return true;
 }
 
-template <int D>
+template <int D, bool ROPE>
 int launch_decode_attention_units(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* block_table,
                                   int bt_stride, const int* cu_q, const int* kv_before, const int* units,
                                   const int* n_work, int max_work, int grid_blocks, float* part_acc, float* part_ml,
                                   void* out, int* done, int nh, int nkv, int page_size, float scale, int window,
-                                  int max_parts, int* error, cudaStream_t stream) {
+                                  int max_parts, int* error, const TdRope& rp, cudaStream_t stream) {
   const int smem = td_stages<D>() * td_stage_bytes<D>() + 1024;
-  auto kern = decode_attention_units_kernel<D>;
+  auto kern = decode_attention_units_kernel<D, ROPE>;
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -512,7 +628,32 @@ int launch_decode_attention_units(const CUtensorMap& mk, const CUtensorMap& mv, 
   return launch_pdl(kern, dim3(grid_blocks), dim3(64), (size_t)smem, stream, mk, mv, (const __nv_bfloat16*)q,
                     block_table, bt_stride, cu_q, kv_before, reinterpret_cast<const int4*>(units), n_work, max_work,
                     part_acc, part_ml, (__nv_bfloat16*)out, done, nh, nkv, page_size,
-                    scale * 1.4426950408889634f, window, max_parts, error);
+                    scale * 1.4426950408889634f, window, max_parts, error, rp);
+}
+
+static int decode_attention_units(const void* q, const TdRope& rp, bool rope, const void* kcache, const void* vcache,
+                                  long long n_pages, const int* block_table, int bt_stride, const int* cu_q,
+                                  const int* kv_before, const int* units, const int* n_work, int max_work,
+                                  int grid_blocks, float* part_acc, float* part_ml, void* out, int* done, int nh,
+                                  int nkv, int D, int page_size, float scale, int window, int max_parts, int* error,
+                                  cudaStream_t stream) {
+  if (max_work <= 0 || grid_blocks <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || nh / nkv > 16 || n_pages <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (max_parts <= 0 || max_parts > 0x7fff) return TM_ERR_UNSUPPORTED_SHAPE;
+  if (D != 64 && D != 128) return TM_ERR_UNSUPPORTED_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(kcache) | reinterpret_cast<uintptr_t>(vcache) | reinterpret_cast<uintptr_t>(units)) & 15)
+    return TM_ERR_UNSUPPORTED_SHAPE;
+  if (!part_acc || !part_ml || !done || !out || !error || !units || !n_work) return TM_ERR_SCRATCH_TOO_SMALL;
+  CUtensorMap mk, mv;
+  if (!td_map_for(kcache, n_pages * page_size, page_size, nkv, D, &mk) ||
+      !td_map_for(vcache, n_pages * page_size, page_size, nkv, D, &mv))
+    return 90006;
+#define TD_UNITS_ARGS mk, mv, q, block_table, bt_stride, cu_q, kv_before, units, n_work, max_work, grid_blocks, part_acc, \
+                      part_ml, out, done, nh, nkv, page_size, scale, window, max_parts, error, rp, stream
+  if (D == 64) return rope ? launch_decode_attention_units<64, true>(TD_UNITS_ARGS) : launch_decode_attention_units<64, false>(TD_UNITS_ARGS);
+  return rope ? launch_decode_attention_units<128, true>(TD_UNITS_ARGS) : launch_decode_attention_units<128, false>(TD_UNITS_ARGS);
+#undef TD_UNITS_ARGS
 }
 
 }  // namespace tmk
@@ -543,23 +684,35 @@ extern "C" int tm_decode_attention_units_bf16(const void* q, const void* kcache,
                                               int grid_blocks, float* part_acc, float* part_ml, void* out, int* done,
                                               int nh, int nkv, int D, int page_size, float scale, int window,
                                               int max_parts, int* error, cudaStream_t stream) {
-  if (max_work <= 0 || grid_blocks <= 0) return 0;
-  if (nkv <= 0 || nh % nkv || nh / nkv > 16 || n_pages <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
-  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TM_ERR_UNSUPPORTED_SHAPE;
-  if (max_parts <= 0 || max_parts > 0x7fff) return TM_ERR_UNSUPPORTED_SHAPE;
-  if (D != 64 && D != 128) return TM_ERR_UNSUPPORTED_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(kcache) | reinterpret_cast<uintptr_t>(vcache) | reinterpret_cast<uintptr_t>(units)) & 15)
+  if (!q) return TM_ERR_SCRATCH_TOO_SMALL;
+  return tmk::decode_attention_units(q, tmk::TdRope{}, false, kcache, vcache, n_pages, block_table, bt_stride, cu_q,
+                                     kv_before, units, n_work, max_work, grid_blocks, part_acc, part_ml, out, done, nh,
+                                     nkv, D, page_size, scale, window, max_parts, error, stream);
+}
+
+// The same straight from the raw q/k/v product of the step's tokens: qkv [T, (nh + 2 nkv) D] bfloat16 (bias [..]
+// float32 or null not yet added, nothing rotated), positions [T], rotate-half tables cos / sin [n_pos, D / 2]
+// float32, slot_map [T] (the cache slot of each token's key and value; negative: not written). The kernel adds the
+// bias, rotates the query rows as it loads them, and finishes, writes to the cache and uses each new token's key
+// and value itself: the kernel that would do that between the product and the attention (rope_cache.cu) is not
+// launched. A position outside the tables is clamped and raises error code 31.
+extern "C" int tm_decode_attention_units_rope_bf16(const void* qkv, const float* bias, const int* positions,
+                                                   const float* cos_t, const float* sin_t, int n_pos,
+                                                   const int* slot_map, void* kcache, void* vcache, long long n_pages,
+                                                   const int* block_table, int bt_stride, const int* cu_q,
+                                                   const int* kv_before, const int* units, const int* n_work,
+                                                   int max_work, int grid_blocks, float* part_acc, float* part_ml,
+                                                   void* out, int* done, int nh, int nkv, int D, int page_size,
+                                                   float scale, int window, int max_parts, int* error,
+                                                   cudaStream_t stream) {
+  if (!qkv || !positions || !cos_t || !sin_t || n_pos <= 0) return TM_ERR_SCRATCH_TOO_SMALL;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 3) || (reinterpret_cast<uintptr_t>(bias) & 7) ||
+      (reinterpret_cast<uintptr_t>(cos_t) & 7) || (reinterpret_cast<uintptr_t>(sin_t) & 7))
     return TM_ERR_UNSUPPORTED_SHAPE;
-  if (!part_acc || !part_ml || !done || !out || !error || !units || !n_work) return TM_ERR_SCRATCH_TOO_SMALL;
-  CUtensorMap mk, mv;
-  if (!tmk::td_map_for(kcache, n_pages * page_size, page_size, nkv, D, &mk) ||
-      !tmk::td_map_for(vcache, n_pages * page_size, page_size, nkv, D, &mv))
-    return 90006;
-  if (D == 64)
-    return tmk::launch_decode_attention_units<64>(mk, mv, q, block_table, bt_stride, cu_q, kv_before, units, n_work,
-                                                  max_work, grid_blocks, part_acc, part_ml, out, done, nh, nkv,
-                                                  page_size, scale, window, max_parts, error, stream);
-  return tmk::launch_decode_attention_units<128>(mk, mv, q, block_table, bt_stride, cu_q, kv_before, units, n_work,
-                                                 max_work, grid_blocks, part_acc, part_ml, out, done, nh, nkv,
-                                                 page_size, scale, window, max_parts, error, stream);
+  tmk::TdRope rp{};
+  rp.qkv = (const __nv_bfloat16*)qkv; rp.bias = bias; rp.positions = positions; rp.cos_t = cos_t; rp.sin_t = sin_t;
+  rp.slot_map = slot_map; rp.kcache = (__nv_bfloat16*)kcache; rp.vcache = (__nv_bfloat16*)vcache; rp.n_pos = n_pos;
+  return tmk::decode_attention_units(nullptr, rp, true, kcache, vcache, n_pages, block_table, bt_stride, cu_q, kv_before,
+                                     units, n_work, max_work, grid_blocks, part_acc, part_ml, out, done, nh, nkv, D,
+                                     page_size, scale, window, max_parts, error, stream);
 }

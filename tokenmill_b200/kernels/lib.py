@@ -44,6 +44,8 @@ _SIGNATURES: dict[str, list] = {
     "tm_decode_attention_bf16": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
     "tm_decode_attention_units_bf16": [_P, _P, _P, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I,
                                        _I, _P, _P],
+    "tm_decode_attention_units_rope_bf16": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P,
+                                            _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "tm_decode_attention_units_slots": [_I, _I],
     "tm_prefill_attention_bf16": [_P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "tm_prefill_attention_tc_timing": [_P],

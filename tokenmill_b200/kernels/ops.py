@@ -226,6 +226,50 @@ def decode_attention_units_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: t
     return out
 
 
+_DECODE_ROPE = os.environ.get("TOKENMILL_DECODE_ROPE", "1") != "0"
+
+
+def decode_rope_fused_ok() -> bool:
+    """Whether the unit-driven decode attention finishes the q/k/v projection itself (bias, rotation, cache
+    write) instead of the kernel that otherwise stands between the two. TOKENMILL_DECODE_ROPE=0 keeps that kernel."""
+    return _DECODE_ROPE
+
+
+def decode_attention_units_rope_bf16(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor,
+                                     cos: torch.Tensor, sin: torch.Tensor, slot_map: torch.Tensor, kcache: torch.Tensor,
+                                     vcache: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor,
+                                     kv_before: torch.Tensor, units: torch.Tensor, n_work: torch.Tensor,
+                                     out: torch.Tensor, *, scale: float, window: int, max_parts: int, grid: int,
+                                     part_acc: torch.Tensor, part_ml: torch.Tensor, done: torch.Tensor) -> torch.Tensor:
+    """``decode_attention_units_bf16`` straight from the raw q/k/v product ``qkv`` [T, (nh + 2 nkv) D]: the kernel
+    adds the bias, rotates queries and the new keys (rotate-half tables ``cos`` / ``sin`` [n_pos, D / 2]), writes
+    each token's key and value to cache slot ``slot_map[t]`` and attends. ``out``: [T, nh, D]."""
+    T, nh, D = out.shape
+    page_size, nkv = kcache.shape[1], kcache.shape[2]
+    bf, i32, f32 = torch.bfloat16, torch.int32, torch.float32
+    n_seqs = kv_before.numel()
+    need = T * nh * max_parts
+    if part_acc.numel() < need * D or part_ml.numel() < need * 2:
+        raise lib.KernelError("decode_attention_units_rope_bf16: scratch too small")
+    if qkv.shape != (T, (nh + 2 * nkv) * D) or not qkv.is_contiguous() or kcache.shape[3] != D or vcache.shape != kcache.shape:
+        raise lib.KernelError("decode_attention_units_rope_bf16: qkv / cache / out shapes disagree")
+    if cos.shape != sin.shape or cos.shape[1] != D // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+        raise lib.KernelError("decode_attention_units_rope_bf16: rotation tables of [positions, head_dim / 2] wanted")
+    if done.numel() < n_seqs * nkv:
+        raise lib.KernelError("decode_attention_units_rope_bf16: too few arrival counters")
+    if units.dim() != 2 or units.shape[1] != 4 or units.data_ptr() % 16:
+        raise lib.KernelError("decode_attention_units_rope_bf16: units must be 16-byte aligned int32 records of 4")
+    lib.call("tm_decode_attention_units_rope_bf16", _req(qkv, "qkv", bf), _opt(bias, "bias", f32),
+             _req(positions, "positions", i32), _req(cos, "cos", f32), _req(sin, "sin", f32), cos.shape[0],
+             _req(slot_map, "slot_map", i32), _req(kcache, "kcache", bf), _req(vcache, "vcache", bf), kcache.shape[0],
+             _req(block_table, "block_table", i32), block_table.stride(0), _req(cu_q, "cu_q", i32),
+             _req(kv_before, "kv_before", i32), _req(units, "units", i32), _req(n_work, "n_work", i32),
+             units.shape[0] * nkv, int(grid), _req(part_acc, "part_acc", f32), _req(part_ml, "part_ml", f32),
+             _req(out, "out", bf), _req(done, "done", i32), nh, nkv, D, page_size, float(scale), int(window),
+             int(max_parts), _tc_flag(out.device).data_ptr(), _stream())
+    return out
+
+
 def prefill_attention_bf16(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                            units, counters: torch.Tensor, out: torch.Tensor, *, scale: float, window: int = 0,
                            part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,

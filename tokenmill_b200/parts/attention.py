@@ -197,6 +197,11 @@ class GroupedQueryAttention:
             # prompt step: the tcgen05 kernel keeps the product in tensor memory and finishes it the same way
             ops.tc_qkv_rope_write(x, self.w_qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, q,
                                   kc, vc, self.nh, self.nkv, self.D)
+        elif rotary and cache.writes and self._decode_by_units(step) and ops.decode_rope_fused_ok():
+            # decoding by units: the attention kernel finishes the projection itself (bias, rotation, cache write)
+            qkv = ops.linear(x, self.w_qkv)
+            self._attend_units(None, step, cache, q, raw=(qkv, slot_map))     # (q is the output buffer here)
+            return self._project_out(q, T, residual)
         elif rotary or self.position is None:
             # library (or 32-bit) product, then bias + rotation (none without an encoding) + cache write
             qkv = ops.linear(x, self.w_qkv)
@@ -213,6 +218,9 @@ class GroupedQueryAttention:
                 ops.kv_cache_write(k, v, slot_map, cache.k, cache.v)
         out = torch.empty_like(q)
         self.attend(q, step, cache, out)
+        return self._project_out(out, T, residual)
+
+    def _project_out(self, out: torch.Tensor, T: int, residual: torch.Tensor | None) -> torch.Tensor | None:
         flat = out.view(T, self.q_size)
         if ops.skinny_ok(flat, self.w_o, allow_split=True):
             return ops.skinny_linear(flat, self.w_o, k_splits=ops.skinny_k_splits(T, self.q_size))
@@ -223,6 +231,27 @@ class GroupedQueryAttention:
             ops.tc_linear_add(flat, self.w_o, residual)
             return None
         return ops.linear(flat, self.w_o)
+
+    def _decode_by_units(self, step: StepInputs) -> bool:
+        meta = step.meta.get(self.metadata_key())
+        return meta is not None and meta.host.get("path") == "decode" and "decode_units" in meta.arrays
+
+    def _attend_units(self, q: torch.Tensor | None, step: StepInputs, cache: LayerCache, out: torch.Tensor, raw=None) -> None:
+        """The unit-driven decode kernel: from finished queries ``q``, or (``raw`` = (qkv, slot_map)) from the raw
+        q/k/v product, which it then finishes itself."""
+        meta = self._meta(step)
+        max_parts = meta.host["max_parts"]
+        part_acc, part_ml, done = self._decode_scratch(step.workspace, out.shape[0], step.n_seqs, max_parts, "_units")
+        common = dict(scale=self.scale, window=self.window, max_parts=max_parts, grid=meta.host["decode_grid"],
+                      part_acc=part_acc, part_ml=part_ml, done=done)
+        table, units, n_work = step.block_tables[cache.group], meta.arrays["decode_units"], meta.arrays["decode_n_work"]
+        if raw is not None:
+            qkv, slot_map = raw
+            ops.decode_attention_units_rope_bf16(qkv, self.b_qkv, step.positions, self.cos, self.sin, slot_map, cache.k,
+                                                 cache.v, table, step.cu_q, step.kv_before, units, n_work, out, **common)
+        else:
+            ops.decode_attention_units_bf16(q, cache.k, cache.v, table, step.cu_q, step.kv_before, units, n_work, out,
+                                            **common)
 
     def emit(self, b, x, cache: LayerCache):
         """The prompt-step launches (library product, bias + rotation + cache write, attention, library
@@ -362,13 +391,7 @@ class GroupedQueryAttention:
         path, ws = meta.host["path"], step.workspace
         split_keys, max_splits = meta.host["split_keys"], meta.host["max_splits"]
         if path == "decode" and "decode_units" in meta.arrays:
-            max_parts = meta.host["max_parts"]
-            part_acc, part_ml, done = self._decode_scratch(ws, q.shape[0], step.n_seqs, max_parts, "_units")
-            ops.decode_attention_units_bf16(q, cache.k, cache.v, step.block_tables[cache.group], step.cu_q,
-                                            step.kv_before, meta.arrays["decode_units"], meta.arrays["decode_n_work"],
-                                            out, scale=self.scale, window=self.window, max_parts=max_parts,
-                                            grid=meta.host["decode_grid"], part_acc=part_acc, part_ml=part_ml,
-                                            done=done)
+            self._attend_units(q, step, cache, out)
             return
         if path == "decode":
             part_acc, part_ml, done = self._decode_scratch(ws, q.shape[0], step.n_seqs, max_splits)
