@@ -535,7 +535,9 @@ def run_workload(args) -> dict:
             from tokenmill_b200 import EngineConfig
             from tokenmill_b200.engine import LLMEngine
             from tokenmill_b200.sampling import SamplingParams
-            engine = LLMEngine(EngineConfig(**base))
+            engine = LLMEngine(EngineConfig(cuda_graphs=True, cuda_graph_max_batch=max(64, w["n"]), **base))   # (graphs on in both arms)
+        if hasattr(engine, "capture_graphs"):
+            engine.capture_graphs()             # (the reference captures its graphs when the engine is built)
         sp = SamplingParams(max_tokens=w["new"], ignore_eos=True)
         warm = engine.generate([prompts_[0][:64]], SamplingParams(max_tokens=4, ignore_eos=True))    # compile / warm paths
         assert len(warm[0]) == 4

@@ -132,6 +132,11 @@ class LLMEngine:
         log.info("engine ready: %d pages of %d tokens in %d group(s) (%.0f MiB), dtype %s, device %s", num_pages,
                  cfg.block_size, n_groups, self.pools.nbytes / 2 ** 20, self.dtype, self.device)
 
+    def capture_graphs(self) -> int:
+        """With ``cuda_graphs``: capture every decode graph now, so that no request waits for a capture later
+        (otherwise each is captured at the first step that needs it). Returns how many graphs there are."""
+        return self.runner.capture_decode_graphs()
+
     # --- requests -------------------------------------------------------------------------------
 
     def add_request(self, request_id: str, prompt_ids: list[int], params: SamplingParams,

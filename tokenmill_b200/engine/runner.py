@@ -256,6 +256,26 @@ class ModelRunner:
 
     # --- decode graphs --------------------------------------------------------------------------
 
+    def _graph_sizes(self) -> list[int]:
+        """The batch sizes decode graphs are captured for."""
+        if self.fused is not None:
+            return [self.graph_max_batch]
+        return [b for b in GRAPH_BATCH_SIZES if b < self.graph_max_batch] + [self.graph_max_batch]
+
+    @torch.inference_mode()
+    def capture_decode_graphs(self) -> int:
+        """Capture every decode graph now instead of at the first step that needs it (a capture takes tens of
+        milliseconds, which a serving loop would otherwise pay in the middle of its requests; the reference captures
+        at start-up too, src/infer/engine/cuda_graphs.py:45-80). Returns how many graphs there are."""
+        if not self.graph_max_batch:
+            return 0
+        for bucket in sorted(self._graph_sizes(), reverse=True):        # the largest first: the others share its buffers
+            if self.fused is not None and bucket <= self.fused.max_tokens:
+                continue
+            if bucket not in self._graphs:
+                self._graphs[bucket] = _DecodeGraph(self, bucket)
+        return len(self._graphs)
+
     def _graph_step(self, entries: list[StepEntry], token_src: torch.Tensor | None = None,
                     token_rows: list[int] | None = None) -> torch.Tensor:
         n = len(entries)
