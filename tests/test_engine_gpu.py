@@ -702,6 +702,28 @@ def test_graph_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_di
         assert len(ids_s) == sp.max_tokens and -1 not in ids_a
 
 
+@pytest.mark.parametrize("dtype,n_graphs", [("bfloat16", 1), ("float32", 6)])
+def test_decode_graphs_captured_at_start_change_nothing_but_when(d64_dir, dtype, n_graphs):
+    """``LLMEngine.capture_graphs()`` captures every decode graph before the first request (one graph of the
+    largest batch where the whole-step kernel takes the small steps, one per power of two otherwise); the
+    requests then get the tokens they get from an engine that captures when it first needs a graph."""
+    from tokenmill_b200.sampling import SamplingParams
+    rng = random.Random(11)
+    vocab = json.loads((Path(d64_dir) / "config.json").read_text())["vocab_size"]
+    prompts = [[rng.randrange(vocab) for _ in range(rng.randrange(3, 40))] for _ in range(24)]
+    params = [SamplingParams(max_tokens=4 + (7 * i) % 19, ignore_eos=True) for i in range(24)]
+    results = []
+    for early in (True, False):
+        eng = engine_for(d64_dir, dtype=dtype, max_num_seqs=32, max_num_batched_tokens=1024, kv_cache_mb=32,
+                         cuda_graphs=True, cuda_graph_max_batch=32, async_decode=False)
+        if early:
+            assert eng.capture_graphs() == n_graphs and len(eng.runner._graphs) == n_graphs
+            assert eng.capture_graphs() == n_graphs                     # (a second call finds them all there)
+        results.append(_run_requests(eng, prompts, params))
+        assert eng.runner.stats["graph_steps"] >= 3 and len(eng.runner._graphs) <= n_graphs
+    assert [r[0] for r in results[0]] == [r[0] for r in results[1]]
+
+
 @pytest.mark.parametrize("trial", [0, 3, 4])
 def test_random_workloads_with_tiny_pools(d64_dir, trial):
     """Sixty requests of random lengths and sampling settings arriving at random times into a pool so small
