@@ -13,6 +13,8 @@
 // products [n_partials, n_tokens, H] from a split-K matrix product; they are summed in index order.
 // Rows whose width is a multiple of 4 move four elements per access; the order of the row's sum of
 // squares is fixed by the width and the block size alone.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tmk {
@@ -152,8 +154,7 @@ __global__ void __launch_bounds__(128) add_rmsnorm_warp_kernel(
 
 template <typename T, int CH, typename... Args>
 int launch_add_rmsnorm_warp(int n_rows, cudaStream_t stream, Args... args) {
-  // Few rows: one warp per block, so that they spread over the SMs; many: four.
-  const int warps = n_rows >= 1024 ? 4 : 1;
+  const int warps = 4;
   return launch_pdl(add_rmsnorm_warp_kernel<T, CH>, dim3((n_rows + warps - 1) / warps), dim3(32 * warps), 0, stream,
                     args..., n_rows);
 }
@@ -169,7 +170,11 @@ int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, 
                         reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(table) |
                         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight);
   const bool vec = H % 4 == 0 && (all & 15) == 0 && (partial_stride % 4 == 0);
-  if (vec && H <= 128 * 16) {
+  // A warp per row pays for long prompts of narrow rows (2,048 rows of 896: 5.2 us against 6.1; 4,096: 8.5 against
+  // 10.3); a block per row wins everywhere else (64 rows of 896: 2.2 us against 4.6; rows of 1,536: 2.8 against 7.1,
+  // and 7.9 against 12.4 at 2,048 rows, where a lane holds too much of the row). The two sum the squares in different
+  // orders, so the 32-bit path, whose results do not move with the cut of a step, stays with one of them.
+  if (vec && std::is_same<T, __nv_bfloat16>::value && H <= 128 * 8 && n_rows >= 1536) {
     const int chunks = (H + 127) / 128;
 #define TM_NORM_WARP(CH)                                                                                          \
   return launch_add_rmsnorm_warp<T, CH>(n_rows, stream, resid, (const T*)branch, partials, n_partials, partial_stride, \
@@ -177,8 +182,7 @@ int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, 
     if (chunks <= 1) TM_NORM_WARP(1);
     if (chunks <= 2) TM_NORM_WARP(2);
     if (chunks <= 4) TM_NORM_WARP(4);
-    if (chunks <= 8) TM_NORM_WARP(8);
-    TM_NORM_WARP(16);
+    TM_NORM_WARP(8);
 #undef TM_NORM_WARP
   }
   auto kern = vec ? add_rmsnorm_kernel<T, 4> : add_rmsnorm_kernel<T, 1>;
