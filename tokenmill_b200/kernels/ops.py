@@ -714,13 +714,14 @@ def tc_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None)
 
 _TC_ADD = os.environ.get("TOKENMILL_TC_DECODE", "1") != "0"
 _TC_ADD_ALL = os.environ.get("TOKENMILL_TC_DECODE", "1") == "all"
-TC_ADD_MIN_TOKENS, TC_ADD_MAX_TOKENS = 17, 128
+TC_ADD_MIN_TOKENS, TC_ADD_MAX_TOKENS = 1, 128
 TC_ADD_MIN_K = 2048     # shorter rows: the library's kernel is as fast (o_proj of 896: 4.9 us against 6 us here)
 
 
 def tc_add_ok(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor | None) -> bool:
-    """Whether ``tc_linear_add`` takes this projection: a step of 17 to 128 tokens (below, the weight-streaming
-    kernels; above, the library product is one pass over the weights at full tiles anyway), rows long enough
+    """Whether ``tc_linear_add`` takes this projection: a step of up to 128 tokens (the callers ask the
+    weight-streaming kernels first, which take small matrices at up to 16 tokens; above 128 tokens the library
+    product is one pass over the weights at full tiles anyway), rows long enough
     that cutting them pays (the down projection: 7.9 us against the library's 9.5 at 64 x 4864 -> 896), bfloat16
     operands, a 32-bit residual stream of the product's shape. TOKENMILL_TC_DECODE=0 switches it off; =all takes
     short rows too."""
@@ -734,7 +735,7 @@ def tc_add_ok(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor | None) -> b
 
 
 def tc_swiglu_decode_ok(x: torch.Tensor, w_gate_up: torch.Tensor) -> bool:
-    """Whether a step of 17 to 128 tokens takes its gate/up projection with the activation in the epilogue on
+    """Whether a step of up to 128 tokens takes its gate/up projection with the activation in the epilogue on
     tcgen05 (tiles of 32 gate and 32 up rows, one for every multiprocessor) instead of the library product and
     the activation kernel. Only with TOKENMILL_TC_DECODE=all: measured at 64 tokens, 896 -> 2 x 4864, the fused
     kernel takes about 16 us against the library's 7.0 + 2.8 us (every tile reads all of x again, 14 blocks of K
