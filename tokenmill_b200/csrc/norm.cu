@@ -190,6 +190,7 @@ int launch_add_rmsnorm(float* resid, const void* branch, const float* partials, 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
+  // (256 threads a row: larger blocks gain half a microsecond at 8 rows of 3,584 and lose a factor at 2,048 rows.)
   return launch_pdl(kern, dim3(n_rows), dim3(256), smem, stream, resid, (const T*)branch, partials, n_partials,
                     partial_stride, ids, (const T*)table, rows, weight, eps, (T*)out, H);
 }

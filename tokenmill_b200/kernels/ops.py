@@ -715,7 +715,9 @@ def tc_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None)
 _TC_ADD = os.environ.get("TOKENMILL_TC_DECODE", "1") != "0"
 _TC_ADD_ALL = os.environ.get("TOKENMILL_TC_DECODE", "1") == "all"
 TC_ADD_MIN_TOKENS, TC_ADD_MAX_TOKENS = 1, 128
-TC_ADD_MIN_K = 2048     # shorter rows: the library's kernel is as fast (o_proj of 896: 4.9 us against 6 us here)
+TC_ADD_MIN_K = 2048     # shorter rows: the library's kernel is as fast (o_proj of 896: 4.9 us against 6 us here). Rows of
+                        # 3,584 (the 7B sizes' output projection) win inside the step (3.45 against 3.54 ms at batch 8)
+                        # although the library's kernel is ahead when both are timed alone (9 against 12 us).
 
 
 def tc_add_ok(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor | None) -> bool:
