@@ -260,6 +260,37 @@ def test_decode_attention_by_units_finishing_the_projection_itself(nh, nkv, D, p
     assert torch.equal(out_a, out_b)
 
 
+def test_decode_attention_finishing_the_projection_reports_a_position_outside_the_tables():
+    """A position beyond the rotation tables is never used to index them: the row is clamped and the error word
+    raised, which the next check turns into an exception."""
+    import numpy as np
+    from tokenmill_b200.kernels import lib
+    from tokenmill_b200.parts.attention_plan import decode_units
+    ops = _ops()
+    nh, nkv, D, page = 4, 2, 64, 16
+    c = _paged_case(nh, nkv, D, page, q_lens=[1, 1], befores=[10, 130], dtype=torch.bfloat16, seed=3)
+    qkv = torch.randn(2, (nh + 2 * nkv) * D).bfloat16().to(DEV)
+    n_pos = 100                                                           # the second token stands at 130
+    ang = torch.arange(n_pos)[:, None] * torch.ones(D // 2)[None, :]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    table = c["table"].cpu()
+    positions = torch.tensor([10, 130], dtype=torch.int32, device=DEV)
+    slot_map = torch.tensor([int(table[0, 0]) * page + 10, int(table[1, 130 // page]) * page + 130 % page],
+                            dtype=torch.int32, device=DEV)
+    rec, n_units, max_parts = decode_units(np.array([1, 1]), np.array([10, 130]), 0, kv_heads=nkv, slots=8, cap=16, head_dim=D)
+    out = torch.empty(2, nh, D, dtype=torch.bfloat16, device=DEV)
+    ops.tc_check(torch.device(DEV))
+    ops.decode_attention_units_rope_bf16(
+        qkv, None, positions, cos, sin, slot_map, c["kc"], c["vc"], c["table"], c["cu"], c["before"],
+        torch.from_numpy(rec).to(DEV), torch.tensor([n_units * nkv], dtype=torch.int32, device=DEV), out,
+        scale=D ** -0.5, window=0, max_parts=max_parts, grid=4, part_acc=torch.empty(2 * nh * max_parts * D, device=DEV),
+        part_ml=torch.empty(2 * nh * max_parts * 2, device=DEV), done=torch.zeros(2 * nkv, dtype=torch.int32, device=DEV))
+    with pytest.raises(lib.KernelError, match="position"):
+        ops.tc_check(torch.device(DEV))
+    ops.tc_check(torch.device(DEV))                                        # (the word is cleared by the check)
+    assert torch.isfinite(out.float()).all()
+
+
 @pytest.mark.parametrize("nh,nkv,D,page,window", [
     (14, 2, 64, 16, 0), (12, 2, 128, 16, 0), (3, 3, 64, 1, 0), (4, 1, 128, 7, 0), (14, 2, 64, 16, 70), (4, 2, 64, 8, 1),
     (6, 2, 128, 32, 200),
@@ -489,7 +520,7 @@ def test_tcgen05_linear(T, N, K):
 
 
 @pytest.mark.parametrize("T,N,K", [(64, 896, 4864), (17, 896, 896), (100, 1536, 8960), (128, 3584, 18944), (33, 100, 72),
-                                   (64, 132, 200), (48, 896, 64)])
+                                   (64, 132, 200), (48, 896, 64), (1, 1536, 8960), (8, 3584, 18944)])
 def test_tcgen05_linear_added_into_a_float32_stream(T, N, K):
     """The product of a step of a few dozen tokens, its K range cut over the chip and every piece added into the
     32-bit stream: the stream's own values stay, rows beyond T stay untouched, twice in a row adds twice."""
