@@ -85,11 +85,30 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
   const int begin = blockIdx.y * kArgmaxChunk, end = min(V, begin + kArgmaxChunk);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
+  if (((reinterpret_cast<uintptr_t>(row) | (uintptr_t)begin * 4) & 15) == 0 && end - begin == kArgmaxChunk) {
+    // a whole chunk of an aligned row: 16 bytes a load, a thread's four loads asked for together
+    float4 v[kArgmaxChunk / 4 / 256];
+#pragma unroll
+    for (int j = 0; j < kArgmaxChunk / 4 / 256; ++j)
+      v[j] = __ldg(reinterpret_cast<const float4*>(row + begin) + j * 256 + threadIdx.x);
+#pragma unroll
+    for (int j = 0; j < kArgmaxChunk / 4 / 256; ++j) {
+      const int i0 = begin + (j * 256 + (int)threadIdx.x) * 4;        // (indices rise: a later equal value never wins)
+      const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (e[k] > best) {
+          best = e[k];
+          bi = i0 + k;
+        }
+    }
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best || (v == best && i < bi)) {
+        best = v;
+        bi = i;
+      }
     }
   }
 #pragma unroll
