@@ -111,6 +111,10 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attention_tc_kernel(
   t5_fence_before();
   __syncthreads();
   t5_fence_after();
+  // (Launched with programmatic dependent launch: the set-up above overlaps the end of the kernel in front, which
+  // wrote the queries and the step's keys and values; nothing of a step is read before this wait.)
+  pdl_launch_dependents();
+  pdl_wait();
   // Thread t and thread t + 128 work on row t (tensor-memory lane t; a warp reaches the 32 lanes of its index
   // modulo 4): the first on keys 0..63 of a block and output columns 0..31, the second on the other halves.
   const int rt = tid & 127, half = tid >> 7;
@@ -497,9 +501,9 @@ extern "C" int tm_prefill_attention_tc_bf16(const void* q, const void* kcache, c
   const long long units = (long long)n_units * nkv;
   long long grid = (long long)n_sm * blocks_per_sm;
   if (grid > units) grid = units;
-  kern<<<(int)grid, tmk::kTaThreads, tmk::kTaSmem, stream>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table, bt_stride,
-      reinterpret_cast<const int4*>(unit_rec), n_units, chunk_keys, part_acc, part_ml, tile_done, counters,
-      (__nv_bfloat16*)out, nh, nkv, page_size, scale * 1.4426950408889634f, window, error);
-  return tmk::launch_status();
+  return tmk::launch_pdl(kern, dim3((unsigned)grid), dim3(tmk::kTaThreads), (size_t)tmk::kTaSmem, stream,
+                         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_table,
+                         bt_stride, reinterpret_cast<const int4*>(unit_rec), n_units, chunk_keys, part_acc, part_ml,
+                         tile_done, counters, (__nv_bfloat16*)out, nh, nkv, page_size, scale * 1.4426950408889634f,
+                         window, error);
 }

@@ -77,6 +77,7 @@ __global__ void qkv_rope_write_vec_kernel(const TIn* __restrict__ qkv, const flo
                                           T* __restrict__ q_out, T* __restrict__ kcache, T* __restrict__ vcache,
                                           int nh, int nkv, int D, int n_pos, int* __restrict__ error) {
   pdl_launch_dependents();                     // (the kernel behind this one may start its own preparations)
+  pdl_wait();                                  // the product comes from the kernel in front of this one
   const int t = blockIdx.x;
   const int half = D >> 1, quads = half >> 2;
   const int heads = nh + 2 * nkv;
@@ -179,9 +180,9 @@ extern "C" int tm_qkv_rope_write(int in_dtype, int dtype, const void* qkv, const
 #define TM_ROPE_LAUNCH(TIN, TOUT)                                                                            \
   do {                                                                                                       \
     if (vec)                                                                                                 \
-      tmk::qkv_rope_write_vec_kernel<TIN, TOUT><<<T, threads, 0, stream>>>(                                  \
-          (const TIN*)qkv, bias, positions, cos_t, sin_t, slot_map, (TOUT*)q_out, (TOUT*)kcache,             \
-          (TOUT*)vcache, nh, nkv, D, n_pos, error);                                                               \
+      return tmk::launch_pdl(tmk::qkv_rope_write_vec_kernel<TIN, TOUT>, dim3(T), dim3(threads), 0, stream,   \
+                             (const TIN*)qkv, bias, positions, cos_t, sin_t, slot_map, (TOUT*)q_out, (TOUT*)kcache, \
+                             (TOUT*)vcache, nh, nkv, D, n_pos, error);                                       \
     else                                                                                                     \
       tmk::qkv_rope_write_kernel<TIN, TOUT><<<T, threads, 0, stream>>>(                                      \
           (const TIN*)qkv, bias, positions, cos_t, sin_t, slot_map, (TOUT*)q_out, (TOUT*)kcache,             \

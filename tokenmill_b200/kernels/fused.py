@@ -328,10 +328,11 @@ class FusedDecoder:
         so it reports a failure once the stream has been synchronised, at the latest one step later."""
         code = int(self._err_host[0])
         if code:
-            self._err_host.zero_()
-            self.error.zero_()
-            self.bar.zero_()
-            self.attn_count.zero_()
+            with torch.inference_mode():     # (whichever mode the caller is in: the words may be inference tensors)
+                self._err_host.zero_()
+                self.error.zero_()
+                self.bar.zero_()
+                self.attn_count.zero_()
             what = "the output matrix kernel gave up waiting for its weights" if code == 21 else \
                 "a token's position lies outside the position tables" if code == 31 else \
                 f"the fused decode kernel gave up at a bounded wait (code {code}: 100 + n grid barrier n, 1000 / 2000 " \

@@ -647,7 +647,8 @@ def tc_poll(device: torch.device) -> None:
     shows once the stream has been synchronised, at the latest one step later)."""
     host = _tc_host.get(device)
     if host is not None and int(host[0]):
-        host.zero_()
+        with torch.inference_mode():         # (the word may have been made inside a step: an inference tensor)
+            host.zero_()
         tc_check(device)
 
 
@@ -659,7 +660,8 @@ def tc_check(device: torch.device) -> None:
     if flag is not None:
         code = int(flag.item())
         if code:
-            flag.zero_()
+            with torch.inference_mode():     # (the word may have been made inside a step: an inference tensor)
+                flag.zero_()
             if code == 32:
                 raise lib.KernelError("decode attention met a request with more rows than a tile holds, keys beyond "
                                       "max_splits * split_keys or a unit of more stages than it takes; its output is "
