@@ -101,6 +101,66 @@ __device__ __forceinline__ TdItem td_item(const int4* __restrict__ units, int w,
   return it;
 }
 
+// The merge of a (request, kv head)'s partial results, by one warp. A lane owns 4 columns of up to SLOTS rows at
+// a time and takes the parts PP at a time, in part order: the loads of a pass (2 x SLOTS x PP a lane, 32 in both
+// shapes used) are all asked for before the first is used, so a pass costs one trip to the L2. Few rows (heads
+// of 64 in groups of up to 8: two rows share a warp's 32 lanes) take 4 parts a pass, more rows 2.
+template <int D, int SLOTS, int PP>
+__device__ __forceinline__ void td_merge_parts(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                               __nv_bfloat16* __restrict__ out, const TdItem& it, int n_rows, int G,
+                                               int nh, int max_parts, int lane) {
+  constexpr int GROUPS = D / 4, LANE_ROWS = 32 / GROUPS;
+  const int d = (lane % GROUPS) * 4;
+  for (int rb = 0; rb < n_rows; rb += SLOTS * LANE_ROWS) {
+    int orow[SLOTS];
+    float mx[SLOTS], lsum[SLOTS], acc[SLOTS][4];
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+      const int r = rb + i * LANE_ROWS + lane / GROUPS;
+      orow[i] = r < n_rows ? (it.q_start + r / G) * nh + it.kvh * G + r % G : -1;
+      mx[i] = -INFINITY;
+      lsum[i] = 0.f;
+      acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    }
+    for (int z0 = 0; z0 < it.parts; z0 += PP) {
+      float2 ml[SLOTS][PP];
+      float4 pv[SLOTS][PP];
+#pragma unroll
+      for (int i = 0; i < SLOTS; ++i)
+#pragma unroll
+        for (int u = 0; u < PP; ++u) {
+          const bool have = orow[i] >= 0 && z0 + u < it.parts;
+          const size_t at = (size_t)max(orow[i], 0) * max_parts + min(z0 + u, it.parts - 1);
+          ml[i][u] = have ? __ldcg(reinterpret_cast<const float2*>(part_ml + at * 2)) : make_float2(-INFINITY, 0.f);
+          pv[i][u] = have ? __ldcg(reinterpret_cast<const float4*>(part_acc + at * D + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int u = 0; u < PP; ++u)
+#pragma unroll
+        for (int i = 0; i < SLOTS; ++i) {
+          const float m_new = fmaxf(mx[i], ml[i][u].x);
+          const float sub = m_new == -INFINITY ? 0.f : m_new;      // (no key yet on either side: both weigh 0)
+          const float keep = td_exp2(mx[i] - sub), wgt = td_exp2(ml[i][u].x - sub);
+          lsum[i] = lsum[i] * keep + ml[i][u].y * wgt;
+          acc[i][0] = acc[i][0] * keep + pv[i][u].x * wgt;
+          acc[i][1] = acc[i][1] * keep + pv[i][u].y * wgt;
+          acc[i][2] = acc[i][2] * keep + pv[i][u].z * wgt;
+          acc[i][3] = acc[i][3] * keep + pv[i][u].w * wgt;
+          mx[i] = m_new;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i)
+      if (orow[i] >= 0) {
+        const float inv = lsum[i] > 0.f ? 1.0f / lsum[i] : 0.f;
+        uint2 ov;
+        ov.x = pack_bf16(acc[i][0] * inv, acc[i][1] * inv);
+        ov.y = pack_bf16(acc[i][2] * inv, acc[i][3] * inv);
+        *reinterpret_cast<uint2*>(out + (size_t)orow[i] * D + d) = ov;
+      }
+  }
+}
+
 // What the kernel needs to finish the q/k/v projection itself (ROPE variant): the raw product of the step's tokens,
 // the bias, the rotation tables and where each token's key and value go. Then no kernel stands between the
 // projection and the attention: the consumer warp adds the bias and rotates its query rows while it loads them
@@ -486,59 +546,10 @@ __global__ void __launch_bounds__(64) decode_attention_units_kernel(
         if (item < 7) td_stamp(stamps, 2 + 8 * item + 7);
         if (last) {
           __threadfence();
-          // A lane owns 4 columns of up to 8 rows at a time and takes the parts two by two: the loads of a pass
-          // (up to 32 a lane) are all asked for before the first is used, so a pass costs one trip to the L2.
-          constexpr int GROUPS = D / 4, LANE_ROWS = 32 / GROUPS;
-          const int d = (lane % GROUPS) * 4;
-          for (int rb = 0; rb < n_rows; rb += 8 * LANE_ROWS) {
-            int orow[8];
-            float mx[8], lsum[8], acc[8][4];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = rb + i * LANE_ROWS + lane / GROUPS;
-              orow[i] = r < n_rows ? (it.q_start + r / G) * nh + it.kvh * G + r % G : -1;
-              mx[i] = -INFINITY;
-              lsum[i] = 0.f;
-              acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-            }
-            for (int z0 = 0; z0 < it.parts; z0 += 2) {
-              float2 ml[8][2];
-              float4 pv[8][2];
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                  const bool have = orow[i] >= 0 && z0 + u < it.parts;
-                  const size_t at = (size_t)max(orow[i], 0) * max_parts + min(z0 + u, it.parts - 1);
-                  ml[i][u] = have ? __ldcg(reinterpret_cast<const float2*>(part_ml + at * 2)) : make_float2(-INFINITY, 0.f);
-                  pv[i][u] = have ? __ldcg(reinterpret_cast<const float4*>(part_acc + at * D + d))
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-              for (int u = 0; u < 2; ++u)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float m_new = fmaxf(mx[i], ml[i][u].x);
-                  const float sub = m_new == -INFINITY ? 0.f : m_new;      // (no key yet on either side: both weigh 0)
-                  const float keep = td_exp2(mx[i] - sub), wgt = td_exp2(ml[i][u].x - sub);
-                  lsum[i] = lsum[i] * keep + ml[i][u].y * wgt;
-                  acc[i][0] = acc[i][0] * keep + pv[i][u].x * wgt;
-                  acc[i][1] = acc[i][1] * keep + pv[i][u].y * wgt;
-                  acc[i][2] = acc[i][2] * keep + pv[i][u].z * wgt;
-                  acc[i][3] = acc[i][3] * keep + pv[i][u].w * wgt;
-                  mx[i] = m_new;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (orow[i] >= 0) {
-                const float inv = lsum[i] > 0.f ? 1.0f / lsum[i] : 0.f;
-                uint2 ov;
-                ov.x = pack_bf16(acc[i][0] * inv, acc[i][1] * inv);
-                ov.y = pack_bf16(acc[i][2] * inv, acc[i][3] * inv);
-                *reinterpret_cast<uint2*>(out + (size_t)orow[i] * D + d) = ov;
-              }
-          }
+          if ((n_rows + (32 / (D / 4)) - 1) / (32 / (D / 4)) <= 4)
+            td_merge_parts<D, 4, 4>(part_acc, part_ml, out, it, n_rows, G, nh, max_parts, lane);
+          else
+            td_merge_parts<D, 8, 2>(part_acc, part_ml, out, it, n_rows, G, nh, max_parts, lane);
           if (lane == 0) done[it.s * nkv + it.kvh] = 0;
         }
       }
