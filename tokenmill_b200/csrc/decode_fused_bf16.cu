@@ -1076,23 +1076,32 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
     fu_stamp(a, l * 16 + 4);
     if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
     fu_stamp(a, l * 16 + 5);
-    // C: output projection
-    fu_project<FU_ADD_RESID>(a, L, R, s_layers, t_o, R.no, R.ko, R.cpt_single, R.ch_q, a.H, a.nh * a.D, a.attn, stage_bar,
-                             n_staged & 1u, xs, rb_q, red, &s_ok);
-    if (R.no > 0) ++n_staged;
-    fu_stamp(a, l * 16 + 6);
-    if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
-    // D: norm + gate/up + SwiGLU
-    fu_norm_rows(a.T, a.H, nullptr, a.token_ids, nullptr, a.resid, L.ln2_w, a.eps2, xs, rb_h);
-    __syncthreads();
-    fu_stamp(a, l * 16 + 7);
-    fu_gate_up(a, R, s_layers, t_gu, l, xs, rb_h, &s_ok);
-    fu_stamp(a, l * 16 + 8);
-    if (!(ok = fu_grid_sync(a, k, &s_ok))) break;
-    // E: down projection
-    fu_project<FU_ADD_RESID>(a, L, R, s_layers, t_down, R.nd, R.kd, R.cpt_single, R.ch_i, a.H, a.I, a.act, stage_bar,
-                             n_staged & 1u, xs, rb_i, red, &s_ok, a.halves != 0);
-    if (R.nd > 0) n_staged += a.halves ? 2 : 1;
+    // C: output projection; then D: norm + gate/up + SwiGLU, and E: down projection. The two projections that add
+    // into the stream share ONE copy of their code (a loop of two that is not unrolled): the kernel's instructions
+    // (190 KB with a copy each) are more than a multiprocessor's instruction cache holds, every layer walks through
+    // all of them, and 24 KB less made every phase a little faster (29.9 -> 29.1 us a layer at batch 8).
+    bool left = false;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      if (which == 1) {
+        fu_norm_rows(a.T, a.H, nullptr, a.token_ids, nullptr, a.resid, L.ln2_w, a.eps2, xs, rb_h);
+        __syncthreads();
+        fu_stamp(a, l * 16 + 7);
+        fu_gate_up(a, R, s_layers, t_gu, l, xs, rb_h, &s_ok);
+        fu_stamp(a, l * 16 + 8);
+        if (!(ok = fu_grid_sync(a, k, &s_ok))) { left = true; break; }
+      }
+      const bool down = which == 1;
+      fu_project<FU_ADD_RESID>(a, L, R, s_layers, down ? t_down : t_o, down ? R.nd : R.no, down ? R.kd : R.ko, R.cpt_single,
+                               down ? R.ch_i : R.ch_q, a.H, down ? a.I : a.nh * a.D, down ? a.act : a.attn, stage_bar,
+                               n_staged & 1u, xs, down ? rb_i : rb_q, red, &s_ok, down && a.halves != 0);
+      if ((down ? R.nd : R.no) > 0) n_staged += (down && a.halves) ? 2 : 1;
+      if (!down) {
+        fu_stamp(a, l * 16 + 6);
+        if (!(ok = fu_grid_sync(a, k, &s_ok))) { left = true; break; }
+      }
+    }
+    if (left) break;
     if (threadIdx.x == 0) fu_overlay_issue(a, R, s_layers, l + 1);   // the staging area has been read: it is free again
     if (R.ov_base && l + 1 < a.n_layers) ov_issued = l + 2;
     fu_stamp(a, l * 16 + 9);
