@@ -702,6 +702,37 @@ def test_graph_decode_steps_in_flight_give_the_synchronous_loop_s_results(d64_di
         assert len(ids_s) == sp.max_tokens and -1 not in ids_a
 
 
+@pytest.mark.parametrize("variant", ["default", "units_off", "rope_kernel", "library_down", "own_o_and_gate_up"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_decode_steps_of_many_requests_against_plain_under_every_switch(wide_dir, variant, graphs, monkeypatch):
+    """Twenty requests decoding together at the Qwen2.5-0.5B layer sizes (more than the whole-step kernel takes):
+    captured graph or launch-by-launch, with the default kernels and with each switch turned the other way (the
+    decode attention by fixed splits; the rotation kernel between projection and attention; the library's down
+    projection; this repository's kernels for the output projection and gate/up too). Every logits row the
+    engine sampled from is compared with the plain implementation on the request's own history."""
+    from tokenmill_b200.kernels import ops
+    from tokenmill_b200.sampling import SamplingParams
+    if variant == "units_off":
+        monkeypatch.setattr(ops, "_DECODE_UNITS", False)
+    elif variant == "rope_kernel":
+        monkeypatch.setattr(ops, "_DECODE_ROPE", False)
+    elif variant == "library_down":
+        monkeypatch.setattr(ops, "_TC_ADD", False)
+    elif variant == "own_o_and_gate_up":
+        monkeypatch.setattr(ops, "_TC_ADD_ALL", True)
+    if not graphs:
+        monkeypatch.setenv("TOKENMILL_STEP_PROGRAM", "0")          # (every launch from Python: the parts' forward paths)
+    rng = random.Random(23)
+    vocab = json.loads((Path(wide_dir) / "config.json").read_text())["vocab_size"]
+    prompts = [[rng.randrange(vocab) for _ in range(rng.randrange(5, 150))] for _ in range(20)]
+    eng = engine_for(wide_dir, dtype="bfloat16", max_model_len=512, max_num_seqs=32, max_num_batched_tokens=2048,
+                     kv_cache_mb=64, cuda_graphs=graphs, cuda_graph_max_batch=32, async_decode=False)
+    outs, tap = generate_tapped(eng, prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    st = eng.runner.stats
+    assert st["graph_steps" if graphs else "steps"] >= 8
+    assert assert_logits_match_plain(wide_dir, prompts, outs, tap, "bfloat16") >= 20 * 12
+
+
 @pytest.mark.parametrize("dtype,n_graphs", [("bfloat16", 1), ("float32", 6)])
 def test_decode_graphs_captured_at_start_change_nothing_but_when(d64_dir, dtype, n_graphs):
     """``LLMEngine.capture_graphs()`` captures every decode graph before the first request (one graph of the
