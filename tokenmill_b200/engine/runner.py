@@ -34,6 +34,7 @@ from .batch import (Layout, StepEntry, build_step_inputs, collect_metadata, devi
 from .workspace import Workspace
 
 GRAPH_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64, 128, 256]
+FUSED_DECODE_LIMIT_BESIDE_GRAPHS = 10
 
 
 class ModelRunner:
@@ -74,6 +75,13 @@ class ModelRunner:
             self.fused = fused.FusedDecoder(model, self.layer_caches, max_model_len)
             if self.fused.max_tokens == 0:          # not even one token fits beside a ring stage at these sizes
                 self.fused = None
+        # Decode steps of up to this many requests take the whole-step kernel. Beside decode graphs the graph wins
+        # from 11 requests on (0.5B sizes: 9 / 10 / 12 / 16 requests 0.88 / 0.95 / 0.97 / 1.00 ms a step in the
+        # kernel, which takes 9 to 16 tokens in two passes, against 0.95 to 0.96 ms for any of them in the graph).
+        self._fused_decode_limit = 0
+        if self.fused is not None:
+            self._fused_decode_limit = min(self.fused.max_tokens, FUSED_DECODE_LIMIT_BESIDE_GRAPHS) \
+                if self.graph_max_batch >= self.fused.max_tokens else self.fused.max_tokens
         # The output matrix of those steps goes through this library's own streaming kernel, from a packed copy of
         # the matrix (as much memory again; hidden sizes up to 1024). It runs at the memory's read rate like the
         # library's kernel (52 against 50 us for 272 MB), and it finds the arg-max of greedy rows in its epilogue,
@@ -104,12 +112,14 @@ class ModelRunner:
         ops.tc_poll(self.device)
         if self.fused is not None:
             self.fused.check()
-            if len(entries) <= self.fused.max_tokens and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+            decoding = all(len(e.tokens) == 1 and e.want == [0] for e in entries)
+            if decoding and len(entries) <= self._fused_decode_limit:
                 self.stats["fused_steps"] += 1
                 hidden = self.fused.run_decode(entries, self.cache.page_size)
                 self.stats["h2d_bytes"] = self.fused.h2d_bytes
                 return self._decode_logits(hidden)
-            if sum(len(e.tokens) for e in entries) <= self.fused.max_tokens:
+            if sum(len(e.tokens) for e in entries) <= self.fused.max_tokens and \
+                    not (decoding and len(entries) <= self.graph_max_batch):
                 # A short prompt has more rows per kv head than an attention unit of the kernel holds: it goes in
                 # as several pieces of a few tokens each (same pages, consecutive starts). All keys and values of
                 # a layer are in the cache before its attention begins, so a piece sees the pieces before it.
@@ -181,7 +191,7 @@ class ModelRunner:
 
     def takes_greedy_steps(self, n_entries: int) -> bool:
         """Whether ``step_greedy`` takes a decode step of this many requests."""
-        return (self.fused is not None and self._packed_output is not None and 0 < n_entries <= self.fused.max_tokens
+        return (self.fused is not None and self._packed_output is not None and 0 < n_entries <= self._fused_decode_limit
                 and ops.lm_head_ok(n_entries, self.model.spec.hidden_size))
 
     @torch.inference_mode()
@@ -226,7 +236,7 @@ class ModelRunner:
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
         """Whether ``step_fed`` takes a decode step of this many requests: the whole-step kernel reads the ids
         itself, a captured graph has them gathered into its static input buffer."""
-        if self.fused is not None and 0 < n_entries <= self.fused.max_tokens:
+        if self.fused is not None and 0 < n_entries <= self._fused_decode_limit:
             return True
         if 0 < n_entries <= self.graph_max_batch:
             return True
@@ -244,7 +254,7 @@ class ModelRunner:
                 raise ValueError(f"a request would reach {e.start + 1} tokens; max_model_len is {self.max_model_len}")
         self.stats["steps"] += 1
         self.stats["tokens"] += len(entries)
-        if self.fused is None or len(entries) > self.fused.max_tokens:
+        if self.fused is None or len(entries) > self._fused_decode_limit:
             if len(entries) <= self.graph_max_batch:
                 return self._graph_step(entries, token_src, token_rows)
             return self._general_step(entries, token_src, token_rows)
@@ -270,7 +280,7 @@ class ModelRunner:
         if not self.graph_max_batch:
             return 0
         for bucket in sorted(self._graph_sizes(), reverse=True):        # the largest first: the others share its buffers
-            if self.fused is not None and bucket <= self.fused.max_tokens:
+            if self.fused is not None and bucket <= self._fused_decode_limit:
                 continue
             if bucket not in self._graphs:
                 self._graphs[bucket] = _DecodeGraph(self, bucket)
