@@ -626,6 +626,49 @@ def test_sampling_matches_the_plain_rules(V):
     assert again == [got[3], got[3], got[0]]
 
 
+@pytest.mark.parametrize("V,scale", [(151936, 0.5), (151936, 3.0), (151936, 12.0), (5000, 3.0), (33, 1.0)])
+def test_sampling_cuts_inside_and_outside_the_band_of_candidates(V, scale):
+    """Top-k and top-p over flat rows (the cut reaches far below the maximum: the kernel reads the whole row pass by
+    pass), ordinary and peaked rows (the cut lies among the few thousand tokens next to the maximum, which the
+    kernel copies to shared memory), with exact ties at the cut: whichever way the kernel takes, the token lies in
+    the kept set of the plain rules and the uniform number falls into its interval of the kept distribution."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(V + int(scale * 10))
+    ks = [0, 1, 2, 40, 1000, 5000, 0, 0, 40, 3, 0, 200]
+    ps = [0.9, 1.0, 0.5, 0.95, 0.999, 1.0, 0.1, 0.999, 0.2, 0.99, 0.5, 0.7]
+    n = len(ks)
+    logits = scale * torch.randn(n, V, generator=g)
+    top = logits.topk(min(V, 60), dim=-1).indices
+    for i in range(n):                                             # ties: the 3rd to 6th largest are equal, and a far run too
+        logits[i, top[i, 3:6]] = float(logits[i, top[i, 2]])
+        if V > 50:
+            logits[i, top[i, 45:50]] = float(logits[i, top[i, 44]])
+    temps = torch.tensor([1.0, 0.7, 1.3, 0.8] * 3)
+    top_k = torch.tensor([k if k < V else 0 for k in ks], dtype=torch.int32)
+    top_p = torch.tensor(ps)
+    for trial in range(3):
+        u = torch.rand(n, generator=g)
+        if trial == 0:
+            u[:] = 0.0
+        elif trial == 1:
+            u[:] = 0.9999999
+        got = ops.sample(logits.to(DEV), temps.to(DEV), top_k.to(DEV), top_p.to(DEV), u.to(DEV)).cpu().tolist()
+        for i in range(n):
+            probs = plain_filtered_probs(logits[i], float(temps[i]), int(top_k[i]), float(top_p[i]))
+            if probs[got[i]] == 0:
+                # The one difference from the plain rules, by design: tokens tied exactly at a cut value are all
+                # kept (a sort keeps as many of them as fit and drops the rest in no particular order).
+                assert float(logits[i, got[i]]) == float(logits[i][probs > 0].min()), \
+                    f"row {i}: token {got[i]} lies outside the kept set"
+                continue
+            tied = int((logits[i] == logits[i][probs > 0].min()).sum()) > int(((logits[i] == logits[i][probs > 0].min()) & (probs > 0)).sum())
+            if tied:
+                continue                                           # (the kept set is larger by the ties: other intervals)
+            cdf = probs.cumsum(0)
+            lo = float(cdf[got[i]] - probs[got[i]])
+            assert lo - 1e-5 <= float(u[i]) <= float(cdf[got[i]]) + 1e-5, (i, got[i], plain_inverse_cdf(probs, float(u[i])))
+
+
 def test_sampling_frequencies_follow_the_distribution():
     ops = _ops()
     logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]]).repeat(4000, 1)
