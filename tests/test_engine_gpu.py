@@ -733,6 +733,30 @@ def test_decode_steps_of_many_requests_against_plain_under_every_switch(wide_dir
     assert assert_logits_match_plain(wide_dir, prompts, outs, tap, "bfloat16") >= 20 * 12
 
 
+def test_long_contexts_move_small_decode_steps_from_the_whole_step_kernel_to_the_graph(d64_dir, monkeypatch):
+    """Beside decode graphs, four or more requests whose contexts add up to many keys decode in the graph (its
+    attention kernel streams long contexts faster), fewer keys or fewer requests in the whole-step kernel. With the
+    limit lowered to 150 keys, five short requests cross it while they decode: both paths run, and every logits
+    row agrees with the plain implementation."""
+    from tokenmill_b200.engine import runner as runner_mod
+    from tokenmill_b200.sampling import SamplingParams
+    monkeypatch.setattr(runner_mod, "FUSED_DECODE_MAX_KEYS_BESIDE_GRAPHS", 150)
+    rng = random.Random(31)
+    vocab = json.loads((Path(d64_dir) / "config.json").read_text())["vocab_size"]
+    prompts = [[rng.randrange(vocab) for _ in range(20)] for _ in range(5)]
+    eng = engine_for(d64_dir, dtype="bfloat16", max_num_seqs=16, cuda_graphs=True, cuda_graph_max_batch=16,
+                     async_decode=False, kv_cache_mb=16)
+    outs, tap = generate_tapped(eng, prompts, SamplingParams(max_tokens=24, ignore_eos=True))
+    st = eng.runner.stats
+    assert st["fused_steps"] >= 5 and st["graph_steps"] >= 5, st
+    assert assert_logits_match_plain(d64_dir, prompts, outs, tap, "bfloat16") >= 5 * 24
+    # three requests stay in the kernel however long they are
+    eng2 = engine_for(d64_dir, dtype="bfloat16", max_num_seqs=16, cuda_graphs=True, cuda_graph_max_batch=16,
+                      async_decode=False, kv_cache_mb=16)
+    generate_tapped(eng2, prompts[:3], SamplingParams(max_tokens=80, ignore_eos=True))
+    assert eng2.runner.stats["graph_steps"] == 0 and eng2.runner.stats["fused_steps"] >= 79
+
+
 @pytest.mark.parametrize("dtype,n_graphs", [("bfloat16", 1), ("float32", 6)])
 def test_decode_graphs_captured_at_start_change_nothing_but_when(d64_dir, dtype, n_graphs):
     """``LLMEngine.capture_graphs()`` captures every decode graph before the first request (one graph of the

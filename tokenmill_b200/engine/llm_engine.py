@@ -242,7 +242,7 @@ class LLMEngine:
             else:
                 entries.append(StepEntry(req.cache, [0], it.start, [0]))
                 rows.append(prev.row_of[id(req)])
-        if self.on_logits is None and all(r.params.greedy for r in reqs) and self.runner.takes_greedy_steps(len(entries)):
+        if self.on_logits is None and all(r.params.greedy for r in reqs) and self.runner.takes_greedy_steps(len(entries), entries):
             # Every request wants its most likely token and nobody looks at the logits: the output matrix's
             # kernel finds the arg-max itself and no logits are written.
             src = None if prev is None else prev.pending.dev

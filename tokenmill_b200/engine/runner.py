@@ -35,6 +35,7 @@ from .workspace import Workspace
 
 GRAPH_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64, 128, 256]
 FUSED_DECODE_LIMIT_BESIDE_GRAPHS = 10
+FUSED_DECODE_MAX_KEYS_BESIDE_GRAPHS = 72_000
 
 
 class ModelRunner:
@@ -113,7 +114,7 @@ class ModelRunner:
         if self.fused is not None:
             self.fused.check()
             decoding = all(len(e.tokens) == 1 and e.want == [0] for e in entries)
-            if decoding and len(entries) <= self._fused_decode_limit:
+            if decoding and self._fused_takes_decode(entries):
                 self.stats["fused_steps"] += 1
                 hidden = self.fused.run_decode(entries, self.cache.page_size)
                 self.stats["h2d_bytes"] = self.fused.h2d_bytes
@@ -189,10 +190,25 @@ class ModelRunner:
             return ops.lm_head(hidden, self._packed_output, self.model.spec.vocab_size, error=self.fused.error)
         return ops.linear(hidden, self.model.output_weight, out_dtype=torch.float32)
 
-    def takes_greedy_steps(self, n_entries: int) -> bool:
-        """Whether ``step_greedy`` takes a decode step of this many requests."""
-        return (self.fused is not None and self._packed_output is not None and 0 < n_entries <= self._fused_decode_limit
-                and ops.lm_head_ok(n_entries, self.model.spec.hidden_size))
+    def _fused_takes_decode(self, entries: list[StepEntry]) -> bool:
+        """Whether a decode step of these requests goes to the whole-step kernel. Beside decode graphs it does not
+        where four or more requests hold very long contexts: the kernel's attention phase copies keys with
+        16-byte loads by a unit's own warps (2.2 TB/s at best), the graph's attention kernel with tensor-map
+        copies (8 requests of 16,000 keys, 0.5B sizes: 1.52 ms a step in the kernel, 1.34 in the graph; they
+        meet at 8 x 8,000 keys; one to two requests stay faster in the kernel up to 32,000 keys and beyond)."""
+        n = len(entries)
+        if self.fused is None or not 0 < n <= self._fused_decode_limit:
+            return False
+        if self.graph_max_batch >= n >= 4 and self._fused_decode_limit < self.fused.max_tokens:
+            return sum(e.start + 1 for e in entries) <= FUSED_DECODE_MAX_KEYS_BESIDE_GRAPHS
+        return True
+
+    def takes_greedy_steps(self, n_entries: int, entries: list[StepEntry] | None = None) -> bool:
+        """Whether ``step_greedy`` takes a decode step of this many requests (of these requests, when given)."""
+        if not (self.fused is not None and self._packed_output is not None and 0 < n_entries <= self._fused_decode_limit
+                and ops.lm_head_ok(n_entries, self.model.spec.hidden_size)):
+            return False
+        return entries is None or self._fused_takes_decode(entries)
 
     @torch.inference_mode()
     def step_greedy(self, entries: list[StepEntry], out: torch.Tensor, token_src: torch.Tensor | None = None,
@@ -202,7 +218,7 @@ class ModelRunner:
         logits are written. With ``token_src`` the entries' tokens come from the device as in ``step_fed``. For
         steps the whole-step kernel takes (``takes_greedy_steps``)."""
         n = len(entries)
-        if not self.takes_greedy_steps(n) or any(len(e.tokens) != 1 for e in entries):
+        if not self.takes_greedy_steps(n, entries) or any(len(e.tokens) != 1 for e in entries):
             raise RuntimeError("this step cannot have its arg-max taken in the output matrix's epilogue")
         for e in entries:
             if e.start + 1 > self.max_model_len:
@@ -254,7 +270,7 @@ class ModelRunner:
                 raise ValueError(f"a request would reach {e.start + 1} tokens; max_model_len is {self.max_model_len}")
         self.stats["steps"] += 1
         self.stats["tokens"] += len(entries)
-        if self.fused is None or len(entries) > self._fused_decode_limit:
+        if not self._fused_takes_decode(entries):
             if len(entries) <= self.graph_max_batch:
                 return self._graph_step(entries, token_src, token_rows)
             return self._general_step(entries, token_src, token_rows)

@@ -109,7 +109,7 @@ def choose_chunk(q_lens: np.ndarray, starts: np.ndarray, group_size: int, kv_hea
 
 DECODE_STAGE_KEYS = 64          # keys of a stage of the decode kernel
 DECODE_MAX_UNIT_STAGES = 32     # most stages the kernel takes in one unit
-DECODE_MIN_PARTS = 16           # partial results a request may have at least (the scratch is sized by the cap)
+DECODE_MIN_PARTS = 64           # partial results a request may have at least (the scratch is sized by the cap)
 _UNIT_CANDIDATES = np.array([1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 20, 24, 28, 32], dtype=np.int64)
 
 
@@ -153,7 +153,7 @@ def decode_units(q_lens: np.ndarray, starts: np.ndarray, window: int, *, kv_head
     items = parts_c.sum(axis=1) * kv_heads
     longest = (-(-n[None, :] // parts_c)).max(axis=1)
     most = parts_c.max(axis=1)
-    merge_us = np.where(most > 1, 1.5 + 0.75 * most, 0.0)                           # the last unit counts and merges
+    merge_us = np.where(most > 1, 1.5 + (0.4 if head_dim <= 64 else 0.75) * most, 0.0)   # the last unit counts and merges
     cost = -(-items // slots) * (longest * stage_us + 3.0) + merge_us
     best_u = int(cand[len(cost) - 1 - int(np.argmin(cost[::-1]))])                  # (ties: the longer unit)
     parts = -(-n // best_u)
