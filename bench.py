@@ -153,14 +153,14 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead:
         h = cache.new_handle()
         cache.allocate(h, p)
         handles.append((h, p))
-    for lo in range(0, batch, 4):                               # prefill, four prompts a step
-        runner.step([StepEntry(h, p, 0, []) for h, p in handles[lo:lo + 4]])
+    together = 4 if PROMPT_LEN <= 4096 else 1                   # prefill, four prompts a step (long ones alone)
+    for lo in range(0, batch, together):
+        runner.step([StepEntry(h, p, 0, []) for h, p in handles[lo:lo + together]])
     length = PROMPT_LEN
     tok = [p[-1] for _, p in handles]
     # The timed steps lie in the middle of the NEW_TOKENS new tokens; the steps before them run untimed.
     forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup) if skip_ahead else 0
 
-    greedy = runner.takes_greedy_steps(batch)      # the arg-max comes out of the output matrix's own kernel
     chosen = torch.zeros(max(batch, 16), dtype=torch.int32, device=runner.device)
 
     def one():
@@ -168,7 +168,7 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead:
         for h, _ in handles:
             cache.grow(h, length + 1)
         entries = [StepEntry(h, [t], length, [0]) for (h, _), t in zip(handles, tok)]
-        if greedy:
+        if runner.takes_greedy_steps(batch, entries):   # the arg-max comes out of the output matrix's own kernel
             runner.step_greedy(entries, chosen)
         else:
             ops.argmax(runner.step(entries), out=chosen[:batch])
@@ -660,6 +660,7 @@ def run_reference(args) -> dict:
 
 
 def main() -> int:
+    global PROMPT_LEN, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -671,6 +672,8 @@ def main() -> int:
                          "'decode_attention[:<case>]' and print its time")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="profiling aid with --only decode_b<batch>: prompts of this many tokens instead of 512")
     ap.add_argument("--no-skip", action="store_true", help="profiling aid: time the decode steps right behind the prompt")
     ap.add_argument("--no-fp32", action="store_true", help="leave out the float32 engine's points")
     ap.add_argument("--workload", default="", choices=["", *WORKLOADS],
@@ -683,6 +686,11 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.sizes:
         use_sizes(args.sizes)
+    if args.prompt_len:
+        if not args.only.startswith("decode_b"):
+            print("bench.py: --prompt-len goes with --only decode_b<batch>")
+            return 2
+        PROMPT_LEN, CONTEXT = args.prompt_len, max(CONTEXT, args.prompt_len + NEW_TOKENS + 64)
     if args.workload:
         result = run_workload(args)
     else:

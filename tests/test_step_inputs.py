@@ -138,3 +138,24 @@ def test_decode_units_cover_every_stage_once_and_fill_the_slots():
     # the example of the docstring: two rounds, not three
     rec, n, _ = decode_units(np.ones(27, int), np.full(27, 4400), 0, kv_heads=4, slots=444, cap=16)
     assert n * 4 <= 2 * 444
+
+
+def test_the_whole_step_kernels_key_split_weighs_unit_length_against_the_merge():
+    """Keys per attention unit of the whole-step kernel: a multiple of 64 that keeps the blocks evenly loaded
+    (several rounds of short units may beat one round of long ones); one short request is not cut into 64-key units (their merge costs more than a
+    warp's second 16 keys would), and many requests get units long enough for one round."""
+    from types import SimpleNamespace
+    from tokenmill_b200.kernels.fused import SPLIT_KEYS, FusedDecoder
+    for D, nkv, n_sm in [(64, 2, 148), (128, 4, 148), (80, 3, 132)]:
+        me = SimpleNamespace(nkv=nkv, n_sm=n_sm, D=D, _split_cache={})
+        for n_seqs in (1, 2, 3, 8, 16):
+            for kv in (1, 63, 64, 65, 770, 2256, 4256, 8256, 16256, 32256, 131072):
+                split = FusedDecoder.split_for(me, n_seqs, kv)
+                assert split % SPLIT_KEYS == 0 and split >= SPLIT_KEYS
+                # the work of the slowest block stays within twice an even spread of 16-key rounds over the warps
+                units = n_seqs * nkv * -(-kv // split)
+                per_block = -(-units // n_sm) * -(-split // 128)
+                assert per_block <= 2 * max(1, -(-n_seqs * nkv * -(-kv // 64) // (2 * n_sm))) + 1, (n_seqs, kv, split)
+    me = SimpleNamespace(nkv=2, n_sm=148, D=64, _split_cache={})
+    assert FusedDecoder.split_for(me, 1, 770) == 128 and FusedDecoder.split_for(me, 1, 4256) in (128, 256)
+    assert FusedDecoder.split_for(me, 8, 770) == 128 and FusedDecoder.split_for(me, 8, 4256) == 512

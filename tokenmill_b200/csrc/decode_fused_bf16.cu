@@ -936,19 +936,30 @@ __device__ __forceinline__ void fu_attention(const FusedArgs& a, const FusedLaye
           // One pass in split order: the running maximum rescales what has been summed so far. The loads do
           // not depend on the running state, so several splits are in flight at a time.
           float mx = -INFINITY, lsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-          for (int zz = z0; zz <= z1; ++zz) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (orow * a.max_splits + zz) * 2));
-            const float4 pa = __ldcg(reinterpret_cast<const float4*>(a.part_acc + (orow * a.max_splits + zz) * D + d));
-            const float m_new = fmaxf(mx, ml.x);
-            const float keep = mx == -INFINITY ? 0.f : expf(mx - m_new);
-            const float w = ml.x == -INFINITY ? 0.f : expf(ml.x - m_new);
-            lsum = lsum * keep + ml.y * w;
-            acc[0] = acc[0] * keep + pa.x * w;
-            acc[1] = acc[1] * keep + pa.y * w;
-            acc[2] = acc[2] * keep + pa.z * w;
-            acc[3] = acc[3] * keep + pa.w * w;
-            mx = m_new;
+          for (int zb = z0; zb <= z1; zb += 8) {
+            // Eight splits' loads are in flight before the first is used (past the end: the last split again,
+            // left out of the sum).
+            float2 ml[8];
+            float4 pa[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int zz = min(zb + i, z1);
+              ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (orow * a.max_splits + zz) * 2));
+              pa[i] = __ldcg(reinterpret_cast<const float4*>(a.part_acc + (orow * a.max_splits + zz) * D + d));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (zb + i > z1) break;
+              const float m_new = fmaxf(mx, ml[i].x);
+              const float keep = mx == -INFINITY ? 0.f : expf(mx - m_new);
+              const float w = ml[i].x == -INFINITY ? 0.f : expf(ml[i].x - m_new);
+              lsum = lsum * keep + ml[i].y * w;
+              acc[0] = acc[0] * keep + pa[i].x * w;
+              acc[1] = acc[1] * keep + pa[i].y * w;
+              acc[2] = acc[2] * keep + pa[i].z * w;
+              acc[3] = acc[3] * keep + pa[i].w * w;
+              mx = m_new;
+            }
           }
           const float inv = 1.0f / lsum;
           uint2 ov;
