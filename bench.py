@@ -691,6 +691,8 @@ def main() -> int:
             print("bench.py: --prompt-len goes with --only decode_b<batch>")
             return 2
         PROMPT_LEN, CONTEXT = args.prompt_len, max(CONTEXT, args.prompt_len + NEW_TOKENS + 64)
+    if args.only == "prefill":
+        CONTEXT = max(CONTEXT, args.prefill_tokens + 64)
     if args.workload:
         result = run_workload(args)
     else:
