@@ -601,7 +601,7 @@ def test_argmax_lowest_index_on_ties(n, V):
     assert got.tolist() == logits.argmax(-1).tolist() and got[0] == V // 2
 
 
-@pytest.mark.parametrize("V", [7, 1000, 151936])
+@pytest.mark.parametrize("V", [7, 1000, 8195, 151936, 300000])
 def test_sampling_matches_the_plain_rules(V):
     ops = _ops()
     g = torch.Generator().manual_seed(V)
@@ -624,11 +624,19 @@ def test_sampling_matches_the_plain_rules(V):
     again = ops.sample(logits.to(DEV), temps[[3, 3, 0]].to(DEV), top_k[[3, 3, 0]].to(DEV), top_p[[3, 3, 0]].to(DEV),
                        u[[3, 3, 0]].to(DEV), rows=rows.to(DEV)).cpu().tolist()
     assert again == [got[3], got[3], got[0]]
+    # ... and lands where the row lies when asked to scatter; the other entries stay
+    out = torch.full((n,), -5, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), temps[[3, 0]].to(DEV), top_k[[3, 0]].to(DEV), top_p[[3, 0]].to(DEV), u[[3, 0]].to(DEV),
+               rows=torch.tensor([3, 0], dtype=torch.int32, device=DEV), out=out, scatter=True)
+    assert out.cpu().tolist() == [got[0], -5, -5, got[3]] + [-5] * (n - 4)
+    ops.tc_check(torch.device(DEV))                                # no block of a cluster gave up waiting
 
 
-@pytest.mark.parametrize("V,scale", [(151936, 0.5), (151936, 3.0), (151936, 12.0), (5000, 3.0), (33, 1.0)])
+@pytest.mark.parametrize("V,scale", [(151936, 0.5), (151936, 3.0), (151936, 12.0), (5000, 3.0), (33, 1.0),
+                                     (8192, 3.0), (20001, 12.0), (20001, 0.5)])
 def test_sampling_cuts_inside_and_outside_the_band_of_candidates(V, scale):
-    """Top-k and top-p over flat rows (the cut reaches far below the maximum: the kernel reads the whole row pass by
+    """(Rows of 8,192 logits and more are sampled by a cluster of eight blocks, narrower ones by one block.)
+    Top-k and top-p over flat rows (the cut reaches far below the maximum: the kernel reads the whole row pass by
     pass), ordinary and peaked rows (the cut lies among the few thousand tokens next to the maximum, which the
     kernel copies to shared memory), with exact ties at the cut: whichever way the kernel takes, the token lies in
     the kept set of the plain rules and the uniform number falls into its interval of the kept distribution."""

@@ -1,4 +1,5 @@
-// Token selection from 32-bit logits, one block per row.
+// Token selection from 32-bit logits: one block per row, and for rows of 8,192 logits and more a cluster of eight
+// blocks per row (sample_cluster_kernel, at the end of this file).
 //
 // Greedy: the index of the largest logit, the lowest index on ties (torch.argmax's rule, which the
 // reference uses: src/infer/sampling.py:30-33).
@@ -12,7 +13,8 @@
 // finds the two cut values by bisection on the float bit pattern, so tokens tied exactly at a cut
 // are all kept. The bisections run over the few thousand tokens next to the row's maximum, copied to
 // shared memory, whenever the cuts lie among them (sample_from_candidates: 0.12 to 0.15 ms a step at a
-// vocabulary of 152k), and over the whole row otherwise (1 to 1.7 ms).
+// vocabulary of 152k with one block per row, 0.03 to 0.05 ms with a cluster), and over the whole row otherwise
+// (1 to 1.7 ms with one block, 0.12 ms with a cluster, which keeps the row in shared memory).
 #include "common.cuh"
 
 namespace tmk {
@@ -194,80 +196,12 @@ __device__ __forceinline__ float sample_band(int b) {
   return b == 0 ? 1.f : b == 1 ? 2.f : b == 2 ? 3.f : b == 3 ? 4.f : b == 4 ? 6.f : b == 5 ? 8.f : b == 6 ? 12.f : 16.f;
 }
 
-__device__ bool sample_from_candidates(const float* __restrict__ row, int V, float inv_t, float mx, int k, float tp,
-                                       float u, float* redf, int* redi, int* token) {
-  __shared__ float cz[kCandidates];
-  __shared__ int ci[kCandidates];
-  __shared__ int band_count[32][kBands];
-  __shared__ float warp_mass[32];
-  __shared__ int s_band;
+// The cuts and the draw among candidates in shared memory: cz / ci hold the n_cand tokens with z >= v0 in index
+// order, all_mass the whole row's weight sum(exp(z - mx)). False when a cut lies below the candidates.
+__device__ bool sample_among_candidates(const float* cz, const int* ci, int n_cand, float v0, float mx, float all_mass,
+                                        int k, int V, float tp, float u, float* redf, int* redi, int* redi2,
+                                        int* token) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
-  const int span = (V + nwarp - 1) / nwarp;
-  const int begin = warp * span, end = min(V, begin + span);
-
-  // Pass 1: per warp span, how many tokens lie in each band, and the span's weight.
-  int cnt[kBands];
-#pragma unroll
-  for (int b = 0; b < kBands; ++b) cnt[b] = 0;
-  float mass = 0.f;
-  float floor_of[kBands];                                    // a band's tokens: z >= mx - width, compared as floats
-#pragma unroll
-  for (int b = 0; b < kBands; ++b) floor_of[b] = mx - sample_band(b);
-  for (int i = begin + lane; i < end; i += 32) {
-    const float zv = row[i] * inv_t;
-    mass += expf(zv - mx);
-#pragma unroll
-    for (int b = 0; b < kBands; ++b) cnt[b] += zv >= floor_of[b] ? 1 : 0;
-  }
-#pragma unroll
-  for (int b = 0; b < kBands; ++b) {
-    int c = cnt[b];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-    if (lane == 0) band_count[warp][b] = c;
-  }
-  mass = warp_sum(mass);
-  if (lane == 0) warp_mass[warp] = mass;
-  __syncthreads();
-  if (tid == 0) {
-    int chosen = -1;
-    for (int b = 0; b < kBands; ++b) {
-      int c = 0;
-      for (int w = 0; w < nwarp; ++w) c += band_count[w][b];
-      if (c <= kCandidates) chosen = b;
-    }
-    s_band = chosen;
-  }
-  __syncthreads();
-  const int band = s_band;
-  if (band < 0) return false;                                // more than kCandidates tokens within 1 of the maximum
-  const float v0 = mx - sample_band(band);                   // candidates: z >= v0 (the comparison the counts used)
-  float all_mass = 0.f;
-  int offset = 0, n_cand = 0;
-  for (int w = 0; w < nwarp; ++w) {
-    all_mass += warp_mass[w];
-    if (w < warp) offset += band_count[w][band];
-    n_cand += band_count[w][band];
-  }
-  // Pass 2: the band's tokens to shared memory, in index order.
-  for (int base = begin; base < end; base += 32) {
-    const int i = base + lane;
-    float zv = 0.f;
-    bool in = false;
-    if (i < end) {
-      zv = row[i] * inv_t;
-      in = zv >= v0;
-    }
-    const unsigned int ballot = __ballot_sync(0xffffffffu, in);
-    if (in) {
-      const int at = offset + __popc(ballot & ((1u << lane) - 1u));
-      cz[at] = zv;
-      ci[at] = i;
-    }
-    offset += __popc(ballot);
-  }
-  __syncthreads();
-
   // Top-k inside the band: the largest value v with count(z >= v) >= k.
   float cut = -INFINITY;
   if (k > 0 && k < V) {
@@ -358,20 +292,97 @@ __device__ bool sample_from_candidates(const float* __restrict__ row, int V, flo
   for (int o = 16; o > 0; o >>= 1) lastk = max(lastk, __shfl_xor_sync(0xffffffffu, lastk, o));
   if (lane == 0) {
     redi[warp] = best;
-    band_count[warp][0] = lastk;
+    redi2[warp] = lastk;
   }
   __syncthreads();
   if (tid == 0) {
     int b = 0x7fffffff, l = -1;
     for (int w = 0; w < nwarp; ++w) {
       b = min(b, redi[w]);
-      l = max(l, band_count[w][0]);
+      l = max(l, redi2[w]);
     }
     const int j = b != 0x7fffffff ? b : l;
     *token = j >= 0 ? ci[j] : -1;
   }
   __syncthreads();
   return true;
+}
+
+__device__ bool sample_from_candidates(const float* __restrict__ row, int V, float inv_t, float mx, int k, float tp,
+                                       float u, float* redf, int* redi, int* token) {
+  __shared__ float cz[kCandidates];
+  __shared__ int ci[kCandidates];
+  __shared__ int redi2[32];
+  __shared__ int band_count[32][kBands];
+  __shared__ float warp_mass[32];
+  __shared__ int s_band;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  const int span = (V + nwarp - 1) / nwarp;
+  const int begin = warp * span, end = min(V, begin + span);
+
+  // Pass 1: per warp span, how many tokens lie in each band, and the span's weight.
+  int cnt[kBands];
+#pragma unroll
+  for (int b = 0; b < kBands; ++b) cnt[b] = 0;
+  float mass = 0.f;
+  float floor_of[kBands];                                    // a band's tokens: z >= mx - width, compared as floats
+#pragma unroll
+  for (int b = 0; b < kBands; ++b) floor_of[b] = mx - sample_band(b);
+  for (int i = begin + lane; i < end; i += 32) {
+    const float zv = row[i] * inv_t;
+    mass += expf(zv - mx);
+#pragma unroll
+    for (int b = 0; b < kBands; ++b) cnt[b] += zv >= floor_of[b] ? 1 : 0;
+  }
+#pragma unroll
+  for (int b = 0; b < kBands; ++b) {
+    int c = cnt[b];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (lane == 0) band_count[warp][b] = c;
+  }
+  mass = warp_sum(mass);
+  if (lane == 0) warp_mass[warp] = mass;
+  __syncthreads();
+  if (tid == 0) {
+    int chosen = -1;
+    for (int b = 0; b < kBands; ++b) {
+      int c = 0;
+      for (int w = 0; w < nwarp; ++w) c += band_count[w][b];
+      if (c <= kCandidates) chosen = b;
+    }
+    s_band = chosen;
+  }
+  __syncthreads();
+  const int band = s_band;
+  if (band < 0) return false;                                // more than kCandidates tokens within 1 of the maximum
+  const float v0 = mx - sample_band(band);                   // candidates: z >= v0 (the comparison the counts used)
+  float all_mass = 0.f;
+  int offset = 0, n_cand = 0;
+  for (int w = 0; w < nwarp; ++w) {
+    all_mass += warp_mass[w];
+    if (w < warp) offset += band_count[w][band];
+    n_cand += band_count[w][band];
+  }
+  // Pass 2: the band's tokens to shared memory, in index order.
+  for (int base = begin; base < end; base += 32) {
+    const int i = base + lane;
+    float zv = 0.f;
+    bool in = false;
+    if (i < end) {
+      zv = row[i] * inv_t;
+      in = zv >= v0;
+    }
+    const unsigned int ballot = __ballot_sync(0xffffffffu, in);
+    if (in) {
+      const int at = offset + __popc(ballot & ((1u << lane) - 1u));
+      cz[at] = zv;
+      ci[at] = i;
+    }
+    offset += __popc(ballot);
+  }
+  __syncthreads();
+  return sample_among_candidates(cz, ci, n_cand, v0, mx, all_mass, k, V, tp, u, redf, redi, redi2, token);
 }
 
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
@@ -509,6 +520,385 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
   if (tid == 0) out[scatter && rows ? rows[rowi] : rowi] = s_token < 0 ? 0 : s_token;
 }
 
+
+// ---- A row over a cluster of blocks -------------------------------------------------------------------------
+// One block per row reads 600 KB alone at a vocabulary of 152k, once per pass. Here a cluster of eight blocks
+// takes a row: each block copies an eighth of it to its shared memory once (z = logit / T), every later pass runs
+// there, and what the blocks have to tell each other (the maximum, counts, sums) goes through distributed shared
+// memory: a block writes its few words into every block's table and arrives on every block's mbarrier; a block
+// goes on when all eight have arrived on its own. Sums are taken in thread order inside a block and in rank
+// order across blocks, so the result does not depend on timing. The rules are the ones above (same cuts, same
+// ties, same inverse-CDF walk in index order); candidates go to the first block's shared memory.
+// Every wait is bounded; a block that gives up raises the error word, and all blocks meet at the cluster's
+// hardware barrier before they leave, so none leaves while another may still write to it.
+constexpr int kClusterBlocks = 8;
+constexpr int kClusterThreads = 512;
+constexpr int kClusterWarps = kClusterThreads / 32;
+constexpr int kClusterVals = 12;             // 32-bit words a block hands to the others in one round
+constexpr uint32_t kClusterSpin = 1u << 22;
+constexpr int kClusterMinVocab = 8192;            // narrower rows stay with one block
+constexpr int kClusterMaxSliceBytes = 160 * 1024;  // a block's slice of a row (a vocabulary of up to 327k)
+
+__device__ __forceinline__ uint32_t sm_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {   // the same variable in another block
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_store(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+struct ClusterComm {
+  uint32_t bar;        // this block's two mbarriers (shared-memory address): rounds alternate between them
+  uint32_t table;      // this block's table [2][kClusterBlocks][kClusterVals] (shared-memory address)
+  const uint32_t* got; // the same table through a generic pointer
+  uint32_t* mine;      // [kClusterVals]: what this block hands out in the next round
+  uint32_t rank;
+  unsigned round;
+  int* error;
+};
+
+// One round: words mine[0 .. n) of every block land in row `rank` of every block's table; returns that table
+// (row r = block r's words) once all blocks have arrived, or null when the wait ran out (same answer in every
+// thread of the block). Two tables and two mbarriers alternate: a block can be one round ahead of another,
+// never two, so an arrival for the round after next cannot be counted with this round's.
+__device__ __forceinline__ const uint32_t* cluster_round(ClusterComm& c, int n) {
+  const int tid = threadIdx.x;
+  const unsigned b = c.round & 1u;
+  __syncthreads();                                           // mine[] is complete
+  if (tid < kClusterBlocks * n) {
+    const int dst = tid / n, idx = tid - dst * n;
+    cluster_store(cluster_addr(c.table + ((b * kClusterBlocks + c.rank) * kClusterVals + idx) * 4u, dst), c.mine[idx]);
+  }
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");       // (the candidates' stores of a round without words too)
+  __syncthreads();                                           // this block's stores come before its arrivals
+  const uint32_t bar = c.bar + b * 8u, parity = (c.round >> 1) & 1u;
+  if (tid < kClusterBlocks)
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr(bar, tid)) : "memory");
+  uint32_t spins = 0, done = 0;
+  while (!done) {
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (!done && ++spins > kClusterSpin) break;
+  }
+  const int bad = __syncthreads_or(done ? 0 : 1);
+  c.round += 1;
+  if (bad) {
+    if (tid == 0) atomicCAS(c.error, 0, 41);
+    return nullptr;
+  }
+  return c.got + (size_t)b * kClusterBlocks * kClusterVals;
+}
+
+// The token at which the running sum of kept weights (z >= cut), in index order over this block's slice, passes
+// `target`; `before` is the sum over the blocks in front. warp_tot: the kept weight of each warp's span (already
+// there). When the target lies beyond everything (u * total rounded up to the total) the last kept token.
+__device__ __forceinline__ void cluster_draw_in_block(const float* zs, int n, int index0, float cut, float mx,
+                                                      float target, float before, const float* warp_tot, int* s_token) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int span = (n + kClusterWarps - 1) / kClusterWarps;
+  const int begin = min(n, warp * span), end = min(n, begin + span);
+  int owner = -1;
+  float run0 = before;
+  for (int w = 0; w < kClusterWarps; ++w) {
+    if (target < run0 + warp_tot[w]) {
+      owner = w;
+      break;
+    }
+    run0 += warp_tot[w];
+  }
+  if (owner < 0) {
+    run0 = before;
+    for (int w = 0; w < kClusterWarps; ++w)
+      if (warp_tot[w] > 0.f) owner = w;
+    for (int w = 0; w < owner; ++w) run0 += warp_tot[w];
+  }
+  if (tid == 0) *s_token = -1;
+  __syncthreads();
+  if (warp == owner) {
+    float run = run0;
+    int found = -1, last_kept = -1;
+    for (int base = begin; base < end && found < 0; base += 32) {
+      const int j = base + lane;
+      float wgt = 0.f;
+      if (j < end) wgt = zs[j] >= cut ? expf(zs[j] - mx) : 0.f;
+      float incl = wgt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const unsigned int hit = __ballot_sync(0xffffffffu, wgt > 0.f && target < run + incl);
+      const unsigned int kept = __ballot_sync(0xffffffffu, wgt > 0.f);
+      if (kept) last_kept = base + (31 - __clz(kept));
+      if (hit) found = base + (__ffs(hit) - 1);
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) *s_token = index0 + (found >= 0 ? found : last_kept);
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void sample_cluster_body(ClusterComm& c, const float* zs, int n, int index0, int V, float mx_local,
+                                                    int k, float tp, float u, float* cz, int* ci, float* redf, int* redi,
+                                                    int* redi2, int (*band_count)[kBands], float* warp_tot,
+                                                    int* s_token, int* out_slot) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int span = (n + kClusterWarps - 1) / kClusterWarps;
+  const int begin = min(n, warp * span), end = min(n, begin + span);      // this warp's contiguous span of the slice
+  // The row's maximum.
+  if (tid == 0) c.mine[0] = __float_as_uint(mx_local);
+  const uint32_t* got = cluster_round(c, 1);
+  if (!got) return;
+  float mx = -INFINITY;
+  for (int r = 0; r < kClusterBlocks; ++r) mx = fmaxf(mx, __uint_as_float(got[r * kClusterVals]));
+
+  float cut = -INFINITY;
+  const bool has_k = k > 0 && k < V;
+  if (has_k || tp < 1.0f) {
+    // The candidates: counts per band and the weight of each warp's span; the blocks' sums go round.
+    int cnt[kBands];
+    float floor_of[kBands];
+#pragma unroll
+    for (int b = 0; b < kBands; ++b) {
+      cnt[b] = 0;
+      floor_of[b] = mx - sample_band(b);
+    }
+    float mass = 0.f;
+    for (int j = begin + lane; j < end; j += 32) {
+      const float zv = zs[j];
+      mass += expf(zv - mx);
+#pragma unroll
+      for (int b = 0; b < kBands; ++b) cnt[b] += zv >= floor_of[b] ? 1 : 0;
+    }
+#pragma unroll
+    for (int b = 0; b < kBands; ++b) {
+      int v = cnt[b];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) band_count[warp][b] = v;
+    }
+    mass = warp_sum(mass);
+    if (lane == 0) warp_tot[warp] = mass;
+    __syncthreads();
+    if (tid < kBands) {
+      int v = 0;
+      for (int w = 0; w < kClusterWarps; ++w) v += band_count[w][tid];
+      c.mine[tid] = (uint32_t)v;
+    }
+    if (tid == kBands) {
+      float m = 0.f;
+      for (int w = 0; w < kClusterWarps; ++w) m += warp_tot[w];
+      c.mine[kBands] = __float_as_uint(m);
+    }
+    got = cluster_round(c, kBands + 1);
+    if (!got) return;
+    int band = -1;
+    for (int b = 0; b < kBands; ++b) {
+      int v = 0;
+      for (int r = 0; r < kClusterBlocks; ++r) v += (int)got[r * kClusterVals + b];
+      if (v <= kCandidates) band = b;
+    }
+    if (band >= 0) {
+      float all_mass = 0.f;
+      int offset = 0, n_cand = 0;
+      for (int r = 0; r < kClusterBlocks; ++r) {
+        all_mass += __uint_as_float(got[r * kClusterVals + kBands]);
+        const int v = (int)got[r * kClusterVals + band];
+        if (r < (int)c.rank) offset += v;
+        n_cand += v;
+      }
+      for (int w = 0; w < warp; ++w) offset += band_count[w][band];
+      const float v0 = mx - sample_band(band);
+      // The band's tokens into the first block's shared memory, in index order.
+      const uint32_t cz0 = cluster_addr(sm_addr(cz), 0), ci0 = cluster_addr(sm_addr(ci), 0);
+      for (int base = begin; base < end; base += 32) {
+        const int j = base + lane;
+        float zv = 0.f;
+        bool in = false;
+        if (j < end) {
+          zv = zs[j];
+          in = zv >= v0;
+        }
+        const unsigned int ballot = __ballot_sync(0xffffffffu, in);
+        if (in) {
+          const int at = offset + __popc(ballot & ((1u << lane) - 1u));
+          cluster_store(cz0 + at * 4u, __float_as_uint(zv));
+          cluster_store(ci0 + at * 4u, (uint32_t)(index0 + j));
+        }
+        offset += __popc(ballot);
+      }
+      if (!cluster_round(c, 0)) return;                      // every block's candidates are in place
+      if (c.rank == 0) {
+        const bool done = sample_among_candidates(cz, ci, n_cand, v0, mx, all_mass, k, V, tp, u, redf, redi, redi2, s_token);
+        if (tid == 0) {
+          c.mine[0] = done ? 1u : 0u;
+          if (done) *out_slot = *s_token < 0 ? 0 : *s_token;
+        }
+      } else if (tid == 0) {
+        c.mine[0] = 0u;
+      }
+      got = cluster_round(c, 1);
+      if (!got) return;
+      if (got[0]) return;                                    // the first block has drawn
+    }
+    // A cut below the candidates: the bisections over the whole row, a round of the cluster per step.
+    if (has_k) {
+      unsigned int lo = float_order_bits(-INFINITY), hi = float_order_bits(mx);
+      while (lo < hi) {
+        const unsigned int mid = lo + ((hi - lo + 1u) >> 1);
+        const float v = order_bits_float(mid);
+        int cn = 0;
+        for (int j = tid; j < n; j += kClusterThreads) cn += zs[j] >= v ? 1 : 0;
+        cn = block_count(cn, redi);
+        if (tid == 0) c.mine[0] = (uint32_t)cn;
+        got = cluster_round(c, 1);
+        if (!got) return;
+        int all = 0;
+        for (int r = 0; r < kClusterBlocks; ++r) all += (int)got[r * kClusterVals];
+        if (all >= k) lo = mid; else hi = mid - 1u;
+      }
+      cut = order_bits_float(lo);
+    }
+    if (tp < 1.0f) {
+      auto mass_above = [&](float x, bool strictly) -> float {     // kept weight above x, over the whole row
+        float m = 0.f;
+        for (int j = tid; j < n; j += kClusterThreads) {
+          const float zv = zs[j];
+          m += ((strictly ? zv > x : true) && zv >= cut) ? expf(zv - mx) : 0.f;
+        }
+        m = block_total(m, redf);
+        if (tid == 0) c.mine[0] = __float_as_uint(m);
+        const uint32_t* g = cluster_round(c, 1);
+        if (!g) return -1.f;
+        float all = 0.f;
+        for (int r = 0; r < kClusterBlocks; ++r) all += __uint_as_float(g[r * kClusterVals]);
+        return all;
+      };
+      const float zk = mass_above(0.f, false);
+      if (zk < 0.f) return;
+      const float budget = tp * zk;
+      unsigned int lo = float_order_bits(cut), hi = float_order_bits(mx);   // predicate true at hi (mass 0)
+      while (lo < hi) {
+        const unsigned int mid = lo + ((hi - lo) >> 1);
+        const float m = mass_above(order_bits_float(mid), true);
+        if (m < 0.f) return;
+        if (m <= budget) hi = mid; else lo = mid + 1u;
+      }
+      cut = fmaxf(cut, order_bits_float(lo));
+    }
+  }
+
+  // The draw over the whole row: the kept weight of every warp's span, of every block, then the walk in the
+  // block the target falls into.
+  float part = 0.f;
+  for (int j = begin + lane; j < end; j += 32) part += zs[j] >= cut ? expf(zs[j] - mx) : 0.f;
+  part = warp_sum(part);
+  __syncthreads();
+  if (lane == 0) warp_tot[warp] = part;
+  __syncthreads();
+  if (tid == 0) {
+    float m = 0.f;
+    for (int w = 0; w < kClusterWarps; ++w) m += warp_tot[w];
+    c.mine[0] = __float_as_uint(m);
+  }
+  got = cluster_round(c, 1);
+  if (!got) return;
+  float total = 0.f;
+  for (int r = 0; r < kClusterBlocks; ++r) total += __uint_as_float(got[r * kClusterVals]);
+  const float target = u * total;
+  int owner = -1;
+  float before = 0.f;
+  for (int r = 0; r < kClusterBlocks; ++r) {
+    const float m = __uint_as_float(got[r * kClusterVals]);
+    if (target < before + m) {
+      owner = r;
+      break;
+    }
+    before += m;
+  }
+  if (owner < 0) {                                           // u * total rounded up to the total
+    before = 0.f;
+    for (int r = 0; r < kClusterBlocks; ++r)
+      if (__uint_as_float(got[r * kClusterVals]) > 0.f) owner = r;
+    for (int r = 0; r < owner; ++r) before += __uint_as_float(got[r * kClusterVals]);
+  }
+  if ((int)c.rank == owner) {
+    cluster_draw_in_block(zs, n, index0, cut, mx, target, before, warp_tot, s_token);
+    if (tid == 0) *out_slot = *s_token < 0 ? 0 : *s_token;
+  }
+}
+
+__global__ void __cluster_dims__(kClusterBlocks, 1, 1) __launch_bounds__(kClusterThreads) sample_cluster_kernel(
+    const float* __restrict__ logits, int V, long long row_stride, const float* __restrict__ temperature,
+    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
+    const int* __restrict__ rows, int* __restrict__ out, int scatter, int per, int vec, int* error) {
+  extern __shared__ __align__(16) float zs[];                // this block's slice of z = logit / T
+  __shared__ float cz[kCandidates];
+  __shared__ int ci[kCandidates];
+  __shared__ uint32_t table[2][kClusterBlocks][kClusterVals];
+  __shared__ uint32_t mine[kClusterVals];
+  __shared__ __align__(8) unsigned long long bar[2];
+  __shared__ float redf[32];
+  __shared__ int redi[32], redi2[32];
+  __shared__ int band_count[kClusterWarps][kBands];
+  __shared__ float warp_tot[kClusterWarps];
+  __shared__ int s_token;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster_rank();
+  const int rowi = blockIdx.x / kClusterBlocks;
+  const float* row = logits + (size_t)(rows ? rows[rowi] : rowi) * row_stride;
+  const float inv_t = 1.0f / temperature[rowi];
+  const int index0 = min(V, (int)rank * per), n = min(V, index0 + per) - index0;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sm_addr(&bar[0])), "r"(kClusterBlocks));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sm_addr(&bar[1])), "r"(kClusterBlocks));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // The slice, once, and its maximum.
+  float mx = -INFINITY;
+  if (vec) {
+    const float4* src = reinterpret_cast<const float4*>(row + index0);
+    for (int j = tid; j < n / 4; j += kClusterThreads) {
+      float4 v = __ldg(src + j);
+      v.x *= inv_t; v.y *= inv_t; v.z *= inv_t; v.w *= inv_t;
+      *reinterpret_cast<float4*>(zs + 4 * j) = v;
+      mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
+    for (int j = n / 4 * 4 + tid; j < n; j += kClusterThreads) {
+      const float v = row[index0 + j] * inv_t;
+      zs[j] = v;
+      mx = fmaxf(mx, v);
+    }
+  } else {
+    for (int j = tid; j < n; j += kClusterThreads) {
+      const float v = row[index0 + j] * inv_t;
+      zs[j] = v;
+      mx = fmaxf(mx, v);
+    }
+  }
+  mx = warp_max(mx);
+  if (lane == 0) redf[warp] = mx;
+  __syncthreads();
+  mx = -INFINITY;
+  for (int w = 0; w < kClusterWarps; ++w) mx = fmaxf(mx, redf[w]);
+  __syncthreads();
+  cluster_sync_all();                                        // every block's mbarrier is ready before anyone arrives on it
+  ClusterComm c{sm_addr(&bar[0]), sm_addr(&table[0][0][0]), &table[0][0][0], mine, rank, 0u, error};
+  sample_cluster_body(c, zs, n, index0, V, mx, top_k[rowi], top_p[rowi], uniform[rowi], cz, ci, redf, redi, redi2,
+                      band_count, warp_tot, &s_token, out + (scatter && rows ? rows[rowi] : rowi));
+  cluster_sync_all();                                        // nobody leaves while another may still write to it
+}
+
 }  // namespace tmk
 
 // How many chunks tm_argmax cuts a row of V logits into (scratch: n_rows * chunks floats and ints).
@@ -536,9 +926,25 @@ extern "C" int tm_argmax(const float* logits, int n_rows, int V, long long row_s
 // logits rows: draw i then lands in out[rows[i]] (the other entries stay as they are).
 extern "C" int tm_sample(const float* logits, int n_rows, int V, long long row_stride, const float* temperature,
                          const int* top_k, const float* top_p, const float* uniform, const int* rows, int* out,
-                         int scatter, cudaStream_t stream) {
+                         int scatter, int* error, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return TM_ERR_UNSUPPORTED_SHAPE;
+  // A wide row goes over a cluster of blocks, an eighth of it in each block's shared memory (`error`: the
+  // device word a block raises when its wait for the others runs out; without one the single-block kernel runs).
+  const int per = ((V + tmk::kClusterBlocks - 1) / tmk::kClusterBlocks + 3) / 4 * 4;
+  if (error && V >= tmk::kClusterMinVocab && per * (int)sizeof(float) <= tmk::kClusterMaxSliceBytes) {
+    static bool prepared = false;
+    if (!prepared) {
+      cudaError_t e = cudaFuncSetAttribute(tmk::sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           tmk::kClusterMaxSliceBytes);
+      if (e != cudaSuccess) return (int)e;
+      prepared = true;
+    }
+    const int vec = (reinterpret_cast<uintptr_t>(logits) % 16 == 0 && row_stride % 4 == 0) ? 1 : 0;
+    tmk::sample_cluster_kernel<<<n_rows * tmk::kClusterBlocks, tmk::kClusterThreads, per * sizeof(float), stream>>>(
+        logits, V, row_stride, temperature, top_k, top_p, uniform, rows, out, scatter, per, vec, error);
+    return tmk::launch_status();
+  }
   tmk::sample_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, temperature, top_k, top_p,
                                                               uniform, rows, out, scatter);
   return tmk::launch_status();

@@ -68,7 +68,7 @@ _SIGNATURES: dict[str, list] = {
     "tm_swiglu_partials": [_P, _I, _LL, _P, _I, _I, _P],
     "tm_gemm_f32_nt": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "tm_argmax": [_P, _I, _I, _LL, _P, _P, _P, _P],
-    "tm_sample": [_P, _I, _I, _LL, _P, _P, _P, _P, _P, _P, _I, _P],
+    "tm_sample": [_P, _I, _I, _LL, _P, _P, _P, _P, _P, _P, _I, _P, _P],
 }
 
 

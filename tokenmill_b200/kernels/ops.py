@@ -402,6 +402,11 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     return out
 
 
+# TOKENMILL_SAMPLE_CLUSTER=0: every row sampled by one block (else rows of 8,192 logits and more go over a cluster
+# of eight blocks, an eighth of the row in each block's shared memory).
+_SAMPLE_CLUSTER = os.environ.get("TOKENMILL_SAMPLE_CLUSTER", "1") != "0"
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            uniform: torch.Tensor, rows: torch.Tensor | None = None, out: torch.Tensor | None = None,
            scatter: bool = False) -> torch.Tensor:
@@ -419,7 +424,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     lib.call("tm_sample", logits.data_ptr(), n, V, logits.stride(0), _req(temperature, "temperature", torch.float32),
              _req(top_k, "top_k", torch.int32), _req(top_p, "top_p", torch.float32),
              _req(uniform, "uniform", torch.float32), _opt(rows, "rows", torch.int32),
-             _req(out, "out", torch.int32), int(bool(scatter and rows is not None)), _stream())
+             _req(out, "out", torch.int32), int(bool(scatter and rows is not None)),
+             _tc_flag(logits.device).data_ptr() if _SAMPLE_CLUSTER else None, _stream())
     return out
 
 
@@ -669,6 +675,9 @@ def tc_check(device: torch.device) -> None:
             if code in (33, 34):
                 raise lib.KernelError(f"decode attention gave up waiting for {'a stage of keys' if code == 33 else 'a free stage'}"
                                       f" (code {code}); its output is incomplete")
+            if code == 41:
+                raise lib.KernelError("sampling: a block of a row's cluster gave up waiting for the others; the "
+                                      "step's tokens are incomplete")
             if code == 31:
                 raise lib.KernelError("a token's position lies outside the position tables (the rotation was not "
                                       "applied as asked; the step's results are wrong)")
