@@ -193,13 +193,15 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead:
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launched, "mean_ctx": mean_ctx}
 
 
-def decode_end_to_end(engine, batch: int, steps: int, warmup: int) -> dict:
-    """K decode steps through LLMEngine.step: host token ids in, host token ids out, every step."""
+def decode_end_to_end(engine, batch: int, steps: int, warmup: int, sampled: bool = False) -> dict:
+    """K decode steps through LLMEngine.step: host token ids in, host token ids out, every step. ``sampled``:
+    temperature 0.8, top-k 40, top-p 0.95 with a seed per request instead of greedy choice."""
     import torch
     from tokenmill_b200.sampling import SamplingParams
 
     forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup)
-    sp = SamplingParams(max_tokens=forward + steps + warmup + 4, ignore_eos=True)
+    sp = SamplingParams(max_tokens=forward + steps + warmup + 4, ignore_eos=True,
+                        **(dict(temperature=0.8, top_k=40, top_p=0.95, seed=7) if sampled else {}))
     seqs = [engine.add_request(f"e2e-{batch}-{i}", p, sp) for i, p in enumerate(prompts(batch, PROMPT_LEN, seed=99))]
     while any(s.n_output == 0 for s in seqs):
         engine.step()
@@ -238,6 +240,34 @@ def prefill_timed(engine, tokens: int, reps: int = 5) -> dict:
             times.append(start.elapsed_time(end))
         cache.free(h)
     return {"ms": statistics.median(times)}
+
+
+def sampling_timed(vocab: int = 151936, reps: int = 20) -> list[dict]:
+    """Profiling aid (--only sampling): the sampling kernel alone over rows of `vocab` random logits (standard
+    deviation 3), 1, 8 and 64 rows, by kind of cut; us a launch, CUDA events around `reps` launches."""
+    import torch
+    from tokenmill_b200.kernels import ops
+    dev, out = torch.device("cuda:0"), []
+    kinds = {"temperature": (0, 1.0), "top_k 40": (40, 1.0), "top_p 0.9 (below the candidates)": (0, 0.9),
+             "top_k 40 + top_p 0.9": (40, 0.9)}
+    for n in (1, 8, 64):
+        logits = torch.randn(n, vocab, device=dev, generator=torch.Generator(device=dev).manual_seed(n)) * 3
+        for name, (k, p) in kinds.items():
+            temp, u = torch.full((n,), 0.8, device=dev), torch.rand(n, device=dev)
+            tk, tp = torch.full((n,), k, dtype=torch.int32, device=dev), torch.full((n,), p, device=dev)
+            res = torch.empty(n, dtype=torch.int32, device=dev)
+            for _ in range(3):
+                ops.sample(logits, temp, tk, tp, u, out=res)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(reps):
+                ops.sample(logits, temp, tk, tp, u, out=res)
+            b.record()
+            torch.cuda.synchronize()
+            out.append({"rows": n, "vocab": vocab, "kind": name, "us": round(a.elapsed_time(b) / reps * 1000, 1)})
+    ops.tc_check(dev)
+    return out
 
 
 def products_timed(tokens: int = 8) -> list[dict]:
@@ -405,6 +435,10 @@ def run_ours(args) -> dict:
         for row in products_timed():
             print(json.dumps(row))
         return {}
+    if args.only == "sampling":
+        for row in sampling_timed():
+            print(json.dumps(row))
+        return {}
     if args.only.startswith("decode_attention"):
         parts = args.only.split(":")
         cases = [parts[1]] if len(parts) > 1 and parts[1] else list(ATTENTION_CASES)
@@ -439,6 +473,7 @@ def run_ours(args) -> dict:
         b64 = decode_device_timed(engine, 64, side, args.warmup)
         e1 = decode_end_to_end(engine, 1, side, args.warmup)
         e64 = decode_end_to_end(engine, 64, side, args.warmup)
+        es8 = decode_end_to_end(engine, BATCH, side, args.warmup, sampled=True)
         pre = prefill_timed(engine, PREFILL_TOKENS)
         clocks = sampler.stop()
         if not args.no_fp32:
@@ -479,7 +514,8 @@ def run_ours(args) -> dict:
         "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1),
                    "decode_b1_ms": round(b1["ms_per_step"], 4), "decode_b64_ms": round(b64["ms_per_step"], 4),
                    "decode_b1_hbm_frac": hbm_frac(1, b1), "decode_b64_hbm_frac": hbm_frac(64, b64),
-                   "e2e_b1": round(e1["tok_s"], 1), "e2e_b64": round(e64["tok_s"], 1)},
+                   "e2e_b1": round(e1["tok_s"], 1), "e2e_b64": round(e64["tok_s"], 1),
+                   "e2e_b8_sampled": round(es8["tok_s"], 1)},     # temperature 0.8, top-k 40, top-p 0.95
         "clocks": clocks,
     }
     if fp32 is not None:
@@ -668,7 +704,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0 = all)")
     ap.add_argument("--sizes", default="", help="another named size (qwen2.5-1.5b, qwen2.5-7b) instead of Qwen2.5-0.5B")
-    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>', 'products' or "
+    ap.add_argument("--only", default="", help="profiling aid: run only 'prefill', 'decode_b<batch>', 'products', 'sampling' or "
                          "'decode_attention[:<case>]' and print its time")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: decode without CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
