@@ -253,3 +253,20 @@ def test_a_request_whose_last_token_is_still_on_the_device_is_not_admitted():
         a.output_ids[-1] = 11
         plan = sched.plan_step()
         assert [i.req.id for i in plan.items][0] == "a" and a.phase == Phase.RUNNING
+
+
+def test_a_requests_random_numbers_depend_on_its_seed_and_draw_count_only():
+    """The sampler's per-request stream: the array form the engine uses gives, bit for bit, the numbers of the
+    one-at-a-time form, whichever other requests share the call; numbers lie in [0, 1) and are exact in float32."""
+    import random
+    import numpy as np
+    from tokenmill_b200.sampling.sampler import uniform_for, uniforms_for
+    r = random.Random(3)
+    seeds = [r.getrandbits(62) for _ in range(500)] + [0, 1, (1 << 64) - 1, (1 << 70) + 5]
+    draws = [r.randrange(0, 100000) for _ in range(500)] + [0, 1, 2, 3]
+    one = np.array([uniform_for(s, d) for s, d in zip(seeds, draws)], dtype=np.float64)
+    many = uniforms_for(seeds, draws)
+    assert many.dtype == np.float32 and (many.astype(np.float64) == one).all()
+    assert (many >= 0).all() and (many < 1).all()
+    assert (uniforms_for(seeds[5:9], draws[5:9]) == many[5:9]).all()
+    assert len(set(one.tolist())) > 490                              # (not one number over and over)
