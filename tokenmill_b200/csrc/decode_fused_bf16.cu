@@ -1011,6 +1011,10 @@ __global__ void __launch_bounds__(kFuThreads, 1) decode_fused_kernel(const Fused
   uint32_t n_staged = 0;                      // uses of the staging barrier so far (its phase parity)
   int ov_issued = 0;                          // tiles asked for into the overlay stage so far
 
+  // (The kernel behind this one, when it was launched as a programmatic dependent, may be scheduled as soon as
+  // multiprocessors become free, and do what depends on nothing here, before this grid has drained: every block
+  // of this grid is resident by now, so nothing can get in its way.)
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     s_ok = 1;
     for (int s = 0; s < kFuMaxStages; ++s) s_issued[s] = 0;
