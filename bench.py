@@ -45,6 +45,7 @@ SIZES = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hid
              tie_word_embeddings=True, max_position_embeddings=32768)
 MODEL_LABEL = "Qwen2.5-0.5B"
 PROMPT_LEN, NEW_TOKENS, CONTEXT, BATCH, PREFILL_TOKENS, PAGE = 512, 512, 4096, 8, 2048, 16
+LONG_PROMPT = 3072      # the long-context decode point (prompt + new tokens stay within CONTEXT)
 
 
 def use_sizes(name: str) -> None:
@@ -141,22 +142,25 @@ def prompts(batch: int, length: int, seed: int = 0) -> list[list[int]]:
     return [[rng.randrange(1000, 150000) for _ in range(length)] for _ in range(batch)]
 
 
-def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead: bool = True) -> dict:
-    """K decode steps of the step function, CUDA events on the launching stream."""
+def decode_device_timed(engine, batch: int, steps: int, warmup: int, skip_ahead: bool = True,
+                        prompt_len: int = 0) -> dict:
+    """K decode steps of the step function, CUDA events on the launching stream (``prompt_len``: another prompt
+    length than the headline's)."""
     import torch
     from tokenmill_b200.engine.batch import StepEntry
     from tokenmill_b200.kernels import lib, ops
 
     runner, cache = engine.runner, engine.cache
+    prompt_len = prompt_len or PROMPT_LEN
     handles = []
-    for p in prompts(batch, PROMPT_LEN, seed=batch):
+    for p in prompts(batch, prompt_len, seed=batch):
         h = cache.new_handle()
         cache.allocate(h, p)
         handles.append((h, p))
-    together = 4 if PROMPT_LEN <= 4096 else 1                   # prefill, four prompts a step (long ones alone)
+    together = 4 if prompt_len <= 2048 else 1                   # prefill, four prompts a step (long ones alone)
     for lo in range(0, batch, together):
         runner.step([StepEntry(h, p, 0, []) for h, p in handles[lo:lo + together]])
-    length = PROMPT_LEN
+    length = prompt_len
     tok = [p[-1] for _, p in handles]
     # The timed steps lie in the middle of the NEW_TOKENS new tokens; the steps before them run untimed.
     forward = max(0, NEW_TOKENS // 2 - steps // 2 - warmup) if skip_ahead else 0
@@ -471,6 +475,7 @@ def run_ours(args) -> dict:
         side = max(16, args.steps // 2)
         b1 = decode_device_timed(engine, 1, side, args.warmup)
         b64 = decode_device_timed(engine, 64, side, args.warmup)
+        long8 = decode_device_timed(engine, BATCH, side, args.warmup, prompt_len=LONG_PROMPT)
         e1 = decode_end_to_end(engine, 1, side, args.warmup)
         e64 = decode_end_to_end(engine, 64, side, args.warmup)
         es8 = decode_end_to_end(engine, BATCH, side, args.warmup, sampled=True)
@@ -515,7 +520,10 @@ def run_ours(args) -> dict:
                    "decode_b1_ms": round(b1["ms_per_step"], 4), "decode_b64_ms": round(b64["ms_per_step"], 4),
                    "decode_b1_hbm_frac": hbm_frac(1, b1), "decode_b64_hbm_frac": hbm_frac(64, b64),
                    "e2e_b1": round(e1["tok_s"], 1), "e2e_b64": round(e64["tok_s"], 1),
-                   "e2e_b8_sampled": round(es8["tok_s"], 1)},     # temperature 0.8, top-k 40, top-p 0.95
+                   "e2e_b8_sampled": round(es8["tok_s"], 1),      # temperature 0.8, top-k 40, top-p 0.95
+                   # batch 8 behind prompts of LONG_PROMPT tokens (mean context LONG_PROMPT + 256)
+                   "decode_b8_long": round(long8["tok_s"], 1), "decode_b8_long_ms": round(long8["ms_per_step"], 4),
+                   "decode_b8_long_ctx": round(long8["mean_ctx"], 1), "decode_b8_long_hbm_frac": hbm_frac(BATCH, long8)},
         "clocks": clocks,
     }
     if fp32 is not None:

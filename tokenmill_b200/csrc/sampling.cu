@@ -943,7 +943,9 @@ extern "C" int tm_sample(const float* logits, int n_rows, int V, long long row_s
     const int vec = (reinterpret_cast<uintptr_t>(logits) % 16 == 0 && row_stride % 4 == 0) ? 1 : 0;
     tmk::sample_cluster_kernel<<<n_rows * tmk::kClusterBlocks, tmk::kClusterThreads, per * sizeof(float), stream>>>(
         logits, V, row_stride, temperature, top_k, top_p, uniform, rows, out, scatter, per, vec, error);
-    return tmk::launch_status();
+    if (cudaGetLastError() == cudaSuccess) return 0;
+    // (A device that cannot place the cluster refuses the launch; the rows then go to one block each. An error
+    // that is not about the launch shows again below.)
   }
   tmk::sample_kernel<<<n_rows, tmk::kSampleThreads, 0, stream>>>(logits, V, row_stride, temperature, top_k, top_p,
                                                               uniform, rows, out, scatter);
