@@ -159,3 +159,10 @@ def test_the_whole_step_kernels_key_split_weighs_unit_length_against_the_merge()
     me = SimpleNamespace(nkv=2, n_sm=148, D=64, _split_cache={})
     assert FusedDecoder.split_for(me, 1, 770) == 128 and FusedDecoder.split_for(me, 1, 4256) in (128, 256)
     assert FusedDecoder.split_for(me, 8, 770) == 128 and FusedDecoder.split_for(me, 8, 4256) == 512
+
+
+def test_small_steps_of_wide_heads_keep_the_fixed_key_split():
+    from tokenmill_b200.parts.attention_plan import decode_units_pay
+    assert not decode_units_pay(1, 2, 128) and not decode_units_pay(8, 2, 128) and not decode_units_pay(4, 4, 128)
+    assert decode_units_pay(9, 2, 128) and decode_units_pay(5, 4, 128)
+    assert decode_units_pay(1, 2, 64) and decode_units_pay(1, 1, 16)

@@ -26,7 +26,7 @@ import torch
 
 from ..kernels import ops
 from ..registry import get_part, register_mixer
-from .attention_plan import choose_chunk, decode_parts_cap, decode_units, packed_units, tiles_for
+from .attention_plan import choose_chunk, decode_parts_cap, decode_units, decode_units_pay, packed_units, tiles_for
 from .base import (LayerCache, PartMeta, PrefillUnits, StepInputs, StepMetadata, StepShape, part_limit_positions,
                    part_max_positions)
 from .spec import PagedKVNeed, PartSpec, StateNeed, WeightSpec
@@ -142,7 +142,7 @@ class GroupedQueryAttention:
         constant = True                           # (a graph replays q_lens of 1: nothing else depends on starts)
         if self.fast and max_q * G <= 16:
             host["path"] = "decode"
-            if ops.decode_units_ok(shape.page_size, self.D):
+            if ops.decode_units_ok(shape.page_size, self.D) and decode_units_pay(int(q_lens.size), self.nkv, self.D):
                 # The persistent kernel's list of units, made anew for every step (a captured graph has room for
                 # the most units its requests can have, and is told at each replay how many there are).
                 S = int(q_lens.size)
