@@ -252,6 +252,10 @@ __device__ __noinline__ void fu_norm_rows(int T, int H, const __nv_bfloat16* emb
         store4<__nv_bfloat16>(dst + g * 4, y);
       }
     }
+    // The columns between H and the end of the last 32-wide chunk are multiplied too (by the packed matrices'
+    // zero padding): they must hold zeros, not what an earlier phase left there (a NaN pattern times zero is NaN).
+    const int kpad = (H + 31) / 32 * 32;
+    if (lane < (kpad - H) / 8) *reinterpret_cast<uint4*>(dst + H + lane * 8) = make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
