@@ -899,3 +899,31 @@ def test_short_prompts_go_through_the_whole_step_kernel_in_pieces(d64_dir, tmp_p
     outputs = run_trace(d64_dir, "bfloat16", steps, 512, tmp_path / "o")
     check_against_plain(steps, outputs, reqs, plain_for(d64_dir, reqs, plain_cache), "bfloat16")
     assert calls.count("tm_decode_fused") == 5 and "tm_program_run" not in calls
+
+
+@pytest.mark.parametrize("shape", [(128, 1, 5, 432, 344, 1), (128, 4, 7, 488, 1312, 3), (64, 2, 1, 640, 1632, 2),
+                                   (64, 3, 5, 280, 696, 2), (32, 4, 2, 216, 616, 2)],
+                         ids=lambda s: "d%d_kv%d_g%d_h%d" % s[:4])
+def test_scheduling_options_over_shapes_no_named_model_has(shape, tmp_path):
+    """Head sizes, groupings and widths (no multiples of 32 among them) that the named models do not have, through
+    ``LLMEngine`` with its options one after the other (plain; decode graphs; chunked prompts under a budget of 64
+    tokens; prefix caching with graphs at another page size; a pool so small that requests are evicted): the
+    logits behind every generated token against the plain implementation on the request's own history."""
+    from tokenmill_b200.weights import qwen2_config, write_random_model
+    D, nkv, G, H, I, L = shape
+    cfg = qwen2_config(vocab_size=1013, hidden_size=H, intermediate_size=I, num_hidden_layers=L, num_attention_heads=nkv * G,
+                       num_key_value_heads=nkv, head_dim=D, rope_theta=50000.0, rms_norm_eps=1e-6,
+                       tie_word_embeddings=bool(L % 2), max_position_embeddings=1024)
+    folder = write_random_model(tmp_path / "model", cfg, seed=H)
+    rng = random.Random(H)
+    prompts = prompts_for(folder, [rng.randrange(1, 150) for _ in range(14)])
+    small_pool = 700 * L * 2 * nkv * D * 2 / 2 ** 20                   # room for 700 tokens: 14 requests need about 1,400
+    for kw in (dict(), dict(cuda_graphs=True, cuda_graph_max_batch=16),
+               dict(enable_chunked_prefill=True, max_num_batched_tokens=64),
+               dict(enable_prefix_caching=True, cuda_graphs=True, cuda_graph_max_batch=8, block_size=32),
+               dict(kv_cache_mb=small_pool, enable_chunked_prefill=True, max_num_batched_tokens=96)):
+        eng = engine_for(folder, "bfloat16", **kw)
+        outs, tap = generate_tapped(eng, prompts, greedy(24))
+        assert assert_logits_match_plain(folder, prompts, outs, tap, "bfloat16") >= 14 * 24
+        if "kv_cache_mb" in kw:
+            assert eng.scheduler.evictions > 0 and eng.cache.all_free
