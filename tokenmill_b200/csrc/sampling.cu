@@ -196,24 +196,84 @@ __device__ __forceinline__ float sample_band(int b) {
   return b == 0 ? 1.f : b == 1 ? 2.f : b == 2 ? 3.f : b == 3 ? 4.f : b == 4 ? 6.f : b == 5 ? 8.f : b == 6 ? 12.f : 16.f;
 }
 
+// Three block-wide sums at once, each taken exactly as block_sum takes one (so a sum does not depend on what it
+// shares the pass with). `red` holds 3 x 32 floats.
+__device__ __forceinline__ void block_sum3(float (&v)[3], float (*red)[32]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int j = 0; j < 3; ++j) v[j] = warp_sum(v[j]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) red[j][warp] = v[j];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    float total = 0.f;
+    for (int w = 0; w < nwarp; ++w) total += red[j][w];
+    v[j] = total;
+  }
+}
+
+// Three block-wide counts of at most 2^20 each, packed into one 64-bit sum.
+__device__ __forceinline__ void block_count3(int (&c)[3], unsigned long long* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  unsigned long long v = (unsigned long long)c[0] | ((unsigned long long)c[1] << 21) | ((unsigned long long)c[2] << 42);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  unsigned long long total = 0;
+  for (int w = 0; w < nwarp; ++w) total += red[w];
+  c[0] = (int)(total & 0x1fffffull);
+  c[1] = (int)((total >> 21) & 0x1fffffull);
+  c[2] = (int)((total >> 42) & 0x1fffffull);
+}
+
 // The cuts and the draw among candidates in shared memory: cz / ci hold the n_cand tokens with z >= v0 in index
 // order, all_mass the whole row's weight sum(exp(z - mx)). False when a cut lies below the candidates.
 __device__ bool sample_among_candidates(const float* cz, const int* ci, int n_cand, float v0, float mx, float all_mass,
                                         int k, int V, float tp, float u, float* redf, int* redi, int* redi2,
                                         int* token) {
+  __shared__ float red3[3][32];
+  __shared__ unsigned long long red64[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
   // Top-k inside the band: the largest value v with count(z >= v) >= k.
   float cut = -INFINITY;
   if (k > 0 && k < V) {
     if (k > n_cand) return false;                            // the k-th token lies below the band
     unsigned int lo = float_order_bits(v0), hi = float_order_bits(mx);     // count(z >= v0) = n_cand >= k: the invariant
+    // Three probes a pass cut the range in four (12 to 16 passes where halving takes 31): the counts are
+    // monotone, so the largest probe that still has k tokens at or above it is the new lower end.
     while (lo < hi) {
-      const unsigned int mid = lo + ((hi - lo + 1u) >> 1);
-      const float v = order_bits_float(mid);
-      int c = 0;
-      for (int j = tid; j < n_cand; j += blockDim.x) c += cz[j] >= v ? 1 : 0;
-      c = block_count(c, redi);
-      if (c >= k) lo = mid; else hi = mid - 1u;
+      const unsigned long long span = hi - lo;
+      unsigned int m[3];
+      float v[3];
+      int c[3] = {0, 0, 0};
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        m[q] = lo + (unsigned int)((span * (q + 1) + 3ull) / 4ull);          // lo < m[0] <= m[1] <= m[2] <= hi
+        v[q] = order_bits_float(m[q]);
+      }
+      for (int j = tid; j < n_cand; j += blockDim.x) {
+        const float zv = cz[j];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) c[q] += zv >= v[q] ? 1 : 0;
+      }
+      block_count3(c, red64);
+      if (c[2] >= k) {
+        lo = m[2];
+      } else if (c[1] >= k) {
+        lo = m[1];
+        hi = m[2] - 1u;
+      } else if (c[0] >= k) {
+        lo = m[0];
+        hi = m[1] - 1u;
+      } else {
+        hi = m[0] - 1u;
+      }
     }
     cut = order_bits_float(lo);
   }
@@ -236,13 +296,35 @@ __device__ bool sample_among_candidates(const float* cz, const int* ci, int n_ca
       // (the cut itself is the answer: every token the top-k kept stays)
     } else {
       unsigned int lo = float_order_bits(floor_x), hi = float_order_bits(mx);   // predicate true at hi (mass 0)
+      // Three probes a pass here too: the mass above a value falls as the value rises, so the smallest probe
+      // whose mass fits the budget is the new upper end. (Each mass is summed as a pass of its own would.)
       while (lo < hi) {
-        const unsigned int mid = lo + ((hi - lo) >> 1);
-        const float x = order_bits_float(mid);
-        float m = 0.f;
-        for (int j = tid; j < n_cand; j += blockDim.x) m += (cz[j] > x && cz[j] >= cut) ? expf(cz[j] - mx) : 0.f;
-        m = block_total(m, redf);
-        if (m <= budget) hi = mid; else lo = mid + 1u;
+        const unsigned long long span = hi - lo;
+        unsigned int p[3];
+        float x[3], m[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          p[q] = lo + (unsigned int)(span * (q + 1) / 4ull);                  // lo <= p[0] <= p[1] <= p[2] < hi
+          x[q] = order_bits_float(p[q]);
+        }
+        for (int j = tid; j < n_cand; j += blockDim.x) {
+          const float zv = cz[j];
+          const float wgt = zv >= cut ? expf(zv - mx) : 0.f;
+#pragma unroll
+          for (int q = 0; q < 3; ++q) m[q] += zv > x[q] ? wgt : 0.f;
+        }
+        block_sum3(m, red3);
+        if (m[0] <= budget) {
+          hi = p[0];
+        } else if (m[1] <= budget) {
+          lo = p[0] + 1u;
+          hi = p[1];
+        } else if (m[2] <= budget) {
+          lo = p[1] + 1u;
+          hi = p[2];
+        } else {
+          lo = p[2] + 1u;
+        }
       }
       cut = fmaxf(cut, order_bits_float(lo));
     }
