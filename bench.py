@@ -11,8 +11,13 @@ kernel, the output matrix and the arg-max kernel per step); ``e2e`` is the same 
 entry point (``LLMEngine.step``: scheduler, pinned host-to-device metadata copy, kernels, sampling, token ids
 read back to the host every step), timed on the host between two device synchronisations. ``prefill`` times
 one 2,048-token prompt; ``roofline`` relates the decode step to the memory bandwidth it needs (every weight
-once plus the live requests' cache); ``points`` holds decode at batch 1 and 64 (device-timed and end to end);
-``fp32`` the float32 engine's decode step at batch 8 and its 2,048-token prompt.
+once plus the live requests' cache); ``points`` holds decode at batch 1 and 64 (device-timed and end to end),
+batch 8 end to end with sampled requests (temperature 0.8, top-k 40, top-p 0.95) and batch 8 behind prompts of
+3,072 tokens; ``fp32`` the float32 engine's decode step at batch 8 and its 2,048-token prompt.
+
+Profiling aids that print their own lines instead of the contract's: ``--only prefill | decode_b<batch> |
+products | sampling | decode_attention[:<case>]``, with ``--prompt-len N`` (decode behind prompts of N tokens),
+``--prefill-tokens N``, ``--layers L``, ``--sizes qwen2.5-1.5b | qwen2.5-7b``, ``--no-graphs``.
 
 ``--workload`` runs one of the two other workloads the baseline names, through ``LLMEngine`` with every
 request submitted at once and stepped to completion (the reference's bench/common.py:58-76 method), and prints
