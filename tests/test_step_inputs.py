@@ -162,7 +162,10 @@ def test_the_whole_step_kernels_key_split_weighs_unit_length_against_the_merge()
 
 
 def test_small_steps_of_wide_heads_keep_the_fixed_key_split():
+    """... outside captured graphs and at short contexts only: a graph serves every context with one kernel."""
     from tokenmill_b200.parts.attention_plan import decode_units_pay
-    assert not decode_units_pay(1, 2, 128) and not decode_units_pay(8, 2, 128) and not decode_units_pay(4, 4, 128)
-    assert decode_units_pay(9, 2, 128) and decode_units_pay(5, 4, 128)
-    assert decode_units_pay(1, 2, 64) and decode_units_pay(1, 1, 16)
+    assert not decode_units_pay(1, 2, 128, 800, False) and not decode_units_pay(8, 2, 128, 1024, False)
+    assert not decode_units_pay(4, 4, 128, 64, False)
+    assert decode_units_pay(9, 2, 128, 800, False) and decode_units_pay(5, 4, 128, 800, False)
+    assert decode_units_pay(1, 2, 128, 1025, False) and decode_units_pay(1, 2, 128, 800, True)
+    assert decode_units_pay(1, 2, 64, 100, False) and decode_units_pay(1, 1, 16, 100, False)

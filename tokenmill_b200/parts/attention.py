@@ -142,7 +142,8 @@ class GroupedQueryAttention:
         constant = True                           # (a graph replays q_lens of 1: nothing else depends on starts)
         if self.fast and max_q * G <= 16:
             host["path"] = "decode"
-            if ops.decode_units_ok(shape.page_size, self.D) and decode_units_pay(int(q_lens.size), self.nkv, self.D):
+            if ops.decode_units_ok(shape.page_size, self.D) and decode_units_pay(int(q_lens.size), self.nkv, self.D,
+                                                                                    int(shape.max_kv_len), shape.for_graph):
                 # The persistent kernel's list of units, made anew for every step (a captured graph has room for
                 # the most units its requests can have, and is told at each replay how many there are).
                 S = int(q_lens.size)

@@ -113,18 +113,17 @@ DECODE_MIN_PARTS = 64           # partial results a request may have at least (t
 _UNIT_CANDIDATES = np.array([1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 20, 24, 28, 32], dtype=np.int64)
 
 
-def decode_units_pay(n_seqs: int, kv_heads: int, head_dim: int) -> bool:
-    """Whether a decode step of this many requests goes to the unit-driven kernel. Not with heads of 128 and at
-    most 16 (request, kv head) pairs: a unit's one consumer warp takes 2 us a stage of 64 keys there and the merge
-    0.75 us a part, and the kernel with one block of four warps per fixed key split is ahead. Measured with the
-    unit-driven kernel switched off altogether against on (1.5B sizes, context 768, decode graphs): 1 / 2 / 4
-    requests 1.48 / 1.45 / 1.45 ms a step against 1.54 / 1.52 / 1.55; 8 requests 1.49 either way; 16 requests 1.57
-    against 1.55; 7B sizes, 8 layers: 1 / 2 / 4 requests 1.16 / 1.19 / 1.15 against 1.22 / 1.25 / 1.17. With this
-    rule the small graphs take 1.51 / 1.52 ms at 1 / 4 requests: about half of the difference. The other half is
-    not the kernel: with a graph of 64 rows holding the unit-driven kernel in the same process, the graph of 4
-    rows replays in 1.52 ms, with largest graphs of 16 or 32 rows in 1.45 ms (the same kernels with the same
-    durations when timed one by one; the cause is not known)."""
-    return not (head_dim >= 128 and n_seqs * kv_heads <= 16)
+def decode_units_pay(n_seqs: int, kv_heads: int, head_dim: int, max_kv_len: int, for_graph: bool) -> bool:
+    """Whether a decode step of this many requests goes to the unit-driven kernel. Not with heads of 128, at most
+    16 (request, kv head) pairs and contexts of at most 1,024 keys: a unit's one consumer warp takes 2 us a stage
+    of 64 keys there and the merge 0.75 us a part, and the kernel with one block of four warps per fixed key split
+    is ahead. Measured with the unit-driven kernel switched off altogether against on (1.5B sizes, context 768):
+    1 / 2 / 4 requests 1.48 / 1.45 / 1.45 ms a step against 1.54 / 1.52 / 1.55; 8 requests 1.49 either way; 16
+    requests 1.57 against 1.55; 7B sizes, 8 layers: 1 / 2 / 4 requests 1.16 / 1.19 / 1.15 against 1.22 / 1.25 /
+    1.17. At context 3,328 it is the other way round (1.5B sizes, 4 / 8 requests: 1.75 / 1.82 ms by splits, 1.65 /
+    1.70 by units), and a captured graph serves every context with the kernel it was captured with: graphs
+    therefore always take the unit-driven kernel, and this rule is for steps outside graphs."""
+    return for_graph or not (head_dim >= 128 and n_seqs * kv_heads <= 16 and max_kv_len <= 1024)
 
 
 def decode_parts_cap(max_kv_len: int) -> int:
